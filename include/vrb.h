@@ -1,0 +1,240 @@
+/*
+ * vrb.h -- C ABI of the B200 (sm_100a) non-GEMM operator library for the vrhino runtime.
+ *
+ * This is the boundary a vrhino::Backend implementation binds to: every entry point takes
+ * raw DEVICE pointers, sizes and a CUDA stream, allocates nothing, launches asynchronously
+ * on the given stream and returns 0 or a negative vrb_status (text via vrb_last_error()).
+ * The *_host entry points at the end take HOST pointers instead and stage through device
+ * buffers the library owns.
+ *
+ * Each declaration cites the reference interface it replaces; paths are inside the
+ * reference project and, when no file is named, mean
+ * native/src/backend/cuda/cuda_backend.cu.
+ *
+ * Dtype codes are the reference's DType enumerators (native/include/vrhino/tensor.h:13).
+ * All tensors are dense and contiguous (the reference has no strided tensors).
+ */
+#ifndef VRB_H_
+#define VRB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VRB_ABI_VERSION 1
+
+typedef enum vrb_dtype { VRB_F32 = 0, VRB_BF16 = 2, VRB_U8 = 5 } vrb_dtype;
+
+typedef enum vrb_status {
+    VRB_OK = 0,
+    VRB_ERR_INVALID = -1,     /* null pointer, non-positive extent, bad enum, illegal broadcast */
+    VRB_ERR_UNSUPPORTED = -2, /* dtype / layout combination the reference also rejects */
+    VRB_ERR_CUDA = -3,        /* a CUDA runtime call failed; text names it */
+    VRB_ERR_WORKSPACE = -4    /* caller's scratch buffer is too small or misaligned */
+} vrb_status;
+
+/* enum Activation, native/include/vrhino/backend.h:14 */
+typedef enum vrb_activation_kind {
+    VRB_SILU = 0, VRB_GELU = 1, VRB_GELU_TANH = 2, VRB_TANH = 3, VRB_RELU = 4
+} vrb_activation_kind;
+
+/* binary<Kind>, :3871-3902 */
+typedef enum vrb_binary_kind { VRB_ADD = 0, VRB_MUL = 1, VRB_DIV = 2, VRB_MAX = 3 } vrb_binary_kind;
+
+/* QuantType, native/include/vrhino/tensor.h:35 (order of dequantize_kernel<T,Kind>, :641) */
+typedef enum vrb_quant_kind { VRB_Q_FP8_E4M3FN = 0, VRB_Q_INT8 = 1, VRB_Q_INT4 = 2 } vrb_quant_kind;
+
+typedef void* vrb_stream; /* cudaStream_t; NULL = the legacy default stream the reference uses */
+
+int vrb_abi_version(void);
+/* Text of the calling thread's most recent failure ("" if none). */
+const char* vrb_last_error(void);
+/* Number of kernels this library has launched in the process (all threads, all streams). */
+uint64_t vrb_launch_count(void);
+
+/* ------------------------------------------------------------------ per-operator forms -- */
+
+/* CudaBackend::add/mul/div/maximum (:3871-3902) on operands already in `dtype`.
+ * Shapes broadcast right-aligned, rank <= 8 (:525); out has the broadcast shape. */
+int vrb_binary(int kind, const void* a, const int64_t* a_shape, int a_rank,
+               const void* b, const int64_t* b_shape, int b_rank,
+               void* out, int dtype, vrb_stream stream);
+
+/* CudaBackend::cast (:3978) / the conversion kernels :597-628.  src dtype may be VRB_U8. */
+int vrb_cast(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t count,
+             vrb_stream stream);
+
+/* CudaBackend::activation (:4179-4188), clamp (:5128), exp, sqrt (:5134-5173). */
+int vrb_activation(int kind, const void* x, void* out, int dtype, int64_t count, vrb_stream stream);
+int vrb_clamp(const void* x, void* out, int dtype, int64_t count, float minimum, float maximum,
+              vrb_stream stream);
+int vrb_exp(const void* x, void* out, int dtype, int64_t count, vrb_stream stream);
+int vrb_sqrt(const void* x, void* out, int dtype, int64_t count, vrb_stream stream);
+
+/* CudaBackend::layer_norm (:4057-4089).  Output dtype = x's.  weight/bias may be NULL; they
+ * may be given in F32 or BF16 and are converted to x's dtype as the reference does. */
+int vrb_layer_norm(const void* x, int dtype, const void* weight, int weight_dtype,
+                   const void* bias, int bias_dtype, void* out,
+                   int64_t rows, int64_t width, float eps, vrb_stream stream);
+
+/* CudaBackend::rms_norm over the last axis (:4091-4160).  out_dtype = x_dtype, or F32 for
+ * BF16 input (needs a weight, :4123).  weight is converted to out_dtype. */
+int vrb_rms_norm(const void* x, int x_dtype, const void* weight, int weight_dtype,
+                 void* out, int out_dtype, int64_t rows, int64_t width, float eps,
+                 vrb_stream stream);
+
+/* CudaBackend::rms_norm over an inner axis (:4161-4176): x is [outer, axis, inner]. */
+int vrb_rms_norm_axis(const void* x, int dtype, const void* weight, int weight_dtype, void* out,
+                      int64_t outer, int64_t axis, int64_t inner, float eps, int fuse_silu,
+                      vrb_stream stream);
+
+/* CudaBackend::rope_nd (:4198-4213).  cos/sin have f_shape and broadcast against x_shape. */
+int vrb_rope(const void* x, int x_dtype, const int64_t* x_shape, int x_rank,
+             const void* cosine, const void* sine, int f_dtype, const int64_t* f_shape, int f_rank,
+             void* out, vrb_stream stream);
+
+/* copy_to_device, quantized branch (:3214-3296): packed [rows, inner] with scales
+ * [rows, ceil(inner/group_size)] -> out_dtype.  FP8 decode :630-638. */
+int vrb_dequantize(int kind, const void* packed, const float* scales, void* out, int out_dtype,
+                   int64_t rows, int64_t inner, int64_t group_size, vrb_stream stream);
+
+/* CudaBackend::group_norm (:4919-5008) on x [batch, channels, spatial], optionally followed by
+ * the SiLU the VAE call sites apply next (native/src/components/autoencoder_kl.cpp:40-41).
+ * workspace: vrb_group_norm_workspace_bytes() bytes of device scratch, 256-byte aligned. */
+size_t vrb_group_norm_workspace_bytes(int64_t batch, int groups);
+int vrb_group_norm(const void* x, int dtype, const void* weight, int weight_dtype,
+                   const void* bias, int bias_dtype, void* out,
+                   int64_t batch, int64_t channels, int64_t spatial, int groups, float eps,
+                   int fuse_silu, void* workspace, size_t workspace_bytes, vrb_stream stream);
+
+/* The two halves of vrb_group_norm for a tensor whose spatial axis is split over ranks:
+ * moments[unit] = {n, sum(x - shift[unit]), sum((x - shift[unit])^2)} as three doubles per
+ * unit over this rank's slice; slices add; vrb_group_norm_finalize turns the added moments
+ * into mean / inverse-stddev; vrb_group_norm_apply normalises a slice.
+ * x is [batch, channels, spatial_local]. */
+int vrb_group_norm_moments(const void* x, int dtype, int64_t batch, int64_t channels,
+                           int64_t spatial_local, int groups, const float* shift,
+                           double* moments, void* workspace, size_t workspace_bytes,
+                           vrb_stream stream);
+int vrb_group_norm_finalize(const double* moments, const float* shift, int64_t units, float eps,
+                            float* mean, float* inverse, vrb_stream stream);
+int vrb_group_norm_apply(const void* x, int dtype, const void* weight, int weight_dtype,
+                         const void* bias, int bias_dtype, void* out,
+                         int64_t batch, int64_t channels, int64_t spatial_local, int groups,
+                         const float* mean, const float* inverse, int fuse_silu,
+                         vrb_stream stream);
+
+/* ------------------------------------------------------------------------ fused chains -- */
+/* Each fused form produces what the cited chain of separate reference kernels produces,
+ * including every intermediate rounding, while reading each tensor once. */
+
+/* layer_norm (:4057) -> modulate (native/src/architectures/common.cpp:51-61) -> cast to
+ * out_dtype (the consumer cast, :3674).  scale/shift are [mod_vectors, width]; row r uses
+ * vector (r / rows_per_vector) % mod_vectors.  shift may be NULL.  weight/bias may be NULL. */
+int vrb_layer_norm_modulate(const void* x, int x_dtype, const void* weight, int weight_dtype,
+                            const void* bias, int bias_dtype,
+                            const void* scale, const void* shift, int mod_dtype,
+                            int64_t rows_per_vector, int64_t mod_vectors,
+                            void* out, int out_dtype, int64_t rows, int64_t width, float eps,
+                            vrb_stream stream);
+
+/* layer_norm (:4057) -> cast to out_dtype: the F32-residual policy's norm3 feeding the
+ * cross-attention projections (native/src/architectures/wan.cpp:98-104), whose linear
+ * converts its F32 operand to BF16 (:3674). */
+int vrb_layer_norm_cast(const void* x, int x_dtype, const void* weight, int weight_dtype,
+                        const void* bias, int bias_dtype, void* out, int out_dtype,
+                        int64_t rows, int64_t width, float eps, vrb_stream stream);
+
+/* rms_norm(x, no weight, eps) (:4091) -> modulate (common.cpp:51-61) -> cast: the LTX block
+ * (native/src/architectures/ltx_self_attention_graph.cpp:30-44). */
+int vrb_rms_norm_modulate(const void* x, int x_dtype, const void* scale, const void* shift,
+                          int mod_dtype, int64_t rows_per_vector, int64_t mod_vectors,
+                          void* out, int out_dtype, int64_t rows, int64_t width, float eps,
+                          vrb_stream stream);
+
+/* rms_norm(x, no weight, eps) * (1 + scale) multiplied in x's dtype:
+ * native/src/architectures/mochi.cpp:230-231.  out dtype = x's. */
+int vrb_rms_norm_scale(const void* x, int dtype, const void* scale, int scale_dtype,
+                       int64_t rows_per_vector, int64_t mod_vectors,
+                       void* out, int64_t rows, int64_t width, float eps, vrb_stream stream);
+
+/* attention_norm (common.cpp:62-68: rms_norm widened to F32) -> operation_rope
+ * (common.cpp:69-76) -> cast to out_dtype (operation_attention, common.cpp:77-87).
+ * norm_width is the normalised extent: `width` (Wan: whole model dim, then head split) or
+ * the head width (Mochi / Hunyuan per-head norm); rows*width/norm_width rows are normalised.
+ * cos/sin: F32 [f_rows, f_width] with f_width dividing width; element (row r, column c)
+ * uses table row (r / rows_per_f_row) % f_rows, column c % f_width.  cosine may be NULL
+ * (norm + cast only: the cross-attention q/k of native/src/architectures/wan.cpp:38-46). */
+int vrb_rms_norm_rope(const void* x, int x_dtype, const void* weight, int weight_dtype,
+                      const void* cosine, const void* sine, int64_t f_rows, int64_t f_width,
+                      int64_t rows_per_f_row, void* out, int out_dtype,
+                      int64_t rows, int64_t width, int64_t norm_width, float eps,
+                      vrb_stream stream);
+
+/* gated_residual (common.cpp:139-144) and, with gate == NULL, residual_add (:134-138):
+ * out = T(residual) + round_T(T(branch) * T(gate)), T = state_dtype.  gate is
+ * [gate_vectors, width]; row r uses vector (r / rows_per_vector) % gate_vectors. */
+int vrb_gated_residual(const void* residual, int residual_dtype, const void* branch, int branch_dtype,
+                       const void* gate, int gate_dtype, int64_t rows_per_vector, int64_t gate_vectors,
+                       void* out, int state_dtype, int64_t rows, int64_t width, vrb_stream stream);
+
+/* normalized_gated_residual (mochi.cpp:204-211) with the gate already bounded by tanh:
+ * out = T(residual) + round_T(T(rms_norm(branch, none, eps)) * T(gate)). */
+int vrb_rms_norm_gated_residual(const void* residual, int residual_dtype,
+                                const void* branch, int branch_dtype,
+                                const void* gate, int gate_dtype,
+                                int64_t rows_per_vector, int64_t gate_vectors,
+                                void* out, int state_dtype, int64_t rows, int64_t width,
+                                float eps, vrb_stream stream);
+
+/* SwiGLU (mochi.cpp:195-202) without the two slice copies: projected is [rows, 2*hidden],
+ * out[r, j] = round(projected[r, j] * round(silu(projected[r, hidden + j]))). */
+int vrb_swiglu(const void* projected, void* out, int dtype, int64_t rows, int64_t hidden,
+               vrb_stream stream);
+
+/* SamplingPrimitives::cfg_combine (native/src/sampling/sampling.cpp:181-183).
+ * scalar_role != 0: the guidance coefficient has a declared scalar role, so each multiply is
+ * done in F32 and rounded to `dtype` (native/src/precision/precision.cpp:196-223);
+ * 0: legacy, the coefficient itself is rounded to `dtype` first. */
+int vrb_cfg_combine(const void* unconditional, const void* conditional, void* out, int dtype,
+                    int64_t count, float scale, int scalar_role, vrb_stream stream);
+
+/* SamplingPrimitives::euler_update (sampling.cpp:185-193): out = sample + prediction *
+ * (delta * (subtract ? -1 : 1)) with the reference's rounding of each product.  delta is the
+ * value the one-element coefficient tensor holds (a caller whose execution dtype is BF16 and
+ * whose policy declares no solver role passes the BF16-rounded delta, as the reference's
+ * host-scalar multiply produces). */
+int vrb_euler_update(const void* sample, const void* prediction, void* out, int dtype,
+                     int64_t count, float delta, int subtract_prediction, int scalar_role,
+                     vrb_stream stream);
+
+/* SamplingPrimitives::flow_to_x0 (sampling.cpp:200-202): out = sample + output * (-sigma). */
+int vrb_flow_to_x0(const void* sample, const void* model_output, void* out, int dtype,
+                   int64_t count, float sigma, int scalar_role, vrb_stream stream);
+
+/* cfg_combine followed by euler_update on its result, one pass (sampling.cpp:465-477).
+ * guided (optional, may be NULL) receives the cfg_combine result. */
+int vrb_cfg_euler(const void* sample, const void* unconditional, const void* conditional,
+                  void* guided, void* out, int dtype, int64_t count, float scale, float delta,
+                  int subtract_prediction, int guidance_role, int solver_role, vrb_stream stream);
+
+/* ---------------------------------------------------------------- host-buffer entry points -- */
+/* The reference's operators accept host tensors and upload them on demand (copy_to_device,
+ * :3195); results come back through copy_to_host.  These forms do the same for whole fused
+ * chains: arguments are HOST pointers, rows are streamed through pinned staging and device
+ * buffers owned by the library in row blocks so upload, kernel and download overlap.
+ * host_is_pinned != 0 promises x and out are page-locked (cudaMallocHost / cudaHostRegister),
+ * which lets the copies run straight from and to them.  Synchronous: returns when out holds
+ * the result.  vrb_host_release() frees the staging buffers. */
+int vrb_host_layer_norm_modulate(const void* x, int x_dtype, const void* scale, const void* shift,
+                                 int mod_dtype, void* out, int out_dtype,
+                                 int64_t rows, int64_t width, float eps, int host_is_pinned);
+void vrb_host_release(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VRB_H_ */

@@ -1,0 +1,101 @@
+"""Shared fixtures.  Tests marked ``gpu`` need a B200 and call the CUDA library through its C
+ABI; everything else runs on CPU (oracle pins, host logic, ABI/symbol checks, gloo ranks)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture(scope="session")
+def orc():
+    from oracle import oracle
+    oracle.build()
+    return oracle
+
+
+@pytest.fixture(scope="session")
+def cuda_lib():
+    """Build (if stale) and load libvrb.so; building needs nvcc only, not a GPU."""
+    from vrhino_b200 import _lib, build
+    if not os.path.exists(_lib.LIB_PATH):
+        build.build()
+    return _lib.load()
+
+
+@pytest.fixture(scope="session")
+def gpu():
+    """(backend, ops module) on cuda:0.  Fails -- never skips -- when the extension is absent."""
+    import torch
+    assert torch.cuda.is_available(), "gpu-marked test collected without a CUDA device"
+    from vrhino_b200 import ops
+    return ops.B200Backend(), ops
+
+
+# ---- helpers shared by the parity tests -----------------------------------------------------
+def to_torch(t, device="cuda"):
+    """Oracle tensor -> torch tensor with the same bits."""
+    import torch
+    if t.dtype == "bf16":
+        return torch.from_numpy(t.data.view(np.int16).copy()).view(torch.bfloat16).to(device)
+    if t.dtype == "u8":
+        return torch.from_numpy(t.data.copy()).to(device)
+    return torch.from_numpy(t.data.copy()).to(device)
+
+
+def from_torch(x):
+    """torch tensor -> (numpy payload, dtype tag): bf16 as uint16 bits."""
+    import torch
+    x = x.detach().cpu().contiguous()
+    if x.dtype == torch.bfloat16:
+        return x.view(torch.int16).numpy().view(np.uint16), "bf16"
+    return x.numpy(), "f32"
+
+
+def assert_close(orc, got, want, max_ulp=2, rel=1e-5, atol=0.0, what=""):
+    """bf16: <= max_ulp on the bf16 grid (or within atol when stated); f32: |d| <= atol + rel*|ref|."""
+    data, tag = from_torch(got)
+    assert tag == want.dtype, f"{what}: dtype {tag} != {want.dtype}"
+    assert tuple(data.shape) == tuple(want.shape), f"{what}: shape {data.shape} != {want.shape}"
+    if tag == "bf16":
+        d = orc.bf16_ulp_distance(data, want.data)
+        bad = d > max_ulp
+        if atol > 0 and bad.any():
+            diff = np.abs(orc.bf16_bits_to_f32(data) - want.f32())
+            bad &= ~(diff <= atol)
+        if bad.any():
+            i = np.unravel_index(np.argmax(np.where(bad, d, 0)), d.shape)
+            raise AssertionError(f"{what}: {int(bad.sum())} of {d.size} elements differ by more than {max_ulp} bf16 ulp; "
+                                 f"worst at {i}: got {orc.bf16_bits_to_f32(data)[i]!r} want {want.f32()[i]!r}")
+        return float((d > 0).mean())
+    ref = want.data.astype(np.float64)
+    diff = np.abs(data.astype(np.float64) - ref)
+    nan_mismatch = np.isnan(data) != np.isnan(want.data)
+    tol = atol + np.maximum(rel * np.abs(ref), 1e-8)   # relative, with an absolute floor of 1e-8
+    both_nan = np.isnan(data) & np.isnan(want.data)
+    same_inf = np.isinf(data) & (data == want.data)
+    bad = ~(diff <= tol) & ~both_nan & ~same_inf
+    bad |= nan_mismatch
+    if bad.any():
+        i = np.unravel_index(np.argmax(np.where(bad, diff, 0)), diff.shape)
+        raise AssertionError(f"{what}: {int(bad.sum())} of {diff.size} f32 elements out of tolerance; "
+                             f"worst at {i}: got {data[i]!r} want {want.data[i]!r}")
+    return float((data != want.data).mean())
+
+
+def assert_bits_equal(got, want, what=""):
+    data, tag = from_torch(got)
+    assert tag == want.dtype and tuple(data.shape) == tuple(want.shape), what
+    a = data.view(np.uint16 if tag == "bf16" else np.uint32)
+    b = want.data.view(np.uint16 if tag == "bf16" else np.uint32)
+    if not np.array_equal(a, b):
+        n = int((a != b).sum())
+        raise AssertionError(f"{what}: {n} of {a.size} elements are not bit-identical")

@@ -1,0 +1,299 @@
+"""GPU parity of the elementwise / broadcast kernels against the CPU oracle, through the C ABI.
+
+Tolerances: integer-like and single-IEEE-operation results are compared bit for bit; results
+that go through expf / tanhf / erff are compared at <= 2 bf16 ulp (bf16) or 1e-5 relative
+(f32), because the CUDA and the C math libraries are each specified to 1-2 ulp.  Where
+1 + tanhf / 1 + erff cancels (negative tail of GELU) two conforming libraries agree only
+absolutely, so an absolute bound of 4 * 2^-24 * |x| is allowed there and stated in the test.
+"""
+import numpy as np
+import pytest
+
+from conftest import assert_bits_equal, assert_close, to_torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["f32", "bf16"]
+
+
+def indexing_input(orc, shape, dtype, seed):
+    """Inputs of native/tests/cuda_binary_indexing_tests.cu:50-61 (incl. +-0, +-inf, NaN)."""
+    count = int(np.prod(shape)) if len(shape) else 1
+    i = np.arange(count, dtype=np.int64)
+    v = (((i * 17 + seed) % 255 - 127).astype(np.float32) / np.float32(128.0))
+    special = np.array([0.0, -0.0, np.inf, -np.inf, np.nan], dtype=np.float32)
+    for k in range(min(count, 5)):
+        v[k] = special[(k + seed) % 5]
+    return orc.tensor(v.reshape(shape), dtype)
+
+
+BINARY_CASES = [
+    ("full", (1, 32760, 1536), (1, 32760, 1536)),
+    ("suffix", (1, 32760, 1536), (1, 1, 1536)),
+    ("scalar_first", (), (3, 257)),
+    ("scalar_last", (3, 257), (1, 1)),
+    ("suffix_first", (7,), (3, 5, 7)),
+    ("suffix_matrix", (3, 7), (2, 3, 7)),
+    ("internal_singleton", (3, 1, 7), (1, 5, 1)),
+    ("rank8", (1, 1, 1, 1, 1, 1, 257, 3), (257, 3)),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("label,a_shape,b_shape", BINARY_CASES)
+def test_binary_indexing_bit_exact(orc, gpu, dtype, label, a_shape, b_shape):
+    """The 64 byte-exact cases of cuda_binary_indexing_tests.cu:111-118, Wan adaLN shape included."""
+    be, ops = gpu
+    obe = orc.OracleBackend(execution_dtype=dtype)
+    a, b = indexing_input(orc, a_shape, dtype, 1), indexing_input(orc, b_shape, dtype, 3)
+    ta, tb = to_torch(a), to_torch(b)
+    for kind, name in enumerate(["add", "mul", "div", "maximum"]):
+        want = obe._binary(kind, a, b)
+        got = getattr(be, name)(ta, tb)
+        assert_bits_equal(got, want, f"{label}/{dtype}/{name}")
+
+
+def test_binary_rejections(gpu):
+    be, ops = gpu
+    import torch
+    with pytest.raises(ops.VrbError, match="CUDA primitive rank exceeds 8"):
+        be.add(torch.zeros((1,) * 9, device="cuda", dtype=torch.bfloat16), torch.zeros((), device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(ops.VrbError, match="Incompatible broadcast shapes"):
+        be.mul(torch.zeros(2, 3, device="cuda"), torch.zeros(2, 4, device="cuda"))
+
+
+def test_binary_operand_dtype_rule(orc, gpu):
+    """add(bf16, f32) computes in bf16, add(f32, bf16) in f32 (cuda_backend.cu:3875-3880)."""
+    be, ops = gpu
+    obe = orc.OracleBackend()
+    from vrhino_b200 import synth
+    a = orc.tensor(synth.normal((5, 64), seed=1), "bf16")
+    b = orc.tensor(synth.normal((5, 64), seed=2), "f32")
+    for x, y in ((a, b), (b, a)):
+        want = obe.add(x, y)
+        got = be.add(to_torch(x), to_torch(y))
+        assert_bits_equal(got, want, f"add({x.dtype},{y.dtype})")
+
+
+@pytest.mark.parametrize("n", [4, 1000, 8 * 1031])
+def test_cast_bit_exact(orc, gpu, n):
+    be, ops = gpu
+    import torch
+    from vrhino_b200 import synth
+    obe = orc.OracleBackend()
+    x = orc.tensor(np.concatenate([synth.normal((n - 4,), std=3.0, seed=n), np.array([np.inf, -np.inf, np.nan, -0.0], dtype=np.float32)]))
+    want = obe.cast(x, "bf16")
+    got = be.cast(to_torch(x), torch.bfloat16)
+    assert_bits_equal(got, want, "f32->bf16")
+    assert_bits_equal(be.cast(got, torch.float32), obe.cast(want, "f32"), "bf16->f32")
+    assert be.cast(got, torch.bfloat16) is got  # same handle on a no-op cast
+    kat = be.cast(be.cast(torch.tensor([1.1, -2.3, 0, 8], device="cuda"), torch.bfloat16), torch.float32)
+    assert kat.tolist() == [1.1015625, -2.296875, 0.0, 8.0]
+    u8 = torch.arange(0, 256, dtype=torch.uint8, device="cuda")
+    assert torch.equal(be.cast(u8, torch.float32).cpu(), torch.arange(0, 256, dtype=torch.float32))
+
+
+ACT_NAMES = {0: "silu", 1: "gelu", 2: "gelu_tanh", 3: "tanh", 4: "relu"}
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2, 3, 4])
+def test_activation_exhaustive_bf16(orc, gpu, kind):
+    """Every finite bf16 input (and the infinities): the whole function table of the kernel."""
+    be, ops = gpu
+    bits = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    finite_or_inf = (bits & 0x7FFF) <= 0x7F80
+    bits = bits[finite_or_inf]
+    x = orc.T(bits, "bf16")
+    want = orc.OracleBackend().activation(x, kind)
+    got = be.activation(to_torch(x), kind)
+    xf = np.abs(x.f32())
+    from conftest import from_torch
+    data, _ = from_torch(got)
+    d = orc.bf16_ulp_distance(data, want.data)
+    diff = np.abs(orc.bf16_bits_to_f32(data).astype(np.float64) - want.f32().astype(np.float64))
+    with np.errstate(invalid="ignore"):
+        allowed = (d <= 2) | (diff <= 4 * 2.0 ** -24 * xf) | (np.isnan(orc.bf16_bits_to_f32(data)) & np.isnan(want.f32()))
+    assert allowed.all(), (ACT_NAMES[kind], int((~allowed).sum()), x.f32()[~allowed][:5])
+    assert (d == 0).mean() > 0.99, f"{ACT_NAMES[kind]}: only {(d == 0).mean():.4f} of the table is bit-identical"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kind", [0, 2, 3])
+@pytest.mark.parametrize("n", [37, 8 * 4096 + 8])
+def test_activation_random(orc, gpu, dtype, kind, n):
+    be, ops = gpu
+    from vrhino_b200 import synth
+    x = orc.tensor(synth.normal((n,), std=2.0, seed=kind + n), dtype)
+    want = orc.OracleBackend().activation(x, kind)
+    got = be.activation(to_torch(x), kind)
+    assert_close(orc, got, want, max_ulp=2, rel=1e-5, atol=float(4 * 2.0 ** -24 * np.abs(x.f32()).max()), what=ACT_NAMES[kind])
+
+
+def test_clamp_exp_sqrt(orc, gpu):
+    be, ops = gpu
+    from vrhino_b200 import synth
+    obe = orc.OracleBackend()
+    for dtype in DTYPES:
+        x = orc.tensor(synth.normal((3, 1000), std=2.0, seed=5), dtype)
+        tx = to_torch(x)
+        assert_bits_equal(be.clamp(tx, -0.5, 0.75), obe.clamp(x, -0.5, 0.75), "clamp")
+        assert_close(orc, be.exp(tx), obe.exp(x), what="exp")
+        pos = orc.tensor(np.abs(x.f32()), dtype)
+        assert_bits_equal(be.sqrt(to_torch(pos)), obe.sqrt(pos), "sqrt")  # sqrtf is correctly rounded on both sides
+    with pytest.raises(ops.VrbError, match="Invalid clamp bounds"):
+        be.clamp(tx, 1.0, 0.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden", [(5, 24), (3, 7), (33, 8192)])
+def test_swiglu(orc, gpu, dtype, rows, hidden):
+    be, ops = gpu
+    from vrhino_b200 import synth
+    proj = orc.tensor(synth.normal((1, rows, 2 * hidden), seed=rows), dtype)
+    want = orc.swiglu_hidden(orc.OracleBackend(), proj)
+    got = ops.fused_swiglu(be, to_torch(proj))
+    assert_close(orc, got, want, what="swiglu")
+
+
+@pytest.mark.parametrize("res_dt,br_dt,state", [("bf16", "bf16", "bf16"), ("f32", "bf16", "f32"), ("bf16", "bf16", "f32"), ("f32", "f32", "f32")])
+@pytest.mark.parametrize("rows,width,batch", [(6, 64, 1), (6, 64, 2), (5, 7, 1)])
+@pytest.mark.parametrize("gated", [True, False])
+def test_gated_residual_bit_exact(orc, gpu, res_dt, br_dt, state, rows, width, batch, gated):
+    """gated_residual / residual_add are chains of single IEEE operations: bit for bit."""
+    import torch
+    be, ops = gpu
+    from vrhino_b200 import synth
+    obe = orc.OracleBackend()
+    res = orc.tensor(synth.normal((batch, rows, width), seed=1), res_dt)
+    br = orc.tensor(synth.normal((batch, rows, width), seed=2), br_dt)
+    gate = orc.tensor(synth.normal((batch, 1, width), std=0.1, seed=3), "f32")
+    opol = orc.Policy(residual=state)
+    pol = ops.Policy(residual=torch.float32 if state == "f32" else torch.bfloat16)
+    want = orc.gated_residual(obe, opol, res, br, gate) if gated else orc.residual_add(obe, opol, res, br)
+    got = ops.fused_gated_residual(be, pol, to_torch(res), to_torch(br), to_torch(gate) if gated else None)
+    assert_bits_equal(got, want, "fused gated_residual")
+    chain = ops.gated_residual(be, pol, to_torch(res), to_torch(br), to_torch(gate)) if gated else \
+        ops.residual_add(be, pol, to_torch(res), to_torch(br))
+    assert_bits_equal(chain, want, "per-op chain")
+
+
+@pytest.mark.parametrize("x_dt", DTYPES)
+@pytest.mark.parametrize("f_dt", DTYPES)
+@pytest.mark.parametrize("shape,f_shape", [((1, 3, 2, 6), (1, 3, 1, 6)), ((1, 3, 2, 64), (1, 3, 1, 64)), ((1, 3, 2, 128), (1, 3, 1, 128)),
+                                           ((2, 5, 4, 128), (1, 5, 4, 128)), ((2, 5, 256), (2, 5, 256)), ((2, 3, 4, 16), (2, 1, 1, 16))])
+def test_rope_bit_exact(orc, gpu, x_dt, f_dt, shape, f_shape):
+    """rope_nd is three IEEE operations per element with fixed rounding: bit for bit, on the
+    dtype matrix of precision_operation_contract_tests.cpp:41-83 plus per-head, per-batch and
+    inner-broadcast tables."""
+    be, ops = gpu
+    from vrhino_b200 import synth
+    x = orc.tensor(synth.normal(shape, seed=11), x_dt)
+    phase = synth.uniform_range(f_shape, -3.1, 3.1, seed=12)
+    co, si = orc.tensor(np.cos(phase), f_dt), orc.tensor(np.sin(phase), f_dt)
+    want = orc.OracleBackend().rope_nd(x, co, si)
+    got = be.rope_nd(to_torch(x), to_torch(co), to_torch(si))
+    assert_bits_equal(got, want, "rope")
+
+
+def test_rope_no_contraction_kat(gpu):
+    """precision_operation_contract_tests.cpp:26-37"""
+    import torch
+    be, ops = gpu
+    u = 2.0 ** -23
+    x = torch.tensor([1.0 + u, 1.0], device="cuda").reshape(1, 1, 1, 2)
+    c = torch.tensor([1.0 - u, 0.0], device="cuda").reshape(1, 1, 1, 2)
+    s = torch.tensor([1.0, 0.0], device="cuda").reshape(1, 1, 1, 2)
+    assert be.rope_nd(x, c, s).reshape(-1)[0].item() == 0.0
+    with pytest.raises(ops.VrbError, match="RoPE width must be even"):
+        be.rope_nd(torch.zeros(1, 2, 1, 3, device="cuda"), torch.zeros(1, 2, 1, 3, device="cuda"), torch.zeros(1, 2, 1, 3, device="cuda"))
+
+
+@pytest.mark.parametrize("out_dt", DTYPES)
+@pytest.mark.parametrize("kind,rows,inner,group", [("fp8_e4m3fn", 6, 8, 4), ("fp8_e4m3fn", 16, 256, 256), ("fp8_e4m3fn", 5, 96, 32),
+                                                   ("fp8_e4m3fn", 3, 40, 8), ("int8", 16, 256, 64), ("int8", 3, 10, 5), ("int4", 4, 16, 8)])
+def test_dequantize_bit_exact(orc, gpu, out_dt, kind, rows, inner, group):
+    import torch
+    be, ops = gpu
+    from vrhino_b200 import synth
+    count = rows * inner
+    if kind == "fp8_e4m3fn":
+        packed = np.arange(count, dtype=np.int64).astype(np.uint8) if count >= 256 else synth.fp8_codes((count,), seed=3)
+    elif kind == "int8":
+        packed = (np.arange(count) * 37 % 256).astype(np.uint8)
+    else:
+        packed = (np.arange((count + 1) // 2) * 53 % 256).astype(np.uint8)
+    groups = (inner + group - 1) // group
+    scales = synth.uniform_range((rows, groups), 1e-3, 1e-2, seed=4)
+    t = orc.T(packed, "u8", host=True, quant={"type": kind, "group_size": group, "scales": scales, "shape": (rows, inner)})
+    want = orc.OracleBackend().copy_to_device(t, out_dt)
+    code = {"fp8_e4m3fn": 0, "int8": 1, "int4": 2}[kind]
+    got = be.dequantize(torch.from_numpy(packed), torch.from_numpy(scales), group, kind=code,
+                        dtype=torch.float32 if out_dt == "f32" else torch.bfloat16, shape=(rows, inner))
+    assert_bits_equal(got, want, f"dequant {kind}")
+
+
+def test_dequantize_all_fp8_codes(orc, gpu):
+    """All 256 codes, scale 1: the decode table itself, incl. 0x7f/0xff -> +-480 and -0."""
+    import torch
+    be, ops = gpu
+    packed = np.arange(256, dtype=np.uint8)
+    got = be.dequantize(torch.from_numpy(packed), torch.ones(1, 1), 256, dtype=torch.float32, shape=(1, 256)).cpu().numpy().reshape(-1)
+    want = np.array([orc.lib().orc_decode_fp8(int(c)) for c in packed], dtype=np.float32)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+SAMPLER_POLICIES = ["fp32", "bf16_legacy", "bf16_roles", "bf16_guidance_only"]
+
+
+def _policies(orc, ops, name):
+    import torch
+    if name == "fp32":
+        return orc.Policy.fp32(), ops.Policy.fp32(), "f32", orc.F32, torch.float32
+    o, p = orc.Policy.unqualified_default("bf16"), ops.Policy.unqualified_default(torch.bfloat16)
+    if name == "bf16_roles":
+        roles = {"GuidanceCoefficient", "SolverCoefficient", "Sigma"}
+        o, p = o.with_scalar_roles(roles), p.with_scalar_roles(roles)
+    if name == "bf16_guidance_only":
+        o, p = o.with_scalar_roles({"GuidanceCoefficient"}), p.with_scalar_roles({"GuidanceCoefficient"})
+    return o, p, "bf16", orc.BF16, torch.bfloat16
+
+
+@pytest.mark.parametrize("policy", SAMPLER_POLICIES)
+@pytest.mark.parametrize("n", [12, 2 * 16 * 21 * 13])
+def test_sampler_updates_bit_exact(orc, gpu, policy, n):
+    """cfg_combine / euler_update / flow_to_x0 and the fused cfg+euler: chains of single IEEE
+    operations, so bit for bit under every scalar contract (semantic_scalar_tests.cpp:20-28)."""
+    _, ops = gpu
+    opol, pol, dt, oexec, texec = _policies(orc, ops, policy)
+    be = ops.B200Backend(execution_dtype=texec)
+    obe = orc.OracleBackend(execution_dtype=oexec)
+    from vrhino_b200 import synth
+    x, u, c = (orc.tensor(synth.normal((n,), seed=s), dt) for s in (1, 2, 3))
+    tx, tu, tc = to_torch(x), to_torch(u), to_torch(c)
+    scale, delta, sigma = 5.0, 0.02, 0.877877295
+    want_g = orc.cfg_combine(obe, opol, u, c, scale)
+    assert_bits_equal(ops.fused_cfg_combine(be, pol, tu, tc, scale), want_g, "fused cfg")
+    assert_bits_equal(ops.cfg_combine(be, pol, tu, tc, scale), want_g, "chain cfg")
+    want_e = orc.euler_update(obe, opol, x, u, orc.scalar_f32(delta), True)
+    assert_bits_equal(ops.fused_euler_update(be, pol, tx, tu, delta, True), want_e, "fused euler")
+    assert_bits_equal(ops.euler_update(be, pol, tx, tu, delta, True), want_e, "chain euler")
+    want_f = orc.flow_to_x0(obe, opol, x, u, sigma)
+    assert_bits_equal(ops.fused_flow_to_x0(be, pol, tx, tu, sigma), want_f, "fused flow_to_x0")
+    want_ge = orc.euler_update(obe, opol, x, want_g, orc.scalar_f32(delta), True)
+    out, guided = ops.fused_cfg_euler(be, pol, tx, tu, tc, scale, delta, True, want_guided=True)
+    assert_bits_equal(guided, want_g, "fused cfg+euler guided")
+    assert_bits_equal(out, want_ge, "fused cfg+euler")
+
+
+def test_null_and_empty_arguments_are_rejected(gpu):
+    import ctypes
+    be, ops = gpu
+    from vrhino_b200 import _lib
+    lib = _lib.load()
+    assert lib.vrb_activation(0, None, None, 0, 16, None) == -1
+    assert b"null tensor" in lib.vrb_last_error()
+    import torch
+    x = torch.zeros(8, device="cuda")
+    assert lib.vrb_activation(0, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x.data_ptr()), 0, 0, None) == -1
+    assert lib.vrb_activation(9, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x.data_ptr()), 0, 8, None) == -1
+    assert lib.vrb_activation(0, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x.data_ptr()), 5, 8, None) == -2

@@ -1,0 +1,99 @@
+"""ctypes binding of ``libvrb.so`` (the C ABI declared in ``include/vrb.h``).
+
+There is no fallback: if the shared library is missing or a call fails, an exception is
+raised.  ``VrbError`` mirrors ``vrhino::Error`` (native/include/vrhino/error.h:8-13 of the
+reference) -- the text is what ``vrb_last_error()`` reports.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libvrb.so")
+
+F32, BF16, U8 = 0, 2, 5
+SILU, GELU, GELU_TANH, TANH, RELU = 0, 1, 2, 3, 4
+ADD, MUL, DIV, MAX = 0, 1, 2, 3
+Q_FP8, Q_INT8, Q_INT4 = 0, 1, 2
+
+
+class VrbError(RuntimeError):
+    """Raised when an entry point returns a negative status."""
+
+
+_c = ctypes
+_vp, _i, _i64, _f, _sz = _c.c_void_p, _c.c_int, _c.c_int64, _c.c_float, _c.c_size_t
+_pi64 = _c.POINTER(_c.c_int64)
+
+# name -> argtypes; every entry returns int unless listed in _RESTYPES
+SIGNATURES = {
+    "vrb_abi_version": [],
+    "vrb_last_error": [],
+    "vrb_launch_count": [],
+    "vrb_binary": [_i, _vp, _pi64, _i, _vp, _pi64, _i, _vp, _i, _vp],
+    "vrb_cast": [_vp, _i, _vp, _i, _i64, _vp],
+    "vrb_activation": [_i, _vp, _vp, _i, _i64, _vp],
+    "vrb_clamp": [_vp, _vp, _i, _i64, _f, _f, _vp],
+    "vrb_exp": [_vp, _vp, _i, _i64, _vp],
+    "vrb_sqrt": [_vp, _vp, _i, _i64, _vp],
+    "vrb_layer_norm": [_vp, _i, _vp, _i, _vp, _i, _vp, _i64, _i64, _f, _vp],
+    "vrb_rms_norm": [_vp, _i, _vp, _i, _vp, _i, _i64, _i64, _f, _vp],
+    "vrb_rms_norm_axis": [_vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _f, _i, _vp],
+    "vrb_rope": [_vp, _i, _pi64, _i, _vp, _vp, _i, _pi64, _i, _vp, _vp],
+    "vrb_dequantize": [_i, _vp, _vp, _vp, _i, _i64, _i64, _i64, _vp],
+    "vrb_group_norm_workspace_bytes": [_i64, _i],
+    "vrb_group_norm": [_vp, _i, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i, _f, _i, _vp, _sz, _vp],
+    "vrb_group_norm_moments": [_vp, _i, _i64, _i64, _i64, _i, _vp, _vp, _vp, _sz, _vp],
+    "vrb_group_norm_finalize": [_vp, _vp, _i64, _f, _vp, _vp, _vp],
+    "vrb_group_norm_apply": [_vp, _i, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i, _vp, _vp, _i, _vp],
+    "vrb_layer_norm_modulate": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i64, _i64, _vp, _i, _i64, _i64, _f, _vp],
+    "vrb_layer_norm_cast": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i64, _i64, _f, _vp],
+    "vrb_rms_norm_modulate": [_vp, _i, _vp, _vp, _i, _i64, _i64, _vp, _i, _i64, _i64, _f, _vp],
+    "vrb_rms_norm_scale": [_vp, _i, _vp, _i, _i64, _i64, _vp, _i64, _i64, _f, _vp],
+    "vrb_rms_norm_rope": [_vp, _i, _vp, _i, _vp, _vp, _i64, _i64, _i64, _vp, _i, _i64, _i64, _i64, _f, _vp],
+    "vrb_gated_residual": [_vp, _i, _vp, _i, _vp, _i, _i64, _i64, _vp, _i, _i64, _i64, _vp],
+    "vrb_rms_norm_gated_residual": [_vp, _i, _vp, _i, _vp, _i, _i64, _i64, _vp, _i, _i64, _i64, _f, _vp],
+    "vrb_swiglu": [_vp, _vp, _i, _i64, _i64, _vp],
+    "vrb_cfg_combine": [_vp, _vp, _vp, _i, _i64, _f, _i, _vp],
+    "vrb_euler_update": [_vp, _vp, _vp, _i, _i64, _f, _i, _i, _vp],
+    "vrb_flow_to_x0": [_vp, _vp, _vp, _i, _i64, _f, _i, _vp],
+    "vrb_cfg_euler": [_vp, _vp, _vp, _vp, _vp, _i, _i64, _f, _f, _i, _i, _i, _vp],
+    "vrb_host_layer_norm_modulate": [_vp, _i, _vp, _vp, _i, _vp, _i, _i64, _i64, _f, _i],
+    "vrb_host_release": [],
+}
+_RESTYPES = {
+    "vrb_last_error": _c.c_char_p,
+    "vrb_launch_count": _c.c_uint64,
+    "vrb_group_norm_workspace_bytes": _c.c_size_t,
+    "vrb_host_release": None,
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load libvrb.so, declaring every signature.  Raises if the library was not built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise VrbError(f"{LIB_PATH} is missing: build it with `python -m vrhino_b200.build` "
+                           "(nvcc, sm_100a); there is no CPU or PyTorch fallback")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = _RESTYPES.get(name, _c.c_int)
+        _lib = lib
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        text = load().vrb_last_error().decode("utf-8", "replace")
+        raise VrbError(text or f"vrb status {status}")
+
+
+def call(name: str, *args) -> None:
+    """Invoke an int-returning entry point and raise VrbError on a negative status."""
+    check(getattr(load(), name)(*args))

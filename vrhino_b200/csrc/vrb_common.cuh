@@ -1,0 +1,133 @@
+// Shared device helpers and launch plumbing for the sm_100a operator kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "vrb.h"
+
+namespace vrb {
+
+// ------------------------------------------------------------------ host-side plumbing --
+void set_error(const char* format, ...);
+extern std::atomic<uint64_t> g_launches;
+
+// SM count of the current device, cached per device index.
+int sm_count();
+
+inline cudaStream_t as_stream(vrb_stream s) { return static_cast<cudaStream_t>(s); }
+inline bool is_float_dtype(int dt) { return dt == VRB_F32 || dt == VRB_BF16; }
+inline size_t dtype_bytes(int dt) { return dt == VRB_F32 ? 4 : dt == VRB_BF16 ? 2 : 1; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+#define VRB_REQUIRE(cond, code, ...)      \
+    do {                                  \
+        if (!(cond)) {                    \
+            ::vrb::set_error(__VA_ARGS__); \
+            return (code);                \
+        }                                 \
+    } while (0)
+
+// Call after a kernel launch: counts it and turns a launch error into a status.
+inline int after_launch(const char* what) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("CUDA error: %s (%s)", cudaGetErrorString(e), what);
+        return VRB_ERR_CUDA;
+    }
+    return VRB_OK;
+}
+
+// Persistent-style grid: enough CTAs to fill every SM `per_sm` times, never more than `work`.
+inline int grid_for(int64_t work_items, int per_sm) {
+    const int64_t cap = static_cast<int64_t>(sm_count()) * per_sm;
+    const int64_t g = work_items < cap ? work_items : cap;
+    return static_cast<int>(g < 1 ? 1 : g);
+}
+
+// ------------------------------------------------------------------------ device side --
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
+    return __uint_as_float(bits16 << 16);
+}
+// RNE narrowing, identical to __float2bfloat16 (NaN -> 0x7fff).
+__device__ __forceinline__ uint32_t float_to_bf16_bits(float v) {
+    return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(v)));
+}
+__device__ __forceinline__ float round_to_bf16(float v) {
+    return __bfloat162float(__float2bfloat16_rn(v));
+}
+// Value a tensor of dtype `dt` would hold after storing v.
+__device__ __forceinline__ float round_to(int dt, float v) {
+    return dt == VRB_BF16 ? round_to_bf16(v) : v;
+}
+
+// 128-bit streaming load of 8 consecutive elements starting at element index `e`
+// (e % 8 == 0, base 16-byte aligned).  bf16: one 16-byte load; f32: two.
+template <bool kStreaming>
+__device__ __forceinline__ void load8(const void* base, int dt, int64_t e, float (&v)[8]) {
+    if (dt == VRB_BF16) {
+        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + e);
+        const uint4 r = kStreaming ? __ldcs(p) : __ldg(p);
+        v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+        v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+        v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xffff0000u);
+        v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xffff0000u);
+    } else {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + e);
+        const float4 a = kStreaming ? __ldcs(p) : __ldg(p);
+        const float4 b = kStreaming ? __ldcs(p + 1) : __ldg(p + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);  // .x = lo (low half), RNE each
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Streaming store of 8 consecutive elements (RNE narrowing for bf16).
+__device__ __forceinline__ void store8(void* base, int dt, int64_t e, const float (&v)[8]) {
+    if (dt == VRB_BF16) {
+        uint4 r;
+        r.x = pack_bf16x2(v[0], v[1]); r.y = pack_bf16x2(v[2], v[3]);
+        r.z = pack_bf16x2(v[4], v[5]); r.w = pack_bf16x2(v[6], v[7]);
+        __stcs(reinterpret_cast<uint4*>(static_cast<uint16_t*>(base) + e), r);
+    } else {
+        float4* p = reinterpret_cast<float4*>(static_cast<float*>(base) + e);
+        __stcs(p, make_float4(v[0], v[1], v[2], v[3]));
+        __stcs(p + 1, make_float4(v[4], v[5], v[6], v[7]));
+    }
+}
+
+__device__ __forceinline__ float load1(const void* base, int dt, int64_t e) {
+    return dt == VRB_BF16 ? bf16_bits_to_float(static_cast<const uint16_t*>(base)[e])
+                          : static_cast<const float*>(base)[e];
+}
+__device__ __forceinline__ void store1(void* base, int dt, int64_t e, float v) {
+    if (dt == VRB_BF16) static_cast<__nv_bfloat16*>(base)[e] = __float2bfloat16_rn(v);
+    else static_cast<float*>(base)[e] = v;
+}
+
+// The reference's activation_kernel expressions (cuda_backend.cu:1098-1109), written so the
+// compiler sees the same operations in the same order.
+__device__ __forceinline__ float activation_value(int kind, float x) {
+    if (kind == VRB_SILU) return x / (1.0f + expf(-x));
+    if (kind == VRB_GELU) return 0.5f * x * (1.0f + erff(x * 0.7071067811865475f));
+    if (kind == VRB_GELU_TANH)
+        return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    if (kind == VRB_TANH) return tanhf(x);
+    return fmaxf(x, 0.0f);
+}
+
+#endif  // __CUDACC__
+
+}  // namespace vrb

@@ -1,0 +1,619 @@
+// Elementwise and broadcast kernels: binary arithmetic, casts, activations, SwiGLU, gated
+// residual, RoPE, weight dequantisation and the sampler's guidance / Euler updates.
+//
+// All of them are pure HBM streams, so the shape is the same everywhere: a persistent grid
+// (a multiple of the SM count), every thread moving 16 bytes per access with several
+// independent accesses in flight, streaming cache hints on tensors that are touched once,
+// read-only cached loads on the small broadcast operands.  Arithmetic restates the
+// reference kernels of native/src/backend/cuda/cuda_backend.cu expression for expression.
+#include "vrb_common.cuh"
+
+namespace vrb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kPerSm = 8;  // 8 x 256 threads = a full SM
+
+inline bool vec8_ok(int64_t count, std::initializer_list<const void*> ptrs) {
+    if (count % 8) return false;
+    for (const void* p : ptrs) if (p && !aligned16(p)) return false;
+    return true;
+}
+
+// ------------------------------------------------------------------------------- unary --
+enum UnaryOp { kActSilu = 0, kActGelu, kActGeluTanh, kActTanh, kActRelu, kClamp, kExp, kSqrt, kCast };
+
+template <int OP>
+__device__ __forceinline__ float unary_value(float x, float p0, float p1) {
+    if constexpr (OP <= kActRelu) return activation_value(OP, x);
+    else if constexpr (OP == kClamp) return fminf(p1, fmaxf(p0, x));   // :2188
+    else if constexpr (OP == kExp) return expf(x);                     // :2195
+    else if constexpr (OP == kSqrt) return sqrtf(x);                   // :2202
+    else return x;                                                     // cast
+}
+
+template <int OP>
+__global__ void __launch_bounds__(kThreads) unary_vec_kernel(const void* x, int in_dt, void* out, int out_dt,
+                                                            int64_t chunks, float p0, float p1) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride) {
+        float v[8];
+        load8<true>(x, in_dt, i * 8, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = unary_value<OP>(v[e], p0, p1);
+        store8(out, out_dt, i * 8, v);
+    }
+}
+template <int OP>
+__global__ void __launch_bounds__(kThreads) unary_scalar_kernel(const void* x, int in_dt, void* out, int out_dt,
+                                                               int64_t count, float p0, float p1) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride)
+        store1(out, out_dt, i, unary_value<OP>(load1(x, in_dt, i), p0, p1));
+}
+__global__ void __launch_bounds__(kThreads) cast_u8_kernel(const uint8_t* x, void* out, int out_dt, int64_t count) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride)
+        store1(out, out_dt, i, static_cast<float>(x[i]));
+}
+
+template <int OP>
+int launch_unary(const void* x, int in_dt, void* out, int out_dt, int64_t count, float p0, float p1,
+                 cudaStream_t stream, const char* what) {
+    VRB_REQUIRE(x && out, VRB_ERR_INVALID, "%s: null tensor", what);
+    VRB_REQUIRE(count > 0, VRB_ERR_INVALID, "%s: element count must be positive", what);
+    VRB_REQUIRE(is_float_dtype(in_dt) && is_float_dtype(out_dt), VRB_ERR_UNSUPPORTED, "%s: dtype must be F32 or BF16", what);
+    if (vec8_ok(count, {x, out})) {
+        const int64_t chunks = count / 8;
+        unary_vec_kernel<OP><<<grid_for((chunks + kThreads - 1) / kThreads, kPerSm), kThreads, 0, stream>>>(
+            x, in_dt, out, out_dt, chunks, p0, p1);
+    } else {
+        unary_scalar_kernel<OP><<<grid_for((count + kThreads - 1) / kThreads, kPerSm), kThreads, 0, stream>>>(
+            x, in_dt, out, out_dt, count, p0, p1);
+    }
+    return after_launch(what);
+}
+
+// ------------------------------------------------------------------------------ binary --
+struct Meta { int rank; int64_t shape[8]; int64_t strides[8]; };
+
+template <int KIND>
+__device__ __forceinline__ float binary_value(float a, float b) {
+    if constexpr (KIND == VRB_ADD) return __fadd_rn(a, b);
+    else if constexpr (KIND == VRB_MUL) return __fmul_rn(a, b);
+    else if constexpr (KIND == VRB_DIV) return __fdiv_rn(a, b);
+    else return fmaxf(a, b);
+}
+
+// Operand classes after shape analysis: the whole tensor, one scalar, or a dense trailing
+// block that repeats every `period` elements (the adaLN [S,D] op [1,1,D] case).
+template <int KIND>
+__global__ void __launch_bounds__(kThreads) binary_flat_vec_kernel(const void* a, const void* b, void* out, int dt,
+                                                                   int64_t chunks, int64_t a_period, int64_t b_period,
+                                                                   int64_t count) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride) {
+        const int64_t e0 = i * 8;
+        float av[8], bv[8];
+        if (a_period == count) load8<true>(a, dt, e0, av);
+        else if (a_period == 1) { const float s = load1(a, dt, 0);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) av[e] = s; }
+        else load8<false>(a, dt, e0 % a_period, av);
+        if (b_period == count) load8<true>(b, dt, e0, bv);
+        else if (b_period == 1) { const float s = load1(b, dt, 0);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) bv[e] = s; }
+        else load8<false>(b, dt, e0 % b_period, bv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) av[e] = binary_value<KIND>(av[e], bv[e]);
+        store8(out, dt, e0, av);
+    }
+}
+
+__device__ __forceinline__ int64_t broadcast_offset(int64_t linear, const Meta& o, const Meta& in) {
+    int64_t offset = 0;
+    const int shift = o.rank - in.rank;
+    for (int d = o.rank - 1; d >= 0; --d) {
+        const int64_t c = linear % o.shape[d];
+        linear /= o.shape[d];
+        const int id = d - shift;
+        if (id >= 0 && in.shape[id] != 1) offset += c * in.strides[id];
+    }
+    return offset;
+}
+template <int KIND>
+__global__ void __launch_bounds__(kThreads) binary_general_kernel(const void* a, const void* b, void* out, int dt,
+                                                                  int64_t count, Meta om, Meta am, Meta bm) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride)
+        store1(out, dt, i, binary_value<KIND>(load1(a, dt, broadcast_offset(i, om, am)),
+                                              load1(b, dt, broadcast_offset(i, om, bm))));
+}
+
+Meta make_meta(const int64_t* shape, int rank) {
+    Meta m{};
+    m.rank = rank;
+    int64_t s = 1;
+    for (int d = rank - 1; d >= 0; --d) { m.shape[d] = shape[d]; m.strides[d] = s; s *= shape[d]; }
+    return m;
+}
+// Elements after which a trailing-dense operand repeats; 0 when the operand broadcasts along
+// an inner axis and needs general indexing.
+int64_t flat_period(const Meta& out, const Meta& in) {
+    int64_t elements = 1;
+    for (int d = 0; d < in.rank; ++d) elements *= in.shape[d];
+    if (elements <= 0) return 0;
+    int64_t remaining = elements;
+    const int shift = out.rank - in.rank;
+    for (int d = out.rank - 1; remaining > 1 && d >= 0; --d) {
+        const int id = d - shift;
+        if (id < 0 || in.shape[id] != out.shape[d]) return 0;
+        remaining /= out.shape[d];
+    }
+    return remaining == 1 ? elements : 0;
+}
+
+template <int KIND>
+int launch_binary(const void* a, const Meta& am, const void* b, const Meta& bm, void* out, const Meta& om,
+                  int64_t count, int dt, cudaStream_t stream) {
+    const int64_t ap = flat_period(om, am), bp = flat_period(om, bm);
+    const bool periods_ok = ap && bp && (ap == count || ap == 1 || ap % 8 == 0) && (bp == count || bp == 1 || bp % 8 == 0);
+    if (periods_ok && vec8_ok(count, {a, b, out})) {
+        const int64_t chunks = count / 8;
+        binary_flat_vec_kernel<KIND><<<grid_for((chunks + kThreads - 1) / kThreads, kPerSm), kThreads, 0, stream>>>(
+            a, b, out, dt, chunks, ap, bp, count);
+    } else {
+        binary_general_kernel<KIND><<<grid_for((count + kThreads - 1) / kThreads, kPerSm), kThreads, 0, stream>>>(
+            a, b, out, dt, count, om, am, bm);
+    }
+    return after_launch("binary");
+}
+
+// ------------------------------------------------------------------------------ SwiGLU --
+// mochi.cpp:195-202: silu(b) is stored (rounded to the tensor dtype) before a * silu(b).
+__global__ void __launch_bounds__(kThreads) swiglu_kernel(const void* proj, void* out, int dt, int64_t rows,
+                                                         int64_t hidden_chunks) {
+    const int64_t total = rows * hidden_chunks;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t row = i / hidden_chunks, chunk = i - row * hidden_chunks;
+        const int64_t in0 = (row * 2 * hidden_chunks + chunk) * 8;
+        float a[8], g[8];
+        load8<true>(proj, dt, in0, a);
+        load8<true>(proj, dt, in0 + hidden_chunks * 8, g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] = __fmul_rn(a[e], round_to(dt, activation_value(VRB_SILU, g[e])));
+        store8(out, dt, i * 8, a);
+    }
+}
+__global__ void __launch_bounds__(kThreads) swiglu_scalar_kernel(const void* proj, void* out, int dt, int64_t rows,
+                                                                int64_t hidden) {
+    const int64_t total = rows * hidden;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t row = i / hidden, c = i - row * hidden;
+        const float a = load1(proj, dt, row * 2 * hidden + c), g = load1(proj, dt, row * 2 * hidden + hidden + c);
+        store1(out, dt, i, __fmul_rn(a, round_to(dt, activation_value(VRB_SILU, g))));
+    }
+}
+
+// ----------------------------------------------------------------------- gated residual --
+// common.cpp:134-144 with T = state dtype: T(res) + round_T(T(branch) * T(gate)).
+__global__ void __launch_bounds__(kThreads) gated_residual_kernel(
+        const void* res, int res_dt, const void* branch, int br_dt, const void* gate, int gate_dt,
+        void* out, int state_dt, int64_t rows, int64_t width_chunks, int64_t rows_per_vector, int64_t vectors) {
+    const int64_t total = rows * width_chunks;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        float r[8], b[8], g[8];
+        load8<true>(res, res_dt, i * 8, r);
+        load8<true>(branch, br_dt, i * 8, b);
+        if (gate) {
+            const int64_t row = i / width_chunks, chunk = i - row * width_chunks;
+            const int64_t vec = (row / rows_per_vector) % vectors;
+            load8<false>(gate, gate_dt, (vec * width_chunks + chunk) * 8, g);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float br = round_to(state_dt, b[e]);
+            if (gate) br = round_to(state_dt, __fmul_rn(br, round_to(state_dt, g[e])));
+            r[e] = __fadd_rn(round_to(state_dt, r[e]), br);
+        }
+        store8(out, state_dt, i * 8, r);
+    }
+}
+__global__ void __launch_bounds__(kThreads) gated_residual_scalar_kernel(
+        const void* res, int res_dt, const void* branch, int br_dt, const void* gate, int gate_dt,
+        void* out, int state_dt, int64_t rows, int64_t width, int64_t rows_per_vector, int64_t vectors) {
+    const int64_t total = rows * width;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        float br = round_to(state_dt, load1(branch, br_dt, i));
+        if (gate) {
+            const int64_t row = i / width, c = i - row * width;
+            const int64_t vec = (row / rows_per_vector) % vectors;
+            br = round_to(state_dt, __fmul_rn(br, round_to(state_dt, load1(gate, gate_dt, vec * width + c))));
+        }
+        store1(out, state_dt, i, __fadd_rn(round_to(state_dt, load1(res, res_dt, i)), br));
+    }
+}
+
+// -------------------------------------------------------------------------------- RoPE --
+// rope_kernel :1200-1215 (standalone form).  Tables may broadcast along any axis.
+__global__ void __launch_bounds__(kThreads) rope_general_kernel(const void* x, int x_dt, const void* cosine, const void* sine,
+                                                               int f_dt, void* out, int64_t count, Meta xm, Meta fm) {
+    const int64_t width = xm.shape[xm.rank - 1];
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride) {
+        const int64_t col = i % width;
+        const float paired = load1(x, x_dt, i - col + (col ^ 1));
+        const float rotated = (i & 1) ? paired : -paired;
+        const int64_t f = broadcast_offset(i, xm, fm);
+        store1(out, x_dt, i, __fadd_rn(__fmul_rn(load1(x, x_dt, i), load1(cosine, f_dt, f)),
+                                       __fmul_rn(rotated, load1(sine, f_dt, f))));
+    }
+}
+// Two table layouts cover the pipelines.  heads == 0: the table equals x's trailing axes and
+// repeats every `period` elements.  heads > 0: one table row of `width` per token shared by
+// that token's `heads` rows of x ([.., T, 1, W] against [.., T, H, W]); f_tokens table rows.
+__global__ void __launch_bounds__(kThreads) rope_vec_kernel(const void* x, int x_dt, const void* cosine, const void* sine,
+                                                           int f_dt, void* out, int64_t chunks, int64_t width,
+                                                           int64_t heads, int64_t f_tokens, int64_t period) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride) {
+        float v[8], co[8], si[8], r[8];
+        const int64_t e0 = i * 8;
+        load8<true>(x, x_dt, e0, v);
+        int64_t f;
+        if (heads > 0) f = ((e0 / (heads * width)) % f_tokens) * width + e0 % width;
+        else f = e0 % period;
+        load8<false>(cosine, f_dt, f, co);
+        load8<false>(sine, f_dt, f, si);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float rotated = (e & 1) ? v[e ^ 1] : -v[e ^ 1];
+            r[e] = __fadd_rn(__fmul_rn(v[e], co[e]), __fmul_rn(rotated, si[e]));
+        }
+        store8(out, x_dt, i * 8, r);
+    }
+}
+
+// ------------------------------------------------------------------------ dequantisation --
+// decode_fp8_e4m3fn :630-638 as bit manipulation: value = sign * (e ? (8+m) * 2^(e-10) : m * 2^-9).
+// Both forms are exact in F32, so this equals ldexpf() on every one of the 256 codes
+// (0x7f / 0xff give +-480, no NaN case, as in the reference).
+__device__ __forceinline__ float decode_fp8(uint32_t raw) {
+    const uint32_t e = (raw >> 3) & 0xfu, m = raw & 0x7u;
+    const float mag = e ? __uint_as_float(((e + 120u) << 23) | (m << 20))   // (1 + m/8) * 2^(e-7)
+                        : static_cast<float>(m) * 0.001953125f;             // m * 2^-9
+    return (raw & 0x80u) ? -mag : mag;
+}
+template <int KIND>
+__device__ __forceinline__ float quant_value(const uint8_t* packed, int64_t index) {
+    if constexpr (KIND == VRB_Q_FP8_E4M3FN) return decode_fp8(packed[index]);
+    else if constexpr (KIND == VRB_Q_INT8) return static_cast<float>(static_cast<int8_t>(packed[index]));
+    else {
+        const uint8_t byte = packed[index / 2];
+        const uint32_t nibble = (index & 1) ? (byte >> 4) : (byte & 0xfu);
+        return static_cast<float>(nibble >= 8 ? static_cast<int>(nibble) - 16 : static_cast<int>(nibble));
+    }
+}
+// General form (:641-658): any group size, any alignment.
+template <int KIND>
+__global__ void __launch_bounds__(kThreads) dequant_scalar_kernel(const uint8_t* packed, const float* scales, void* out,
+                                                                 int out_dt, int64_t count, int64_t inner, int64_t groups,
+                                                                 int64_t group_size) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride) {
+        const int64_t outer = i / inner, group = (i % inner) / group_size;
+        store1(out, out_dt, i, __fmul_rn(quant_value<KIND>(packed, i), scales[outer * groups + group]));
+    }
+}
+// Byte-per-element kinds with inner % 16 == 0 and group_size % 16 == 0: 16 codes per thread
+// per step (one 16-byte load), one scale per step, two 16-byte (bf16) or four (f32) stores.
+template <int KIND>
+__global__ void __launch_bounds__(kThreads) dequant_vec_kernel(const uint8_t* packed, const float* scales, void* out,
+                                                              int out_dt, int64_t chunks, int64_t inner_chunks,
+                                                              int64_t groups, int64_t group_chunks) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride) {
+        const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(packed) + i);
+        const int64_t outer = i / inner_chunks, group = (i - outer * inner_chunks) / group_chunks;
+        const float scale = __ldg(scales + outer * groups + group);
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+        float v[16];
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t code = (words[w] >> (8 * k)) & 0xffu;
+                const float q = KIND == VRB_Q_FP8_E4M3FN ? decode_fp8(code)
+                                                         : static_cast<float>(static_cast<int8_t>(code));
+                v[w * 4 + k] = __fmul_rn(q, scale);
+            }
+        float lo[8], hi[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { lo[e] = v[e]; hi[e] = v[8 + e]; }
+        store8(out, out_dt, i * 16, lo);
+        store8(out, out_dt, i * 16 + 8, hi);
+    }
+}
+
+// -------------------------------------------------------------------- sampler arithmetic --
+// precision_scalar_binary (precision.cpp:196-223): value (x) coefficient.
+//   declared role: F32 product, result rounded to the storage dtype
+//   legacy:        coefficient rounded to the storage dtype first, product rounded
+__device__ __forceinline__ float coef_mul(int dt, int role, float v, float coef) {
+    return round_to(dt, __fmul_rn(v, role ? coef : round_to(dt, coef)));
+}
+struct SamplerParams {
+    const void* sample; const void* uncond; const void* cond; void* guided; void* out;
+    int dt, mode;            // mode 0 cfg, 1 euler, 2 cfg+euler, 3 flow_to_x0
+    int role, axpy_role;     // declared scalar role of the guidance / of the solver-or-sigma coefficient
+    float scale, coefficient; // coefficient: value of the one-element Euler / sigma multiplier tensor
+};
+// cfg:   g = u + ((c + u*(-1)) * s)                                  sampling.cpp:181-183
+// euler: x' = x + p * k, k = delta * (+-1) computed on a 1-element tensor  sampling.cpp:185-193
+__device__ __forceinline__ float cfg_value(int dt, int role, float u, float c, float s) {
+    const float n = coef_mul(dt, role, u, -1.0f);
+    const float d = round_to(dt, __fadd_rn(c, n));
+    const float e = coef_mul(dt, role, d, s);
+    return round_to(dt, __fadd_rn(u, e));
+}
+__device__ __forceinline__ float axpy_value(int dt, int role, float x, float p, float k) {
+    return round_to(dt, __fadd_rn(x, coef_mul(dt, role, p, k)));
+}
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads) sampler_kernel(SamplerParams q, int64_t n) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        constexpr int W = VEC ? 8 : 1;
+        float x[8], u[8], c[8], g[8], y[8];
+        if constexpr (VEC) {
+            if (q.sample) load8<true>(q.sample, q.dt, i * 8, x);
+            if (q.uncond) load8<true>(q.uncond, q.dt, i * 8, u);
+            if (q.cond) load8<true>(q.cond, q.dt, i * 8, c);
+        } else {
+            if (q.sample) x[0] = load1(q.sample, q.dt, i);
+            if (q.uncond) u[0] = load1(q.uncond, q.dt, i);
+            if (q.cond) c[0] = load1(q.cond, q.dt, i);
+        }
+#pragma unroll
+        for (int e = 0; e < W; ++e) {
+            if (q.mode == 0) y[e] = cfg_value(q.dt, q.role, u[e], c[e], q.scale);
+            else if (q.mode == 1 || q.mode == 3) y[e] = axpy_value(q.dt, q.axpy_role, x[e], u[e], q.coefficient);
+            else { g[e] = cfg_value(q.dt, q.role, u[e], c[e], q.scale); y[e] = axpy_value(q.dt, q.axpy_role, x[e], g[e], q.coefficient); }
+        }
+        if constexpr (VEC) {
+            if (q.mode == 2 && q.guided) store8(q.guided, q.dt, i * 8, g);
+            store8(q.out, q.dt, i * 8, y);
+        } else {
+            if (q.mode == 2 && q.guided) store1(q.guided, q.dt, i, g[0]);
+            store1(q.out, q.dt, i, y[0]);
+        }
+    }
+}
+int launch_sampler(SamplerParams q, int64_t count, cudaStream_t stream, const char* what) {
+    VRB_REQUIRE(q.out && count > 0, VRB_ERR_INVALID, "%s: null output or empty tensor", what);
+    VRB_REQUIRE(is_float_dtype(q.dt), VRB_ERR_UNSUPPORTED, "%s: dtype must be F32 or BF16", what);
+    if (vec8_ok(count, {q.sample, q.uncond, q.cond, q.guided, q.out})) {
+        const int64_t chunks = count / 8;
+        sampler_kernel<true><<<grid_for((chunks + kThreads - 1) / kThreads, kPerSm), kThreads, 0, stream>>>(q, chunks);
+    } else {
+        sampler_kernel<false><<<grid_for((count + kThreads - 1) / kThreads, kPerSm), kThreads, 0, stream>>>(q, count);
+    }
+    return after_launch(what);
+}
+// The Euler coefficient: k = delta (x) (+-1) is itself a product on a one-element F32 tensor
+// (exact), so k = +-delta in F32 for both scalar contracts.
+inline float euler_coefficient(float delta, int subtract) { return subtract ? -delta : delta; }
+
+}  // namespace
+}  // namespace vrb
+
+using namespace vrb;
+
+extern "C" int vrb_cast(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t count, vrb_stream stream) {
+    if (src_dtype == VRB_U8) {
+        VRB_REQUIRE(src && dst && count > 0, VRB_ERR_INVALID, "cast: null tensor or empty");
+        VRB_REQUIRE(is_float_dtype(dst_dtype), VRB_ERR_UNSUPPORTED, "Unsupported CUDA dtype conversion");
+        cast_u8_kernel<<<grid_for((count + kThreads - 1) / kThreads, kPerSm), kThreads, 0, as_stream(stream)>>>(
+            static_cast<const uint8_t*>(src), dst, dst_dtype, count);
+        return after_launch("cast");
+    }
+    return launch_unary<kCast>(src, src_dtype, dst, dst_dtype, count, 0.f, 0.f, as_stream(stream), "cast");
+}
+
+extern "C" int vrb_activation(int kind, const void* x, void* out, int dtype, int64_t count, vrb_stream stream) {
+    cudaStream_t s = as_stream(stream);
+    switch (kind) {
+        case VRB_SILU: return launch_unary<kActSilu>(x, dtype, out, dtype, count, 0.f, 0.f, s, "activation");
+        case VRB_GELU: return launch_unary<kActGelu>(x, dtype, out, dtype, count, 0.f, 0.f, s, "activation");
+        case VRB_GELU_TANH: return launch_unary<kActGeluTanh>(x, dtype, out, dtype, count, 0.f, 0.f, s, "activation");
+        case VRB_TANH: return launch_unary<kActTanh>(x, dtype, out, dtype, count, 0.f, 0.f, s, "activation");
+        case VRB_RELU: return launch_unary<kActRelu>(x, dtype, out, dtype, count, 0.f, 0.f, s, "activation");
+        default: set_error("activation: unknown kind %d", kind); return VRB_ERR_INVALID;
+    }
+}
+extern "C" int vrb_clamp(const void* x, void* out, int dtype, int64_t count, float minimum, float maximum, vrb_stream stream) {
+    VRB_REQUIRE(minimum <= maximum, VRB_ERR_INVALID, "Invalid clamp bounds");
+    return launch_unary<kClamp>(x, dtype, out, dtype, count, minimum, maximum, as_stream(stream), "clamp");
+}
+extern "C" int vrb_exp(const void* x, void* out, int dtype, int64_t count, vrb_stream stream) {
+    return launch_unary<kExp>(x, dtype, out, dtype, count, 0.f, 0.f, as_stream(stream), "exp");
+}
+extern "C" int vrb_sqrt(const void* x, void* out, int dtype, int64_t count, vrb_stream stream) {
+    return launch_unary<kSqrt>(x, dtype, out, dtype, count, 0.f, 0.f, as_stream(stream), "sqrt");
+}
+
+extern "C" int vrb_binary(int kind, const void* a, const int64_t* a_shape, int a_rank,
+                          const void* b, const int64_t* b_shape, int b_rank,
+                          void* out, int dtype, vrb_stream stream) {
+    VRB_REQUIRE(a && b && out, VRB_ERR_INVALID, "binary: null tensor");
+    VRB_REQUIRE(a_rank >= 0 && b_rank >= 0 && a_rank <= 8 && b_rank <= 8, VRB_ERR_INVALID, "CUDA primitive rank exceeds 8");
+    VRB_REQUIRE((a_rank == 0 || a_shape) && (b_rank == 0 || b_shape), VRB_ERR_INVALID, "binary: null shape");
+    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "binary: dtype must be F32 or BF16");
+    const int rank = a_rank > b_rank ? a_rank : b_rank;
+    int64_t oshape[8];
+    int64_t count = 1;
+    for (int i = 0; i < rank; ++i) {
+        const int ai = i - (rank - a_rank), bi = i - (rank - b_rank);
+        const int64_t av = ai < 0 ? 1 : a_shape[ai], bv = bi < 0 ? 1 : b_shape[bi];
+        VRB_REQUIRE(av > 0 && bv > 0, VRB_ERR_INVALID, "binary: extents must be positive");
+        VRB_REQUIRE(av == bv || av == 1 || bv == 1, VRB_ERR_INVALID, "Incompatible broadcast shapes");
+        oshape[i] = av > bv ? av : bv;
+        count *= oshape[i];
+    }
+    const Meta om = make_meta(oshape, rank), am = make_meta(a_shape, a_rank), bm = make_meta(b_shape, b_rank);
+    cudaStream_t s = as_stream(stream);
+    switch (kind) {
+        case VRB_ADD: return launch_binary<VRB_ADD>(a, am, b, bm, out, om, count, dtype, s);
+        case VRB_MUL: return launch_binary<VRB_MUL>(a, am, b, bm, out, om, count, dtype, s);
+        case VRB_DIV: return launch_binary<VRB_DIV>(a, am, b, bm, out, om, count, dtype, s);
+        case VRB_MAX: return launch_binary<VRB_MAX>(a, am, b, bm, out, om, count, dtype, s);
+        default: set_error("binary: unknown kind %d", kind); return VRB_ERR_INVALID;
+    }
+}
+
+extern "C" int vrb_swiglu(const void* projected, void* out, int dtype, int64_t rows, int64_t hidden, vrb_stream stream) {
+    VRB_REQUIRE(projected && out, VRB_ERR_INVALID, "swiglu: null tensor");
+    VRB_REQUIRE(rows > 0 && hidden > 0, VRB_ERR_INVALID, "swiglu: extents must be positive");
+    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "swiglu: dtype must be F32 or BF16");
+    if (hidden % 8 == 0 && aligned16(projected) && aligned16(out)) {
+        const int64_t work = rows * (hidden / 8);
+        swiglu_kernel<<<grid_for((work + kThreads - 1) / kThreads, kPerSm), kThreads, 0, as_stream(stream)>>>(
+            projected, out, dtype, rows, hidden / 8);
+    } else {
+        const int64_t work = rows * hidden;
+        swiglu_scalar_kernel<<<grid_for((work + kThreads - 1) / kThreads, kPerSm), kThreads, 0, as_stream(stream)>>>(
+            projected, out, dtype, rows, hidden);
+    }
+    return after_launch("swiglu");
+}
+
+extern "C" int vrb_gated_residual(const void* residual, int residual_dtype, const void* branch, int branch_dtype,
+                                  const void* gate, int gate_dtype, int64_t rows_per_vector, int64_t gate_vectors,
+                                  void* out, int state_dtype, int64_t rows, int64_t width, vrb_stream stream) {
+    VRB_REQUIRE(residual && branch && out, VRB_ERR_INVALID, "gated_residual: null tensor");
+    VRB_REQUIRE(rows > 0 && width > 0, VRB_ERR_INVALID, "gated_residual: extents must be positive");
+    VRB_REQUIRE(!gate || (rows_per_vector > 0 && gate_vectors > 0), VRB_ERR_INVALID,
+                "gated_residual: rows_per_vector and vector count must be positive");
+    VRB_REQUIRE(is_float_dtype(residual_dtype) && is_float_dtype(branch_dtype) && is_float_dtype(state_dtype) &&
+                (!gate || is_float_dtype(gate_dtype)), VRB_ERR_UNSUPPORTED, "gated_residual: dtypes must be F32 or BF16");
+    if (width % 8 == 0 && aligned16(residual) && aligned16(branch) && aligned16(out) && (!gate || aligned16(gate))) {
+        const int64_t work = rows * (width / 8);
+        gated_residual_kernel<<<grid_for((work + kThreads - 1) / kThreads, kPerSm), kThreads, 0, as_stream(stream)>>>(
+            residual, residual_dtype, branch, branch_dtype, gate, gate_dtype, out, state_dtype, rows, width / 8,
+            rows_per_vector, gate_vectors);
+    } else {
+        const int64_t work = rows * width;
+        gated_residual_scalar_kernel<<<grid_for((work + kThreads - 1) / kThreads, kPerSm), kThreads, 0, as_stream(stream)>>>(
+            residual, residual_dtype, branch, branch_dtype, gate, gate_dtype, out, state_dtype, rows, width,
+            rows_per_vector, gate_vectors);
+    }
+    return after_launch("gated_residual");
+}
+
+extern "C" int vrb_rope(const void* x, int x_dtype, const int64_t* x_shape, int x_rank,
+                        const void* cosine, const void* sine, int f_dtype, const int64_t* f_shape, int f_rank,
+                        void* out, vrb_stream stream) {
+    VRB_REQUIRE(x && cosine && sine && out && x_shape && f_shape, VRB_ERR_INVALID, "rope: null tensor");
+    VRB_REQUIRE(x_rank >= 1 && x_rank <= 8 && f_rank >= 0 && f_rank <= x_rank, VRB_ERR_INVALID, "CUDA primitive rank exceeds 8");
+    VRB_REQUIRE(is_float_dtype(x_dtype) && is_float_dtype(f_dtype), VRB_ERR_UNSUPPORTED, "rope: dtypes must be F32 or BF16");
+    VRB_REQUIRE(x_shape[x_rank - 1] % 2 == 0, VRB_ERR_INVALID, "RoPE width must be even");
+    int64_t count = 1;
+    for (int d = 0; d < x_rank; ++d) { VRB_REQUIRE(x_shape[d] > 0, VRB_ERR_INVALID, "rope: extents must be positive"); count *= x_shape[d]; }
+    for (int d = 0; d < f_rank; ++d) {
+        const int64_t xv = x_shape[d + (x_rank - f_rank)];
+        VRB_REQUIRE(f_shape[d] == xv || f_shape[d] == 1, VRB_ERR_INVALID, "Incompatible broadcast shapes");
+    }
+    const Meta xm = make_meta(x_shape, x_rank), fm = make_meta(f_shape, f_rank);
+    const int64_t width = x_shape[x_rank - 1];
+    // Fast layouts (after dropping the table's leading broadcast axes): the table equals x's
+    // trailing axes, or it is [T.., 1, W] against x's [T.., H, W].
+    bool fast = width % 8 == 0 && aligned16(x) && aligned16(out) && aligned16(cosine) && aligned16(sine) &&
+                f_rank >= 1 && f_shape[f_rank - 1] == width;
+    int64_t heads = 0, f_tokens = 1, period = 1;
+    if (fast) {
+        const int shift = x_rank - f_rank;
+        int first = 0;
+        while (first < f_rank - 1 && f_shape[first] == 1) ++first;
+        bool same = true;
+        for (int k = first; k < f_rank; ++k) { same = same && f_shape[k] == x_shape[k + shift]; period *= f_shape[k]; }
+        if (!same) {
+            const int h = f_rank - 2;
+            bool shared = h >= first && f_shape[h] == 1;
+            for (int k = first; shared && k < h; ++k) { shared = f_shape[k] == x_shape[k + shift]; f_tokens *= f_shape[k]; }
+            if (shared) heads = x_shape[h + shift];
+            else fast = false;
+        }
+    }
+    cudaStream_t s = as_stream(stream);
+    if (fast) {
+        const int64_t chunks = count / 8;
+        rope_vec_kernel<<<grid_for((chunks + kThreads - 1) / kThreads, kPerSm), kThreads, 0, s>>>(
+            x, x_dtype, cosine, sine, f_dtype, out, chunks, width, heads, f_tokens, period);
+    } else {
+        rope_general_kernel<<<grid_for((count + kThreads - 1) / kThreads, kPerSm), kThreads, 0, s>>>(
+            x, x_dtype, cosine, sine, f_dtype, out, count, xm, fm);
+    }
+    return after_launch("rope");
+}
+
+extern "C" int vrb_dequantize(int kind, const void* packed, const float* scales, void* out, int out_dtype,
+                              int64_t rows, int64_t inner, int64_t group_size, vrb_stream stream) {
+    VRB_REQUIRE(packed && scales && out, VRB_ERR_INVALID, "dequantize: null tensor");
+    VRB_REQUIRE(rows > 0 && inner > 0 && group_size > 0, VRB_ERR_INVALID, "Unsupported quantized tensor layout/policy");
+    VRB_REQUIRE(is_float_dtype(out_dtype), VRB_ERR_UNSUPPORTED, "Quantized tensors require CPU storage and float compute output");
+    VRB_REQUIRE(kind >= 0 && kind <= 2, VRB_ERR_UNSUPPORTED, "Unsupported quantized tensor packing");
+    const int64_t count = rows * inner, groups = (inner + group_size - 1) / group_size;
+    const uint8_t* p = static_cast<const uint8_t*>(packed);
+    cudaStream_t s = as_stream(stream);
+    const bool vec = kind != VRB_Q_INT4 && inner % 16 == 0 && group_size % 16 == 0 && aligned16(packed) && aligned16(out);
+    if (vec) {
+        const int64_t chunks = count / 16;
+        const int grid = grid_for((chunks + kThreads - 1) / kThreads, kPerSm);
+        if (kind == VRB_Q_FP8_E4M3FN)
+            dequant_vec_kernel<VRB_Q_FP8_E4M3FN><<<grid, kThreads, 0, s>>>(p, scales, out, out_dtype, chunks, inner / 16, groups, group_size / 16);
+        else
+            dequant_vec_kernel<VRB_Q_INT8><<<grid, kThreads, 0, s>>>(p, scales, out, out_dtype, chunks, inner / 16, groups, group_size / 16);
+    } else {
+        const int grid = grid_for((count + kThreads - 1) / kThreads, kPerSm);
+        if (kind == VRB_Q_FP8_E4M3FN) dequant_scalar_kernel<VRB_Q_FP8_E4M3FN><<<grid, kThreads, 0, s>>>(p, scales, out, out_dtype, count, inner, groups, group_size);
+        else if (kind == VRB_Q_INT8) dequant_scalar_kernel<VRB_Q_INT8><<<grid, kThreads, 0, s>>>(p, scales, out, out_dtype, count, inner, groups, group_size);
+        else dequant_scalar_kernel<VRB_Q_INT4><<<grid, kThreads, 0, s>>>(p, scales, out, out_dtype, count, inner, groups, group_size);
+    }
+    return after_launch("dequantize");
+}
+
+extern "C" int vrb_cfg_combine(const void* unconditional, const void* conditional, void* out, int dtype,
+                               int64_t count, float scale, int scalar_role, vrb_stream stream) {
+    VRB_REQUIRE(unconditional && conditional, VRB_ERR_INVALID, "cfg_combine: null tensor");
+    SamplerParams q{}; q.uncond = unconditional; q.cond = conditional; q.out = out; q.dt = dtype;
+    q.role = scalar_role; q.mode = 0; q.scale = scale;
+    return launch_sampler(q, count, as_stream(stream), "cfg_combine");
+}
+extern "C" int vrb_euler_update(const void* sample, const void* prediction, void* out, int dtype,
+                                int64_t count, float delta, int subtract_prediction, int scalar_role, vrb_stream stream) {
+    VRB_REQUIRE(sample && prediction, VRB_ERR_INVALID, "euler_update: null tensor");
+    SamplerParams q{}; q.sample = sample; q.uncond = prediction; q.out = out; q.dt = dtype;
+    q.axpy_role = scalar_role; q.mode = 1; q.coefficient = euler_coefficient(delta, subtract_prediction);
+    return launch_sampler(q, count, as_stream(stream), "euler_update");
+}
+extern "C" int vrb_flow_to_x0(const void* sample, const void* model_output, void* out, int dtype,
+                              int64_t count, float sigma, int scalar_role, vrb_stream stream) {
+    VRB_REQUIRE(sample && model_output, VRB_ERR_INVALID, "flow_to_x0: null tensor");
+    SamplerParams q{}; q.sample = sample; q.uncond = model_output; q.out = out; q.dt = dtype;
+    q.axpy_role = scalar_role; q.mode = 3; q.coefficient = -sigma;
+    return launch_sampler(q, count, as_stream(stream), "flow_to_x0");
+}
+extern "C" int vrb_cfg_euler(const void* sample, const void* unconditional, const void* conditional,
+                             void* guided, void* out, int dtype, int64_t count, float scale, float delta,
+                             int subtract_prediction, int guidance_role, int solver_role, vrb_stream stream) {
+    VRB_REQUIRE(sample && unconditional && conditional, VRB_ERR_INVALID, "cfg_euler: null tensor");
+    SamplerParams q{}; q.sample = sample; q.uncond = unconditional; q.cond = conditional; q.guided = guided; q.out = out;
+    q.dt = dtype; q.role = guidance_role; q.axpy_role = solver_role; q.mode = 2; q.scale = scale;
+    q.coefficient = euler_coefficient(delta, subtract_prediction);
+    return launch_sampler(q, count, as_stream(stream), "cfg_euler");
+}

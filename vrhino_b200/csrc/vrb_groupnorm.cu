@@ -1,0 +1,336 @@
+// GroupNorm (+SiLU) and channel-axis RMSNorm (+SiLU) for the VAE feature maps.
+//
+// GroupNorm reference: native/src/backend/cuda/cuda_backend.cu:1884-2030 (kernels) and
+// :4919-5008 (host).  The reference reads x three times (shifted mean, centred variance,
+// normalise) plus a separate SiLU kernel.  Here x is read twice and written once:
+//   1. gn_partial_kernel   every CTA reduces one slice of one (batch, group) unit to the
+//                          shifted sums S1 = sum(x - a), S2 = sum((x - a)^2) with
+//                          a = the unit's first element (the reference's anchor); F32 inside a
+//                          128-bit vector, double across vectors
+//   2. gn_finalize_kernel  adds the slices of a unit in slice order (deterministic),
+//                          mean = a + S1/n, var = S2/n - (S1/n)^2, inv = rsqrtf(var + eps)
+//   3. gn_apply_kernel     y = fma((x - mean) * inv, gamma, beta) rounded to x's dtype, then
+//                          optionally SiLU of that rounded value, rounded again
+// The shifted one-pass variance in double agrees with the reference's centred two-pass F32
+// variance to F32 rounding.  The three pieces are also exported separately so a tensor that is
+// split along its spatial axis over several GPUs can add the per-slice sums between 1 and 2.
+//
+// Axis RMSNorm reference: rms_norm_axis_parallel_kernel :1045-1095.
+#include "vrb_common.cuh"
+
+namespace vrb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxSplits = 64;
+
+struct GnGeom {
+    int64_t batch, channels, spatial, count, units;
+    int groups, channels_per;
+};
+
+// Slices per unit: enough CTAs to fill the machine several times over, at least 16 K elements
+// per slice so the per-CTA reduction stays negligible.
+int choose_splits(int64_t units, int64_t count) {
+    const int64_t want = (static_cast<int64_t>(sm_count()) * 8 + units - 1) / units;
+    int64_t by_size = count / 16384;
+    if (by_size < 1) by_size = 1;
+    int64_t s = want < by_size ? want : by_size;
+    if (s > kMaxSplits) s = kMaxSplits;
+    if (s < 1) s = 1;
+    return static_cast<int>(s);
+}
+
+__device__ __forceinline__ void block_reduce2(double& a, double& b, double (*ws)[8]) {
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, offset);
+        b += __shfl_xor_sync(0xffffffffu, b, offset);
+    }
+    if ((threadIdx.x & 31) == 0) { ws[0][threadIdx.x >> 5] = a; ws[1][threadIdx.x >> 5] = b; }
+    __syncthreads();
+    a = 0.0; b = 0.0;
+    for (int w = 0; w < kThreads / 32; ++w) { a += ws[0][w]; b += ws[1][w]; }
+}
+
+// partial[(unit * splits + split) * 2 + {0,1}] = {S1, S2} over the slice.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads) gn_partial_kernel(const void* x, int dt, const float* shift,
+                                                             double* partial, int64_t count, int splits) {
+    __shared__ double ws[2][8];
+    const int64_t unit = blockIdx.x / splits;
+    const int split = blockIdx.x % splits;
+    const int64_t base = unit * count;
+    const float a = shift ? shift[unit] : load1(x, dt, base);
+    double s1 = 0.0, s2 = 0.0;
+    if constexpr (VEC) {
+        const int64_t chunks = count >> 3;
+        const int64_t begin = chunks * split / splits, end = chunks * (split + 1) / splits;
+        for (int64_t c = begin + threadIdx.x; c < end; c += kThreads) {
+            float v[8];
+            load8<true>(x, dt, base + c * 8, v);
+            float t1 = 0.0f, t2 = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float d = __fsub_rn(v[e], a);
+                t1 = __fadd_rn(t1, d);
+                t2 = __fmaf_rn(d, d, t2);
+            }
+            s1 += static_cast<double>(t1);
+            s2 += static_cast<double>(t2);
+        }
+    } else {
+        const int64_t begin = count * split / splits, end = count * (split + 1) / splits;
+        for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
+            const double d = static_cast<double>(__fsub_rn(load1(x, dt, base + i), a));
+            s1 += d;
+            s2 = fma(d, d, s2);
+        }
+    }
+    block_reduce2(s1, s2, ws);
+    if (threadIdx.x == 0) {
+        partial[(unit * splits + split) * 2] = s1;
+        partial[(unit * splits + split) * 2 + 1] = s2;
+    }
+}
+
+// moments[unit*3 + {0,1,2}] = {n, S1, S2}: slices added in slice order.
+__global__ void gn_collect_kernel(const double* partial, double* moments, int64_t units, int splits, int64_t count) {
+    const int64_t unit = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (unit >= units) return;
+    double s1 = 0.0, s2 = 0.0;
+    for (int s = 0; s < splits; ++s) { s1 += partial[(unit * splits + s) * 2]; s2 += partial[(unit * splits + s) * 2 + 1]; }
+    moments[unit * 3] = static_cast<double>(count);
+    moments[unit * 3 + 1] = s1;
+    moments[unit * 3 + 2] = s2;
+}
+
+__global__ void gn_finalize_kernel(const double* moments, const float* shift, const void* x, int dt, int64_t count,
+                                   int64_t units, float eps, float* mean, float* inverse) {
+    const int64_t unit = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (unit >= units) return;
+    const double a = shift ? static_cast<double>(shift[unit]) : static_cast<double>(load1(x, dt, unit * count));
+    const double n = moments[unit * 3], m1 = moments[unit * 3 + 1] / n;
+    double var = moments[unit * 3 + 2] / n - m1 * m1;
+    if (var < 0.0) var = 0.0;
+    mean[unit] = static_cast<float>(a + m1);
+    inverse[unit] = rsqrtf(__fadd_rn(static_cast<float>(var), eps));
+}
+
+__device__ __forceinline__ float gn_value(float x, float mean, float inv, float gamma, float beta, int dt, int silu) {
+    float y = round_to(dt, __fmaf_rn(__fmul_rn(__fsub_rn(x, mean), inv), gamma, beta));
+    if (silu) y = activation_value(VRB_SILU, y);
+    return y;
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads) gn_apply_kernel(const void* x, int dt, const void* weight, int w_dt,
+                                                           const void* bias, int b_dt, void* out, GnGeom g,
+                                                           const float* mean, const float* inverse, int silu) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int64_t total = g.units * g.count;
+    const int64_t items = VEC ? total >> 3 : total;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < items; i += stride) {
+        const int64_t e0 = VEC ? i * 8 : i;
+        const int64_t plane = e0 / g.spatial;          // batch * channels + channel
+        const int64_t channel = plane % g.channels;
+        const int64_t unit = (plane / g.channels) * g.groups + channel / g.channels_per;
+        const float m = __ldg(mean + unit), inv = __ldg(inverse + unit);
+        // gamma / beta are converted to x's dtype first (:4929)
+        const float gamma = weight ? round_to(dt, load1(weight, w_dt, channel)) : 1.0f;
+        const float beta = bias ? round_to(dt, load1(bias, b_dt, channel)) : 0.0f;
+        if constexpr (VEC) {
+            float v[8];
+            load8<true>(x, dt, e0, v);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = gn_value(v[e], m, inv, gamma, beta, dt, silu);
+            store8(out, dt, e0, v);
+        } else {
+            store1(out, dt, e0, gn_value(load1(x, dt, e0), m, inv, gamma, beta, dt, silu));
+        }
+    }
+}
+
+int make_geom(GnGeom& g, int64_t batch, int64_t channels, int64_t spatial, int groups, const char* what) {
+    VRB_REQUIRE(batch > 0 && channels > 0 && spatial > 0 && groups > 0 && channels % groups == 0, VRB_ERR_INVALID,
+                "%s: group norm shape/groups mismatch", what);
+    g.batch = batch; g.channels = channels; g.spatial = spatial; g.groups = groups;
+    g.channels_per = static_cast<int>(channels / groups);
+    g.count = g.channels_per * spatial;
+    g.units = batch * groups;
+    VRB_REQUIRE(g.units * kMaxSplits <= 0x7fffffffLL, VRB_ERR_INVALID,
+                "%s: group norm launch extent exceeds CUDA grid capacity", what);
+    return VRB_OK;
+}
+
+size_t workspace_layout(int64_t units, size_t* moments_off, size_t* mean_off) {
+    size_t partial_bytes = static_cast<size_t>(units) * kMaxSplits * 2 * sizeof(double);
+    size_t moments_bytes = static_cast<size_t>(units) * 3 * sizeof(double);
+    size_t stats_bytes = static_cast<size_t>(units) * 2 * sizeof(float);
+    auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+    if (moments_off) *moments_off = up(partial_bytes);
+    if (mean_off) *mean_off = up(partial_bytes) + up(moments_bytes);
+    return up(partial_bytes) + up(moments_bytes) + up(stats_bytes);
+}
+
+int run_moments(const void* x, int dt, const GnGeom& g, const float* shift, double* partial, double* moments,
+                cudaStream_t s) {
+    const int splits = choose_splits(g.units, g.count);
+    const bool vec = g.count % 8 == 0 && aligned16(x);
+    const int grid = static_cast<int>(g.units * splits);
+    if (vec) gn_partial_kernel<true><<<grid, kThreads, 0, s>>>(x, dt, shift, partial, g.count, splits);
+    else gn_partial_kernel<false><<<grid, kThreads, 0, s>>>(x, dt, shift, partial, g.count, splits);
+    if (int rc = after_launch("group_norm moments")) return rc;
+    gn_collect_kernel<<<static_cast<int>((g.units + 127) / 128), 128, 0, s>>>(partial, moments, g.units, splits, g.count);
+    return after_launch("group_norm collect");
+}
+
+int run_apply(const void* x, int dt, const void* weight, int w_dt, const void* bias, int b_dt, void* out,
+              const GnGeom& g, const float* mean, const float* inverse, int silu, cudaStream_t s) {
+    const bool vec = g.spatial % 8 == 0 && aligned16(x) && aligned16(out);
+    const int64_t total = g.units * g.count;
+    if (vec) {
+        const int64_t chunks = total / 8;
+        gn_apply_kernel<true><<<grid_for((chunks + kThreads - 1) / kThreads, 8), kThreads, 0, s>>>(
+            x, dt, weight, w_dt, bias, b_dt, out, g, mean, inverse, silu);
+    } else {
+        gn_apply_kernel<false><<<grid_for((total + kThreads - 1) / kThreads, 8), kThreads, 0, s>>>(
+            x, dt, weight, w_dt, bias, b_dt, out, g, mean, inverse, silu);
+    }
+    return after_launch("group_norm apply");
+}
+
+// ---- RMSNorm over an inner axis: x [outer, axis, inner] ------------------------------------
+// Pass 1 accumulates sum of squares over the axis in double per inner position, pass 2
+// normalises; a thread owns 8 consecutive inner positions (VEC) or one.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads) rms_axis_kernel(const void* x, int dt, const void* weight, int w_dt,
+                                                           void* out, int64_t outer, int64_t axis, int64_t inner,
+                                                           float eps, int silu) {
+    constexpr int W = VEC ? 8 : 1;
+    const int64_t inner_items = VEC ? inner >> 3 : inner;
+    const int64_t items = outer * inner_items;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < items; i += stride) {
+        const int64_t o = i / inner_items, p = (i - o * inner_items) * W;
+        const int64_t base = o * axis * inner + p;
+        double sq[W];
+#pragma unroll
+        for (int e = 0; e < W; ++e) sq[e] = 0.0;
+        for (int64_t c = 0; c < axis; ++c) {
+            float v[8];
+            if constexpr (VEC) load8<false>(x, dt, base + c * inner, v);
+            else v[0] = load1(x, dt, base + c * inner);
+#pragma unroll
+            for (int e = 0; e < W; ++e) sq[e] = fma(static_cast<double>(v[e]), static_cast<double>(v[e]), sq[e]);
+        }
+        float inv[W];
+#pragma unroll
+        for (int e = 0; e < W; ++e) inv[e] = rsqrtf(__fadd_rn(static_cast<float>(sq[e] / static_cast<double>(axis)), eps));
+        for (int64_t c = 0; c < axis; ++c) {
+            float v[8];
+            if constexpr (VEC) load8<false>(x, dt, base + c * inner, v);
+            else v[0] = load1(x, dt, base + c * inner);
+            const float w = weight ? round_to(dt, load1(weight, w_dt, c)) : 1.0f;
+#pragma unroll
+            for (int e = 0; e < W; ++e) {
+                float y = __fmul_rn(v[e], inv[e]);
+                if (dt == VRB_BF16) y = round_to_bf16(y);
+                if (weight) y = __fmul_rn(y, w);
+                y = round_to(dt, y);
+                if (silu) y = activation_value(VRB_SILU, y);
+                v[e] = y;
+            }
+            if constexpr (VEC) store8(out, dt, base + c * inner, v);
+            else store1(out, dt, base + c * inner, v[0]);
+        }
+    }
+}
+
+}  // namespace
+}  // namespace vrb
+
+using namespace vrb;
+
+extern "C" size_t vrb_group_norm_workspace_bytes(int64_t batch, int groups) {
+    if (batch <= 0 || groups <= 0) return 0;
+    return workspace_layout(batch * groups, nullptr, nullptr);
+}
+
+extern "C" int vrb_group_norm(const void* x, int dtype, const void* weight, int weight_dtype,
+                              const void* bias, int bias_dtype, void* out,
+                              int64_t batch, int64_t channels, int64_t spatial, int groups, float eps,
+                              int fuse_silu, void* workspace, size_t workspace_bytes, vrb_stream stream) {
+    VRB_REQUIRE(x && out, VRB_ERR_INVALID, "group_norm: null tensor");
+    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "group_norm: dtype must be F32 or BF16");
+    GnGeom g;
+    if (int rc = make_geom(g, batch, channels, spatial, groups, "group_norm")) return rc;
+    size_t moments_off, mean_off;
+    const size_t need = workspace_layout(g.units, &moments_off, &mean_off);
+    VRB_REQUIRE(workspace && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0,
+                VRB_ERR_WORKSPACE, "group_norm: workspace needs %zu bytes, 256-byte aligned", need);
+    char* ws = static_cast<char*>(workspace);
+    double* partial = reinterpret_cast<double*>(ws);
+    double* moments = reinterpret_cast<double*>(ws + moments_off);
+    float* mean = reinterpret_cast<float*>(ws + mean_off);
+    float* inverse = mean + g.units;
+    cudaStream_t s = as_stream(stream);
+    if (int rc = run_moments(x, dtype, g, nullptr, partial, moments, s)) return rc;
+    gn_finalize_kernel<<<static_cast<int>((g.units + 127) / 128), 128, 0, s>>>(moments, nullptr, x, dtype, g.count,
+                                                                             g.units, eps, mean, inverse);
+    if (int rc = after_launch("group_norm finalize")) return rc;
+    return run_apply(x, dtype, weight, weight_dtype, bias, bias_dtype, out, g, mean, inverse, fuse_silu, s);
+}
+
+extern "C" int vrb_group_norm_moments(const void* x, int dtype, int64_t batch, int64_t channels,
+                                      int64_t spatial_local, int groups, const float* shift,
+                                      double* moments, void* workspace, size_t workspace_bytes, vrb_stream stream) {
+    VRB_REQUIRE(x && moments && shift, VRB_ERR_INVALID, "group_norm_moments: null tensor");
+    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "group_norm_moments: dtype must be F32 or BF16");
+    GnGeom g;
+    if (int rc = make_geom(g, batch, channels, spatial_local, groups, "group_norm_moments")) return rc;
+    // A spatial slice of a unit is not contiguous: channel c of the unit starts at
+    // (unit*channels_per + c) * spatial_local, and those planes are adjacent, so the unit's
+    // slice IS one contiguous run of channels_per * spatial_local elements.
+    const size_t need = workspace_layout(g.units, nullptr, nullptr);
+    VRB_REQUIRE(workspace && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0,
+                VRB_ERR_WORKSPACE, "group_norm_moments: workspace needs %zu bytes, 256-byte aligned", need);
+    return run_moments(x, dtype, g, shift, static_cast<double*>(workspace), moments, as_stream(stream));
+}
+
+extern "C" int vrb_group_norm_finalize(const double* moments, const float* shift, int64_t units, float eps,
+                                       float* mean, float* inverse, vrb_stream stream) {
+    VRB_REQUIRE(moments && shift && mean && inverse && units > 0, VRB_ERR_INVALID, "group_norm_finalize: null tensor");
+    gn_finalize_kernel<<<static_cast<int>((units + 127) / 128), 128, 0, as_stream(stream)>>>(
+        moments, shift, nullptr, VRB_F32, 0, units, eps, mean, inverse);
+    return after_launch("group_norm finalize");
+}
+
+extern "C" int vrb_group_norm_apply(const void* x, int dtype, const void* weight, int weight_dtype,
+                                    const void* bias, int bias_dtype, void* out,
+                                    int64_t batch, int64_t channels, int64_t spatial_local, int groups,
+                                    const float* mean, const float* inverse, int fuse_silu, vrb_stream stream) {
+    VRB_REQUIRE(x && out && mean && inverse, VRB_ERR_INVALID, "group_norm_apply: null tensor");
+    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "group_norm_apply: dtype must be F32 or BF16");
+    GnGeom g;
+    if (int rc = make_geom(g, batch, channels, spatial_local, groups, "group_norm_apply")) return rc;
+    return run_apply(x, dtype, weight, weight_dtype, bias, bias_dtype, out, g, mean, inverse, fuse_silu, as_stream(stream));
+}
+
+extern "C" int vrb_rms_norm_axis(const void* x, int dtype, const void* weight, int weight_dtype, void* out,
+                                 int64_t outer, int64_t axis, int64_t inner, float eps, int fuse_silu,
+                                 vrb_stream stream) {
+    VRB_REQUIRE(x && out, VRB_ERR_INVALID, "rms_norm_axis: null tensor");
+    VRB_REQUIRE(outer > 0 && axis > 0 && inner > 0, VRB_ERR_INVALID, "rms_norm axis invalid");
+    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "rms_norm_axis: dtype must be F32 or BF16");
+    cudaStream_t s = as_stream(stream);
+    if (inner % 8 == 0 && aligned16(x) && aligned16(out)) {
+        const int64_t items = outer * (inner / 8);
+        rms_axis_kernel<true><<<grid_for((items + kThreads - 1) / kThreads, 8), kThreads, 0, s>>>(
+            x, dtype, weight, weight_dtype, out, outer, axis, inner, eps, fuse_silu);
+    } else {
+        const int64_t items = outer * inner;
+        rms_axis_kernel<false><<<grid_for((items + kThreads - 1) / kThreads, 8), kThreads, 0, s>>>(
+            x, dtype, weight, weight_dtype, out, outer, axis, inner, eps, fuse_silu);
+    }
+    return after_launch("rms_norm_axis");
+}

@@ -1,0 +1,534 @@
+"""Host-side mirror of the reference's operator interface for the non-GEMM path, on top of the
+C ABI in ``libvrb.so``.  torch is used for device memory and streams only.
+
+* ``B200Backend`` has the per-operator methods of ``vrhino::Backend``
+  (native/include/vrhino/backend.h:74-207 of the reference) that lie on the path, with the
+  same names, argument meaning, operand-dtype rules and error texts as the CUDA backend
+  (native/src/backend/cuda/cuda_backend.cu).
+* module functions ``modulate`` ... ``flow_to_x0`` have the signatures of the helper seams
+  (native/include/vrhino/architecture.h:63-86, native/include/vrhino/sampling.h:171-203) and
+  run the same chain of per-operator kernels.
+* ``fused_*`` functions are the one-pass forms of those chains; each states which chain it
+  replaces.  They return exactly what the chain returns.
+
+Every call goes to the CUDA library; nothing here computes on the CPU or through torch ops.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+
+import torch
+
+from . import _lib
+from ._lib import VrbError, call
+
+F32, BF16 = torch.float32, torch.bfloat16
+_CODE = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.uint8: _lib.U8}
+SILU, GELU, GELU_TANH, TANH, RELU = 0, 1, 2, 3, 4
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise VrbError("Tensor must be device-resident")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _code(t_or_dtype):
+    dt = t_or_dtype.dtype if isinstance(t_or_dtype, torch.Tensor) else t_or_dtype
+    try:
+        return _CODE[dt]
+    except KeyError:
+        raise VrbError(f"Unsupported dtype {dt}") from None
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _shape(t):
+    n = max(t.dim(), 1)
+    return (ctypes.c_int64 * n)(*t.shape), t.dim()
+
+
+def _dense(t):
+    if not t.is_contiguous():
+        raise VrbError("Tensor must be contiguous")
+    return t
+
+
+class HostScalar:
+    """A rank-0 host F32 value (scalar_f32 of native/src/tensor_util.cpp:20)."""
+
+    def __init__(self, value: float):
+        self.value = float(value)
+
+
+def scalar_f32(value: float) -> HostScalar:
+    return HostScalar(value)
+
+
+class B200Backend:
+    """Per-operator surface; every method launches one kernel of libvrb.so."""
+
+    def __init__(self, execution_dtype=BF16, device="cuda:0"):
+        _lib.load()
+        if not torch.cuda.is_available():
+            raise VrbError("B200Backend requires a CUDA device; there is no CPU path")
+        self.device = torch.device(device)
+        self.execution_dtype = execution_dtype
+        self._gn_workspace = None
+
+    def name(self):
+        return "b200"
+
+    # ---- dtype rule shared by the CUDA host wrappers ----
+    def _dtype_of(self, t):
+        if isinstance(t, torch.Tensor) and t.is_cuda and t.dtype in (F32, BF16):
+            return t.dtype
+        return self.execution_dtype
+
+    def copy_to_device(self, t, dtype):
+        if isinstance(t, HostScalar):
+            return torch.tensor(t.value, dtype=torch.float32).to(self.device).to(dtype) if dtype == F32 else \
+                self.cast(torch.tensor(t.value, dtype=torch.float32, device=self.device), dtype)
+        if not t.is_cuda:
+            t = t.to(self.device)
+        return t if t.dtype == dtype else self.cast(t, dtype)
+
+    def cast(self, x, dtype):
+        if isinstance(x, HostScalar):
+            return self.copy_to_device(x, dtype)
+        if not x.is_cuda:
+            x = x.to(self.device)
+        if x.dtype == dtype:
+            return x  # same handle, as the reference (cuda_backend.cu:3200)
+        x = _dense(x)
+        out = torch.empty(x.shape, dtype=dtype, device=x.device)
+        if x.numel():
+            call("vrb_cast", _ptr(x), _code(x), _ptr(out), _code(dtype), x.numel(), _stream())
+        return out
+
+    def _binary(self, kind, a_raw, b_raw):
+        if isinstance(a_raw, torch.Tensor) and a_raw.is_cuda and a_raw.dtype in (F32, BF16):
+            dtype = a_raw.dtype
+        elif isinstance(b_raw, torch.Tensor) and b_raw.is_cuda and b_raw.dtype in (F32, BF16):
+            dtype = b_raw.dtype
+        else:
+            dtype = self.execution_dtype
+        a, b = _dense(self.copy_to_device(a_raw, dtype)), _dense(self.copy_to_device(b_raw, dtype))
+        try:
+            shape = torch.broadcast_shapes(a.shape, b.shape)
+        except RuntimeError:
+            raise VrbError("Incompatible broadcast shapes") from None
+        out = torch.empty(shape, dtype=dtype, device=self.device)
+        (ashape, arank), (bshape, brank) = _shape(a), _shape(b)
+        call("vrb_binary", kind, _ptr(a), ashape, arank, _ptr(b), bshape, brank, _ptr(out), _code(dtype), _stream())
+        return out
+
+    def add(self, a, b): return self._binary(_lib.ADD, a, b)
+    def mul(self, a, b): return self._binary(_lib.MUL, a, b)
+    def div(self, a, b): return self._binary(_lib.DIV, a, b)
+    def maximum(self, a, b): return self._binary(_lib.MAX, a, b)
+
+    def reshape(self, x, shape):
+        return self.copy_to_device(x, self._dtype_of(x)).reshape(shape)
+
+    def _param(self, t):
+        """Optional affine parameter: uploaded if it still lives on the host."""
+        return None if t is None else _dense(t if t.is_cuda else t.to(self.device))
+
+    def layer_norm(self, raw, weight, bias, eps):
+        weight, bias = self._param(weight), self._param(bias)
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        width = x.shape[-1]
+        for name, t in (("weight", weight), ("bias", bias)):
+            if t is not None and t.numel() != width:
+                raise VrbError(f"layer norm {name} mismatch")
+        out = torch.empty_like(x)
+        call("vrb_layer_norm", _ptr(x), _code(x), _ptr(weight), _code(weight) if weight is not None else 0,
+             _ptr(bias), _code(bias) if bias is not None else 0, _ptr(out), x.numel() // width, width,
+             ctypes.c_float(eps), _stream())
+        return out
+
+    def rms_norm(self, raw, weight, eps, axis=-1, output=None):
+        """``output=None`` is the reference default (DType::F16 meaning "same as the input")."""
+        weight = self._param(weight)
+        rank = raw.dim()
+        if axis < 0:
+            axis += rank
+        if not 0 <= axis < rank:
+            raise VrbError("rms_norm axis invalid")
+        dtype = self._dtype_of(raw)
+        out_dtype = dtype if output is None else output
+        x = _dense(self.copy_to_device(raw, dtype))
+        if weight is not None and weight.numel() != x.shape[axis]:
+            raise VrbError("rms norm weight mismatch")
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        wcode = _code(weight) if weight is not None else 0
+        if axis == rank - 1:
+            width = x.shape[-1]
+            call("vrb_rms_norm", _ptr(x), _code(x), _ptr(weight), wcode, _ptr(out), _code(out_dtype),
+                 x.numel() // width, width, ctypes.c_float(eps), _stream())
+        else:
+            if out_dtype != dtype:
+                raise VrbError("mixed-dtype rms_norm currently requires final axis")
+            width = x.shape[axis]
+            inner = 1
+            for d in x.shape[axis + 1:]:
+                inner *= d
+            call("vrb_rms_norm_axis", _ptr(x), _code(x), _ptr(weight), wcode, _ptr(out),
+                 x.numel() // (width * inner), width, inner, ctypes.c_float(eps), 0, _stream())
+        return out
+
+    def activation(self, raw, kind):
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        out = torch.empty_like(x)
+        call("vrb_activation", int(kind), _ptr(x), _ptr(out), _code(x), x.numel(), _stream())
+        return out
+
+    def clamp(self, raw, minimum, maximum):
+        x = _dense(self.copy_to_device(raw, self._dtype_of(raw)))
+        out = torch.empty_like(x)
+        call("vrb_clamp", _ptr(x), _ptr(out), _code(x), x.numel(), ctypes.c_float(minimum), ctypes.c_float(maximum), _stream())
+        return out
+
+    def exp(self, raw):
+        x = _dense(self.copy_to_device(raw, self._dtype_of(raw)))
+        out = torch.empty_like(x)
+        call("vrb_exp", _ptr(x), _ptr(out), _code(x), x.numel(), _stream())
+        return out
+
+    def sqrt(self, raw):
+        x = _dense(self.copy_to_device(raw, self._dtype_of(raw)))
+        out = torch.empty_like(x)
+        call("vrb_sqrt", _ptr(x), _ptr(out), _code(x), x.numel(), _stream())
+        return out
+
+    def rope_nd(self, raw, cos_raw, sin_raw):
+        dtype = self._dtype_of(raw)
+        f_dtype = cos_raw.dtype if (cos_raw.is_cuda and cos_raw.dtype in (F32, BF16)) else dtype
+        x = _dense(self.copy_to_device(raw, dtype))
+        c, s = _dense(self.copy_to_device(cos_raw, f_dtype)), _dense(self.copy_to_device(sin_raw, f_dtype))
+        if c.shape != s.shape:
+            raise VrbError("RoPE frequency mismatch")
+        out = torch.empty_like(x)
+        (xs, xr), (fs, fr) = _shape(x), _shape(c)
+        call("vrb_rope", _ptr(x), _code(x), xs, xr, _ptr(c), _ptr(s), _code(c), fs, fr, _ptr(out), _stream())
+        return out
+
+    def dequantize(self, packed, scales, group_size, kind=_lib.Q_FP8, dtype=BF16, shape=None):
+        """copy_to_device of a quantized weight (cuda_backend.cu:3214-3296)."""
+        packed = _dense(packed.to(self.device))
+        scales = _dense(scales.to(self.device, torch.float32))
+        shape = tuple(shape or packed.shape)
+        rows = shape[0]
+        inner = 1
+        for d in shape[1:]:
+            inner *= d
+        out = torch.empty(shape, dtype=dtype, device=self.device)
+        call("vrb_dequantize", kind, _ptr(packed), _ptr(scales), _ptr(out), _code(dtype), rows, inner, group_size, _stream())
+        return out
+
+    def _workspace(self, batch, groups):
+        need = _lib.load().vrb_group_norm_workspace_bytes(batch, groups)
+        if self._gn_workspace is None or self._gn_workspace.numel() < need:
+            self._gn_workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        return self._gn_workspace, need
+
+    def group_norm(self, raw, groups, weight, bias, eps, fuse_silu=False):
+        if raw.dim() < 3 or groups <= 0 or raw.shape[1] % groups:
+            raise VrbError("group norm shape/groups mismatch")
+        weight, bias = self._param(weight), self._param(bias)
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        batch, channels = x.shape[0], x.shape[1]
+        spatial = x.numel() // (batch * channels)
+        out = torch.empty_like(x)
+        ws, need = self._workspace(batch, groups)
+        call("vrb_group_norm", _ptr(x), _code(x), _ptr(weight), _code(weight) if weight is not None else 0,
+             _ptr(bias), _code(bias) if bias is not None else 0, _ptr(out), batch, channels, spatial, groups,
+             ctypes.c_float(eps), int(fuse_silu), _ptr(ws), need, _stream())
+        return out
+
+
+# ------------------------------------------------------------------ precision policy view --
+GUIDANCE, SOLVER, SIGMA = "GuidanceCoefficient", "SolverCoefficient", "Sigma"
+
+
+@dataclass
+class Policy:
+    """The decisions of native/src/precision/precision.cpp the path depends on: residual-state
+    dtype, requested dtype, and which scalar roles a v2 policy declares.  Modulation and RoPE
+    contracts are F32 under every policy (precision.cpp:311-327)."""
+    requested: torch.dtype = BF16
+    residual: torch.dtype = BF16
+    scalar_roles: frozenset = field(default_factory=frozenset)
+
+    @staticmethod
+    def unqualified_default(dtype=BF16):
+        return Policy(dtype, dtype)
+
+    @staticmethod
+    def production_bf16():
+        return Policy(BF16, F32)
+
+    @staticmethod
+    def fp32():
+        return Policy(F32, F32)
+
+    def with_scalar_roles(self, roles):
+        return Policy(self.requested, self.residual, frozenset(roles))
+
+
+# ------------------------------------------------ helper seams: same chains as the reference --
+def modulate(be, policy, x, shift, scale):
+    """native/src/architectures/common.cpp:51-61"""
+    t = be.add(be.mul(be.cast(x, F32), be.add(scalar_f32(1.0), be.cast(scale, F32))), be.cast(shift, F32))
+    return be.cast(t, F32)
+
+
+def attention_norm(be, policy, x, weight, eps, axis=-1):
+    """common.cpp:62-68"""
+    return be.rms_norm(x, weight, eps, axis, F32)
+
+
+def operation_rope(be, policy, x, cosine, sine):
+    """common.cpp:69-76"""
+    return be.rope_nd(be.cast(x, F32), cosine, sine)
+
+
+def residual_add(be, policy, residual, branch):
+    """common.cpp:134-138"""
+    d = policy.residual
+    return be.add(be.cast(residual, d), be.cast(branch, d))
+
+
+def gated_residual(be, policy, residual, branch, gate):
+    """common.cpp:139-144"""
+    d = policy.residual
+    return be.add(be.cast(residual, d), be.mul(be.cast(branch, d), be.cast(gate, d)))
+
+
+def precision_scalar_binary(be, policy, role, value, coefficient: float):
+    """native/src/precision/precision.cpp:196-223, Multiply with a host F32 scalar."""
+    if role not in policy.scalar_roles:
+        return be.mul(value, scalar_f32(coefficient))
+    result = be.mul(be.copy_to_device(value, F32), be.copy_to_device(scalar_f32(coefficient), F32))
+    return result if result.dtype == value.dtype else be.cast(result, value.dtype)
+
+
+def cfg_combine(be, policy, unconditional, conditional, scale):
+    """native/src/sampling/sampling.cpp:181-183"""
+    neg = precision_scalar_binary(be, policy, GUIDANCE, unconditional, -1.0)
+    diff = be.add(conditional, neg)
+    return be.add(unconditional, precision_scalar_binary(be, policy, GUIDANCE, diff, scale))
+
+
+def _euler_delta(be, policy, delta: float) -> float:
+    """Magnitude the one-element coefficient tensor of euler_update holds (sampling.cpp:185-193):
+    with a declared solver role, or F32 execution, delta itself; otherwise the product of two
+    host scalars runs in the BF16 execution dtype and rounds delta to BF16."""
+    if SOLVER in policy.scalar_roles or be.execution_dtype == F32:
+        return float(delta)
+    return float(torch.tensor(delta, dtype=torch.float32).to(torch.bfloat16).float())
+
+
+def euler_update(be, policy, sample, prediction, delta: float, subtract_prediction: bool):
+    k = _euler_delta(be, policy, delta) * (-1.0 if subtract_prediction else 1.0)
+    return be.add(sample, precision_scalar_binary(be, policy, SOLVER, prediction, k))
+
+
+def flow_to_x0(be, policy, sample, model_output, sigma: float):
+    """sampling.cpp:200-202"""
+    return be.add(sample, precision_scalar_binary(be, policy, SIGMA, model_output, -sigma))
+
+
+# ------------------------------------------------------------------------- fused one-pass forms --
+def _vec_layout(rows, x_shape, vec):
+    """rows_per_vector / vector count for a [B,1,D]- or [B,S,D]-shaped (or flat [D]) vector."""
+    width = x_shape[-1]
+    n = vec.numel() // width
+    if n * width != vec.numel():
+        raise VrbError("Incompatible broadcast shapes")
+    if n == 1:
+        return rows, 1
+    if n == rows:
+        return 1, rows
+    batch = x_shape[0]
+    if n == batch and rows % batch == 0:
+        return rows // batch, batch
+    raise VrbError("Incompatible broadcast shapes")
+
+
+def fused_layer_norm_modulate(be, x, weight, bias, eps, shift, scale, out_dtype=BF16):
+    """cast(modulate(layer_norm(x, weight, bias, eps), shift, scale), out_dtype) in one pass."""
+    x = _dense(x)
+    width = x.shape[-1]
+    rows = x.numel() // width
+    rpv, nvec = _vec_layout(rows, x.shape, scale)
+    if shift is not None and (shift.dtype != scale.dtype or shift.numel() != scale.numel()):
+        raise VrbError("modulate: shift and scale must share dtype and shape")
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    call("vrb_layer_norm_modulate", _ptr(x), _code(x), _ptr(weight), _code(weight) if weight is not None else 0,
+         _ptr(bias), _code(bias) if bias is not None else 0, _ptr(_dense(scale)), _ptr(shift), _code(scale),
+         rpv, nvec, _ptr(out), _code(out_dtype), rows, width, ctypes.c_float(eps), _stream())
+    return out
+
+
+def fused_layer_norm_cast(be, x, weight, bias, eps, out_dtype=BF16):
+    """cast(layer_norm(x, weight, bias, eps), out_dtype) in one pass."""
+    x = _dense(x)
+    width = x.shape[-1]
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    call("vrb_layer_norm_cast", _ptr(x), _code(x), _ptr(weight), _code(weight) if weight is not None else 0,
+         _ptr(bias), _code(bias) if bias is not None else 0, _ptr(out), _code(out_dtype), x.numel() // width, width,
+         ctypes.c_float(eps), _stream())
+    return out
+
+
+def fused_rms_norm_modulate(be, x, eps, shift, scale, out_dtype=BF16):
+    """cast(modulate(rms_norm(x, None, eps), shift, scale), out_dtype) -- the LTX block."""
+    x = _dense(x)
+    width = x.shape[-1]
+    rows = x.numel() // width
+    rpv, nvec = _vec_layout(rows, x.shape, scale)
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    call("vrb_rms_norm_modulate", _ptr(x), _code(x), _ptr(_dense(scale)), _ptr(shift), _code(scale), rpv, nvec,
+         _ptr(out), _code(out_dtype), rows, width, ctypes.c_float(eps), _stream())
+    return out
+
+
+def fused_rms_norm_scale(be, x, scale, eps=1e-6):
+    """mul(rms_norm(x, None, eps), add(1, scale[B,1,D])) -- native/src/architectures/mochi.cpp:230-231."""
+    x = _dense(x)
+    width = x.shape[-1]
+    rows = x.numel() // width
+    rpv, nvec = _vec_layout(rows, x.shape, scale)
+    out = torch.empty_like(x)
+    call("vrb_rms_norm_scale", _ptr(x), _code(x), _ptr(_dense(scale)), _code(scale), rpv, nvec, _ptr(out),
+         rows, width, ctypes.c_float(eps), _stream())
+    return out
+
+
+def fused_rms_norm_rope(be, x, weight, eps, cosine, sine, heads=1, per_head_norm=False, out_dtype=BF16):
+    """cast(operation_rope(split_heads(attention_norm(x, weight, eps)), cos, sin), out_dtype).
+
+    x is [B, S, D].  per_head_norm=False: normalise over D, then split into `heads` (Wan,
+    native/src/architectures/wan.cpp:38-52); True: split first, normalise each head (Mochi,
+    mochi.cpp:182-187).  cosine/sine: F32 [1|B, S, 1, d] (shared by the heads) or [1|B, S, H, d],
+    or None for norm + cast only.
+    """
+    x = _dense(x)
+    width = x.shape[-1]
+    rows = x.numel() // width
+    head_width = width // heads
+    norm_width = head_width if per_head_norm else width
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    if cosine is None:
+        f_rows, f_width, rpf, cp, sp = 0, 8, 1, None, None
+    else:
+        if cosine.dtype != F32 or cosine.shape != sine.shape:
+            raise VrbError("RoPE frequency mismatch")
+        cosine, sine = _dense(cosine), _dense(sine)
+        f_width = cosine.shape[-1] * cosine.shape[-2] if cosine.dim() >= 2 else cosine.shape[-1]
+        if cosine.shape[-1] != head_width or f_width not in (head_width, width):
+            raise VrbError("Incompatible broadcast shapes")
+        f_rows = cosine.numel() // f_width
+        if f_rows not in (rows, rows // x.shape[0]):
+            raise VrbError("Incompatible broadcast shapes")
+        rpf, cp, sp = 1, _ptr(cosine), _ptr(sine)
+    call("vrb_rms_norm_rope", _ptr(x), _code(x), _ptr(weight), _code(weight), cp, sp, f_rows, f_width, rpf,
+         _ptr(out), _code(out_dtype), rows, width, norm_width, ctypes.c_float(eps), _stream())
+    return out
+
+
+def fused_gated_residual(be, policy, residual, branch, gate):
+    """gated_residual(...) / residual_add(...) (gate None) of common.cpp:134-144 in one pass."""
+    residual, branch = _dense(residual), _dense(branch)
+    width = residual.shape[-1]
+    rows = residual.numel() // width
+    rpv, nvec = (1, 1) if gate is None else _vec_layout(rows, residual.shape, gate)
+    out = torch.empty(residual.shape, dtype=policy.residual, device=residual.device)
+    call("vrb_gated_residual", _ptr(residual), _code(residual), _ptr(branch), _code(branch),
+         _ptr(gate), _code(gate) if gate is not None else 0, rpv, nvec, _ptr(out), _code(policy.residual),
+         rows, width, _stream())
+    return out
+
+
+def fused_rms_norm_gated_residual(be, policy, residual, branch, bounded_gate, eps=1e-6):
+    """gated_residual(residual, rms_norm(branch, None, eps), bounded_gate) -- mochi.cpp:204-211
+    after the tanh on the [B, D] gate."""
+    residual, branch = _dense(residual), _dense(branch)
+    width = residual.shape[-1]
+    rows = residual.numel() // width
+    rpv, nvec = _vec_layout(rows, residual.shape, bounded_gate)
+    out = torch.empty(residual.shape, dtype=policy.residual, device=residual.device)
+    call("vrb_rms_norm_gated_residual", _ptr(residual), _code(residual), _ptr(branch), _code(branch),
+         _ptr(_dense(bounded_gate)), _code(bounded_gate), rpv, nvec, _ptr(out), _code(policy.residual),
+         rows, width, ctypes.c_float(eps), _stream())
+    return out
+
+
+def fused_swiglu(be, projected):
+    """mul(parts[0], silu(parts[1])) with parts = split(projected, 2, -1) -- mochi.cpp:195-202."""
+    projected = _dense(projected)
+    hidden = projected.shape[-1] // 2
+    rows = projected.numel() // (2 * hidden)
+    out = torch.empty(projected.shape[:-1] + (hidden,), dtype=projected.dtype, device=projected.device)
+    call("vrb_swiglu", _ptr(projected), _ptr(out), _code(projected), rows, hidden, _stream())
+    return out
+
+
+def fused_cfg_combine(be, policy, unconditional, conditional, scale):
+    out = torch.empty_like(unconditional)
+    call("vrb_cfg_combine", _ptr(_dense(unconditional)), _ptr(_dense(conditional)), _ptr(out), _code(out),
+         out.numel(), ctypes.c_float(scale), int(GUIDANCE in policy.scalar_roles), _stream())
+    return out
+
+
+def fused_euler_update(be, policy, sample, prediction, delta, subtract_prediction):
+    out = torch.empty_like(sample)
+    k = _euler_delta(be, policy, delta)
+    call("vrb_euler_update", _ptr(_dense(sample)), _ptr(_dense(prediction)), _ptr(out), _code(out), out.numel(),
+         ctypes.c_float(k), int(subtract_prediction), int(SOLVER in policy.scalar_roles), _stream())
+    return out
+
+
+def fused_flow_to_x0(be, policy, sample, model_output, sigma):
+    out = torch.empty_like(sample)
+    call("vrb_flow_to_x0", _ptr(_dense(sample)), _ptr(_dense(model_output)), _ptr(out), _code(out), out.numel(),
+         ctypes.c_float(sigma), int(SIGMA in policy.scalar_roles), _stream())
+    return out
+
+
+def fused_cfg_euler(be, policy, sample, unconditional, conditional, scale, delta, subtract_prediction=True,
+                    want_guided=False):
+    """euler_update(sample, cfg_combine(u, c, scale), delta, subtract) in one pass."""
+    out = torch.empty_like(sample)
+    guided = torch.empty_like(sample) if want_guided else None
+    k = _euler_delta(be, policy, delta)
+    call("vrb_cfg_euler", _ptr(_dense(sample)), _ptr(_dense(unconditional)), _ptr(_dense(conditional)), _ptr(guided),
+         _ptr(out), _code(out), out.numel(), ctypes.c_float(scale), ctypes.c_float(k), int(subtract_prediction),
+         int(GUIDANCE in policy.scalar_roles), int(SOLVER in policy.scalar_roles), _stream())
+    return (out, guided) if want_guided else out
+
+
+def fused_group_norm_silu(be, x, groups, weight, bias, eps):
+    """activation(group_norm(x, ...), Silu) -- native/src/components/autoencoder_kl.cpp:40-41."""
+    return be.group_norm(x, groups, weight, bias, eps, fuse_silu=True)
+
+
+def fused_rms_channel_silu(be, x, gamma, eps=1e-12):
+    """silu(rms_norm(x, gamma, eps, axis=1)) -- native/src/components/executor.cpp:90-98 as the Wan VAE uses it."""
+    x = _dense(x)
+    axis = x.shape[1]
+    inner = x.numel() // (x.shape[0] * axis)
+    out = torch.empty_like(x)
+    call("vrb_rms_norm_axis", _ptr(x), _code(x), _ptr(gamma), _code(gamma), _ptr(out), x.shape[0], axis, inner,
+         ctypes.c_float(eps), 1, _stream())
+    return out

@@ -1,0 +1,125 @@
+"""The benchmark workloads: the non-GEMM operator chains of one DiT block / sampler step / VAE
+norm at the sizes the headline configurations name, expressed as lists of fused launches with
+their algorithmic HBM bytes.
+
+Algorithmic bytes of one launch = every distinct input tensor read once + every output
+written once, at storage dtype; broadcast vectors counted once.  GroupNorm, whose reduction
+unit is far larger than on-chip memory, counts its input twice (statistics pass + apply pass).
+
+Inputs are synthetic: activations ~N(0,1) (seeded on the device), modulation vectors
+~N(0,0.1), norm weights ~N(1,0.1); the "GEMM outputs" the chain consumes are synthesised too,
+since GEMMs and attention are not part of this path.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List
+
+import torch
+
+from . import ops, synth
+
+BF16, F32 = torch.bfloat16, torch.float32
+
+
+@dataclass
+class Launch:
+    name: str
+    fn: Callable[[], object]
+    bytes: int
+    kernels: int = 1
+
+
+def _nbytes(*tensors) -> int:
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None)
+
+
+def _randn(shape, dtype, gen, mean=0.0, std=1.0):
+    return (torch.randn(shape, device="cuda", dtype=torch.float32, generator=gen) * std + mean).to(dtype)
+
+
+class WanBlock:
+    """Wan2.1-1.3B style DiT block, one CFG branch: B=1, S tokens, D = heads*head_dim, FFN F.
+
+    Chain (native/src/architectures/wan_self_attention_graph.h:46-70 and wan.cpp:68-119 of the
+    reference): A LN->modulate->bf16; B rms(q),rms(k)->RoPE->bf16; C x + proj*gate;
+    D LN(gamma,beta); E rms(cross q), rms(cross k on the text rows); F x + cross;
+    G LN->modulate->bf16 (rows 3,4); H GELU-tanh on [S,F]; I x + ffn*gate.
+    """
+
+    def __init__(self, be, tokens=32760, dim=1536, heads=12, ffn=8960, grid=(21, 30, 52), text_tokens=512,
+                 hidden_dtype=BF16, seed=0):
+        assert grid[0] * grid[1] * grid[2] == tokens
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        self.be, S, D = be, tokens, dim
+        self.policy = ops.Policy(BF16, hidden_dtype)
+        hd = hidden_dtype
+        self.x = _randn((1, S, D), hd, g)
+        self.mod = _randn((1, 6, D), F32, g, std=0.1)                 # combined modulation rows
+        self.rows = [self.mod[:, i:i + 1, :].contiguous() for i in range(6)]
+        self.q, self.k, self.proj, self.cross_q, self.cross, self.ffn_out = (_randn((1, S, D), BF16, g) for _ in range(6))
+        self.cross_k = _randn((1, text_tokens, D), BF16, g)
+        self.ffn_hidden = _randn((1, S, ffn), BF16, g)
+        self.wq, self.wk, self.wcq, self.wck, self.gamma3 = (_randn((D,), F32, g, 1.0, 0.1) for _ in range(5))
+        self.beta3 = _randn((D,), F32, g, 0.0, 0.1)
+        cos, sin = synth.wan_rope_tables(*grid, head_dim=dim // heads)
+        self.cos, self.sin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+        self.heads, self.eps = heads, 1e-6
+        self.out = {}
+
+    def launches(self) -> List[Launch]:
+        be, p, r, e, o = self.be, self.policy, self.rows, self.eps, self.out
+        S, D = self.x.shape[1], self.x.shape[2]
+        act = S * D
+        hb = self.x.element_size()
+        vec = D * 4
+
+        def A(): o["A"] = ops.fused_layer_norm_modulate(be, self.x, None, None, e, r[0], r[1])
+        def Bq(): o["Bq"] = ops.fused_rms_norm_rope(be, self.q, self.wq, e, self.cos, self.sin, heads=self.heads)
+        def Bk(): o["Bk"] = ops.fused_rms_norm_rope(be, self.k, self.wk, e, self.cos, self.sin, heads=self.heads)
+        def C(): o["C"] = ops.fused_gated_residual(be, p, self.x, self.proj, r[2])
+        def Dn(): o["D"] = be.layer_norm(self.x, self.gamma3, self.beta3, e) if self.x.dtype == BF16 else \
+            ops.fused_layer_norm_cast(be, self.x, self.gamma3, self.beta3, e)
+        def Eq(): o["Eq"] = ops.fused_rms_norm_rope(be, self.cross_q, self.wcq, e, None, None, heads=self.heads)
+        def Ek(): o["Ek"] = ops.fused_rms_norm_rope(be, self.cross_k, self.wck, e, None, None, heads=self.heads)
+        def Fr(): o["F"] = ops.fused_gated_residual(be, p, self.x, self.cross, None)
+        def G(): o["G"] = ops.fused_layer_norm_modulate(be, self.x, None, None, e, r[3], r[4])
+        def H(): o["H"] = be.activation(self.ffn_hidden, ops.GELU_TANH)
+        def I(): o["I"] = ops.fused_gated_residual(be, p, self.x, self.ffn_out, r[5])
+
+        table = self.cos.numel() * 4 * 2
+        return [
+            Launch("A ln_modulate", A, act * (hb + 2) + 2 * vec),
+            Launch("B rms_rope q", Bq, act * 4 + vec + table // 2),
+            Launch("B rms_rope k", Bk, act * 4 + vec + table // 2),
+            Launch("C gated_residual", C, act * (hb + 2 + hb) + vec),
+            Launch("D ln_affine", Dn, act * (hb + 2) + 2 * vec),
+            Launch("E rms cross q", Eq, act * 4 + vec),
+            Launch("E rms cross k", Ek, self.cross_k.numel() * 4 + vec),
+            Launch("F residual_add", Fr, act * (hb + 2 + hb)),
+            Launch("G ln_modulate", G, act * (hb + 2) + 2 * vec),
+            Launch("H gelu_tanh", H, self.ffn_hidden.numel() * 4),
+            Launch("I gated_residual", I, act * (hb + 2 + hb) + vec),
+        ]
+
+
+def time_launches(launches: List[Launch], steps: int, warmup: int):
+    """Per-launch device time with CUDA events on the current stream; returns
+    (total_ms_per_step, {name: mean_ms})."""
+    for _ in range(warmup):
+        for l in launches:
+            l.fn()
+    torch.cuda.synchronize()
+    per = {l.name: 0.0 for l in launches}
+    events = []
+    for _ in range(steps):
+        for l in launches:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            l.fn()
+            b.record()
+            events.append((l.name, a, b))
+    torch.cuda.synchronize()
+    for name, a, b in events:
+        per[name] += a.elapsed_time(b) / steps
+    return sum(per.values()), per
