@@ -59,6 +59,14 @@ static inline void st(void* p, int dt, int64_t i, float v) {
     else ((float*)p)[i] = v;
 }
 static inline float rsqrt_ref(float v) { return 1.0f / sqrtf(v); }
+/* fmaxf as the device evaluates it (PTX max.f32): a NaN operand yields the other operand and
+ * -0 orders below +0; C's fmaxf leaves the sign of max(-0,+0) unspecified. */
+static inline float max_ref(float a, float b) {
+    if (isnan(a)) return b;
+    if (isnan(b)) return a;
+    if (a == 0.0f && b == 0.0f) return (signbit(a) && signbit(b)) ? -0.0f : 0.0f;
+    return a > b ? a : b;
+}
 
 uint16_t orc_f32_to_bf16(float f) { return f32_to_bf16(f); }
 float orc_bf16_to_f32(uint16_t v) { return bf16_to_f32(v); }
@@ -117,7 +125,7 @@ int orc_binary(int kind, const void* a, int a_rank, const int64_t* a_shape,
         if (kind == 0) r = av + bv;
         else if (kind == 1) r = av * bv;
         else if (kind == 2) r = av / bv;
-        else r = fmaxf(av, bv);
+        else r = max_ref(av, bv);
         st(out, dt, i, r);
     }
     return rank;
@@ -135,14 +143,14 @@ static inline float act_value(int kind, float x) {
         return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * inner));
     }
     if (kind == 3) return tanhf(x);
-    return fmaxf(x, 0.0f);
+    return max_ref(x, 0.0f);
 }
 void orc_activation(int kind, const void* x, void* out, int dt, int64_t n) {
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; ++i) st(out, dt, i, act_value(kind, ld(x, dt, i)));
 }
 void orc_clamp(const void* x, void* out, int dt, int64_t n, float lo, float hi) {
-    for (int64_t i = 0; i < n; ++i) st(out, dt, i, fminf(hi, fmaxf(lo, ld(x, dt, i))));
+    for (int64_t i = 0; i < n; ++i) st(out, dt, i, -max_ref(-hi, -max_ref(lo, ld(x, dt, i))));
 }
 void orc_exp(const void* x, void* out, int dt, int64_t n) {
     for (int64_t i = 0; i < n; ++i) st(out, dt, i, expf(ld(x, dt, i)));

@@ -60,8 +60,16 @@ def from_torch(x):
     return x.numpy(), "f32"
 
 
-def assert_close(orc, got, want, max_ulp=2, rel=1e-5, atol=0.0, what=""):
-    """bf16: <= max_ulp on the bf16 grid (or within atol when stated); f32: |d| <= atol + rel*|ref|."""
+def assert_close(orc, got, want, max_ulp=2, rel=1e-5, atol=0.0, flip_atol=0.0, flip_frac=0.0, what=""):
+    """bf16 outputs: <= max_ulp on the bf16 grid (or within atol when stated).
+    f32 outputs: |d| <= atol + max(rel*|ref|, 1e-8).
+
+    flip_atol / flip_frac: an F32 output computed FROM a value the reference rounds to bf16
+    mid-chain (the normalised value of rms_norm, the LayerNorm output under a bf16 hidden
+    state) jumps by one bf16 ulp of that intermediate whenever rsqrtf (CUDA) and 1/sqrtf (C)
+    differ in their last bit and the intermediate sits on a rounding boundary.  At most
+    flip_frac of the elements may miss the tight tolerance, and those must stay within
+    flip_atol (one bf16 ulp of the largest intermediate)."""
     data, tag = from_torch(got)
     assert tag == want.dtype, f"{what}: dtype {tag} != {want.dtype}"
     assert tuple(data.shape) == tuple(want.shape), f"{what}: shape {data.shape} != {want.shape}"
@@ -84,6 +92,10 @@ def assert_close(orc, got, want, max_ulp=2, rel=1e-5, atol=0.0, what=""):
     same_inf = np.isinf(data) & (data == want.data)
     bad = ~(diff <= tol) & ~both_nan & ~same_inf
     bad |= nan_mismatch
+    if bad.any() and flip_frac > 0:
+        within_flip = bad & (diff <= flip_atol) & ~nan_mismatch
+        if bad.mean() <= flip_frac and within_flip.sum() == bad.sum():
+            bad[:] = False
     if bad.any():
         i = np.unravel_index(np.argmax(np.where(bad, diff, 0)), diff.shape)
         raise AssertionError(f"{what}: {int(bad.sum())} of {diff.size} f32 elements out of tolerance; "
@@ -94,8 +106,13 @@ def assert_close(orc, got, want, max_ulp=2, rel=1e-5, atol=0.0, what=""):
 def assert_bits_equal(got, want, what=""):
     data, tag = from_torch(got)
     assert tag == want.dtype and tuple(data.shape) == tuple(want.shape), what
-    a = data.view(np.uint16 if tag == "bf16" else np.uint32)
-    b = want.data.view(np.uint16 if tag == "bf16" else np.uint32)
+    a = data.view(np.uint16 if tag == "bf16" else np.uint32).copy()
+    b = want.data.view(np.uint16 if tag == "bf16" else np.uint32).copy()
+    if tag == "f32":
+        # an F32 NaN produced by arithmetic carries a platform-chosen sign / payload
+        # (x86 gives 0xffc00000, the GPU 0x7fffffff); a NaN must match a NaN, bits aside
+        a[np.isnan(data)] = 0x7FC00000
+        b[np.isnan(want.data)] = 0x7FC00000
     if not np.array_equal(a, b):
         n = int((a != b).sum())
         raise AssertionError(f"{what}: {n} of {a.size} elements are not bit-identical")

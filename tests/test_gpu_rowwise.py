@@ -34,8 +34,11 @@ def test_layer_norm(orc, gpu, dtype, width, affine):
     b = orc.tensor(synth.normal((width,), 0.0, 0.1, seed=2), "f32") if affine else None
     want = orc.OracleBackend().layer_norm(x, w, b, 1e-6)
     got = be.layer_norm(to_torch(x), to_torch(w) if affine else None, to_torch(b) if affine else None, 1e-6)
-    frac = assert_close(orc, got, want, rel=1e-5, atol=2e-6 if affine else 0.0, what=f"layer_norm w={width}")
-    assert frac < 0.02
+    # outputs near zero come from x - mean cancelling: absolute 2e-6 (the reference's own F32 gate
+    # is 2e-5 + 2e-5|r|, native/tests/neural_graph_layernorm_tests.cpp:161)
+    frac = assert_close(orc, got, want, rel=1e-5, atol=2e-6, what=f"layer_norm w={width}")
+    if dtype == "bf16":
+        assert frac < 0.02, "more than 2% of the bf16 outputs are not bit-identical to the oracle"
 
 
 def test_layer_norm_repeat_is_bit_exact(gpu):
@@ -79,7 +82,9 @@ def test_rms_norm(orc, gpu, in_dt, out_dt, weighted, width):
     w = orc.tensor(synth.normal((width,), 1.0, 0.1, seed=3), "f32") if weighted else None
     want = orc.OracleBackend().rms_norm(x, w, 1e-6, -1, None if out_dt == in_dt else out_dt)
     got = be.rms_norm(to_torch(x), to_torch(w) if weighted else None, 1e-6, -1, None if out_dt == in_dt else _torch_dtype(out_dt))
-    assert_close(orc, got, want, rel=1e-5, what=f"rms_norm w={width}")
+    # bf16 -> F32 output: the normalised value is rounded to bf16 before the weight multiply
+    flips = dict(flip_atol=2.0 ** -8 * 8.0, flip_frac=2e-3) if (in_dt, out_dt) == ("bf16", "f32") else {}
+    assert_close(orc, got, want, rel=1e-5, what=f"rms_norm w={width}", **flips)
 
 
 def test_rms_norm_rejections(gpu):
@@ -131,7 +136,8 @@ def test_layer_norm_modulate(orc, gpu, x_dt, out_dt, width, batch, per_token):
     want = obe.cast(orc.modulate(obe, opol, obe.layer_norm(x, None, None, 1e-6), shift, scale), out_dt)
     tx, tsh, tsc = to_torch(x), to_torch(shift), to_torch(scale)
     got = ops.fused_layer_norm_modulate(be, tx, None, None, 1e-6, tsh, tsc, _torch_dtype(out_dt))
-    assert_close(orc, got, want, rel=1e-5, atol=2e-6, what="fused ln+modulate")
+    flips = dict(flip_atol=2.0 ** -8 * 8.0, flip_frac=2e-3) if (x_dt, out_dt) == ("bf16", "f32") else {}
+    assert_close(orc, got, want, rel=1e-5, atol=2e-6, what="fused ln+modulate", **flips)
     chain = be.cast(ops.modulate(be, ops.Policy(), be.layer_norm(tx, None, None, 1e-6), tsh, tsc), _torch_dtype(out_dt))
     import torch
     assert torch.equal(chain.view(torch.int16 if out_dt == "bf16" else torch.int32),
@@ -216,7 +222,7 @@ def test_rms_norm_rope(orc, gpu, out_dt, mode):
     got = ops.fused_rms_norm_rope(be, to_torch(x), to_torch(w), eps, to_torch(co) if c is not None else None,
                                   to_torch(si) if c is not None else None, heads=heads, per_head_norm=per_head,
                                   out_dtype=_torch_dtype(out_dt))
-    assert_close(orc, got, want, rel=1e-5, atol=1e-6, what=f"rms+rope {mode}")
+    assert_close(orc, got, want, rel=1e-5, atol=1e-6, flip_atol=2.0 ** -8 * 8.0, flip_frac=2e-3, what=f"rms+rope {mode}")
 
 
 @pytest.mark.parametrize("state", DTYPES)

@@ -51,6 +51,13 @@ inline int grid_for(int64_t work_items, int per_sm) {
     return static_cast<int>(g < 1 ? 1 : g);
 }
 
+// Table-driven bf16 unary / SwiGLU kernels (vrb_lut.cu).  op: 0-4 activation kinds, 5 clamp,
+// 6 exp, 7 sqrt.  Worth their ~10 us table fill only for large tensors.
+constexpr int64_t kLutMinElements = int64_t{32} << 20;
+bool unary_lut_applicable(int dtype, int64_t count, const void* x, const void* out);
+int launch_unary_lut(int op, const void* x, void* out, int64_t count, float p0, float p1, cudaStream_t stream);
+int launch_swiglu_lut(const void* proj, void* out, int64_t rows, int64_t hidden, cudaStream_t stream);
+
 // ------------------------------------------------------------------------ device side --
 #ifdef __CUDACC__
 
@@ -92,6 +99,16 @@ __device__ __forceinline__ void load8(const void* base, int dt, int64_t e, float
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);  // .x = lo (low half), RNE each
     return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Round eight F32 values to bf16 precision in place, two per conversion instruction.
+__device__ __forceinline__ void round8_bf16_inplace(float (&v)[8]) {
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+        const uint32_t h = pack_bf16x2(v[e], v[e + 1]);
+        v[e] = __uint_as_float(h << 16);
+        v[e + 1] = __uint_as_float(h & 0xffff0000u);
+    }
 }
 
 // Streaming store of 8 consecutive elements (RNE narrowing for bf16).

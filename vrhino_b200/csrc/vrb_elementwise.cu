@@ -35,13 +35,20 @@ __device__ __forceinline__ float unary_value(float x, float p0, float p1) {
 template <int OP>
 __global__ void __launch_bounds__(kThreads) unary_vec_kernel(const void* x, int in_dt, void* out, int out_dt,
                                                             int64_t chunks, float p0, float p1) {
+    constexpr int U = 4;  // independent 16-byte loads in flight per thread
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride) {
-        float v[8];
-        load8<true>(x, in_dt, i * 8, v);
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride * U) {
+        float v[U][8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = unary_value<OP>(v[e], p0, p1);
-        store8(out, out_dt, i * 8, v);
+        for (int u = 0; u < U; ++u)
+            if (i + u * stride < chunks) load8<true>(x, in_dt, (i + u * stride) * 8, v[u]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (i + u * stride >= chunks) break;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[u][e] = unary_value<OP>(v[u][e], p0, p1);
+            store8(out, out_dt, (i + u * stride) * 8, v[u]);
+        }
     }
 }
 template <int OP>
@@ -63,6 +70,8 @@ int launch_unary(const void* x, int in_dt, void* out, int out_dt, int64_t count,
     VRB_REQUIRE(x && out, VRB_ERR_INVALID, "%s: null tensor", what);
     VRB_REQUIRE(count > 0, VRB_ERR_INVALID, "%s: element count must be positive", what);
     VRB_REQUIRE(is_float_dtype(in_dt) && is_float_dtype(out_dt), VRB_ERR_UNSUPPORTED, "%s: dtype must be F32 or BF16", what);
+    if (OP != kCast && in_dt == out_dt && unary_lut_applicable(in_dt, count, x, out))
+        return launch_unary_lut(OP, x, out, count, p0, p1, stream);
     if (vec8_ok(count, {x, out})) {
         const int64_t chunks = count / 8;
         unary_vec_kernel<OP><<<grid_for((chunks + kThreads - 1) / kThreads, kPerSm), kThreads, 0, stream>>>(
@@ -203,26 +212,120 @@ __global__ void __launch_bounds__(kThreads) swiglu_scalar_kernel(const void* pro
 __global__ void __launch_bounds__(kThreads) gated_residual_kernel(
         const void* res, int res_dt, const void* branch, int br_dt, const void* gate, int gate_dt,
         void* out, int state_dt, int64_t rows, int64_t width_chunks, int64_t rows_per_vector, int64_t vectors) {
+    constexpr int U = 2;
     const int64_t total = rows * width_chunks;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        float r[8], b[8], g[8];
-        load8<true>(res, res_dt, i * 8, r);
-        load8<true>(branch, br_dt, i * 8, b);
-        if (gate) {
-            const int64_t row = i / width_chunks, chunk = i - row * width_chunks;
-            const int64_t vec = (row / rows_per_vector) % vectors;
-            load8<false>(gate, gate_dt, (vec * width_chunks + chunk) * 8, g);
+    for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
+        float r[U][8], b[U][8], g[U][8];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t i = i0 + u * stride;
+            if (i >= total) break;
+            load8<true>(res, res_dt, i * 8, r[u]);
+            load8<true>(branch, br_dt, i * 8, b[u]);
+            if (gate) {
+                const int64_t row = i / width_chunks, chunk = i - row * width_chunks;
+                const int64_t vec = vectors > 1 ? (row / rows_per_vector) % vectors : 0;
+                load8<false>(gate, gate_dt, (vec * width_chunks + chunk) * 8, g[u]);
+            }
         }
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            float br = round_to(state_dt, b[e]);
-            if (gate) br = round_to(state_dt, __fmul_rn(br, round_to(state_dt, g[e])));
-            r[e] = __fadd_rn(round_to(state_dt, r[e]), br);
+        for (int u = 0; u < U; ++u) {
+            const int64_t i = i0 + u * stride;
+            if (i >= total) break;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float br = round_to(state_dt, b[u][e]);
+                if (gate) br = round_to(state_dt, __fmul_rn(br, round_to(state_dt, g[u][e])));
+                r[u][e] = __fadd_rn(round_to(state_dt, r[u][e]), br);
+            }
+            store8(out, state_dt, i * 8, r[u]);
         }
-        store8(out, state_dt, i * 8, r);
     }
 }
+// Same arithmetic with the three tensor dtypes fixed at compile time and 32-bit indexing (the
+// common case: fewer than 2^31 chunks).  All-bf16 takes two packed bf16 instructions per pair of
+// elements: the product of two bf16 values is exact in F32, so mul.rn.bf16x2 rounds once exactly
+// like the reference's F32 multiply + bf16 store; likewise add.rn.bf16x2 (an exact bf16 sum needs
+// at most 24 bits whenever it is not absorbed by the larger operand).
+template <bool BF16>
+__device__ __forceinline__ void load8_typed(const void* base, int64_t e, float (&v)[8]) {
+    load8<true>(base, BF16 ? VRB_BF16 : VRB_F32, e, v);
+}
+template <bool RES_BF16, bool BR_BF16, bool STATE_BF16>
+__global__ void __launch_bounds__(kThreads) gated_residual_typed_kernel(
+        const void* __restrict__ res, const void* __restrict__ branch, const void* __restrict__ gate, int gate_dt,
+        void* __restrict__ out, unsigned total, unsigned width_chunks, unsigned rows_per_vector, unsigned vectors) {
+    constexpr int U = 2;
+    const unsigned stride = gridDim.x * blockDim.x;
+    for (unsigned i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
+        if constexpr (RES_BF16 && BR_BF16 && STATE_BF16) {
+            uint4 r[U], b[U];
+            float g[U][8];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const unsigned i = i0 + u * stride;
+                if (i >= total) break;
+                r[u] = __ldcs(static_cast<const uint4*>(res) + i);
+                b[u] = __ldcs(static_cast<const uint4*>(branch) + i);
+                if (gate) {
+                    const unsigned row = i / width_chunks, chunk = i - row * width_chunks;
+                    const unsigned vec = vectors > 1 ? (row / rows_per_vector) % vectors : 0;
+                    load8<false>(gate, gate_dt, (static_cast<int64_t>(vec) * width_chunks + chunk) * 8, g[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const unsigned i = i0 + u * stride;
+                if (i >= total) break;
+                const uint32_t rw[4] = {r[u].x, r[u].y, r[u].z, r[u].w};
+                const uint32_t bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+                uint32_t ow[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    __nv_bfloat162 br = *reinterpret_cast<const __nv_bfloat162*>(&bw[k]);
+                    if (gate) br = __hmul2_rn(br, __floats2bfloat162_rn(g[u][2 * k], g[u][2 * k + 1]));
+                    const __nv_bfloat162 sum = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&rw[k]), br);
+                    ow[k] = *reinterpret_cast<const uint32_t*>(&sum);
+                }
+                __stcs(static_cast<uint4*>(out) + i, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+            }
+        } else {
+            float r[U][8], b[U][8], g[U][8];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const unsigned i = i0 + u * stride;
+                if (i >= total) break;
+                load8_typed<RES_BF16>(res, static_cast<int64_t>(i) * 8, r[u]);
+                load8_typed<BR_BF16>(branch, static_cast<int64_t>(i) * 8, b[u]);
+                if (gate) {
+                    const unsigned row = i / width_chunks, chunk = i - row * width_chunks;
+                    const unsigned vec = vectors > 1 ? (row / rows_per_vector) % vectors : 0;
+                    load8<false>(gate, gate_dt, (static_cast<int64_t>(vec) * width_chunks + chunk) * 8, g[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const unsigned i = i0 + u * stride;
+                if (i >= total) break;
+                if constexpr (STATE_BF16) {
+                    if constexpr (!RES_BF16) round8_bf16_inplace(r[u]);
+                    if constexpr (!BR_BF16) round8_bf16_inplace(b[u]);
+                }
+                if (gate) {
+                    if constexpr (STATE_BF16) round8_bf16_inplace(g[u]);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) b[u][e] = __fmul_rn(b[u][e], g[u][e]);
+                    if constexpr (STATE_BF16) round8_bf16_inplace(b[u]);
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) r[u][e] = __fadd_rn(r[u][e], b[u][e]);
+                store8(out, STATE_BF16 ? VRB_BF16 : VRB_F32, static_cast<int64_t>(i) * 8, r[u]);
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) gated_residual_scalar_kernel(
         const void* res, int res_dt, const void* branch, int br_dt, const void* gate, int gate_dt,
         void* out, int state_dt, int64_t rows, int64_t width, int64_t rows_per_vector, int64_t vectors) {
@@ -480,6 +583,8 @@ extern "C" int vrb_swiglu(const void* projected, void* out, int dtype, int64_t r
     VRB_REQUIRE(projected && out, VRB_ERR_INVALID, "swiglu: null tensor");
     VRB_REQUIRE(rows > 0 && hidden > 0, VRB_ERR_INVALID, "swiglu: extents must be positive");
     VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "swiglu: dtype must be F32 or BF16");
+    if (dtype == VRB_BF16 && hidden % 8 == 0 && aligned16(projected) && aligned16(out) && rows * hidden >= kLutMinElements)
+        return launch_swiglu_lut(projected, out, rows, hidden, as_stream(stream));
     if (hidden % 8 == 0 && aligned16(projected) && aligned16(out)) {
         const int64_t work = rows * (hidden / 8);
         swiglu_kernel<<<grid_for((work + kThreads - 1) / kThreads, kPerSm), kThreads, 0, as_stream(stream)>>>(
@@ -501,7 +606,27 @@ extern "C" int vrb_gated_residual(const void* residual, int residual_dtype, cons
                 "gated_residual: rows_per_vector and vector count must be positive");
     VRB_REQUIRE(is_float_dtype(residual_dtype) && is_float_dtype(branch_dtype) && is_float_dtype(state_dtype) &&
                 (!gate || is_float_dtype(gate_dtype)), VRB_ERR_UNSUPPORTED, "gated_residual: dtypes must be F32 or BF16");
-    if (width % 8 == 0 && aligned16(residual) && aligned16(branch) && aligned16(out) && (!gate || aligned16(gate))) {
+    const bool vec_ok = width % 8 == 0 && aligned16(residual) && aligned16(branch) && aligned16(out) && (!gate || aligned16(gate));
+    const int64_t chunks = vec_ok ? rows * (width / 8) : 0;
+    if (vec_ok && chunks < (int64_t{1} << 31) && rows_per_vector < (int64_t{1} << 31) && gate_vectors < (int64_t{1} << 31)) {
+        const int grid = grid_for((chunks + kThreads - 1) / kThreads, kPerSm);
+        const unsigned total = static_cast<unsigned>(chunks), wc = static_cast<unsigned>(width / 8);
+        const unsigned rpv = static_cast<unsigned>(gate ? rows_per_vector : 1), nv = static_cast<unsigned>(gate ? gate_vectors : 1);
+        cudaStream_t s = as_stream(stream);
+        const int key = (residual_dtype == VRB_BF16 ? 4 : 0) | (branch_dtype == VRB_BF16 ? 2 : 0) | (state_dtype == VRB_BF16 ? 1 : 0);
+#define VRB_GR(R, B, S) gated_residual_typed_kernel<R, B, S><<<grid, kThreads, 0, s>>>(residual, branch, gate, gate_dtype, out, total, wc, rpv, nv)
+        switch (key) {
+            case 0: VRB_GR(false, false, false); break;
+            case 1: VRB_GR(false, false, true); break;
+            case 2: VRB_GR(false, true, false); break;
+            case 3: VRB_GR(false, true, true); break;
+            case 4: VRB_GR(true, false, false); break;
+            case 5: VRB_GR(true, false, true); break;
+            case 6: VRB_GR(true, true, false); break;
+            default: VRB_GR(true, true, true); break;
+        }
+#undef VRB_GR
+    } else if (vec_ok) {
         const int64_t work = rows * (width / 8);
         gated_residual_kernel<<<grid_for((work + kThreads - 1) / kThreads, kPerSm), kThreads, 0, as_stream(stream)>>>(
             residual, residual_dtype, branch, branch_dtype, gate, gate_dtype, out, state_dtype, rows, width / 8,

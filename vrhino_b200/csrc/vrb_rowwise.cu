@@ -1,48 +1,15 @@
-// Row-wise normalisation kernels (LayerNorm / RMSNorm) fused with the operator that the
-// reference's pipelines apply next: adaLN modulation, the Mochi (1+scale) product, RoPE, or
-// a gated residual.  One kernel family, one pass over HBM: a row is loaded once with 128-bit
-// loads, kept in registers while its statistics are reduced (warp shuffles, plus one shared-
-// memory exchange when a row spans several warps), then normalised, post-processed and
-// stored.  Every rounding the reference's chain of separate kernels performs between its
-// steps is reproduced in registers.
-//
-// Reference semantics restated here (native/src/backend/cuda/cuda_backend.cu):
-//   layer_norm_parallel_kernel :910-943  double sum / sum of squares, mean = float(S/W),
-//       inv = rsqrtf(float(Q/W - double(mean)*mean) + eps), (x-mean)*inv [*w] [+b]
-//   rms_norm_contiguous_f32_kernel :853-907  F32 sum of squares, mean = S*(1/W),
-//       inv = rsqrtf(mean+eps), x*inv, round to bf16 if the input is bf16, *w
-//   rms_norm_parallel_kernel :963-991 (and :1013-1040)  same with a double sum and
-//       inv = rsqrtf(float(Q/W) + eps); chosen by rms_contiguous_reduction_lanes :838-850
-//   rope_kernel :1200-1215, modulate / gated_residual: native/src/architectures/common.cpp
-#include "vrb_common.cuh"
+// Entry points of the row-wise normalisation family, the dispatch onto the templated vector
+// kernels (vrb_rowwise.cuh, instantiated in vrb_rowwise_ln.cu / _rms_a.cu / _rms_b.cu) and the
+// scalar kernel that covers any width or alignment.
+#include "vrb_rowwise.cuh"
 
 namespace vrb {
+namespace rowwise {
 namespace {
-
-enum Norm { kNormLayer = 1, kNormRmsF32 = 2, kNormRmsF64 = 3 };
-enum Post { kPostNone = 0, kPostModulate = 1, kPostScaleX = 2, kPostRope = 3, kPostGatedResidual = 4 };
-
-struct RowParams {
-    const void* x; void* out;
-    const void* weight; const void* bias;
-    const void* scale; const void* shift;
-    const void* cosine; const void* sine;
-    const void* residual; const void* gate;
-    int64_t rows, width;       // storage rows
-    int64_t norm_width;        // normalised extent, divides width
-    int64_t rows_per_vector, vectors;            // scale / shift / gate row selection
-    int64_t f_rows, f_width, rows_per_f_row;     // cos / sin table selection
-    float eps;
-    int x_dt, out_dt, w_dt, b_dt, mod_dt, f_dt, res_dt, gate_dt, state_dt;
-    int norm, norm_out_dt, post, affine_fma;
-    int tpr;                   // threads cooperating on one normalised row (power of two)
-};
-
-constexpr int kRowThreads = 256;
 
 // The reference's choice between the F32-accumulating and the double-accumulating RMS
 // kernels depends on the row width and the row count (launch-geometry rule of
-// rms_contiguous_reduction_lanes).  Returns true when the F32 kernel would run.
+// rms_contiguous_reduction_lanes, cuda_backend.cu:838-850).  True when the F32 kernel runs.
 bool rms_uses_f32_accumulation(int64_t width, int64_t rows) {
     if (width <= 0 || rows <= 0) return false;
     if (width > 128 && (width & 3)) return false;
@@ -56,206 +23,6 @@ bool rms_uses_f32_accumulation(int64_t width, int64_t rows) {
     const int64_t per_lane = (width + lanes - 1) / lanes;
     const int64_t limit = groups * 16 < 256 ? groups * 16 : 256;
     return per_lane < limit;
-}
-
-// ---- per-element pipeline shared by the vector and the scalar kernels --------------------
-
-// Normalised value as the unfused norm operator would have stored it (dtype norm_out_dt).
-__device__ __forceinline__ float normalise(const RowParams& p, float x, float mean, float inv,
-                                           float w, float b) {
-    float v;
-    if (p.norm == kNormLayer) {
-        v = __fmul_rn(__fsub_rn(x, mean), inv);
-        if (p.weight && p.bias && p.affine_fma) v = __fmaf_rn(v, w, b);
-        else {
-            if (p.weight) v = __fmul_rn(v, w);
-            if (p.bias) v = __fadd_rn(v, b);
-        }
-    } else {
-        v = __fmul_rn(x, inv);
-        if (p.x_dt == VRB_BF16) v = round_to_bf16(v);
-        if (p.weight) v = __fmul_rn(v, w);
-    }
-    return round_to(p.norm_out_dt, v);
-}
-
-// LayerNorm converts weight and bias to x's dtype; RMSNorm converts the weight to the norm's
-// output dtype (host wrappers :4069-4070, :4115).
-__device__ __forceinline__ float affine_operand(const RowParams& p, float raw) {
-    return round_to(p.norm == kNormLayer ? p.x_dt : p.norm_out_dt, raw);
-}
-
-__device__ __forceinline__ float post_modulate(float v, float scale, float shift, bool has_shift) {
-    // common.cpp:51-61: three separately rounded F32 kernels
-    const float t = __fmul_rn(v, __fadd_rn(1.0f, scale));
-    return has_shift ? __fadd_rn(t, shift) : t;
-}
-__device__ __forceinline__ float post_scale_x(int dt, float v, float scale) {
-    // mochi.cpp:230-231: (1+scale) is an F32 tensor, converted to x's dtype by the binary
-    // operand rule, product rounded to x's dtype
-    const float s = round_to(dt, __fadd_rn(1.0f, scale));
-    return round_to(dt, __fmul_rn(v, s));
-}
-__device__ __forceinline__ float post_gated(int dt, float residual, float v, float gate, bool has_gate) {
-    // common.cpp:134-144 in state dtype dt
-    float branch = round_to(dt, v);
-    if (has_gate) branch = round_to(dt, __fmul_rn(branch, round_to(dt, gate)));
-    return round_to(dt, __fadd_rn(round_to(dt, residual), branch));
-}
-
-// ---- vector kernel: width % 8 == 0, 16-byte aligned operands -----------------------------
-template <int NCH>
-__global__ void __launch_bounds__(kRowThreads) row_kernel(const RowParams p) {
-    __shared__ double s_red[2][2][kRowThreads / 32];
-    const int tpr = p.tpr;
-    const int lane_in_row = threadIdx.x & (tpr - 1);
-    const int row_in_cta = threadIdx.x / tpr;
-    const int rows_per_cta = blockDim.x / tpr;
-    const int nchunks = static_cast<int>(p.norm_width >> 3);
-    const int64_t sub = p.width / p.norm_width;
-    const int64_t nrows = p.rows * sub;
-    const int warps_per_row = tpr >> 5;
-    int parity = 0;
-
-    for (int64_t base = static_cast<int64_t>(blockIdx.x) * rows_per_cta; base < nrows;
-         base += static_cast<int64_t>(gridDim.x) * rows_per_cta) {
-        const int64_t nrow = base + row_in_cta;
-        const bool valid = nrow < nrows;
-        const int64_t row_offset = nrow * p.norm_width;
-
-        float v[NCH][8];
-#pragma unroll
-        for (int i = 0; i < NCH; ++i) {
-            const int chunk = lane_in_row + i * tpr;
-            if (valid && chunk < nchunks) load8<true>(p.x, p.x_dt, row_offset + chunk * 8, v[i]);
-            else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[i][e] = 0.0f;
-            }
-        }
-
-        // ---- statistics ----
-        double acc0 = 0.0, acc1 = 0.0;
-        if (p.norm == kNormLayer) {
-#pragma unroll
-            for (int i = 0; i < NCH; ++i)
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const double d = static_cast<double>(v[i][e]);
-                    acc0 += d;
-                    acc1 = fma(d, d, acc1);
-                }
-        } else if (p.norm == kNormRmsF64) {
-#pragma unroll
-            for (int i = 0; i < NCH; ++i)
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const double d = static_cast<double>(v[i][e]);
-                    acc1 = fma(d, d, acc1);
-                }
-        } else {
-            float s = 0.0f;
-#pragma unroll
-            for (int i = 0; i < NCH; ++i)
-#pragma unroll
-                for (int e = 0; e < 8; ++e) s = __fadd_rn(s, __fmul_rn(v[i][e], v[i][e]));
-            acc1 = static_cast<double>(s);  // carried as a double container; summed in F32 below
-        }
-        const bool f32_sum = p.norm == kNormRmsF32;
-        const int span = tpr < 32 ? tpr : 32;
-        for (int offset = span >> 1; offset > 0; offset >>= 1) {
-            if (f32_sum) {
-                const float mine = static_cast<float>(acc1);
-                acc1 = static_cast<double>(__fadd_rn(mine, __shfl_xor_sync(0xffffffffu, mine, offset)));
-            } else {
-                acc0 += __shfl_xor_sync(0xffffffffu, acc0, offset);
-                acc1 += __shfl_xor_sync(0xffffffffu, acc1, offset);
-            }
-        }
-        if (warps_per_row > 1) {
-            const int warp = threadIdx.x >> 5;
-            if ((threadIdx.x & 31) == 0) { s_red[parity][0][warp] = acc0; s_red[parity][1][warp] = acc1; }
-            __syncthreads();
-            const int first = row_in_cta * warps_per_row;
-            acc0 = 0.0; acc1 = 0.0;
-            if (f32_sum) {
-                float s = 0.0f;
-                for (int w = 0; w < warps_per_row; ++w)
-                    s = __fadd_rn(s, static_cast<float>(s_red[parity][1][first + w]));
-                acc1 = static_cast<double>(s);
-            } else {
-                for (int w = 0; w < warps_per_row; ++w) {
-                    acc0 += s_red[parity][0][first + w];
-                    acc1 += s_red[parity][1][first + w];
-                }
-            }
-            parity ^= 1;
-        }
-        float mean = 0.0f, inv;
-        const double w_d = static_cast<double>(p.norm_width);
-        if (p.norm == kNormLayer) {
-            mean = static_cast<float>(acc0 / w_d);
-            inv = rsqrtf(static_cast<float>(acc1 / w_d - static_cast<double>(mean) * mean) + p.eps);
-        } else if (p.norm == kNormRmsF64) {
-            inv = rsqrtf(static_cast<float>(acc1 / w_d) + p.eps);
-        } else {
-            const float m = __fmul_rn(static_cast<float>(acc1), __fdiv_rn(1.0f, static_cast<float>(p.norm_width)));
-            inv = rsqrtf(__fadd_rn(m, p.eps));
-        }
-        if (!valid) continue;  // no barrier follows in this iteration
-
-        // ---- normalise, post-process, store ----
-        const int64_t srow = nrow / sub;                              // storage row
-        const int64_t col0 = (nrow - srow * sub) * p.norm_width;      // first storage column
-        const int64_t vec = p.vectors > 0 ? (srow / p.rows_per_vector) % p.vectors : 0;
-        const int64_t frow = p.f_rows > 0 ? (srow / p.rows_per_f_row) % p.f_rows : 0;
-#pragma unroll
-        for (int i = 0; i < NCH; ++i) {
-            const int chunk = lane_in_row + i * tpr;
-            if (chunk >= nchunks) continue;
-            const int c = chunk * 8;
-            float w[8], b[8], y[8];
-            if (p.weight) load8<false>(p.weight, p.w_dt, c, w);
-            if (p.bias) load8<false>(p.bias, p.b_dt, c, b);
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-                y[e] = normalise(p, v[i][e], mean, inv,
-                                 p.weight ? affine_operand(p, w[e]) : 1.0f,
-                                 p.bias ? affine_operand(p, b[e]) : 0.0f);
-            if (p.post == kPostModulate) {
-                float sc[8], sh[8];
-                load8<false>(p.scale, p.mod_dt, vec * p.width + col0 + c, sc);
-                if (p.shift) load8<false>(p.shift, p.mod_dt, vec * p.width + col0 + c, sh);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) y[e] = post_modulate(y[e], sc[e], p.shift ? sh[e] : 0.0f, p.shift != nullptr);
-            } else if (p.post == kPostScaleX) {
-                float sc[8];
-                load8<false>(p.scale, p.mod_dt, vec * p.width + col0 + c, sc);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) y[e] = post_scale_x(p.norm_out_dt, y[e], sc[e]);
-            } else if (p.post == kPostRope) {
-                float co[8], si[8], r[8];
-                const int64_t f = frow * p.f_width + (col0 + c) % p.f_width;
-                load8<false>(p.cosine, p.f_dt, f, co);
-                load8<false>(p.sine, p.f_dt, f, si);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float rotated = (e & 1) ? y[e ^ 1] : -y[e ^ 1];
-                    r[e] = __fadd_rn(__fmul_rn(y[e], co[e]), __fmul_rn(rotated, si[e]));
-                }
-#pragma unroll
-                for (int e = 0; e < 8; ++e) y[e] = r[e];
-            } else if (p.post == kPostGatedResidual) {
-                float res[8], g[8];
-                load8<true>(p.residual, p.res_dt, row_offset + c, res);
-                if (p.gate) load8<false>(p.gate, p.gate_dt, vec * p.width + col0 + c, g);
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                    y[e] = post_gated(p.state_dt, res[e], y[e], p.gate ? g[e] : 0.0f, p.gate != nullptr);
-            }
-            store8(p.out, p.out_dt, row_offset + c, y);
-        }
-    }
 }
 
 // ---- scalar kernel: any width / alignment; one CTA per normalised row ---------------------
@@ -279,27 +46,32 @@ __device__ __forceinline__ float block_sum_f32(float value, float* ws) {
     return total;
 }
 
+template <int NORM>
 __global__ void __launch_bounds__(kRowThreads) row_kernel_scalar(const RowParams p) {
     __shared__ double ws_d[8];
     __shared__ float ws_f[8];
     const int64_t sub = p.width / p.norm_width;
     const int64_t nrows = p.rows * sub;
+    const bool has_w = p.weight != nullptr, has_b = p.bias != nullptr;
+    const bool x_bf16 = p.x_dt == VRB_BF16;
+    const int affine_dt = NORM == kNormLayer ? p.x_dt : p.norm_out_dt;
+    const bool f32_sum = NORM == kNormRms && !p.rms_f64;
     for (int64_t nrow = blockIdx.x; nrow < nrows; nrow += gridDim.x) {
         const int64_t row_offset = nrow * p.norm_width;
         double a0 = 0.0, a1 = 0.0;
         float s = 0.0f;
         for (int64_t c = threadIdx.x; c < p.norm_width; c += blockDim.x) {
             const float x = load1(p.x, p.x_dt, row_offset + c);
-            if (p.norm == kNormRmsF32) s = __fadd_rn(s, __fmul_rn(x, x));
+            if (f32_sum) s = __fadd_rn(s, __fmul_rn(x, x));
             else { a0 += x; a1 = fma(static_cast<double>(x), static_cast<double>(x), a1); }
         }
         float mean = 0.0f, inv;
         const double w_d = static_cast<double>(p.norm_width);
-        if (p.norm == kNormLayer) {
+        if constexpr (NORM == kNormLayer) {
             const double t0 = block_sum(a0, ws_d), t1 = block_sum(a1, ws_d);
             mean = static_cast<float>(t0 / w_d);
             inv = rsqrtf(static_cast<float>(t1 / w_d - static_cast<double>(mean) * mean) + p.eps);
-        } else if (p.norm == kNormRmsF64) {
+        } else if (!f32_sum) {
             inv = rsqrtf(static_cast<float>(block_sum(a1, ws_d) / w_d) + p.eps);
         } else {
             const float m = __fmul_rn(block_sum_f32(s, ws_f), __fdiv_rn(1.0f, static_cast<float>(p.norm_width)));
@@ -310,9 +82,9 @@ __global__ void __launch_bounds__(kRowThreads) row_kernel_scalar(const RowParams
         const int64_t vec = p.vectors > 0 ? (srow / p.rows_per_vector) % p.vectors : 0;
         const int64_t frow = p.f_rows > 0 ? (srow / p.rows_per_f_row) % p.f_rows : 0;
         auto value_at = [&](int64_t c) {
-            return normalise(p, load1(p.x, p.x_dt, row_offset + c), mean, inv,
-                             p.weight ? affine_operand(p, load1(p.weight, p.w_dt, c)) : 1.0f,
-                             p.bias ? affine_operand(p, load1(p.bias, p.b_dt, c)) : 0.0f);
+            return normalise<NORM>(p, load1(p.x, p.x_dt, row_offset + c), mean, inv,
+                                   has_w ? round_to(affine_dt, load1(p.weight, p.w_dt, c)) : 1.0f,
+                                   has_b ? round_to(affine_dt, load1(p.bias, p.b_dt, c)) : 0.0f, has_w, has_b, x_bf16);
         };
         for (int64_t c = threadIdx.x; c < p.norm_width; c += blockDim.x) {
             float y = value_at(c);
@@ -335,20 +107,22 @@ __global__ void __launch_bounds__(kRowThreads) row_kernel_scalar(const RowParams
     }
 }
 
-// ---- launch ------------------------------------------------------------------------------
+// ---- dispatch ----------------------------------------------------------------------------
 constexpr int kMaxChunks = 8;
 
-// Grid = every CTA the device can hold at once (occupancy of this instantiation x SM count),
-// capped by the amount of work; CTAs stride over the rows.
-template <int NCH>
-void launch_row_kernel(const RowParams& p, int64_t ctas, cudaStream_t stream) {
-    static int per_sm = 0;
-    if (per_sm == 0) {
-        int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, row_kernel<NCH>, kRowThreads, 0) != cudaSuccess || n < 1) n = 1;
-        per_sm = n;
+// Which dtype classes exist for a (norm, post) pair; anything else takes the scalar kernel.
+template <int NORM, int POST>
+bool launch_by_dtype(const RowParams& p, int geometry, int64_t ctas, size_t smem, cudaStream_t s) {
+    constexpr bool rope = POST == kPostRope || POST == kPostRopeShared;
+    const bool x_bf16 = p.x_dt == VRB_BF16, n_bf16 = p.norm_out_dt == VRB_BF16;
+    if (!x_bf16 && !n_bf16) { launch_row_variant<NORM, POST, kF32F32>(p, geometry, ctas, smem, s); return true; }
+    if constexpr (!rope) {
+        if (x_bf16 && n_bf16) { launch_row_variant<NORM, POST, kBf16Bf16>(p, geometry, ctas, smem, s); return true; }
     }
-    row_kernel<NCH><<<grid_for(ctas, per_sm), kRowThreads, 0, stream>>>(p);
+    if constexpr (NORM == kNormRms && (POST == kPostNone || rope)) {
+        if (x_bf16 && !n_bf16) { launch_row_variant<NORM, POST, kBf16F32>(p, geometry, ctas, smem, s); return true; }
+    }
+    return false;
 }
 
 int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
@@ -357,37 +131,81 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
                 VRB_ERR_INVALID, "%s: rows/width must be positive and norm_width must divide width", what);
     VRB_REQUIRE(is_float_dtype(p.x_dt) && is_float_dtype(p.out_dt), VRB_ERR_UNSUPPORTED,
                 "%s: tensors must be F32 or BF16", what);
-    const int64_t nrows = p.rows * (p.width / p.norm_width);
+    const int64_t sub = p.width / p.norm_width;
+    const int64_t nrows = p.rows * sub;
     bool vector_ok = (p.norm_width % 8 == 0) && aligned16(p.x) && aligned16(p.out) &&
                      (!p.weight || aligned16(p.weight)) && (!p.bias || aligned16(p.bias)) &&
                      (!p.scale || aligned16(p.scale)) && (!p.shift || aligned16(p.shift)) &&
                      (!p.cosine || (aligned16(p.cosine) && aligned16(p.sine) && p.f_width % 8 == 0)) &&
                      (!p.residual || aligned16(p.residual)) && (!p.gate || aligned16(p.gate));
     const int64_t chunks = p.norm_width / 8;
-    if (vector_ok && chunks > static_cast<int64_t>(kMaxChunks) * kRowThreads) vector_ok = false;
-    if (!vector_ok) {
+    if (chunks > static_cast<int64_t>(kMaxChunks) * kRowThreads) vector_ok = false;
+    // The vector kernel indexes rows and table rows in 32 bits.
+    if (nrows >= (1LL << 31) || p.rows_per_vector >= (1LL << 31) || p.vectors >= (1LL << 31) ||
+        p.f_rows >= (1LL << 31) || p.rows_per_f_row >= (1LL << 31) || p.width >= (1LL << 31))
+        vector_ok = false;
+    auto scalar_path = [&]() {
         p.tpr = kRowThreads;
-        row_kernel_scalar<<<grid_for(nrows, 8), kRowThreads, 0, stream>>>(p);
+        const int grid = grid_for(nrows, 8);
+        if (p.norm == kNormLayer) row_kernel_scalar<kNormLayer><<<grid, kRowThreads, 0, stream>>>(p);
+        else row_kernel_scalar<kNormRms><<<grid, kRowThreads, 0, stream>>>(p);
         return after_launch(what);
+    };
+    if (!vector_ok) return scalar_path();
+    // Threads per row: a row of up to 32*6 chunks stays inside one warp (no barrier); narrower
+    // rows take a fraction of a warp with 1-2 chunks per thread; wider rows take 2-8 warps.
+    int tpr;
+    if (chunks <= 32 * 6) {
+        tpr = 8;
+        while (tpr < 32 && static_cast<int64_t>(tpr) * 2 < chunks) tpr <<= 1;
+    } else {
+        tpr = 64;
+        while (tpr < kRowThreads && static_cast<int64_t>(tpr) * 6 < chunks) tpr <<= 1;
     }
-    // Threads per row: the smallest power of two (8..256) that leaves at most 4 chunks of 8
-    // elements per thread; wider rows take more chunks per thread, up to kMaxChunks.
-    int tpr = 8;
-    while (tpr < kRowThreads && static_cast<int64_t>(tpr) * 4 < chunks) tpr <<= 1;
-    const int nch = static_cast<int>((chunks + tpr - 1) / tpr);
+    int nch = static_cast<int>((chunks + tpr - 1) / tpr);
+    if (nch == 7) nch = 8;
+    int geometry = nch <= 6 ? nch - 1 : 6;
+    switch (p.norm_width) {   // production widths have exact instantiations
+        case 1536: geometry = kExact1536; tpr = 32; break;
+        case 3072: geometry = kExact3072; tpr = 64; break;
+        case 5120: geometry = kExact5120; tpr = 128; break;
+        case 2048: geometry = kExact2048; tpr = 64; break;
+        case 128: geometry = kExact128; tpr = 8; break;
+        default: break;
+    }
     p.tpr = tpr;
+    p.nrows32 = static_cast<unsigned>(nrows);
+    p.sub32 = static_cast<unsigned>(sub);
     const int rows_per_cta = kRowThreads / tpr;
     const int64_t ctas = (nrows + rows_per_cta - 1) / rows_per_cta;
-    switch (nch) {
-        case 1: launch_row_kernel<1>(p, ctas, stream); break;
-        case 2: launch_row_kernel<2>(p, ctas, stream); break;
-        case 3: launch_row_kernel<3>(p, ctas, stream); break;
-        case 4: launch_row_kernel<4>(p, ctas, stream); break;
-        case 5: launch_row_kernel<5>(p, ctas, stream); break;
-        case 6: launch_row_kernel<6>(p, ctas, stream); break;
-        case 7: launch_row_kernel<7>(p, ctas, stream); break;
-        default: launch_row_kernel<8>(p, ctas, stream); break;
+    // One modulation vector for all rows and small enough for the default shared-memory limit:
+    // stage 1+scale and shift per CTA instead of re-reading them for every row.
+    size_t smem = 0;
+    int post = p.post;
+    if (post == kPostModulate && p.vectors == 1 && sub == 1 && p.norm_width * 8 <= 40 * 1024) {
+        post = kPostModulateStaged;
+        smem = static_cast<size_t>(p.norm_width) * 8;
     }
+    // RoPE table shared by the heads: the columns a thread needs are the same for all its chunks.
+    if (post == kPostRope && p.norm_width % p.f_width == 0 && (static_cast<int64_t>(tpr) * 8) % p.f_width == 0)
+        post = kPostRopeShared;
+    bool launched;
+    if (p.norm == kNormLayer) {
+        if (post == kPostModulateStaged) launched = launch_by_dtype<kNormLayer, kPostModulateStaged>(p, geometry, ctas, smem, stream);
+        else if (post == kPostModulate) launched = launch_by_dtype<kNormLayer, kPostModulate>(p, geometry, ctas, smem, stream);
+        else launched = launch_by_dtype<kNormLayer, kPostNone>(p, geometry, ctas, smem, stream);
+    } else {
+        switch (post) {
+            case kPostModulateStaged: launched = launch_by_dtype<kNormRms, kPostModulateStaged>(p, geometry, ctas, smem, stream); break;
+            case kPostModulate: launched = launch_by_dtype<kNormRms, kPostModulate>(p, geometry, ctas, smem, stream); break;
+            case kPostScaleX: launched = launch_by_dtype<kNormRms, kPostScaleX>(p, geometry, ctas, smem, stream); break;
+            case kPostRopeShared: launched = launch_by_dtype<kNormRms, kPostRopeShared>(p, geometry, ctas, smem, stream); break;
+            case kPostRope: launched = launch_by_dtype<kNormRms, kPostRope>(p, geometry, ctas, smem, stream); break;
+            case kPostGatedResidual: launched = launch_by_dtype<kNormRms, kPostGatedResidual>(p, geometry, ctas, smem, stream); break;
+            default: launched = launch_by_dtype<kNormRms, kPostNone>(p, geometry, ctas, smem, stream); break;
+        }
+    }
+    if (!launched) return scalar_path();
     return after_launch(what);
 }
 
@@ -400,6 +218,11 @@ RowParams blank() {
     return p;
 }
 
+void set_rms(RowParams& p, int64_t norm_rows) {
+    p.norm = kNormRms;
+    p.rms_f64 = rms_uses_f32_accumulation(p.norm_width, norm_rows) ? 0 : 1;
+}
+
 int check_vectors(const char* what, int64_t rows_per_vector, int64_t vectors) {
     VRB_REQUIRE(rows_per_vector > 0 && vectors > 0, VRB_ERR_INVALID,
                 "%s: rows_per_vector and vector count must be positive", what);
@@ -407,15 +230,23 @@ int check_vectors(const char* what, int64_t rows_per_vector, int64_t vectors) {
 }
 
 }  // namespace
+}  // namespace rowwise
 }  // namespace vrb
 
 using namespace vrb;
+using namespace vrb::rowwise;
 
 extern "C" int vrb_layer_norm(const void* x, int dtype, const void* weight, int weight_dtype,
                               const void* bias, int bias_dtype, void* out,
                               int64_t rows, int64_t width, float eps, vrb_stream stream) {
+    return vrb_layer_norm_cast(x, dtype, weight, weight_dtype, bias, bias_dtype, out, dtype, rows, width, eps, stream);
+}
+
+extern "C" int vrb_layer_norm_cast(const void* x, int x_dtype, const void* weight, int weight_dtype,
+                                   const void* bias, int bias_dtype, void* out, int out_dtype,
+                                   int64_t rows, int64_t width, float eps, vrb_stream stream) {
     RowParams p = blank();
-    p.x = x; p.out = out; p.x_dt = p.out_dt = p.norm_out_dt = dtype;
+    p.x = x; p.out = out; p.x_dt = p.norm_out_dt = x_dtype; p.out_dt = out_dtype;
     p.weight = weight; p.w_dt = weight_dtype; p.bias = bias; p.b_dt = bias_dtype;
     VRB_REQUIRE((!weight || is_float_dtype(weight_dtype)) && (!bias || is_float_dtype(bias_dtype)),
                 VRB_ERR_UNSUPPORTED, "layer_norm: weight/bias must be F32 or BF16");
@@ -434,7 +265,7 @@ extern "C" int vrb_rms_norm(const void* x, int x_dtype, const void* weight, int 
     p.x = x; p.out = out; p.x_dt = x_dtype; p.out_dt = p.norm_out_dt = out_dtype;
     p.weight = weight; p.w_dt = weight_dtype;
     p.rows = rows; p.width = p.norm_width = width; p.eps = eps;
-    p.norm = rms_uses_f32_accumulation(width, rows) ? kNormRmsF32 : kNormRmsF64;
+    set_rms(p, rows);
     return launch_rows(p, as_stream(stream), "rms_norm");
 }
 
@@ -467,7 +298,7 @@ extern "C" int vrb_rms_norm_modulate(const void* x, int x_dtype, const void* sca
     p.scale = scale; p.shift = shift; p.mod_dt = mod_dtype;
     p.rows_per_vector = rows_per_vector; p.vectors = mod_vectors;
     p.rows = rows; p.width = p.norm_width = width; p.eps = eps;
-    p.norm = rms_uses_f32_accumulation(width, rows) ? kNormRmsF32 : kNormRmsF64;
+    set_rms(p, rows);
     p.post = kPostModulate;
     return launch_rows(p, as_stream(stream), "rms_norm_modulate");
 }
@@ -482,7 +313,7 @@ extern "C" int vrb_rms_norm_scale(const void* x, int dtype, const void* scale, i
     p.scale = scale; p.mod_dt = scale_dtype;
     p.rows_per_vector = rows_per_vector; p.vectors = mod_vectors;
     p.rows = rows; p.width = p.norm_width = width; p.eps = eps;
-    p.norm = rms_uses_f32_accumulation(width, rows) ? kNormRmsF32 : kNormRmsF64;
+    set_rms(p, rows);
     p.post = kPostScaleX;
     return launch_rows(p, as_stream(stream), "rms_norm_scale");
 }
@@ -501,7 +332,7 @@ extern "C" int vrb_rms_norm_rope(const void* x, int x_dtype, const void* weight,
     p.norm_out_dt = VRB_F32;  // attention_norm widens to F32 (precision.cpp:292-297)
     p.weight = weight; p.w_dt = weight_dtype;
     p.rows = rows; p.width = width; p.norm_width = norm_width; p.eps = eps;
-    p.norm = rms_uses_f32_accumulation(norm_width, rows * (width / norm_width)) ? kNormRmsF32 : kNormRmsF64;
+    set_rms(p, rows * (width / norm_width));
     if (cosine) {
         VRB_REQUIRE(f_rows > 0 && f_width > 0 && rows_per_f_row > 0 && width % f_width == 0 && (norm_width % 2) == 0,
                     VRB_ERR_INVALID, "rms_norm_rope: table extents must be positive, f_width must divide width, width even");
@@ -525,19 +356,7 @@ extern "C" int vrb_rms_norm_gated_residual(const void* residual, int residual_dt
     p.residual = residual; p.res_dt = residual_dtype; p.gate = gate; p.gate_dt = gate_dtype;
     p.rows_per_vector = rows_per_vector; p.vectors = gate ? gate_vectors : 0;
     p.rows = rows; p.width = p.norm_width = width; p.eps = eps;
-    p.norm = rms_uses_f32_accumulation(width, rows) ? kNormRmsF32 : kNormRmsF64;
+    set_rms(p, rows);
     p.post = kPostGatedResidual;
     return launch_rows(p, as_stream(stream), "rms_norm_gated_residual");
-}
-
-extern "C" int vrb_layer_norm_cast(const void* x, int x_dtype, const void* weight, int weight_dtype,
-                                   const void* bias, int bias_dtype, void* out, int out_dtype,
-                                   int64_t rows, int64_t width, float eps, vrb_stream stream) {
-    RowParams p = blank();
-    p.x = x; p.out = out; p.x_dt = p.norm_out_dt = x_dtype; p.out_dt = out_dtype;
-    p.weight = weight; p.w_dt = weight_dtype; p.bias = bias; p.b_dt = bias_dtype;
-    VRB_REQUIRE((!weight || is_float_dtype(weight_dtype)) && (!bias || is_float_dtype(bias_dtype)),
-                VRB_ERR_UNSUPPORTED, "layer_norm_cast: weight/bias must be F32 or BF16");
-    p.rows = rows; p.width = p.norm_width = width; p.eps = eps; p.norm = kNormLayer;
-    return launch_rows(p, as_stream(stream), "layer_norm_cast");
 }

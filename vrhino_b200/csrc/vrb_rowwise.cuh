@@ -1,0 +1,447 @@
+// Row-wise normalisation kernel family (LayerNorm / RMSNorm) fused with the operator the
+// reference's pipelines apply next: adaLN modulation, the Mochi (1+scale) product, RoPE, or a
+// gated residual.  One pass over HBM: a row is loaded once with 128-bit loads, kept PACKED in
+// registers while its statistics are reduced, then normalised, post-processed and stored.
+// Every rounding the reference's chain of separate kernels performs between its steps is
+// reproduced in registers.
+//
+// Work split: `tpr` threads (8..256, power of two) cooperate on one normalised row, each
+// holding NCH chunks of 8 elements.  Rows narrower than a warp pack several rows into one
+// warp; a row of at most 32*6 chunks stays inside one warp and needs no barrier at all; wider
+// rows exchange one partial per warp through shared memory under a NAMED barrier that only the
+// warps of that row wait on, so the rows of a CTA never wait for each other.
+//
+// At 6.5 TB/s an SM has about 22 issue slots per bf16 element it streams, so the per-element
+// instruction count is what decides whether these kernels reach the HBM roofline.  Hence:
+// dtype classes are template parameters (no per-element dtype tests), bf16 roundings are done
+// two at a time (cvt.rn.bf16x2.f32), and the statistics are accumulated per thread in F32
+// (at most 64 terms, pairwise inside a chunk) and only then widened to double for the
+// cross-thread reduction and the final mean / variance formula.
+//
+// Reference semantics restated (native/src/backend/cuda/cuda_backend.cu):
+//   layer_norm_parallel_kernel :910-943  sum / sum of squares (double in the reference),
+//       mean = float(S/W), inv = rsqrtf(float(Q/W - double(mean)*mean) + eps),
+//       (x-mean)*inv [*w] [+b]
+//   rms_norm_contiguous_f32_kernel :853-907  F32 sum of squares, mean = S*(1/W),
+//       inv = rsqrtf(mean+eps), x*inv, round to bf16 if the input is bf16, *w
+//   rms_norm_parallel_kernel :963-991 (and :1013-1040)  same with a double sum and
+//       inv = rsqrtf(float(Q/W) + eps); chosen by rms_contiguous_reduction_lanes :838-850
+//   rope_kernel :1200-1215; modulate / gated_residual: native/src/architectures/common.cpp
+#pragma once
+
+#include "vrb_common.cuh"
+
+namespace vrb {
+namespace rowwise {
+
+enum Norm { kNormLayer = 1, kNormRms = 2 };
+enum Post {
+    kPostNone = 0, kPostModulate = 1, kPostScaleX = 2, kPostRope = 3, kPostGatedResidual = 4,
+    kPostModulateStaged = 5,   // modulate with one vector for all rows, staged in shared memory
+    kPostRopeShared = 6,       // RoPE whose table columns do not depend on the thread's chunk index
+};
+// dtype class of (x, output of the unfused norm operator)
+enum DtClass { kF32F32 = 0, kBf16Bf16 = 1, kBf16F32 = 2 };
+
+struct RowParams {
+    const void* x; void* out;
+    const void* weight; const void* bias;
+    const void* scale; const void* shift;
+    const void* cosine; const void* sine;
+    const void* residual; const void* gate;
+    int64_t rows, width;       // storage rows
+    int64_t norm_width;        // normalised extent, divides width
+    int64_t rows_per_vector, vectors;            // scale / shift / gate row selection
+    int64_t f_rows, f_width, rows_per_f_row;     // cos / sin table selection
+    float eps;
+    int x_dt, out_dt, w_dt, b_dt, mod_dt, f_dt, res_dt, gate_dt, state_dt;
+    int norm, norm_out_dt, post, affine_fma;
+    int rms_f64;               // RMS: the reference's double-accumulating fallback formula
+    int tpr;                   // threads per normalised row
+    unsigned nrows32, sub32;   // normalised rows, normalised rows per storage row
+};
+
+constexpr int kRowThreads = 256;
+
+#ifdef __CUDACC__
+
+template <bool X_BF16> struct Packed;
+template <> struct Packed<true> { uint4 r; };
+template <> struct Packed<false> { float4 a, b; };
+
+template <bool X_BF16>
+__device__ __forceinline__ Packed<X_BF16> load_packed(const void* base, int64_t e) {
+    Packed<X_BF16> c;
+    if constexpr (X_BF16) c.r = __ldcs(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + e));
+    else {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + e);
+        c.a = __ldcs(p); c.b = __ldcs(p + 1);
+    }
+    return c;
+}
+template <bool X_BF16>
+__device__ __forceinline__ Packed<X_BF16> zero_packed() {
+    Packed<X_BF16> c;
+    if constexpr (X_BF16) c.r = make_uint4(0, 0, 0, 0);
+    else { c.a = make_float4(0, 0, 0, 0); c.b = c.a; }
+    return c;
+}
+template <bool X_BF16>
+__device__ __forceinline__ void unpack(const Packed<X_BF16>& c, float (&v)[8]) {
+    if constexpr (X_BF16) {
+        v[0] = __uint_as_float(c.r.x << 16); v[1] = __uint_as_float(c.r.x & 0xffff0000u);
+        v[2] = __uint_as_float(c.r.y << 16); v[3] = __uint_as_float(c.r.y & 0xffff0000u);
+        v[4] = __uint_as_float(c.r.z << 16); v[5] = __uint_as_float(c.r.z & 0xffff0000u);
+        v[6] = __uint_as_float(c.r.w << 16); v[7] = __uint_as_float(c.r.w & 0xffff0000u);
+    } else {
+        v[0] = c.a.x; v[1] = c.a.y; v[2] = c.a.z; v[3] = c.a.w;
+        v[4] = c.b.x; v[5] = c.b.y; v[6] = c.b.z; v[7] = c.b.w;
+    }
+}
+
+// Round eight values to bf16 precision, two per conversion instruction.
+__device__ __forceinline__ void round8_bf16(float (&v)[8]) {
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+        const uint32_t h = pack_bf16x2(v[e], v[e + 1]);
+        v[e] = __uint_as_float(h << 16);
+        v[e + 1] = __uint_as_float(h & 0xffff0000u);
+    }
+}
+template <bool BF16>
+__device__ __forceinline__ void round8(float (&v)[8]) {
+    if constexpr (BF16) round8_bf16(v);
+}
+__device__ __forceinline__ void round8_rt(int dt, float (&v)[8]) {
+    if (dt == VRB_BF16) round8_bf16(v);
+}
+
+// ---- scalar forms of the per-element pipeline (used by the any-width kernel) --------------
+template <int NORM>
+__device__ __forceinline__ float normalise(const RowParams& p, float x, float mean, float inv,
+                                           float w, float b, bool has_w, bool has_b, bool x_bf16) {
+    float v;
+    if constexpr (NORM == kNormLayer) {
+        v = __fmul_rn(__fsub_rn(x, mean), inv);
+        if (has_w && has_b && p.affine_fma) v = __fmaf_rn(v, w, b);
+        else {
+            if (has_w) v = __fmul_rn(v, w);
+            if (has_b) v = __fadd_rn(v, b);
+        }
+    } else {
+        v = __fmul_rn(x, inv);
+        if (x_bf16) v = round_to_bf16(v);
+        if (has_w) v = __fmul_rn(v, w);
+    }
+    return round_to(p.norm_out_dt, v);
+}
+__device__ __forceinline__ float post_modulate(float v, float scale, float shift, bool has_shift) {
+    // common.cpp:51-61: three separately rounded F32 kernels
+    const float t = __fmul_rn(v, __fadd_rn(1.0f, scale));
+    return has_shift ? __fadd_rn(t, shift) : t;
+}
+__device__ __forceinline__ float post_scale_x(int dt, float v, float scale) {
+    // mochi.cpp:230-231: (1+scale) is an F32 tensor, converted to x's dtype by the binary
+    // operand rule, product rounded to x's dtype
+    const float s = round_to(dt, __fadd_rn(1.0f, scale));
+    return round_to(dt, __fmul_rn(v, s));
+}
+__device__ __forceinline__ float post_gated(int dt, float residual, float v, float gate, bool has_gate) {
+    // common.cpp:134-144 in state dtype dt
+    float branch = round_to(dt, v);
+    if (has_gate) branch = round_to(dt, __fmul_rn(branch, round_to(dt, gate)));
+    return round_to(dt, __fadd_rn(round_to(dt, residual), branch));
+}
+
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// ---- vector kernel: norm_width % 8 == 0, 16-byte aligned operands ------------------------
+// CTAs per SM the register allocator must leave room for: the packed row takes 4 (bf16) or 8
+// (f32) registers per chunk; the rest of the budget is working state.
+constexpr int min_ctas_per_sm(int nch, bool x_bf16) {
+    const int row_regs = nch * (x_bf16 ? 4 : 8);
+    return row_regs <= 16 ? 4 : row_regs <= 32 ? 3 : 2;
+}
+
+// Geometry: TPR == 0 reads the threads-per-row from the parameters and guards every chunk;
+// TPR > 0 with FULL means the row is exactly NCH * TPR chunks wide, so chunk offsets are
+// compile-time constants and no chunk needs a bounds test (the production widths).
+template <int NCH, int TPR, bool FULL, int NORM, int POST, int DT>
+__global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F32)) row_kernel(const RowParams p) {
+    constexpr bool X_BF16 = DT != kF32F32;
+    constexpr bool N_BF16 = DT == kBf16Bf16;     // the unfused norm operator would store bf16
+    constexpr bool kStaged = POST == kPostModulateStaged;
+    constexpr bool kModulate = POST == kPostModulate || kStaged;
+    constexpr bool kRope = POST == kPostRope || POST == kPostRopeShared;
+    __shared__ double s_red[2][kRowThreads / 32][2];
+    extern __shared__ __align__(16) float s_vec[];   // staged modulate: [1+scale | shift]
+    const int tpr = TPR ? TPR : p.tpr;
+    const int lane_in_row = threadIdx.x & (tpr - 1);
+    const int row_in_cta = threadIdx.x / tpr;
+    const int rows_per_cta = kRowThreads / tpr;
+    const int nchunks = FULL ? NCH * TPR : static_cast<int>(p.norm_width >> 3);
+    const int width = nchunks * 8;
+    const unsigned nrows = p.nrows32;
+    const int warps_per_row = tpr >> 5;
+    const bool has_w = p.weight != nullptr, has_b = p.bias != nullptr;
+    const bool has_shift = p.shift != nullptr;
+    const bool f32_formula = NORM == kNormRms && !p.rms_f64;
+    int parity = 0;
+
+    if constexpr (kStaged) {
+        // one modulation vector for every row: keep 1+scale and shift in shared memory
+        for (int c = threadIdx.x; c < width; c += kRowThreads) {
+            s_vec[c] = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, c));
+            s_vec[width + c] = has_shift ? load1(p.shift, p.mod_dt, c) : 0.0f;
+        }
+        __syncthreads();
+    }
+    // elements of this thread that exist (a partial last chunk never happens: width % 8 == 0)
+    int own = 0;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) own += (FULL || lane_in_row + i * tpr < nchunks) ? 8 : 0;
+
+    for (unsigned base = blockIdx.x * rows_per_cta; base < nrows; base += gridDim.x * rows_per_cta) {
+        const unsigned nrow = base + row_in_cta;
+        const bool valid = nrow < nrows;
+        const int64_t row_offset = static_cast<int64_t>(nrow) * width;
+
+        Packed<X_BF16> xr[NCH];
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+            const int chunk = lane_in_row + i * tpr;
+            xr[i] = (valid && (FULL || chunk < nchunks)) ? load_packed<X_BF16>(p.x, row_offset + chunk * 8) : zero_packed<X_BF16>();
+        }
+
+        // ---- statistics: per-thread F32 partials (pairwise inside a chunk) ----
+        // LayerNorm sums x - K and (x - K)^2 with K = the thread's first element, so the
+        // partials stay small and accurate however large the row's common offset is; the exact
+        // sums are rebuilt in double: S = s1 + n K, Q = s2 + 2 K s1 + n K^2.
+        float s1 = 0.0f, s2 = 0.0f, pivot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+            float v[8];
+            unpack<X_BF16>(xr[i], v);
+            if constexpr (NORM == kNormLayer) {
+                if (i == 0) pivot = v[0];
+                if (FULL || lane_in_row + i * tpr < nchunks) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] -= pivot;
+                    s1 += ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+                }
+            }
+            float qa = v[0] * v[0], qb = v[4] * v[4];
+            qa = fmaf(v[1], v[1], qa); qb = fmaf(v[5], v[5], qb);
+            qa = fmaf(v[2], v[2], qa); qb = fmaf(v[6], v[6], qb);
+            qa = fmaf(v[3], v[3], qa); qb = fmaf(v[7], v[7], qb);
+            s2 += qa + qb;
+        }
+        const int span = tpr < 32 ? tpr : 32;
+        double acc0 = 0.0, acc1 = 0.0;
+        if (f32_formula) {
+            for (int offset = span >> 1; offset > 0; offset >>= 1)
+                s2 = __fadd_rn(s2, __shfl_xor_sync(0xffffffffu, s2, offset));
+        } else {
+            if constexpr (NORM == kNormLayer) {
+                const double k = static_cast<double>(pivot), n = static_cast<double>(own), d1 = static_cast<double>(s1);
+                acc0 = d1 + n * k;
+                acc1 = static_cast<double>(s2) + (2.0 * k) * d1 + (n * k) * k;
+            } else {
+                acc1 = static_cast<double>(s2);
+            }
+            for (int offset = span >> 1; offset > 0; offset >>= 1) {
+                if constexpr (NORM == kNormLayer) acc0 += __shfl_xor_sync(0xffffffffu, acc0, offset);
+                acc1 += __shfl_xor_sync(0xffffffffu, acc1, offset);
+            }
+        }
+        if (warps_per_row > 1) {
+            const int warp = threadIdx.x >> 5;
+            if ((threadIdx.x & 31) == 0) {
+                s_red[parity][warp][0] = acc0;
+                s_red[parity][warp][1] = f32_formula ? static_cast<double>(s2) : acc1;
+            }
+            named_barrier(1 + row_in_cta, tpr);
+            const int first = row_in_cta * warps_per_row;
+            acc0 = 0.0; acc1 = 0.0; s2 = 0.0f;
+            for (int w = 0; w < warps_per_row; ++w) {
+                acc0 += s_red[parity][first + w][0];
+                if (f32_formula) s2 = __fadd_rn(s2, static_cast<float>(s_red[parity][first + w][1]));
+                else acc1 += s_red[parity][first + w][1];
+            }
+            parity ^= 1;
+        }
+        float mean = 0.0f, inv;
+        if constexpr (NORM == kNormLayer) {
+            const double w_d = static_cast<double>(width);
+            mean = static_cast<float>(acc0 / w_d);
+            inv = rsqrtf(static_cast<float>(acc1 / w_d - static_cast<double>(mean) * mean) + p.eps);
+        } else if (f32_formula) {
+            const float m = __fmul_rn(s2, __fdiv_rn(1.0f, static_cast<float>(width)));
+            inv = rsqrtf(__fadd_rn(m, p.eps));
+        } else {
+            inv = rsqrtf(static_cast<float>(acc1 / static_cast<double>(width)) + p.eps);
+        }
+        if (!valid) continue;
+
+        // ---- per-row operand offsets (32-bit arithmetic) ----
+        unsigned srow = nrow, col0 = 0;
+        if (p.sub32 > 1) { srow = nrow / p.sub32; col0 = (nrow - srow * p.sub32) * static_cast<unsigned>(width); }
+        int64_t vec_offset = col0;
+        if constexpr (POST == kPostModulate || POST == kPostScaleX || POST == kPostGatedResidual) {
+            if (p.vectors > 1) {
+                const unsigned vec = (srow / static_cast<unsigned>(p.rows_per_vector)) % static_cast<unsigned>(p.vectors);
+                vec_offset += static_cast<int64_t>(vec) * p.width;
+            }
+        }
+        int64_t f_offset = 0;
+        const unsigned f_width = static_cast<unsigned>(p.f_width);
+        float co[8], si[8];
+        if constexpr (kRope) {
+            unsigned frow = srow;
+            if (p.rows_per_f_row != 1) frow = srow / static_cast<unsigned>(p.rows_per_f_row);
+            if (frow >= static_cast<unsigned>(p.f_rows)) frow %= static_cast<unsigned>(p.f_rows);
+            f_offset = static_cast<int64_t>(frow) * p.f_width;
+            if constexpr (POST == kPostRopeShared) {
+                // every chunk of this thread reads the same table columns: load them once
+                const unsigned fc = (static_cast<unsigned>(lane_in_row) * 8u) % f_width;
+                load8<false>(p.cosine, p.f_dt, f_offset + fc, co);
+                load8<false>(p.sine, p.f_dt, f_offset + fc, si);
+            }
+        }
+
+        // ---- normalise, post-process, store ----
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+            const int chunk = lane_in_row + i * tpr;
+            if (!FULL && chunk >= nchunks) continue;
+            const int c = chunk * 8;
+            float y[8];
+            unpack<X_BF16>(xr[i], y);
+            if constexpr (NORM == kNormLayer) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(__fsub_rn(y[e], mean), inv);
+                if (has_w || has_b) {
+                    // weight / bias are converted to x's dtype first (:4069-4070)
+                    float w[8], b[8];
+                    if (has_w) { load8<false>(p.weight, p.w_dt, c, w); round8<X_BF16>(w); }
+                    if (has_b) { load8<false>(p.bias, p.b_dt, c, b); round8<X_BF16>(b); }
+                    if (has_w && has_b && p.affine_fma) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) y[e] = __fmaf_rn(y[e], w[e], b[e]);
+                    } else {
+                        if (has_w) {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(y[e], w[e]);
+                        }
+                        if (has_b) {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) y[e] = __fadd_rn(y[e], b[e]);
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(y[e], inv);
+                round8<X_BF16>(y);   // the normalised value is stored in the input dtype first (:900-902)
+                if (has_w) {
+                    // the weight is converted to the norm's output dtype (:4115)
+                    float w[8];
+                    load8<false>(p.weight, p.w_dt, c, w);
+                    round8<N_BF16>(w);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(y[e], w[e]);
+                }
+            }
+            round8<N_BF16>(y);       // what the unfused norm operator stores
+
+            if constexpr (kModulate) {
+                // common.cpp:51-61: 1+scale, product, +shift are three separately rounded F32 steps
+                float t1[8], sh[8];
+                if constexpr (kStaged) {
+                    const float4* a = reinterpret_cast<const float4*>(s_vec + c);
+                    const float4* b = reinterpret_cast<const float4*>(s_vec + width + c);
+                    const float4 a0 = a[0], a1 = a[1], b0 = b[0], b1 = b[1];
+                    t1[0] = a0.x; t1[1] = a0.y; t1[2] = a0.z; t1[3] = a0.w; t1[4] = a1.x; t1[5] = a1.y; t1[6] = a1.z; t1[7] = a1.w;
+                    sh[0] = b0.x; sh[1] = b0.y; sh[2] = b0.z; sh[3] = b0.w; sh[4] = b1.x; sh[5] = b1.y; sh[6] = b1.z; sh[7] = b1.w;
+                } else {
+                    load8<false>(p.scale, p.mod_dt, vec_offset + c, t1);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) t1[e] = __fadd_rn(1.0f, t1[e]);
+                    if (has_shift) load8<false>(p.shift, p.mod_dt, vec_offset + c, sh);
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    y[e] = __fmul_rn(y[e], t1[e]);
+                    if (has_shift) y[e] = __fadd_rn(y[e], sh[e]);
+                }
+            } else if constexpr (POST == kPostScaleX) {
+                float sc[8];
+                load8<false>(p.scale, p.mod_dt, vec_offset + c, sc);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sc[e] = __fadd_rn(1.0f, sc[e]);
+                round8<N_BF16>(sc);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(y[e], sc[e]);
+                round8<N_BF16>(y);
+            } else if constexpr (kRope) {
+                float r[8];
+                if constexpr (POST == kPostRope) {
+                    const unsigned fc = (col0 + static_cast<unsigned>(c)) % f_width;
+                    load8<false>(p.cosine, p.f_dt, f_offset + fc, co);
+                    load8<false>(p.sine, p.f_dt, f_offset + fc, si);
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float rotated = (e & 1) ? y[e ^ 1] : -y[e ^ 1];
+                    r[e] = __fadd_rn(__fmul_rn(y[e], co[e]), __fmul_rn(rotated, si[e]));
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) y[e] = r[e];
+            } else if constexpr (POST == kPostGatedResidual) {
+                float res[8], g[8];
+                load8<true>(p.residual, p.res_dt, row_offset + c, res);
+                const bool has_gate = p.gate != nullptr;
+                const int sd = p.state_dt;
+                round8_rt(sd, res);
+                round8_rt(sd, y);
+                if (has_gate) {
+                    load8<false>(p.gate, p.gate_dt, vec_offset + c, g);
+                    round8_rt(sd, g);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(y[e], g[e]);
+                    round8_rt(sd, y);
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) y[e] = __fadd_rn(res[e], y[e]);
+            }
+            store8(p.out, p.out_dt, row_offset + c, y);
+        }
+    }
+}
+
+#endif  // __CUDACC__
+
+// Row geometries with their own instantiation: the generic ones (threads per row read at run
+// time, every chunk guarded) for 1..8 chunks per thread, and the exact ones for the
+// production widths.
+enum Geometry {
+    kGenericFirst = 0,   // + index into {1,2,3,4,5,6,8} chunks per thread
+    kExact1536 = 7,      // 6 chunks x 32 threads   (Wan2.1-1.3B, Mochi text stream)
+    kExact3072 = 8,      // 6 chunks x 64 threads   (Mochi visual stream)
+    kExact5120 = 9,      // 5 chunks x 128 threads  (Wan2.2-A14B)
+    kExact2048 = 10,     // 4 chunks x 64 threads   (LTX)
+    kExact128 = 11,      // 2 chunks x 8 threads    (per-head q/k norm)
+};
+
+// Launches the row_kernel instantiation for `geometry`; one definition per (NORM, POST, DT)
+// lives in its own translation unit so the family compiles in parallel.
+template <int NORM, int POST, int DT>
+void launch_row_variant(const RowParams& p, int geometry, int64_t ctas, size_t smem, cudaStream_t stream);
+
+}  // namespace rowwise
+}  // namespace vrb

@@ -1,0 +1,48 @@
+// Instantiation helper for the row kernel family: each translation unit that includes this
+// header defines launch_row_variant<> for a few (NORM, POST, dtype class) combinations.
+#pragma once
+
+#include "vrb_rowwise.cuh"
+
+namespace vrb {
+namespace rowwise {
+
+// Grid = every CTA the device can hold at once (occupancy of this instantiation x SM count),
+// capped by the amount of work; CTAs stride over the rows.
+template <int NCH, int TPR, bool FULL, int NORM, int POST, int DT>
+void launch_one(const RowParams& p, int64_t ctas, size_t smem, cudaStream_t stream) {
+    static int per_sm = 0;
+    static size_t per_sm_smem = ~size_t{0};
+    if (per_sm == 0 || per_sm_smem != smem) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, row_kernel<NCH, TPR, FULL, NORM, POST, DT>, kRowThreads, smem) !=
+                cudaSuccess || n < 1)
+            n = 1;
+        per_sm = n;
+        per_sm_smem = smem;
+    }
+    row_kernel<NCH, TPR, FULL, NORM, POST, DT><<<grid_for(ctas, per_sm), kRowThreads, smem, stream>>>(p);
+}
+
+#define VRB_DEFINE_ROW_VARIANT(NORM, POST, DT)                                                                       \
+    template <>                                                                                                      \
+    void launch_row_variant<NORM, POST, DT>(const RowParams& p, int geometry, int64_t ctas, size_t smem,             \
+                                            cudaStream_t s) {                                                        \
+        switch (geometry) {                                                                                          \
+            case 0: launch_one<1, 0, false, NORM, POST, DT>(p, ctas, smem, s); break;                                \
+            case 1: launch_one<2, 0, false, NORM, POST, DT>(p, ctas, smem, s); break;                                \
+            case 2: launch_one<3, 0, false, NORM, POST, DT>(p, ctas, smem, s); break;                                \
+            case 3: launch_one<4, 0, false, NORM, POST, DT>(p, ctas, smem, s); break;                                \
+            case 4: launch_one<5, 0, false, NORM, POST, DT>(p, ctas, smem, s); break;                                \
+            case 5: launch_one<6, 0, false, NORM, POST, DT>(p, ctas, smem, s); break;                                \
+            case 6: launch_one<8, 0, false, NORM, POST, DT>(p, ctas, smem, s); break;                                \
+            case kExact1536: launch_one<6, 32, true, NORM, POST, DT>(p, ctas, smem, s); break;                       \
+            case kExact3072: launch_one<6, 64, true, NORM, POST, DT>(p, ctas, smem, s); break;                       \
+            case kExact5120: launch_one<5, 128, true, NORM, POST, DT>(p, ctas, smem, s); break;                      \
+            case kExact2048: launch_one<4, 64, true, NORM, POST, DT>(p, ctas, smem, s); break;                       \
+            default: launch_one<2, 8, true, NORM, POST, DT>(p, ctas, smem, s); break;                                \
+        }                                                                                                            \
+    }
+
+}  // namespace rowwise
+}  // namespace vrb
