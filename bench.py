@@ -1,0 +1,269 @@
+#!/usr/bin/env python
+"""Benchmark of the non-GEMM operator path: fused-op HBM GB/s on the Wan2.1-1.3B DiT-block chain.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 is launched with torch.distributed.run, one rank per GPU (NCCL); the driver of this
+repository's round runs `python -m torch.distributed.run --nnodes=1 --nproc-per-node N ...`.
+
+A step = one pass of the chain over one batch: both classifier-free-guidance branches of one
+DiT block (2 x 11 fused launches, 32760 tokens x 1536, FFN 8960; synthetic data).  The path
+partitions by token rows and needs no collective, so ranks work on independent batches
+(weak scaling) and `value` is the bytes all ranks moved divided by the slowest rank's time.
+`strong` additionally reports the same single batch split by tokens over the N ranks.
+
+One JSON line on stdout (rank 0):
+  value      algorithmic GB/s with inputs resident in HBM, CUDA-event time, max over ranks
+  e2e        the same metric through the host-buffer entry points of the C ABI (pinned host
+             inputs uploaded, results downloaded, inside the timed region)
+  roofline   the dominant kernel (table-driven GELU-tanh) against the measured HBM copy peak
+  cpu_baseline  the CPU oracle's chain on a bounded row sample, all host cores (N=1 only)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "fused-op HBM GB/s (Wan2.1-1.3B DiT-block non-GEMM chain)"
+UNIT = "GB/s"
+WORKLOAD = {
+    "workload": "wan2.1-1.3b dit block non-gemm chain, batch 2 (cfg)", "tokens": 32760, "dim": 1536, "heads": 12,
+    "head_dim": 128, "ffn": 8960, "hidden_dtype": "bf16", "launches_per_step": 22,
+    "l2": "every launch streams 0.2-1.2 GB of distinct tensors (> 126 MB L2), no flush needed",
+}
+# DRAM bytes (read + write) of one launch of the dominant kernel, unary_lut_kernel<2> on
+# [32760, 8960] bf16, from the ncu capture summarised in profiles/gelu_tanh_lut_wan21.md
+DOMINANT_TRAFFIC_BYTES = None
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock / throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the reference's host path / the CPU oracle's chain on the host cores."""
+    if rank != 0:
+        return
+    from oracle import cpu_chain
+    tokens = 2048   # bounded sample of the 2 x 32760 rows of a step
+    dt, nbytes, threads = cpu_chain.time_chain(tokens, steps=max(args.steps, 1), warmup=max(args.warmup, 1))
+    value = nbytes / dt / 1e9
+    sample = f"{tokens} of 65520 token rows per step (the chain is row-independent), {threads} OpenMP threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": WORKLOAD,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    from vrhino_b200 import _lib, ops, workloads
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = _lib.load()
+    be = ops.B200Backend(device=f"cuda:{local}")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- resident arm: both CFG branches of one block -------------------------------------------
+    branches = [workloads.WanBlock(be, seed=1000 * rank + b) for b in range(2)]
+    launches = [l for blk in branches for l in blk.launches()]
+    step_bytes = sum(l.bytes for l in launches)
+    dominant = [l for l in launches if l.name.startswith("H ")]
+    for _ in range(args.warmup):
+        for l in launches:
+            l.fn()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches_before = lib.vrb_launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dom_events = []
+    barrier()
+    start.record()
+    for _ in range(args.steps):
+        for l in launches:
+            if l in dominant:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); l.fn(); b.record()
+                dom_events.append((a, b))
+            else:
+                l.fn()
+    stop.record()
+    barrier()
+    total_ms = max_over_ranks(start.elapsed_time(stop))
+    gpu_launches = lib.vrb_launch_count() - launches_before
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = total_ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+    dom_ms = statistics.mean(a.elapsed_time(b) for a, b in dom_events)
+    dom_bytes = dominant[0].bytes
+    peak, peak_kind = measured_hbm_peak()
+    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+
+    # ---- strong scaling: one batch split by tokens over the ranks ------------------------------
+    strong = None
+    if world > 1:
+        tokens = 32760 // world
+        del branches, launches
+        torch.cuda.empty_cache()
+        shard = [workloads.WanBlock(be, tokens=tokens, grid=(1, 1, tokens), seed=7 + b) for b in range(2)]
+        sl = [l for blk in shard for l in blk.launches()]
+        for _ in range(args.warmup):
+            for l in sl:
+                l.fn()
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            for l in sl:
+                l.fn()
+        s1.record()
+        barrier()
+        strong_ms = max_over_ranks(s0.elapsed_time(s1)) / args.steps
+        strong = {"us_per_dit_block": strong_ms * 1e3, "tokens_per_rank": tokens,
+                  "value": world * sum(l.bytes for l in sl) / (strong_ms * 1e-3) / 1e9, "unit": UNIT}
+        del shard, sl
+        torch.cuda.empty_cache()
+        branches = [workloads.WanBlock(be, seed=1000 * rank)]
+    # ---- end-to-end arm: host buffers through the C ABI ------------------------------------------
+    e2e = workloads.WanBlockHost(branches[0])
+    e2e.step()   # first call sizes the staging buffers
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        e2e.step()
+    torch.cuda.synchronize()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / args.e2e_steps
+    # one branch per e2e step: half the bytes of a resident step
+    e2e_value = world * e2e.bytes_per_step / (e2e_ms * 1e-3) / 1e9
+    e2e_obj = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e.h2d_bytes, "d2h_bytes_per_step": e2e.d2h_bytes,
+               "ms_per_step": e2e_ms, "note": "one CFG branch (11 launches) per e2e step, pinned host buffers, 3-stream pipeline"}
+    lib.vrb_host_release()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import cpu_chain
+        tokens = 2048
+        dt, nbytes, threads = cpu_chain.time_chain(tokens, steps=3, warmup=1)
+        cpu = {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"{tokens} of 65520 token rows per step, unfused operator chain of the CPU oracle, {threads} OpenMP threads"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": WORKLOAD,
+            "us_per_dit_block": ms_per_step * 1e3,
+            "pct_of_nominal_8tbs": 100.0 * value / world / NOMINAL_HBM_GBS,
+            "pct_of_measured_copy_peak": 100.0 * value / world / peak,
+            "roofline": {"bound": "hbm", "kernel": "unary_lut_kernel<gelu_tanh> on [32760, 8960] bf16", "achieved": achieved,
+                         "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": DOMINANT_TRAFFIC_BYTES, "algorithmic_bytes": dom_bytes, "ms_per_launch": dom_ms},
+            "e2e": e2e_obj, "gpu_launches": int(gpu_launches), "clocks": clocks,
+        }
+        if strong:
+            line["strong"] = strong
+        if cpu:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -224,14 +224,30 @@ int vrb_cfg_euler(const void* sample, const void* unconditional, const void* con
 /* ---------------------------------------------------------------- host-buffer entry points -- */
 /* The reference's operators accept host tensors and upload them on demand (copy_to_device,
  * :3195); results come back through copy_to_host.  These forms do the same for whole fused
- * chains: arguments are HOST pointers, rows are streamed through pinned staging and device
- * buffers owned by the library in row blocks so upload, kernel and download overlap.
- * host_is_pinned != 0 promises x and out are page-locked (cudaMallocHost / cudaHostRegister),
- * which lets the copies run straight from and to them.  Synchronous: returns when out holds
- * the result.  vrb_host_release() frees the staging buffers. */
-int vrb_host_layer_norm_modulate(const void* x, int x_dtype, const void* scale, const void* shift,
+ * chains: every pointer is a HOST pointer.  Rows are cut into blocks and streamed through
+ * device buffers the library owns on three streams, so upload, kernel and download overlap;
+ * operands shared by all rows (vectors of `width`, the norm weight) are uploaded once.
+ * Full overlap needs page-locked host buffers (cudaMallocHost / cudaHostRegister).
+ * Synchronous: when a call returns, `out` holds the result.  These are the only entry points
+ * that allocate device memory; vrb_host_release() frees it. */
+
+/* vrb_layer_norm_modulate on host buffers; scale == NULL gives vrb_layer_norm_cast. */
+int vrb_host_layer_norm_modulate(const void* x, int x_dtype, const void* weight, int weight_dtype,
+                                 const void* bias, int bias_dtype, const void* scale, const void* shift,
                                  int mod_dtype, void* out, int out_dtype,
-                                 int64_t rows, int64_t width, float eps, int host_is_pinned);
+                                 int64_t rows, int64_t width, float eps);
+/* vrb_rms_norm_rope on host buffers; cos / sin are F32 [rows, f_width] (one table row per token,
+ * f_width dividing width) or NULL. */
+int vrb_host_rms_norm_rope(const void* x, int x_dtype, const void* weight, int weight_dtype,
+                           const void* cosine, const void* sine, int64_t f_width,
+                           void* out, int out_dtype, int64_t rows, int64_t width, int64_t norm_width,
+                           float eps);
+/* vrb_gated_residual on host buffers with one gate vector [width] (or NULL). */
+int vrb_host_gated_residual(const void* residual, int residual_dtype, const void* branch, int branch_dtype,
+                            const void* gate, int gate_dtype, void* out, int state_dtype,
+                            int64_t rows, int64_t width);
+/* vrb_activation on a host tensor viewed as [rows, width]. */
+int vrb_host_activation(int kind, const void* x, void* out, int dtype, int64_t rows, int64_t width);
 void vrb_host_release(void);
 
 #ifdef __cplusplus

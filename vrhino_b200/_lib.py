@@ -59,7 +59,10 @@ SIGNATURES = {
     "vrb_euler_update": [_vp, _vp, _vp, _i, _i64, _f, _i, _i, _vp],
     "vrb_flow_to_x0": [_vp, _vp, _vp, _i, _i64, _f, _i, _vp],
     "vrb_cfg_euler": [_vp, _vp, _vp, _vp, _vp, _i, _i64, _f, _f, _i, _i, _i, _vp],
-    "vrb_host_layer_norm_modulate": [_vp, _i, _vp, _vp, _i, _vp, _i, _i64, _i64, _f, _i],
+    "vrb_host_layer_norm_modulate": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i64, _i64, _f],
+    "vrb_host_rms_norm_rope": [_vp, _i, _vp, _i, _vp, _vp, _i64, _vp, _i, _i64, _i64, _i64, _f],
+    "vrb_host_gated_residual": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i64, _i64],
+    "vrb_host_activation": [_i, _vp, _vp, _i, _i64, _i64],
     "vrb_host_release": [],
 }
 _RESTYPES = {

@@ -123,3 +123,73 @@ def time_launches(launches: List[Launch], steps: int, warmup: int):
     for name, a, b in events:
         per[name] += a.elapsed_time(b) / steps
     return sum(per.values()), per
+
+
+class WanBlockHost:
+    """The same chain with every operand in page-locked HOST memory, run through the host-buffer
+    entry points of the C ABI (upload, kernel, download pipelined inside each call)."""
+
+    def __init__(self, blk: WanBlock):
+        import ctypes
+        from . import _lib
+        self._c, self._lib = ctypes, _lib
+        self.blk = blk
+
+        def pin(t):
+            return t.detach().cpu().contiguous().pin_memory()
+
+        self.x, self.q, self.k, self.proj = pin(blk.x), pin(blk.q), pin(blk.k), pin(blk.proj)
+        self.cross_q, self.cross_k, self.cross, self.ffn_out = pin(blk.cross_q), pin(blk.cross_k), pin(blk.cross), pin(blk.ffn_out)
+        self.ffn_hidden = pin(blk.ffn_hidden)
+        self.rows = [pin(r) for r in blk.rows]
+        self.wq, self.wk, self.wcq, self.wck = pin(blk.wq), pin(blk.wk), pin(blk.wcq), pin(blk.wck)
+        self.gamma3, self.beta3 = pin(blk.gamma3), pin(blk.beta3)
+        S = blk.x.shape[1]
+        self.cos, self.sin = pin(blk.cos.reshape(S, -1)), pin(blk.sin.reshape(S, -1))
+        hd = blk.x.dtype
+
+        def out_like(t, dtype=BF16):
+            return torch.empty(t.shape, dtype=dtype).pin_memory()
+
+        self.out = {k: out_like(self.x) for k in ("A", "Bq", "Bk", "D", "Eq", "G")}
+        self.out.update({k: out_like(self.x, hd) for k in ("C", "F", "I")})
+        self.out["Ek"] = out_like(self.cross_k)
+        self.out["H"] = out_like(self.ffn_hidden)
+        ins = [self.x] * 6 + [self.q, self.k, self.proj, self.cross_q, self.cross_k, self.cross, self.ffn_out, self.ffn_hidden,
+                              self.cos, self.sin, self.cos, self.sin]
+        self.h2d_bytes = _nbytes(*ins) + 6 * self.rows[0].numel() * 4 + 6 * self.wq.numel() * 4
+        self.d2h_bytes = _nbytes(*self.out.values())
+        self.bytes_per_step = sum(l.bytes for l in blk.launches())
+
+    def step(self):
+        P = lambda t: None if t is None else self._c.c_void_p(t.data_ptr())
+        code = lambda t: 0 if t is None else (2 if t.dtype == BF16 else 0)
+        call, o, r = self._lib.call, self.out, self.rows
+        S, D = self.x.shape[1], self.x.shape[2]
+        eps = self._c.c_float(1e-6)
+        F = self.ffn_hidden.shape[-1]
+        T = self.cross_k.shape[1]
+        d = self.cos.shape[-1]
+
+        def ln_mod(out, shift, scale, w=None, b=None):
+            call("vrb_host_layer_norm_modulate", P(self.x), code(self.x), P(w), code(w), P(b), code(b), P(scale), P(shift), 0,
+                 P(out), code(out), S, D, eps)
+
+        def rms_rope(x, w, out, rows, rope=True):
+            call("vrb_host_rms_norm_rope", P(x), code(x), P(w), 0, P(self.cos) if rope else None, P(self.sin) if rope else None,
+                 d, P(out), code(out), rows, D, D, eps)
+
+        def gated(branch, gate, out):
+            call("vrb_host_gated_residual", P(self.x), code(self.x), P(branch), code(branch), P(gate), 0, P(out), code(out), S, D)
+
+        ln_mod(o["A"], r[0], r[1])
+        rms_rope(self.q, self.wq, o["Bq"], S)
+        rms_rope(self.k, self.wk, o["Bk"], S)
+        gated(self.proj, r[2], o["C"])
+        ln_mod(o["D"], None, None, self.gamma3, self.beta3)
+        rms_rope(self.cross_q, self.wcq, o["Eq"], S, rope=False)
+        rms_rope(self.cross_k, self.wck, o["Ek"], T, rope=False)
+        gated(self.cross, None, o["F"])
+        ln_mod(o["G"], r[3], r[4])
+        call("vrb_host_activation", 2, P(self.ffn_hidden), P(o["H"]), 2, S, F)
+        gated(self.ffn_out, r[5], o["I"])
