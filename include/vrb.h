@@ -110,6 +110,27 @@ int vrb_group_norm(const void* x, int dtype, const void* weight, int weight_dtyp
                    int64_t batch, int64_t channels, int64_t spatial, int groups, float eps,
                    int fuse_silu, void* workspace, size_t workspace_bytes, vrb_stream stream);
 
+/* vrb_group_norm without a caller-provided workspace.  This entry point has no counterpart in
+ * the reference (whose operators take scratch from the backend's own temporary pool); it exists
+ * for callers that cannot hand over device scratch: a backend whose device budget is entirely
+ * owned by a memory planner, so nothing may be allocated once a step is running, or a host
+ * thread that must stay out of cudaMalloc because that call synchronises the device.
+ * The scratch is a fixed array inside the library's device image: each GPU that loads the
+ * library holds about 1 MiB for it until the process exits, and it limits the call to
+ * batch * groups <= VRB_GROUP_NORM_FIXED_SCRATCH_MAX_UNITS; larger problems are refused with
+ * VRB_ERR_WORKSPACE and must use vrb_group_norm.  No memory is allocated or freed, here or in
+ * anything it calls.  The first call on a device looks up the array's device address (one
+ * runtime query with that device current); make that first call before any stream capture
+ * begins.  All calls on a device share the one array, which keeps whatever the previous call
+ * wrote; this operator overwrites every slot it later reads, so nothing needs clearing, but
+ * two calls whose kernels can overlap on the GPU (different streams, no ordering between them)
+ * race on it -- order them on one stream or with events. */
+#define VRB_GROUP_NORM_FIXED_SCRATCH_MAX_UNITS 1024
+int vrb_group_norm_fixed_scratch(const void* x, int dtype, const void* weight, int weight_dtype,
+                                 const void* bias, int bias_dtype, void* out,
+                                 int64_t batch, int64_t channels, int64_t spatial, int groups, float eps,
+                                 int fuse_silu, vrb_stream stream);
+
 /* The two halves of vrb_group_norm for a tensor whose spatial axis is split over ranks:
  * moments[unit] = {n, sum(x - shift[unit]), sum((x - shift[unit])^2)} as three doubles per
  * unit over this rank's slice; slices add; vrb_group_norm_finalize turns the added moments

@@ -44,6 +44,7 @@ SIGNATURES = {
     "vrb_dequantize": [_i, _vp, _vp, _vp, _i, _i64, _i64, _i64, _vp],
     "vrb_group_norm_workspace_bytes": [_i64, _i],
     "vrb_group_norm": [_vp, _i, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i, _f, _i, _vp, _sz, _vp],
+    "vrb_group_norm_fixed_scratch": [_vp, _i, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i, _f, _i, _vp],
     "vrb_group_norm_moments": [_vp, _i, _i64, _i64, _i64, _i, _vp, _vp, _vp, _sz, _vp],
     "vrb_group_norm_finalize": [_vp, _vp, _i64, _f, _vp, _vp, _vp],
     "vrb_group_norm_apply": [_vp, _i, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i, _vp, _vp, _i, _vp],

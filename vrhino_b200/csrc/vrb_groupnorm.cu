@@ -16,6 +16,8 @@
 // split along its spatial axis over several GPUs can add the per-slice sums between 1 and 2.
 //
 // Axis RMSNorm reference: rms_norm_axis_parallel_kernel :1045-1095.
+#include <mutex>
+
 #include "vrb_common.cuh"
 
 namespace vrb {
@@ -279,6 +281,72 @@ extern "C" int vrb_group_norm(const void* x, int dtype, const void* weight, int 
                                                                              g.units, eps, mean, inverse);
     if (int rc = after_launch("group_norm finalize")) return rc;
     return run_apply(x, dtype, weight, weight_dtype, bias, bias_dtype, out, g, mean, inverse, fuse_silu, s);
+}
+
+// ---- GroupNorm with built-in scratch ----------------------------------------------------------
+// vrb_group_norm wants a caller-provided scratch buffer.  Some callers have no way to get one:
+// a backend whose whole device budget has been handed to a planner-owned pool (nothing may be
+// allocated while a step runs, and every byte is accounted for), or a host thread that must
+// never enter cudaMalloc because that call synchronises the device.  For them the library
+// carries a fixed scratch area of its own.  It is a plain global array in device memory, so
+// every GPU that loads the library gives up kFixedScratchBytes (about 1 MiB) until the process
+// exits, and it bounds the problem size: at most kFixedScratchUnits (batch x groups) units.
+namespace {
+constexpr int64_t kFixedScratchUnits = 1024;
+constexpr size_t fixed_up(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+constexpr size_t kFixedScratchBytes =
+    fixed_up(static_cast<size_t>(kFixedScratchUnits) * vrb::kMaxSplits * 2 * sizeof(double)) +
+    fixed_up(static_cast<size_t>(kFixedScratchUnits) * 3 * sizeof(double)) +
+    fixed_up(static_cast<size_t>(kFixedScratchUnits) * 2 * sizeof(float));
+
+static __device__ __align__(256) unsigned char g_fixed_scratch[kFixedScratchBytes];
+
+// In host code `g_fixed_scratch` is only a handle for the symbol, not an address a kernel can
+// use; the device address has to be asked for, per device, with that device current.
+std::mutex g_fixed_mutex;
+void* g_fixed_address[64] = {nullptr};
+
+int fixed_scratch_address(void** address) {
+    int device = 0;
+    const cudaError_t e0 = cudaGetDevice(&device);
+    if (e0 != cudaSuccess || device < 0 || device >= 64) {
+        vrb::set_error("group_norm_fixed_scratch: cannot identify the current device (%s)", cudaGetErrorString(e0));
+        return VRB_ERR_CUDA;
+    }
+    std::lock_guard<std::mutex> lock(g_fixed_mutex);
+    if (!g_fixed_address[device]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_fixed_scratch);
+        if (e != cudaSuccess || !p) {
+            vrb::set_error("CUDA error: %s (address of the built-in GroupNorm scratch)", cudaGetErrorString(e));
+            return VRB_ERR_CUDA;
+        }
+        g_fixed_address[device] = p;
+    }
+    *address = g_fixed_address[device];
+    return VRB_OK;
+}
+}  // namespace
+
+static_assert(kFixedScratchUnits == VRB_GROUP_NORM_FIXED_SCRATCH_MAX_UNITS, "header and kernel file disagree on the limit");
+
+extern "C" int vrb_group_norm_fixed_scratch(const void* x, int dtype, const void* weight, int weight_dtype,
+                                            const void* bias, int bias_dtype, void* out,
+                                            int64_t batch, int64_t channels, int64_t spatial, int groups, float eps,
+                                            int fuse_silu, vrb_stream stream) {
+    VRB_REQUIRE(batch > 0 && groups > 0, VRB_ERR_INVALID, "group_norm_fixed_scratch: group norm shape/groups mismatch");
+    const int64_t units = batch * groups;
+    VRB_REQUIRE(units <= kFixedScratchUnits, VRB_ERR_WORKSPACE,
+                "group_norm_fixed_scratch: %lld (batch x groups) units exceed the built-in scratch, which holds %lld; "
+                "use vrb_group_norm with a caller-provided workspace",
+                static_cast<long long>(units), static_cast<long long>(kFixedScratchUnits));
+    void* scratch = nullptr;
+    if (int rc = fixed_scratch_address(&scratch)) return rc;
+    // Nothing in the scratch has to start at zero: every slot this call reads (per-slice sums,
+    // per-unit moments, mean / inverse) is written earlier in the same call, so whatever the
+    // previous call left behind is simply overwritten.
+    return vrb_group_norm(x, dtype, weight, weight_dtype, bias, bias_dtype, out, batch, channels, spatial, groups, eps,
+                          fuse_silu, scratch, kFixedScratchBytes, stream);
 }
 
 extern "C" int vrb_group_norm_moments(const void* x, int dtype, int64_t batch, int64_t channels,
