@@ -1,0 +1,200 @@
+"""ctypes front-ends of the two libraries built from the REFERENCE's own sources by
+``oracle/Makefile`` (``make -C oracle ref``): ``_ref/libvrhino_ref_host.so`` (the reference's
+F32 host test backend + helper seams) and ``_ref/libvrhino_ref_cuda.so`` (the reference's CUDA
+backend compiled for sm_100a).
+
+TEST / BASELINE INFRASTRUCTURE ONLY: used to validate the oracle, to generate the golden
+vectors under ``tests/golden/`` and to time baselines.  ``available_*()`` say whether the
+libraries exist; nothing here reads the reference tree at run time.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+HOST_LIB = os.path.join(_HERE, "_ref", "libvrhino_ref_host.so")
+CUDA_LIB = os.path.join(_HERE, "_ref", "libvrhino_ref_cuda.so")
+_c = ctypes
+_fp = _c.POINTER(_c.c_float)
+F32, BF16, U8 = 0, 2, 5
+POLICY_BF16, POLICY_FP32, POLICY_BF16_ROLES, POLICY_BF16_GUIDANCE = 0, 1, 2, 3
+
+
+def available_host() -> bool:
+    return os.path.exists(HOST_LIB)
+
+
+def available_cuda() -> bool:
+    return os.path.exists(CUDA_LIB)
+
+
+def _f(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(_fp)
+
+
+class RefHost:
+    """The reference's host path (F32, family_test::Backend)."""
+
+    def __init__(self):
+        self.lib = ctypes.CDLL(HOST_LIB)
+        self.lib.refh_last_error.restype = _c.c_char_p
+        self.lib.refh_wan_chain_seconds.restype = _c.c_double
+
+    def _check(self, rc):
+        if rc != 0:
+            raise RuntimeError(self.lib.refh_last_error().decode())
+
+    def layer_norm(self, x, w, b, eps):
+        x = _f(x); out = np.empty_like(x)
+        w = None if w is None else _f(w); b = None if b is None else _f(b)
+        self._check(self.lib.refh_layer_norm(_ptr(x), _ptr(w), _ptr(b), _ptr(out), _c.c_int64(x.size // x.shape[-1]),
+                                             _c.c_int64(x.shape[-1]), _c.c_float(eps)))
+        return out
+
+    def rms_norm(self, x, w, eps):
+        x = _f(x); out = np.empty_like(x); w = None if w is None else _f(w)
+        self._check(self.lib.refh_rms_norm(_ptr(x), _ptr(w), _ptr(out), _c.c_int64(x.size // x.shape[-1]),
+                                           _c.c_int64(x.shape[-1]), _c.c_float(eps)))
+        return out
+
+    def activation(self, x, kind):
+        x = _f(x); out = np.empty_like(x)
+        self._check(self.lib.refh_activation(_ptr(x), _ptr(out), _c.c_int64(x.size), int(kind)))
+        return out
+
+    def rope(self, x, c, s):
+        x, c, s = _f(x), _f(c), _f(s); out = np.empty_like(x)
+        _, tokens, heads, width = x.shape
+        self._check(self.lib.refh_rope(_ptr(x), _ptr(c), _ptr(s), _ptr(out), _c.c_int64(tokens), _c.c_int64(heads), _c.c_int64(width)))
+        return out
+
+    def modulate(self, x, shift, scale):
+        x, shift, scale = _f(x), _f(shift), _f(scale); out = np.empty_like(x)
+        self._check(self.lib.refh_modulate(_ptr(x), _ptr(shift), _ptr(scale), _ptr(out), _c.c_int64(x.size // x.shape[-1]),
+                                           _c.c_int64(x.shape[-1])))
+        return out
+
+    def gated_residual(self, res, branch, gate):
+        res, branch = _f(res), _f(branch); out = np.empty_like(res)
+        gate = None if gate is None else _f(gate)
+        self._check(self.lib.refh_gated_residual(_ptr(res), _ptr(branch), _ptr(gate), _ptr(out),
+                                                 _c.c_int64(res.size // res.shape[-1]), _c.c_int64(res.shape[-1])))
+        return out
+
+    def cfg_euler(self, x, u, c, scale, delta):
+        x, u, c = _f(x), _f(u), _f(c)
+        guided, out = np.empty_like(x), np.empty_like(x)
+        self._check(self.lib.refh_cfg_euler(_ptr(x), _ptr(u), _ptr(c), _ptr(guided), _ptr(out), _c.c_int64(x.size),
+                                            _c.c_float(scale), _c.c_float(delta)))
+        return guided, out
+
+    def wan_chain_seconds(self, tokens, threads, steps, dim=1536, heads=12, ffn=8960, text=512, seed=0):
+        """Seconds per step of the Wan block chain on `tokens` rows, and its algorithmic bytes
+        (same accounting as the GPU arm, bf16-hidden contract, so the GB/s are comparable)."""
+        rng = np.random.default_rng(seed)
+        text = min(text, tokens)
+        t = lambda *shape: rng.standard_normal(shape, dtype=np.float32)
+        x, q, k, proj, cq, cr, fo = (t(tokens, dim) for _ in range(7))
+        ck, fh, mod = t(text, dim), t(tokens, ffn), t(6, dim) * 0.1
+        ws = [1 + 0.1 * t(dim) for _ in range(5)]
+        beta = 0.1 * t(dim)
+        ph = rng.uniform(-3, 3, size=(tokens, dim // heads)).astype(np.float32)
+        co, si = np.cos(ph), np.sin(ph)
+        sec = self.lib.refh_wan_chain_seconds(
+            _ptr(x), _ptr(q), _ptr(k), _ptr(proj), _ptr(cq), _ptr(ck), _ptr(cr), _ptr(fo), _ptr(fh), _ptr(mod),
+            _ptr(ws[0]), _ptr(ws[1]), _ptr(ws[2]), _ptr(ws[3]), _ptr(ws[4]), _ptr(beta), _ptr(co), _ptr(si),
+            _c.c_int64(tokens), _c.c_int64(text), _c.c_int64(dim), _c.c_int64(heads), _c.c_int64(ffn), int(threads), int(steps))
+        if sec < 0:
+            raise RuntimeError(self.lib.refh_last_error().decode())
+        act, vec, table = tokens * dim, dim * 4, tokens * (dim // heads) * 4
+        nbytes = (3 * (act * 4 + 2 * vec) + 2 * (act * 4 + vec + table) + 3 * (act * 6) + 2 * vec + (act * 4 + vec)
+                  + (text * dim * 4 + vec) + tokens * ffn * 4)
+        return sec, nbytes
+
+
+class RefCuda:
+    """The reference's CUDA backend; tensors are handles kept on the device between calls."""
+
+    def __init__(self, execution_dtype=BF16):
+        lib = ctypes.CDLL(CUDA_LIB)
+        lib.refc_last_error.restype = _c.c_char_p
+        for name in ("refc_upload", "refc_host_f32", "refc_numel", "refc_binary", "refc_cast", "refc_reshape", "refc_slice",
+                     "refc_layer_norm", "refc_rms_norm", "refc_activation", "refc_rope", "refc_group_norm", "refc_clamp",
+                     "refc_exp", "refc_sqrt", "refc_dequantize", "refc_modulate", "refc_attention_norm", "refc_operation_rope",
+                     "refc_residual_add", "refc_gated_residual", "refc_cfg_combine", "refc_euler_update", "refc_flow_to_x0"):
+            getattr(lib, name).restype = _c.c_int64
+        lib.refc_profile_total_ms.restype = _c.c_double
+        self.lib = lib
+        if lib.refc_init(int(execution_dtype)) != 0:
+            raise RuntimeError(lib.refc_last_error().decode())
+
+    def _h(self, h):
+        if h < 0:
+            raise RuntimeError(self.lib.refc_last_error().decode())
+        return h
+
+    @staticmethod
+    def _shape(shape):
+        return (_c.c_int64 * max(len(shape), 1))(*shape), len(shape)
+
+    def upload(self, array: np.ndarray, dtype: int):
+        """array: float32 payload for F32, uint16 bits for BF16, uint8 for U8."""
+        a = np.ascontiguousarray(array)
+        s, r = self._shape(a.shape)
+        return self._h(self.lib.refc_upload(_c.c_void_p(a.ctypes.data), int(dtype), r, s))
+
+    def host_f32(self, array):
+        a = _f(array)
+        s, r = self._shape(a.shape)
+        return self._h(self.lib.refc_host_f32(_ptr(a), r, s))
+
+    def download(self, h, shape):
+        dt = self.lib.refc_dtype(_c.c_int64(h))
+        np_dt = {F32: np.float32, BF16: np.uint16, U8: np.uint8}[dt]
+        out = np.empty(shape, dtype=np_dt)
+        if self.lib.refc_download(_c.c_int64(h), _c.c_void_p(out.ctypes.data), _c.c_int64(out.nbytes)) != 0:
+            raise RuntimeError(self.lib.refc_last_error().decode())
+        return out, dt
+
+    def free(self, h): self.lib.refc_free(_c.c_int64(h))
+    def clear(self): self.lib.refc_clear()
+    def synchronize(self): self.lib.refc_synchronize()
+
+    def _i(self, h): return _c.c_int64(h or 0)
+
+    def binary(self, kind, a, b): return self._h(self.lib.refc_binary(int(kind), self._i(a), self._i(b)))
+    def cast(self, x, dtype): return self._h(self.lib.refc_cast(self._i(x), int(dtype)))
+    def reshape(self, x, shape):
+        s, r = self._shape(shape)
+        return self._h(self.lib.refc_reshape(self._i(x), r, s))
+    def slice(self, x, dim, start, stop): return self._h(self.lib.refc_slice(self._i(x), _c.c_int64(dim), _c.c_int64(start), _c.c_int64(stop)))
+    def layer_norm(self, x, w, b, eps): return self._h(self.lib.refc_layer_norm(self._i(x), self._i(w), self._i(b), _c.c_float(eps)))
+    def rms_norm(self, x, w, eps, axis=-1, out_dtype=-1):
+        return self._h(self.lib.refc_rms_norm(self._i(x), self._i(w), _c.c_float(eps), _c.c_int64(axis), int(out_dtype)))
+    def activation(self, x, kind): return self._h(self.lib.refc_activation(self._i(x), int(kind)))
+    def rope(self, x, c, s): return self._h(self.lib.refc_rope(self._i(x), self._i(c), self._i(s)))
+    def group_norm(self, x, groups, w, b, eps): return self._h(self.lib.refc_group_norm(self._i(x), int(groups), self._i(w), self._i(b), _c.c_float(eps)))
+    def clamp(self, x, lo, hi): return self._h(self.lib.refc_clamp(self._i(x), _c.c_float(lo), _c.c_float(hi)))
+    def exp(self, x): return self._h(self.lib.refc_exp(self._i(x)))
+    def sqrt(self, x): return self._h(self.lib.refc_sqrt(self._i(x)))
+    def dequantize(self, kind, packed, scales, rows, inner, group_size, out_dtype):
+        p = np.ascontiguousarray(packed, dtype=np.uint8); s = _f(scales)
+        return self._h(self.lib.refc_dequantize(int(kind), _c.c_void_p(p.ctypes.data), _c.c_int64(p.nbytes), _ptr(s),
+                                                _c.c_int64(rows), _c.c_int64(inner), _c.c_int64(group_size), int(out_dtype)))
+    def modulate(self, policy, x, shift, scale): return self._h(self.lib.refc_modulate(int(policy), self._i(x), self._i(shift), self._i(scale)))
+    def attention_norm(self, policy, x, w, eps, axis=-1):
+        return self._h(self.lib.refc_attention_norm(int(policy), self._i(x), self._i(w), _c.c_float(eps), _c.c_int64(axis)))
+    def operation_rope(self, policy, x, c, s): return self._h(self.lib.refc_operation_rope(int(policy), self._i(x), self._i(c), self._i(s)))
+    def residual_add(self, policy, r, b): return self._h(self.lib.refc_residual_add(int(policy), self._i(r), self._i(b)))
+    def gated_residual(self, policy, r, b, g): return self._h(self.lib.refc_gated_residual(int(policy), self._i(r), self._i(b), self._i(g)))
+    def cfg_combine(self, policy, u, c, scale): return self._h(self.lib.refc_cfg_combine(int(policy), self._i(u), self._i(c), _c.c_float(scale)))
+    def euler_update(self, policy, x, pred, delta, subtract=True):
+        return self._h(self.lib.refc_euler_update(int(policy), self._i(x), self._i(pred), _c.c_float(delta), int(subtract)))
+    def flow_to_x0(self, policy, x, out, sigma): return self._h(self.lib.refc_flow_to_x0(int(policy), self._i(x), self._i(out), _c.c_float(sigma)))

@@ -1,0 +1,214 @@
+// C wrapper around the REFERENCE's own CUDA backend, compiled from the reference's sources
+// where they lie (see oracle/Makefile).  TEST INFRASTRUCTURE ONLY: it exists to produce golden
+// vectors from, and to time, the reference's real kernels on the same GPU.  This file contains
+// no reference code; it only calls the reference's public interfaces:
+//   vrhino::CudaBackend            native/include/vrhino/backend/cuda_backend.h
+//   helper seams                   native/include/vrhino/architecture.h:63-86
+//   vrhino::SamplingPrimitives     native/include/vrhino/sampling.h:171-203
+//   vrhino::PrecisionPolicy        native/include/vrhino/precision.h:95-140
+// Tensors are kept in a handle table so chains stay on the device between calls.
+#include <cstdint>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "vrhino/architecture.h"
+#include "vrhino/backend/cuda_backend.h"
+#include "vrhino/error.h"
+#include "vrhino/precision.h"
+#include "vrhino/sampling.h"
+#include "vrhino/tensor_util.h"
+
+using namespace vrhino;
+
+namespace {
+std::unique_ptr<CudaBackend> g_backend;
+std::map<int64_t, Tensor> g_tensors;
+int64_t g_next = 1;
+std::string g_error;
+
+int64_t keep(Tensor t) { g_tensors[g_next] = std::move(t); return g_next++; }
+const Tensor& at(int64_t h) {
+    auto it = g_tensors.find(h);
+    require(it != g_tensors.end(), "unknown tensor handle");
+    return it->second;
+}
+const Tensor* opt(int64_t h) { return h ? &at(h) : nullptr; }
+
+PrecisionPolicy policy_of(int id) {
+    // 0: unqualified_default(BF16) (residual bf16)   1: fp32() (residual F32)
+    // 2: 0 + guidance/solver/sigma scalar roles      3: 0 + guidance role only
+    PrecisionPolicy base = id == 1 ? PrecisionPolicy::fp32() : PrecisionPolicy::unqualified_default(DType::BF16);
+    if (id == 2)
+        return base.with_scalar_roles({PrecisionScalarRole::GuidanceCoefficient, PrecisionScalarRole::SolverCoefficient,
+                                       PrecisionScalarRole::Sigma});
+    if (id == 3) return base.with_scalar_roles({PrecisionScalarRole::GuidanceCoefficient});
+    return base;
+}
+
+template <typename F>
+int64_t guarded(F&& f) {
+    try {
+        require(g_backend != nullptr, "refc_init was not called");
+        return f();
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return -1;
+    }
+}
+}  // namespace
+
+extern "C" {
+
+const char* refc_last_error() { return g_error.c_str(); }
+
+int refc_init(int execution_dtype) {
+    try {
+        if (!g_backend) g_backend = std::make_unique<CudaBackend>();
+        g_backend->set_execution_dtype(static_cast<DType>(execution_dtype));
+        return 0;
+    } catch (const std::exception& e) { g_error = e.what(); return -1; }
+}
+void refc_shutdown() { g_tensors.clear(); g_backend.reset(); }
+void refc_free(int64_t h) { g_tensors.erase(h); }
+void refc_clear() { g_tensors.clear(); }
+void refc_synchronize() { if (g_backend) g_backend->synchronize(); }
+
+// host payload (dtype of the payload = dtype) -> device tensor of the same dtype
+int64_t refc_upload(const void* host, int dtype, int rank, const int64_t* shape) {
+    return guarded([&] {
+        std::vector<int64_t> s(shape, shape + rank);
+        Tensor h = Tensor::host(s, static_cast<DType>(dtype));
+        std::memcpy(h.data(), host, h.bytes());
+        return keep(g_backend->copy_to_device(h, static_cast<DType>(dtype)));
+    });
+}
+// host F32 payload kept on the HOST side (the reference's weights / scalars start there)
+int64_t refc_host_f32(const float* host, int rank, const int64_t* shape) {
+    return guarded([&] {
+        std::vector<int64_t> s(shape, shape + rank);
+        Tensor h = Tensor::host(s, DType::F32);
+        std::memcpy(h.data(), host, h.bytes());
+        return keep(h);
+    });
+}
+int refc_dtype(int64_t h) { return static_cast<int>(guarded([&] { return static_cast<int64_t>(at(h).dtype()); })); }
+int64_t refc_numel(int64_t h) { return guarded([&] { return at(h).numel(); }); }
+int refc_download(int64_t h, void* host, int64_t bytes) {
+    return static_cast<int>(guarded([&] {
+        Tensor t = g_backend->copy_to_host(at(h));
+        require(static_cast<int64_t>(t.bytes()) == bytes, "download size mismatch");
+        std::memcpy(host, t.data(), t.bytes());
+        return int64_t{0};
+    }));
+}
+
+int64_t refc_binary(int kind, int64_t a, int64_t b) {
+    return guarded([&] {
+        switch (kind) {
+            case 0: return keep(g_backend->add(at(a), at(b)));
+            case 1: return keep(g_backend->mul(at(a), at(b)));
+            case 2: return keep(g_backend->div(at(a), at(b)));
+            default: return keep(g_backend->maximum(at(a), at(b)));
+        }
+    });
+}
+int64_t refc_cast(int64_t x, int dtype) { return guarded([&] { return keep(g_backend->cast(at(x), static_cast<DType>(dtype))); }); }
+int64_t refc_reshape(int64_t x, int rank, const int64_t* shape) {
+    return guarded([&] { return keep(g_backend->reshape(at(x), std::vector<int64_t>(shape, shape + rank))); });
+}
+int64_t refc_slice(int64_t x, int64_t dim, int64_t start, int64_t stop) {
+    return guarded([&] { return keep(g_backend->slice(at(x), dim, start, stop)); });
+}
+int64_t refc_layer_norm(int64_t x, int64_t w, int64_t b, float eps) {
+    return guarded([&] { return keep(g_backend->layer_norm(at(x), opt(w), opt(b), eps)); });
+}
+// out_dtype < 0: the reference's default (same as the input)
+int64_t refc_rms_norm(int64_t x, int64_t w, float eps, int64_t axis, int out_dtype) {
+    return guarded([&] {
+        return keep(g_backend->rms_norm(at(x), opt(w), eps, axis, out_dtype < 0 ? DType::F16 : static_cast<DType>(out_dtype)));
+    });
+}
+int64_t refc_activation(int64_t x, int kind) {
+    return guarded([&] { return keep(g_backend->activation(at(x), static_cast<Activation>(kind))); });
+}
+int64_t refc_rope(int64_t x, int64_t c, int64_t s) { return guarded([&] { return keep(g_backend->rope_nd(at(x), at(c), at(s))); }); }
+int64_t refc_group_norm(int64_t x, int groups, int64_t w, int64_t b, float eps) {
+    return guarded([&] { return keep(g_backend->group_norm(at(x), groups, opt(w), opt(b), eps)); });
+}
+int64_t refc_clamp(int64_t x, float lo, float hi) { return guarded([&] { return keep(g_backend->clamp(at(x), lo, hi)); }); }
+int64_t refc_exp(int64_t x) { return guarded([&] { return keep(g_backend->exp(at(x))); }); }
+int64_t refc_sqrt(int64_t x) { return guarded([&] { return keep(g_backend->sqrt(at(x))); }); }
+
+// quantized weight: packed bytes + F32 scales on the host -> dequantised device tensor
+int64_t refc_dequantize(int type, const uint8_t* packed, int64_t packed_bytes, const float* scales, int64_t rows,
+                        int64_t inner, int64_t group_size, int out_dtype) {
+    return guarded([&] {
+        auto payload = std::make_shared<std::vector<uint8_t>>(packed, packed + packed_bytes);
+        Tensor weight = Tensor::borrowed(payload->data(), payload->size(), {rows, inner}, DType::U8);
+        auto info = std::make_shared<QuantizationInfo>();
+        info->type = type == 0 ? QuantType::FP8E4M3FN : type == 1 ? QuantType::INT8Symmetric : QuantType::INT4Symmetric;
+        info->logical_dtype = DType::BF16; info->compute_dtype = DType::BF16; info->accumulation_dtype = DType::F32;
+        info->group_size = group_size; info->axis = 1; info->symmetric = true;
+        info->granularity = group_size == inner ? "per_channel" : "per_group";
+        info->zero_point_mode = "none";
+        info->packing_layout = type == 0 ? "byte_e4m3fn" : type == 1 ? "byte_twos_complement" : "nibble_low_first_twos_complement";
+        const int64_t groups = (inner + group_size - 1) / group_size;
+        info->scales = host_f32({rows, groups}, std::vector<float>(scales, scales + rows * groups));
+        weight.set_quantization(info);
+        Tensor out = g_backend->copy_to_device(weight, static_cast<DType>(out_dtype));
+        g_backend->synchronize();   // payload must outlive the upload
+        return keep(out);
+    });
+}
+
+// ---- helper seams -------------------------------------------------------------------------
+int64_t refc_modulate(int policy, int64_t x, int64_t shift, int64_t scale) {
+    return guarded([&] { return keep(modulate(*g_backend, policy_of(policy), at(x), at(shift), at(scale))); });
+}
+int64_t refc_attention_norm(int policy, int64_t x, int64_t w, float eps, int64_t axis) {
+    return guarded([&] { return keep(attention_norm(*g_backend, policy_of(policy), at(x), opt(w), eps, axis)); });
+}
+int64_t refc_operation_rope(int policy, int64_t x, int64_t c, int64_t s) {
+    return guarded([&] { return keep(operation_rope(*g_backend, policy_of(policy), at(x), at(c), at(s))); });
+}
+int64_t refc_residual_add(int policy, int64_t r, int64_t b) {
+    return guarded([&] { return keep(residual_add(*g_backend, policy_of(policy), at(r), at(b))); });
+}
+int64_t refc_gated_residual(int policy, int64_t r, int64_t b, int64_t g) {
+    return guarded([&] { return keep(gated_residual(*g_backend, policy_of(policy), at(r), at(b), at(g))); });
+}
+int64_t refc_cfg_combine(int policy, int64_t u, int64_t c, float scale) {
+    return guarded([&] { SamplingPrimitives p(*g_backend, policy_of(policy)); return keep(p.cfg_combine(at(u), at(c), scale)); });
+}
+int64_t refc_euler_update(int policy, int64_t x, int64_t pred, float delta, int subtract) {
+    return guarded([&] {
+        SamplingPrimitives p(*g_backend, policy_of(policy));
+        return keep(p.euler_update(at(x), at(pred), scalar_f32(delta), subtract != 0));
+    });
+}
+int64_t refc_flow_to_x0(int policy, int64_t x, int64_t out, float sigma) {
+    return guarded([&] { SamplingPrimitives p(*g_backend, policy_of(policy)); return keep(p.flow_to_x0(at(x), at(out), sigma)); });
+}
+
+// ---- timing through the reference's own profiler ---------------------------------------------
+void refc_profile(int enabled) { if (g_backend) g_backend->enable_profiling(enabled != 0); }
+// Cumulative device milliseconds and call count over every profile entry recorded since
+// profiling was switched on (the reference keeps its aggregates; callers take differences).
+double refc_profile_total_ms(int64_t* calls) {
+    double total = 0.0;
+    int64_t n = 0;
+    try {
+        for (const auto& [name, stat] : g_backend->profile_stats()) {
+            if (name.rfind("reference.", 0) == 0) continue;
+            total += stat.device_milliseconds;
+            n += static_cast<int64_t>(stat.calls);
+        }
+    } catch (const std::exception& e) { g_error = e.what(); return -1.0; }
+    if (calls) *calls = n;
+    return total;
+}
+
+}  // extern "C"
