@@ -99,20 +99,41 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def cpu_arm(steps: int, warmup: int):
+    """Times the CPU arm on a bounded sample of the step's 65520 token rows (the chain is
+    row-independent).  Preferred: the reference's OWN host path (oracle/_ref/libvrhino_ref_host.so,
+    its F32 host backend driven through its helper seams, rows spread over all host threads);
+    otherwise the CPU oracle's restatement with OpenMP.  Returns (GB/s, seconds/step, description)."""
+    from oracle import ref
+    threads = os.cpu_count() or 1
+    if ref.available_host():
+        tokens = 1024
+        host = ref.RefHost()
+        for _ in range(max(warmup, 0)):
+            host.wan_chain_seconds(tokens=tokens, threads=threads, steps=1)
+        sec, nbytes = host.wan_chain_seconds(tokens=tokens, threads=threads, steps=max(steps, 1))
+        return nbytes / sec / 1e9, sec, {
+            "cores": threads, "kind": "reference",
+            "sample": f"{tokens} of 65520 token rows per step; the reference's host backend (F32, family_test::Backend) "
+                      f"through its own modulate/attention_norm/rope/residual helpers, {threads} threads"}
+    from oracle import cpu_chain
+    tokens = 2048
+    sec, nbytes, threads = cpu_chain.time_chain(tokens, steps=max(steps, 1), warmup=max(warmup, 1))
+    return nbytes / sec / 1e9, sec, {
+        "cores": threads, "kind": "port",
+        "sample": f"{tokens} of 65520 token rows per step; unfused operator chain of the CPU oracle, {threads} OpenMP threads"}
+
+
 def run_reference(args, rank, world):
-    """The reference arm: the reference's host path / the CPU oracle's chain on the host cores."""
+    """The reference arm: the reference's CPU implementation of the path on the host cores."""
     if rank != 0:
         return
-    from oracle import cpu_chain
-    tokens = 2048   # bounded sample of the 2 x 32760 rows of a step
-    dt, nbytes, threads = cpu_chain.time_chain(tokens, steps=max(args.steps, 1), warmup=max(args.warmup, 1))
-    value = nbytes / dt / 1e9
-    sample = f"{tokens} of 65520 token rows per step (the chain is row-independent), {threads} OpenMP threads"
+    value, sec, info = cpu_arm(min(args.steps, 20), min(args.warmup, 2))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "config": WORKLOAD,
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32" if info["kind"] == "reference" else "bf16", "data": "synthetic", "config": WORKLOAD,
+        "cpu_baseline": {"value": value, "unit": UNIT, **info},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -237,11 +258,8 @@ def main():
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        from oracle import cpu_chain
-        tokens = 2048
-        dt, nbytes, threads = cpu_chain.time_chain(tokens, steps=3, warmup=1)
-        cpu = {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
-               "sample": f"{tokens} of 65520 token rows per step, unfused operator chain of the CPU oracle, {threads} OpenMP threads"}
+        v, _, info = cpu_arm(steps=3, warmup=1)
+        cpu = {"value": v, "unit": UNIT, **info}
 
     if rank == 0:
         line = {
