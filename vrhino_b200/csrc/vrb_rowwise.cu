@@ -176,15 +176,16 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
     p.tpr = tpr;
     p.nrows32 = static_cast<unsigned>(nrows);
     p.sub32 = static_cast<unsigned>(sub);
+    p.inv_width = 1.0 / static_cast<double>(p.norm_width);
     const int rows_per_cta = kRowThreads / tpr;
     const int64_t ctas = (nrows + rows_per_cta - 1) / rows_per_cta;
     // One modulation vector for all rows and small enough for the default shared-memory limit:
     // stage 1+scale and shift per CTA instead of re-reading them for every row.
     size_t smem = 0;
     int post = p.post;
-    if (post == kPostModulate && p.vectors == 1 && sub == 1 && p.norm_width * 8 <= 40 * 1024) {
+    if (post == kPostModulate && p.vectors == 1 && sub == 1 && p.norm_width * 8 <= 32 * 1024) {
         post = kPostModulateStaged;
-        smem = static_cast<size_t>(p.norm_width) * 8;
+        smem = static_cast<size_t>(geometry <= 6 ? nch : (chunks / tpr)) * tpr * 8 * 2 * sizeof(float);
     }
     // RoPE table shared by the heads: the columns a thread needs are the same for all its chunks.
     if (post == kPostRope && p.norm_width % p.f_width == 0 && (static_cast<int64_t>(tpr) * 8) % p.f_width == 0)

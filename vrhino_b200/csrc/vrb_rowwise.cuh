@@ -59,6 +59,7 @@ struct RowParams {
     int rms_f64;               // RMS: the reference's double-accumulating fallback formula
     int tpr;                   // threads per normalised row
     unsigned nrows32, sub32;   // normalised rows, normalised rows per storage row
+    double inv_width;          // 1 / norm_width
 };
 
 constexpr int kRowThreads = 256;
@@ -160,8 +161,12 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
 // ---- vector kernel: norm_width % 8 == 0, 16-byte aligned operands ------------------------
 // CTAs per SM the register allocator must leave room for: the packed row takes 4 (bf16) or 8
 // (f32) registers per chunk; the rest of the budget is working state.
-constexpr int min_ctas_per_sm(int nch, bool x_bf16) {
-    const int row_regs = nch * (x_bf16 ? 4 : 8);
+__host__ __device__ constexpr int packed_regs(int nch, bool x_bf16) { return nch * (x_bf16 ? 4 : 8); }
+// The exact geometries prefetch the next row into a second register set while the current one
+// is being processed, if two packed rows fit in 48 registers.
+__host__ __device__ constexpr bool prefetches(int nch, bool x_bf16, bool full) { return full && 2 * packed_regs(nch, x_bf16) <= 48; }
+__host__ __device__ constexpr int min_ctas_per_sm(int nch, bool x_bf16, bool full) {
+    const int row_regs = packed_regs(nch, x_bf16) * (prefetches(nch, x_bf16, full) ? 2 : 1);
     return row_regs <= 16 ? 4 : row_regs <= 32 ? 3 : 2;
 }
 
@@ -169,14 +174,15 @@ constexpr int min_ctas_per_sm(int nch, bool x_bf16) {
 // TPR > 0 with FULL means the row is exactly NCH * TPR chunks wide, so chunk offsets are
 // compile-time constants and no chunk needs a bounds test (the production widths).
 template <int NCH, int TPR, bool FULL, int NORM, int POST, int DT>
-__global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F32)) row_kernel(const RowParams p) {
+__global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F32, FULL)) row_kernel(const RowParams p) {
     constexpr bool X_BF16 = DT != kF32F32;
+    constexpr bool PF = prefetches(NCH, X_BF16, FULL);
     constexpr bool N_BF16 = DT == kBf16Bf16;     // the unfused norm operator would store bf16
     constexpr bool kStaged = POST == kPostModulateStaged;
     constexpr bool kModulate = POST == kPostModulate || kStaged;
     constexpr bool kRope = POST == kPostRope || POST == kPostRopeShared;
     __shared__ double s_red[2][kRowThreads / 32][2];
-    extern __shared__ __align__(16) float s_vec[];   // staged modulate: [1+scale | shift]
+    extern __shared__ __align__(16) float s_vec[];   // staged modulate: [1+scale | shift], each NCH*tpr*8 floats
     const int tpr = TPR ? TPR : p.tpr;
     const int lane_in_row = threadIdx.x & (tpr - 1);
     const int row_in_cta = threadIdx.x / tpr;
@@ -192,9 +198,13 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
 
     if constexpr (kStaged) {
         // one modulation vector for every row: keep 1+scale and shift in shared memory
+        // layout: for chunk (l + i*tpr) the two float4 halves sit at float4 index (2i + half)*tpr + l,
+        // so the lanes of a warp read consecutive 16-byte words (no bank conflicts)
         for (int c = threadIdx.x; c < width; c += kRowThreads) {
-            s_vec[c] = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, c));
-            s_vec[width + c] = has_shift ? load1(p.shift, p.mod_dt, c) : 0.0f;
+            const int chunk = c >> 3, e = c & 7, i = chunk / tpr, l = chunk - i * tpr;
+            const int pos = (((i * 2 + (e >> 2)) * tpr + l) << 2) + (e & 3);
+            s_vec[pos] = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, c));
+            s_vec[NCH * tpr * 8 + pos] = has_shift ? load1(p.shift, p.mod_dt, c) : 0.0f;
         }
         __syncthreads();
     }
@@ -203,17 +213,28 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
 #pragma unroll
     for (int i = 0; i < NCH; ++i) own += (FULL || lane_in_row + i * tpr < nchunks) ? 8 : 0;
 
-    for (unsigned base = blockIdx.x * rows_per_cta; base < nrows; base += gridDim.x * rows_per_cta) {
+    const unsigned row_step = gridDim.x * rows_per_cta;
+    auto load_row = [&](unsigned first_row, Packed<X_BF16> (&dst)[NCH]) {
+        const unsigned r = first_row + row_in_cta;
+        const bool ok = r < nrows;
+        const int64_t off = static_cast<int64_t>(r) * width;
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+            const int chunk = lane_in_row + i * tpr;
+            dst[i] = (ok && (FULL || chunk < nchunks)) ? load_packed<X_BF16>(p.x, off + chunk * 8) : zero_packed<X_BF16>();
+        }
+    };
+    Packed<X_BF16> xr[NCH];
+    if constexpr (PF) load_row(blockIdx.x * rows_per_cta, xr);
+
+    for (unsigned base = blockIdx.x * rows_per_cta; base < nrows; base += row_step) {
         const unsigned nrow = base + row_in_cta;
         const bool valid = nrow < nrows;
         const int64_t row_offset = static_cast<int64_t>(nrow) * width;
 
-        Packed<X_BF16> xr[NCH];
-#pragma unroll
-        for (int i = 0; i < NCH; ++i) {
-            const int chunk = lane_in_row + i * tpr;
-            xr[i] = (valid && (FULL || chunk < nchunks)) ? load_packed<X_BF16>(p.x, row_offset + chunk * 8) : zero_packed<X_BF16>();
-        }
+        Packed<X_BF16> xn[PF ? NCH : 1];
+        if constexpr (PF) load_row(base + row_step, xn);   // next row, in flight during this one
+        else load_row(base, xr);
 
         // ---- statistics: per-thread F32 partials (pairwise inside a chunk) ----
         // LayerNorm sums x - K and (x - K)^2 with K = the thread's first element, so the
@@ -277,17 +298,17 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
         }
         float mean = 0.0f, inv;
         if constexpr (NORM == kNormLayer) {
-            const double w_d = static_cast<double>(width);
-            mean = static_cast<float>(acc0 / w_d);
-            inv = rsqrtf(static_cast<float>(acc1 / w_d - static_cast<double>(mean) * mean) + p.eps);
+            // S/W and Q/W as products with 1/W: equal to the quotients to within one ulp of a double,
+            // i.e. the same float except with probability 2^-29
+            mean = static_cast<float>(acc0 * p.inv_width);
+            inv = rsqrtf(static_cast<float>(acc1 * p.inv_width - static_cast<double>(mean) * mean) + p.eps);
         } else if (f32_formula) {
             const float m = __fmul_rn(s2, __fdiv_rn(1.0f, static_cast<float>(width)));
             inv = rsqrtf(__fadd_rn(m, p.eps));
         } else {
-            inv = rsqrtf(static_cast<float>(acc1 / static_cast<double>(width)) + p.eps);
+            inv = rsqrtf(static_cast<float>(acc1 * p.inv_width) + p.eps);
         }
-        if (!valid) continue;
-
+        if (valid) {
         // ---- per-row operand offsets (32-bit arithmetic) ----
         unsigned srow = nrow, col0 = 0;
         if (p.sub32 > 1) { srow = nrow / p.sub32; col0 = (nrow - srow * p.sub32) * static_cast<unsigned>(width); }
@@ -363,9 +384,9 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
                 // common.cpp:51-61: 1+scale, product, +shift are three separately rounded F32 steps
                 float t1[8], sh[8];
                 if constexpr (kStaged) {
-                    const float4* a = reinterpret_cast<const float4*>(s_vec + c);
-                    const float4* b = reinterpret_cast<const float4*>(s_vec + width + c);
-                    const float4 a0 = a[0], a1 = a[1], b0 = b[0], b1 = b[1];
+                    const float4* a = reinterpret_cast<const float4*>(s_vec) + (i * 2 * tpr + lane_in_row);
+                    const float4* b = reinterpret_cast<const float4*>(s_vec + NCH * tpr * 8) + (i * 2 * tpr + lane_in_row);
+                    const float4 a0 = a[0], a1 = a[tpr], b0 = b[0], b1 = b[tpr];
                     t1[0] = a0.x; t1[1] = a0.y; t1[2] = a0.z; t1[3] = a0.w; t1[4] = a1.x; t1[5] = a1.y; t1[6] = a1.z; t1[7] = a1.w;
                     sh[0] = b0.x; sh[1] = b0.y; sh[2] = b0.z; sh[3] = b0.w; sh[4] = b1.x; sh[5] = b1.y; sh[6] = b1.z; sh[7] = b1.w;
                 } else {
@@ -420,6 +441,11 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
                 for (int e = 0; e < 8; ++e) y[e] = __fadd_rn(res[e], y[e]);
             }
             store8(p.out, p.out_dt, row_offset + c, y);
+        }
+        }  // valid
+        if constexpr (PF) {
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) xr[i] = xn[i];
         }
     }
 }

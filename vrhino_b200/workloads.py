@@ -125,6 +125,26 @@ def time_launches(launches: List[Launch], steps: int, warmup: int):
     return sum(per.values()), per
 
 
+def _main():
+    """python -m vrhino_b200.workloads [--tokens N] [--only PREFIX] [--repeat R] [--hidden bf16|f32]
+
+    Runs (selected) launches of the Wan block chain a few times and prints their device times; a
+    small, self-contained command for profilers."""
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--only", default="")
+    ap.add_argument("--repeat", type=int, default=3)
+    ap.add_argument("--hidden", default="bf16", choices=["bf16", "f32"])
+    a = ap.parse_args()
+    be = ops.B200Backend()
+    blk = WanBlock(be, tokens=a.tokens, grid=(1, 1, a.tokens), hidden_dtype=BF16 if a.hidden == "bf16" else F32)
+    launches = [l for l in blk.launches() if l.name.startswith(a.only)]
+    total, per = time_launches(launches, steps=a.repeat, warmup=1)
+    for l in launches:
+        print(f"{l.name:20s} {per[l.name] * 1e3:9.1f} us {l.bytes / per[l.name] / 1e6:9.1f} GB/s {l.bytes / 1e6:9.1f} MB")
+
+
 class WanBlockHost:
     """The same chain with every operand in page-locked HOST memory, run through the host-buffer
     entry points of the C ABI (upload, kernel, download pipelined inside each call)."""
@@ -193,3 +213,7 @@ class WanBlockHost:
         ln_mod(o["G"], r[3], r[4])
         call("vrb_host_activation", 2, P(self.ffn_hidden), P(o["H"]), 2, S, F)
         gated(self.ffn_out, r[5], o["I"])
+
+
+if __name__ == "__main__":
+    _main()
