@@ -216,6 +216,32 @@ def main():
     peak, peak_kind = measured_hbm_peak()
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
 
+    # ---- the same step replayed from a CUDA graph (no host launch latency between kernels) ------
+    graph_obj = None
+    try:
+        side = torch.cuda.Stream()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for l in launches:
+                    l.fn()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            g.replay()
+        barrier()
+        g0.record()
+        for _ in range(args.steps):
+            g.replay()
+        g1.record()
+        barrier()
+        graph_ms = max_over_ranks(g0.elapsed_time(g1)) / args.steps
+        graph_obj = {"ms_per_step": graph_ms, "value": world * step_bytes / (graph_ms * 1e-3) / 1e9, "unit": UNIT,
+                     "kernels_per_replay": len(launches)}
+        del g
+    except Exception as exc:  # graph capture is an extra measurement, never the headline
+        graph_obj = {"error": str(exc)[:200]}
+
     # ---- strong scaling: one batch split by tokens over the ranks ------------------------------
     strong = None
     if world > 1:
@@ -274,6 +300,8 @@ def main():
                          "traffic": DOMINANT_TRAFFIC_BYTES, "algorithmic_bytes": dom_bytes, "ms_per_launch": dom_ms},
             "e2e": e2e_obj, "gpu_launches": int(gpu_launches), "clocks": clocks,
         }
+        if graph_obj:
+            line["cuda_graph_replay"] = graph_obj
         if strong:
             line["strong"] = strong
         if cpu:

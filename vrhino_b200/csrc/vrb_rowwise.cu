@@ -183,9 +183,15 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
     // stage 1+scale and shift per CTA instead of re-reading them for every row.
     size_t smem = 0;
     int post = p.post;
-    if (post == kPostModulate && p.vectors == 1 && sub == 1 && p.norm_width * 8 <= 32 * 1024) {
+    const size_t region = static_cast<size_t>(geometry <= 6 ? nch : (chunks / tpr)) * tpr * 8 * sizeof(float);
+    // LayerNorm weight and bias both present: stage them, converted to x's dtype, per CTA.
+    if (p.norm == kNormLayer && p.weight && p.bias && region * 4 <= 44 * 1024) {
+        p.affine_staged = 1;
+        smem += 2 * region;
+    }
+    if (post == kPostModulate && p.vectors == 1 && sub == 1 && smem + 2 * region <= 46 * 1024) {
         post = kPostModulateStaged;
-        smem = static_cast<size_t>(geometry <= 6 ? nch : (chunks / tpr)) * tpr * 8 * 2 * sizeof(float);
+        smem += 2 * region;
     }
     // RoPE table shared by the heads: the columns a thread needs are the same for all its chunks.
     if (post == kPostRope && p.norm_width % p.f_width == 0 && (static_cast<int64_t>(tpr) * 8) % p.f_width == 0)

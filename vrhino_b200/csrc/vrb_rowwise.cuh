@@ -60,6 +60,7 @@ struct RowParams {
     int tpr;                   // threads per normalised row
     unsigned nrows32, sub32;   // normalised rows, normalised rows per storage row
     double inv_width;          // 1 / norm_width
+    int affine_staged;         // LayerNorm weight / bias pre-rounded into shared memory
 };
 
 constexpr int kRowThreads = 256;
@@ -196,6 +197,19 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
     const bool f32_formula = NORM == kNormRms && !p.rms_f64;
     int parity = 0;
 
+    // LayerNorm weight / bias, already converted to x's dtype, staged once per CTA (same
+    // conflict-free layout as the modulation vectors, placed before them)
+    const int pad = NCH * tpr * 8;
+    float* const s_mod = s_vec + (p.affine_staged ? 2 * pad : 0);
+    if (NORM == kNormLayer && p.affine_staged) {
+        for (int c = threadIdx.x; c < width; c += kRowThreads) {
+            const int chunk = c >> 3, e = c & 7, i = chunk / tpr, l = chunk - i * tpr;
+            const int pos = (((i * 2 + (e >> 2)) * tpr + l) << 2) + (e & 3);
+            s_vec[pos] = has_w ? round_to(p.x_dt, load1(p.weight, p.w_dt, c)) : 1.0f;
+            s_vec[pad + pos] = has_b ? round_to(p.x_dt, load1(p.bias, p.b_dt, c)) : 0.0f;
+        }
+        if constexpr (!kStaged) __syncthreads();
+    }
     if constexpr (kStaged) {
         // one modulation vector for every row: keep 1+scale and shift in shared memory
         // layout: for chunk (l + i*tpr) the two float4 halves sit at float4 index (2i + half)*tpr + l,
@@ -203,8 +217,8 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
         for (int c = threadIdx.x; c < width; c += kRowThreads) {
             const int chunk = c >> 3, e = c & 7, i = chunk / tpr, l = chunk - i * tpr;
             const int pos = (((i * 2 + (e >> 2)) * tpr + l) << 2) + (e & 3);
-            s_vec[pos] = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, c));
-            s_vec[NCH * tpr * 8 + pos] = has_shift ? load1(p.shift, p.mod_dt, c) : 0.0f;
+            s_mod[pos] = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, c));
+            s_mod[pad + pos] = has_shift ? load1(p.shift, p.mod_dt, c) : 0.0f;
         }
         __syncthreads();
     }
@@ -349,8 +363,16 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
                 if (has_w || has_b) {
                     // weight / bias are converted to x's dtype first (:4069-4070)
                     float w[8], b[8];
-                    if (has_w) { load8<false>(p.weight, p.w_dt, c, w); round8<X_BF16>(w); }
-                    if (has_b) { load8<false>(p.bias, p.b_dt, c, b); round8<X_BF16>(b); }
+                    if (p.affine_staged) {
+                        const float4* wa = reinterpret_cast<const float4*>(s_vec) + (i * 2 * tpr + lane_in_row);
+                        const float4* ba = reinterpret_cast<const float4*>(s_vec + pad) + (i * 2 * tpr + lane_in_row);
+                        const float4 w0 = wa[0], w1 = wa[tpr], b0 = ba[0], b1 = ba[tpr];
+                        w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w; w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
+                        b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+                    } else {
+                        if (has_w) { load8<false>(p.weight, p.w_dt, c, w); round8<X_BF16>(w); }
+                        if (has_b) { load8<false>(p.bias, p.b_dt, c, b); round8<X_BF16>(b); }
+                    }
                     if (has_w && has_b && p.affine_fma) {
 #pragma unroll
                         for (int e = 0; e < 8; ++e) y[e] = __fmaf_rn(y[e], w[e], b[e]);
@@ -384,8 +406,8 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
                 // common.cpp:51-61: 1+scale, product, +shift are three separately rounded F32 steps
                 float t1[8], sh[8];
                 if constexpr (kStaged) {
-                    const float4* a = reinterpret_cast<const float4*>(s_vec) + (i * 2 * tpr + lane_in_row);
-                    const float4* b = reinterpret_cast<const float4*>(s_vec + NCH * tpr * 8) + (i * 2 * tpr + lane_in_row);
+                    const float4* a = reinterpret_cast<const float4*>(s_mod) + (i * 2 * tpr + lane_in_row);
+                    const float4* b = reinterpret_cast<const float4*>(s_mod + pad) + (i * 2 * tpr + lane_in_row);
                     const float4 a0 = a[0], a1 = a[tpr], b0 = b[0], b1 = b[tpr];
                     t1[0] = a0.x; t1[1] = a0.y; t1[2] = a0.z; t1[3] = a0.w; t1[4] = a1.x; t1[5] = a1.y; t1[6] = a1.z; t1[7] = a1.w;
                     sh[0] = b0.x; sh[1] = b0.y; sh[2] = b0.z; sh[3] = b0.w; sh[4] = b1.x; sh[5] = b1.y; sh[6] = b1.z; sh[7] = b1.w;
