@@ -7,6 +7,11 @@
 //   vrhino::SamplingPrimitives     native/include/vrhino/sampling.h:171-203
 //   vrhino::PrecisionPolicy        native/include/vrhino/precision.h:95-140
 // Tensors are kept in a handle table so chains stay on the device between calls.
+//
+// Compiled a second time with -DVRB_DROPIN (libvrhino_dropin_cuda.so) the SAME calls drive
+// vrhino_b200::B200Backend wrapped around the reference's CudaBackend: the reference's unmodified
+// helper code (modulate, gated_residual, SamplingPrimitives ...) then runs on this repository's
+// kernels, which is the drop-in claim under test; the refd_* entry points reach the fused forms.
 #include <cstdint>
 #include <cstring>
 #include <map>
@@ -20,11 +25,18 @@
 #include "vrhino/precision.h"
 #include "vrhino/sampling.h"
 #include "vrhino/tensor_util.h"
+#ifdef VRB_DROPIN
+#include "b200_backend.h"
+#endif
 
 using namespace vrhino;
 
 namespace {
+#ifdef VRB_DROPIN
+std::unique_ptr<vrhino_b200::B200Backend> g_backend;
+#else
 std::unique_ptr<CudaBackend> g_backend;
+#endif
 std::map<int64_t, Tensor> g_tensors;
 int64_t g_next = 1;
 std::string g_error;
@@ -66,7 +78,11 @@ const char* refc_last_error() { return g_error.c_str(); }
 
 int refc_init(int execution_dtype) {
     try {
+#ifdef VRB_DROPIN
+        if (!g_backend) g_backend = std::make_unique<vrhino_b200::B200Backend>(std::make_unique<CudaBackend>());
+#else
         if (!g_backend) g_backend = std::make_unique<CudaBackend>();
+#endif
         g_backend->set_execution_dtype(static_cast<DType>(execution_dtype));
         return 0;
     } catch (const std::exception& e) { g_error = e.what(); return -1; }
@@ -192,6 +208,39 @@ int64_t refc_euler_update(int policy, int64_t x, int64_t pred, float delta, int 
 int64_t refc_flow_to_x0(int policy, int64_t x, int64_t out, float sigma) {
     return guarded([&] { SamplingPrimitives p(*g_backend, policy_of(policy)); return keep(p.flow_to_x0(at(x), at(out), sigma)); });
 }
+
+#ifdef VRB_DROPIN
+// ---- fused forms of the drop-in backend (call-site view of vrhino_b200/host/b200_backend.h) ---
+const char* refc_backend_name() { static std::string n; n = g_backend ? g_backend->name() : ""; return n.c_str(); }
+int64_t refd_layer_norm_modulate(int policy, int64_t x, int64_t w, int64_t b, float eps, int64_t shift, int64_t scale, int out_dtype) {
+    return guarded([&] {
+        return keep(vrhino_b200::layer_norm_modulate(*g_backend, policy_of(policy), at(x), opt(w), opt(b), eps, at(shift), at(scale),
+                                                     static_cast<DType>(out_dtype)));
+    });
+}
+int64_t refd_rms_norm_rope(int policy, int64_t x, int64_t w, float eps, int64_t c, int64_t s, int heads, int per_head, int out_dtype) {
+    return guarded([&] {
+        return keep(vrhino_b200::rms_norm_rope(*g_backend, policy_of(policy), at(x), opt(w), eps, opt(c), opt(s), heads, per_head != 0,
+                                               static_cast<DType>(out_dtype)));
+    });
+}
+int64_t refd_gated_residual(int policy, int64_t r, int64_t b, int64_t g) {
+    return guarded([&] { return keep(vrhino_b200::fused_gated_residual(*g_backend, policy_of(policy), at(r), at(b), opt(g))); });
+}
+int64_t refd_swiglu(int64_t x) { return guarded([&] { return keep(vrhino_b200::swiglu(*g_backend, at(x))); }); }
+int64_t refd_group_norm_silu(int64_t x, int groups, int64_t w, int64_t b, float eps) {
+    return guarded([&] { return keep(vrhino_b200::group_norm_silu(*g_backend, at(x), groups, opt(w), opt(b), eps)); });
+}
+int64_t refd_cfg_euler(int64_t x, int64_t u, int64_t c, float guidance, float delta, int subtract, int guidance_role, int solver_role) {
+    return guarded([&] {
+        return keep(g_backend->cfg_euler(at(x), at(u), at(c), guidance, delta, subtract != 0, guidance_role != 0, solver_role != 0));
+    });
+}
+// An operator failure must leave the session terminal, like the reference's (memory.h:225-236).
+int refd_session_terminal() { return g_backend && g_backend->resource_session_terminal() ? 1 : 0; }
+#else
+const char* refc_backend_name() { static std::string n; n = g_backend ? g_backend->name() : ""; return n.c_str(); }
+#endif
 
 // ---- timing through the reference's own profiler ---------------------------------------------
 void refc_profile(int enabled) { if (g_backend) g_backend->enable_profiling(enabled != 0); }

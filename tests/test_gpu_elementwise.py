@@ -117,6 +117,29 @@ def test_activation_exhaustive_bf16(orc, gpu, kind):
     assert (d == 0).mean() > 0.99, f"{ACT_NAMES[kind]}: only {(d == 0).mean():.4f} of the table is bit-identical"
 
 
+def test_table_path_equals_direct_path(gpu):
+    """bf16 tensors of 4M elements and more run through the 128 KB function table in shared
+    memory (prebuilt once per operator and parameters, then reused): every bf16 code must come
+    out exactly as from the direct kernel, on the first launch (which builds the table) and on
+    the second (which reuses it); same for clamp bounds and for SwiGLU's SiLU table."""
+    import torch
+    be, ops = gpu
+    codes = torch.arange(65536, dtype=torch.int32, device="cuda").to(torch.int16).view(torch.bfloat16)
+    big = codes.repeat(80)
+    for label, fn in [("silu", lambda t: be.activation(t, 0)), ("gelu_tanh", lambda t: be.activation(t, 2)),
+                      ("clamp", lambda t: be.clamp(t, -0.5, 0.75)), ("clamp2", lambda t: be.clamp(t, -1.0, 2.0)),
+                      ("exp", be.exp), ("sqrt", be.sqrt)]:
+        direct = fn(codes).view(torch.int16)
+        for attempt in range(2):
+            got = fn(big).view(torch.int16).reshape(80, 65536)
+            assert torch.equal(got, direct.expand(80, 65536)), (label, attempt)
+    from vrhino_b200 import synth
+    proj = torch.from_numpy(synth.normal((1, 640, 2 * 8192), seed=3)).cuda().to(torch.bfloat16)
+    whole = ops.fused_swiglu(be, proj)
+    parts = torch.cat([ops.fused_swiglu(be, proj[:, r:r + 64].contiguous()) for r in range(0, 640, 64)], dim=1)
+    assert torch.equal(whole.view(torch.int16), parts.view(torch.int16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("kind", [0, 2, 3])
 @pytest.mark.parametrize("n", [37, 8 * 4096 + 8])

@@ -17,6 +17,8 @@ CASES = [
     ((1, 64, 4, 16, 16), 32, 1e-6),                        # direct, 5-D statistics
     ((3, 64, 24, 40), 32, 1e-5),                           # direct, Mochi per-frame form
     ((1, 32, 3, 120, 128), 4, 1e-6),                       # count = 368640 > 2^18: multi-partial path
+    ((1, 32, 9, 120, 128), 8, 1e-6),                       # 4.4 M elements: bf16 + SiLU takes the table kernel
+    ((5, 64, 1, 120, 112), 32, 1e-6),                      # same, per-frame form with a ragged last tile
 ]
 
 

@@ -72,7 +72,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             fh.write("\n".join(logs))
     objects = [os.path.join(OBJ, os.path.basename(s)[:-3] + ".o") for s in _sources()]
     if force or jobs or _stale(LIB, objects):
-        subprocess.run([nvcc, "-shared", "-o", LIB, *objects, "-lcudart"], check=True)
+        subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB, *objects, "-lcudart"], check=True)
     return LIB
 
 

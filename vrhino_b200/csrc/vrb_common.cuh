@@ -52,11 +52,17 @@ inline int grid_for(int64_t work_items, int per_sm) {
 }
 
 // Table-driven bf16 unary / SwiGLU kernels (vrb_lut.cu).  op: 0-4 activation kinds, 5 clamp,
-// 6 exp, 7 sqrt.  Worth their ~10 us table fill only for large tensors.
-constexpr int64_t kLutMinElements = int64_t{32} << 20;
+// 6 exp, 7 sqrt.  Worth the 128 KB table copy per SM only for large tensors.
+constexpr int64_t kLutMinElements = int64_t{4} << 20;
 bool unary_lut_applicable(int dtype, int64_t count, const void* x, const void* out);
 int launch_unary_lut(int op, const void* x, void* out, int64_t count, float p0, float p1, cudaStream_t stream);
 int launch_swiglu_lut(const void* proj, void* out, int64_t rows, int64_t hidden, cudaStream_t stream);
+// GroupNorm normalise pass on bf16 followed by SiLU through the table: x is [planes, spatial]
+// with spatial % 8 == 0; plane p belongs to channel p % channels and statistics unit
+// (p / channels) * groups + channel / channels_per.
+int launch_group_norm_apply_silu_lut(const void* x, const void* weight, int w_dt, const void* bias, int b_dt, void* out,
+                                     int64_t planes, int64_t channels, int channels_per, int groups, int64_t spatial,
+                                     const float* mean, const float* inverse, cudaStream_t stream);
 
 // ------------------------------------------------------------------------ device side --
 #ifdef __CUDACC__

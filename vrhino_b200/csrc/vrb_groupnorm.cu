@@ -67,18 +67,25 @@ __global__ void __launch_bounds__(kThreads) gn_partial_kernel(const void* x, int
     if constexpr (VEC) {
         const int64_t chunks = count >> 3;
         const int64_t begin = chunks * split / splits, end = chunks * (split + 1) / splits;
-        for (int64_t c = begin + threadIdx.x; c < end; c += kThreads) {
-            float v[8];
-            load8<true>(x, dt, base + c * 8, v);
-            float t1 = 0.0f, t2 = 0.0f;
+        constexpr int U = 4;   // independent 16-byte loads in flight per thread
+        for (int64_t c0 = begin + threadIdx.x; c0 < end; c0 += kThreads * U) {
+            float v[U][8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const float d = __fsub_rn(v[e], a);
-                t1 = __fadd_rn(t1, d);
-                t2 = __fmaf_rn(d, d, t2);
+            for (int u = 0; u < U; ++u)
+                if (c0 + u * kThreads < end) load8<true>(x, dt, base + (c0 + u * kThreads) * 8, v[u]);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (c0 + u * kThreads >= end) break;
+                float t1 = 0.0f, t2 = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float d = __fsub_rn(v[u][e], a);
+                    t1 = __fadd_rn(t1, d);
+                    t2 = __fmaf_rn(d, d, t2);
+                }
+                s1 += static_cast<double>(t1);
+                s2 += static_cast<double>(t2);
             }
-            s1 += static_cast<double>(t1);
-            s2 += static_cast<double>(t2);
         }
     } else {
         const int64_t begin = count * split / splits, end = count * (split + 1) / splits;
@@ -124,30 +131,58 @@ __device__ __forceinline__ float gn_value(float x, float mean, float inv, float 
     return y;
 }
 
+// Per-plane constants of the normalise pass.  gamma / beta are converted to x's dtype first (:4929).
+struct PlaneTerms {
+    float mean, inv, gamma, beta;
+};
+__device__ __forceinline__ PlaneTerms plane_terms(int64_t plane, const GnGeom& g, int dt, const void* weight, int w_dt,
+                                                  const void* bias, int b_dt, const float* mean, const float* inverse) {
+    const int64_t channel = plane % g.channels;
+    const int64_t unit = (plane / g.channels) * g.groups + channel / g.channels_per;
+    PlaneTerms t;
+    t.mean = __ldg(mean + unit);
+    t.inv = __ldg(inverse + unit);
+    t.gamma = weight ? round_to(dt, load1(weight, w_dt, channel)) : 1.0f;
+    t.beta = bias ? round_to(dt, load1(bias, b_dt, channel)) : 0.0f;
+    return t;
+}
+
+// Normalise pass.  VEC: the tensor is cut into tiles of kThreads * U 8-element chunks that lie
+// inside ONE plane (one channel of one batch entry), so mean / inverse / gamma / beta are looked
+// up once per tile and the inner loop has no index arithmetic beyond an add.
 template <bool VEC>
 __global__ void __launch_bounds__(kThreads) gn_apply_kernel(const void* x, int dt, const void* weight, int w_dt,
                                                            const void* bias, int b_dt, void* out, GnGeom g,
                                                            const float* mean, const float* inverse, int silu) {
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    const int64_t total = g.units * g.count;
-    const int64_t items = VEC ? total >> 3 : total;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < items; i += stride) {
-        const int64_t e0 = VEC ? i * 8 : i;
-        const int64_t plane = e0 / g.spatial;          // batch * channels + channel
-        const int64_t channel = plane % g.channels;
-        const int64_t unit = (plane / g.channels) * g.groups + channel / g.channels_per;
-        const float m = __ldg(mean + unit), inv = __ldg(inverse + unit);
-        // gamma / beta are converted to x's dtype first (:4929)
-        const float gamma = weight ? round_to(dt, load1(weight, w_dt, channel)) : 1.0f;
-        const float beta = bias ? round_to(dt, load1(bias, b_dt, channel)) : 0.0f;
-        if constexpr (VEC) {
-            float v[8];
-            load8<true>(x, dt, e0, v);
+    if constexpr (VEC) {
+        constexpr int U = 4;
+        constexpr int kTile = kThreads * U;
+        const int64_t plane_chunks = g.spatial >> 3;
+        const int64_t tiles_per_plane = (plane_chunks + kTile - 1) / kTile;
+        const int64_t tiles = g.batch * g.channels * tiles_per_plane;
+        for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+            const int64_t plane = t / tiles_per_plane;
+            const int64_t c0 = (t - plane * tiles_per_plane) * kTile + threadIdx.x;
+            const PlaneTerms k = plane_terms(plane, g, dt, weight, w_dt, bias, b_dt, mean, inverse);
+            const int64_t e_plane = plane * g.spatial;
+            float v[U][8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = gn_value(v[e], m, inv, gamma, beta, dt, silu);
-            store8(out, dt, e0, v);
-        } else {
-            store1(out, dt, e0, gn_value(load1(x, dt, e0), m, inv, gamma, beta, dt, silu));
+            for (int u = 0; u < U; ++u)
+                if (c0 + u * kThreads < plane_chunks) load8<true>(x, dt, e_plane + (c0 + u * kThreads) * 8, v[u]);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (c0 + u * kThreads >= plane_chunks) break;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[u][e] = gn_value(v[u][e], k.mean, k.inv, k.gamma, k.beta, dt, silu);
+                store8(out, dt, e_plane + (c0 + u * kThreads) * 8, v[u]);
+            }
+        }
+    } else {
+        const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+        const int64_t total = g.units * g.count;
+        for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+            const PlaneTerms k = plane_terms(i / g.spatial, g, dt, weight, w_dt, bias, b_dt, mean, inverse);
+            store1(out, dt, i, gn_value(load1(x, dt, i), k.mean, k.inv, k.gamma, k.beta, dt, silu));
         }
     }
 }
@@ -191,8 +226,11 @@ int run_apply(const void* x, int dt, const void* weight, int w_dt, const void* b
     const bool vec = g.spatial % 8 == 0 && aligned16(x) && aligned16(out);
     const int64_t total = g.units * g.count;
     if (vec) {
-        const int64_t chunks = total / 8;
-        gn_apply_kernel<true><<<grid_for((chunks + kThreads - 1) / kThreads, 8), kThreads, 0, s>>>(
+        if (dt == VRB_BF16 && silu && total >= kLutMinElements)   // SiLU of a bf16 value: table lookup
+            return launch_group_norm_apply_silu_lut(x, weight, w_dt, bias, b_dt, out, g.batch * g.channels, g.channels,
+                                                    g.channels_per, g.groups, g.spatial, mean, inverse, s);
+        const int64_t tiles = g.batch * g.channels * ((g.spatial / 8 + kThreads * 4 - 1) / (kThreads * 4));
+        gn_apply_kernel<true><<<grid_for(tiles, 8), kThreads, 0, s>>>(
             x, dt, weight, w_dt, bias, b_dt, out, g, mean, inverse, silu);
     } else {
         gn_apply_kernel<false><<<grid_for((total + kThreads - 1) / kThreads, 8), kThreads, 0, s>>>(

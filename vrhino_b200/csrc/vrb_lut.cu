@@ -4,14 +4,21 @@
 // table has 65536 bf16 entries = 128 KB, which fits the shared memory of one SM.  For large
 // tensors that beats evaluating the expression per element: GELU-tanh through tanhf costs
 // about 30 instructions per element, more than the ~22 issue slots per element an SM has at
-// full HBM rate, while a table lookup costs about 3.  Every CTA (one per SM, 1024 threads)
-// first fills its table by evaluating the SAME expression the direct kernel evaluates
-// (activation_value(), i.e. the reference's activation_kernel expressions,
-// native/src/backend/cuda/cuda_backend.cu:1098-1109) on every possible input, then streams the
-// tensor through it.  The result is therefore bit-identical to the direct kernel by
-// construction.  The fill costs about 10 us per launch, so callers use it only above a size
-// threshold.
+// full HBM rate, while a table lookup costs about 3.  The table is built by evaluating the SAME
+// expression the direct kernel evaluates (activation_value(), i.e. the reference's
+// activation_kernel expressions, native/src/backend/cuda/cuda_backend.cu:1098-1109) on every
+// possible input, so the result is bit-identical to the direct kernel by construction.
+//
+// Building the table costs about 10 us of an SM's time, so it is built ONCE per (device,
+// operator, parameters) into device memory by a small kernel and kept; every later launch
+// copies the 128 KB from L2 into its shared memory (about 1 us, issued behind the first tensor
+// loads).  When the table cannot be built ahead (the stream is being captured into a graph, or
+// the small cache is full) the kernel falls back to filling its shared table itself.
 #include "vrb_common.cuh"
+
+#include <cstring>
+#include <mutex>
+#include <vector>
 
 namespace vrb {
 namespace {
@@ -29,10 +36,28 @@ __device__ __forceinline__ float lut_value(float x, float p0, float p1) {
 }
 
 template <int OP>
-__device__ __forceinline__ void fill_table(uint16_t* table, float p0, float p1) {
-    for (int i = threadIdx.x; i < kTableEntries; i += kLutThreads)
-        table[i] = static_cast<uint16_t>(float_to_bf16_bits(lut_value<OP>(bf16_bits_to_float(static_cast<uint32_t>(i)), p0, p1)));
+__device__ __forceinline__ uint16_t table_entry(int i, float p0, float p1) {
+    return static_cast<uint16_t>(float_to_bf16_bits(lut_value<OP>(bf16_bits_to_float(static_cast<uint32_t>(i)), p0, p1)));
+}
+
+// Shared table from the prebuilt copy in device memory (ready != nullptr) or evaluated here.
+template <int OP>
+__device__ __forceinline__ void fill_table(uint16_t* table, const uint4* __restrict__ ready, float p0, float p1) {
+    if (ready != nullptr) {
+        uint4* dst = reinterpret_cast<uint4*>(table);
+#pragma unroll
+        for (int i = 0; i < kTableBytes / 16 / kLutThreads; ++i)
+            dst[threadIdx.x + i * kLutThreads] = __ldg(ready + threadIdx.x + i * kLutThreads);
+    } else {
+        for (int i = threadIdx.x; i < kTableEntries; i += kLutThreads) table[i] = table_entry<OP>(i, p0, p1);
+    }
     __syncthreads();
+}
+
+template <int OP>
+__global__ void __launch_bounds__(kLutThreads) build_table_kernel(uint16_t* __restrict__ table, float p0, float p1) {
+    const int i = blockIdx.x * kLutThreads + threadIdx.x;
+    if (i < kTableEntries) table[i] = table_entry<OP>(i, p0, p1);
 }
 
 __device__ __forceinline__ uint32_t lookup2(const uint16_t* table, uint32_t word) {
@@ -41,16 +66,24 @@ __device__ __forceinline__ uint32_t lookup2(const uint16_t* table, uint32_t word
 
 template <int OP>
 __global__ void __launch_bounds__(kLutThreads, 1) unary_lut_kernel(const uint4* __restrict__ x, uint4* __restrict__ out,
-                                                                  int64_t chunks, float p0, float p1) {
+                                                                  int64_t chunks, const uint4* __restrict__ ready,
+                                                                  float p0, float p1) {
     extern __shared__ __align__(16) uint16_t table[];
-    fill_table<OP>(table, p0, p1);
     constexpr int U = 4;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kLutThreads;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * kLutThreads + threadIdx.x; i < chunks; i += stride * U) {
-        uint4 r[U];
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * kLutThreads + threadIdx.x;
+    uint4 r[U];
+    // The first tensor loads go out before the table copy so HBM is busy while the table arrives.
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-            if (i + u * stride < chunks) r[u] = __ldcs(x + i + u * stride);
+    for (int u = 0; u < U; ++u)
+        if (first + u * stride < chunks) r[u] = __ldcs(x + first + u * stride);
+    fill_table<OP>(table, ready, p0, p1);
+    for (int64_t i = first; i < chunks; i += stride * U) {
+        if (i != first) {
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (i + u * stride < chunks) r[u] = __ldcs(x + i + u * stride);
+        }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             if (i + u * stride >= chunks) break;
@@ -67,9 +100,10 @@ __global__ void __launch_bounds__(kLutThreads, 1) unary_lut_kernel(const uint4* 
 // of two bf16 values rounded once, which is what the reference's F32 multiply followed by the
 // bf16 store produces).
 __global__ void __launch_bounds__(kLutThreads, 1) swiglu_lut_kernel(const uint4* __restrict__ proj, uint4* __restrict__ out,
-                                                                   int64_t rows, int64_t hidden_chunks) {
+                                                                   int64_t rows, int64_t hidden_chunks,
+                                                                   const uint4* __restrict__ ready) {
     extern __shared__ __align__(16) uint16_t table[];
-    fill_table<VRB_SILU>(table, 0.f, 0.f);
+    fill_table<VRB_SILU>(table, ready, 0.f, 0.f);
     constexpr int U = 2;
     const int64_t total = rows * hidden_chunks;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kLutThreads;
@@ -103,6 +137,52 @@ __global__ void __launch_bounds__(kLutThreads, 1) swiglu_lut_kernel(const uint4*
     }
 }
 
+// GroupNorm normalise pass + SiLU on bf16 (CudaBackend::group_norm :4919-5008 followed by
+// activation(Silu), native/src/components/autoencoder_kl.cpp:40-41): y = bf16((x - mean) * inv *
+// gamma + beta) with the reference's rounding order, then silu(y) read from the table, since y is
+// a bf16 value.  Tiles of kLutThreads * U chunks lie inside one plane, so the four constants are
+// fetched once per tile.
+__global__ void __launch_bounds__(kLutThreads, 1) gn_apply_silu_lut_kernel(
+    const uint4* __restrict__ x, uint4* __restrict__ out, const void* __restrict__ weight, int w_dt,
+    const void* __restrict__ bias, int b_dt, const float* __restrict__ mean, const float* __restrict__ inverse,
+    int64_t planes, int64_t channels, int channels_per, int groups, int64_t plane_chunks, const uint4* __restrict__ ready) {
+    extern __shared__ __align__(16) uint16_t table[];
+    fill_table<VRB_SILU>(table, ready, 0.f, 0.f);
+    constexpr int U = 4;
+    constexpr int kTile = kLutThreads * U;
+    const int64_t tiles_per_plane = (plane_chunks + kTile - 1) / kTile;
+    const int64_t tiles = planes * tiles_per_plane;
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t plane = t / tiles_per_plane;
+        const int64_t c0 = (t - plane * tiles_per_plane) * kTile + threadIdx.x;
+        const int64_t channel = plane % channels;
+        const int64_t unit = (plane / channels) * groups + channel / channels_per;
+        const float m = __ldg(mean + unit), inv = __ldg(inverse + unit);
+        const float gamma = weight ? round_to(VRB_BF16, load1(weight, w_dt, channel)) : 1.0f;
+        const float beta = bias ? round_to(VRB_BF16, load1(bias, b_dt, channel)) : 0.0f;
+        const uint4* px = x + plane * plane_chunks;
+        uint4* po = out + plane * plane_chunks;
+        uint4 r[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (c0 + u * kLutThreads < plane_chunks) r[u] = __ldcs(px + c0 + u * kLutThreads);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (c0 + u * kLutThreads >= plane_chunks) break;
+            const uint32_t w[4] = {r[u].x, r[u].y, r[u].z, r[u].w};
+            uint32_t o[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float lo = __uint_as_float(w[k] << 16), hi = __uint_as_float(w[k] & 0xffff0000u);
+                const float ylo = __fmaf_rn(__fmul_rn(__fsub_rn(lo, m), inv), gamma, beta);
+                const float yhi = __fmaf_rn(__fmul_rn(__fsub_rn(hi, m), inv), gamma, beta);
+                o[k] = lookup2(table, pack_bf16x2(ylo, yhi));
+            }
+            __stcs(po + c0 + u * kLutThreads, make_uint4(o[0], o[1], o[2], o[3]));
+        }
+    }
+}
+
 // The 128 KB table needs the opt-in shared-memory limit; set once per kernel and device.
 template <typename K>
 int reserve_table(K kernel, bool* done) {
@@ -118,13 +198,61 @@ int reserve_table(K kernel, bool* done) {
     return VRB_OK;
 }
 
+// Prebuilt tables, one per (device, operator, parameter bits); a handful exist in practice
+// (one per activation kind plus the clamp bounds a model uses), so the cache is a short list.
+struct ReadyTable {
+    int device, op;
+    uint32_t p0, p1;
+    uint16_t* table;
+};
+constexpr size_t kMaxReadyTables = 64;
+std::mutex g_tables_mutex;
+std::vector<ReadyTable> g_tables;
+
+// The device copy of the table, built on `stream` at first use (and waited for, so later
+// launches on any stream may read it).  nullptr when it cannot be prepared now: the caller's
+// kernel then fills its own shared table.
+template <int OP>
+const uint4* ready_table(float p0, float p1, cudaStream_t stream) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return nullptr;
+    uint32_t b0, b1;
+    std::memcpy(&b0, &p0, 4);
+    std::memcpy(&b1, &p1, 4);
+    std::lock_guard<std::mutex> lock(g_tables_mutex);
+    for (const ReadyTable& t : g_tables)
+        if (t.device == device && t.op == OP && t.p0 == b0 && t.p1 == b1) return reinterpret_cast<const uint4*>(t.table);
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    if (g_tables.size() >= kMaxReadyTables) return nullptr;
+    uint16_t* table = nullptr;
+    if (cudaMalloc(&table, kTableBytes) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    build_table_kernel<OP><<<kTableEntries / kLutThreads, kLutThreads, 0, stream>>>(table, p0, p1);
+    if (cudaGetLastError() != cudaSuccess || cudaStreamSynchronize(stream) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(table);
+        return nullptr;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    g_tables.push_back({device, OP, b0, b1, table});
+    return reinterpret_cast<const uint4*>(table);
+}
+
 template <int OP>
 int launch_lut(const void* x, void* out, int64_t count, float p0, float p1, cudaStream_t stream) {
     static bool done[64] = {false};   // one flag set per OP instantiation
     if (int rc = reserve_table(unary_lut_kernel<OP>, done)) return rc;
     const int64_t chunks = count / 8;
-    unary_lut_kernel<OP><<<sm_count(), kLutThreads, kTableBytes, stream>>>(
-        static_cast<const uint4*>(x), static_cast<uint4*>(out), chunks, p0, p1);
+    const int64_t per_cta = (chunks + kLutThreads - 1) / kLutThreads;
+    const int grid = static_cast<int>(per_cta < sm_count() ? per_cta : sm_count());
+    unary_lut_kernel<OP><<<grid, kLutThreads, kTableBytes, stream>>>(
+        static_cast<const uint4*>(x), static_cast<uint4*>(out), chunks, ready_table<OP>(p0, p1, stream), p0, p1);
     return after_launch("unary (table)");
 }
 
@@ -151,8 +279,22 @@ int launch_swiglu_lut(const void* proj, void* out, int64_t rows, int64_t hidden,
     static bool done[64] = {false};
     if (int rc = reserve_table(swiglu_lut_kernel, done)) return rc;
     swiglu_lut_kernel<<<sm_count(), kLutThreads, kTableBytes, stream>>>(
-        static_cast<const uint4*>(proj), static_cast<uint4*>(out), rows, hidden / 8);
+        static_cast<const uint4*>(proj), static_cast<uint4*>(out), rows, hidden / 8, ready_table<VRB_SILU>(0.f, 0.f, stream));
     return after_launch("swiglu (table)");
+}
+
+int launch_group_norm_apply_silu_lut(const void* x, const void* weight, int w_dt, const void* bias, int b_dt, void* out,
+                                     int64_t planes, int64_t channels, int channels_per, int groups, int64_t spatial,
+                                     const float* mean, const float* inverse, cudaStream_t stream) {
+    static bool done[64] = {false};
+    if (int rc = reserve_table(gn_apply_silu_lut_kernel, done)) return rc;
+    const int64_t plane_chunks = spatial / 8;
+    const int64_t tiles = planes * ((plane_chunks + kLutThreads * 4 - 1) / (kLutThreads * 4));
+    const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+    gn_apply_silu_lut_kernel<<<grid, kLutThreads, kTableBytes, stream>>>(
+        static_cast<const uint4*>(x), static_cast<uint4*>(out), weight, w_dt, bias, b_dt, mean, inverse, planes, channels,
+        channels_per, groups, plane_chunks, ready_table<VRB_SILU>(0.f, 0.f, stream));
+    return after_launch("group_norm apply (table)");
 }
 
 }  // namespace vrb

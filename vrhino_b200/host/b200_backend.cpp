@@ -1,0 +1,426 @@
+// B200Backend: the reference's Backend interface over the C ABI of libvrb.so.
+// The host wrappers below keep the conventions of the reference's own wrappers
+// (native/src/backend/cuda/cuda_backend.cu): the operand-dtype rule (a device F32/BF16 tensor
+// keeps its dtype, anything else takes the execution dtype), upload-on-demand of host operands,
+// `cast` / `copy_to_device` to the same dtype returning the SAME handle (:3200), results in
+// freshly allocated device tensors, vrhino::Error on every failure, and a session that turns
+// terminal once an operator has thrown (native/include/vrhino/memory.h:225-236).
+#include "b200_backend.h"
+
+#include <algorithm>
+#include <limits>
+
+#include "vrb.h"
+#include "vrhino/architecture.h"
+#include "vrhino/error.h"
+#include "vrhino/tensor_util.h"
+
+namespace vrhino_b200 {
+
+using vrhino::DeviceId;
+using vrhino::DType;
+using vrhino::Error;
+using vrhino::require;
+using vrhino::Tensor;
+
+namespace {
+
+constexpr vrb_stream kLegacyStream = nullptr;
+
+bool is_float(DType d) { return d == DType::F32 || d == DType::BF16; }
+bool device_float(const Tensor& t) { return t.device() == DeviceId::accelerator() && is_float(t.dtype()); }
+int code(DType d) { return static_cast<int>(d); }   // VRB_F32 / VRB_BF16 / VRB_U8 equal the DType values
+
+void check(int status) {
+    if (status == VRB_OK) return;
+    const char* text = vrb_last_error();
+    throw Error(text && *text ? text : "vrb status " + std::to_string(status));
+}
+
+// Right-aligned broadcast of two shapes (cuda_backend.cu:508-523).
+std::vector<int64_t> broadcast_shape(const std::vector<int64_t>& a, const std::vector<int64_t>& b) {
+    const size_t rank = std::max(a.size(), b.size());
+    std::vector<int64_t> out(rank, 1);
+    for (size_t i = 0; i < rank; ++i) {
+        const int64_t x = i < rank - a.size() ? 1 : a[i - (rank - a.size())];
+        const int64_t y = i < rank - b.size() ? 1 : b[i - (rank - b.size())];
+        require(x == y || x == 1 || y == 1, "Incompatible broadcast shapes");
+        out[i] = std::max(x, y);
+    }
+    return out;
+}
+
+// rows_per_vector / vector count of a modulation-like operand against x = [.., width]:
+// one vector for all rows, one per batch entry, or one per row.
+void vector_layout(const Tensor& x, const Tensor& vec, int64_t& rows_per_vector, int64_t& vectors) {
+    const int64_t width = x.dim(-1), rows = x.numel() / width;
+    require(vec.numel() % width == 0, "Incompatible broadcast shapes");
+    const int64_t n = vec.numel() / width;
+    if (n == 1) { rows_per_vector = rows; vectors = 1; return; }
+    if (n == rows) { rows_per_vector = 1; vectors = rows; return; }
+    require(x.ndim() >= 2 && n == x.dim(0) && rows % n == 0, "Incompatible broadcast shapes");
+    rows_per_vector = rows / n;
+    vectors = n;
+}
+
+}  // namespace
+
+B200Backend::B200Backend(std::unique_ptr<vrhino::Backend> device_runtime) : rt_(std::move(device_runtime)) {
+    require(rt_ != nullptr, "B200Backend needs a device runtime backend");
+    require(vrb_abi_version() == VRB_ABI_VERSION, "libvrb.so ABI version mismatch");
+}
+B200Backend::~B200Backend() = default;
+
+// The reference wraps add/mul/div/maximum, cast, copy_to_device, group_norm, clamp, exp and sqrt in
+// a CudaFailureGuard (cuda_backend.cu:2601-2615, :3064): an exception escaping them leaves the
+// session terminal.  layer_norm, rms_norm, activation and rope_nd carry no guard, so a rejected
+// argument there leaves the session usable.  Both kinds refuse to start on a terminal session,
+// this object's or the device runtime's.
+template <typename F>
+Tensor B200Backend::guarded(F&& body) {
+    begin_operator();
+    try {
+        return body();
+    } catch (...) {
+        retire_resource_session();
+        rt_->retire_resource_session();
+        throw;
+    }
+}
+template <typename F>
+Tensor B200Backend::unguarded(F&& body) {
+    begin_operator();
+    return body();
+}
+void B200Backend::begin_operator() const {
+    require_active_session();
+    rt_->require_active_session();
+}
+
+DType B200Backend::operand_dtype(const Tensor& t) const { return device_float(t) ? t.dtype() : execution_dtype(); }
+
+// Optional affine parameter on the device in a float dtype the kernels convert themselves.
+Tensor B200Backend::parameter(const Tensor& t) {
+    if (device_float(t)) return t;
+    return copy_to_device(t, is_float(t.dtype()) ? t.dtype() : execution_dtype());
+}
+
+Tensor B200Backend::copy_to_device(const Tensor& input, DType dtype) {
+    begin_operator();
+    require(input.defined(), "Cannot upload undefined tensor");
+    if (input.device() == DeviceId::accelerator() && input.dtype() == dtype) return input;
+    if (input.is_quantized()) return dequantize(input, dtype);
+    if (input.device() == DeviceId::accelerator() && is_float(dtype) &&
+        (is_float(input.dtype()) || input.dtype() == DType::U8))
+        return cast(input, dtype);
+    return rt_->copy_to_device(input, dtype);   // host uploads (with the runtime's small-value and weight caches)
+}
+
+// Quantised weights (cuda_backend.cu:3214-3296): packed bytes and F32 scales go up as they are,
+// then one kernel decodes, scales and rounds.  The preconditions and their texts are the reference's.
+Tensor B200Backend::dequantize(const Tensor& input, DType dtype) {
+    return guarded([&] {
+        require(input.device() == DeviceId::host() && is_float(dtype),
+                "Quantized tensors require CPU storage and float compute output");
+        const vrhino::QuantizationInfo& q = input.quantization();
+        require(q.axis == 1 && q.group_size > 0 && q.block_size == 0 && q.symmetric &&
+                    (q.granularity == "per_group" || q.granularity == "per_channel") && q.zero_point_mode == "none" &&
+                    q.dequantization == vrhino::DequantizationSemantics::ScaleThenCast,
+                "Unsupported quantized tensor layout/policy");
+        int kind = -1;
+        if (q.type == vrhino::QuantType::FP8E4M3FN && q.packing_layout == "byte_e4m3fn") kind = VRB_Q_FP8_E4M3FN;
+        else if (q.type == vrhino::QuantType::INT8Symmetric && q.packing_layout == "byte_twos_complement") kind = VRB_Q_INT8;
+        else if (q.type == vrhino::QuantType::INT4Symmetric && q.packing_layout == "nibble_low_first_twos_complement") kind = VRB_Q_INT4;
+        require(kind >= 0, "Unsupported quantized tensor packing");
+        Tensor host_bytes = Tensor::borrowed(input.data(), input.bytes(), {static_cast<int64_t>(input.bytes())}, DType::U8);
+        Tensor packed = rt_->allocate_device(host_bytes.shape(), DType::U8);
+        Tensor scales = rt_->allocate_device(q.scales.shape(), DType::F32);
+        rt_->copy(host_bytes, packed);
+        rt_->copy(q.scales, scales);
+        Tensor output = rt_->allocate_device(input.shape(), dtype);
+        const int64_t rows = input.dim(0), inner = input.numel() / rows;
+        check(vrb_dequantize(kind, packed.data(), scales.data_as<float>(), output.data(), code(dtype), rows, inner,
+                             q.group_size, kLegacyStream));
+        return output;
+    });
+}
+
+Tensor B200Backend::cast(const Tensor& x, DType dtype) {
+    begin_operator();
+    if (x.device() != DeviceId::accelerator()) return copy_to_device(x, dtype);
+    if (x.dtype() == dtype) return x;
+    if (!is_float(dtype) || !(is_float(x.dtype()) || x.dtype() == DType::U8)) return rt_->cast(x, dtype);
+    return guarded([&] {
+        Tensor out = rt_->allocate_device(x.shape(), dtype);
+        if (x.numel() > 0) check(vrb_cast(x.data(), code(x.dtype()), out.data(), code(dtype), x.numel(), kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::binary(int kind, const Tensor& a_raw, const Tensor& b_raw) {
+    return guarded([&] {
+        const DType dtype = device_float(a_raw) ? a_raw.dtype() : device_float(b_raw) ? b_raw.dtype() : execution_dtype();
+        Tensor a = copy_to_device(a_raw, dtype), b = copy_to_device(b_raw, dtype);
+        Tensor out = rt_->allocate_device(broadcast_shape(a.shape(), b.shape()), dtype);
+        const int64_t one = 1;
+        check(vrb_binary(kind, a.data(), a.ndim() ? a.shape().data() : &one, static_cast<int>(a.ndim()),
+                         b.data(), b.ndim() ? b.shape().data() : &one, static_cast<int>(b.ndim()),
+                         out.data(), code(dtype), kLegacyStream));
+        return out;
+    });
+}
+Tensor B200Backend::add(const Tensor& a, const Tensor& b) { return binary(VRB_ADD, a, b); }
+Tensor B200Backend::mul(const Tensor& a, const Tensor& b) { return binary(VRB_MUL, a, b); }
+Tensor B200Backend::div(const Tensor& a, const Tensor& b) { return binary(VRB_DIV, a, b); }
+Tensor B200Backend::maximum(const Tensor& a, const Tensor& b) { return binary(VRB_MAX, a, b); }
+
+Tensor B200Backend::layer_norm(const Tensor& raw, const Tensor* weight_raw, const Tensor* bias_raw, float eps) {
+    return unguarded([&] {
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype), weight, bias;
+        const int64_t width = x.dim(-1);
+        if (weight_raw) { weight = parameter(*weight_raw); require(weight.numel() == width, "layer norm weight mismatch"); }
+        if (bias_raw) { bias = parameter(*bias_raw); require(bias.numel() == width, "layer norm bias mismatch"); }
+        Tensor out = rt_->allocate_device(x.shape(), dtype);
+        check(vrb_layer_norm(x.data(), code(dtype), weight_raw ? weight.data() : nullptr, weight_raw ? code(weight.dtype()) : 0,
+                             bias_raw ? bias.data() : nullptr, bias_raw ? code(bias.dtype()) : 0, out.data(),
+                             x.numel() / width, width, eps, kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::rms_norm(const Tensor& raw, const Tensor* weight_raw, float eps, int64_t axis, DType requested) {
+    return unguarded([&] {
+        if (axis < 0) axis += raw.ndim();
+        require(axis >= 0 && axis < raw.ndim(), "rms_norm axis invalid");
+        const DType dtype = operand_dtype(raw);
+        const DType out_dtype = requested == DType::F16 ? dtype : requested;   // F16 = "same as the input" (:4105)
+        require(out_dtype == dtype || (dtype == DType::BF16 && out_dtype == DType::F32), "rms_norm output dtype unsupported");
+        Tensor x = copy_to_device(raw, dtype), weight;
+        if (weight_raw) { weight = parameter(*weight_raw); require(weight.numel() == x.dim(axis), "rms norm weight mismatch"); }
+        const void* w = weight_raw ? weight.data() : nullptr;
+        const int wcode = weight_raw ? code(weight.dtype()) : 0;
+        Tensor out = rt_->allocate_device(x.shape(), out_dtype);
+        if (axis == x.ndim() - 1) {
+            if (dtype == DType::BF16 && out_dtype == DType::F32)
+                require(weight_raw != nullptr, "BF16-to-FP32 rms_norm requires affine weight");
+            const int64_t width = x.dim(-1);
+            check(vrb_rms_norm(x.data(), code(dtype), w, wcode, out.data(), code(out_dtype), x.numel() / width, width, eps,
+                               kLegacyStream));
+        } else {
+            require(out_dtype == dtype, "mixed-dtype rms_norm currently requires final axis");
+            const int64_t width = x.dim(axis);
+            int64_t inner = 1;
+            for (int64_t i = axis + 1; i < x.ndim(); ++i) inner *= x.dim(i);
+            check(vrb_rms_norm_axis(x.data(), code(dtype), w, wcode, out.data(), x.numel() / (width * inner), width, inner,
+                                    eps, 0, kLegacyStream));
+        }
+        return out;
+    });
+}
+
+// which: 0 activation(kind), 1 clamp(p0, p1), 2 exp, 3 sqrt
+Tensor B200Backend::unary(int which, const Tensor& raw, int kind, float p0, float p1) {
+    auto body = [&] {
+        if (which == 1) require(p0 <= p1, "Invalid clamp bounds");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype), out = rt_->allocate_device(x.shape(), dtype);
+        const int64_t n = x.numel();
+        switch (which) {
+            case 0: check(vrb_activation(kind, x.data(), out.data(), code(dtype), n, kLegacyStream)); break;
+            case 1: check(vrb_clamp(x.data(), out.data(), code(dtype), n, p0, p1, kLegacyStream)); break;
+            case 2: check(vrb_exp(x.data(), out.data(), code(dtype), n, kLegacyStream)); break;
+            default: check(vrb_sqrt(x.data(), out.data(), code(dtype), n, kLegacyStream)); break;
+        }
+        return out;
+    };
+    return which == 0 ? unguarded(body) : guarded(body);
+}
+Tensor B200Backend::activation(const Tensor& x, vrhino::Activation kind) { return unary(0, x, static_cast<int>(kind), 0.f, 0.f); }
+Tensor B200Backend::clamp(const Tensor& x, float minimum, float maximum) { return unary(1, x, 0, minimum, maximum); }
+Tensor B200Backend::exp(const Tensor& x) { return unary(2, x, 0, 0.f, 0.f); }
+Tensor B200Backend::sqrt(const Tensor& x) { return unary(3, x, 0, 0.f, 0.f); }
+
+Tensor B200Backend::rope_nd(const Tensor& raw, const Tensor& cos_raw, const Tensor& sin_raw) {
+    return unguarded([&] {
+        require(raw.dim(-1) % 2 == 0, "RoPE width must be even");
+        const DType dtype = operand_dtype(raw);
+        const DType f_dtype = device_float(cos_raw) ? cos_raw.dtype() : dtype;
+        Tensor x = copy_to_device(raw, dtype), c = copy_to_device(cos_raw, f_dtype), s = copy_to_device(sin_raw, f_dtype);
+        require(c.shape() == s.shape(), "RoPE frequency mismatch");
+        broadcast_shape(x.shape(), c.shape());
+        Tensor out = rt_->allocate_device(x.shape(), dtype);
+        check(vrb_rope(x.data(), code(dtype), x.shape().data(), static_cast<int>(x.ndim()), c.data(), s.data(), code(f_dtype),
+                       c.shape().data(), static_cast<int>(c.ndim()), out.data(), kLegacyStream));
+        return out;
+    });
+}
+
+void* B200Backend::workspace(size_t bytes) {
+    if (!workspace_.defined() || workspace_.bytes() < bytes)
+        workspace_ = rt_->allocate_device({static_cast<int64_t>(bytes)}, DType::U8);
+    return workspace_.data();
+}
+
+Tensor B200Backend::group_norm_impl(const Tensor& raw, int groups, const Tensor* weight_raw, const Tensor* bias_raw,
+                                    float eps, bool silu) {
+    return guarded([&] {
+        require(raw.ndim() >= 3 && groups > 0 && raw.dim(1) % groups == 0, "group norm shape/groups mismatch");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype), weight, bias;
+        if (weight_raw) weight = parameter(*weight_raw);
+        if (bias_raw) bias = parameter(*bias_raw);
+        const int64_t batch = x.dim(0), channels = x.dim(1), spatial = x.numel() / (batch * channels);
+        require(batch * groups <= std::numeric_limits<int>::max(), "group norm launch extent exceeds CUDA grid capacity");
+        const size_t need = vrb_group_norm_workspace_bytes(batch, groups);
+        Tensor out = rt_->allocate_device(x.shape(), dtype);
+        check(vrb_group_norm(x.data(), code(dtype), weight_raw ? weight.data() : nullptr, weight_raw ? code(weight.dtype()) : 0,
+                             bias_raw ? bias.data() : nullptr, bias_raw ? code(bias.dtype()) : 0, out.data(), batch, channels,
+                             spatial, groups, eps, silu ? 1 : 0, workspace(need), need, kLegacyStream));
+        return out;
+    });
+}
+Tensor B200Backend::group_norm(const Tensor& x, int groups, const Tensor* w, const Tensor* b, float eps) {
+    return group_norm_impl(x, groups, w, b, eps, false);
+}
+Tensor B200Backend::group_norm_silu(const Tensor& x, int groups, const Tensor* w, const Tensor* b, float eps) {
+    return group_norm_impl(x, groups, w, b, eps, true);
+}
+
+// ---- fused forms --------------------------------------------------------------------------------
+
+Tensor B200Backend::layer_norm_modulate(const Tensor& raw, const Tensor* weight_raw, const Tensor* bias_raw, float eps,
+                                        const Tensor& shift_raw, const Tensor& scale_raw, DType output) {
+    return guarded([&] {
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype), weight, bias;
+        const int64_t width = x.dim(-1), rows = x.numel() / width;
+        if (weight_raw) { weight = parameter(*weight_raw); require(weight.numel() == width, "layer norm weight mismatch"); }
+        if (bias_raw) { bias = parameter(*bias_raw); require(bias.numel() == width, "layer norm bias mismatch"); }
+        Tensor scale = parameter(scale_raw), shift = copy_to_device(shift_raw, scale.dtype());
+        require(shift.numel() == scale.numel(), "modulate: shift and scale must share dtype and shape");
+        int64_t rows_per_vector = 0, vectors = 0;
+        vector_layout(x, scale, rows_per_vector, vectors);
+        Tensor out = rt_->allocate_device(x.shape(), output);
+        check(vrb_layer_norm_modulate(x.data(), code(dtype), weight_raw ? weight.data() : nullptr,
+                                      weight_raw ? code(weight.dtype()) : 0, bias_raw ? bias.data() : nullptr,
+                                      bias_raw ? code(bias.dtype()) : 0, scale.data(), shift.data(), code(scale.dtype()),
+                                      rows_per_vector, vectors, out.data(), code(output), rows, width, eps, kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::rms_norm_rope(const Tensor& raw, const Tensor* weight_raw, float eps, const Tensor* cos_raw,
+                                  const Tensor* sin_raw, int heads, bool per_head_norm, DType output) {
+    return guarded([&] {
+        require(raw.ndim() == 3 && heads > 0 && raw.dim(2) % heads == 0, "split_heads shape mismatch");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype), weight, c, s;
+        const int64_t width = x.dim(2), rows = x.numel() / width, head_width = width / heads;
+        const int64_t norm_width = per_head_norm ? head_width : width;
+        if (weight_raw) { weight = parameter(*weight_raw); require(weight.numel() == norm_width, "rms norm weight mismatch"); }
+        int64_t f_rows = 0, f_width = 8;
+        if (cos_raw) {
+            require(sin_raw != nullptr, "RoPE frequency mismatch");
+            c = copy_to_device(*cos_raw, DType::F32);
+            s = copy_to_device(*sin_raw, DType::F32);
+            require(c.shape() == s.shape(), "RoPE frequency mismatch");
+            require(c.ndim() >= 2 && c.dim(-1) == head_width, "Incompatible broadcast shapes");
+            f_width = c.dim(-1) * c.dim(-2);
+            require(f_width == head_width || f_width == width, "Incompatible broadcast shapes");
+            f_rows = c.numel() / f_width;
+            require(f_rows == rows || f_rows == rows / x.dim(0), "Incompatible broadcast shapes");
+        }
+        Tensor out = rt_->allocate_device(x.shape(), output);
+        check(vrb_rms_norm_rope(x.data(), code(dtype), weight_raw ? weight.data() : nullptr,
+                                weight_raw ? code(weight.dtype()) : 0, cos_raw ? c.data() : nullptr,
+                                cos_raw ? s.data() : nullptr, f_rows, f_width, 1, out.data(), code(output), rows, width,
+                                norm_width, eps, kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::gated_residual(const Tensor& residual_raw, const Tensor& branch_raw, const Tensor* gate_raw, DType state) {
+    return guarded([&] {
+        Tensor residual = copy_to_device(residual_raw, operand_dtype(residual_raw));
+        Tensor branch = copy_to_device(branch_raw, operand_dtype(branch_raw)), gate;
+        require(residual.shape() == branch.shape(), "Incompatible broadcast shapes");
+        const int64_t width = residual.dim(-1), rows = residual.numel() / width;
+        int64_t rows_per_vector = 1, vectors = 1;
+        if (gate_raw) { gate = parameter(*gate_raw); vector_layout(residual, gate, rows_per_vector, vectors); }
+        Tensor out = rt_->allocate_device(residual.shape(), state);
+        check(vrb_gated_residual(residual.data(), code(residual.dtype()), branch.data(), code(branch.dtype()),
+                                 gate_raw ? gate.data() : nullptr, gate_raw ? code(gate.dtype()) : 0, rows_per_vector,
+                                 vectors, out.data(), code(state), rows, width, kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::swiglu(const Tensor& raw) {
+    return guarded([&] {
+        const DType dtype = operand_dtype(raw);
+        Tensor projected = copy_to_device(raw, dtype);
+        require(projected.dim(-1) % 2 == 0, "split sections mismatch");
+        const int64_t hidden = projected.dim(-1) / 2, rows = projected.numel() / (2 * hidden);
+        std::vector<int64_t> shape = projected.shape();
+        shape.back() = hidden;
+        Tensor out = rt_->allocate_device(shape, dtype);
+        check(vrb_swiglu(projected.data(), out.data(), code(dtype), rows, hidden, kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::cfg_euler(const Tensor& sample_raw, const Tensor& u_raw, const Tensor& c_raw, float guidance,
+                              float delta, bool subtract_prediction, bool guidance_role, bool solver_role) {
+    return guarded([&] {
+        const DType dtype = operand_dtype(sample_raw);
+        Tensor sample = copy_to_device(sample_raw, dtype), u = copy_to_device(u_raw, dtype), c = copy_to_device(c_raw, dtype);
+        require(sample.shape() == u.shape() && u.shape() == c.shape(), "Incompatible broadcast shapes");
+        Tensor out = rt_->allocate_device(sample.shape(), dtype);
+        check(vrb_cfg_euler(sample.data(), u.data(), c.data(), nullptr, out.data(), code(dtype), sample.numel(), guidance,
+                            delta, subtract_prediction ? 1 : 0, guidance_role ? 1 : 0, solver_role ? 1 : 0, kLegacyStream));
+        return out;
+    });
+}
+
+// ---- call-site view -----------------------------------------------------------------------------
+
+Tensor layer_norm_modulate(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy, const Tensor& x,
+                           const Tensor* weight, const Tensor* bias, float eps, const Tensor& shift, const Tensor& scale,
+                           DType output) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend))
+        return b200->layer_norm_modulate(x, weight, bias, eps, shift, scale, output);
+    return backend.cast(vrhino::modulate(backend, policy, backend.layer_norm(x, weight, bias, eps), shift, scale), output);
+}
+
+Tensor rms_norm_rope(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy, const Tensor& x, const Tensor* weight,
+                     float eps, const Tensor* cosine, const Tensor* sine, int heads, bool per_head_norm, DType output) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend))
+        return b200->rms_norm_rope(x, weight, eps, cosine, sine, heads, per_head_norm, output);
+    Tensor t = per_head_norm ? vrhino::attention_norm(backend, policy, vrhino::split_heads(backend, x, heads), weight, eps)
+                             : vrhino::split_heads(backend, vrhino::attention_norm(backend, policy, x, weight, eps), heads);
+    if (cosine) t = vrhino::operation_rope(backend, policy, t, *cosine, *sine);
+    return backend.cast(vrhino::merge_heads(backend, t), output);
+}
+
+Tensor fused_gated_residual(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy, const Tensor& residual,
+                            const Tensor& branch, const Tensor* gate) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend))
+        return b200->gated_residual(residual, branch, gate, policy.persistent_state_dtype(vrhino::PrecisionSemantic::ResidualState));
+    return gate ? vrhino::gated_residual(backend, policy, residual, branch, *gate)
+                : vrhino::residual_add(backend, policy, residual, branch);
+}
+
+Tensor swiglu(vrhino::Backend& backend, const Tensor& projected) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend)) return b200->swiglu(projected);
+    const int64_t hidden = projected.dim(-1) / 2;
+    std::vector<Tensor> parts = backend.split(projected, {hidden, hidden}, -1);
+    return backend.mul(parts[0], backend.activation(parts[1], vrhino::Activation::Silu));
+}
+
+Tensor group_norm_silu(vrhino::Backend& backend, const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend)) return b200->group_norm_silu(x, groups, weight, bias, eps);
+    return backend.activation(backend.group_norm(x, groups, weight, bias, eps), vrhino::Activation::Silu);
+}
+
+}  // namespace vrhino_b200

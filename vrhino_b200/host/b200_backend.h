@@ -1,0 +1,188 @@
+// C++ host layer of the B200 operator path: a vrhino::Backend whose elementwise, reduction and
+// broadcast operators run on the sm_100a kernels of libvrb.so (include/vrb.h), plus the fused
+// forms of the helper seams.  It compiles against the reference's public headers
+// (native/include/vrhino) and is meant to be built inside the reference's tree, next to
+// native/src/backend/cuda/cuda_backend.cu.
+//
+// Everything that is not on this path -- allocation and the temporary pool, host<->device
+// transfers and fences, GEMM, attention, convolutions, the memory runtime, profiling -- is
+// forwarded to the device runtime backend given at construction (normally the reference's own
+// CudaBackend), so call sites that hold a `Backend&` (native/include/vrhino/architecture.h:33-42)
+// need no change: construct B200Backend(std::make_unique<CudaBackend>()) where they used to
+// construct CudaBackend.
+//
+// Replaced virtuals (same signatures, defaults, dtype rules and error texts as
+// native/src/backend/cuda/cuda_backend.cu): add, mul, div, maximum (:3871-3902), cast (:3978),
+// layer_norm (:4057), rms_norm (:4091), activation (:4179), rope_nd (:4198), group_norm (:4919),
+// clamp (:5128), exp, sqrt (:5134-5173) and the quantised branch of copy_to_device (:3214-3296).
+// Kernels run on the legacy default stream, which the runtime's pool reuse relies on
+// (cuda_backend.cu:55-59).
+#pragma once
+
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "vrhino/backend.h"
+#include "vrhino/precision.h"
+
+namespace vrhino_b200 {
+
+class B200Backend final : public vrhino::Backend {
+public:
+    using Tensor = vrhino::Tensor;
+    using DType = vrhino::DType;
+
+    explicit B200Backend(std::unique_ptr<vrhino::Backend> device_runtime);
+    ~B200Backend() override;
+    vrhino::Backend& device_runtime() { return *rt_; }
+
+    // ---- operators on this path -------------------------------------------------------------
+    Tensor add(const Tensor& a, const Tensor& b) override;
+    Tensor mul(const Tensor& a, const Tensor& b) override;
+    Tensor div(const Tensor& a, const Tensor& b) override;
+    Tensor maximum(const Tensor& a, const Tensor& b) override;
+    Tensor cast(const Tensor& x, DType dtype) override;
+    Tensor layer_norm(const Tensor& x, const Tensor* weight, const Tensor* bias, float eps) override;
+    Tensor rms_norm(const Tensor& x, const Tensor* weight, float eps, int64_t axis = -1,
+                    DType output = DType::F16) override;
+    Tensor activation(const Tensor& x, vrhino::Activation kind) override;
+    Tensor rope_nd(const Tensor& x, const Tensor& cosine, const Tensor& sine) override;
+    Tensor group_norm(const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps) override;
+    Tensor clamp(const Tensor& x, float minimum, float maximum) override;
+    Tensor exp(const Tensor& x) override;
+    Tensor sqrt(const Tensor& x) override;
+    Tensor copy_to_device(const Tensor& input, DType dtype) override;
+
+    // ---- fused forms (one kernel each); see the free functions below for the call-site view --
+    Tensor layer_norm_modulate(const Tensor& x, const Tensor* weight, const Tensor* bias, float eps,
+                               const Tensor& shift, const Tensor& scale, DType output);
+    Tensor rms_norm_rope(const Tensor& x, const Tensor* weight, float eps, const Tensor* cosine,
+                         const Tensor* sine, int heads, bool per_head_norm, DType output);
+    Tensor gated_residual(const Tensor& residual, const Tensor& branch, const Tensor* gate, DType state);
+    Tensor swiglu(const Tensor& projected);
+    Tensor group_norm_silu(const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps);
+    Tensor cfg_euler(const Tensor& sample, const Tensor& unconditional, const Tensor& conditional,
+                     float guidance, float delta, bool subtract_prediction, bool guidance_role, bool solver_role);
+
+    // ---- forwarded to the device runtime -----------------------------------------------------
+    std::string name() const override { return "b200+" + rt_->name(); }
+    int device_count() const override { return rt_->device_count(); }
+    vrhino::DeviceCapability device_capability(int device = 0) const override { return rt_->device_capability(device); }
+    vrhino::BackendMemoryCapabilities memory_capabilities() const override { return rt_->memory_capabilities(); }
+    bool supports(DType dtype) const override { return rt_->supports(dtype); }
+    void set_execution_dtype(DType dtype) override { rt_->set_execution_dtype(dtype); }
+    DType execution_dtype() const override { return rt_->execution_dtype(); }
+    Tensor allocate_host(const std::vector<int64_t>& s, DType d) override { return rt_->allocate_host(s, d); }
+    Tensor allocate_device(const std::vector<int64_t>& s, DType d) override { return rt_->allocate_device(s, d); }
+    vrhino::TransferFence copy(const Tensor& s, Tensor& d, CopyMode m = CopyMode::Synchronous) override { return rt_->copy(s, d, m); }
+    vrhino::TransferFence create_fence(int device = 0) override { return rt_->create_fence(device); }
+    void record_fence(vrhino::TransferFence f) override { rt_->record_fence(f); }
+    void wait_fence(vrhino::TransferFence f) override { rt_->wait_fence(f); }
+    bool query_fence(vrhino::TransferFence f) override { return rt_->query_fence(f); }
+    void destroy_fence(vrhino::TransferFence f) override { rt_->destroy_fence(f); }
+    Tensor copy_to_host(const Tensor& input) override { return rt_->copy_to_host(input); }
+    void synchronize() override { rt_->synchronize(); }
+    void release_cached_device_memory() override { require_active_session(); rt_->release_cached_device_memory(); }
+    size_t peak_device_bytes() const override { return rt_->peak_device_bytes(); }
+    size_t weight_upload_bytes() const override { return rt_->weight_upload_bytes(); }
+    double weight_upload_seconds() const override { return rt_->weight_upload_seconds(); }
+    void enable_profiling(bool e) override { rt_->enable_profiling(e); }
+    bool profiling_enabled() const override { return rt_->profiling_enabled(); }
+    std::map<std::string, vrhino::ProfileStat> profile_stats() override { return rt_->profile_stats(); }
+    void profile_region_begin(const std::string& n) override { rt_->profile_region_begin(n); }
+    void profile_region_end() override { rt_->profile_region_end(); }
+    uint64_t weight_cache_hits() const override { return rt_->weight_cache_hits(); }
+    uint64_t weight_cache_misses() const override { return rt_->weight_cache_misses(); }
+    size_t weight_cache_resident_bytes() const override { return rt_->weight_cache_resident_bytes(); }
+    size_t weight_cache_capacity_bytes() const override { return rt_->weight_cache_capacity_bytes(); }
+    void enable_weight_cache(bool e) override { rt_->enable_weight_cache(e); }
+    void enable_true_quant_compute(bool e) override { rt_->enable_true_quant_compute(e); }
+    bool true_quant_compute_enabled() const override { return rt_->true_quant_compute_enabled(); }
+    vrhino::QuantComputeStats quant_compute_stats() const override { return rt_->quant_compute_stats(); }
+    void reset_quant_compute_stats() override { rt_->reset_quant_compute_stats(); }
+    void configure_memory_runtime(const vrhino::MemoryBudget& b, const vrhino::MemoryRuntimeOptions& o) override { rt_->configure_memory_runtime(b, o); }
+    bool memory_runtime_enabled() const override { return rt_->memory_runtime_enabled(); }
+    void set_vrm_mapped_bytes(size_t b) override { rt_->set_vrm_mapped_bytes(b); }
+    void begin_memory_trace() override { rt_->begin_memory_trace(); }
+    std::vector<vrhino::MemoryAccess> end_memory_trace() override { return rt_->end_memory_trace(); }
+    void set_memory_trace(std::vector<vrhino::MemoryAccess> t) override { rt_->set_memory_trace(std::move(t)); }
+    vrhino::MemoryRuntimeStats memory_runtime_stats() const override { return rt_->memory_runtime_stats(); }
+
+    Tensor linear(const Tensor& x, const Tensor& w, const Tensor* b = nullptr, DType c = DType::F16, DType o = DType::F16) override { return rt_->linear(x, w, b, c, o); }
+    Tensor batched_matmul(const Tensor& a, const Tensor& b) override { return rt_->batched_matmul(a, b); }
+    Tensor reshape(const Tensor& x, const std::vector<int64_t>& s) override { return rt_->reshape(x, s); }
+    Tensor permute(const Tensor& x, const std::vector<int64_t>& d) override { return rt_->permute(x, d); }
+    Tensor concat(const std::vector<Tensor>& t, int64_t d) override { return rt_->concat(t, d); }
+    std::vector<Tensor> split(const Tensor& x, const std::vector<int64_t>& s, int64_t d) override { return rt_->split(x, s, d); }
+    Tensor slice(const Tensor& x, int64_t d, int64_t a, int64_t b) override { return rt_->slice(x, d, a, b); }
+    Tensor indexed_gather(const Tensor& t, const Tensor& i) override { return rt_->indexed_gather(t, i); }
+    Tensor sinusoidal_embedding(const Tensor& p, int64_t w, bool f, double d, bool r) override { return rt_->sinusoidal_embedding(p, w, f, d, r); }
+    Tensor attention(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor* mask = nullptr, bool causal = false,
+                     float scale = 0.0f, const Tensor* bias = nullptr, vrhino::AttentionObservation* obs = nullptr) override {
+        return rt_->attention(q, k, v, mask, causal, scale, bias, obs);
+    }
+    Tensor conv3d(const Tensor& x, const Tensor& w, const Tensor* b, const std::vector<int>& s, const std::vector<int>& p,
+                  const std::vector<int>& d = {1, 1, 1}, int g = 1) override { return rt_->conv3d(x, w, b, s, p, d, g); }
+    Tensor pad(const Tensor& x, const std::vector<int64_t>& p, float v = 0.0f, vrhino::PadMode m = vrhino::PadMode::Constant) override { return rt_->pad(x, p, v, m); }
+    Tensor reduce_sum(const Tensor& x, int64_t d, bool k = false) override { return rt_->reduce_sum(x, d, k); }
+    Tensor softmax(const Tensor& x, int64_t a) override { return rt_->softmax(x, a); }
+    Tensor conv2d(const Tensor& x, const Tensor& w, const Tensor* b, const std::vector<int>& s, const std::vector<int>& p,
+                  const std::vector<int>& d = {1, 1}, int g = 1) override { return rt_->conv2d(x, w, b, s, p, d, g); }
+    Tensor conv_transpose2d(const Tensor& x, const Tensor& w, const Tensor* b, const std::vector<int>& s, const std::vector<int>& p,
+                            const std::vector<int>& op = {0, 0}, const std::vector<int>& d = {1, 1}, int g = 1) override {
+        return rt_->conv_transpose2d(x, w, b, s, p, op, d, g);
+    }
+    Tensor max_pool2d(const Tensor& x, const std::vector<int>& k, const std::vector<int>& s, const std::vector<int>& p = {0, 0}) override { return rt_->max_pool2d(x, k, s, p); }
+    Tensor interpolate_nearest(const Tensor& x, const std::vector<double>& f) override { return rt_->interpolate_nearest(x, f); }
+    Tensor interpolate_bilinear_2d(const Tensor& x, int64_t h, int64_t w, bool a) override { return rt_->interpolate_bilinear_2d(x, h, w, a); }
+    Tensor pixel_norm(const Tensor& x, int64_t d, float e) override { return rt_->pixel_norm(x, d, e); }
+    Tensor l2_normalize(const Tensor& x, int64_t d, float e) override { return rt_->l2_normalize(x, d, e); }
+    Tensor pixel_shuffle_nd(const Tensor& x, const std::vector<int64_t>& f) override { return rt_->pixel_shuffle_nd(x, f); }
+    Tensor rng_normal(vrhino::RngState& s, const std::vector<int64_t>& shape, DType d) override { return rt_->rng_normal(s, shape, d); }
+
+private:
+    DType operand_dtype(const Tensor& t) const;
+    Tensor binary(int kind, const Tensor& a, const Tensor& b);
+    Tensor unary(int which, const Tensor& x, int kind, float p0, float p1);
+    Tensor parameter(const Tensor& t);
+    Tensor dequantize(const Tensor& input, DType dtype);
+    Tensor group_norm_impl(const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps, bool silu);
+    void* workspace(size_t bytes);
+    void begin_operator() const;
+    template <typename F> Tensor guarded(F&& body);
+    template <typename F> Tensor unguarded(F&& body);
+
+    std::unique_ptr<vrhino::Backend> rt_;
+    Tensor workspace_;
+};
+
+// ---- call-site view ---------------------------------------------------------------------------
+// Same arguments as the seams of native/include/vrhino/architecture.h:63-86 they merge.  With a
+// B200Backend behind `backend` each is ONE kernel; with any other backend they compose the
+// reference's own seams, so a call site can be switched unconditionally.
+
+// cast(modulate(layer_norm(x, weight, bias, eps), shift, scale), output)   (wan.cpp:85-92)
+vrhino::Tensor layer_norm_modulate(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy,
+                                   const vrhino::Tensor& x, const vrhino::Tensor* weight, const vrhino::Tensor* bias,
+                                   float eps, const vrhino::Tensor& shift, const vrhino::Tensor& scale,
+                                   vrhino::DType output = vrhino::DType::BF16);
+// cast(operation_rope(split_heads(attention_norm(x, weight, eps)), cos, sin), output) for x [B,S,D]
+// (wan.cpp:38-52); per_head_norm: heads are split before the norm (mochi.cpp:182-187).  cosine /
+// sine may be null (norm + cast only).  The result keeps x's [B,S,D] shape.
+vrhino::Tensor rms_norm_rope(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy,
+                             const vrhino::Tensor& x, const vrhino::Tensor* weight, float eps,
+                             const vrhino::Tensor* cosine, const vrhino::Tensor* sine, int heads,
+                             bool per_head_norm = false, vrhino::DType output = vrhino::DType::BF16);
+// gated_residual / residual_add (gate == nullptr) of common.cpp:134-144.
+vrhino::Tensor fused_gated_residual(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy,
+                                    const vrhino::Tensor& residual, const vrhino::Tensor& branch,
+                                    const vrhino::Tensor* gate);
+// mul(parts[0], silu(parts[1])), parts = split(projected, {H, H}, -1)   (mochi.cpp:195-202)
+vrhino::Tensor swiglu(vrhino::Backend& backend, const vrhino::Tensor& projected);
+// activation(group_norm(x, groups, weight, bias, eps), Silu)   (autoencoder_kl.cpp:31-41)
+vrhino::Tensor group_norm_silu(vrhino::Backend& backend, const vrhino::Tensor& x, int groups,
+                               const vrhino::Tensor* weight, const vrhino::Tensor* bias, float eps);
+
+}  // namespace vrhino_b200

@@ -59,6 +59,16 @@ def _dense(t):
     return t
 
 
+def _result(out, shape, dtype, device):
+    """The output tensor of an operator: a fresh one, or the caller's reusable buffer after a
+    shape / dtype / device / density check."""
+    if out is None:
+        return torch.empty(tuple(shape), dtype=dtype, device=device)
+    if tuple(out.shape) != tuple(shape) or out.dtype != dtype or out.device != device or not out.is_contiguous():
+        raise VrbError("output buffer does not match the result's shape, dtype or device")
+    return out
+
+
 class HostScalar:
     """A rank-0 host F32 value (scalar_f32 of native/src/tensor_util.cpp:20)."""
 
@@ -140,7 +150,7 @@ class B200Backend:
         """Optional affine parameter: uploaded if it still lives on the host."""
         return None if t is None else _dense(t if t.is_cuda else t.to(self.device))
 
-    def layer_norm(self, raw, weight, bias, eps):
+    def layer_norm(self, raw, weight, bias, eps, out=None):
         weight, bias = self._param(weight), self._param(bias)
         dtype = self._dtype_of(raw)
         x = _dense(self.copy_to_device(raw, dtype))
@@ -148,7 +158,7 @@ class B200Backend:
         for name, t in (("weight", weight), ("bias", bias)):
             if t is not None and t.numel() != width:
                 raise VrbError(f"layer norm {name} mismatch")
-        out = torch.empty_like(x)
+        out = _result(out, x.shape, x.dtype, x.device)
         call("vrb_layer_norm", _ptr(x), _code(x), _ptr(weight), _code(weight) if weight is not None else 0,
              _ptr(bias), _code(bias) if bias is not None else 0, _ptr(out), x.numel() // width, width,
              ctypes.c_float(eps), _stream())
@@ -184,10 +194,10 @@ class B200Backend:
                  x.numel() // (width * inner), width, inner, ctypes.c_float(eps), 0, _stream())
         return out
 
-    def activation(self, raw, kind):
+    def activation(self, raw, kind, out=None):
         dtype = self._dtype_of(raw)
         x = _dense(self.copy_to_device(raw, dtype))
-        out = torch.empty_like(x)
+        out = _result(out, x.shape, x.dtype, x.device)
         call("vrb_activation", int(kind), _ptr(x), _ptr(out), _code(x), x.numel(), _stream())
         return out
 
@@ -221,7 +231,7 @@ class B200Backend:
         call("vrb_rope", _ptr(x), _code(x), xs, xr, _ptr(c), _ptr(s), _code(c), fs, fr, _ptr(out), _stream())
         return out
 
-    def dequantize(self, packed, scales, group_size, kind=_lib.Q_FP8, dtype=BF16, shape=None):
+    def dequantize(self, packed, scales, group_size, kind=_lib.Q_FP8, dtype=BF16, shape=None, out=None):
         """copy_to_device of a quantized weight (cuda_backend.cu:3214-3296)."""
         packed = _dense(packed.to(self.device))
         scales = _dense(scales.to(self.device, torch.float32))
@@ -230,7 +240,7 @@ class B200Backend:
         inner = 1
         for d in shape[1:]:
             inner *= d
-        out = torch.empty(shape, dtype=dtype, device=self.device)
+        out = _result(out, shape, dtype, packed.device)
         call("vrb_dequantize", kind, _ptr(packed), _ptr(scales), _ptr(out), _code(dtype), rows, inner, group_size, _stream())
         return out
 
@@ -240,7 +250,7 @@ class B200Backend:
             self._gn_workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
         return self._gn_workspace, need
 
-    def group_norm(self, raw, groups, weight, bias, eps, fuse_silu=False):
+    def group_norm(self, raw, groups, weight, bias, eps, fuse_silu=False, out=None):
         if raw.dim() < 3 or groups <= 0 or raw.shape[1] % groups:
             raise VrbError("group norm shape/groups mismatch")
         weight, bias = self._param(weight), self._param(bias)
@@ -248,7 +258,7 @@ class B200Backend:
         x = _dense(self.copy_to_device(raw, dtype))
         batch, channels = x.shape[0], x.shape[1]
         spatial = x.numel() // (batch * channels)
-        out = torch.empty_like(x)
+        out = _result(out, x.shape, x.dtype, x.device)
         ws, need = self._workspace(batch, groups)
         call("vrb_group_norm", _ptr(x), _code(x), _ptr(weight), _code(weight) if weight is not None else 0,
              _ptr(bias), _code(bias) if bias is not None else 0, _ptr(out), batch, channels, spatial, groups,
@@ -365,7 +375,7 @@ def _vec_layout(rows, x_shape, vec):
     raise VrbError("Incompatible broadcast shapes")
 
 
-def fused_layer_norm_modulate(be, x, weight, bias, eps, shift, scale, out_dtype=BF16):
+def fused_layer_norm_modulate(be, x, weight, bias, eps, shift, scale, out_dtype=BF16, out=None):
     """cast(modulate(layer_norm(x, weight, bias, eps), shift, scale), out_dtype) in one pass."""
     x = _dense(x)
     width = x.shape[-1]
@@ -373,49 +383,49 @@ def fused_layer_norm_modulate(be, x, weight, bias, eps, shift, scale, out_dtype=
     rpv, nvec = _vec_layout(rows, x.shape, scale)
     if shift is not None and (shift.dtype != scale.dtype or shift.numel() != scale.numel()):
         raise VrbError("modulate: shift and scale must share dtype and shape")
-    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    out = _result(out, x.shape, out_dtype, x.device)
     call("vrb_layer_norm_modulate", _ptr(x), _code(x), _ptr(weight), _code(weight) if weight is not None else 0,
          _ptr(bias), _code(bias) if bias is not None else 0, _ptr(_dense(scale)), _ptr(shift), _code(scale),
          rpv, nvec, _ptr(out), _code(out_dtype), rows, width, ctypes.c_float(eps), _stream())
     return out
 
 
-def fused_layer_norm_cast(be, x, weight, bias, eps, out_dtype=BF16):
+def fused_layer_norm_cast(be, x, weight, bias, eps, out_dtype=BF16, out=None):
     """cast(layer_norm(x, weight, bias, eps), out_dtype) in one pass."""
     x = _dense(x)
     width = x.shape[-1]
-    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    out = _result(out, x.shape, out_dtype, x.device)
     call("vrb_layer_norm_cast", _ptr(x), _code(x), _ptr(weight), _code(weight) if weight is not None else 0,
          _ptr(bias), _code(bias) if bias is not None else 0, _ptr(out), _code(out_dtype), x.numel() // width, width,
          ctypes.c_float(eps), _stream())
     return out
 
 
-def fused_rms_norm_modulate(be, x, eps, shift, scale, out_dtype=BF16):
+def fused_rms_norm_modulate(be, x, eps, shift, scale, out_dtype=BF16, out=None):
     """cast(modulate(rms_norm(x, None, eps), shift, scale), out_dtype) -- the LTX block."""
     x = _dense(x)
     width = x.shape[-1]
     rows = x.numel() // width
     rpv, nvec = _vec_layout(rows, x.shape, scale)
-    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    out = _result(out, x.shape, out_dtype, x.device)
     call("vrb_rms_norm_modulate", _ptr(x), _code(x), _ptr(_dense(scale)), _ptr(shift), _code(scale), rpv, nvec,
          _ptr(out), _code(out_dtype), rows, width, ctypes.c_float(eps), _stream())
     return out
 
 
-def fused_rms_norm_scale(be, x, scale, eps=1e-6):
+def fused_rms_norm_scale(be, x, scale, eps=1e-6, out=None):
     """mul(rms_norm(x, None, eps), add(1, scale[B,1,D])) -- native/src/architectures/mochi.cpp:230-231."""
     x = _dense(x)
     width = x.shape[-1]
     rows = x.numel() // width
     rpv, nvec = _vec_layout(rows, x.shape, scale)
-    out = torch.empty_like(x)
+    out = _result(out, x.shape, x.dtype, x.device)
     call("vrb_rms_norm_scale", _ptr(x), _code(x), _ptr(_dense(scale)), _code(scale), rpv, nvec, _ptr(out),
          rows, width, ctypes.c_float(eps), _stream())
     return out
 
 
-def fused_rms_norm_rope(be, x, weight, eps, cosine, sine, heads=1, per_head_norm=False, out_dtype=BF16):
+def fused_rms_norm_rope(be, x, weight, eps, cosine, sine, heads=1, per_head_norm=False, out_dtype=BF16, out=None):
     """cast(operation_rope(split_heads(attention_norm(x, weight, eps)), cos, sin), out_dtype).
 
     x is [B, S, D].  per_head_norm=False: normalise over D, then split into `heads` (Wan,
@@ -428,7 +438,7 @@ def fused_rms_norm_rope(be, x, weight, eps, cosine, sine, heads=1, per_head_norm
     rows = x.numel() // width
     head_width = width // heads
     norm_width = head_width if per_head_norm else width
-    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    out = _result(out, x.shape, out_dtype, x.device)
     if cosine is None:
         f_rows, f_width, rpf, cp, sp = 0, 8, 1, None, None
     else:
@@ -447,52 +457,52 @@ def fused_rms_norm_rope(be, x, weight, eps, cosine, sine, heads=1, per_head_norm
     return out
 
 
-def fused_gated_residual(be, policy, residual, branch, gate):
+def fused_gated_residual(be, policy, residual, branch, gate, out=None):
     """gated_residual(...) / residual_add(...) (gate None) of common.cpp:134-144 in one pass."""
     residual, branch = _dense(residual), _dense(branch)
     width = residual.shape[-1]
     rows = residual.numel() // width
     rpv, nvec = (1, 1) if gate is None else _vec_layout(rows, residual.shape, gate)
-    out = torch.empty(residual.shape, dtype=policy.residual, device=residual.device)
+    out = _result(out, residual.shape, policy.residual, residual.device)
     call("vrb_gated_residual", _ptr(residual), _code(residual), _ptr(branch), _code(branch),
          _ptr(gate), _code(gate) if gate is not None else 0, rpv, nvec, _ptr(out), _code(policy.residual),
          rows, width, _stream())
     return out
 
 
-def fused_rms_norm_gated_residual(be, policy, residual, branch, bounded_gate, eps=1e-6):
+def fused_rms_norm_gated_residual(be, policy, residual, branch, bounded_gate, eps=1e-6, out=None):
     """gated_residual(residual, rms_norm(branch, None, eps), bounded_gate) -- mochi.cpp:204-211
     after the tanh on the [B, D] gate."""
     residual, branch = _dense(residual), _dense(branch)
     width = residual.shape[-1]
     rows = residual.numel() // width
     rpv, nvec = _vec_layout(rows, residual.shape, bounded_gate)
-    out = torch.empty(residual.shape, dtype=policy.residual, device=residual.device)
+    out = _result(out, residual.shape, policy.residual, residual.device)
     call("vrb_rms_norm_gated_residual", _ptr(residual), _code(residual), _ptr(branch), _code(branch),
          _ptr(_dense(bounded_gate)), _code(bounded_gate), rpv, nvec, _ptr(out), _code(policy.residual),
          rows, width, ctypes.c_float(eps), _stream())
     return out
 
 
-def fused_swiglu(be, projected):
+def fused_swiglu(be, projected, out=None):
     """mul(parts[0], silu(parts[1])) with parts = split(projected, 2, -1) -- mochi.cpp:195-202."""
     projected = _dense(projected)
     hidden = projected.shape[-1] // 2
     rows = projected.numel() // (2 * hidden)
-    out = torch.empty(projected.shape[:-1] + (hidden,), dtype=projected.dtype, device=projected.device)
+    out = _result(out, projected.shape[:-1] + (hidden,), projected.dtype, projected.device)
     call("vrb_swiglu", _ptr(projected), _ptr(out), _code(projected), rows, hidden, _stream())
     return out
 
 
-def fused_cfg_combine(be, policy, unconditional, conditional, scale):
-    out = torch.empty_like(unconditional)
+def fused_cfg_combine(be, policy, unconditional, conditional, scale, out=None):
+    out = _result(out, unconditional.shape, unconditional.dtype, unconditional.device)
     call("vrb_cfg_combine", _ptr(_dense(unconditional)), _ptr(_dense(conditional)), _ptr(out), _code(out),
          out.numel(), ctypes.c_float(scale), int(GUIDANCE in policy.scalar_roles), _stream())
     return out
 
 
-def fused_euler_update(be, policy, sample, prediction, delta, subtract_prediction):
-    out = torch.empty_like(sample)
+def fused_euler_update(be, policy, sample, prediction, delta, subtract_prediction, out=None):
+    out = _result(out, sample.shape, sample.dtype, sample.device)
     k = _euler_delta(be, policy, delta)
     call("vrb_euler_update", _ptr(_dense(sample)), _ptr(_dense(prediction)), _ptr(out), _code(out), out.numel(),
          ctypes.c_float(k), int(subtract_prediction), int(SOLVER in policy.scalar_roles), _stream())
@@ -507,9 +517,9 @@ def fused_flow_to_x0(be, policy, sample, model_output, sigma):
 
 
 def fused_cfg_euler(be, policy, sample, unconditional, conditional, scale, delta, subtract_prediction=True,
-                    want_guided=False):
+                    want_guided=False, out=None):
     """euler_update(sample, cfg_combine(u, c, scale), delta, subtract) in one pass."""
-    out = torch.empty_like(sample)
+    out = _result(out, sample.shape, sample.dtype, sample.device)
     guided = torch.empty_like(sample) if want_guided else None
     k = _euler_delta(be, policy, delta)
     call("vrb_cfg_euler", _ptr(_dense(sample)), _ptr(_dense(unconditional)), _ptr(_dense(conditional)), _ptr(guided),
@@ -518,9 +528,9 @@ def fused_cfg_euler(be, policy, sample, unconditional, conditional, scale, delta
     return (out, guided) if want_guided else out
 
 
-def fused_group_norm_silu(be, x, groups, weight, bias, eps):
+def fused_group_norm_silu(be, x, groups, weight, bias, eps, out=None):
     """activation(group_norm(x, ...), Silu) -- native/src/components/autoencoder_kl.cpp:40-41."""
-    return be.group_norm(x, groups, weight, bias, eps, fuse_silu=True)
+    return be.group_norm(x, groups, weight, bias, eps, fuse_silu=True, out=out)
 
 
 def fused_rms_channel_silu(be, x, gamma, eps=1e-12):

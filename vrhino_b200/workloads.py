@@ -74,18 +74,18 @@ class WanBlock:
         hb = self.x.element_size()
         vec = D * 4
 
-        def A(): o["A"] = ops.fused_layer_norm_modulate(be, self.x, None, None, e, r[0], r[1])
-        def Bq(): o["Bq"] = ops.fused_rms_norm_rope(be, self.q, self.wq, e, self.cos, self.sin, heads=self.heads)
-        def Bk(): o["Bk"] = ops.fused_rms_norm_rope(be, self.k, self.wk, e, self.cos, self.sin, heads=self.heads)
-        def C(): o["C"] = ops.fused_gated_residual(be, p, self.x, self.proj, r[2])
-        def Dn(): o["D"] = be.layer_norm(self.x, self.gamma3, self.beta3, e) if self.x.dtype == BF16 else \
-            ops.fused_layer_norm_cast(be, self.x, self.gamma3, self.beta3, e)
-        def Eq(): o["Eq"] = ops.fused_rms_norm_rope(be, self.cross_q, self.wcq, e, None, None, heads=self.heads)
-        def Ek(): o["Ek"] = ops.fused_rms_norm_rope(be, self.cross_k, self.wck, e, None, None, heads=self.heads)
-        def Fr(): o["F"] = ops.fused_gated_residual(be, p, self.x, self.cross, None)
-        def G(): o["G"] = ops.fused_layer_norm_modulate(be, self.x, None, None, e, r[3], r[4])
-        def H(): o["H"] = be.activation(self.ffn_hidden, ops.GELU_TANH)
-        def I(): o["I"] = ops.fused_gated_residual(be, p, self.x, self.ffn_out, r[5])
+        def A(): o["A"] = ops.fused_layer_norm_modulate(be, self.x, None, None, e, r[0], r[1], out=o.get("A"))
+        def Bq(): o["Bq"] = ops.fused_rms_norm_rope(be, self.q, self.wq, e, self.cos, self.sin, heads=self.heads, out=o.get("Bq"))
+        def Bk(): o["Bk"] = ops.fused_rms_norm_rope(be, self.k, self.wk, e, self.cos, self.sin, heads=self.heads, out=o.get("Bk"))
+        def C(): o["C"] = ops.fused_gated_residual(be, p, self.x, self.proj, r[2], out=o.get("C"))
+        def Dn(): o["D"] = be.layer_norm(self.x, self.gamma3, self.beta3, e, out=o.get("D")) if self.x.dtype == BF16 else \
+            ops.fused_layer_norm_cast(be, self.x, self.gamma3, self.beta3, e, out=o.get("D"))
+        def Eq(): o["Eq"] = ops.fused_rms_norm_rope(be, self.cross_q, self.wcq, e, None, None, heads=self.heads, out=o.get("Eq"))
+        def Ek(): o["Ek"] = ops.fused_rms_norm_rope(be, self.cross_k, self.wck, e, None, None, heads=self.heads, out=o.get("Ek"))
+        def Fr(): o["F"] = ops.fused_gated_residual(be, p, self.x, self.cross, None, out=o.get("F"))
+        def G(): o["G"] = ops.fused_layer_norm_modulate(be, self.x, None, None, e, r[3], r[4], out=o.get("G"))
+        def H(): o["H"] = be.activation(self.ffn_hidden, ops.GELU_TANH, out=o.get("H"))
+        def I(): o["I"] = ops.fused_gated_residual(be, p, self.x, self.ffn_out, r[5], out=o.get("I"))
 
         table = self.cos.numel() * 4 * 2
         return [
@@ -125,24 +125,142 @@ def time_launches(launches: List[Launch], steps: int, warmup: int):
     return sum(per.values()), per
 
 
-def _main():
-    """python -m vrhino_b200.workloads [--tokens N] [--only PREFIX] [--repeat R] [--hidden bf16|f32]
+class Wan22Step:
+    """Wan2.2-A14B step pieces: the D=5120 / FFN=13824 block chain, the FP8-e4m3 weight dequant
+    [5120, 13824] with per-output-channel F32 scales (copy_to_device's quantised branch,
+    native/src/backend/cuda/cuda_backend.cu:3214-3296), and cfg_combine + euler_update on the
+    F32 latent [1,16,21,60,104] (native/src/sampling.cpp:181-193)."""
 
-    Runs (selected) launches of the Wan block chain a few times and prints their device times; a
+    def __init__(self, be, tokens=32760, seed=0, with_block=True):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        self.be = be
+        self.block = WanBlock(be, tokens=tokens, dim=5120, heads=40, ffn=13824, grid=(1, 1, tokens), seed=seed) if with_block else None
+        rows, cols = 5120, 13824
+        codes = torch.randint(0, 254, (rows, cols), device="cuda", dtype=torch.int16, generator=g)
+        self.packed = (codes + (codes >= 127).to(torch.int16)).to(torch.uint8)   # the 254 finite codes: no 0x7f, 0xff
+        self.scales = (torch.rand((rows, 1), device="cuda", generator=g) * 9e-3 + 1e-3).float()
+        self.latent, self.uncond, self.cond = (_randn((1, 16, 21, 60, 104), F32, g) for _ in range(3))
+        self.policy = ops.Policy.fp32()
+        self.out = {}
+
+    def launches(self) -> List[Launch]:
+        be, o = self.be, self.out
+        n = self.latent.numel()
+
+        def dq(): o["dequant"] = be.dequantize(self.packed, self.scales, self.packed.shape[1], out=o.get("dequant"))
+        def cfg(): o["cfg"] = ops.fused_cfg_combine(be, self.policy, self.uncond, self.cond, 5.0, out=o.get("cfg"))
+        def euler(): o["euler"] = ops.fused_euler_update(be, self.policy, self.latent, self.uncond, 0.02, True, out=o.get("euler"))
+        def both(): o["cfg_euler"] = ops.fused_cfg_euler(be, self.policy, self.latent, self.uncond, self.cond, 5.0, 0.02, True, out=o.get("cfg_euler"))
+
+        extra = [
+            Launch("fp8 dequant", dq, self.packed.numel() * 3 + self.scales.numel() * 4),
+            Launch("cfg_combine", cfg, n * 12),
+            Launch("euler_update", euler, n * 12),
+            Launch("cfg+euler fused", both, n * 16),
+        ]
+        return (self.block.launches() if self.block is not None else []) + extra
+
+
+class MochiBlock:
+    """Mochi-style visual stream, per rank: S tokens of dim 3072, 24 heads x 128, SwiGLU hidden
+    8192 (native/src/architectures/mochi.cpp:182-231): RMS(no weight) -> *(1+scale) -> bf16;
+    per-head RMS(w, 1e-5) -> RoPE with per-head tables -> bf16 for q and k; SwiGLU;
+    residual + RMS(branch) * tanh-bounded gate."""
+
+    def __init__(self, be, tokens=44520, dim=3072, heads=24, hidden=8192, seed=0, hidden_dtype=BF16):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        self.be, S, D = be, tokens, dim
+        self.heads = heads
+        self.policy = ops.Policy(BF16, hidden_dtype)
+        self.x = _randn((1, S, D), hidden_dtype, g)
+        self.h, self.q, self.k, self.branch = (_randn((1, S, D), BF16, g) for _ in range(4))
+        self.scale = _randn((1, 1, D), F32, g, std=0.1)
+        self.gate = torch.tanh(_randn((1, 1, D), F32, g, std=0.1))
+        self.wq, self.wk = (_randn((D // heads,), F32, g, 1.0, 0.1) for _ in range(2))
+        phase = torch.rand((1, S, heads, D // heads), device="cuda", generator=g) * 6.2831853
+        self.cos, self.sin = torch.cos(phase), torch.sin(phase)
+        del phase
+        self.proj = _randn((1, S, 2 * hidden), BF16, g)
+        self.out = {}
+
+    def launches(self) -> List[Launch]:
+        be, p, o = self.be, self.policy, self.out
+        act = self.h.numel()
+        hb = self.x.element_size()
+        vec = self.scale.numel() * 4
+        table = self.cos.numel() * 4 * 2
+
+        def pre(): o["pre"] = ops.fused_rms_norm_scale(be, self.h, self.scale, 1e-6, out=o.get("pre"))
+        def q(): o["q"] = ops.fused_rms_norm_rope(be, self.q, self.wq, 1e-5, self.cos, self.sin, heads=self.heads, per_head_norm=True, out=o.get("q"))
+        def k(): o["k"] = ops.fused_rms_norm_rope(be, self.k, self.wk, 1e-5, self.cos, self.sin, heads=self.heads, per_head_norm=True, out=o.get("k"))
+        def sw(): o["swiglu"] = ops.fused_swiglu(be, self.proj, out=o.get("swiglu"))
+        def res(): o["res"] = ops.fused_rms_norm_gated_residual(be, p, self.x, self.branch, self.gate, 1e-6, out=o.get("res"))
+
+        return [
+            Launch("rms_scale", pre, act * 4 + vec),
+            Launch("head rms_rope q", q, act * 4 + table + 512),
+            Launch("head rms_rope k", k, act * 4 + table + 512),
+            Launch("swiglu", sw, self.proj.numel() * 2 + self.proj.numel()),
+            Launch("rms_gated_residual", res, act * (2 + 2 * hb) + vec),
+        ]
+
+
+class VaeGroupNorm:
+    """VAE decoder GroupNorm(32 groups, eps 1e-6) + SiLU on [N, 256, T, H, W] bf16 ~N(0, 2)
+    (native/src/components/autoencoder_kl.cpp:31-41).  Statistics pass + apply pass: the input
+    counts twice in the algorithmic bytes, the output once."""
+
+    def __init__(self, be, shape=(1, 256, 28, 240, 424), groups=32, seed=0):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        self.be, self.groups = be, groups
+        self.x = _randn(shape, BF16, g, 0.0, 2.0)
+        self.gamma = _randn((shape[1],), F32, g, 1.0, 0.1)
+        self.beta = _randn((shape[1],), F32, g, 0.0, 0.1)
+        self.out = {}
+
+    def launches(self) -> List[Launch]:
+        def gn(): self.out["gn"] = ops.fused_group_norm_silu(self.be, self.x, self.groups, self.gamma, self.beta, 1e-6, out=self.out.get("gn"))
+        return [Launch("group_norm_silu", gn, self.x.numel() * 6, kernels=4)]
+
+
+def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None):
+    """The launch list of headline configuration 2..5 (optionally at a reduced token / frame count)."""
+    if config == 2:
+        t = tokens or 32760
+        return WanBlock(be, tokens=t, grid=(21, 30, 52) if t == 32760 else (1, 1, t), hidden_dtype=hidden_dtype)
+    if config == 3:
+        return Wan22Step(be, tokens=tokens or 32760)
+    if config == 4:
+        return MochiBlock(be, tokens=tokens or 44520, hidden_dtype=hidden_dtype)
+    if config == 5:
+        return VaeGroupNorm(be, shape=(1, 256, frames or 28, 240, 424))
+    if config == 6:
+        return VaeGroupNorm(be, shape=(frames or 28, 256, 1, 240, 424))
+    raise ValueError("config must be 2..6 (6 = config 5 in Mochi's per-frame form)")
+
+
+def _main():
+    """python -m vrhino_b200.workloads [--config C] [--tokens N] [--frames T] [--only PREFIX]
+    [--repeat R] [--hidden bf16|f32]
+
+    Runs (selected) launches of one configuration a few times and prints their device times; a
     small, self-contained command for profilers."""
     import argparse
     ap = argparse.ArgumentParser()
+    ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--frames", type=int, default=None)
     ap.add_argument("--only", default="")
     ap.add_argument("--repeat", type=int, default=3)
     ap.add_argument("--hidden", default="bf16", choices=["bf16", "f32"])
     a = ap.parse_args()
     be = ops.B200Backend()
-    blk = WanBlock(be, tokens=a.tokens, grid=(1, 1, a.tokens), hidden_dtype=BF16 if a.hidden == "bf16" else F32)
-    launches = [l for l in blk.launches() if l.name.startswith(a.only)]
+    work = build_config(be, a.config, tokens=a.tokens, hidden_dtype=BF16 if a.hidden == "bf16" else F32, frames=a.frames)
+    launches = [l for l in work.launches() if l.name.startswith(a.only)]
     total, per = time_launches(launches, steps=a.repeat, warmup=1)
     for l in launches:
         print(f"{l.name:20s} {per[l.name] * 1e3:9.1f} us {l.bytes / per[l.name] / 1e6:9.1f} GB/s {l.bytes / 1e6:9.1f} MB")
+    print(f"{'total':20s} {total * 1e3:9.1f} us {sum(l.bytes for l in launches) / total / 1e6:9.1f} GB/s")
 
 
 class WanBlockHost:
