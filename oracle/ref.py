@@ -17,6 +17,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 HOST_LIB = os.path.join(_HERE, "_ref", "libvrhino_ref_host.so")
 CUDA_LIB = os.path.join(_HERE, "_ref", "libvrhino_ref_cuda.so")
+DROPIN_LIB = os.path.join(_HERE, "_ref", "libvrhino_dropin_cuda.so")
 _c = ctypes
 _fp = _c.POINTER(_c.c_float)
 F32, BF16, U8 = 0, 2, 5
@@ -29,6 +30,10 @@ def available_host() -> bool:
 
 def available_cuda() -> bool:
     return os.path.exists(CUDA_LIB)
+
+
+def available_dropin() -> bool:
+    return os.path.exists(DROPIN_LIB)
 
 
 def _f(a):
@@ -122,9 +127,12 @@ class RefHost:
 class RefCuda:
     """The reference's CUDA backend; tensors are handles kept on the device between calls."""
 
+    LIB = CUDA_LIB
+
     def __init__(self, execution_dtype=BF16):
-        lib = ctypes.CDLL(CUDA_LIB)
+        lib = ctypes.CDLL(self.LIB)
         lib.refc_last_error.restype = _c.c_char_p
+        lib.refc_backend_name.restype = _c.c_char_p
         for name in ("refc_upload", "refc_host_f32", "refc_numel", "refc_binary", "refc_cast", "refc_reshape", "refc_slice",
                      "refc_layer_norm", "refc_rms_norm", "refc_activation", "refc_rope", "refc_group_norm", "refc_clamp",
                      "refc_exp", "refc_sqrt", "refc_dequantize", "refc_modulate", "refc_attention_norm", "refc_operation_rope",
@@ -198,3 +206,32 @@ class RefCuda:
     def euler_update(self, policy, x, pred, delta, subtract=True):
         return self._h(self.lib.refc_euler_update(int(policy), self._i(x), self._i(pred), _c.c_float(delta), int(subtract)))
     def flow_to_x0(self, policy, x, out, sigma): return self._h(self.lib.refc_flow_to_x0(int(policy), self._i(x), self._i(out), _c.c_float(sigma)))
+
+
+class RefDropin(RefCuda):
+    """The same call surface over vrhino_b200::B200Backend (this repository's C++ host layer and
+    kernels) wrapped around the reference's CudaBackend: the reference's unmodified helper code
+    runs on the replaced operators.  The fused_* methods reach the one-kernel forms."""
+    LIB = DROPIN_LIB
+
+    def __init__(self, execution_dtype=BF16):
+        super().__init__(execution_dtype)
+        for name in ("refd_layer_norm_modulate", "refd_rms_norm_rope", "refd_gated_residual", "refd_swiglu",
+                     "refd_group_norm_silu", "refd_cfg_euler"):
+            getattr(self.lib, name).restype = _c.c_int64
+
+    def name(self): return self.lib.refc_backend_name().decode()
+    def session_terminal(self): return bool(self.lib.refd_session_terminal())
+    def fused_layer_norm_modulate(self, policy, x, w, b, eps, shift, scale, out_dtype=BF16):
+        return self._h(self.lib.refd_layer_norm_modulate(int(policy), self._i(x), self._i(w), self._i(b), _c.c_float(eps),
+                                                         self._i(shift), self._i(scale), int(out_dtype)))
+    def fused_rms_norm_rope(self, policy, x, w, eps, c, s, heads, per_head=False, out_dtype=BF16):
+        return self._h(self.lib.refd_rms_norm_rope(int(policy), self._i(x), self._i(w), _c.c_float(eps), self._i(c), self._i(s),
+                                                   int(heads), int(per_head), int(out_dtype)))
+    def fused_gated_residual(self, policy, r, b, g): return self._h(self.lib.refd_gated_residual(int(policy), self._i(r), self._i(b), self._i(g)))
+    def fused_swiglu(self, x): return self._h(self.lib.refd_swiglu(self._i(x)))
+    def fused_group_norm_silu(self, x, groups, w, b, eps):
+        return self._h(self.lib.refd_group_norm_silu(self._i(x), int(groups), self._i(w), self._i(b), _c.c_float(eps)))
+    def fused_cfg_euler(self, x, u, c, guidance, delta, subtract=True, guidance_role=False, solver_role=False):
+        return self._h(self.lib.refd_cfg_euler(self._i(x), self._i(u), self._i(c), _c.c_float(guidance), _c.c_float(delta),
+                                               int(subtract), int(guidance_role), int(solver_role)))

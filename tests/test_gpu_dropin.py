@@ -1,0 +1,129 @@
+"""The C++ host layer as a drop-in: vrhino_b200::B200Backend (vrhino_b200/host) wrapped around the
+reference's own CudaBackend, built by `make -C oracle dropin` against the reference's headers.
+
+The SAME call sequences that produced the golden vectors on the reference's CUDA backend
+(tests/golden/cases.py: run_reference, i.e. the reference's unmodified helper code -- modulate,
+attention_norm, operation_rope, gated_residual, SamplingPrimitives ...) are run with the replaced
+backend behind the `Backend&`, and compared with those golden vectors under the tolerances of
+test_golden.py.  Then the fused call-site forms, and the error / session behaviour.
+
+Skipped where the drop-in library has not been built (it needs the reference's headers).
+"""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "golden"))
+
+import cases  # noqa: E402
+from test_golden import compare, golden  # noqa: E402,F401  (fixture)
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dropin():
+    from oracle import ref
+    if not ref.available_dropin():
+        pytest.skip("oracle/_ref/libvrhino_dropin_cuda.so has not been built (make -C oracle dropin)")
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    rd = ref.RefDropin()
+    assert rd.name().startswith("b200+")
+    yield rd
+    rd.lib.refc_shutdown()
+
+
+@pytest.mark.parametrize("case", cases.CASES, ids=[c["name"] for c in cases.CASES])
+def test_reference_call_sites_on_the_replaced_backend(orc, golden, dropin, case):
+    want = golden[case["name"]]
+    got = cases.run_reference(dropin, case)
+    assert set(got) == set(want)
+    for name in want:
+        compare(orc, case, name, got[name], want[name], strict_tables=True)
+
+
+def _upload(rd, case):
+    from oracle import ref
+    code = {"f32": ref.F32, "bf16": ref.BF16}
+    return {k: rd.upload(cases.to_bits(a, dt), code[dt]) for k, (a, dt) in cases._inputs(case).items() if dt != "u8"}
+
+
+def _grab(rd, case, handle, shape):
+    from oracle import ref
+    payload, dt = rd.download(handle, shape)
+    return cases._sub(case, payload), {ref.F32: "f32", ref.BF16: "bf16"}[dt]
+
+
+@pytest.mark.parametrize("case", [c for c in cases.CASES if c["kind"] in
+                                  ("ln_modulate", "rms_rope", "gated_residual", "mochi", "group_norm", "sampler")],
+                         ids=lambda c: c["name"])
+def test_fused_call_site_forms(orc, golden, dropin, case):
+    """One kernel per chain through vrhino_b200::layer_norm_modulate / rms_norm_rope / ... ."""
+    from oracle import ref
+    rd, want, k = dropin, golden[case["name"]], case["kind"]
+    h = _upload(rd, case)
+    pol = ref.POLICY_BF16
+    try:
+        if k == "ln_modulate":
+            got = rd.fused_layer_norm_modulate(pol, h["x"], 0, 0, cases.EPS, h["shift"], h["scale"])
+            compare(orc, case, "cast", _grab(rd, case, got, case["shape"]), want["cast"])
+        elif k == "rms_rope":
+            S, H, d = case["tokens"], case["heads"], case["head_dim"]
+            got = rd.fused_rms_norm_rope(pol, h["x"], h["w"], 1e-5 if case["per_head"] else cases.EPS, h["cos"], h["sin"], H,
+                                         per_head=case["per_head"])
+            compare(orc, case, "cast", _grab(rd, case, got, (1, S, H, d)), want["cast"])
+            got = rd.fused_rms_norm_rope(pol, h["x"], h["w"], 1e-5 if case["per_head"] else cases.EPS, 0, 0, H,
+                                         per_head=case["per_head"])
+            compare(orc, case, "norm_cast", _grab(rd, case, got, (1, S, H, d)), want["norm_cast"])
+        elif k == "gated_residual":
+            p = ref.POLICY_BF16 if case["state"] == "bf16" else ref.POLICY_FP32
+            compare(orc, case, "gated", _grab(rd, case, rd.fused_gated_residual(p, h["res"], h["branch"], h["gate"]), case["shape"]),
+                    want["gated"])
+            compare(orc, case, "added", _grab(rd, case, rd.fused_gated_residual(p, h["res"], h["branch"], 0), case["shape"]),
+                    want["added"])
+        elif k == "mochi":
+            B, S, D = case["shape"]
+            compare(orc, case, "swiglu", _grab(rd, case, rd.fused_swiglu(h["proj"]), (B, S, case["hidden"])), want["swiglu"])
+        elif k == "group_norm":
+            got = rd.fused_group_norm_silu(h["x"], case["groups"], h["w"], h["b"], case["eps"])
+            compare(orc, case, "silu", _grab(rd, case, got, case["shape"]), want["silu"])
+        elif k == "sampler":
+            rd.lib.refc_init(ref.F32 if case["policy"] == "fp32" else ref.BF16)
+            roles = case["policy"] == "bf16_roles"
+            delta = 0.02
+            if case["policy"] == "bf16":     # no solver role: the coefficient tensor is rounded to the execution dtype
+                delta = float(orc.bf16_bits_to_f32(cases.to_bits(np.array([0.02], dtype=np.float32), "bf16"))[0])
+            got = rd.fused_cfg_euler(h["x"], h["u"], h["c"], 5.0, delta, True, roles, roles)
+            rd.lib.refc_init(ref.BF16)
+            compare(orc, case, "euler", _grab(rd, case, got, case["shape"]), want["euler"])
+    finally:
+        rd.clear()
+
+
+def test_errors_and_session_semantics(dropin):
+    """Same texts as the reference's wrappers; a rejected argument in an unguarded operator
+    (layer_norm) leaves the session usable, one in a guarded operator (clamp) retires it, after
+    which every call fails with the reference's terminal-session message."""
+    from oracle import ref
+    rd = dropin
+    try:
+        x = rd.upload(np.zeros((2, 8), dtype=np.float32), ref.F32)
+        w = rd.upload(np.ones((7,), dtype=np.float32), ref.F32)
+        with pytest.raises(RuntimeError, match="layer norm weight mismatch"):
+            rd.layer_norm(x, w, 0, 1e-5)
+        assert not rd.session_terminal()
+        a, _ = rd.download(rd.layer_norm(x, 0, 0, 1e-5), (2, 8))
+        assert np.isfinite(a).all()
+        with pytest.raises(RuntimeError, match="Invalid clamp bounds"):
+            rd.clamp(x, 1.0, 0.0)
+        assert rd.session_terminal()
+        with pytest.raises(RuntimeError, match="Resource session is terminal"):
+            rd.activation(x, 0)
+    finally:
+        rd.lib.refc_shutdown()          # a fresh backend for whoever uses the library next
+        rd.lib.refc_init(ref.BF16)

@@ -54,8 +54,8 @@ __device__ __forceinline__ void block_reduce2(double& a, double& b, double (*ws)
     for (int w = 0; w < kThreads / 32; ++w) { a += ws[0][w]; b += ws[1][w]; }
 }
 
-// partial[(unit * splits + split) * 2 + {0,1}] = {S1, S2} over the slice.
-template <bool VEC>
+// partial[(unit * splits + split) * 2 + {0,1}] = {S1, S2} over the slice; element-wise form for
+// units whose size or alignment rules out 16-byte loads.
 __global__ void __launch_bounds__(kThreads) gn_partial_kernel(const void* x, int dt, const float* shift,
                                                              double* partial, int64_t count, int splits) {
     __shared__ double ws[2][8];
@@ -64,36 +64,91 @@ __global__ void __launch_bounds__(kThreads) gn_partial_kernel(const void* x, int
     const int64_t base = unit * count;
     const float a = shift ? shift[unit] : load1(x, dt, base);
     double s1 = 0.0, s2 = 0.0;
-    if constexpr (VEC) {
-        const int64_t chunks = count >> 3;
-        const int64_t begin = chunks * split / splits, end = chunks * (split + 1) / splits;
-        constexpr int U = 4;   // independent 16-byte loads in flight per thread
-        for (int64_t c0 = begin + threadIdx.x; c0 < end; c0 += kThreads * U) {
-            float v[U][8];
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-                if (c0 + u * kThreads < end) load8<true>(x, dt, base + (c0 + u * kThreads) * 8, v[u]);
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (c0 + u * kThreads >= end) break;
-                float t1 = 0.0f, t2 = 0.0f;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float d = __fsub_rn(v[u][e], a);
-                    t1 = __fadd_rn(t1, d);
-                    t2 = __fmaf_rn(d, d, t2);
-                }
-                s1 += static_cast<double>(t1);
-                s2 += static_cast<double>(t2);
-            }
-        }
+    const int64_t begin = count * split / splits, end = count * (split + 1) / splits;
+    for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
+        const double d = static_cast<double>(__fsub_rn(load1(x, dt, base + i), a));
+        s1 += d;
+        s2 = fma(d, d, s2);
+    }
+    block_reduce2(s1, s2, ws);
+    if (threadIdx.x == 0) {
+        partial[(unit * splits + split) * 2] = s1;
+        partial[(unit * splits + split) * 2 + 1] = s2;
+    }
+}
+
+// The vector form of the moments pass, software-pipelined: the 16-byte loads of the next
+// iteration are issued before the current registers are consumed, so every warp always has U
+// loads in flight; x stays packed in registers until it is used.  BF16: U = 4 chunks of 8
+// elements per thread and iteration; F32: U = 2 chunks (two 16-byte loads each).
+template <bool X_BF16>
+struct Packed8 {
+    uint4 lo, hi;   // BF16 uses lo only
+};
+template <bool X_BF16>
+__device__ __forceinline__ Packed8<X_BF16> load_packed8(const void* x, int64_t element) {
+    Packed8<X_BF16> r;
+    if constexpr (X_BF16) {
+        r.lo = __ldcs(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + element));
     } else {
-        const int64_t begin = count * split / splits, end = count * (split + 1) / splits;
-        for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
-            const double d = static_cast<double>(__fsub_rn(load1(x, dt, base + i), a));
-            s1 += d;
-            s2 = fma(d, d, s2);
-        }
+        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const float*>(x) + element);
+        r.lo = __ldcs(p);
+        r.hi = __ldcs(p + 1);
+    }
+    return r;
+}
+template <bool X_BF16>
+__device__ __forceinline__ void accumulate_packed8(const Packed8<X_BF16>& r, float a, double& s1, double& s2) {
+    float v[8];
+    if constexpr (X_BF16) {
+        v[0] = __uint_as_float(r.lo.x << 16); v[1] = __uint_as_float(r.lo.x & 0xffff0000u);
+        v[2] = __uint_as_float(r.lo.y << 16); v[3] = __uint_as_float(r.lo.y & 0xffff0000u);
+        v[4] = __uint_as_float(r.lo.z << 16); v[5] = __uint_as_float(r.lo.z & 0xffff0000u);
+        v[6] = __uint_as_float(r.lo.w << 16); v[7] = __uint_as_float(r.lo.w & 0xffff0000u);
+    } else {
+        v[0] = __uint_as_float(r.lo.x); v[1] = __uint_as_float(r.lo.y); v[2] = __uint_as_float(r.lo.z); v[3] = __uint_as_float(r.lo.w);
+        v[4] = __uint_as_float(r.hi.x); v[5] = __uint_as_float(r.hi.y); v[6] = __uint_as_float(r.hi.z); v[7] = __uint_as_float(r.hi.w);
+    }
+    // two independent 4-long chains per sum instead of one 8-long chain
+    float t1a = 0.0f, t1b = 0.0f, t2a = 0.0f, t2b = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float da = __fsub_rn(v[e], a), db = __fsub_rn(v[e + 4], a);
+        t1a = __fadd_rn(t1a, da); t1b = __fadd_rn(t1b, db);
+        t2a = __fmaf_rn(da, da, t2a); t2b = __fmaf_rn(db, db, t2b);
+    }
+    s1 += static_cast<double>(__fadd_rn(t1a, t1b));
+    s2 += static_cast<double>(__fadd_rn(t2a, t2b));
+}
+
+template <bool X_BF16>
+__global__ void __launch_bounds__(kThreads, 4) gn_partial_vec_kernel(const void* __restrict__ x, const float* __restrict__ shift,
+                                                                    double* __restrict__ partial, int64_t count, int splits) {
+    __shared__ double ws[2][8];
+    constexpr int U = X_BF16 ? 4 : 2;
+    const int64_t unit = blockIdx.x / splits;
+    const int split = blockIdx.x % splits;
+    const int64_t base = unit * count;
+    const float a = shift ? shift[unit] : load1(x, X_BF16 ? VRB_BF16 : VRB_F32, base);
+    const int64_t chunks = count >> 3;
+    const int64_t begin = chunks * split / splits, end = chunks * (split + 1) / splits;
+    double s1 = 0.0, s2 = 0.0;
+    Packed8<X_BF16> cur[U], nxt[U];
+    int64_t c0 = begin + threadIdx.x;
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+        if (c0 + u * kThreads < end) cur[u] = load_packed8<X_BF16>(x, base + (c0 + u * kThreads) * 8);
+    while (c0 < end) {
+        const int64_t c1 = c0 + kThreads * U;
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (c1 + u * kThreads < end) nxt[u] = load_packed8<X_BF16>(x, base + (c1 + u * kThreads) * 8);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (c0 + u * kThreads < end) accumulate_packed8<X_BF16>(cur[u], a, s1, s2);
+#pragma unroll
+        for (int u = 0; u < U; ++u) cur[u] = nxt[u];
+        c0 = c1;
     }
     block_reduce2(s1, s2, ws);
     if (threadIdx.x == 0) {
@@ -147,43 +202,48 @@ __device__ __forceinline__ PlaneTerms plane_terms(int64_t plane, const GnGeom& g
     return t;
 }
 
-// Normalise pass.  VEC: the tensor is cut into tiles of kThreads * U 8-element chunks that lie
-// inside ONE plane (one channel of one batch entry), so mean / inverse / gamma / beta are looked
-// up once per tile and the inner loop has no index arithmetic beyond an add.
-template <bool VEC>
+// Normalise pass, vector form.  Every plane (one channel of one batch entry) is cut into
+// tiles_per_plane equal tiles of at most kThreads * U chunks, so mean / inverse / gamma / beta are
+// looked up once per tile, the inner loop has no index arithmetic beyond an add, and no tile is
+// much emptier than the others.
+template <bool X_BF16, bool SILU>
+__global__ void __launch_bounds__(kThreads, 4) gn_apply_vec_kernel(const void* __restrict__ x, const void* weight, int w_dt,
+                                                                  const void* bias, int b_dt, void* __restrict__ out, GnGeom g,
+                                                                  const float* mean, const float* inverse,
+                                                                  int64_t tiles_per_plane, int64_t tile_chunks) {
+    constexpr int U = 4;
+    constexpr int dt = X_BF16 ? VRB_BF16 : VRB_F32;
+    const int64_t plane_chunks = g.spatial >> 3;
+    const int64_t tiles = g.batch * g.channels * tiles_per_plane;
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t plane = t / tiles_per_plane;
+        const int64_t tile_begin = (t - plane * tiles_per_plane) * tile_chunks;
+        const int64_t tile_end = tile_begin + tile_chunks < plane_chunks ? tile_begin + tile_chunks : plane_chunks;
+        const int64_t c0 = tile_begin + threadIdx.x;
+        const PlaneTerms k = plane_terms(plane, g, dt, weight, w_dt, bias, b_dt, mean, inverse);
+        const int64_t e_plane = plane * g.spatial;
+        float v[U][8];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (c0 + u * kThreads < tile_end) load8<true>(x, dt, e_plane + (c0 + u * kThreads) * 8, v[u]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (c0 + u * kThreads >= tile_end) break;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[u][e] = gn_value(v[u][e], k.mean, k.inv, k.gamma, k.beta, dt, SILU ? 1 : 0);
+            store8(out, dt, e_plane + (c0 + u * kThreads) * 8, v[u]);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) gn_apply_kernel(const void* x, int dt, const void* weight, int w_dt,
                                                            const void* bias, int b_dt, void* out, GnGeom g,
                                                            const float* mean, const float* inverse, int silu) {
-    if constexpr (VEC) {
-        constexpr int U = 4;
-        constexpr int kTile = kThreads * U;
-        const int64_t plane_chunks = g.spatial >> 3;
-        const int64_t tiles_per_plane = (plane_chunks + kTile - 1) / kTile;
-        const int64_t tiles = g.batch * g.channels * tiles_per_plane;
-        for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
-            const int64_t plane = t / tiles_per_plane;
-            const int64_t c0 = (t - plane * tiles_per_plane) * kTile + threadIdx.x;
-            const PlaneTerms k = plane_terms(plane, g, dt, weight, w_dt, bias, b_dt, mean, inverse);
-            const int64_t e_plane = plane * g.spatial;
-            float v[U][8];
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-                if (c0 + u * kThreads < plane_chunks) load8<true>(x, dt, e_plane + (c0 + u * kThreads) * 8, v[u]);
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (c0 + u * kThreads >= plane_chunks) break;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[u][e] = gn_value(v[u][e], k.mean, k.inv, k.gamma, k.beta, dt, silu);
-                store8(out, dt, e_plane + (c0 + u * kThreads) * 8, v[u]);
-            }
-        }
-    } else {
-        const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-        const int64_t total = g.units * g.count;
-        for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-            const PlaneTerms k = plane_terms(i / g.spatial, g, dt, weight, w_dt, bias, b_dt, mean, inverse);
-            store1(out, dt, i, gn_value(load1(x, dt, i), k.mean, k.inv, k.gamma, k.beta, dt, silu));
-        }
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int64_t total = g.units * g.count;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const PlaneTerms k = plane_terms(i / g.spatial, g, dt, weight, w_dt, bias, b_dt, mean, inverse);
+        store1(out, dt, i, gn_value(load1(x, dt, i), k.mean, k.inv, k.gamma, k.beta, dt, silu));
     }
 }
 
@@ -214,8 +274,9 @@ int run_moments(const void* x, int dt, const GnGeom& g, const float* shift, doub
     const int splits = choose_splits(g.units, g.count);
     const bool vec = g.count % 8 == 0 && aligned16(x);
     const int grid = static_cast<int>(g.units * splits);
-    if (vec) gn_partial_kernel<true><<<grid, kThreads, 0, s>>>(x, dt, shift, partial, g.count, splits);
-    else gn_partial_kernel<false><<<grid, kThreads, 0, s>>>(x, dt, shift, partial, g.count, splits);
+    if (vec && dt == VRB_BF16) gn_partial_vec_kernel<true><<<grid, kThreads, 0, s>>>(x, shift, partial, g.count, splits);
+    else if (vec) gn_partial_vec_kernel<false><<<grid, kThreads, 0, s>>>(x, shift, partial, g.count, splits);
+    else gn_partial_kernel<<<grid, kThreads, 0, s>>>(x, dt, shift, partial, g.count, splits);
     if (int rc = after_launch("group_norm moments")) return rc;
     gn_collect_kernel<<<static_cast<int>((g.units + 127) / 128), 128, 0, s>>>(partial, moments, g.units, splits, g.count);
     return after_launch("group_norm collect");
@@ -229,11 +290,17 @@ int run_apply(const void* x, int dt, const void* weight, int w_dt, const void* b
         if (dt == VRB_BF16 && silu && total >= kLutMinElements)   // SiLU of a bf16 value: table lookup
             return launch_group_norm_apply_silu_lut(x, weight, w_dt, bias, b_dt, out, g.batch * g.channels, g.channels,
                                                     g.channels_per, g.groups, g.spatial, mean, inverse, s);
-        const int64_t tiles = g.batch * g.channels * ((g.spatial / 8 + kThreads * 4 - 1) / (kThreads * 4));
-        gn_apply_kernel<true><<<grid_for(tiles, 8), kThreads, 0, s>>>(
-            x, dt, weight, w_dt, bias, b_dt, out, g, mean, inverse, silu);
+        const int64_t plane_chunks = g.spatial / 8;
+        const int64_t tiles_per_plane = (plane_chunks + kThreads * 4 - 1) / (kThreads * 4);
+        const int64_t tile_chunks = ((plane_chunks + tiles_per_plane - 1) / tiles_per_plane + 7) & ~int64_t{7};   // tiles start on 128-byte lines
+        const int grid = grid_for(g.batch * g.channels * tiles_per_plane, 4);
+#define VRB_GN_APPLY(BF, SI) gn_apply_vec_kernel<BF, SI><<<grid, kThreads, 0, s>>>( \
+            x, weight, w_dt, bias, b_dt, out, g, mean, inverse, tiles_per_plane, tile_chunks)
+        if (dt == VRB_BF16) { if (silu) VRB_GN_APPLY(true, true); else VRB_GN_APPLY(true, false); }
+        else { if (silu) VRB_GN_APPLY(false, true); else VRB_GN_APPLY(false, false); }
+#undef VRB_GN_APPLY
     } else {
-        gn_apply_kernel<false><<<grid_for((total + kThreads - 1) / kThreads, 8), kThreads, 0, s>>>(
+        gn_apply_kernel<<<grid_for((total + kThreads - 1) / kThreads, 8), kThreads, 0, s>>>(
             x, dt, weight, w_dt, bias, b_dt, out, g, mean, inverse, silu);
     }
     return after_launch("group_norm apply");

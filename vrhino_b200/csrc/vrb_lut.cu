@@ -140,21 +140,22 @@ __global__ void __launch_bounds__(kLutThreads, 1) swiglu_lut_kernel(const uint4*
 // GroupNorm normalise pass + SiLU on bf16 (CudaBackend::group_norm :4919-5008 followed by
 // activation(Silu), native/src/components/autoencoder_kl.cpp:40-41): y = bf16((x - mean) * inv *
 // gamma + beta) with the reference's rounding order, then silu(y) read from the table, since y is
-// a bf16 value.  Tiles of kLutThreads * U chunks lie inside one plane, so the four constants are
-// fetched once per tile.
+// a bf16 value.  Every plane is cut into equal tiles of at most kLutThreads * U chunks, so the
+// four constants are fetched once per tile and no tile is much emptier than the others.
 __global__ void __launch_bounds__(kLutThreads, 1) gn_apply_silu_lut_kernel(
     const uint4* __restrict__ x, uint4* __restrict__ out, const void* __restrict__ weight, int w_dt,
     const void* __restrict__ bias, int b_dt, const float* __restrict__ mean, const float* __restrict__ inverse,
-    int64_t planes, int64_t channels, int channels_per, int groups, int64_t plane_chunks, const uint4* __restrict__ ready) {
+    int64_t planes, int64_t channels, int channels_per, int groups, int64_t plane_chunks, int64_t tiles_per_plane,
+    int64_t tile_chunks, const uint4* __restrict__ ready) {
     extern __shared__ __align__(16) uint16_t table[];
     fill_table<VRB_SILU>(table, ready, 0.f, 0.f);
     constexpr int U = 4;
-    constexpr int kTile = kLutThreads * U;
-    const int64_t tiles_per_plane = (plane_chunks + kTile - 1) / kTile;
     const int64_t tiles = planes * tiles_per_plane;
     for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
         const int64_t plane = t / tiles_per_plane;
-        const int64_t c0 = (t - plane * tiles_per_plane) * kTile + threadIdx.x;
+        const int64_t tile_begin = (t - plane * tiles_per_plane) * tile_chunks;
+        const int64_t tile_end = tile_begin + tile_chunks < plane_chunks ? tile_begin + tile_chunks : plane_chunks;
+        const int64_t c0 = tile_begin + threadIdx.x;
         const int64_t channel = plane % channels;
         const int64_t unit = (plane / channels) * groups + channel / channels_per;
         const float m = __ldg(mean + unit), inv = __ldg(inverse + unit);
@@ -165,10 +166,10 @@ __global__ void __launch_bounds__(kLutThreads, 1) gn_apply_silu_lut_kernel(
         uint4 r[U];
 #pragma unroll
         for (int u = 0; u < U; ++u)
-            if (c0 + u * kLutThreads < plane_chunks) r[u] = __ldcs(px + c0 + u * kLutThreads);
+            if (c0 + u * kLutThreads < tile_end) r[u] = __ldcs(px + c0 + u * kLutThreads);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            if (c0 + u * kLutThreads >= plane_chunks) break;
+            if (c0 + u * kLutThreads >= tile_end) break;
             const uint32_t w[4] = {r[u].x, r[u].y, r[u].z, r[u].w};
             uint32_t o[4];
 #pragma unroll
@@ -289,11 +290,13 @@ int launch_group_norm_apply_silu_lut(const void* x, const void* weight, int w_dt
     static bool done[64] = {false};
     if (int rc = reserve_table(gn_apply_silu_lut_kernel, done)) return rc;
     const int64_t plane_chunks = spatial / 8;
-    const int64_t tiles = planes * ((plane_chunks + kLutThreads * 4 - 1) / (kLutThreads * 4));
+    const int64_t tiles_per_plane = (plane_chunks + kLutThreads * 4 - 1) / (kLutThreads * 4);
+    const int64_t tile_chunks = ((plane_chunks + tiles_per_plane - 1) / tiles_per_plane + 7) & ~int64_t{7};   // tiles start on 128-byte lines
+    const int64_t tiles = planes * tiles_per_plane;
     const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
     gn_apply_silu_lut_kernel<<<grid, kLutThreads, kTableBytes, stream>>>(
         static_cast<const uint4*>(x), static_cast<uint4*>(out), weight, w_dt, bias, b_dt, mean, inverse, planes, channels,
-        channels_per, groups, plane_chunks, ready_table<VRB_SILU>(0.f, 0.f, stream));
+        channels_per, groups, plane_chunks, tiles_per_plane, tile_chunks, ready_table<VRB_SILU>(0.f, 0.f, stream));
     return after_launch("group_norm apply (table)");
 }
 
