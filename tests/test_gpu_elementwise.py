@@ -265,6 +265,32 @@ def test_dequantize_all_fp8_codes(orc, gpu):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+def test_dequantize_scale_extremes(orc, gpu):
+    """Every code against scales that stress the branch-free decode (which multiplies the code
+    lifted by 2^-120 with the scale lifted by 2^120): zero and negative zero, a denormal, the
+    largest scale the lifted form takes, scales beyond it (other path), huge and negative ones.
+    Expected: the F32 product decode(code) * scale rounded once, then to the output dtype."""
+    import torch
+    be, ops = gpu
+    scales = np.array([0.0, -0.0, 1e-40, 2.0 ** -126, 1e-3, 127.99, 128.0, 300.0, 1e30, -3.5, 2.0 ** 100, -1e-42],
+                      dtype=np.float32)
+    rows = scales.size
+    packed = np.tile(np.arange(256, dtype=np.uint8), (rows, 1))
+    decoded = np.array([orc.lib().orc_decode_fp8(int(c)) for c in range(256)], dtype=np.float32)
+    with np.errstate(over="ignore", under="ignore"):
+        want = decoded[None, :] * scales[:, None]            # one IEEE F32 multiply per element
+    got = be.dequantize(torch.from_numpy(packed), torch.from_numpy(scales.reshape(rows, 1)), 256, dtype=torch.float32).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), np.argwhere(got.view(np.uint32) != want.view(np.uint32))[:5]
+    got16 = be.dequantize(torch.from_numpy(packed), torch.from_numpy(scales.reshape(rows, 1)), 256, dtype=torch.bfloat16)
+    want16 = torch.from_numpy(want).to(torch.bfloat16)
+    assert torch.equal(got16.cpu().view(torch.int16), want16.view(torch.int16))
+    # per-group scales on the same path
+    gs = np.linspace(1e-3, 1e-2, rows * 16, dtype=np.float32).reshape(rows, 16)
+    got = be.dequantize(torch.from_numpy(packed), torch.from_numpy(gs), 16, dtype=torch.float32).cpu().numpy()
+    want = decoded[None, :] * np.repeat(gs, 16, axis=1)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
 SAMPLER_POLICIES = ["fp32", "bf16_legacy", "bf16_roles", "bf16_guidance_only"]
 
 

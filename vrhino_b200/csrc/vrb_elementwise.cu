@@ -413,34 +413,86 @@ __global__ void __launch_bounds__(kThreads) dequant_scalar_kernel(const uint8_t*
         store1(out, out_dt, i, __fmul_rn(quant_value<KIND>(packed, i), scales[outer * groups + group]));
     }
 }
-// Byte-per-element kinds with inner % 16 == 0 and group_size % 16 == 0: 16 codes per thread
-// per step (one 16-byte load), one scale per step, two 16-byte (bf16) or four (f32) stores.
-template <int KIND>
-__global__ void __launch_bounds__(kThreads) dequant_vec_kernel(const uint8_t* packed, const float* scales, void* out,
-                                                              int out_dt, int64_t chunks, int64_t inner_chunks,
-                                                              int64_t groups, int64_t group_chunks) {
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride) {
-        const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(packed) + i);
-        const int64_t outer = i / inner_chunks, group = (i - outer * inner_chunks) / group_chunks;
-        const float scale = __ldg(scales + outer * groups + group);
-        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-        float v[16];
+// Byte-per-element kinds with inner % 16 == 0 and group_size % 16 == 0.  Every row is cut into
+// equal tiles of at most kThreads * U 16-code chunks, so the row (and with per-channel scales
+// the scale itself) is found once per tile instead of by two 64-bit divisions per chunk.
+//
+// FP8 decode without a branch: the seven magnitude bits eeee mmm placed at bits 26..20 of an
+// F32 word read as (1 + m/8) * 2^(e-127) for e != 0 and as the F32 denormal m/8 * 2^-126 for
+// e == 0, i.e. exactly the e4m3 value times 2^-120 in both cases (0x7f / 0xff give 480 * 2^-120,
+// no NaN case, as decode_fp8_e4m3fn :630-638).  Multiplying by scale * 2^120 (exact while
+// |scale| < 2^7, checked per tile) therefore rounds the same real product the reference rounds;
+// the code's sign bit is XOR-ed into the scale.  Five integer/FP instructions per code.
+__device__ __forceinline__ float fp8_times(uint32_t word, int k, uint32_t scale_bits) {   // scale_bits = bits of scale * 2^120
+    const uint32_t mag = (k == 3 ? word >> 4 : word << (20 - 8 * k)) & 0x07f00000u;
+    const uint32_t sign = (k == 3 ? word : word << (24 - 8 * k)) & 0x80000000u;
+    return __fmul_rn(__uint_as_float(mag), __uint_as_float(scale_bits ^ sign));
+}
+template <int KIND, bool OUT_BF16, bool ROW_SCALE>
+__global__ void __launch_bounds__(kThreads, 4) dequant_tile_kernel(const uint4* __restrict__ packed, const float* __restrict__ scales,
+                                                                  void* __restrict__ out, int64_t rows, int64_t inner_chunks,
+                                                                  int64_t groups, int group_chunks, int64_t tiles_per_row,
+                                                                  int64_t tile_chunks) {
+    constexpr int U = 2;
+    const int64_t tiles = rows * tiles_per_row;
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t row = t / tiles_per_row;
+        const int64_t tile_begin = (t - row * tiles_per_row) * tile_chunks;
+        const int64_t tile_end = tile_begin + tile_chunks < inner_chunks ? tile_begin + tile_chunks : inner_chunks;
+        const int64_t c0 = tile_begin + threadIdx.x;
+        const uint4* src = packed + row * inner_chunks;
+        uint4 raw[U];
 #pragma unroll
-        for (int w = 0; w < 4; ++w)
+        for (int u = 0; u < U; ++u)
+            if (c0 + u * kThreads < tile_end) raw[u] = __ldcs(src + c0 + u * kThreads);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const uint32_t code = (words[w] >> (8 * k)) & 0xffu;
-                const float q = KIND == VRB_Q_FP8_E4M3FN ? decode_fp8(code)
-                                                         : static_cast<float>(static_cast<int8_t>(code));
-                v[w * 4 + k] = __fmul_rn(q, scale);
+        for (int u = 0; u < U; ++u) {
+            const int64_t c = c0 + u * kThreads;
+            if (c >= tile_end) break;
+            const float scale = __ldg(scales + (ROW_SCALE ? row : row * groups + static_cast<int>(c) / group_chunks));
+            const uint32_t words[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+            float v[16];
+            const float lifted = scale * 0x1p120f;
+            if (KIND == VRB_Q_FP8_E4M3FN && fabsf(scale) < 128.0f) {
+                const uint32_t sb = __float_as_uint(lifted);
+#pragma unroll
+                for (int w = 0; w < 4; ++w)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) v[w * 4 + k] = fp8_times(words[w], k, sb);
+            } else {
+#pragma unroll
+                for (int w = 0; w < 4; ++w)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t code = (words[w] >> (8 * k)) & 0xffu;
+                        const float q = KIND == VRB_Q_FP8_E4M3FN ? decode_fp8(code)
+                                                                 : static_cast<float>(static_cast<int8_t>(code));
+                        v[w * 4 + k] = __fmul_rn(q, scale);
+                    }
             }
-        float lo[8], hi[8];
+            const int64_t e0 = (row * inner_chunks + c) * 16;
+            float lo[8], hi[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { lo[e] = v[e]; hi[e] = v[8 + e]; }
-        store8(out, out_dt, i * 16, lo);
-        store8(out, out_dt, i * 16 + 8, hi);
+            for (int e = 0; e < 8; ++e) { lo[e] = v[e]; hi[e] = v[8 + e]; }
+            store8(out, OUT_BF16 ? VRB_BF16 : VRB_F32, e0, lo);
+            store8(out, OUT_BF16 ? VRB_BF16 : VRB_F32, e0 + 8, hi);
+        }
     }
+}
+template <int KIND>
+void launch_dequant_tiles(const uint8_t* packed, const float* scales, void* out, int out_dtype, int64_t rows, int64_t inner,
+                          int64_t groups, int64_t group_size, cudaStream_t s) {
+    const int64_t inner_chunks = inner / 16;
+    const int64_t tiles_per_row = (inner_chunks + kThreads * 2 - 1) / (kThreads * 2);
+    const int64_t tile_chunks = ((inner_chunks + tiles_per_row - 1) / tiles_per_row + 7) & ~int64_t{7};
+    const int grid = grid_for(rows * tiles_per_row, 8);
+    const uint4* p = reinterpret_cast<const uint4*>(packed);
+    const int gc = static_cast<int>(group_size / 16);
+#define VRB_DQ(BF, ROW) dequant_tile_kernel<KIND, BF, ROW><<<grid, kThreads, 0, s>>>( \
+        p, scales, out, rows, inner_chunks, groups, gc, tiles_per_row, tile_chunks)
+    if (out_dtype == VRB_BF16) { if (groups == 1) VRB_DQ(true, true); else VRB_DQ(true, false); }
+    else { if (groups == 1) VRB_DQ(false, true); else VRB_DQ(false, false); }
+#undef VRB_DQ
 }
 
 // -------------------------------------------------------------------- sampler arithmetic --
@@ -695,14 +747,11 @@ extern "C" int vrb_dequantize(int kind, const void* packed, const float* scales,
     const int64_t count = rows * inner, groups = (inner + group_size - 1) / group_size;
     const uint8_t* p = static_cast<const uint8_t*>(packed);
     cudaStream_t s = as_stream(stream);
-    const bool vec = kind != VRB_Q_INT4 && inner % 16 == 0 && group_size % 16 == 0 && aligned16(packed) && aligned16(out);
+    const bool vec = kind != VRB_Q_INT4 && inner % 16 == 0 && group_size % 16 == 0 && inner / 16 < 0x7fffffff && aligned16(packed) &&
+                     aligned16(out);
     if (vec) {
-        const int64_t chunks = count / 16;
-        const int grid = grid_for((chunks + kThreads - 1) / kThreads, kPerSm);
-        if (kind == VRB_Q_FP8_E4M3FN)
-            dequant_vec_kernel<VRB_Q_FP8_E4M3FN><<<grid, kThreads, 0, s>>>(p, scales, out, out_dtype, chunks, inner / 16, groups, group_size / 16);
-        else
-            dequant_vec_kernel<VRB_Q_INT8><<<grid, kThreads, 0, s>>>(p, scales, out, out_dtype, chunks, inner / 16, groups, group_size / 16);
+        if (kind == VRB_Q_FP8_E4M3FN) launch_dequant_tiles<VRB_Q_FP8_E4M3FN>(p, scales, out, out_dtype, rows, inner, groups, group_size, s);
+        else launch_dequant_tiles<VRB_Q_INT8>(p, scales, out, out_dtype, rows, inner, groups, group_size, s);
     } else {
         const int grid = grid_for((count + kThreads - 1) / kThreads, kPerSm);
         if (kind == VRB_Q_FP8_E4M3FN) dequant_scalar_kernel<VRB_Q_FP8_E4M3FN><<<grid, kThreads, 0, s>>>(p, scales, out, out_dtype, count, inner, groups, group_size);
