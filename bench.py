@@ -43,7 +43,7 @@ WORKLOAD = {
 }
 # DRAM bytes (read + write) of one launch of the dominant kernel, unary_lut_kernel<2> on
 # [32760, 8960] bf16, from the ncu capture summarised in profiles/gelu_tanh_lut_wan21.md
-DOMINANT_TRAFFIC_BYTES = None
+DOMINANT_TRAFFIC_BYTES = 1_125_900_000
 NOMINAL_HBM_GBS = 8000.0
 
 
@@ -67,7 +67,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -75,16 +75,20 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.monotonic(), line.strip()))
 
-    def stop(self):
+    def stop(self, begin=None, end=None):
+        """Summary of the samples taken between `begin` and `end` (time.monotonic() values of the
+        timed region); all samples if the window caught none."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
+        inside = [l for t, l in self.lines if begin is not None and begin <= t <= end + 0.03]
+        window = "timed region" if inside else "whole run"
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for line in (inside or [l for _, l in self.lines]):
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -96,7 +100,7 @@ class ClockSampler:
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "window": window, "reasons": sorted(reasons)}
 
 
 def cpu_arm(steps: int, warmup: int):
@@ -143,7 +147,7 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=2)
@@ -184,17 +188,18 @@ def main():
     launches = [l for blk in branches for l in blk.launches()]
     step_bytes = sum(l.bytes for l in launches)
     dominant = [l for l in launches if l.name.startswith("H ")]
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         for l in launches:
             l.fn()
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     launches_before = lib.vrb_launch_count()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     dom_events = []
     barrier()
+    wall_begin = time.monotonic()
     start.record()
     for _ in range(args.steps):
         for l in launches:
@@ -206,9 +211,10 @@ def main():
                 l.fn()
     stop.record()
     barrier()
+    wall_end = time.monotonic()
     total_ms = max_over_ranks(start.elapsed_time(stop))
     gpu_launches = lib.vrb_launch_count() - launches_before
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(wall_begin, wall_end) if rank == 0 else None
     ms_per_step = total_ms / args.steps
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
     dom_ms = statistics.mean(a.elapsed_time(b) for a, b in dom_events)
