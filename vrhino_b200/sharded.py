@@ -14,8 +14,8 @@ The shift that makes the one-pass variance safe must be the same on every rank: 
 element of each unit is broadcast (units floats) before the moments pass.
 
 ``MomentsBackend`` abstracts the three GroupNorm pieces so the choreography (what is reduced,
-in which order, with which shapes) is testable on CPU ranks with gloo, where the CPU oracle
-stands in for the kernels; on GPUs the pieces are the C-ABI entry points.
+in which order, with which shapes) is testable on CPU ranks with gloo, where the test supplies
+CPU stand-ins for the three kernels; on GPUs the pieces are the C-ABI entry points.
 """
 from __future__ import annotations
 
