@@ -250,6 +250,22 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
         if constexpr (PF) load_row(base + row_step, xn);   // next row, in flight during this one
         else load_row(base, xr);
 
+        // Gated residual with a bf16 residual: its row is requested now, so the loads are in
+        // flight during the statistics instead of stalling the epilogue chunk by chunk.
+        constexpr bool kEarlyResidual = POST == kPostGatedResidual && FULL && X_BF16 &&
+                                        min_ctas_per_sm(NCH, X_BF16, FULL) == 2;   // only where 128 registers are available
+        Packed<true> early_res[kEarlyResidual ? NCH : 1];
+        const bool early = kEarlyResidual && p.res_dt == VRB_BF16;
+        if constexpr (kEarlyResidual) {
+            if (early && valid) {
+#pragma unroll
+                for (int i = 0; i < NCH; ++i) {
+                    const int chunk = lane_in_row + i * tpr;
+                    if (FULL || chunk < nchunks) early_res[i] = load_packed<true>(p.residual, row_offset + chunk * 8);
+                }
+            }
+        }
+
         // ---- statistics: per-thread F32 partials (pairwise inside a chunk) ----
         // LayerNorm sums x - K and (x - K)^2 with K = the thread's first element, so the
         // partials stay small and accurate however large the row's common offset is; the exact
@@ -447,7 +463,8 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
                 for (int e = 0; e < 8; ++e) y[e] = r[e];
             } else if constexpr (POST == kPostGatedResidual) {
                 float res[8], g[8];
-                load8<true>(p.residual, p.res_dt, row_offset + c, res);
+                if (early) unpack<true>(early_res[i], res);
+                else load8<true>(p.residual, p.res_dt, row_offset + c, res);
                 const bool has_gate = p.gate != nullptr;
                 const int sd = p.state_dt;
                 round8_rt(sd, res);
