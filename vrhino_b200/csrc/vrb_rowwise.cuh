@@ -250,6 +250,35 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
         if constexpr (PF) load_row(base + row_step, xn);   // next row, in flight during this one
         else load_row(base, xr);
 
+        // ---- per-row operand offsets (32-bit arithmetic) ----
+        unsigned srow = nrow, col0 = 0;
+        if (p.sub32 > 1) { srow = nrow / p.sub32; col0 = (nrow - srow * p.sub32) * static_cast<unsigned>(width); }
+        int64_t vec_offset = col0;
+        if constexpr (POST == kPostModulate || POST == kPostScaleX || POST == kPostGatedResidual) {
+            if (p.vectors > 1) {
+                const unsigned vec = (srow / static_cast<unsigned>(p.rows_per_vector)) % static_cast<unsigned>(p.vectors);
+                vec_offset += static_cast<int64_t>(vec) * p.width;
+            }
+        }
+        int64_t f_offset = 0;
+        const unsigned f_width = static_cast<unsigned>(p.f_width);
+        float co[8], si[8];
+        if constexpr (kRope) {
+            unsigned frow = srow;
+            if (p.rows_per_f_row != 1) frow = srow / static_cast<unsigned>(p.rows_per_f_row);
+            if (frow >= static_cast<unsigned>(p.f_rows)) frow %= static_cast<unsigned>(p.f_rows);
+            f_offset = static_cast<int64_t>(frow) * p.f_width;
+            if constexpr (POST == kPostRopeShared) {
+                // every chunk of this thread reads the same table columns: load them once, and
+                // now, so that they arrive while the statistics are reduced
+                if (valid) {
+                    const unsigned fc = (static_cast<unsigned>(lane_in_row) * 8u) % f_width;
+                    load8<false>(p.cosine, p.f_dt, f_offset + fc, co);
+                    load8<false>(p.sine, p.f_dt, f_offset + fc, si);
+                }
+            }
+        }
+
         // Gated residual with a bf16 residual: its row is requested now, so the loads are in
         // flight during the statistics instead of stalling the epilogue chunk by chunk.
         constexpr bool kEarlyResidual = POST == kPostGatedResidual && FULL && X_BF16 &&
@@ -339,32 +368,6 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
             inv = rsqrtf(static_cast<float>(acc1 * p.inv_width) + p.eps);
         }
         if (valid) {
-        // ---- per-row operand offsets (32-bit arithmetic) ----
-        unsigned srow = nrow, col0 = 0;
-        if (p.sub32 > 1) { srow = nrow / p.sub32; col0 = (nrow - srow * p.sub32) * static_cast<unsigned>(width); }
-        int64_t vec_offset = col0;
-        if constexpr (POST == kPostModulate || POST == kPostScaleX || POST == kPostGatedResidual) {
-            if (p.vectors > 1) {
-                const unsigned vec = (srow / static_cast<unsigned>(p.rows_per_vector)) % static_cast<unsigned>(p.vectors);
-                vec_offset += static_cast<int64_t>(vec) * p.width;
-            }
-        }
-        int64_t f_offset = 0;
-        const unsigned f_width = static_cast<unsigned>(p.f_width);
-        float co[8], si[8];
-        if constexpr (kRope) {
-            unsigned frow = srow;
-            if (p.rows_per_f_row != 1) frow = srow / static_cast<unsigned>(p.rows_per_f_row);
-            if (frow >= static_cast<unsigned>(p.f_rows)) frow %= static_cast<unsigned>(p.f_rows);
-            f_offset = static_cast<int64_t>(frow) * p.f_width;
-            if constexpr (POST == kPostRopeShared) {
-                // every chunk of this thread reads the same table columns: load them once
-                const unsigned fc = (static_cast<unsigned>(lane_in_row) * 8u) % f_width;
-                load8<false>(p.cosine, p.f_dt, f_offset + fc, co);
-                load8<false>(p.sine, p.f_dt, f_offset + fc, si);
-            }
-        }
-
         // ---- normalise, post-process, store ----
 #pragma unroll
         for (int i = 0; i < NCH; ++i) {
