@@ -270,6 +270,26 @@ def main():
         strong_ms = max_over_ranks(s0.elapsed_time(s1)) / args.steps
         strong = {"us_per_dit_block": strong_ms * 1e3, "tokens_per_rank": tokens,
                   "value": world * sum(l.bytes for l in sl) / (strong_ms * 1e-3) / 1e9, "unit": UNIT}
+        try:   # small per-rank kernels are launch-bound: the same sharded step from a CUDA graph
+            side = torch.cuda.Stream()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side):
+                    for l in sl:
+                        l.fn()
+            for _ in range(3):
+                g.replay()
+            barrier()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record()
+            for _ in range(args.steps):
+                g.replay()
+            g1.record()
+            barrier()
+            strong["us_per_dit_block_cuda_graph"] = max_over_ranks(g0.elapsed_time(g1)) / args.steps * 1e3
+            del g
+        except Exception as exc:
+            strong["cuda_graph_error"] = str(exc)[:200]
         del shard, sl
         torch.cuda.empty_cache()
         branches = [workloads.WanBlock(be, seed=1000 * rank)]
