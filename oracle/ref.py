@@ -207,6 +207,20 @@ class RefCuda:
         return self._h(self.lib.refc_euler_update(int(policy), self._i(x), self._i(pred), _c.c_float(delta), int(subtract)))
     def flow_to_x0(self, policy, x, out, sigma): return self._h(self.lib.refc_flow_to_x0(int(policy), self._i(x), self._i(out), _c.c_float(sigma)))
 
+    def wan_chain_graph(self, tokens, width, heads, hidden_dtype, eps, handles, fused=False):
+        """Evaluates the non-GEMM part of the Wan self-attention graph (built node for node in
+        ref_cuda.cpp) through neural_graph::evaluate, or -- drop-in build, fused=True -- through
+        vrhino_b200::evaluate_fused.  handles: hidden, modulation, cos, sin, q, k, projection,
+        table, norm_q, norm_k.  Returns ([attention input, q operand, k operand, residual], stats)."""
+        h = (_c.c_int64 * 10)(*handles)
+        out = (_c.c_int64 * 4)()
+        stats = (_c.c_int * 5)()
+        rc = self.lib.refc_wan_chain_graph(_c.c_int64(tokens), _c.c_int64(width), _c.c_int64(heads), int(hidden_dtype),
+                                           _c.c_float(eps), h, int(fused), out, stats)
+        if rc != 0:
+            raise RuntimeError(self.lib.refc_last_error().decode())
+        return list(out), list(stats)
+
 
 class RefDropin(RefCuda):
     """The same call surface over vrhino_b200::B200Backend (this repository's C++ host layer and

@@ -25,8 +25,10 @@
 #include "vrhino/precision.h"
 #include "vrhino/sampling.h"
 #include "vrhino/tensor_util.h"
+#include "runtime/neural_graph.h"
 #ifdef VRB_DROPIN
 #include "b200_backend.h"
+#include "graph_fusion.h"
 #endif
 
 using namespace vrhino;
@@ -241,6 +243,85 @@ int refd_session_terminal() { return g_backend && g_backend->resource_session_te
 #else
 const char* refc_backend_name() { static std::string n; n = g_backend ? g_backend->name() : ""; return n.c_str(); }
 #endif
+
+// ---- executable graphs (native/src/runtime/neural_graph.h) ------------------------------------
+// The non-GEMM part of the Wan self-attention graph (native/src/architectures/
+// wan_self_attention_graph.h:46-70), node for node, with the GEMM / attention results (q, k and
+// the attention projection) supplied as inputs: modulation table + input -> slices; LayerNorm ->
+// [Cast] -> Mul(1 + scale) -> Add(shift) -> Cast; RmsNorm -> Reshape -> Rope -> Cast for q and k;
+// Cast -> Mul(gate) -> Add(residual).  Outputs: attention input, q, k operands, first residual.
+namespace {
+neural_graph::Graph wan_chain_graph(int64_t s, int64_t width, int64_t heads_count, DType execution, DType hidden_dtype, float eps) {
+    namespace ng = neural_graph;
+    const int64_t b = 1, head_width = width / heads_count;
+    const std::vector<int64_t> hidden{b, s, width}, part{b, 1, width}, heads{b, s, heads_count, head_width};
+    ng::Description d;
+    d.schema = ng::schema_v1;
+    d.execution_dtype = execution;
+    // 0 hidden, 1 modulation, 2 cos, 3 sin, 4 q, 5 k, 6 projection | 7 table, 8 norm_q, 9 norm_k | 10 one
+    d.values = {{hidden, hidden_dtype}, {{b, 6, width}}, {{1, s, 1, head_width}}, {{1, s, 1, head_width}},
+                {hidden, execution}, {hidden, execution}, {hidden, execution},
+                {{1, 6, width}}, {{width}}, {{width}}, {{1}}};
+    d.inputs = {0, 1, 2, 3, 4, 5, 6};
+    d.parameters = {7, 8, 9};
+    d.constants = {{10, 1.0f}};
+    auto node = [&](ng::Primitive op, const std::vector<int64_t>& shape, DType dtype = DType::F32) {
+        auto id = static_cast<ng::ValueId>(d.values.size());
+        d.values.push_back({shape, dtype});
+        d.nodes.push_back({id, std::move(op)});
+        return id;
+    };
+    auto cast = [&](ng::ValueId x, DType dtype) { return d.values[x].dtype == dtype ? x : node(ng::Cast{x, dtype}, d.values[x].shape, dtype); };
+    auto combined = node(ng::Add{7, 1}, {b, 6, width});
+    auto shift = node(ng::Slice{combined, 1, 0, 1}, part);
+    auto scale = node(ng::Slice{combined, 1, 1, 2}, part);
+    auto gate = node(ng::Slice{combined, 1, 2, 3}, part);
+    auto norm = node(ng::LayerNorm{0, {}, {}, eps}, hidden, hidden_dtype);
+    auto scale_one = node(ng::Add{10, scale}, part);
+    auto scaled = node(ng::Mul{cast(norm, DType::F32), scale_one}, hidden);
+    auto self_input = node(ng::Add{scaled, shift}, hidden);
+    auto operand = cast(self_input, execution);
+    auto q_norm = node(ng::RmsNorm{4, 8, 2, eps}, hidden);
+    auto k_norm = node(ng::RmsNorm{5, 9, 2, eps}, hidden);
+    auto q_heads = node(ng::Reshape{q_norm, heads}, heads);
+    auto k_heads = node(ng::Reshape{k_norm, heads}, heads);
+    auto q_rope = node(ng::Rope{q_heads, 2, 3}, heads);
+    auto k_rope = node(ng::Rope{k_heads, 2, 3}, heads);
+    auto q_operand = cast(q_rope, execution), k_operand = cast(k_rope, execution);
+    auto gated = node(ng::Mul{cast(6, DType::F32), gate}, hidden);
+    auto residual = node(ng::Add{cast(0, DType::F32), gated}, hidden);
+    d.outputs = {operand, q_operand, k_operand, residual};
+    return ng::admit(d);
+}
+}  // namespace
+
+// handles: hidden, modulation, cos, sin, q, k, projection, table, norm_q, norm_k (10); out: 4 handles.
+// fused != 0 (drop-in build only) runs vrhino_b200::evaluate_fused; stats (may be null) receives
+// {layer_norm_modulate, rms_norm_rope, gated_residual, nodes_total, nodes_absorbed}.
+int refc_wan_chain_graph(int64_t s, int64_t width, int64_t heads, int hidden_dtype, float eps, const int64_t* handles,
+                         int fused, int64_t* out, int* stats) {
+    return static_cast<int>(guarded([&] {
+        const auto graph = wan_chain_graph(s, width, heads, g_backend->execution_dtype(), static_cast<DType>(hidden_dtype), eps);
+        std::vector<Tensor> inputs, parameters;
+        for (int i = 0; i < 7; ++i) inputs.push_back(at(handles[i]));
+        for (int i = 7; i < 10; ++i) parameters.push_back(at(handles[i]));
+        std::vector<Tensor> results;
+        if (fused) {
+#ifdef VRB_DROPIN
+            vrhino_b200::FusionStats fs;
+            results = vrhino_b200::evaluate_fused(*g_backend, graph, inputs, parameters, &fs);
+            if (stats) { stats[0] = fs.layer_norm_modulate; stats[1] = fs.rms_norm_rope; stats[2] = fs.gated_residual;
+                         stats[3] = fs.nodes_total; stats[4] = fs.nodes_absorbed; }
+#else
+            throw Error("the fused evaluator exists only in the drop-in build");
+#endif
+        } else {
+            results = neural_graph::evaluate(*g_backend, graph, inputs, parameters);
+        }
+        for (size_t i = 0; i < results.size(); ++i) out[i] = keep(results[i]);
+        return int64_t{0};
+    }));
+}
 
 // ---- timing through the reference's own profiler ---------------------------------------------
 void refc_profile(int enabled) { if (g_backend) g_backend->enable_profiling(enabled != 0); }

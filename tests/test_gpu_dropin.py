@@ -105,6 +105,57 @@ def test_fused_call_site_forms(orc, golden, dropin, case):
         rd.clear()
 
 
+@pytest.mark.parametrize("hidden", ["bf16", "f32"])
+def test_graph_fusion_pass(orc, dropin, hidden):
+    """The non-GEMM part of the Wan self-attention graph (the reference's node sequence, q / k / the
+    attention projection supplied as inputs) evaluated three ways: the reference's evaluator on
+    the reference's CUDA backend; the reference's evaluator on the replaced backend (node by
+    node); vrhino_b200::evaluate_fused, which must find 1 LayerNorm-modulate, 2 RMSNorm-RoPE and
+    1 gated-residual chain and launch nothing for the nodes inside them."""
+    from oracle import ref
+    from vrhino_b200 import synth
+    if not ref.available_cuda():
+        pytest.skip("reference CUDA library not built")
+    S, W, H, d = 600, 1536, 12, 128
+    hd = ref.BF16 if hidden == "bf16" else ref.F32
+    n = lambda shape, st, mean=0.0, std=1.0: synth.normal(shape, mean, std, seed=77, stream=st)
+    cos, sin = synth.wan_rope_tables(2, 15, 20, head_dim=d)
+    host = {
+        "hidden": (n((1, S, W), 0), hidden), "modulation": (n((1, 6, W), 1, 0, 0.1), "f32"),
+        "cos": (cos.reshape(1, S, 1, d), "f32"), "sin": (sin.reshape(1, S, 1, d), "f32"),
+        "q": (n((1, S, W), 2), "bf16"), "k": (n((1, S, W), 3), "bf16"), "proj": (n((1, S, W), 4), "bf16"),
+        "table": (n((1, 6, W), 5, 0, 0.1), "f32"), "norm_q": (n((W,), 6, 1.0, 0.1), "f32"), "norm_k": (n((W,), 7, 1.0, 0.1), "f32"),
+    }
+    order = ["hidden", "modulation", "cos", "sin", "q", "k", "proj", "table", "norm_q", "norm_k"]
+    code = {"f32": ref.F32, "bf16": ref.BF16}
+    shapes = [(1, S, W), (1, S, H, d), (1, S, H, d), (1, S, W)]
+
+    def run(backend, fused):
+        handles = [backend.upload(cases.to_bits(host[k][0], host[k][1]), code[host[k][1]]) for k in order]
+        outs, stats = backend.wan_chain_graph(S, W, H, hd, 1e-6, handles, fused=fused)
+        got = [backend.download(o, shape) for o, shape in zip(outs, shapes)]
+        backend.clear()
+        return got, stats
+
+    rc = ref.RefCuda()
+    want, _ = run(rc, False)
+    node_by_node, _ = run(dropin, False)
+    fused, stats = run(dropin, True)
+    assert stats[:3] == [1, 2, 1], stats
+    assert stats[4] >= 9, stats            # LN, (cast), mul, add, 1+scale; 2 x (rms, reshape, rope); casts, mul
+    for got in (node_by_node, fused):
+        for (g, gdt), (w, wdt), name in zip(got, want, ("attention input", "q operand", "k operand", "residual")):
+            assert gdt == wdt and g.shape == w.shape, name
+            if name == "residual":         # exact casts, one F32 multiply, one F32 add
+                assert np.array_equal(g.view(np.uint32), w.view(np.uint32)), name
+                continue
+            dist = orc.bf16_ulp_distance(g, w)
+            bad = dist > 2
+            if bad.any():                   # RoPE cancellation: see test_golden.compare
+                diff = np.abs(orc.bf16_bits_to_f32(g).astype(np.float64) - orc.bf16_bits_to_f32(w).astype(np.float64))
+                assert name != "attention input" and bad.mean() <= 2e-3 and (diff[bad] <= 2.0 ** -8 * 8.0).all(), (name, int(bad.sum()))
+
+
 def test_errors_and_session_semantics(dropin):
     """Same texts as the reference's wrappers; a rejected argument in an unguarded operator
     (layer_norm) leaves the session usable, one in a guarded operator (clamp) retires it, after
