@@ -207,6 +207,18 @@ class RefCuda:
         return self._h(self.lib.refc_euler_update(int(policy), self._i(x), self._i(pred), _c.c_float(delta), int(subtract)))
     def flow_to_x0(self, policy, x, out, sigma): return self._h(self.lib.refc_flow_to_x0(int(policy), self._i(x), self._i(out), _c.c_float(sigma)))
 
+    def wan_self_attention_graph(self, tokens, width, heads, handles, fused=False):
+        """The reference's production Wan self-attention graph (GEMMs and attention included).
+        handles: hidden, modulation, cos, sin + the 11 canonical parameters.  Returns
+        ([first residual, combined modulation], stats)."""
+        h = (_c.c_int64 * 15)(*handles)
+        out = (_c.c_int64 * 2)()
+        stats = (_c.c_int * 5)()
+        rc = self.lib.refc_wan_self_attention_graph(_c.c_int64(tokens), _c.c_int64(width), _c.c_int64(heads), h, int(fused), out, stats)
+        if rc != 0:
+            raise RuntimeError(self.lib.refc_last_error().decode())
+        return list(out), list(stats)
+
     def wan_chain_graph(self, tokens, width, heads, hidden_dtype, eps, handles, fused=False):
         """Evaluates the non-GEMM part of the Wan self-attention graph (built node for node in
         ref_cuda.cpp) through neural_graph::evaluate, or -- drop-in build, fused=True -- through

@@ -26,6 +26,7 @@
 #include "vrhino/sampling.h"
 #include "vrhino/tensor_util.h"
 #include "runtime/neural_graph.h"
+#include "architectures/wan_self_attention_graph.h"
 #ifdef VRB_DROPIN
 #include "b200_backend.h"
 #include "graph_fusion.h"
@@ -305,6 +306,38 @@ int refc_wan_chain_graph(int64_t s, int64_t width, int64_t heads, int hidden_dty
         std::vector<Tensor> inputs, parameters;
         for (int i = 0; i < 7; ++i) inputs.push_back(at(handles[i]));
         for (int i = 7; i < 10; ++i) parameters.push_back(at(handles[i]));
+        std::vector<Tensor> results;
+        if (fused) {
+#ifdef VRB_DROPIN
+            vrhino_b200::FusionStats fs;
+            results = vrhino_b200::evaluate_fused(*g_backend, graph, inputs, parameters, &fs);
+            if (stats) { stats[0] = fs.layer_norm_modulate; stats[1] = fs.rms_norm_rope; stats[2] = fs.gated_residual;
+                         stats[3] = fs.nodes_total; stats[4] = fs.nodes_absorbed; }
+#else
+            throw Error("the fused evaluator exists only in the drop-in build");
+#endif
+        } else {
+            results = neural_graph::evaluate(*g_backend, graph, inputs, parameters);
+        }
+        for (size_t i = 0; i < results.size(); ++i) out[i] = keep(results[i]);
+        return int64_t{0};
+    }));
+}
+
+// The reference's production Wan self-attention graph itself (wan_self_attention_graph.h:22-72),
+// GEMMs and attention included.  handles: hidden, modulation, cos, sin, then the 11 parameters in
+// the header's canonical order, already on the device in the dtypes the graph declares.
+// out: {first residual, combined modulation}.
+int refc_wan_self_attention_graph(int64_t s, int64_t width, int64_t heads, const int64_t* handles, int fused, int64_t* out,
+                                  int* stats) {
+    return static_cast<int>(guarded([&] {
+        wan_family::Config config;
+        config.dim = width; config.heads = heads;
+        const Tensor& hidden = at(handles[0]);
+        const auto graph = wan_internal::self_attention_graph(1, s, g_backend->execution_dtype(), hidden.dtype(), false, config);
+        std::vector<Tensor> inputs, parameters;
+        for (int i = 0; i < 4; ++i) inputs.push_back(at(handles[i]));
+        for (int i = 4; i < 15; ++i) parameters.push_back(at(handles[i]));
         std::vector<Tensor> results;
         if (fused) {
 #ifdef VRB_DROPIN

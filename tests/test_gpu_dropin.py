@@ -156,6 +156,50 @@ def test_graph_fusion_pass(orc, dropin, hidden):
                 assert name != "attention input" and bad.mean() <= 2e-3 and (diff[bad] <= 2.0 ** -8 * 8.0).all(), (name, int(bad.sum()))
 
 
+def test_production_wan_graph_with_fusion(orc, dropin):
+    """The reference's production Wan self-attention graph itself
+    (native/src/architectures/wan_self_attention_graph.h), GEMMs and attention included, on a small
+    configuration (256 wide, 2 heads, 128 tokens): the reference's evaluator on its CUDA backend
+    against evaluate_fused on the replaced backend.  GEMM and attention run in the reference's own
+    code on both sides; the fused chains may flip single bf16 roundings of their operands, so the
+    F32 residual is compared statistically (mean |d| <= 2e-3, max |d| <= 5e-2 on O(1) values)."""
+    from oracle import ref
+    from vrhino_b200 import synth
+    if not ref.available_cuda():
+        pytest.skip("reference CUDA library not built")
+    S, W, H = 128, 256, 2
+    d = W // H
+    n = lambda shape, st, mean=0.0, std=1.0: synth.normal(shape, mean, std, seed=91, stream=st)
+    cos, sin = synth.wan_rope_tables(2, 8, 8, head_dim=d)
+    lin = 1.0 / np.sqrt(W)
+    host = [
+        (n((1, S, W), 0), "bf16"), (n((1, 6, W), 1, 0, 0.1), "f32"), (cos.reshape(1, S, 1, d), "f32"), (sin.reshape(1, S, 1, d), "f32"),
+        (n((1, 6, W), 2, 0, 0.1), "f32"),
+        (n((W, W), 3, 0, lin), "bf16"), (n((W,), 4, 0, 0.02), "bf16"), (n((W, W), 5, 0, lin), "bf16"), (n((W,), 6, 0, 0.02), "bf16"),
+        (n((W, W), 7, 0, lin), "bf16"), (n((W,), 8, 0, 0.02), "bf16"),
+        (n((W,), 9, 1.0, 0.1), "f32"), (n((W,), 10, 1.0, 0.1), "f32"),
+        (n((W, W), 11, 0, lin), "bf16"), (n((W,), 12, 0, 0.02), "bf16"),
+    ]
+    code = {"f32": ref.F32, "bf16": ref.BF16}
+
+    def run(backend, fused):
+        handles = [backend.upload(cases.to_bits(a, dt), code[dt]) for a, dt in host]
+        outs, stats = backend.wan_self_attention_graph(S, W, H, handles, fused=fused)
+        residual, _ = backend.download(outs[0], (1, S, W))
+        combined, _ = backend.download(outs[1], (1, 6, W))
+        backend.clear()
+        return residual, combined, stats
+
+    rc = ref.RefCuda()
+    want, want_combined, _ = run(rc, False)
+    got, got_combined, stats = run(dropin, True)
+    assert stats[:3] == [1, 2, 1], stats
+    assert np.array_equal(got_combined.view(np.uint32), want_combined.view(np.uint32))
+    assert np.isfinite(want).all() and np.abs(want).max() > 0.5
+    diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert diff.mean() <= 2e-3 and diff.max() <= 5e-2, (float(diff.mean()), float(diff.max()))
+
+
 def test_errors_and_session_semantics(dropin):
     """Same texts as the reference's wrappers; a rejected argument in an unguarded operator
     (layer_norm) leaves the session usable, one in a guarded operator (clamp) retires it, after
