@@ -38,12 +38,14 @@ METRIC = "fused-op HBM GB/s (Wan2.1-1.3B DiT-block non-GEMM chain)"
 UNIT = "GB/s"
 WORKLOAD = {
     "workload": "wan2.1-1.3b dit block non-gemm chain, batch 2 (cfg)", "tokens": 32760, "dim": 1536, "heads": 12,
-    "head_dim": 128, "ffn": 8960, "hidden_dtype": "bf16", "launches_per_step": 22,
+    "head_dim": 128, "ffn": 8960, "hidden_dtype": "bf16", "launches_per_step": 11,
+    "batching": "both CFG branches as one [2, 32760, 1536] batch, one modulation vector set per branch",
     "l2": "every launch streams 0.2-1.2 GB of distinct tensors (> 126 MB L2), no flush needed",
 }
 # DRAM bytes (read + write) of one launch of the dominant kernel, unary_lut_kernel<2> on
-# [32760, 8960] bf16, from the ncu capture summarised in profiles/gelu_tanh_lut_wan21.md
-DOMINANT_TRAFFIC_BYTES = 1_125_900_000
+# [2, 32760, 8960] bf16: twice the figure the ncu capture of one [32760, 8960] branch gives
+# (profiles/gelu_tanh_lut_wan21.md); the kernel streams, so its traffic grows with the element count
+DOMINANT_TRAFFIC_BYTES = 2 * 1_125_900_000
 NOMINAL_HBM_GBS = 8000.0
 
 
@@ -184,7 +186,7 @@ def main():
         return float(t.item())
 
     # ---- resident arm: both CFG branches of one block -------------------------------------------
-    branches = [workloads.WanBlock(be, seed=1000 * rank + b) for b in range(2)]
+    branches = [workloads.WanBlock(be, seed=1000 * rank, batch=2)]
     launches = [l for blk in branches for l in blk.launches()]
     step_bytes = sum(l.bytes for l in launches)
     dominant = [l for l in launches if l.name.startswith("H ")]
@@ -252,9 +254,7 @@ def main():
     strong = None
     if world > 1:
         tokens = 32760 // world
-        del branches, launches
-        torch.cuda.empty_cache()
-        shard = [workloads.WanBlock(be, tokens=tokens, grid=(1, 1, tokens), seed=7 + b) for b in range(2)]
+        shard = [workloads.WanBlock(be, tokens=tokens, grid=(1, 1, tokens), seed=7, batch=2)]
         sl = [l for blk in shard for l in blk.launches()]
         for _ in range(args.warmup):
             for l in sl:
@@ -292,7 +292,9 @@ def main():
             strong["cuda_graph_error"] = str(exc)[:200]
         del shard, sl
         torch.cuda.empty_cache()
-        branches = [workloads.WanBlock(be, seed=1000 * rank)]
+    del branches, launches
+    torch.cuda.empty_cache()
+    branches = [workloads.WanBlock(be, seed=1000 * rank)]
     # ---- end-to-end arm: host buffers through the C ABI ------------------------------------------
     e2e = workloads.WanBlockHost(branches[0])
     e2e.step()   # first call sizes the staging buffers
@@ -321,7 +323,7 @@ def main():
             "us_per_dit_block": ms_per_step * 1e3,
             "pct_of_nominal_8tbs": 100.0 * value / world / NOMINAL_HBM_GBS,
             "pct_of_measured_copy_peak": 100.0 * value / world / peak,
-            "roofline": {"bound": "hbm", "kernel": "unary_lut_kernel<gelu_tanh> on [32760, 8960] bf16", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": "unary_lut_kernel<gelu_tanh> on [2, 32760, 8960] bf16", "achieved": achieved,
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": DOMINANT_TRAFFIC_BYTES, "algorithmic_bytes": dom_bytes, "ms_per_launch": dom_ms},
             "e2e": e2e_obj, "gpu_launches": int(gpu_launches), "clocks": clocks,

@@ -121,7 +121,8 @@ def test_rms_norm_axis(orc, gpu, dtype, shape, axis):
 # ------------------------------------------------------------------------------ fused chains --
 @pytest.mark.parametrize("x_dt", DTYPES)
 @pytest.mark.parametrize("out_dt", DTYPES)
-@pytest.mark.parametrize("width,batch,per_token", [(1536, 1, False), (1536, 2, False), (64, 2, True), (17, 1, False), (5120, 1, False)])
+@pytest.mark.parametrize("width,batch,per_token", [(1536, 1, False), (1536, 2, False), (1536, 3, False), (1536, 4, False), (1536, 5, False),
+                                                    (64, 2, True), (17, 1, False), (5120, 1, False), (5120, 2, False)])
 def test_layer_norm_modulate(orc, gpu, x_dt, out_dt, width, batch, per_token):
     """Config-1 chain: layer_norm(no affine) -> modulate -> consumer cast, vs the same chain of
     per-operator kernels and vs the oracle."""

@@ -182,12 +182,13 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
     size_t smem = 0;
     int post = p.post;
     const size_t region = static_cast<size_t>(geometry <= 6 ? nch : (chunks / tpr)) * tpr * 8 * sizeof(float);
-    // One modulation vector for all rows and small enough for the default shared-memory limit:
-    // stage 1+scale and shift per CTA instead of re-reading them for every row.
+    // Up to four modulation vectors (one per batch entry) that fit the default shared-memory
+    // limit: stage 1+scale and shift per CTA instead of re-reading them for every row.
     const size_t budget = 46 * 1024;
-    if (post == kPostModulate && p.vectors == 1 && sub == 1 && 2 * region <= budget) {
+    if (post == kPostModulate && p.vectors >= 1 && p.vectors <= 4 && sub == 1 &&
+        static_cast<size_t>(p.vectors) * 2 * region <= budget) {
         post = kPostModulateStaged;
-        smem += 2 * region;
+        smem += static_cast<size_t>(p.vectors) * 2 * region;
     }
     // LayerNorm weight and bias both present: stage them per CTA, already converted to x's dtype.
     // (Staging the RMSNorm weight the same way was measured and does not pay: its 16-byte loads

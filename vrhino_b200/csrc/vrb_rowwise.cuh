@@ -211,14 +211,17 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
         if constexpr (!kStaged) __syncthreads();
     }
     if constexpr (kStaged) {
-        // one modulation vector for every row: keep 1+scale and shift in shared memory
+        // a few modulation vectors (one per batch entry): keep 1+scale and shift in shared memory,
+        // vector v at s_mod + v * 2 * pad
         // layout: for chunk (l + i*tpr) the two float4 halves sit at float4 index (2i + half)*tpr + l,
         // so the lanes of a warp read consecutive 16-byte words (no bank conflicts)
-        for (int c = threadIdx.x; c < width; c += kRowThreads) {
+        const int staged_vectors = static_cast<int>(p.vectors);
+        for (int cv = threadIdx.x; cv < width * staged_vectors; cv += kRowThreads) {
+            const int v = cv / width, c = cv - v * width;
             const int chunk = c >> 3, e = c & 7, i = chunk / tpr, l = chunk - i * tpr;
-            const int pos = (((i * 2 + (e >> 2)) * tpr + l) << 2) + (e & 3);
-            s_mod[pos] = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, c));
-            s_mod[pad + pos] = has_shift ? load1(p.shift, p.mod_dt, c) : 0.0f;
+            const int pos = v * 2 * pad + (((i * 2 + (e >> 2)) * tpr + l) << 2) + (e & 3);
+            s_mod[pos] = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, static_cast<int64_t>(v) * p.width + c));
+            s_mod[pad + pos] = has_shift ? load1(p.shift, p.mod_dt, static_cast<int64_t>(v) * p.width + c) : 0.0f;
         }
         __syncthreads();
     }
@@ -254,6 +257,11 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
         unsigned srow = nrow, col0 = 0;
         if (p.sub32 > 1) { srow = nrow / p.sub32; col0 = (nrow - srow * p.sub32) * static_cast<unsigned>(width); }
         int64_t vec_offset = col0;
+        int staged_base = 0;   // staged modulate: float offset of this row's vector pair in s_mod
+        if constexpr (kStaged) {
+            if (p.vectors > 1)
+                staged_base = static_cast<int>((srow / static_cast<unsigned>(p.rows_per_vector)) % static_cast<unsigned>(p.vectors)) * 2 * pad;
+        }
         if constexpr (POST == kPostModulate || POST == kPostScaleX || POST == kPostGatedResidual) {
             if (p.vectors > 1) {
                 const unsigned vec = (srow / static_cast<unsigned>(p.rows_per_vector)) % static_cast<unsigned>(p.vectors);
@@ -425,8 +433,8 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
                 // common.cpp:51-61: 1+scale, product, +shift are three separately rounded F32 steps
                 float t1[8], sh[8];
                 if constexpr (kStaged) {
-                    const float4* a = reinterpret_cast<const float4*>(s_mod) + (i * 2 * tpr + lane_in_row);
-                    const float4* b = reinterpret_cast<const float4*>(s_mod + pad) + (i * 2 * tpr + lane_in_row);
+                    const float4* a = reinterpret_cast<const float4*>(s_mod + staged_base) + (i * 2 * tpr + lane_in_row);
+                    const float4* b = reinterpret_cast<const float4*>(s_mod + staged_base + pad) + (i * 2 * tpr + lane_in_row);
                     const float4 a0 = a[0], a1 = a[tpr], b0 = b[0], b1 = b[tpr];
                     t1[0] = a0.x; t1[1] = a0.y; t1[2] = a0.z; t1[3] = a0.w; t1[4] = a1.x; t1[5] = a1.y; t1[6] = a1.z; t1[7] = a1.w;
                     sh[0] = b0.x; sh[1] = b0.y; sh[2] = b0.z; sh[3] = b0.w; sh[4] = b1.x; sh[5] = b1.y; sh[6] = b1.z; sh[7] = b1.w;

@@ -48,18 +48,20 @@ class WanBlock:
     """
 
     def __init__(self, be, tokens=32760, dim=1536, heads=12, ffn=8960, grid=(21, 30, 52), text_tokens=512,
-                 hidden_dtype=BF16, seed=0):
+                 hidden_dtype=BF16, seed=0, batch=1):
+        """batch > 1: the CFG branches as one batched tensor [batch, S, D] with one modulation
+        vector set per batch entry (the RoPE tables are shared by the batch)."""
         assert grid[0] * grid[1] * grid[2] == tokens
         g = torch.Generator(device="cuda").manual_seed(seed)
-        self.be, S, D = be, tokens, dim
+        self.be, S, D, B = be, tokens, dim, batch
         self.policy = ops.Policy(BF16, hidden_dtype)
         hd = hidden_dtype
-        self.x = _randn((1, S, D), hd, g)
-        self.mod = _randn((1, 6, D), F32, g, std=0.1)                 # combined modulation rows
+        self.x = _randn((B, S, D), hd, g)
+        self.mod = _randn((B, 6, D), F32, g, std=0.1)                 # combined modulation rows
         self.rows = [self.mod[:, i:i + 1, :].contiguous() for i in range(6)]
-        self.q, self.k, self.proj, self.cross_q, self.cross, self.ffn_out = (_randn((1, S, D), BF16, g) for _ in range(6))
-        self.cross_k = _randn((1, text_tokens, D), BF16, g)
-        self.ffn_hidden = _randn((1, S, ffn), BF16, g)
+        self.q, self.k, self.proj, self.cross_q, self.cross, self.ffn_out = (_randn((B, S, D), BF16, g) for _ in range(6))
+        self.cross_k = _randn((B, text_tokens, D), BF16, g)
+        self.ffn_hidden = _randn((B, S, ffn), BF16, g)
         self.wq, self.wk, self.wcq, self.wck, self.gamma3 = (_randn((D,), F32, g, 1.0, 0.1) for _ in range(5))
         self.beta3 = _randn((D,), F32, g, 0.0, 0.1)
         cos, sin = synth.wan_rope_tables(*grid, head_dim=dim // heads)
@@ -69,10 +71,10 @@ class WanBlock:
 
     def launches(self) -> List[Launch]:
         be, p, r, e, o = self.be, self.policy, self.rows, self.eps, self.out
-        S, D = self.x.shape[1], self.x.shape[2]
-        act = S * D
+        B, S, D = self.x.shape
+        act = B * S * D
         hb = self.x.element_size()
-        vec = D * 4
+        vec = B * D * 4
 
         def A(): o["A"] = ops.fused_layer_norm_modulate(be, self.x, None, None, e, r[0], r[1], out=o.get("A"))
         def Bq(): o["Bq"] = ops.fused_rms_norm_rope(be, self.q, self.wq, e, self.cos, self.sin, heads=self.heads, out=o.get("Bq"))
@@ -223,11 +225,11 @@ class VaeGroupNorm:
         return [Launch("group_norm_silu", gn, self.x.numel() * 6, kernels=4)]
 
 
-def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None):
+def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, batch=1):
     """The launch list of headline configuration 2..5 (optionally at a reduced token / frame count)."""
     if config == 2:
         t = tokens or 32760
-        return WanBlock(be, tokens=t, grid=(21, 30, 52) if t == 32760 else (1, 1, t), hidden_dtype=hidden_dtype)
+        return WanBlock(be, tokens=t, grid=(21, 30, 52) if t == 32760 else (1, 1, t), hidden_dtype=hidden_dtype, batch=batch)
     if config == 3:
         return Wan22Step(be, tokens=tokens or 32760)
     if config == 4:
@@ -253,9 +255,11 @@ def _main():
     ap.add_argument("--only", default="")
     ap.add_argument("--repeat", type=int, default=3)
     ap.add_argument("--hidden", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--batch", type=int, default=1, help="config 2: CFG branches batched into one tensor")
     a = ap.parse_args()
     be = ops.B200Backend()
-    work = build_config(be, a.config, tokens=a.tokens, hidden_dtype=BF16 if a.hidden == "bf16" else F32, frames=a.frames)
+    work = build_config(be, a.config, tokens=a.tokens, hidden_dtype=BF16 if a.hidden == "bf16" else F32, frames=a.frames,
+                        batch=a.batch)
     launches = [l for l in work.launches() if l.name.startswith(a.only)]
     total, per = time_launches(launches, steps=a.repeat, warmup=1)
     for l in launches:
