@@ -110,6 +110,18 @@ int vrb_group_norm(const void* x, int dtype, const void* weight, int weight_dtyp
                    int64_t batch, int64_t channels, int64_t spatial, int groups, float eps,
                    int fuse_silu, void* workspace, size_t workspace_bytes, vrb_stream stream);
 
+/* Per-frame GroupNorm of a video feature map without the two permutes: x and out are
+ * [batch, channels, frames, spatial]; statistics per (batch entry, frame, group), i.e. what
+ * frame_group_norm (native/src/architectures/mochi.cpp:365-371) computes by permuting to
+ * [batch*frames, channels, spatial], calling group_norm and permuting back.  Needs spatial % 8 == 0,
+ * 16-byte aligned tensors and channels/groups <= 64 (VRB_ERR_UNSUPPORTED otherwise: permute and
+ * call vrb_group_norm).  workspace: vrb_group_norm_frames_workspace_bytes() bytes, 256-byte aligned. */
+size_t vrb_group_norm_frames_workspace_bytes(int64_t batch, int64_t frames, int groups);
+int vrb_group_norm_frames(const void* x, int dtype, const void* weight, int weight_dtype,
+                          const void* bias, int bias_dtype, void* out,
+                          int64_t batch, int64_t channels, int64_t frames, int64_t spatial, int groups,
+                          float eps, int fuse_silu, void* workspace, size_t workspace_bytes, vrb_stream stream);
+
 /* vrb_group_norm without a caller-provided workspace.  This entry point has no counterpart in
  * the reference (whose operators take scratch from the backend's own temporary pool); it exists
  * for callers that cannot hand over device scratch: a backend whose device budget is entirely

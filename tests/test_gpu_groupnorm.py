@@ -115,3 +115,34 @@ def test_group_norm_split_statistics_match_whole(orc, gpu):
     assert_close(orc, joined, want, rel=1e-5, atol=2e-6, what="sliced group_norm+silu")
     d = orc.bf16_ulp_distance(from_torch(joined)[0], from_torch(whole)[0])
     assert d.max() <= 1 and (d > 0).mean() < 1e-3
+
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("shape,groups", [((2, 32, 3, 8, 16), 8), ((1, 64, 5, 24, 40), 32), ((1, 32, 9, 120, 128), 8)])
+@pytest.mark.parametrize("silu", [False, True])
+def test_group_norm_frames_equals_permute_norm_permute(orc, gpu, dtype, shape, groups, silu):
+    """frame_group_norm (native/src/architectures/mochi.cpp:365-371): permute [B,C,T,H,W] ->
+    [B*T,C,H,W], group_norm(32, 1e-5), permute back.  The kernel reads and writes [B,C,T,H,W]
+    directly; the oracle does the three steps."""
+    be, ops = gpu
+    from vrhino_b200 import synth
+    B, C, T, H, W = shape
+    obe = orc.OracleBackend()
+    raw = synth.normal(shape, 0.3, 2.0, seed=T)
+    x = orc.tensor(raw, dtype)
+    w = orc.tensor(synth.normal((C,), 1.0, 0.1, seed=1))
+    b = orc.tensor(synth.normal((C,), 0.0, 0.1, seed=2))
+    frames = orc.T(np.ascontiguousarray(x.data.transpose(0, 2, 1, 3, 4)).reshape(B * T, C, H, W), dtype)
+    normed = obe.group_norm(frames, groups, w, b, 1e-5)
+    if silu:
+        normed = obe.activation(normed, orc.SILU)
+    want = orc.T(np.ascontiguousarray(normed.data.reshape(B, T, C, H, W).transpose(0, 2, 1, 3, 4)), dtype)
+    got = be.group_norm_frames(to_torch(x), groups, to_torch(w), to_torch(b), 1e-5, fuse_silu=silu)
+    if silu and dtype == "bf16":
+        # SiLU amplifies a one-ulp difference of a very negative y: compare through the unfused pair
+        y = be.group_norm_frames(to_torch(x), groups, to_torch(w), to_torch(b), 1e-5)
+        import torch
+        assert torch.equal(got.view(torch.int16), be.activation(y, 0).view(torch.int16))
+        return
+    assert_close(orc, got, want, rel=1e-5, atol=2e-6, what="group_norm_frames")

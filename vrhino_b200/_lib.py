@@ -44,6 +44,8 @@ SIGNATURES = {
     "vrb_dequantize": [_i, _vp, _vp, _vp, _i, _i64, _i64, _i64, _vp],
     "vrb_group_norm_workspace_bytes": [_i64, _i],
     "vrb_group_norm": [_vp, _i, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i, _f, _i, _vp, _sz, _vp],
+    "vrb_group_norm_frames_workspace_bytes": [_i64, _i64, _i],
+    "vrb_group_norm_frames": [_vp, _i, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i64, _i, _f, _i, _vp, _sz, _vp],
     "vrb_group_norm_fixed_scratch": [_vp, _i, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i, _f, _i, _vp],
     "vrb_group_norm_moments": [_vp, _i, _i64, _i64, _i64, _i, _vp, _vp, _vp, _sz, _vp],
     "vrb_group_norm_finalize": [_vp, _vp, _i64, _f, _vp, _vp, _vp],
@@ -70,6 +72,7 @@ _RESTYPES = {
     "vrb_last_error": _c.c_char_p,
     "vrb_launch_count": _c.c_uint64,
     "vrb_group_norm_workspace_bytes": _c.c_size_t,
+    "vrb_group_norm_frames_workspace_bytes": _c.c_size_t,
     "vrb_host_release": None,
 }
 

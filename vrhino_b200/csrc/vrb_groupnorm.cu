@@ -26,10 +26,21 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kMaxSplits = 64;
 
+// frames == 1: x is [batch, channels, spatial] and a unit (batch entry, group) is one contiguous
+// run of channels_per * spatial elements.  frames > 1: x is [batch, channels, frames, spatial] and a
+// unit is (batch entry, frame, group): channels_per separate runs of `spatial` elements, which is
+// what the reference reaches by permuting to [batch*frames, channels, spatial] first
+// (frame_group_norm, native/src/architectures/mochi.cpp:365-371).
 struct GnGeom {
-    int64_t batch, channels, spatial, count, units;
+    int64_t batch, channels, spatial, count, units, frames;
     int groups, channels_per;
 };
+// First element of run `j` (channel j of the group) of unit `unit`.
+__device__ __forceinline__ int64_t run_base(const GnGeom& g, int64_t unit, int j) {
+    if (g.frames == 1) return unit * g.count + static_cast<int64_t>(j) * g.spatial;
+    const int64_t group = unit % g.groups, bt = unit / g.groups, t = bt % g.frames, b = bt / g.frames;
+    return (((b * g.channels + group * g.channels_per + j) * g.frames) + t) * g.spatial;
+}
 
 // Slices per unit: enough CTAs to fill the machine several times over, at least 16 K elements
 // per slice so the per-CTA reduction stays negligible.
@@ -121,17 +132,30 @@ __device__ __forceinline__ void accumulate_packed8(const Packed8<X_BF16>& r, flo
     s2 += static_cast<double>(__fadd_rn(t2a, t2b));
 }
 
+// frames == 1: the unit's `count` elements are cut into `splits` slices.  frames > 1: the unit's
+// channels_per runs are cut into splits / channels_per slices each, run-major, so the partials of
+// a unit are again combined in element order.
 template <bool X_BF16>
 __global__ void __launch_bounds__(kThreads, 4) gn_partial_vec_kernel(const void* __restrict__ x, const float* __restrict__ shift,
-                                                                    double* __restrict__ partial, int64_t count, int splits) {
+                                                                    double* __restrict__ partial, GnGeom g, int splits) {
     __shared__ double ws[2][8];
     constexpr int U = X_BF16 ? 4 : 2;
     const int64_t unit = blockIdx.x / splits;
     const int split = blockIdx.x % splits;
-    const int64_t base = unit * count;
-    const float a = shift ? shift[unit] : load1(x, X_BF16 ? VRB_BF16 : VRB_F32, base);
-    const int64_t chunks = count >> 3;
-    const int64_t begin = chunks * split / splits, end = chunks * (split + 1) / splits;
+    const float a = shift ? shift[unit] : load1(x, X_BF16 ? VRB_BF16 : VRB_F32, run_base(g, unit, 0));
+    int64_t base, begin, end;
+    if (g.frames == 1) {
+        const int64_t chunks = g.count >> 3;
+        base = unit * g.count;
+        begin = chunks * split / splits;
+        end = chunks * (split + 1) / splits;
+    } else {
+        const int per_run = splits / g.channels_per, j = split / per_run, part = split - j * per_run;
+        const int64_t chunks = g.spatial >> 3;
+        base = run_base(g, unit, j);
+        begin = chunks * part / per_run;
+        end = chunks * (part + 1) / per_run;
+    }
     double s1 = 0.0, s2 = 0.0;
     Packed8<X_BF16> cur[U], nxt[U];
     int64_t c0 = begin + threadIdx.x;
@@ -168,16 +192,43 @@ __global__ void gn_collect_kernel(const double* partial, double* moments, int64_
     moments[unit * 3 + 2] = s2;
 }
 
-__global__ void gn_finalize_kernel(const double* moments, const float* shift, const void* x, int dt, int64_t count,
+__global__ void gn_finalize_kernel(const double* moments, const float* shift, const void* x, int dt, GnGeom g,
                                    int64_t units, float eps, float* mean, float* inverse) {
     const int64_t unit = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (unit >= units) return;
-    const double a = shift ? static_cast<double>(shift[unit]) : static_cast<double>(load1(x, dt, unit * count));
+    const double a = shift ? static_cast<double>(shift[unit]) : static_cast<double>(load1(x, dt, run_base(g, unit, 0)));
     const double n = moments[unit * 3], m1 = moments[unit * 3 + 1] / n;
     double var = moments[unit * 3 + 2] / n - m1 * m1;
     if (var < 0.0) var = 0.0;
     mean[unit] = static_cast<float>(a + m1);
     inverse[unit] = rsqrtf(__fadd_rn(static_cast<float>(var), eps));
+}
+
+// Slice sums -> mean / inverse in one launch for the whole-operator path: one warp per unit, lane
+// l adds slices l and l + 32 (at most 64 slices), then a fixed shuffle tree; lane 0 applies the
+// formulas of gn_finalize_kernel.  The order of additions depends only on the slice count.
+__global__ void __launch_bounds__(128) gn_collect_finalize_kernel(const double* __restrict__ partial, const void* x, int dt,
+                                                                  GnGeom g, int splits, float eps, float* mean, float* inverse) {
+    const int64_t unit = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (unit >= g.units) return;
+    double s1 = 0.0, s2 = 0.0;
+    for (int s = lane; s < splits; s += 32) {
+        s1 += partial[(unit * splits + s) * 2];
+        s2 += partial[(unit * splits + s) * 2 + 1];
+    }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, offset);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, offset);
+    }
+    if (lane == 0) {
+        const double a = static_cast<double>(load1(x, dt, run_base(g, unit, 0)));
+        const double n = static_cast<double>(g.count), m1 = s1 / n;
+        double var = s2 / n - m1 * m1;
+        if (var < 0.0) var = 0.0;
+        mean[unit] = static_cast<float>(a + m1);
+        inverse[unit] = rsqrtf(__fadd_rn(static_cast<float>(var), eps));
+    }
 }
 
 __device__ __forceinline__ float gn_value(float x, float mean, float inv, float gamma, float beta, int dt, int silu) {
@@ -192,8 +243,11 @@ struct PlaneTerms {
 };
 __device__ __forceinline__ PlaneTerms plane_terms(int64_t plane, const GnGeom& g, int dt, const void* weight, int w_dt,
                                                   const void* bias, int b_dt, const float* mean, const float* inverse) {
-    const int64_t channel = plane % g.channels;
-    const int64_t unit = (plane / g.channels) * g.groups + channel / g.channels_per;
+    // plane = (batch entry, channel, frame); frames == 1 for the contiguous form
+    int64_t frame = 0, bc = plane;
+    if (g.frames > 1) { bc = plane / g.frames; frame = plane - bc * g.frames; }
+    const int64_t channel = bc % g.channels;
+    const int64_t unit = ((bc / g.channels) * g.frames + frame) * g.groups + channel / g.channels_per;
     PlaneTerms t;
     t.mean = __ldg(mean + unit);
     t.inv = __ldg(inverse + unit);
@@ -214,7 +268,7 @@ __global__ void __launch_bounds__(kThreads, 4) gn_apply_vec_kernel(const void* _
     constexpr int U = 4;
     constexpr int dt = X_BF16 ? VRB_BF16 : VRB_F32;
     const int64_t plane_chunks = g.spatial >> 3;
-    const int64_t tiles = g.batch * g.channels * tiles_per_plane;
+    const int64_t tiles = g.batch * g.channels * g.frames * tiles_per_plane;
     for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
         const int64_t plane = t / tiles_per_plane;
         const int64_t tile_begin = (t - plane * tiles_per_plane) * tile_chunks;
@@ -242,18 +296,18 @@ __global__ void __launch_bounds__(kThreads) gn_apply_kernel(const void* x, int d
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     const int64_t total = g.units * g.count;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const PlaneTerms k = plane_terms(i / g.spatial, g, dt, weight, w_dt, bias, b_dt, mean, inverse);
+        const PlaneTerms k = plane_terms(i / g.spatial, g, dt, weight, w_dt, bias, b_dt, mean, inverse);   // plane-major order
         store1(out, dt, i, gn_value(load1(x, dt, i), k.mean, k.inv, k.gamma, k.beta, dt, silu));
     }
 }
 
-int make_geom(GnGeom& g, int64_t batch, int64_t channels, int64_t spatial, int groups, const char* what) {
-    VRB_REQUIRE(batch > 0 && channels > 0 && spatial > 0 && groups > 0 && channels % groups == 0, VRB_ERR_INVALID,
+int make_geom(GnGeom& g, int64_t batch, int64_t channels, int64_t spatial, int groups, const char* what, int64_t frames = 1) {
+    VRB_REQUIRE(batch > 0 && channels > 0 && spatial > 0 && groups > 0 && channels % groups == 0 && frames > 0, VRB_ERR_INVALID,
                 "%s: group norm shape/groups mismatch", what);
-    g.batch = batch; g.channels = channels; g.spatial = spatial; g.groups = groups;
+    g.batch = batch; g.channels = channels; g.spatial = spatial; g.groups = groups; g.frames = frames;
     g.channels_per = static_cast<int>(channels / groups);
     g.count = g.channels_per * spatial;
-    g.units = batch * groups;
+    g.units = batch * frames * groups;
     VRB_REQUIRE(g.units * kMaxSplits <= 0x7fffffffLL, VRB_ERR_INVALID,
                 "%s: group norm launch extent exceeds CUDA grid capacity", what);
     return VRB_OK;
@@ -270,14 +324,23 @@ size_t workspace_layout(int64_t units, size_t* moments_off, size_t* mean_off) {
 }
 
 int run_moments(const void* x, int dt, const GnGeom& g, const float* shift, double* partial, double* moments,
-                cudaStream_t s) {
-    const int splits = choose_splits(g.units, g.count);
-    const bool vec = g.count % 8 == 0 && aligned16(x);
+                cudaStream_t s, int* splits_out = nullptr) {
+    int splits = choose_splits(g.units, g.count);
+    const bool vec = (g.frames == 1 ? g.count : g.spatial) % 8 == 0 && aligned16(x);
+    if (g.frames > 1) {
+        // per-frame form: whole runs per slice, vector kernel only
+        VRB_REQUIRE(vec && g.channels_per <= kMaxSplits, VRB_ERR_UNSUPPORTED,
+                    "group_norm_frames: needs spatial %% 8 == 0, 16-byte aligned x and at most %d channels per group", kMaxSplits);
+        int per_run = splits / g.channels_per;
+        if (per_run < 1) per_run = 1;
+        splits = per_run * g.channels_per;
+    }
     const int grid = static_cast<int>(g.units * splits);
-    if (vec && dt == VRB_BF16) gn_partial_vec_kernel<true><<<grid, kThreads, 0, s>>>(x, shift, partial, g.count, splits);
-    else if (vec) gn_partial_vec_kernel<false><<<grid, kThreads, 0, s>>>(x, shift, partial, g.count, splits);
+    if (vec && dt == VRB_BF16) gn_partial_vec_kernel<true><<<grid, kThreads, 0, s>>>(x, shift, partial, g, splits);
+    else if (vec) gn_partial_vec_kernel<false><<<grid, kThreads, 0, s>>>(x, shift, partial, g, splits);
     else gn_partial_kernel<<<grid, kThreads, 0, s>>>(x, dt, shift, partial, g.count, splits);
     if (int rc = after_launch("group_norm moments")) return rc;
+    if (splits_out) { *splits_out = splits; return VRB_OK; }   // the caller combines the slices itself
     gn_collect_kernel<<<static_cast<int>((g.units + 127) / 128), 128, 0, s>>>(partial, moments, g.units, splits, g.count);
     return after_launch("group_norm collect");
 }
@@ -287,13 +350,13 @@ int run_apply(const void* x, int dt, const void* weight, int w_dt, const void* b
     const bool vec = g.spatial % 8 == 0 && aligned16(x) && aligned16(out);
     const int64_t total = g.units * g.count;
     if (vec) {
-        if (dt == VRB_BF16 && silu && total >= kLutMinElements)   // SiLU of a bf16 value: table lookup
-            return launch_group_norm_apply_silu_lut(x, weight, w_dt, bias, b_dt, out, g.batch * g.channels, g.channels,
-                                                    g.channels_per, g.groups, g.spatial, mean, inverse, s);
+        if (dt == VRB_BF16 && silu && total >= kLutMinElements && total / 8 < (int64_t{1} << 31))   // SiLU of a bf16 value: table lookup
+            return launch_group_norm_apply_silu_lut(x, weight, w_dt, bias, b_dt, out, g.batch * g.channels * g.frames, g.channels,
+                                                    g.channels_per, g.groups, g.frames, g.spatial, mean, inverse, s);
         const int64_t plane_chunks = g.spatial / 8;
         const int64_t tiles_per_plane = (plane_chunks + kThreads * 4 - 1) / (kThreads * 4);
         const int64_t tile_chunks = ((plane_chunks + tiles_per_plane - 1) / tiles_per_plane + 7) & ~int64_t{7};   // tiles start on 128-byte lines
-        const int grid = grid_for(g.batch * g.channels * tiles_per_plane, 4);
+        const int grid = grid_for(g.batch * g.channels * g.frames * tiles_per_plane, 4);
 #define VRB_GN_APPLY(BF, SI) gn_apply_vec_kernel<BF, SI><<<grid, kThreads, 0, s>>>( \
             x, weight, w_dt, bias, b_dt, out, g, mean, inverse, tiles_per_plane, tile_chunks)
         if (dt == VRB_BF16) { if (silu) VRB_GN_APPLY(true, true); else VRB_GN_APPLY(true, false); }
@@ -363,14 +426,10 @@ extern "C" size_t vrb_group_norm_workspace_bytes(int64_t batch, int groups) {
     return workspace_layout(batch * groups, nullptr, nullptr);
 }
 
-extern "C" int vrb_group_norm(const void* x, int dtype, const void* weight, int weight_dtype,
-                              const void* bias, int bias_dtype, void* out,
-                              int64_t batch, int64_t channels, int64_t spatial, int groups, float eps,
-                              int fuse_silu, void* workspace, size_t workspace_bytes, vrb_stream stream) {
-    VRB_REQUIRE(x && out, VRB_ERR_INVALID, "group_norm: null tensor");
-    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "group_norm: dtype must be F32 or BF16");
-    GnGeom g;
-    if (int rc = make_geom(g, batch, channels, spatial, groups, "group_norm")) return rc;
+namespace {
+int group_norm_whole(const GnGeom& g, const void* x, int dtype, const void* weight, int weight_dtype,
+                     const void* bias, int bias_dtype, void* out, float eps, int fuse_silu, void* workspace,
+                     size_t workspace_bytes, vrb_stream stream) {
     size_t moments_off, mean_off;
     const size_t need = workspace_layout(g.units, &moments_off, &mean_off);
     VRB_REQUIRE(workspace && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0,
@@ -381,11 +440,43 @@ extern "C" int vrb_group_norm(const void* x, int dtype, const void* weight, int 
     float* mean = reinterpret_cast<float*>(ws + mean_off);
     float* inverse = mean + g.units;
     cudaStream_t s = as_stream(stream);
-    if (int rc = run_moments(x, dtype, g, nullptr, partial, moments, s)) return rc;
-    gn_finalize_kernel<<<static_cast<int>((g.units + 127) / 128), 128, 0, s>>>(moments, nullptr, x, dtype, g.count,
-                                                                             g.units, eps, mean, inverse);
+    int splits = 0;
+    if (int rc = run_moments(x, dtype, g, nullptr, partial, moments, s, &splits)) return rc;
+    gn_collect_finalize_kernel<<<static_cast<int>((g.units * 32 + 127) / 128), 128, 0, s>>>(partial, x, dtype, g, splits, eps,
+                                                                                         mean, inverse);
     if (int rc = after_launch("group_norm finalize")) return rc;
     return run_apply(x, dtype, weight, weight_dtype, bias, bias_dtype, out, g, mean, inverse, fuse_silu, s);
+}
+}  // namespace
+
+extern "C" int vrb_group_norm(const void* x, int dtype, const void* weight, int weight_dtype,
+                              const void* bias, int bias_dtype, void* out,
+                              int64_t batch, int64_t channels, int64_t spatial, int groups, float eps,
+                              int fuse_silu, void* workspace, size_t workspace_bytes, vrb_stream stream) {
+    VRB_REQUIRE(x && out, VRB_ERR_INVALID, "group_norm: null tensor");
+    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "group_norm: dtype must be F32 or BF16");
+    GnGeom g;
+    if (int rc = make_geom(g, batch, channels, spatial, groups, "group_norm")) return rc;
+    return group_norm_whole(g, x, dtype, weight, weight_dtype, bias, bias_dtype, out, eps, fuse_silu, workspace,
+                            workspace_bytes, stream);
+}
+
+extern "C" size_t vrb_group_norm_frames_workspace_bytes(int64_t batch, int64_t frames, int groups) {
+    if (batch <= 0 || frames <= 0 || groups <= 0) return 0;
+    return workspace_layout(batch * frames * groups, nullptr, nullptr);
+}
+
+extern "C" int vrb_group_norm_frames(const void* x, int dtype, const void* weight, int weight_dtype,
+                                     const void* bias, int bias_dtype, void* out,
+                                     int64_t batch, int64_t channels, int64_t frames, int64_t spatial, int groups,
+                                     float eps, int fuse_silu, void* workspace, size_t workspace_bytes, vrb_stream stream) {
+    VRB_REQUIRE(x && out, VRB_ERR_INVALID, "group_norm_frames: null tensor");
+    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "group_norm_frames: dtype must be F32 or BF16");
+    GnGeom g;
+    if (int rc = make_geom(g, batch, channels, spatial, groups, "group_norm_frames", frames)) return rc;
+    VRB_REQUIRE(aligned16(out), VRB_ERR_UNSUPPORTED, "group_norm_frames: out must be 16-byte aligned");
+    return group_norm_whole(g, x, dtype, weight, weight_dtype, bias, bias_dtype, out, eps, fuse_silu, workspace,
+                            workspace_bytes, stream);
 }
 
 // ---- GroupNorm with built-in scratch ----------------------------------------------------------
@@ -474,7 +565,7 @@ extern "C" int vrb_group_norm_finalize(const double* moments, const float* shift
                                        float* mean, float* inverse, vrb_stream stream) {
     VRB_REQUIRE(moments && shift && mean && inverse && units > 0, VRB_ERR_INVALID, "group_norm_finalize: null tensor");
     gn_finalize_kernel<<<static_cast<int>((units + 127) / 128), 128, 0, as_stream(stream)>>>(
-        moments, shift, nullptr, VRB_F32, 0, units, eps, mean, inverse);
+        moments, shift, nullptr, VRB_F32, GnGeom{}, units, eps, mean, inverse);
     return after_launch("group_norm finalize");
 }
 

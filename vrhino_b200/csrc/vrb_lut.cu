@@ -145,24 +145,28 @@ __global__ void __launch_bounds__(kLutThreads, 1) swiglu_lut_kernel(const uint4*
 __global__ void __launch_bounds__(kLutThreads, 1) gn_apply_silu_lut_kernel(
     const uint4* __restrict__ x, uint4* __restrict__ out, const void* __restrict__ weight, int w_dt,
     const void* __restrict__ bias, int b_dt, const float* __restrict__ mean, const float* __restrict__ inverse,
-    int64_t planes, int64_t channels, int channels_per, int groups, int64_t plane_chunks, int64_t tiles_per_plane,
-    int64_t tile_chunks, const uint4* __restrict__ ready) {
+    int64_t planes, int64_t channels, int channels_per, int groups, int64_t frames, int64_t plane_chunks,
+    int64_t tiles_per_plane, int64_t tile_chunks, const uint4* __restrict__ ready) {
     extern __shared__ __align__(16) uint16_t table[];
     fill_table<VRB_SILU>(table, ready, 0.f, 0.f);
     constexpr int U = 4;
-    const int64_t tiles = planes * tiles_per_plane;
-    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
-        const int64_t plane = t / tiles_per_plane;
-        const int64_t tile_begin = (t - plane * tiles_per_plane) * tile_chunks;
+    // the launcher guarantees planes * tiles_per_plane < 2^31: 32-bit index arithmetic
+    const unsigned tiles = static_cast<unsigned>(planes * tiles_per_plane), tpp = static_cast<unsigned>(tiles_per_plane);
+    const unsigned nframes = static_cast<unsigned>(frames), nchannels = static_cast<unsigned>(channels);
+    for (unsigned t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const unsigned plane = t / tpp;
+        const int64_t tile_begin = static_cast<int64_t>(t - plane * tpp) * tile_chunks;
         const int64_t tile_end = tile_begin + tile_chunks < plane_chunks ? tile_begin + tile_chunks : plane_chunks;
         const int64_t c0 = tile_begin + threadIdx.x;
-        const int64_t channel = plane % channels;
-        const int64_t unit = (plane / channels) * groups + channel / channels_per;
+        unsigned frame = 0, bc = plane;
+        if (nframes > 1) { bc = plane / nframes; frame = plane - bc * nframes; }
+        const unsigned batch_entry = bc / nchannels, channel = bc - batch_entry * nchannels;
+        const unsigned unit = (batch_entry * nframes + frame) * static_cast<unsigned>(groups) + channel / static_cast<unsigned>(channels_per);
         const float m = __ldg(mean + unit), inv = __ldg(inverse + unit);
         const float gamma = weight ? round_to(VRB_BF16, load1(weight, w_dt, channel)) : 1.0f;
         const float beta = bias ? round_to(VRB_BF16, load1(bias, b_dt, channel)) : 0.0f;
-        const uint4* px = x + plane * plane_chunks;
-        uint4* po = out + plane * plane_chunks;
+        const uint4* px = x + static_cast<int64_t>(plane) * plane_chunks;
+        uint4* po = out + static_cast<int64_t>(plane) * plane_chunks;
         uint4 r[U];
 #pragma unroll
         for (int u = 0; u < U; ++u)
@@ -285,8 +289,8 @@ int launch_swiglu_lut(const void* proj, void* out, int64_t rows, int64_t hidden,
 }
 
 int launch_group_norm_apply_silu_lut(const void* x, const void* weight, int w_dt, const void* bias, int b_dt, void* out,
-                                     int64_t planes, int64_t channels, int channels_per, int groups, int64_t spatial,
-                                     const float* mean, const float* inverse, cudaStream_t stream) {
+                                     int64_t planes, int64_t channels, int channels_per, int groups, int64_t frames,
+                                     int64_t spatial, const float* mean, const float* inverse, cudaStream_t stream) {
     static bool done[64] = {false};
     if (int rc = reserve_table(gn_apply_silu_lut_kernel, done)) return rc;
     const int64_t plane_chunks = spatial / 8;
@@ -296,7 +300,7 @@ int launch_group_norm_apply_silu_lut(const void* x, const void* weight, int w_dt
     const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
     gn_apply_silu_lut_kernel<<<grid, kLutThreads, kTableBytes, stream>>>(
         static_cast<const uint4*>(x), static_cast<uint4*>(out), weight, w_dt, bias, b_dt, mean, inverse, planes, channels,
-        channels_per, groups, plane_chunks, tiles_per_plane, tile_chunks, ready_table<VRB_SILU>(0.f, 0.f, stream));
+        channels_per, groups, frames, plane_chunks, tiles_per_plane, tile_chunks, ready_table<VRB_SILU>(0.f, 0.f, stream));
     return after_launch("group_norm apply (table)");
 }
 

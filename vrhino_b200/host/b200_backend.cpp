@@ -287,6 +287,25 @@ Tensor B200Backend::group_norm_silu(const Tensor& x, int groups, const Tensor* w
     return group_norm_impl(x, groups, w, b, eps, true);
 }
 
+Tensor B200Backend::group_norm_frames(const Tensor& raw, int groups, const Tensor* weight_raw, const Tensor* bias_raw,
+                                      float eps, bool silu) {
+    return guarded([&] {
+        require(raw.ndim() == 5 && groups > 0 && raw.dim(1) % groups == 0, "group norm shape/groups mismatch");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype), weight, bias;
+        if (weight_raw) weight = parameter(*weight_raw);
+        if (bias_raw) bias = parameter(*bias_raw);
+        const int64_t batch = x.dim(0), channels = x.dim(1), frames = x.dim(2), spatial = x.dim(3) * x.dim(4);
+        const size_t need = vrb_group_norm_frames_workspace_bytes(batch, frames, groups);
+        Tensor out = rt_->allocate_device(x.shape(), dtype);
+        check(vrb_group_norm_frames(x.data(), code(dtype), weight_raw ? weight.data() : nullptr,
+                                    weight_raw ? code(weight.dtype()) : 0, bias_raw ? bias.data() : nullptr,
+                                    bias_raw ? code(bias.dtype()) : 0, out.data(), batch, channels, frames, spatial, groups,
+                                    eps, silu ? 1 : 0, workspace(need), need, kLegacyStream));
+        return out;
+    });
+}
+
 // ---- fused forms --------------------------------------------------------------------------------
 
 Tensor B200Backend::layer_norm_modulate(const Tensor& raw, const Tensor* weight_raw, const Tensor* bias_raw, float eps,
@@ -421,6 +440,16 @@ Tensor swiglu(vrhino::Backend& backend, const Tensor& projected) {
 Tensor group_norm_silu(vrhino::Backend& backend, const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps) {
     if (auto* b200 = dynamic_cast<B200Backend*>(&backend)) return b200->group_norm_silu(x, groups, weight, bias, eps);
     return backend.activation(backend.group_norm(x, groups, weight, bias, eps), vrhino::Activation::Silu);
+}
+
+Tensor frame_group_norm(vrhino::Backend& backend, const Tensor& x, int groups, const Tensor* weight, const Tensor* bias,
+                        float eps, bool silu) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend)) return b200->group_norm_frames(x, groups, weight, bias, eps, silu);
+    const int64_t b = x.dim(0), c = x.dim(1), t = x.dim(2), h = x.dim(3), w = x.dim(4);
+    Tensor frames = backend.reshape(backend.permute(x, {0, 2, 1, 3, 4}), {b * t, c, h, w});
+    frames = backend.group_norm(frames, groups, weight, bias, eps);
+    Tensor out = backend.permute(backend.reshape(frames, {b, t, c, h, w}), {0, 2, 1, 3, 4});
+    return silu ? backend.activation(out, vrhino::Activation::Silu) : out;
 }
 
 }  // namespace vrhino_b200

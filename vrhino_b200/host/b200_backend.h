@@ -63,6 +63,8 @@ public:
     Tensor gated_residual(const Tensor& residual, const Tensor& branch, const Tensor* gate, DType state);
     Tensor swiglu(const Tensor& projected);
     Tensor group_norm_silu(const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps);
+    // x [B, C, T, H, W]: statistics per (batch entry, frame, group), no permutes
+    Tensor group_norm_frames(const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps, bool silu);
     Tensor cfg_euler(const Tensor& sample, const Tensor& unconditional, const Tensor& conditional,
                      float guidance, float delta, bool subtract_prediction, bool guidance_role, bool solver_role);
 
@@ -184,5 +186,11 @@ vrhino::Tensor swiglu(vrhino::Backend& backend, const vrhino::Tensor& projected)
 // activation(group_norm(x, groups, weight, bias, eps), Silu)   (autoencoder_kl.cpp:31-41)
 vrhino::Tensor group_norm_silu(vrhino::Backend& backend, const vrhino::Tensor& x, int groups,
                                const vrhino::Tensor* weight, const vrhino::Tensor* bias, float eps);
+
+// frame_group_norm (native/src/architectures/mochi.cpp:365-371), optionally with the SiLU its callers
+// apply next (:375-377): permute to [B*T, C, H, W] -> group_norm -> permute back, or one pass
+// over the unpermuted tensor with a B200Backend.
+vrhino::Tensor frame_group_norm(vrhino::Backend& backend, const vrhino::Tensor& x, int groups,
+                                const vrhino::Tensor* weight, const vrhino::Tensor* bias, float eps, bool silu = false);
 
 }  // namespace vrhino_b200

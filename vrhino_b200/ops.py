@@ -266,6 +266,26 @@ class B200Backend:
         return out
 
 
+    def group_norm_frames(self, raw, groups, weight, bias, eps, fuse_silu=False, out=None):
+        """Per-frame GroupNorm of [B, C, T, H, W] without the two permutes of frame_group_norm
+        (native/src/architectures/mochi.cpp:365-371): statistics per (batch entry, frame, group)."""
+        if raw.dim() != 5 or groups <= 0 or raw.shape[1] % groups:
+            raise VrbError("group norm shape/groups mismatch")
+        weight, bias = self._param(weight), self._param(bias)
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        batch, channels, frames = x.shape[0], x.shape[1], x.shape[2]
+        spatial = x.shape[3] * x.shape[4]
+        out = _result(out, x.shape, x.dtype, x.device)
+        need = _lib.load().vrb_group_norm_frames_workspace_bytes(batch, frames, groups)
+        if self._gn_workspace is None or self._gn_workspace.numel() < need:
+            self._gn_workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        call("vrb_group_norm_frames", _ptr(x), _code(x), _ptr(weight), _code(weight) if weight is not None else 0,
+             _ptr(bias), _code(bias) if bias is not None else 0, _ptr(out), batch, channels, frames, spatial, groups,
+             ctypes.c_float(eps), int(fuse_silu), _ptr(self._gn_workspace), need, _stream())
+        return out
+
+
 # ------------------------------------------------------------------ precision policy view --
 GUIDANCE, SOLVER, SIGMA = "GuidanceCoefficient", "SolverCoefficient", "Sigma"
 

@@ -212,9 +212,11 @@ class VaeGroupNorm:
     (native/src/components/autoencoder_kl.cpp:31-41).  Statistics pass + apply pass: the input
     counts twice in the algorithmic bytes, the output once."""
 
-    def __init__(self, be, shape=(1, 256, 28, 240, 424), groups=32, seed=0):
+    def __init__(self, be, shape=(1, 256, 28, 240, 424), groups=32, seed=0, per_frame=False):
+        """per_frame: statistics per (batch entry, frame, group) on the [N, C, T, H, W] tensor as it
+        lies (frame_group_norm, native/src/architectures/mochi.cpp:365-371, minus its permutes)."""
         g = torch.Generator(device="cuda").manual_seed(seed)
-        self.be, self.groups = be, groups
+        self.be, self.groups, self.per_frame = be, groups, per_frame
         self.x = _randn(shape, BF16, g, 0.0, 2.0)
         self.gamma = _randn((shape[1],), F32, g, 1.0, 0.1)
         self.beta = _randn((shape[1],), F32, g, 0.0, 0.1)
@@ -222,6 +224,10 @@ class VaeGroupNorm:
 
     def launches(self) -> List[Launch]:
         def gn(): self.out["gn"] = ops.fused_group_norm_silu(self.be, self.x, self.groups, self.gamma, self.beta, 1e-6, out=self.out.get("gn"))
+        def gf(): self.out["gn"] = self.be.group_norm_frames(self.x, self.groups, self.gamma, self.beta, 1e-5, fuse_silu=True,
+                                                             out=self.out.get("gn"))
+        if self.per_frame:
+            return [Launch("group_norm_frames_silu", gf, self.x.numel() * 6, kernels=4)]
         return [Launch("group_norm_silu", gn, self.x.numel() * 6, kernels=4)]
 
 
@@ -238,7 +244,10 @@ def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, b
         return VaeGroupNorm(be, shape=(1, 256, frames or 28, 240, 424))
     if config == 6:
         return VaeGroupNorm(be, shape=(frames or 28, 256, 1, 240, 424))
-    raise ValueError("config must be 2..6 (6 = config 5 in Mochi's per-frame form)")
+    if config == 7:
+        return VaeGroupNorm(be, shape=(1, 256, frames or 28, 240, 424), per_frame=True)
+    raise ValueError("config must be 2..7 (6 = config 5 as a pre-permuted per-frame tensor, 7 = per-frame statistics "
+                     "on the unpermuted [N,C,T,H,W] tensor)")
 
 
 def _main():
