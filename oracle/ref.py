@@ -136,7 +136,8 @@ class RefCuda:
         for name in ("refc_upload", "refc_host_f32", "refc_numel", "refc_binary", "refc_cast", "refc_reshape", "refc_slice",
                      "refc_layer_norm", "refc_rms_norm", "refc_activation", "refc_rope", "refc_group_norm", "refc_clamp",
                      "refc_exp", "refc_sqrt", "refc_dequantize", "refc_modulate", "refc_attention_norm", "refc_operation_rope",
-                     "refc_residual_add", "refc_gated_residual", "refc_cfg_combine", "refc_euler_update", "refc_flow_to_x0"):
+                     "refc_residual_add", "refc_gated_residual", "refc_cfg_combine", "refc_euler_update", "refc_flow_to_x0",
+                     "refc_frame_group_norm"):
             getattr(lib, name).restype = _c.c_int64
         lib.refc_profile_total_ms.restype = _c.c_double
         self.lib = lib
@@ -206,6 +207,9 @@ class RefCuda:
     def euler_update(self, policy, x, pred, delta, subtract=True):
         return self._h(self.lib.refc_euler_update(int(policy), self._i(x), self._i(pred), _c.c_float(delta), int(subtract)))
     def flow_to_x0(self, policy, x, out, sigma): return self._h(self.lib.refc_flow_to_x0(int(policy), self._i(x), self._i(out), _c.c_float(sigma)))
+
+    def frame_group_norm(self, x, groups, w, b, eps, silu=False):
+        return self._h(self.lib.refc_frame_group_norm(self._i(x), int(groups), self._i(w), self._i(b), _c.c_float(eps), int(silu)))
 
     def wan_self_attention_graph(self, tokens, width, heads, handles, fused=False):
         """The reference's production Wan self-attention graph (GEMMs and attention included).

@@ -245,6 +245,24 @@ int refd_session_terminal() { return g_backend && g_backend->resource_session_te
 const char* refc_backend_name() { static std::string n; n = g_backend ? g_backend->name() : ""; return n.c_str(); }
 #endif
 
+// frame_group_norm of native/src/architectures/mochi.cpp:365-371 (+ SiLU): the reference's permute ->
+// group_norm -> permute on its backend, or, in the drop-in build, vrhino_b200::frame_group_norm
+// (one pass over the unpermuted tensor).
+int64_t refc_frame_group_norm(int64_t x, int groups, int64_t w, int64_t b, float eps, int silu) {
+    return guarded([&] {
+#ifdef VRB_DROPIN
+        return keep(vrhino_b200::frame_group_norm(*g_backend, at(x), groups, opt(w), opt(b), eps, silu != 0));
+#else
+        const Tensor& input = at(x);
+        const int64_t n = input.dim(0), c = input.dim(1), t = input.dim(2), h = input.dim(3), wd = input.dim(4);
+        Tensor frames = g_backend->reshape(g_backend->permute(input, {0, 2, 1, 3, 4}), {n * t, c, h, wd});
+        frames = g_backend->group_norm(frames, groups, opt(w), opt(b), eps);
+        Tensor out = g_backend->permute(g_backend->reshape(frames, {n, t, c, h, wd}), {0, 2, 1, 3, 4});
+        return keep(silu ? g_backend->activation(out, Activation::Silu) : out);
+#endif
+    });
+}
+
 // ---- executable graphs (native/src/runtime/neural_graph.h) ------------------------------------
 // The non-GEMM part of the Wan self-attention graph (native/src/architectures/
 // wan_self_attention_graph.h:46-70), node for node, with the GEMM / attention results (q, k and

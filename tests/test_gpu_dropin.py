@@ -156,6 +156,35 @@ def test_graph_fusion_pass(orc, dropin, hidden):
                 assert name != "attention input" and bad.mean() <= 2e-3 and (diff[bad] <= 2.0 ** -8 * 8.0).all(), (name, int(bad.sum()))
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_frame_group_norm_without_permutes(orc, dropin, dt):
+    """Mochi's frame_group_norm: the reference permutes [B,C,T,H,W] to frames, normalises and permutes
+    back on its CUDA backend; vrhino_b200::frame_group_norm reads and writes the tensor as it lies."""
+    from oracle import ref
+    from vrhino_b200 import synth
+    if not ref.available_cuda():
+        pytest.skip("reference CUDA library not built")
+    shape, groups = (1, 64, 5, 24, 40), 32
+    code = {"f32": ref.F32, "bf16": ref.BF16}[dt]
+    x = cases.to_bits(synth.normal(shape, 0.3, 2.0, seed=3), dt)
+    w, b = synth.normal((64,), 1.0, 0.1, seed=1), synth.normal((64,), 0.0, 0.1, seed=2)
+
+    def run(backend):
+        hx, hw, hb = backend.upload(x, code), backend.upload(w, ref.F32), backend.upload(b, ref.F32)
+        out, _ = backend.download(backend.frame_group_norm(hx, groups, hw, hb, 1e-5, silu=False), shape)
+        backend.clear()
+        return out
+
+    want, got = run(ref.RefCuda()), run(dropin)
+    if dt == "bf16":
+        d = orc.bf16_ulp_distance(got, want)
+        diff = np.abs(orc.bf16_bits_to_f32(got).astype(np.float64) - orc.bf16_bits_to_f32(want).astype(np.float64))
+        assert ((d <= 2) | (diff <= 2e-6)).all(), int(d.max())
+    else:
+        diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
+        assert (diff <= 2e-6 + 1e-5 * np.abs(want)).all(), float(diff.max())
+
+
 def test_production_wan_graph_with_fusion(orc, dropin):
     """The reference's production Wan self-attention graph itself
     (native/src/architectures/wan_self_attention_graph.h), GEMMs and attention included, on a small
