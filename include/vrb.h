@@ -160,6 +160,21 @@ int vrb_group_norm_apply(const void* x, int dtype, const void* weight, int weigh
                          const float* mean, const float* inverse, int fuse_silu,
                          vrb_stream stream);
 
+/* vrb_group_norm_apply whose stores do the all-gather of an H-sharded feature map: x is this
+ * rank's slice [batch, channels, frames, spatial_local] (spatial_local = local rows x row width);
+ * every destination is a FULL tensor [batch, channels, frames, spatial_full] -- this GPU's own and
+ * the peer-mapped ones of the other ranks -- and receives the slice at element offset
+ * spatial_offset of every (batch entry, channel, frame) plane.  mean / inverse are per
+ * (batch entry, group) as vrb_group_norm_finalize produced them from the all-reduced moments.
+ * Plain st.global to the peer pointers; the caller orders the ranks afterwards (any collective
+ * or barrier on the stream).  spatial_local, spatial_full and spatial_offset must be multiples
+ * of 8 elements.  No counterpart in the reference, which has no multi-GPU path. */
+int vrb_group_norm_apply_scatter(const void* x, int dtype, const void* weight, int weight_dtype,
+                                 const void* bias, int bias_dtype, void* const* destinations, int destination_count,
+                                 int64_t batch, int64_t channels, int64_t frames, int64_t spatial_local,
+                                 int64_t spatial_full, int64_t spatial_offset, int groups,
+                                 const float* mean, const float* inverse, int fuse_silu, vrb_stream stream);
+
 /* ------------------------------------------------------------------------ fused chains -- */
 /* Each fused form produces what the cited chain of separate reference kernels produces,
  * including every intermediate rounding, while reading each tensor once. */

@@ -146,3 +146,32 @@ def test_group_norm_frames_equals_permute_norm_permute(orc, gpu, dtype, shape, g
         assert torch.equal(got.view(torch.int16), be.activation(y, 0).view(torch.int16))
         return
     assert_close(orc, got, want, rel=1e-5, atol=2e-6, what="group_norm_frames")
+
+
+@pytest.mark.parametrize("dtype,silu", [("bf16", True), ("bf16", False), ("f32", True)])
+def test_group_norm_apply_scatter_places_the_slice(gpu, dtype, silu):
+    """The normalise pass that stores an H-slice into several full-size tensors (the all-gather of
+    an H-sharded feature map done by the kernel's stores): on one GPU, two destination buffers
+    stand in for this rank's and a peer's tensor.  Rows [row0, row0 + h_local) of every plane must
+    equal the plain apply pass on the slice, everything else must stay untouched."""
+    import torch
+    from vrhino_b200 import sharded
+    be, ops = gpu
+    td = torch.bfloat16 if dtype == "bf16" else torch.float32
+    n, c, t, h_full, w, groups, row0, h_local = 1, 64, 3, 20, 424, 8, 5, 10
+    if silu and dtype == "bf16":
+        t = 36                                          # 64 * 36 * 10 * 424 = 9.8 M elements: the table kernel
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = (torch.randn((n, c, t, h_local, w), device="cuda", generator=g) * 2).to(td)
+    gamma = torch.randn(c, device="cuda", generator=g) * 0.1 + 1
+    beta = torch.randn(c, device="cuda", generator=g) * 0.1
+    pieces = sharded.KernelMoments(be)
+    shift = pieces.first_elements(x, groups)
+    mean, inv = pieces.finalize(pieces.moments(x, groups, shift), shift, 1e-6)
+    want = pieces.apply(x, groups, gamma, beta, mean, inv, silu)
+    dests = [torch.full((n, c, t, h_full, w), 7.0, device="cuda", dtype=td) for _ in range(2)]
+    pieces.apply_scatter(x, groups, gamma, beta, mean, inv, silu, [d.data_ptr() for d in dests], h_full, row0)
+    torch.cuda.synchronize()
+    for d in dests:
+        assert torch.equal(d[:, :, :, row0:row0 + h_local], want)
+        assert bool((d[:, :, :, :row0] == 7.0).all()) and bool((d[:, :, :, row0 + h_local:] == 7.0).all())

@@ -1,5 +1,6 @@
-"""Two NCCL ranks on two GPUs (skipped on a single-GPU box): the sharded GroupNorm+SiLU and the
-sharded sampler update give the single-GPU result; token-sharded row kernels give the same rows."""
+"""Two NCCL ranks on two GPUs (skipped on a single-GPU box): the sharded GroupNorm+SiLU (with the
+output gathered by NCCL, and by the normalise kernel's own peer stores) and the sharded sampler
+update give the single-GPU result; token-sharded row kernels give the same rows."""
 import os
 import socket
 import sys
@@ -33,6 +34,12 @@ def _rank(rank, world, port, tmp):
     h0, h1 = sharded.h_range(shape[3], rank, world)
     full = sharded.sharded_group_norm(sharded.KernelMoments(be), x[:, :, :, h0:h1, :].contiguous(), groups, w, b, eps, True, None, 3)
     whole = ops.fused_group_norm_silu(be, x, groups, w, b, eps)
+    # the same with the gather done by the normalise kernel's stores into every rank's (peer-mapped) output
+    peer = sharded.PeerOutput(shape, torch.bfloat16, torch.device("cuda", rank))
+    via_peer = sharded.sharded_group_norm(sharded.KernelMoments(be), x[:, :, :, h0:h1, :].contiguous(), groups, w, b, eps, True,
+                                          None, None, peer, h0)
+    torch.cuda.synchronize()
+    assert torch.equal(via_peer.view(torch.int16), full.view(torch.int16)), "peer-store gather differs from the NCCL gather"
     torch.save({"full": full.cpu(), "whole": whole.cpu()}, os.path.join(tmp, f"gn_{rank}.pt"))
     pol = ops.Policy.fp32()
     n = 16 * 21 * 60 * 104

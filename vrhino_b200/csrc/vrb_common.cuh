@@ -57,12 +57,23 @@ constexpr int64_t kLutMinElements = int64_t{4} << 20;
 bool unary_lut_applicable(int dtype, int64_t count, const void* x, const void* out);
 int launch_unary_lut(int op, const void* x, void* out, int64_t count, float p0, float p1, cudaStream_t stream);
 int launch_swiglu_lut(const void* proj, void* out, int64_t rows, int64_t hidden, cudaStream_t stream);
+// Where the GroupNorm normalise pass writes.  count == 0: `out`, laid out like x.  count > 0: the
+// same values go to every dst[k] (this GPU's and peer-mapped full-size tensors), plane p of x
+// landing at element p * plane_stride + plane_offset -- the all-gather of an H-sharded feature map
+// done by the kernel's own stores.
+struct GnScatter {
+    void* dst[8];
+    int count;
+    int64_t plane_stride, plane_offset;
+};
 // GroupNorm normalise pass on bf16 followed by SiLU through the table: x is [planes, spatial]
 // with spatial % 8 == 0; plane p = (batch entry, channel, frame) (frames == 1 for the contiguous
-// form) belongs to statistics unit ((batch entry) * frames + frame) * groups + channel / channels_per.
+// form) belongs to statistics unit ((batch entry) * stat_frames + (stat_frames > 1 ? frame : 0)) *
+// groups + channel / channels_per.
 int launch_group_norm_apply_silu_lut(const void* x, const void* weight, int w_dt, const void* bias, int b_dt, void* out,
                                      int64_t planes, int64_t channels, int channels_per, int groups, int64_t frames,
-                                     int64_t spatial, const float* mean, const float* inverse, cudaStream_t stream);
+                                     int64_t stat_frames, int64_t spatial, const float* mean, const float* inverse,
+                                     const GnScatter& scatter, cudaStream_t stream);
 
 // ------------------------------------------------------------------------ device side --
 #ifdef __CUDACC__

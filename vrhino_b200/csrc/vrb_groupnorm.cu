@@ -33,6 +33,7 @@ constexpr int kMaxSplits = 64;
 // (frame_group_norm, native/src/architectures/mochi.cpp:365-371).
 struct GnGeom {
     int64_t batch, channels, spatial, count, units, frames;
+    int64_t stat_frames;   // == frames; 1 when planes are split by frame but the statistics span all frames
     int groups, channels_per;
 };
 // First element of run `j` (channel j of the group) of unit `unit`.
@@ -247,7 +248,8 @@ __device__ __forceinline__ PlaneTerms plane_terms(int64_t plane, const GnGeom& g
     int64_t frame = 0, bc = plane;
     if (g.frames > 1) { bc = plane / g.frames; frame = plane - bc * g.frames; }
     const int64_t channel = bc % g.channels;
-    const int64_t unit = ((bc / g.channels) * g.frames + frame) * g.groups + channel / g.channels_per;
+    const int64_t unit = (g.stat_frames > 1 ? (bc / g.channels) * g.frames + frame : bc / g.channels) * g.groups +
+                         channel / g.channels_per;
     PlaneTerms t;
     t.mean = __ldg(mean + unit);
     t.inv = __ldg(inverse + unit);
@@ -264,7 +266,7 @@ template <bool X_BF16, bool SILU>
 __global__ void __launch_bounds__(kThreads, 4) gn_apply_vec_kernel(const void* __restrict__ x, const void* weight, int w_dt,
                                                                   const void* bias, int b_dt, void* __restrict__ out, GnGeom g,
                                                                   const float* mean, const float* inverse,
-                                                                  int64_t tiles_per_plane, int64_t tile_chunks) {
+                                                                  int64_t tiles_per_plane, int64_t tile_chunks, GnScatter scatter) {
     constexpr int U = 4;
     constexpr int dt = X_BF16 ? VRB_BF16 : VRB_F32;
     const int64_t plane_chunks = g.spatial >> 3;
@@ -285,7 +287,12 @@ __global__ void __launch_bounds__(kThreads, 4) gn_apply_vec_kernel(const void* _
             if (c0 + u * kThreads >= tile_end) break;
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[u][e] = gn_value(v[u][e], k.mean, k.inv, k.gamma, k.beta, dt, SILU ? 1 : 0);
-            store8(out, dt, e_plane + (c0 + u * kThreads) * 8, v[u]);
+            if (scatter.count == 0) {
+                store8(out, dt, e_plane + (c0 + u * kThreads) * 8, v[u]);
+            } else {
+                const int64_t at = plane * scatter.plane_stride + scatter.plane_offset + (c0 + u * kThreads) * 8;
+                for (int d = 0; d < scatter.count; ++d) store8(scatter.dst[d], dt, at, v[u]);
+            }
         }
     }
 }
@@ -304,7 +311,7 @@ __global__ void __launch_bounds__(kThreads) gn_apply_kernel(const void* x, int d
 int make_geom(GnGeom& g, int64_t batch, int64_t channels, int64_t spatial, int groups, const char* what, int64_t frames = 1) {
     VRB_REQUIRE(batch > 0 && channels > 0 && spatial > 0 && groups > 0 && channels % groups == 0 && frames > 0, VRB_ERR_INVALID,
                 "%s: group norm shape/groups mismatch", what);
-    g.batch = batch; g.channels = channels; g.spatial = spatial; g.groups = groups; g.frames = frames;
+    g.batch = batch; g.channels = channels; g.spatial = spatial; g.groups = groups; g.frames = frames; g.stat_frames = frames;
     g.channels_per = static_cast<int>(channels / groups);
     g.count = g.channels_per * spatial;
     g.units = batch * frames * groups;
@@ -346,23 +353,27 @@ int run_moments(const void* x, int dt, const GnGeom& g, const float* shift, doub
 }
 
 int run_apply(const void* x, int dt, const void* weight, int w_dt, const void* bias, int b_dt, void* out,
-              const GnGeom& g, const float* mean, const float* inverse, int silu, cudaStream_t s) {
+              const GnGeom& g, const float* mean, const float* inverse, int silu, cudaStream_t s,
+              const GnScatter& scatter = GnScatter{}) {
     const bool vec = g.spatial % 8 == 0 && aligned16(x) && aligned16(out);
     const int64_t total = g.units * g.count;
     if (vec) {
         if (dt == VRB_BF16 && silu && total >= kLutMinElements && total / 8 < (int64_t{1} << 31))   // SiLU of a bf16 value: table lookup
             return launch_group_norm_apply_silu_lut(x, weight, w_dt, bias, b_dt, out, g.batch * g.channels * g.frames, g.channels,
-                                                    g.channels_per, g.groups, g.frames, g.spatial, mean, inverse, s);
+                                                    g.channels_per, g.groups, g.frames, g.stat_frames, g.spatial, mean, inverse,
+                                                    scatter, s);
         const int64_t plane_chunks = g.spatial / 8;
         const int64_t tiles_per_plane = (plane_chunks + kThreads * 4 - 1) / (kThreads * 4);
         const int64_t tile_chunks = ((plane_chunks + tiles_per_plane - 1) / tiles_per_plane + 7) & ~int64_t{7};   // tiles start on 128-byte lines
         const int grid = grid_for(g.batch * g.channels * g.frames * tiles_per_plane, 4);
 #define VRB_GN_APPLY(BF, SI) gn_apply_vec_kernel<BF, SI><<<grid, kThreads, 0, s>>>( \
-            x, weight, w_dt, bias, b_dt, out, g, mean, inverse, tiles_per_plane, tile_chunks)
+            x, weight, w_dt, bias, b_dt, out, g, mean, inverse, tiles_per_plane, tile_chunks, scatter)
         if (dt == VRB_BF16) { if (silu) VRB_GN_APPLY(true, true); else VRB_GN_APPLY(true, false); }
         else { if (silu) VRB_GN_APPLY(false, true); else VRB_GN_APPLY(false, false); }
 #undef VRB_GN_APPLY
     } else {
+        VRB_REQUIRE(scatter.count == 0, VRB_ERR_UNSUPPORTED,
+                    "group_norm_apply_scatter: needs a local plane size that is a multiple of 8 and 16-byte aligned tensors");
         gn_apply_kernel<<<grid_for((total + kThreads - 1) / kThreads, 8), kThreads, 0, s>>>(
             x, dt, weight, w_dt, bias, b_dt, out, g, mean, inverse, silu);
     }
@@ -578,6 +589,34 @@ extern "C" int vrb_group_norm_apply(const void* x, int dtype, const void* weight
     GnGeom g;
     if (int rc = make_geom(g, batch, channels, spatial_local, groups, "group_norm_apply")) return rc;
     return run_apply(x, dtype, weight, weight_dtype, bias, bias_dtype, out, g, mean, inverse, fuse_silu, as_stream(stream));
+}
+
+extern "C" int vrb_group_norm_apply_scatter(const void* x, int dtype, const void* weight, int weight_dtype,
+                                            const void* bias, int bias_dtype, void* const* destinations, int destination_count,
+                                            int64_t batch, int64_t channels, int64_t frames, int64_t spatial_local,
+                                            int64_t spatial_full, int64_t spatial_offset, int groups,
+                                            const float* mean, const float* inverse, int fuse_silu, vrb_stream stream) {
+    VRB_REQUIRE(x && destinations && mean && inverse, VRB_ERR_INVALID, "group_norm_apply_scatter: null tensor");
+    VRB_REQUIRE(destination_count >= 1 && destination_count <= 8, VRB_ERR_INVALID,
+                "group_norm_apply_scatter: 1 to 8 destinations");
+    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "group_norm_apply_scatter: dtype must be F32 or BF16");
+    VRB_REQUIRE(spatial_offset >= 0 && spatial_local > 0 && spatial_offset + spatial_local <= spatial_full &&
+                    spatial_offset % 8 == 0 && spatial_full % 8 == 0,
+                VRB_ERR_INVALID, "group_norm_apply_scatter: the slice must lie inside the full plane on an 8-element boundary");
+    GnGeom g;
+    if (int rc = make_geom(g, batch, channels, spatial_local, groups, "group_norm_apply_scatter", frames)) return rc;
+    g.stat_frames = 1;   // mean / inverse are per (batch entry, group): the frames only split the planes
+    GnScatter scatter{};
+    scatter.count = destination_count;
+    scatter.plane_stride = spatial_full;
+    scatter.plane_offset = spatial_offset;
+    for (int k = 0; k < destination_count; ++k) {
+        VRB_REQUIRE(destinations[k] != nullptr && aligned16(destinations[k]), VRB_ERR_INVALID,
+                    "group_norm_apply_scatter: destinations must be non-null and 16-byte aligned");
+        scatter.dst[k] = destinations[k];
+    }
+    return run_apply(x, dtype, weight, weight_dtype, bias, bias_dtype, scatter.dst[0], g, mean, inverse, fuse_silu,
+                     as_stream(stream), scatter);
 }
 
 extern "C" int vrb_rms_norm_axis(const void* x, int dtype, const void* weight, int weight_dtype, void* out,

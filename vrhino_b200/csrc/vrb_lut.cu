@@ -145,8 +145,8 @@ __global__ void __launch_bounds__(kLutThreads, 1) swiglu_lut_kernel(const uint4*
 __global__ void __launch_bounds__(kLutThreads, 1) gn_apply_silu_lut_kernel(
     const uint4* __restrict__ x, uint4* __restrict__ out, const void* __restrict__ weight, int w_dt,
     const void* __restrict__ bias, int b_dt, const float* __restrict__ mean, const float* __restrict__ inverse,
-    int64_t planes, int64_t channels, int channels_per, int groups, int64_t frames, int64_t plane_chunks,
-    int64_t tiles_per_plane, int64_t tile_chunks, const uint4* __restrict__ ready) {
+    int64_t planes, int64_t channels, int channels_per, int groups, int64_t frames, int64_t stat_frames, int64_t plane_chunks,
+    int64_t tiles_per_plane, int64_t tile_chunks, GnScatter scatter, const uint4* __restrict__ ready) {
     extern __shared__ __align__(16) uint16_t table[];
     fill_table<VRB_SILU>(table, ready, 0.f, 0.f);
     constexpr int U = 4;
@@ -161,7 +161,8 @@ __global__ void __launch_bounds__(kLutThreads, 1) gn_apply_silu_lut_kernel(
         unsigned frame = 0, bc = plane;
         if (nframes > 1) { bc = plane / nframes; frame = plane - bc * nframes; }
         const unsigned batch_entry = bc / nchannels, channel = bc - batch_entry * nchannels;
-        const unsigned unit = (batch_entry * nframes + frame) * static_cast<unsigned>(groups) + channel / static_cast<unsigned>(channels_per);
+        const unsigned unit = (stat_frames > 1 ? batch_entry * nframes + frame : batch_entry) * static_cast<unsigned>(groups) +
+                              channel / static_cast<unsigned>(channels_per);
         const float m = __ldg(mean + unit), inv = __ldg(inverse + unit);
         const float gamma = weight ? round_to(VRB_BF16, load1(weight, w_dt, channel)) : 1.0f;
         const float beta = bias ? round_to(VRB_BF16, load1(bias, b_dt, channel)) : 0.0f;
@@ -183,7 +184,13 @@ __global__ void __launch_bounds__(kLutThreads, 1) gn_apply_silu_lut_kernel(
                 const float yhi = __fmaf_rn(__fmul_rn(__fsub_rn(hi, m), inv), gamma, beta);
                 o[k] = lookup2(table, pack_bf16x2(ylo, yhi));
             }
-            __stcs(po + c0 + u * kLutThreads, make_uint4(o[0], o[1], o[2], o[3]));
+            const uint4 packed = make_uint4(o[0], o[1], o[2], o[3]);
+            if (scatter.count == 0) {
+                __stcs(po + c0 + u * kLutThreads, packed);
+            } else {
+                const int64_t at = (static_cast<int64_t>(plane) * scatter.plane_stride + scatter.plane_offset) / 8 + c0 + u * kLutThreads;
+                for (int k = 0; k < scatter.count; ++k) __stcs(static_cast<uint4*>(scatter.dst[k]) + at, packed);
+            }
         }
     }
 }
@@ -290,7 +297,8 @@ int launch_swiglu_lut(const void* proj, void* out, int64_t rows, int64_t hidden,
 
 int launch_group_norm_apply_silu_lut(const void* x, const void* weight, int w_dt, const void* bias, int b_dt, void* out,
                                      int64_t planes, int64_t channels, int channels_per, int groups, int64_t frames,
-                                     int64_t spatial, const float* mean, const float* inverse, cudaStream_t stream) {
+                                     int64_t stat_frames, int64_t spatial, const float* mean, const float* inverse,
+                                     const GnScatter& scatter, cudaStream_t stream) {
     static bool done[64] = {false};
     if (int rc = reserve_table(gn_apply_silu_lut_kernel, done)) return rc;
     const int64_t plane_chunks = spatial / 8;
@@ -300,7 +308,8 @@ int launch_group_norm_apply_silu_lut(const void* x, const void* weight, int w_dt
     const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
     gn_apply_silu_lut_kernel<<<grid, kLutThreads, kTableBytes, stream>>>(
         static_cast<const uint4*>(x), static_cast<uint4*>(out), weight, w_dt, bias, b_dt, mean, inverse, planes, channels,
-        channels_per, groups, frames, plane_chunks, tiles_per_plane, tile_chunks, ready_table<VRB_SILU>(0.f, 0.f, stream));
+        channels_per, groups, frames, stat_frames, plane_chunks, tiles_per_plane, tile_chunks, scatter,
+        ready_table<VRB_SILU>(0.f, 0.f, stream));
     return after_launch("group_norm apply (table)");
 }
 

@@ -93,7 +93,40 @@ class KernelMoments:
         return out
 
 
-def sharded_group_norm(pieces, x_local, groups, weight, bias, eps, silu=True, group=None, gather_dim=None):
+    def apply_scatter(self, x, groups, weight, bias, mean, inv, silu, destinations, rows_full, row0):
+        """Normalise this rank's H-slice x [N, C, T, h_local, W] and store it into every tensor of
+        `destinations` (data pointers of full [N, C, T, rows_full, W] tensors: this GPU's own and the
+        peer-mapped ones) at rows [row0, row0 + h_local)."""
+        P = ctypes.c_void_p
+        n, c, t, h, w = x.shape
+        ptrs = (ctypes.c_void_p * len(destinations))(*destinations)
+        wp = None if weight is None else P(weight.data_ptr())
+        bp = None if bias is None else P(bias.data_ptr())
+        self._lib.call("vrb_group_norm_apply_scatter", P(x.data_ptr()), self._code(x), wp, 0 if weight is None else self._code(weight),
+                       bp, 0 if bias is None else self._code(bias), ptrs, len(destinations), n, c, t, h * w, rows_full * w, row0 * w,
+                       groups, P(mean.data_ptr()), P(inv.data_ptr()), int(silu),
+                       ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+
+
+class PeerOutput:
+    """The full output tensor of every rank, mapped into every rank (torch symmetric memory):
+    the normalise kernel of each rank stores its H-slice straight into all of them, so no
+    all-gather and no placement copy follow.  `ready()` orders the ranks on the current stream."""
+
+    def __init__(self, shape, dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.tensor = symm.empty(*shape, dtype=dtype, device=device)
+        self.handle = symm.rendezvous(self.tensor, self.group)
+        self.pointers = [int(p) for p in self.handle.buffer_ptrs]
+        self._flag = torch.zeros(1, device=device)
+
+    def ready(self):
+        dist.all_reduce(self._flag, group=self.group)   # every rank's kernel precedes its contribution
+
+
+def sharded_group_norm(pieces, x_local, groups, weight, bias, eps, silu=True, group=None, gather_dim=None, peer_out=None,
+                       row0=0):
     """GroupNorm(+SiLU) of a tensor whose spatial extent is split over the ranks of `group`.
 
     x_local: this rank's slice [N, C, ...] (contiguous).  Returns the normalised slice, or, with
@@ -110,6 +143,11 @@ def sharded_group_norm(pieces, x_local, groups, weight, bias, eps, silu=True, gr
     if world > 1:
         dist.all_reduce(moments, op=dist.ReduceOp.SUM, group=group)
     mean, inv = pieces.finalize(moments, shift, eps)
+    if peer_out is not None:
+        # the "gather" happens in the normalise kernel's stores (peer memory over NVLink)
+        pieces.apply_scatter(x_local, groups, weight, bias, mean, inv, silu, peer_out.pointers, peer_out.tensor.shape[3], row0)
+        peer_out.ready()
+        return peer_out.tensor
     out = pieces.apply(x_local, groups, weight, bias, mean, inv, silu)
     if gather_dim is None or world == 1:
         return out
@@ -146,3 +184,64 @@ def sharded_cfg_euler(be, ops, policy, sample, unconditional, conditional, scale
     full = torch.empty(n, dtype=sample.dtype, device=sample.device)
     dist.all_gather_into_tensor(full, local, group=group)
     return full.reshape(sample.shape)
+
+
+def _main():
+    """torchrun ... -m vrhino_b200.sharded [--frames T] [--steps K]
+
+    GroupNorm(32) + SiLU on [1, 256, T, 240, 424] bf16 split along H over the ranks: device time of
+    the local work + the statistics all-reduce ("compute"), and of the same followed by the
+    all-gather of the output ("compute+gather"); max over ranks, CUDA events."""
+    import argparse
+    import os
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--frames", type=int, default=28)
+    ap.add_argument("--steps", type=int, default=10)
+    a = ap.parse_args()
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from . import ops
+    be = ops.B200Backend(device=f"cuda:{local}")
+    pieces = KernelMoments(be)
+    h0, h1 = h_range(240, rank, world)
+    g = torch.Generator(device="cuda").manual_seed(rank)
+    x = (torch.randn((1, 256, a.frames, h1 - h0, 424), device="cuda", generator=g) * 2.0).to(torch.bfloat16)
+    gamma, beta = torch.ones(256, device="cuda"), torch.zeros(256, device="cuda")
+
+    peer = PeerOutput((1, 256, a.frames, 240, 424), torch.bfloat16, torch.device("cuda", local)) if world > 1 else None
+
+    def timed(gather):
+        def step():
+            if gather == "peer":
+                return sharded_group_norm(pieces, x, 32, gamma, beta, 1e-6, True, None, None, peer, h0)
+            return sharded_group_norm(pieces, x, 32, gamma, beta, 1e-6, True, None, 3 if gather and world > 1 else None)
+        for _ in range(3):
+            step()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / a.steps], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    compute, both = timed(False), timed(True)
+    fused = timed("peer") if world > 1 else compute
+    if rank == 0:
+        full_bytes = 256 * a.frames * 240 * 424 * 6
+        print(f"n_gpus {world}  H rows per rank {h1 - h0}  compute {compute * 1e3:.1f} us ({full_bytes / compute / 1e6:.0f} GB/s aggregate)"
+              f"  compute + NCCL all-gather + placement {both * 1e3:.1f} us  compute with peer stores {fused * 1e3:.1f} us")
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    _main()
