@@ -233,7 +233,8 @@ def test_rope_no_contraction_kat(gpu):
 
 @pytest.mark.parametrize("out_dt", DTYPES)
 @pytest.mark.parametrize("kind,rows,inner,group", [("fp8_e4m3fn", 6, 8, 4), ("fp8_e4m3fn", 16, 256, 256), ("fp8_e4m3fn", 5, 96, 32),
-                                                   ("fp8_e4m3fn", 3, 40, 8), ("int8", 16, 256, 64), ("int8", 3, 10, 5), ("int4", 4, 16, 8)])
+                                                   ("fp8_e4m3fn", 3, 40, 8), ("int8", 16, 256, 64), ("int8", 3, 10, 5), ("int4", 4, 16, 8),
+                                                   ("int4", 6, 1024, 1024), ("int4", 5, 1088, 64), ("int4", 3, 96, 32)])
 def test_dequantize_bit_exact(orc, gpu, out_dt, kind, rows, inner, group):
     import torch
     be, ops = gpu

@@ -479,6 +479,51 @@ __global__ void __launch_bounds__(kThreads, 4) dequant_tile_kernel(const uint4* 
         }
     }
 }
+// INT4 (two's complement nibbles, low nibble first, :641-658 with Kind 2): 32 codes per 16-byte
+// load, same row tiles.  inner % 32 == 0 and group_size % 32 == 0.
+template <bool OUT_BF16, bool ROW_SCALE>
+__global__ void __launch_bounds__(kThreads, 4) dequant_int4_tile_kernel(const uint4* __restrict__ packed, const float* __restrict__ scales,
+                                                                       void* __restrict__ out, int64_t rows, int64_t inner_chunks,
+                                                                       int64_t groups, int group_chunks, int64_t tiles_per_row,
+                                                                       int64_t tile_chunks) {
+    const int64_t tiles = rows * tiles_per_row;
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t row = t / tiles_per_row;
+        const int64_t tile_begin = (t - row * tiles_per_row) * tile_chunks;
+        const int64_t tile_end = tile_begin + tile_chunks < inner_chunks ? tile_begin + tile_chunks : inner_chunks;
+        for (int64_t c = tile_begin + threadIdx.x; c < tile_end; c += kThreads) {
+            const uint4 raw = __ldcs(packed + row * inner_chunks + c);
+            const float scale = __ldg(scales + (ROW_SCALE ? row : row * groups + static_cast<int>(c) / group_chunks));
+            const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+            const int64_t e0 = (row * inner_chunks + c) * 32;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                float v[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int q = static_cast<int>(words[w] << (28 - 4 * k)) >> 28;   // sign-extended nibble k
+                    v[k] = __fmul_rn(static_cast<float>(q), scale);
+                }
+                store8(out, OUT_BF16 ? VRB_BF16 : VRB_F32, e0 + w * 8, v);
+            }
+        }
+    }
+}
+void launch_dequant_int4_tiles(const uint8_t* packed, const float* scales, void* out, int out_dtype, int64_t rows, int64_t inner,
+                               int64_t groups, int64_t group_size, cudaStream_t s) {
+    const int64_t inner_chunks = inner / 32;
+    const int64_t tiles_per_row = (inner_chunks + kThreads * 2 - 1) / (kThreads * 2);
+    const int64_t tile_chunks = ((inner_chunks + tiles_per_row - 1) / tiles_per_row + 7) & ~int64_t{7};
+    const int grid = grid_for(rows * tiles_per_row, 8);
+    const uint4* p = reinterpret_cast<const uint4*>(packed);
+    const int gc = static_cast<int>(group_size / 32);
+#define VRB_DQ4(BF, ROW) dequant_int4_tile_kernel<BF, ROW><<<grid, kThreads, 0, s>>>( \
+        p, scales, out, rows, inner_chunks, groups, gc, tiles_per_row, tile_chunks)
+    if (out_dtype == VRB_BF16) { if (groups == 1) VRB_DQ4(true, true); else VRB_DQ4(true, false); }
+    else { if (groups == 1) VRB_DQ4(false, true); else VRB_DQ4(false, false); }
+#undef VRB_DQ4
+}
+
 template <int KIND>
 void launch_dequant_tiles(const uint8_t* packed, const float* scales, void* out, int out_dtype, int64_t rows, int64_t inner,
                           int64_t groups, int64_t group_size, cudaStream_t s) {
@@ -749,7 +794,11 @@ extern "C" int vrb_dequantize(int kind, const void* packed, const float* scales,
     cudaStream_t s = as_stream(stream);
     const bool vec = kind != VRB_Q_INT4 && inner % 16 == 0 && group_size % 16 == 0 && inner / 16 < 0x7fffffff && aligned16(packed) &&
                      aligned16(out);
-    if (vec) {
+    const bool vec4 = kind == VRB_Q_INT4 && inner % 32 == 0 && group_size % 32 == 0 && inner / 32 < 0x7fffffff &&
+                      aligned16(packed) && aligned16(out);
+    if (vec4) {
+        launch_dequant_int4_tiles(p, scales, out, out_dtype, rows, inner, groups, group_size, s);
+    } else if (vec) {
         if (kind == VRB_Q_FP8_E4M3FN) launch_dequant_tiles<VRB_Q_FP8_E4M3FN>(p, scales, out, out_dtype, rows, inner, groups, group_size, s);
         else launch_dequant_tiles<VRB_Q_INT8>(p, scales, out, out_dtype, rows, inner, groups, group_size, s);
     } else {
