@@ -222,6 +222,14 @@ int vrb_rms_norm_rope(const void* x, int x_dtype, const void* weight, int weight
                       int64_t rows, int64_t width, int64_t norm_width, float eps,
                       vrb_stream stream);
 
+/* vrb_rms_norm_rope with cos / sin tables in `table_dtype` (F32 or BF16; rope_kernel :1200-1215 widens
+ * BF16 frequencies exactly): the LTX graph keeps its tables in the execution dtype
+ * (native/src/architectures/ltx_self_attention_graph.cpp:52-54). */
+int vrb_rms_norm_rope_tables(const void* x, int x_dtype, const void* weight, int weight_dtype,
+                             const void* cosine, const void* sine, int table_dtype, int64_t f_rows,
+                             int64_t f_width, int64_t rows_per_f_row, void* out, int out_dtype,
+                             int64_t rows, int64_t width, int64_t norm_width, float eps, vrb_stream stream);
+
 /* gated_residual (common.cpp:139-144) and, with gate == NULL, residual_add (:134-138):
  * out = T(residual) + round_T(T(branch) * T(gate)), T = state_dtype.  gate is
  * [gate_vectors, width]; row r uses vector (r / rows_per_vector) % gate_vectors. */

@@ -100,6 +100,17 @@ class RefHost:
                                             _c.c_float(scale), _c.c_float(delta)))
         return guided, out
 
+    def fusion_plan(self, which, contract, diagnostics=False, tokens=64):
+        """Chains vrhino_b200::plan_fusion finds in the reference's production graphs.  which: "wan" |
+        "ltx"; contract: "f32" | "bf16_f32_hidden" | "bf16".  Returns a dict of counts."""
+        out = (_c.c_int * 6)()
+        rc = self.lib.refh_fusion_plan({"wan": 0, "ltx": 1}[which], {"f32": 0, "bf16_f32_hidden": 1, "bf16": 2}[contract],
+                                       int(diagnostics), _c.c_int64(tokens), out)
+        if rc != 0:
+            raise RuntimeError(self.lib.refh_last_error().decode())
+        keys = ("layer_norm_modulate", "rms_norm_modulate", "rms_norm_rope", "gated_residual", "nodes_total", "nodes_absorbed")
+        return dict(zip(keys, out))
+
     def wan_chain_seconds(self, tokens, threads, steps, dim=1536, heads=12, ffn=8960, text=512, seed=0):
         """Seconds per step of the Wan block chain on `tokens` rows, and its algorithmic bytes
         (same accounting as the GPU arm, bf16-hidden contract, so the GB/s are comparable)."""
@@ -222,6 +233,17 @@ class RefCuda:
         if rc != 0:
             raise RuntimeError(self.lib.refc_last_error().decode())
         return list(out), list(stats)
+
+    def ltx_self_attention_graph(self, batch, tokens, hidden_bf16, handles, fused=False):
+        """The reference's production LTX self-attention graph (BF16 execution).  handles: hidden,
+        modulation, cos, sin + 11 parameters.  Returns (first residual handle, stats)."""
+        h = (_c.c_int64 * 15)(*handles)
+        out = (_c.c_int64 * 1)()
+        stats = (_c.c_int * 5)()
+        rc = self.lib.refc_ltx_self_attention_graph(_c.c_int64(batch), _c.c_int64(tokens), int(hidden_bf16), h, int(fused), out, stats)
+        if rc != 0:
+            raise RuntimeError(self.lib.refc_last_error().decode())
+        return out[0], list(stats)
 
     def wan_chain_graph(self, tokens, width, heads, hidden_dtype, eps, handles, fused=False):
         """Evaluates the non-GEMM part of the Wan self-attention graph (built node for node in

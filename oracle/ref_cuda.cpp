@@ -27,6 +27,7 @@
 #include "vrhino/tensor_util.h"
 #include "runtime/neural_graph.h"
 #include "architectures/wan_self_attention_graph.h"
+#include "architectures/ltx_self_attention_graph.h"
 #ifdef VRB_DROPIN
 #include "b200_backend.h"
 #include "graph_fusion.h"
@@ -370,6 +371,36 @@ int refc_wan_self_attention_graph(int64_t s, int64_t width, int64_t heads, const
             results = neural_graph::evaluate(*g_backend, graph, inputs, parameters);
         }
         for (size_t i = 0; i < results.size(); ++i) out[i] = keep(results[i]);
+        return int64_t{0};
+    }));
+}
+
+// The reference's production LTX self-attention graph (ltx_self_attention_graph.cpp:10-82; width
+// 2048, 32 heads), GEMMs and attention included.  handles: hidden, modulation, cos, sin, then the 11
+// parameters in the header's order, on the device in the dtypes the BF16 contracts declare.
+int refc_ltx_self_attention_graph(int64_t b, int64_t s, int hidden_bf16, const int64_t* handles, int fused, int64_t* out,
+                                  int* stats) {
+    return static_cast<int>(guarded([&] {
+        const auto contract = hidden_bf16 ? ltx_internal::SelfAttentionContract::BF16Hidden
+                                          : ltx_internal::SelfAttentionContract::BF16F32Hidden;
+        const auto graph = ltx_internal::self_attention_graph(b, s, 1, false, false, contract);
+        std::vector<Tensor> inputs, parameters;
+        for (int i = 0; i < 4; ++i) inputs.push_back(at(handles[i]));
+        for (int i = 4; i < 15; ++i) parameters.push_back(at(handles[i]));
+        std::vector<Tensor> results;
+        if (fused) {
+#ifdef VRB_DROPIN
+            vrhino_b200::FusionStats fs;
+            results = vrhino_b200::evaluate_fused(*g_backend, graph, inputs, parameters, &fs);
+            if (stats) { stats[0] = fs.rms_norm_modulate; stats[1] = fs.rms_norm_rope; stats[2] = fs.gated_residual;
+                         stats[3] = fs.nodes_total; stats[4] = fs.nodes_absorbed; }
+#else
+            throw Error("the fused evaluator exists only in the drop-in build");
+#endif
+        } else {
+            results = neural_graph::evaluate(*g_backend, graph, inputs, parameters);
+        }
+        out[0] = keep(results[0]);
         return int64_t{0};
     }));
 }

@@ -15,6 +15,9 @@
 #include <vector>
 
 #include "family_lowering_test_backend.h"
+#include "architectures/ltx_self_attention_graph.h"
+#include "architectures/wan_self_attention_graph.h"
+#include "graph_fusion.h"
 #include "vrhino/architecture.h"
 #include "vrhino/precision.h"
 #include "vrhino/sampling.h"
@@ -152,6 +155,30 @@ double refh_wan_chain_seconds(const float* x, const float* q, const float* k, co
     }
     const double seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
     return failed ? -1.0 : seconds / (steps > 0 ? steps : 1);
+}
+
+
+// ---- graph fusion plan on the reference's production graphs (analysis only, no device) ------
+// which: 0 Wan self-attention graph (wan_self_attention_graph.h), 1 LTX (ltx_self_attention_graph.cpp).
+// contract: 0 F32, 1 BF16 execution with F32 hidden state, 2 BF16 execution with BF16 hidden state.
+// out: {layer_norm_modulate, rms_norm_modulate, rms_norm_rope, gated_residual, nodes_total, nodes_absorbed}.
+int refh_fusion_plan(int which, int contract, int diagnostics, int64_t tokens, int* out) {
+    try {
+        const DType execution = contract == 0 ? DType::F32 : DType::BF16;
+        const DType hidden = contract == 2 ? DType::BF16 : DType::F32;
+        vrhino_b200::FusionPlan plan;
+        if (which == 0) {
+            plan = vrhino_b200::plan_fusion(wan_internal::self_attention_graph(1, tokens, execution, hidden, diagnostics != 0).description());
+        } else {
+            const auto c = contract == 0 ? ltx_internal::SelfAttentionContract::F32
+                         : contract == 1 ? ltx_internal::SelfAttentionContract::BF16F32Hidden
+                                         : ltx_internal::SelfAttentionContract::BF16Hidden;
+            plan = vrhino_b200::plan_fusion(ltx_internal::self_attention_graph(2, tokens, 1, diagnostics != 0, false, c).description());
+        }
+        out[0] = plan.stats.layer_norm_modulate; out[1] = plan.stats.rms_norm_modulate; out[2] = plan.stats.rms_norm_rope;
+        out[3] = plan.stats.gated_residual; out[4] = plan.stats.nodes_total; out[5] = plan.stats.nodes_absorbed;
+        return 0;
+    } catch (const std::exception& e) { g_error = e.what(); return -1; }
 }
 
 }  // extern "C"

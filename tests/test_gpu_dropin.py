@@ -229,6 +229,46 @@ def test_production_wan_graph_with_fusion(orc, dropin):
     assert diff.mean() <= 2e-3 and diff.max() <= 5e-2, (float(diff.mean()), float(diff.max()))
 
 
+@pytest.mark.parametrize("hidden", ["f32", "bf16"])
+def test_production_ltx_graph_with_fusion(orc, dropin, hidden):
+    """The reference's production LTX self-attention graph (width 2048, 32 heads; RMSNorm-modulate,
+    q/k RMSNorm + RoPE with whole-row bf16 tables, gated residual; GEMMs and attention in the
+    reference's code) for 2 x 96 tokens: reference evaluator on its CUDA backend against
+    evaluate_fused on the replaced backend.  Statistical bound as for the Wan graph."""
+    from oracle import ref
+    from vrhino_b200 import synth
+    if not ref.available_cuda():
+        pytest.skip("reference CUDA library not built")
+    B, S, W = 2, 96, 2048
+    n = lambda shape, st, mean=0.0, std=1.0: synth.normal(shape, mean, std, seed=55, stream=st)
+    phase = synth.uniform_range((B, S, W // 2), -3.0, 3.0, seed=55, stream=20)
+    cos, sin = np.repeat(np.cos(phase), 2, axis=-1).astype(np.float32), np.repeat(np.sin(phase), 2, axis=-1).astype(np.float32)
+    lin = 1.0 / np.sqrt(W)
+    host = [
+        (n((B, S, W), 0), hidden), (n((B, 1, 6 * W), 1, 0, 0.1), "f32"), (cos, "bf16"), (sin, "bf16"),
+        (n((6, W), 2, 0, 0.1), "bf16"),
+        (n((W, W), 3, 0, lin), "bf16"), (n((W,), 4, 0, 0.02), "bf16"), (n((W, W), 5, 0, lin), "bf16"), (n((W,), 6, 0, 0.02), "bf16"),
+        (n((W, W), 7, 0, lin), "bf16"), (n((W,), 8, 0, 0.02), "bf16"),
+        (n((W,), 9, 1.0, 0.1), "bf16"), (n((W,), 10, 1.0, 0.1), "bf16"),
+        (n((W, W), 11, 0, lin), "bf16"), (n((W,), 12, 0, 0.02), "bf16"),
+    ]
+    code = {"f32": ref.F32, "bf16": ref.BF16}
+
+    def run(backend, fused):
+        handles = [backend.upload(cases.to_bits(a, dt), code[dt]) for a, dt in host]
+        out, stats = backend.ltx_self_attention_graph(B, S, hidden == "bf16", handles, fused=fused)
+        residual, _ = backend.download(out, (B, S, W))
+        backend.clear()
+        return residual, stats
+
+    want, _ = run(ref.RefCuda(), False)
+    got, stats = run(dropin, True)
+    assert stats[:3] == [1, 2, 1], stats
+    assert np.isfinite(want).all() and np.abs(want).max() > 0.5
+    diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert diff.mean() <= 2e-3 and diff.max() <= 5e-2, (float(diff.mean()), float(diff.max()))
+
+
 def test_errors_and_session_semantics(dropin):
     """Same texts as the reference's wrappers; a rejected argument in an unguarded operator
     (layer_norm) leaves the session usable, one in a guarded operator (clamp) retires it, after

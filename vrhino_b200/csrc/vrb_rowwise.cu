@@ -334,6 +334,15 @@ extern "C" int vrb_rms_norm_rope(const void* x, int x_dtype, const void* weight,
                                  int64_t rows_per_f_row, void* out, int out_dtype,
                                  int64_t rows, int64_t width, int64_t norm_width, float eps,
                                  vrb_stream stream) {
+    return vrb_rms_norm_rope_tables(x, x_dtype, weight, weight_dtype, cosine, sine, VRB_F32, f_rows, f_width, rows_per_f_row,
+                                    out, out_dtype, rows, width, norm_width, eps, stream);
+}
+
+extern "C" int vrb_rms_norm_rope_tables(const void* x, int x_dtype, const void* weight, int weight_dtype,
+                                        const void* cosine, const void* sine, int table_dtype, int64_t f_rows,
+                                        int64_t f_width, int64_t rows_per_f_row, void* out, int out_dtype,
+                                        int64_t rows, int64_t width, int64_t norm_width, float eps, vrb_stream stream) {
+    VRB_REQUIRE(is_float_dtype(table_dtype), VRB_ERR_UNSUPPORTED, "rms_norm_rope: tables must be F32 or BF16");
     VRB_REQUIRE(weight != nullptr, VRB_ERR_UNSUPPORTED, "BF16-to-FP32 rms_norm requires affine weight");
     VRB_REQUIRE((cosine == nullptr) == (sine == nullptr), VRB_ERR_INVALID, "RoPE frequency mismatch");
     VRB_REQUIRE(norm_width > 0 && width % norm_width == 0, VRB_ERR_INVALID,
@@ -347,7 +356,7 @@ extern "C" int vrb_rms_norm_rope(const void* x, int x_dtype, const void* weight,
     if (cosine) {
         VRB_REQUIRE(f_rows > 0 && f_width > 0 && rows_per_f_row > 0 && width % f_width == 0 && (norm_width % 2) == 0,
                     VRB_ERR_INVALID, "rms_norm_rope: table extents must be positive, f_width must divide width, width even");
-        p.cosine = cosine; p.sine = sine; p.f_dt = VRB_F32;
+        p.cosine = cosine; p.sine = sine; p.f_dt = table_dtype;
         p.f_rows = f_rows; p.f_width = f_width; p.rows_per_f_row = rows_per_f_row;
         p.post = kPostRope;
     }

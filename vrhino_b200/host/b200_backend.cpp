@@ -329,6 +329,22 @@ Tensor B200Backend::layer_norm_modulate(const Tensor& raw, const Tensor* weight_
     });
 }
 
+Tensor B200Backend::rms_norm_modulate(const Tensor& raw, float eps, const Tensor& shift_raw, const Tensor& scale_raw, DType output) {
+    return guarded([&] {
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype);
+        const int64_t width = x.dim(-1), rows = x.numel() / width;
+        Tensor scale = parameter(scale_raw), shift = copy_to_device(shift_raw, scale.dtype());
+        require(shift.numel() == scale.numel(), "modulate: shift and scale must share dtype and shape");
+        int64_t rows_per_vector = 0, vectors = 0;
+        vector_layout(x, scale, rows_per_vector, vectors);
+        Tensor out = rt_->allocate_device(x.shape(), output);
+        check(vrb_rms_norm_modulate(x.data(), code(dtype), scale.data(), shift.data(), code(scale.dtype()), rows_per_vector,
+                                    vectors, out.data(), code(output), rows, width, eps, kLegacyStream));
+        return out;
+    });
+}
+
 Tensor B200Backend::rms_norm_rope(const Tensor& raw, const Tensor* weight_raw, float eps, const Tensor* cos_raw,
                                   const Tensor* sin_raw, int heads, bool per_head_norm, DType output) {
     return guarded([&] {
@@ -339,22 +355,27 @@ Tensor B200Backend::rms_norm_rope(const Tensor& raw, const Tensor* weight_raw, f
         const int64_t norm_width = per_head_norm ? head_width : width;
         if (weight_raw) { weight = parameter(*weight_raw); require(weight.numel() == norm_width, "rms norm weight mismatch"); }
         int64_t f_rows = 0, f_width = 8;
+        DType table_dtype = DType::F32;
         if (cos_raw) {
             require(sin_raw != nullptr, "RoPE frequency mismatch");
-            c = copy_to_device(*cos_raw, DType::F32);
-            s = copy_to_device(*sin_raw, DType::F32);
+            // tables keep their device dtype (F32 or BF16), as rope_nd does (cuda_backend.cu:4201-4203)
+            table_dtype = device_float(*cos_raw) ? cos_raw->dtype() : DType::F32;
+            c = copy_to_device(*cos_raw, table_dtype);
+            s = copy_to_device(*sin_raw, table_dtype);
             require(c.shape() == s.shape(), "RoPE frequency mismatch");
-            require(c.ndim() >= 2 && c.dim(-1) == head_width, "Incompatible broadcast shapes");
-            f_width = c.dim(-1) * c.dim(-2);
-            require(f_width == head_width || f_width == width, "Incompatible broadcast shapes");
+            require(c.ndim() >= 2, "Incompatible broadcast shapes");
+            // [.., S, H|1, d] tables, or [.., S, D] tables spanning the whole row (LTX)
+            f_width = c.dim(-1) == width ? width : c.dim(-1) * c.dim(-2);
+            require((c.dim(-1) == head_width || c.dim(-1) == width) && (f_width == head_width || f_width == width),
+                    "Incompatible broadcast shapes");
             f_rows = c.numel() / f_width;
             require(f_rows == rows || f_rows == rows / x.dim(0), "Incompatible broadcast shapes");
         }
         Tensor out = rt_->allocate_device(x.shape(), output);
-        check(vrb_rms_norm_rope(x.data(), code(dtype), weight_raw ? weight.data() : nullptr,
-                                weight_raw ? code(weight.dtype()) : 0, cos_raw ? c.data() : nullptr,
-                                cos_raw ? s.data() : nullptr, f_rows, f_width, 1, out.data(), code(output), rows, width,
-                                norm_width, eps, kLegacyStream));
+        check(vrb_rms_norm_rope_tables(x.data(), code(dtype), weight_raw ? weight.data() : nullptr,
+                                       weight_raw ? code(weight.dtype()) : 0, cos_raw ? c.data() : nullptr,
+                                       cos_raw ? s.data() : nullptr, code(table_dtype), f_rows, f_width, 1, out.data(),
+                                       code(output), rows, width, norm_width, eps, kLegacyStream));
         return out;
     });
 }

@@ -58,6 +58,8 @@ public:
     // ---- fused forms (one kernel each); see the free functions below for the call-site view --
     Tensor layer_norm_modulate(const Tensor& x, const Tensor* weight, const Tensor* bias, float eps,
                                const Tensor& shift, const Tensor& scale, DType output);
+    // cast(modulate(rms_norm(x, no weight, eps), shift, scale), output) -- the LTX block
+    Tensor rms_norm_modulate(const Tensor& x, float eps, const Tensor& shift, const Tensor& scale, DType output);
     Tensor rms_norm_rope(const Tensor& x, const Tensor* weight, float eps, const Tensor* cosine,
                          const Tensor* sine, int heads, bool per_head_norm, DType output);
     Tensor gated_residual(const Tensor& residual, const Tensor& branch, const Tensor* gate, DType state);

@@ -6,11 +6,13 @@
 // recognises three chains and runs each as ONE kernel of the B200 backend; every other node is
 // dispatched exactly as the reference's evaluator dispatches it.  No architecture file changes.
 //
-//   LayerNorm -> [Cast F32] -> Mul(., Add(1, scale)) -> Add(., shift) -> [Cast execution]
-//                                                              => B200Backend::layer_norm_modulate
-//   RmsNorm(last axis, weight) -> Reshape[B,S,H,d] -> Rope -> Cast execution
-//                                                              => B200Backend::rms_norm_rope
-//   Add([Cast F32] residual, Mul([Cast F32] branch, gate))     => B200Backend::gated_residual
+//   LayerNorm | RmsNorm(no weight) -> [Cast F32] -> Mul(., Add(1, [Cast] scale)) -> Add(., [Cast] shift)
+//       -> [Cast execution]                    => B200Backend::layer_norm_modulate / rms_norm_modulate
+//   RmsNorm(last axis, weight) -> Reshape[B,S,H,d] -> Rope -> Cast execution       (Wan)
+//   RmsNorm(last axis, weight) -> Rope with whole-row tables                        (LTX)
+//                                              => B200Backend::rms_norm_rope
+//   Add([Cast F32] residual, Mul([Cast F32] branch, [Cast F32] gate))
+//                                              => B200Backend::gated_residual
 //
 // A chain is fused only when its interior values have no other consumer and are not graph
 // outputs (so a diagnostics graph, which exports them, runs node by node).
@@ -18,15 +20,35 @@
 
 #include <vector>
 
-#include "b200_backend.h"
+#include <optional>
+
 #include "runtime/neural_graph.h"
 
 namespace vrhino_b200 {
 
+class B200Backend;
+
 struct FusionStats {
-    int layer_norm_modulate = 0, rms_norm_rope = 0, gated_residual = 0;
+    int layer_norm_modulate = 0, rms_norm_modulate = 0, rms_norm_rope = 0, gated_residual = 0;
     int nodes_total = 0, nodes_absorbed = 0;   // absorbed: nodes that no longer launch anything
 };
+
+// The result of the analysis, per node of the Description (no backend involved: this part also
+// builds and runs without CUDA).
+enum class FusedKind { None, LayerNormModulate, RmsNormModulate, RmsNormRope, GatedResidual };
+struct FusedGroup {
+    FusedKind kind = FusedKind::None;
+    vrhino::neural_graph::ValueId x = 0, shift = 0, scale = 0, cosine = 0, sine = 0, residual = 0, branch = 0, gate = 0;
+    std::optional<vrhino::neural_graph::ValueId> weight, bias;
+    float epsilon = 0.0f;
+    int heads = 1;
+};
+struct FusionPlan {
+    std::vector<FusedGroup> anchored;   // per node: the chain that ends (and runs) at this node
+    std::vector<char> absorbed;         // per node: inside a chain, launches nothing itself
+    FusionStats stats;                  // counts of the chains found
+};
+FusionPlan plan_fusion(const vrhino::neural_graph::Description& description);
 
 // Same contract as neural_graph::evaluate: inputs / parameters bound in slot order, host
 // tensors uploaded on demand, outputs in d.outputs order after a synchronize().
