@@ -18,6 +18,12 @@
 // (at most 64 terms, pairwise inside a chunk) and only then widened to double for the
 // cross-thread reduction and the final mean / variance formula.
 //
+// Latency: the exact geometries (production widths) prefetch the next row into a second packed
+// register set while the current one is reduced; everything a row needs besides x -- its RoPE
+// table row, its residual row -- is requested BEFORE the statistics so that it arrives during the
+// reduction instead of stalling the epilogue; vectors shared by all rows (1+scale | shift, LayerNorm
+// weight | bias) are staged once per CTA in shared memory in a bank-conflict-free layout.
+//
 // Reference semantics restated (native/src/backend/cuda/cuda_backend.cu):
 //   layer_norm_parallel_kernel :910-943  sum / sum of squares (double in the reference),
 //       mean = float(S/W), inv = rsqrtf(float(Q/W - double(mean)*mean) + eps),

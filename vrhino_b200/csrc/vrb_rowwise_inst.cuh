@@ -4,6 +4,8 @@
 
 #include "vrb_rowwise.cuh"
 
+#include <mutex>
+
 namespace vrb {
 namespace rowwise {
 
@@ -11,15 +13,23 @@ namespace rowwise {
 // capped by the amount of work; CTAs stride over the rows.
 template <int NCH, int TPR, bool FULL, int NORM, int POST, int DT>
 void launch_one(const RowParams& p, int64_t ctas, size_t smem, cudaStream_t stream) {
-    static int per_sm = 0;
-    static size_t per_sm_smem = ~size_t{0};
-    if (per_sm == 0 || per_sm_smem != smem) {
-        int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, row_kernel<NCH, TPR, FULL, NORM, POST, DT>, kRowThreads, smem) !=
-                cudaSuccess || n < 1)
-            n = 1;
-        per_sm = n;
-        per_sm_smem = smem;
+    // resident CTAs per SM of this instantiation for the last shared-memory size seen; guarded so
+    // that callers on several host threads may launch concurrently
+    static std::mutex mutex;
+    static int cached_per_sm = 0;
+    static size_t cached_smem = ~size_t{0};
+    int per_sm;
+    {
+        std::lock_guard<std::mutex> lock(mutex);
+        if (cached_per_sm == 0 || cached_smem != smem) {
+            int n = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, row_kernel<NCH, TPR, FULL, NORM, POST, DT>, kRowThreads, smem) !=
+                    cudaSuccess || n < 1)
+                n = 1;
+            cached_per_sm = n;
+            cached_smem = smem;
+        }
+        per_sm = cached_per_sm;
     }
     row_kernel<NCH, TPR, FULL, NORM, POST, DT><<<grid_for(ctas, per_sm), kRowThreads, smem, stream>>>(p);
 }
