@@ -433,7 +433,7 @@ __global__ void __launch_bounds__(kThreads, 4) dequant_tile_kernel(const uint4* 
                                                                   void* __restrict__ out, int64_t rows, int64_t inner_chunks,
                                                                   int64_t groups, int group_chunks, int64_t tiles_per_row,
                                                                   int64_t tile_chunks) {
-    constexpr int U = 4;
+    constexpr int U = 2;
     const int64_t tiles = rows * tiles_per_row;
     for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
         const int64_t row = t / tiles_per_row;
@@ -528,7 +528,7 @@ template <int KIND>
 void launch_dequant_tiles(const uint8_t* packed, const float* scales, void* out, int out_dtype, int64_t rows, int64_t inner,
                           int64_t groups, int64_t group_size, cudaStream_t s) {
     const int64_t inner_chunks = inner / 16;
-    const int64_t tiles_per_row = (inner_chunks + kThreads * 4 - 1) / (kThreads * 4);
+    const int64_t tiles_per_row = (inner_chunks + kThreads * 2 - 1) / (kThreads * 2);
     const int64_t tile_chunks = ((inner_chunks + tiles_per_row - 1) / tiles_per_row + 7) & ~int64_t{7};
     const int grid = grid_for(rows * tiles_per_row, 8);
     const uint4* p = reinterpret_cast<const uint4*>(packed);
