@@ -250,6 +250,32 @@ def main():
     except Exception as exc:  # graph capture is an extra measurement, never the headline
         graph_obj = {"error": str(exc)[:200]}
 
+    # ---- the same block with each residual update merged into the LayerNorm that follows it ----
+    # (9 launches; the merged launches read residual + branch and write stream + normalised output,
+    # 4 passes where the two launches they replace make 5, so this form moves fewer bytes: it is
+    # reported in microseconds per block, and in GB/s of the bytes it actually has to move)
+    fused_obj = None
+    try:
+        fused = [l for blk in branches for l in blk.launches(fuse_residual_norm=True)]
+        for _ in range(args.warmup):
+            for l in fused:
+                l.fn()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(args.steps):
+            for l in fused:
+                l.fn()
+        f1.record()
+        barrier()
+        fused_ms = max_over_ranks(f0.elapsed_time(f1)) / args.steps
+        fused_bytes = sum(l.bytes for l in fused)
+        fused_obj = {"ms_per_step": fused_ms, "us_per_dit_block": fused_ms * 1e3, "launches_per_step": len(fused),
+                     "bytes_per_step": fused_bytes, "value": world * fused_bytes / (fused_ms * 1e-3) / 1e9, "unit": UNIT}
+        del fused
+    except Exception as exc:  # an extra measurement, never the headline
+        fused_obj = {"error": str(exc)[:200]}
+
     # ---- strong scaling: one batch split by tokens over the ranks ------------------------------
     strong = None
     if world > 1:
@@ -330,6 +356,8 @@ def main():
         }
         if graph_obj:
             line["cuda_graph_replay"] = graph_obj
+        if fused_obj:
+            line["residual_norm_merged"] = fused_obj
         if strong:
             line["strong"] = strong
         if cpu:

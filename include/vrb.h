@@ -179,6 +179,23 @@ int vrb_group_norm_apply_scatter(const void* x, int dtype, const void* weight, i
 /* Each fused form produces what the cited chain of separate reference kernels produces,
  * including every intermediate rounding, while reading each tensor once. */
 
+/* gated_residual / residual_add (common.cpp:134-144) followed by the LayerNorm the block applies
+ * to the updated stream next, with or without adaLN modulation (wan.cpp:95-110), in one pass:
+ *   state_out = residual + branch * gate          (gate NULL: residual + branch), in state_dtype
+ *   out       = cast(modulate(layer_norm(state_out, weight, bias, eps), shift, scale), out_dtype)
+ *               (scale NULL: cast(layer_norm(...), out_dtype))
+ * Every rounding of the unfused chain is kept.  One kernel when the stream is BF16 throughout
+ * (each tensor crosses HBM once: 8 B per element instead of 6 + 4); other dtype contracts run
+ * the two operators one after the other.  gate is [gate_vectors, width], scale / shift
+ * [mod_vectors, width]. */
+int vrb_gated_residual_layer_norm_modulate(
+    const void* residual, int residual_dtype, const void* branch, int branch_dtype,
+    const void* gate, int gate_dtype, int64_t gate_rows_per_vector, int64_t gate_vectors,
+    void* state_out, int state_dtype,
+    const void* weight, int weight_dtype, const void* bias, int bias_dtype,
+    const void* scale, const void* shift, int mod_dtype, int64_t rows_per_vector, int64_t mod_vectors,
+    void* out, int out_dtype, int64_t rows, int64_t width, float eps, vrb_stream stream);
+
 /* layer_norm (:4057) -> modulate (native/src/architectures/common.cpp:51-61) -> cast to
  * out_dtype (the consumer cast, :3674).  scale/shift are [mod_vectors, width]; row r uses
  * vector (r / rows_per_vector) % mod_vectors.  shift may be NULL.  weight/bias may be NULL. */

@@ -269,7 +269,7 @@ class RefDropin(RefCuda):
     def __init__(self, execution_dtype=BF16):
         super().__init__(execution_dtype)
         for name in ("refd_layer_norm_modulate", "refd_rms_norm_rope", "refd_gated_residual", "refd_swiglu",
-                     "refd_group_norm_silu", "refd_cfg_euler"):
+                     "refd_group_norm_silu", "refd_cfg_euler", "refd_gated_residual_layer_norm"):
             getattr(self.lib, name).restype = _c.c_int64
 
     def name(self): return self.lib.refc_backend_name().decode()
@@ -281,6 +281,13 @@ class RefDropin(RefCuda):
         return self._h(self.lib.refd_rms_norm_rope(int(policy), self._i(x), self._i(w), _c.c_float(eps), self._i(c), self._i(s),
                                                    int(heads), int(per_head), int(out_dtype)))
     def fused_gated_residual(self, policy, r, b, g): return self._h(self.lib.refd_gated_residual(int(policy), self._i(r), self._i(b), self._i(g)))
+    def fused_gated_residual_layer_norm(self, policy, r, b, g, w, bias, eps, shift, scale, out_dtype=BF16):
+        """(state handle, normalised handle)"""
+        state = _c.c_int64(0)
+        normed = self._h(self.lib.refd_gated_residual_layer_norm(int(policy), self._i(r), self._i(b), self._i(g), self._i(w),
+                                                                 self._i(bias), _c.c_float(eps), self._i(shift), self._i(scale),
+                                                                 int(out_dtype), _c.byref(state)))
+        return state.value, normed
     def fused_swiglu(self, x): return self._h(self.lib.refd_swiglu(self._i(x)))
     def fused_group_norm_silu(self, x, groups, w, b, eps):
         return self._h(self.lib.refd_group_norm_silu(self._i(x), int(groups), self._i(w), self._i(b), _c.c_float(eps)))

@@ -231,6 +231,17 @@ int64_t refd_rms_norm_rope(int policy, int64_t x, int64_t w, float eps, int64_t 
 int64_t refd_gated_residual(int policy, int64_t r, int64_t b, int64_t g) {
     return guarded([&] { return keep(vrhino_b200::fused_gated_residual(*g_backend, policy_of(policy), at(r), at(b), opt(g))); });
 }
+// Returns the normalised tensor's handle; *state_handle receives the updated residual stream's.
+int64_t refd_gated_residual_layer_norm(int policy, int64_t r, int64_t b, int64_t g, int64_t w, int64_t bias, float eps,
+                                       int64_t shift, int64_t scale, int out_dtype, int64_t* state_handle) {
+    return guarded([&] {
+        auto both = vrhino_b200::fused_gated_residual_layer_norm(*g_backend, policy_of(policy), at(r), at(b), opt(g), opt(w),
+                                                                 opt(bias), eps, opt(shift), opt(scale),
+                                                                 static_cast<DType>(out_dtype));
+        *state_handle = keep(both.first);
+        return keep(both.second);
+    });
+}
 int64_t refd_swiglu(int64_t x) { return guarded([&] { return keep(vrhino_b200::swiglu(*g_backend, at(x))); }); }
 int64_t refd_group_norm_silu(int64_t x, int groups, int64_t w, int64_t b, float eps) {
     return guarded([&] { return keep(vrhino_b200::group_norm_silu(*g_backend, at(x), groups, opt(w), opt(b), eps)); });

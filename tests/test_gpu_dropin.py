@@ -86,6 +86,30 @@ def test_fused_call_site_forms(orc, golden, dropin, case):
                     want["gated"])
             compare(orc, case, "added", _grab(rd, case, rd.fused_gated_residual(p, h["res"], h["branch"], 0), case["shape"]),
                     want["added"])
+            # the update together with the LayerNorm that reads the updated stream next: the stream
+            # against the golden vector, the normalised tensor bit for bit against the replaced
+            # backend's own layer_norm -> modulate -> cast on that stream
+            width = case["shape"][-1]
+            vec = lambda seed, mean, std: rd.upload(cases.to_bits(np.random.default_rng(seed).normal(mean, std, (1, 1, width))
+                                                                  .astype(np.float32), "f32"), ref.F32)
+            w, b, shift, scale = vec(1, 1.0, 0.1), vec(2, 0.0, 0.1), vec(3, 0.0, 0.1), vec(4, 0.0, 0.1)
+            for gate, key in ((h["gate"], "gated"), (0, "added")):
+                for affine, modulated in ((True, False), (False, True), (False, False)):
+                    state, normed = rd.fused_gated_residual_layer_norm(p, h["res"], h["branch"], gate, w if affine else 0,
+                                                                       b if affine else 0, cases.EPS, shift if modulated else 0,
+                                                                       scale if modulated else 0)
+                    compare(orc, case, key, _grab(rd, case, state, case["shape"]), want[key])
+                    chain = rd.layer_norm(state, w if affine else 0, b if affine else 0, cases.EPS)
+                    if modulated:
+                        chain = rd.modulate(p, chain, shift, scale)
+                    chain = rd.cast(chain, ref.BF16)
+                    got_bits, got_dt = rd.download(normed, case["shape"])
+                    want_bits, want_dt = rd.download(chain, case["shape"])
+                    assert got_dt == want_dt == ref.BF16
+                    if case["state"] == "bf16" and not modulated:
+                        assert np.array_equal(got_bits, want_bits)
+                    else:   # the one-kernel modulate rounds once where the chain rounds per operator
+                        compare(orc, case, "normed", (cases._sub(case, got_bits), "bf16"), (cases._sub(case, want_bits), "bf16"))
         elif k == "mochi":
             B, S, D = case["shape"]
             compare(orc, case, "swiglu", _grab(rd, case, rd.fused_swiglu(h["proj"]), (B, S, case["hidden"])), want["swiglu"])

@@ -97,6 +97,45 @@ def test_wan21_chain_full_size_sampled_rows(orc, gpu):
     assert torch.equal(_bits(got).cpu(), torch.from_numpy(want.data.view(np.int16).reshape(got.shape))), "F"
 
 
+def test_wan21_merged_residual_norm_full_size(orc, gpu):
+    """Config 2 with both CFG branches batched and each residual update merged into the LayerNorm that
+    follows it (9 launches): over EVERY element the updated streams equal the separate residual
+    kernels' and the normalised tensors equal the norm kernels run on those streams; 48 sampled rows
+    of the merged launches against the oracle's unfused chain."""
+    import torch
+    from vrhino_b200 import workloads
+    be, ops = gpu
+    blk = workloads.WanBlock(be, tokens=32760, seed=12, batch=2)
+    for l in blk.launches(fuse_residual_norm=True):
+        l.fn()
+    torch.cuda.synchronize()
+    o, r, e = blk.out, blk.rows, blk.eps
+    pol = blk.policy
+    c = ops.fused_gated_residual(be, pol, blk.x, blk.proj, r[2])
+    assert torch.equal(_bits(o["C"]), _bits(c)), "C stream"
+    assert torch.equal(_bits(o["D"]), _bits(be.layer_norm(c, blk.gamma3, blk.beta3, e))), "D on the updated stream"
+    f = ops.fused_gated_residual(be, pol, blk.x, blk.cross, None)
+    assert torch.equal(_bits(o["F"]), _bits(f)), "F stream"
+    assert torch.equal(_bits(o["G"]), _bits(ops.fused_layer_norm_modulate(be, f, None, None, e, r[3], r[4]))), "G on the updated stream"
+    del c, f
+    rng = np.random.default_rng(1)
+    rows = np.sort(np.concatenate([[0, 32759], rng.choice(32760, 22, replace=False)]))
+    rows_t = torch.from_numpy(rows).cuda()
+    obe, opol = orc.OracleBackend(), orc.Policy.unqualified_default("bf16")
+    f32 = lambda t: orc.T(t.detach().cpu().float().numpy(), "f32")
+    for b in range(2):
+        x = _orc_rows(orc, blk.x[b:b + 1], rows_t)
+        state = orc.gated_residual(obe, opol, x, _orc_rows(orc, blk.proj[b:b + 1], rows_t), f32(r[2][b:b + 1]))
+        got = o["C"][b, rows_t]
+        assert torch.equal(_bits(got).cpu(), torch.from_numpy(state.data.view(np.int16).reshape(got.shape))), "C"
+        _cmp_rows(orc, o["D"][b:b + 1], rows_t, obe.layer_norm(state, f32(blk.gamma3), f32(blk.beta3), e), "C+D normalised")
+        state = orc.residual_add(obe, opol, x, _orc_rows(orc, blk.cross[b:b + 1], rows_t))
+        got = o["F"][b, rows_t]
+        assert torch.equal(_bits(got).cpu(), torch.from_numpy(state.data.view(np.int16).reshape(got.shape))), "F"
+        want = obe.cast(orc.modulate(obe, opol, obe.layer_norm(state, None, None, e), f32(r[3][b:b + 1]), f32(r[4][b:b + 1])), "bf16")
+        _cmp_rows(orc, o["G"][b:b + 1], rows_t, want, "F+G normalised")
+
+
 @pytest.mark.parametrize("kind", [2, 0])
 def test_table_unary_full_size_every_element(gpu, kind):
     """[32760, 8960] bf16 (GELU-tanh of config 2; SiLU for the VAE): out == table[in] everywhere,

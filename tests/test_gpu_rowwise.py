@@ -8,7 +8,7 @@ are F32 sums whose order depends on the launch geometry; same tolerance.
 import numpy as np
 import pytest
 
-from conftest import assert_close, from_torch, to_torch
+from conftest import assert_bits_equal, assert_close, from_torch, to_torch
 
 pytestmark = pytest.mark.gpu
 
@@ -242,3 +242,47 @@ def test_rms_norm_gated_residual_mochi(orc, gpu, state, width, batch):
     bounded = be.activation(to_torch(gate), ops.TANH)
     got = ops.fused_rms_norm_gated_residual(be, pol, to_torch(res), to_torch(branch), bounded, 1e-6)
     assert_close(orc, got, want, rel=1e-5, atol=1e-6, what="mochi normalized gated residual")
+
+
+@pytest.mark.parametrize("width,batch,tokens", [(1536, 1, 21), (1536, 2, 9), (5120, 1, 5), (3072, 2, 6), (2048, 1, 7), (128, 1, 40),
+                                                (264, 1, 11), (24, 3, 5)])
+@pytest.mark.parametrize("gated", [True, False])
+@pytest.mark.parametrize("mode", ["affine", "modulate", "plain"])
+@pytest.mark.parametrize("state", ["bf16", "f32"])
+def test_gated_residual_layer_norm_one_pass(orc, gpu, width, batch, tokens, gated, mode, state):
+    """Residual update + the LayerNorm that follows it (one kernel for a bf16 stream, the two
+    operators otherwise): the updated stream must be bit-identical to gated_residual / residual_add,
+    the normalised output bit-identical to running the norm kernel on that stream, and both match
+    the oracle's unfused chain."""
+    import torch
+    be, ops = gpu
+    from vrhino_b200 import synth
+    obe = orc.OracleBackend()
+    opol = orc.Policy.unqualified_default("bf16") if state == "bf16" else orc.Policy.fp32()
+    pol = ops.Policy.unqualified_default(torch.bfloat16) if state == "bf16" else ops.Policy.fp32()
+    shape = (batch, tokens, width)
+    res = orc.tensor(synth.normal(shape, seed=width + 1), state)
+    branch = orc.tensor(synth.normal(shape, seed=width + 2), "bf16")
+    gate = orc.tensor(synth.normal((batch, 1, width), std=0.3, seed=3)) if gated else None
+    w = orc.tensor(synth.normal((width,), 1.0, 0.1, seed=4)) if mode == "affine" else None
+    b = orc.tensor(synth.normal((width,), 0.0, 0.1, seed=5)) if mode == "affine" else None
+    shift = orc.tensor(synth.normal((batch, 1, width), std=0.1, seed=6)) if mode == "modulate" else None
+    scale = orc.tensor(synth.normal((batch, 1, width), std=0.1, seed=7)) if mode == "modulate" else None
+    T = lambda t: None if t is None else to_torch(t)
+    got_state, got_norm = ops.fused_gated_residual_layer_norm(be, pol, T(res), T(branch), T(gate), T(w), T(b), 1e-6, T(shift), T(scale))
+    # against this library's separate kernels: identical bits
+    sep_state = ops.fused_gated_residual(be, pol, T(res), T(branch), T(gate))
+    if mode == "modulate":
+        sep_norm = ops.fused_layer_norm_modulate(be, sep_state, None, None, 1e-6, T(shift), T(scale))
+    else:
+        sep_norm = ops.fused_layer_norm_cast(be, sep_state, T(w), T(b), 1e-6)
+    bits = lambda t: t.view(torch.int16 if t.dtype == torch.bfloat16 else torch.int32)
+    assert torch.equal(bits(got_state), bits(sep_state)), "updated stream differs from gated_residual"
+    assert torch.equal(bits(got_norm), bits(sep_norm)), "normalised output differs from the norm kernel on the same stream"
+    # against the oracle's chain
+    want_state = orc.gated_residual(obe, opol, res, branch, gate) if gated else orc.residual_add(obe, opol, res, branch)
+    assert_bits_equal(got_state, want_state, "state")
+    normed = obe.layer_norm(want_state, w, b, 1e-6)
+    want = obe.cast(orc.modulate(obe, opol, normed, shift, scale), "bf16") if mode == "modulate" else obe.cast(normed, "bf16")
+    flips = dict(flip_atol=2.0 ** -8 * 8.0, flip_frac=2e-3)
+    assert_close(orc, got_norm, want, rel=1e-5, atol=2e-6, what="norm after residual update", **flips)

@@ -109,12 +109,21 @@ __global__ void __launch_bounds__(kRowThreads) row_kernel_scalar(const RowParams
 
 // ---- dispatch ----------------------------------------------------------------------------
 constexpr int kMaxChunks = 8;
+// launch_rows() result when a fused residual update was asked for but the vector kernel cannot
+// take it (alignment, width, too many gate vectors): the caller then runs the two operators.
+constexpr int kPreNotFused = 1;
 
 // Which dtype classes exist for a (norm, post) pair; anything else takes the scalar kernel.
 template <int NORM, int POST>
 bool launch_by_dtype(const RowParams& p, int geometry, int64_t ctas, size_t smem, cudaStream_t s) {
     constexpr bool rope = POST == kPostRope || POST == kPostRopeShared;
     const bool x_bf16 = p.x_dt == VRB_BF16, n_bf16 = p.norm_out_dt == VRB_BF16;
+    if (p.pre_branch != nullptr) {   // fused residual update: bf16 stream, LayerNorm, no / staged / plain modulate
+        if constexpr (NORM == kNormLayer && (POST == kPostNone || POST == kPostModulate || POST == kPostModulateStaged)) {
+            if (x_bf16 && n_bf16) { launch_row_variant<NORM, POST, kBf16Bf16Pre>(p, geometry, ctas, smem, s); return true; }
+        }
+        return false;
+    }
     if (!x_bf16 && !n_bf16) { launch_row_variant<NORM, POST, kF32F32>(p, geometry, ctas, smem, s); return true; }
     if constexpr (!rope) {
         if (x_bf16 && n_bf16) { launch_row_variant<NORM, POST, kBf16Bf16>(p, geometry, ctas, smem, s); return true; }
@@ -151,6 +160,9 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
         else row_kernel_scalar<kNormRms><<<grid, kRowThreads, 0, stream>>>(p);
         return after_launch(what);
     };
+    if (p.pre_branch != nullptr &&
+        (!vector_ok || !aligned16(p.pre_branch) || !aligned16(p.state_out) || (p.pre_gate && p.pre_vectors > 4) || sub != 1))
+        return kPreNotFused;
     if (!vector_ok) return scalar_path();
     // Threads per row: a row of up to 32*6 chunks stays inside one warp (no barrier); narrower
     // rows take a fraction of a warp with 1-2 chunks per thread; wider rows take 2-8 warps.
@@ -182,9 +194,15 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
     size_t smem = 0;
     int post = p.post;
     const size_t region = static_cast<size_t>(geometry <= 6 ? nch : (chunks / tpr)) * tpr * 8 * sizeof(float);
-    // Up to four modulation vectors (one per batch entry) that fit the default shared-memory
-    // limit: stage 1+scale and shift per CTA instead of re-reading them for every row.
-    const size_t budget = 46 * 1024;
+    // Up to four modulation vectors (one per batch entry): stage 1+scale and shift per CTA instead
+    // of re-reading them for every row.  The budget leaves room for two resident CTAs per SM
+    // (sizes above 48 KB are opted into by the launcher).
+    // The fused residual update with a modulating epilogue runs three CTAs per SM: smaller budget,
+    // its gate vectors included.
+    const bool pre = p.pre_branch != nullptr;
+    const size_t gate_bytes = pre && p.pre_gate ? static_cast<size_t>(p.pre_vectors) * (region / 2) : 0;
+    if (gate_bytes > 48 * 1024) return kPreNotFused;
+    const size_t budget = (pre && post != kPostNone ? 72 * 1024 : 100 * 1024) - gate_bytes;
     if (post == kPostModulate && p.vectors >= 1 && p.vectors <= 4 && sub == 1 &&
         static_cast<size_t>(p.vectors) * 2 * region <= budget) {
         post = kPostModulateStaged;
@@ -197,6 +215,8 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
         p.affine_staged = 1;
         smem += 2 * region;
     }
+    // Fused residual update: the gate vectors, bf16 pairs, behind everything else.
+    if (pre) smem += gate_bytes;
     // RoPE table shared by the heads: the columns a thread needs are the same for all its chunks.
     if (post == kPostRope && p.norm_width % p.f_width == 0 && (static_cast<int64_t>(tpr) * 8) % p.f_width == 0)
         post = kPostRopeShared;
@@ -216,7 +236,7 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
             default: launched = launch_by_dtype<kNormRms, kPostNone>(p, geometry, ctas, smem, stream); break;
         }
     }
-    if (!launched) return scalar_path();
+    if (!launched) return p.pre_branch != nullptr ? kPreNotFused : scalar_path();
     return after_launch(what);
 }
 
@@ -263,6 +283,43 @@ extern "C" int vrb_layer_norm_cast(const void* x, int x_dtype, const void* weigh
                 VRB_ERR_UNSUPPORTED, "layer_norm: weight/bias must be F32 or BF16");
     p.rows = rows; p.width = p.norm_width = width; p.eps = eps; p.norm = kNormLayer;
     return launch_rows(p, as_stream(stream), "layer_norm");
+}
+
+extern "C" int vrb_gated_residual_layer_norm_modulate(
+        const void* residual, int residual_dtype, const void* branch, int branch_dtype,
+        const void* gate, int gate_dtype, int64_t gate_rows_per_vector, int64_t gate_vectors,
+        void* state_out, int state_dtype,
+        const void* weight, int weight_dtype, const void* bias, int bias_dtype,
+        const void* scale, const void* shift, int mod_dtype, int64_t rows_per_vector, int64_t mod_vectors,
+        void* out, int out_dtype, int64_t rows, int64_t width, float eps, vrb_stream stream) {
+    VRB_REQUIRE(residual && branch && state_out && out, VRB_ERR_INVALID, "gated_residual_layer_norm: null tensor");
+    VRB_REQUIRE((!weight || is_float_dtype(weight_dtype)) && (!bias || is_float_dtype(bias_dtype)),
+                VRB_ERR_UNSUPPORTED, "layer_norm: weight/bias must be F32 or BF16");
+    if (gate) { if (int rc = check_vectors("gated_residual_layer_norm", gate_rows_per_vector, gate_vectors)) return rc; }
+    if (scale) { if (int rc = check_vectors("gated_residual_layer_norm", rows_per_vector, mod_vectors)) return rc; }
+    if (residual_dtype == VRB_BF16 && branch_dtype == VRB_BF16 && state_dtype == VRB_BF16) {
+        RowParams p = blank();
+        p.x = residual; p.x_dt = p.norm_out_dt = VRB_BF16; p.out = out; p.out_dt = out_dtype;
+        p.pre_branch = branch; p.pre_gate = gate; p.pre_gate_dt = gate_dtype; p.state_out = state_out;
+        p.pre_rows_per_vector = gate ? gate_rows_per_vector : 1; p.pre_vectors = gate ? gate_vectors : 0;
+        p.weight = weight; p.w_dt = weight_dtype; p.bias = bias; p.b_dt = bias_dtype;
+        p.rows = rows; p.width = p.norm_width = width; p.eps = eps; p.norm = kNormLayer;
+        if (scale) {
+            p.scale = scale; p.shift = shift; p.mod_dt = mod_dtype;
+            p.rows_per_vector = rows_per_vector; p.vectors = mod_vectors; p.post = kPostModulate;
+        }
+        const int rc = launch_rows(p, as_stream(stream), "gated_residual_layer_norm");
+        if (rc != kPreNotFused) return rc;
+    }
+    // any other dtype contract or geometry: the two operators, one after the other
+    if (int rc = vrb_gated_residual(residual, residual_dtype, branch, branch_dtype, gate, gate_dtype, gate_rows_per_vector,
+                                    gate_vectors, state_out, state_dtype, rows, width, stream))
+        return rc;
+    if (scale)
+        return vrb_layer_norm_modulate(state_out, state_dtype, weight, weight_dtype, bias, bias_dtype, scale, shift, mod_dtype,
+                                       rows_per_vector, mod_vectors, out, out_dtype, rows, width, eps, stream);
+    return vrb_layer_norm_cast(state_out, state_dtype, weight, weight_dtype, bias, bias_dtype, out, out_dtype, rows, width, eps,
+                               stream);
 }
 
 extern "C" int vrb_rms_norm(const void* x, int x_dtype, const void* weight, int weight_dtype,

@@ -47,7 +47,10 @@ enum Post {
     kPostRopeShared = 6,       // RoPE whose table columns do not depend on the thread's chunk index
 };
 // dtype class of (x, output of the unfused norm operator)
-enum DtClass { kF32F32 = 0, kBf16Bf16 = 1, kBf16F32 = 2 };
+// kBf16Bf16Pre: like kBf16Bf16, but the row the norm sees is first COMPUTED as the bf16 gated
+// residual  state = residual + branch * gate  (common.cpp:134-144 in a bf16 residual stream) and
+// stored to state_out -- the residual update and the norm that follows it in one pass.
+enum DtClass { kF32F32 = 0, kBf16Bf16 = 1, kBf16F32 = 2, kBf16Bf16Pre = 3 };
 
 struct RowParams {
     const void* x; void* out;
@@ -67,6 +70,11 @@ struct RowParams {
     unsigned nrows32, sub32;   // normalised rows, normalised rows per storage row
     double inv_width;          // 1 / norm_width
     int affine_staged;         // LayerNorm weight / bias pre-rounded into shared memory
+    // kBf16Bf16Pre: x is the residual stream, pre_branch the branch, pre_gate an optional gate
+    // ([pre_vectors, width], staged bf16-rounded), state_out receives the updated stream
+    const void* pre_branch; const void* pre_gate; void* state_out;
+    int pre_gate_dt;
+    int64_t pre_rows_per_vector, pre_vectors;
 };
 
 constexpr int kRowThreads = 256;
@@ -172,8 +180,17 @@ __host__ __device__ constexpr int packed_regs(int nch, bool x_bf16) { return nch
 // The exact geometries prefetch the next row into a second register set while the current one
 // is being processed, if two packed rows fit in 48 registers.
 __host__ __device__ constexpr bool prefetches(int nch, bool x_bf16, bool full) { return full && 2 * packed_regs(nch, x_bf16) <= 48; }
-__host__ __device__ constexpr int min_ctas_per_sm(int nch, bool x_bf16, bool full) {
-    const int row_regs = packed_regs(nch, x_bf16) * (prefetches(nch, x_bf16, full) ? 2 : 1);
+// The fused residual update (dtype class kBf16Bf16Pre) loads two raw rows (residual stream and
+// branch) per normalised row.  With no epilogue operands (plain or affine LayerNorm) it keeps the
+// next pair in flight in a second register set; with a modulating epilogue the extra registers
+// spill, and one more resident CTA without the prefetch measured faster.
+__host__ __device__ constexpr bool pre_prefetches(int nch, bool full, int post) {
+    return prefetches(nch, true, full) && post == kPostNone;
+}
+__host__ __device__ constexpr int min_ctas_per_sm(int nch, bool x_bf16, bool full, bool pre = false, int post = kPostNone) {
+    if (pre && full && prefetches(nch, true, full) && !pre_prefetches(nch, full, post)) return 3;
+    const int sets = (prefetches(nch, x_bf16, full) ? 2 : 1) + (pre ? 1 : 0);
+    const int row_regs = packed_regs(nch, x_bf16) * sets;
     return row_regs <= 16 ? 4 : row_regs <= 32 ? 3 : 2;
 }
 
@@ -181,10 +198,12 @@ __host__ __device__ constexpr int min_ctas_per_sm(int nch, bool x_bf16, bool ful
 // TPR > 0 with FULL means the row is exactly NCH * TPR chunks wide, so chunk offsets are
 // compile-time constants and no chunk needs a bounds test (the production widths).
 template <int NCH, int TPR, bool FULL, int NORM, int POST, int DT>
-__global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F32, FULL)) row_kernel(const RowParams p) {
+__global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F32, FULL, DT == kBf16Bf16Pre, POST))
+row_kernel(const RowParams p) {
     constexpr bool X_BF16 = DT != kF32F32;
-    constexpr bool PF = prefetches(NCH, X_BF16, FULL);
-    constexpr bool N_BF16 = DT == kBf16Bf16;     // the unfused norm operator would store bf16
+    constexpr bool PRE = DT == kBf16Bf16Pre;
+    constexpr bool PF = PRE ? pre_prefetches(NCH, FULL, POST) : prefetches(NCH, X_BF16, FULL);
+    constexpr bool N_BF16 = DT == kBf16Bf16 || PRE;   // the unfused norm operator would store bf16
     constexpr bool kStaged = POST == kPostModulateStaged;
     constexpr bool kModulate = POST == kPostModulate || kStaged;
     constexpr bool kRope = POST == kPostRope || POST == kPostRopeShared;
@@ -231,6 +250,23 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
         }
         __syncthreads();
     }
+    // kBf16Bf16Pre: the gate vectors, rounded to bf16 and packed in pairs, one 16-byte word per chunk
+    // at word index i * tpr + l (conflict-free); vector v at s_gate + v * (pad / 2)
+    uint32_t* const s_gate = reinterpret_cast<uint32_t*>(s_mod + (kStaged ? static_cast<int>(p.vectors) * 2 * pad : 0));
+    const bool has_pre_gate = PRE && p.pre_gate != nullptr;
+    if constexpr (PRE) {
+        if (has_pre_gate) {
+            const int gate_vectors = static_cast<int>(p.pre_vectors);
+            for (int cv = threadIdx.x; cv < (width / 2) * gate_vectors; cv += kRowThreads) {
+                const int v = cv / (width / 2), pair = cv - v * (width / 2);
+                const int c = pair * 2, chunk = c >> 3, i = chunk / tpr, l = chunk - i * tpr;
+                const int64_t at = static_cast<int64_t>(v) * p.width + c;
+                s_gate[v * (pad / 2) + ((i * tpr + l) << 2) + ((c & 7) >> 1)] =
+                    pack_bf16x2(load1(p.pre_gate, p.pre_gate_dt, at), load1(p.pre_gate, p.pre_gate_dt, at + 1));
+            }
+            __syncthreads();
+        }
+    }
     // elements of this thread that exist (a partial last chunk never happens: width % 8 == 0)
     int own = 0;
 #pragma unroll
@@ -247,17 +283,67 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
             dst[i] = (ok && (FULL || chunk < nchunks)) ? load_packed<X_BF16>(p.x, off + chunk * 8) : zero_packed<X_BF16>();
         }
     };
+    // kBf16Bf16Pre: the raw residual-stream row and branch row of a normalised row
+    auto load_raw = [&](unsigned first_row, Packed<true> (&res)[NCH], Packed<true> (&br)[NCH]) {
+        const unsigned r = first_row + row_in_cta;
+        const bool ok = r < nrows;
+        const int64_t off = static_cast<int64_t>(r) * width;
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+            const int chunk = lane_in_row + i * tpr;
+            const bool here = ok && (FULL || chunk < nchunks);
+            res[i] = here ? load_packed<true>(p.x, off + chunk * 8) : zero_packed<true>();
+            br[i] = here ? load_packed<true>(p.pre_branch, off + chunk * 8) : zero_packed<true>();
+        }
+    };
     Packed<X_BF16> xr[NCH];
-    if constexpr (PF) load_row(blockIdx.x * rows_per_cta, xr);
+    Packed<true> raw_res[PRE ? NCH : 1], raw_br[PRE ? NCH : 1];   // PRE: the row being combined next
+    if constexpr (PRE) {
+        if constexpr (PF) load_raw(blockIdx.x * rows_per_cta, raw_res, raw_br);
+    } else if constexpr (PF) {
+        load_row(blockIdx.x * rows_per_cta, xr);
+    }
 
     for (unsigned base = blockIdx.x * rows_per_cta; base < nrows; base += row_step) {
         const unsigned nrow = base + row_in_cta;
         const bool valid = nrow < nrows;
         const int64_t row_offset = static_cast<int64_t>(nrow) * width;
 
-        Packed<X_BF16> xn[PF ? NCH : 1];
-        if constexpr (PF) load_row(base + row_step, xn);   // next row, in flight during this one
-        else load_row(base, xr);
+        Packed<X_BF16> xn[(PF && !PRE) ? NCH : 1];
+        if constexpr (PRE) {
+            if constexpr (!PF) load_raw(base, raw_res, raw_br);
+            // state = residual + branch * gate in packed bf16 (two roundings, as the reference's
+            // F32 multiply and add each followed by the bf16 store), written back as the new stream
+            unsigned gate_base = 0;
+            if (has_pre_gate && p.pre_vectors > 1)
+                gate_base = ((nrow / static_cast<unsigned>(p.pre_rows_per_vector)) % static_cast<unsigned>(p.pre_vectors)) *
+                            static_cast<unsigned>(pad / 2);
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) {
+                const int chunk = lane_in_row + i * tpr;
+                if (!FULL && chunk >= nchunks) continue;
+                const uint32_t rw[4] = {raw_res[i].r.x, raw_res[i].r.y, raw_res[i].r.z, raw_res[i].r.w};
+                const uint32_t bw[4] = {raw_br[i].r.x, raw_br[i].r.y, raw_br[i].r.z, raw_br[i].r.w};
+                uint4 gw = make_uint4(0, 0, 0, 0);
+                if (has_pre_gate) gw = *reinterpret_cast<const uint4*>(s_gate + gate_base + ((i * tpr + lane_in_row) << 2));
+                const uint32_t gws[4] = {gw.x, gw.y, gw.z, gw.w};
+                uint32_t ow[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    __nv_bfloat162 br2 = *reinterpret_cast<const __nv_bfloat162*>(&bw[k]);
+                    if (has_pre_gate) br2 = __hmul2_rn(br2, *reinterpret_cast<const __nv_bfloat162*>(&gws[k]));
+                    const __nv_bfloat162 sum = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&rw[k]), br2);
+                    ow[k] = *reinterpret_cast<const uint32_t*>(&sum);
+                }
+                xr[i].r = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                if (valid) __stcs(reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.state_out) + row_offset + chunk * 8), xr[i].r);
+            }
+            if constexpr (PF) load_raw(base + row_step, raw_res, raw_br);   // next row, in flight during this one
+        } else if constexpr (PF) {
+            load_row(base + row_step, xn);   // next row, in flight during this one
+        } else {
+            load_row(base, xr);
+        }
 
         // ---- per-row operand offsets (32-bit arithmetic) ----
         unsigned srow = nrow, col0 = 0;
@@ -499,7 +585,7 @@ __global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F3
             store8(p.out, p.out_dt, row_offset + c, y);
         }
         }  // valid
-        if constexpr (PF) {
+        if constexpr (PF && !PRE) {
 #pragma unroll
             for (int i = 0; i < NCH; ++i) xr[i] = xn[i];
         }

@@ -13,23 +13,34 @@ namespace rowwise {
 // capped by the amount of work; CTAs stride over the rows.
 template <int NCH, int TPR, bool FULL, int NORM, int POST, int DT>
 void launch_one(const RowParams& p, int64_t ctas, size_t smem, cudaStream_t stream) {
-    // resident CTAs per SM of this instantiation for the last shared-memory size seen; guarded so
-    // that callers on several host threads may launch concurrently
+    // per device: resident CTAs per SM of this instantiation for the last shared-memory size seen,
+    // and the largest dynamic shared-memory size opted into (dynamic plus static above 48 KB needs the opt-in);
+    // guarded so that callers on several host threads may launch concurrently
+    constexpr int kDevices = 32;
     static std::mutex mutex;
-    static int cached_per_sm = 0;
-    static size_t cached_smem = ~size_t{0};
+    static int cached_per_sm[kDevices] = {};
+    static size_t cached_smem[kDevices] = {};
+    static size_t opted_smem[kDevices] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kDevices) device = kDevices - 1;
     int per_sm;
     {
         std::lock_guard<std::mutex> lock(mutex);
-        if (cached_per_sm == 0 || cached_smem != smem) {
+        if (smem > 40 * 1024 && smem > opted_smem[device]) {
+            if (cudaFuncSetAttribute(row_kernel<NCH, TPR, FULL, NORM, POST, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem)) == cudaSuccess)
+                opted_smem[device] = smem;
+            cached_per_sm[device] = 0;
+        }
+        if (cached_per_sm[device] == 0 || cached_smem[device] != smem) {
             int n = 0;
             if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, row_kernel<NCH, TPR, FULL, NORM, POST, DT>, kRowThreads, smem) !=
                     cudaSuccess || n < 1)
                 n = 1;
-            cached_per_sm = n;
-            cached_smem = smem;
+            cached_per_sm[device] = n;
+            cached_smem[device] = smem;
         }
-        per_sm = cached_per_sm;
+        per_sm = cached_per_sm[device];
     }
     row_kernel<NCH, TPR, FULL, NORM, POST, DT><<<grid_for(ctas, per_sm), kRowThreads, smem, stream>>>(p);
 }

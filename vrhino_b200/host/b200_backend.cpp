@@ -396,6 +396,41 @@ Tensor B200Backend::gated_residual(const Tensor& residual_raw, const Tensor& bra
     });
 }
 
+std::pair<Tensor, Tensor> B200Backend::gated_residual_layer_norm(const Tensor& residual_raw, const Tensor& branch_raw,
+                                                                 const Tensor* gate_raw, DType state, const Tensor* weight_raw,
+                                                                 const Tensor* bias_raw, float eps, const Tensor* shift_raw,
+                                                                 const Tensor* scale_raw, DType output) {
+    std::pair<Tensor, Tensor> result;
+    guarded([&] {
+        Tensor residual = copy_to_device(residual_raw, operand_dtype(residual_raw));
+        Tensor branch = copy_to_device(branch_raw, operand_dtype(branch_raw)), gate, weight, bias, scale, shift;
+        require(residual.shape() == branch.shape(), "Incompatible broadcast shapes");
+        require((shift_raw == nullptr) == (scale_raw == nullptr), "modulate: shift and scale must share dtype and shape");
+        const int64_t width = residual.dim(-1), rows = residual.numel() / width;
+        int64_t gate_rows_per_vector = 1, gate_vectors = 1, rows_per_vector = 1, vectors = 1;
+        if (gate_raw) { gate = parameter(*gate_raw); vector_layout(residual, gate, gate_rows_per_vector, gate_vectors); }
+        if (weight_raw) { weight = parameter(*weight_raw); require(weight.numel() == width, "layer norm weight mismatch"); }
+        if (bias_raw) { bias = parameter(*bias_raw); require(bias.numel() == width, "layer norm bias mismatch"); }
+        if (scale_raw) {
+            scale = parameter(*scale_raw);
+            shift = copy_to_device(*shift_raw, scale.dtype());
+            require(shift.numel() == scale.numel(), "modulate: shift and scale must share dtype and shape");
+            vector_layout(residual, scale, rows_per_vector, vectors);
+        }
+        result.first = rt_->allocate_device(residual.shape(), state);
+        result.second = rt_->allocate_device(residual.shape(), output);
+        check(vrb_gated_residual_layer_norm_modulate(
+            residual.data(), code(residual.dtype()), branch.data(), code(branch.dtype()), gate_raw ? gate.data() : nullptr,
+            gate_raw ? code(gate.dtype()) : 0, gate_rows_per_vector, gate_vectors, result.first.data(), code(state),
+            weight_raw ? weight.data() : nullptr, weight_raw ? code(weight.dtype()) : 0, bias_raw ? bias.data() : nullptr,
+            bias_raw ? code(bias.dtype()) : 0, scale_raw ? scale.data() : nullptr, scale_raw ? shift.data() : nullptr,
+            scale_raw ? code(scale.dtype()) : 0, rows_per_vector, vectors, result.second.data(), code(output), rows, width,
+            eps, kLegacyStream));
+        return result.second;
+    });
+    return result;
+}
+
 Tensor B200Backend::swiglu(const Tensor& raw) {
     return guarded([&] {
         const DType dtype = operand_dtype(raw);
@@ -449,6 +484,21 @@ Tensor fused_gated_residual(vrhino::Backend& backend, const vrhino::PrecisionPol
         return b200->gated_residual(residual, branch, gate, policy.persistent_state_dtype(vrhino::PrecisionSemantic::ResidualState));
     return gate ? vrhino::gated_residual(backend, policy, residual, branch, *gate)
                 : vrhino::residual_add(backend, policy, residual, branch);
+}
+
+std::pair<Tensor, Tensor> fused_gated_residual_layer_norm(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy,
+                                                          const Tensor& residual, const Tensor& branch, const Tensor* gate,
+                                                          const Tensor* weight, const Tensor* bias, float eps,
+                                                          const Tensor* shift, const Tensor* scale, DType output) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend))
+        return b200->gated_residual_layer_norm(residual, branch, gate,
+                                               policy.persistent_state_dtype(vrhino::PrecisionSemantic::ResidualState), weight,
+                                               bias, eps, shift, scale, output);
+    Tensor state = gate ? vrhino::gated_residual(backend, policy, residual, branch, *gate)
+                        : vrhino::residual_add(backend, policy, residual, branch);
+    Tensor normed = backend.layer_norm(state, weight, bias, eps);
+    if (scale) normed = vrhino::modulate(backend, policy, normed, *shift, *scale);
+    return {state, backend.cast(normed, output)};
 }
 
 Tensor swiglu(vrhino::Backend& backend, const Tensor& projected) {

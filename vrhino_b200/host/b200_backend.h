@@ -21,6 +21,7 @@
 
 #include <map>
 #include <memory>
+#include <utility>
 #include <string>
 #include <vector>
 
@@ -63,6 +64,12 @@ public:
     Tensor rms_norm_rope(const Tensor& x, const Tensor* weight, float eps, const Tensor* cosine,
                          const Tensor* sine, int heads, bool per_head_norm, DType output);
     Tensor gated_residual(const Tensor& residual, const Tensor& branch, const Tensor* gate, DType state);
+    // {state, normed}: state = gated_residual / residual_add (gate == nullptr) in `state` dtype,
+    // normed = cast(layer_norm(state, weight, bias, eps) [modulated by shift, scale], output);
+    // one kernel when the residual stream, the branch and both results are BF16
+    std::pair<Tensor, Tensor> gated_residual_layer_norm(const Tensor& residual, const Tensor& branch, const Tensor* gate,
+                                                        DType state, const Tensor* weight, const Tensor* bias, float eps,
+                                                        const Tensor* shift, const Tensor* scale, DType output);
     Tensor swiglu(const Tensor& projected);
     Tensor group_norm_silu(const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps);
     // x [B, C, T, H, W]: statistics per (batch entry, frame, group), no permutes
@@ -183,6 +190,13 @@ vrhino::Tensor rms_norm_rope(vrhino::Backend& backend, const vrhino::PrecisionPo
 vrhino::Tensor fused_gated_residual(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy,
                                     const vrhino::Tensor& residual, const vrhino::Tensor& branch,
                                     const vrhino::Tensor* gate);
+// The residual update and the LayerNorm of the updated stream that follows it in the Wan block
+// (wan.cpp:95-98: first residual -> norm3; wan.cpp:103-107: residual_add -> layer_norm -> modulate):
+// returns {state, cast(normed, output)}; shift / scale null = no modulation.
+std::pair<vrhino::Tensor, vrhino::Tensor> fused_gated_residual_layer_norm(
+    vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy, const vrhino::Tensor& residual,
+    const vrhino::Tensor& branch, const vrhino::Tensor* gate, const vrhino::Tensor* weight, const vrhino::Tensor* bias,
+    float eps, const vrhino::Tensor* shift, const vrhino::Tensor* scale, vrhino::DType output = vrhino::DType::BF16);
 // mul(parts[0], silu(parts[1])), parts = split(projected, {H, H}, -1)   (mochi.cpp:195-202)
 vrhino::Tensor swiglu(vrhino::Backend& backend, const vrhino::Tensor& projected);
 // activation(group_norm(x, groups, weight, bias, eps), Silu)   (autoencoder_kl.cpp:31-41)

@@ -490,6 +490,31 @@ def fused_gated_residual(be, policy, residual, branch, gate, out=None):
     return out
 
 
+def fused_gated_residual_layer_norm(be, policy, residual, branch, gate, weight, bias, eps, shift=None, scale=None,
+                                    out_dtype=BF16, state_out=None, out=None):
+    """The residual update and the LayerNorm the block applies to the updated stream next
+    (native/src/architectures/wan.cpp:95-110), one pass when the stream is bf16:
+        state = gated_residual(residual, branch, gate)            (residual_add when gate is None)
+        normed = cast(modulate(layer_norm(state, weight, bias, eps), shift, scale), out_dtype)
+                 (no modulation when scale is None)
+    Returns (state, normed)."""
+    residual, branch = _dense(residual), _dense(branch)
+    width = residual.shape[-1]
+    rows = residual.numel() // width
+    grpv, gvec = (1, 1) if gate is None else _vec_layout(rows, residual.shape, gate)
+    mrpv, mvec = (1, 1) if scale is None else _vec_layout(rows, residual.shape, scale)
+    if scale is not None and shift is not None and (shift.dtype != scale.dtype or shift.numel() != scale.numel()):
+        raise VrbError("modulate: shift and scale must share dtype and shape")
+    state = _result(state_out, residual.shape, policy.residual, residual.device)
+    normed = _result(out, residual.shape, out_dtype, residual.device)
+    call("vrb_gated_residual_layer_norm_modulate", _ptr(residual), _code(residual), _ptr(branch), _code(branch),
+         _ptr(gate), _code(gate) if gate is not None else 0, grpv, gvec, _ptr(state), _code(policy.residual),
+         _ptr(weight), _code(weight) if weight is not None else 0, _ptr(bias), _code(bias) if bias is not None else 0,
+         _ptr(_dense(scale)) if scale is not None else None, _ptr(shift), _code(scale) if scale is not None else 0, mrpv, mvec,
+         _ptr(normed), _code(out_dtype), rows, width, ctypes.c_float(eps), _stream())
+    return state, normed
+
+
 def fused_rms_norm_gated_residual(be, policy, residual, branch, bounded_gate, eps=1e-6, out=None):
     """gated_residual(residual, rms_norm(branch, None, eps), bounded_gate) -- mochi.cpp:204-211
     after the tanh on the [B, D] gate."""

@@ -69,7 +69,11 @@ class WanBlock:
         self.heads, self.eps = heads, 1e-6
         self.out = {}
 
-    def launches(self) -> List[Launch]:
+    def launches(self, fuse_residual_norm: bool = False) -> List[Launch]:
+        """fuse_residual_norm: C+D and F+G each as ONE launch (residual update + the LayerNorm that
+        reads the updated stream, wan.cpp:95-107 of the reference) -- 9 launches instead of 11.  Such a
+        launch reads residual and branch and writes stream and normalised output: 4 passes where
+        the two launches it replaces make 5."""
         be, p, r, e, o = self.be, self.policy, self.rows, self.eps, self.out
         B, S, D = self.x.shape
         act = B * S * D
@@ -89,7 +93,24 @@ class WanBlock:
         def H(): o["H"] = be.activation(self.ffn_hidden, ops.GELU_TANH, out=o.get("H"))
         def I(): o["I"] = ops.fused_gated_residual(be, p, self.x, self.ffn_out, r[5], out=o.get("I"))
 
+        def CD(): o["C"], o["D"] = ops.fused_gated_residual_layer_norm(be, p, self.x, self.proj, r[2], self.gamma3, self.beta3, e,
+                                                                       state_out=o.get("C"), out=o.get("D"))
+        def FG(): o["F"], o["G"] = ops.fused_gated_residual_layer_norm(be, p, self.x, self.cross, None, None, None, e, r[3], r[4],
+                                                                       state_out=o.get("F"), out=o.get("G"))
+
         table = self.cos.numel() * 4 * 2
+        if fuse_residual_norm:
+            return [
+                Launch("A ln_modulate", A, act * (hb + 2) + 2 * vec),
+                Launch("B rms_rope q", Bq, act * 4 + vec + table // 2),
+                Launch("B rms_rope k", Bk, act * 4 + vec + table // 2),
+                Launch("C+D gated_residual ln_affine", CD, act * (hb + 2 + hb + 2) + 3 * vec, 1 if hb == 2 else 2),
+                Launch("E rms cross q", Eq, act * 4 + vec),
+                Launch("E rms cross k", Ek, self.cross_k.numel() * 4 + vec),
+                Launch("F+G residual_add ln_modulate", FG, act * (hb + 2 + hb + 2) + 2 * vec, 1 if hb == 2 else 2),
+                Launch("H gelu_tanh", H, self.ffn_hidden.numel() * 4),
+                Launch("I gated_residual", I, act * (hb + 2 + hb) + vec),
+            ]
         return [
             Launch("A ln_modulate", A, act * (hb + 2) + 2 * vec),
             Launch("B rms_rope q", Bq, act * 4 + vec + table // 2),
@@ -252,7 +273,7 @@ def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, b
 
 def _main():
     """python -m vrhino_b200.workloads [--config C] [--tokens N] [--frames T] [--only PREFIX]
-    [--repeat R] [--hidden bf16|f32]
+    [--repeat R] [--hidden bf16|f32] [--batch B] [--fuse-residual-norm]
 
     Runs (selected) launches of one configuration a few times and prints their device times; a
     small, self-contained command for profilers."""
@@ -265,15 +286,18 @@ def _main():
     ap.add_argument("--repeat", type=int, default=3)
     ap.add_argument("--hidden", default="bf16", choices=["bf16", "f32"])
     ap.add_argument("--batch", type=int, default=1, help="config 2: CFG branches batched into one tensor")
+    ap.add_argument("--fuse-residual-norm", action="store_true",
+                    help="config 2: residual update + following LayerNorm as one launch (9 launches per block)")
     a = ap.parse_args()
     be = ops.B200Backend()
     work = build_config(be, a.config, tokens=a.tokens, hidden_dtype=BF16 if a.hidden == "bf16" else F32, frames=a.frames,
                         batch=a.batch)
-    launches = [l for l in work.launches() if l.name.startswith(a.only)]
+    listed = work.launches(fuse_residual_norm=True) if a.fuse_residual_norm else work.launches()
+    launches = [l for l in listed if l.name.startswith(a.only)]
     total, per = time_launches(launches, steps=a.repeat, warmup=1)
     for l in launches:
-        print(f"{l.name:20s} {per[l.name] * 1e3:9.1f} us {l.bytes / per[l.name] / 1e6:9.1f} GB/s {l.bytes / 1e6:9.1f} MB")
-    print(f"{'total':20s} {total * 1e3:9.1f} us {sum(l.bytes for l in launches) / total / 1e6:9.1f} GB/s")
+        print(f"{l.name:32s} {per[l.name] * 1e3:9.1f} us {l.bytes / per[l.name] / 1e6:9.1f} GB/s {l.bytes / 1e6:9.1f} MB")
+    print(f"{'total':32s} {total * 1e3:9.1f} us {sum(l.bytes for l in launches) / total / 1e6:9.1f} GB/s")
 
 
 class WanBlockHost:
