@@ -263,6 +263,31 @@ int vrb_rms_norm_gated_residual(const void* residual, int residual_dtype,
                                 void* out, int state_dtype, int64_t rows, int64_t width,
                                 float eps, vrb_stream stream);
 
+/* ---- the bf16 linear's epilogue and the operator that reads its result --------------------
+ * CudaBackend::linear (native/src/backend/cuda/cuda_backend.cu:3661-3866) leaves the GEMM result in an
+ * F32 accumulation buffer [rows, width] and runs fused_bf16_linear_output_kernel (:754-764, called
+ * at :3831 and :3846):  y = bf16(accumulation + float(bias)),  bias bf16 [width] or NULL.
+ * vrb_linear_output is that kernel.  The three forms below also apply the operator the DiT
+ * blocks run on y next, so y itself is never written; each keeps every rounding of the separate
+ * kernels (results are bit-identical to vrb_linear_output followed by the named entry point). */
+int vrb_linear_output(const float* accumulation, const void* bias, void* out, int64_t rows,
+                      int64_t width, vrb_stream stream);
+/* out = activation(kind, y) as bf16   (wan.cpp:109-112: linear -> activation(GeluTanh)) */
+int vrb_linear_output_activation(const float* accumulation, const void* bias, int kind, void* out,
+                                 int64_t rows, int64_t width, vrb_stream stream);
+/* out = vrb_gated_residual(residual, y, gate)   (wan.cpp:114-116: linear -> gated_residual;
+ * gate NULL = residual_add, wan.cpp:99-103) */
+int vrb_linear_output_gated_residual(const float* accumulation, const void* bias,
+                                     const void* residual, int residual_dtype,
+                                     const void* gate, int gate_dtype,
+                                     int64_t rows_per_vector, int64_t gate_vectors,
+                                     void* out, int state_dtype, int64_t rows, int64_t width,
+                                     vrb_stream stream);
+/* accumulation [rows, 2*hidden], bias [2*hidden]: out = vrb_swiglu(y) as bf16 [rows, hidden]
+ * (mochi.cpp:195-202) */
+int vrb_linear_output_swiglu(const float* accumulation, const void* bias, void* out, int64_t rows,
+                             int64_t hidden, vrb_stream stream);
+
 /* SwiGLU (mochi.cpp:195-202) without the two slice copies: projected is [rows, 2*hidden],
  * out[r, j] = round(projected[r, j] * round(silu(projected[r, hidden + j]))). */
 int vrb_swiglu(const void* projected, void* out, int dtype, int64_t rows, int64_t hidden,

@@ -401,6 +401,17 @@ def gated_residual(be, policy, residual, branch, gate):
     return be.add(be.cast(residual, d), be.mul(be.cast(branch, d), be.cast(gate, d)))
 
 
+def linear_output(accumulation: T, bias: T | None) -> T:
+    """fused_bf16_linear_output_kernel (native/src/backend/cuda/cuda_backend.cu:754-764), the epilogue of
+    CudaBackend::linear for bf16 compute and bf16 output (:3831, :3846): one F32 add of the
+    accumulation and the bf16 bias (broadcast over rows), one RNE rounding to bf16."""
+    assert accumulation.dtype == F32 and (bias is None or bias.dtype == BF16)
+    acc = np.ascontiguousarray(accumulation.data, dtype=np.float32)
+    if bias is not None:
+        acc = (acc + bf16_bits_to_f32(bias.data).reshape(-1).astype(np.float32)).astype(np.float32)
+    return T(f32_to_bf16_bits(acc), BF16)
+
+
 def swiglu_hidden(be, projected):
     half = projected.shape[-1] // 2
     parts = be.split(projected, [half, half], -1)

@@ -148,7 +148,7 @@ class RefCuda:
                      "refc_layer_norm", "refc_rms_norm", "refc_activation", "refc_rope", "refc_group_norm", "refc_clamp",
                      "refc_exp", "refc_sqrt", "refc_dequantize", "refc_modulate", "refc_attention_norm", "refc_operation_rope",
                      "refc_residual_add", "refc_gated_residual", "refc_cfg_combine", "refc_euler_update", "refc_flow_to_x0",
-                     "refc_frame_group_norm"):
+                     "refc_frame_group_norm", "refc_linear"):
             getattr(lib, name).restype = _c.c_int64
         lib.refc_profile_total_ms.restype = _c.c_double
         self.lib = lib
@@ -198,6 +198,7 @@ class RefCuda:
     def layer_norm(self, x, w, b, eps): return self._h(self.lib.refc_layer_norm(self._i(x), self._i(w), self._i(b), _c.c_float(eps)))
     def rms_norm(self, x, w, eps, axis=-1, out_dtype=-1):
         return self._h(self.lib.refc_rms_norm(self._i(x), self._i(w), _c.c_float(eps), _c.c_int64(axis), int(out_dtype)))
+    def linear(self, x, w, bias): return self._h(self.lib.refc_linear(self._i(x), self._i(w), self._i(bias)))
     def activation(self, x, kind): return self._h(self.lib.refc_activation(self._i(x), int(kind)))
     def rope(self, x, c, s): return self._h(self.lib.refc_rope(self._i(x), self._i(c), self._i(s)))
     def group_norm(self, x, groups, w, b, eps): return self._h(self.lib.refc_group_norm(self._i(x), int(groups), self._i(w), self._i(b), _c.c_float(eps)))

@@ -151,6 +151,11 @@ int64_t refc_rms_norm(int64_t x, int64_t w, float eps, int64_t axis, int out_dty
         return keep(g_backend->rms_norm(at(x), opt(w), eps, axis, out_dtype < 0 ? DType::F16 : static_cast<DType>(out_dtype)));
     });
 }
+// CudaBackend::linear with its defaults (execution dtype compute and output): bf16 GEMM, F32
+// accumulation, fused_bf16_linear_output_kernel
+int64_t refc_linear(int64_t x, int64_t w, int64_t bias) {
+    return guarded([&] { return keep(g_backend->linear(at(x), at(w), opt(bias))); });
+}
 int64_t refc_activation(int64_t x, int kind) {
     return guarded([&] { return keep(g_backend->activation(at(x), static_cast<Activation>(kind))); });
 }

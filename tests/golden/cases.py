@@ -55,7 +55,23 @@ def _inputs(case):
         return {"packed": (codes.reshape(rows, inner), "u8"), "scales": (synth.uniform_range((rows, groups), 1e-3, 1e-2, seed=s, stream=1), "f32")}
     if k == "binary":
         return {"a": (n(case["a"], 0), case["dt"]), "b": (n(case["b"], 1), case["dt"])}
+    if k == "linear_output":
+        # A GEMM whose F32 accumulators are exact whatever the summation order: only column 0 of x
+        # is non-zero, so accumulation[m, n] = x[m, 0] * w[n, 0], the exact product of two bf16 values.
+        M, N, K = case["m"], case["n"], case["k"]
+        x = np.zeros((1, M, K), dtype=np.float32)
+        x[0, :, 0] = n((M,), 0)
+        return {"x": (x, "bf16"), "w": (n((N, K), 1, 0.0, 2.0), "bf16"), "bias": (n((N,), 2, 0.0, 0.5), "bf16"),
+                "res": (n((1, M, N), 3), case["state"]), "gate": (n((1, 1, N), 4, 0, 0.3), "f32")}
     raise KeyError(k)
+
+
+def linear_accumulation(case):
+    """The F32 accumulation buffer of a linear_output case (exact, see _inputs)."""
+    ins = _inputs(case)
+    widen = lambda a: (to_bits(a, "bf16").astype(np.uint32) << 16).view(np.float32)
+    x, w = widen(ins["x"][0])[0, :, 0], widen(ins["w"][0])[:, 0]
+    return np.ascontiguousarray(np.outer(x, w).astype(np.float32)[None])
 
 
 CASES = [
@@ -83,6 +99,8 @@ CASES = [
     {"name": "dequant_fp8_all_codes", "kind": "dequant", "rows": 8, "inner": 256, "group": 256, "all_codes": True, "seed": 19},
     {"name": "dequant_fp8_groups", "kind": "dequant", "rows": 16, "inner": 96, "group": 32, "seed": 20},
     {"name": "binary_internal_broadcast", "kind": "binary", "a": (3, 1, 7), "b": (1, 5, 1), "dt": "bf16", "seed": 21},
+    {"name": "linear_output_bf16_state", "kind": "linear_output", "m": 72, "n": 1536, "k": 16, "state": "bf16", "seed": 22, "subsample": 3},
+    {"name": "linear_output_f32_state", "kind": "linear_output", "m": 40, "n": 3072, "k": 32, "state": "f32", "seed": 23, "subsample": 5},
 ]
 
 
@@ -178,6 +196,18 @@ def run_reference(rc, case):
         shape = np.broadcast_shapes(case["a"], case["b"])
         for kind, name in enumerate(("add", "mul", "div", "max")):
             grab(name, rc.binary(kind, h["a"], h["b"]), shape)
+    elif k == "linear_output":
+        M, N = case["m"], case["n"]
+        p = ref.POLICY_BF16 if case["state"] == "bf16" else ref.POLICY_FP32
+        lin = rc.linear(h["x"], h["w"], h["bias"])
+        grab("linear", lin, (1, M, N))
+        grab("linear_nobias", rc.linear(h["x"], h["w"], 0), (1, M, N))
+        grab("gelu_tanh", rc.activation(lin, 2), (1, M, N))
+        grab("silu", rc.activation(lin, 0), (1, M, N))
+        grab("gated", rc.gated_residual(p, h["res"], lin, h["gate"]), (1, M, N))
+        grab("added", rc.residual_add(p, h["res"], lin), (1, M, N))
+        a, g = rc.slice(lin, 2, 0, N // 2), rc.slice(lin, 2, N // 2, N)
+        grab("swiglu", rc.binary(1, a, rc.activation(g, 0)), (1, M, N // 2))
     rc.clear()
     return out
 
@@ -240,6 +270,15 @@ def run_oracle(orc, case):
     elif k == "binary":
         for kind, name in enumerate(("add", "mul", "div", "max")):
             grab(name, be._binary(kind, ins["a"], ins["b"]))
+    elif k == "linear_output":
+        p = orc.Policy(residual=case["state"])
+        acc = orc.T(linear_accumulation(case), "f32")
+        lin = orc.linear_output(acc, ins["bias"])
+        grab("linear", lin); grab("linear_nobias", orc.linear_output(acc, None))
+        grab("gelu_tanh", be.activation(lin, 2)); grab("silu", be.activation(lin, 0))
+        grab("gated", orc.gated_residual(be, p, ins["res"], lin, ins["gate"]))
+        grab("added", orc.residual_add(be, p, ins["res"], lin))
+        grab("swiglu", orc.swiglu_hidden(be, lin))
     return out
 
 
@@ -351,4 +390,20 @@ def run_library(be, ops, case, fused=True):
     elif k == "binary":
         for name in ("add", "mul", "div", "maximum"):
             grab("max" if name == "maximum" else name, getattr(be, name)(ins["a"], ins["b"]))
+    elif k == "linear_output":
+        p = ops.Policy(residual=tdt[case["state"]])
+        acc = torch.from_numpy(linear_accumulation(case)).cuda()
+        lin = ops.linear_output(be, acc, ins["bias"])
+        grab("linear", lin); grab("linear_nobias", ops.linear_output(be, acc, None))
+        if fused:
+            grab("gelu_tanh", ops.linear_output_activation(be, acc, ins["bias"], ops.GELU_TANH))
+            grab("silu", ops.linear_output_activation(be, acc, ins["bias"], ops.SILU))
+            grab("gated", ops.linear_output_gated_residual(be, p, ins["res"], acc, ins["bias"], ins["gate"]))
+            grab("added", ops.linear_output_gated_residual(be, p, ins["res"], acc, ins["bias"], None))
+            grab("swiglu", ops.linear_output_swiglu(be, acc, ins["bias"]))
+        else:
+            grab("gelu_tanh", be.activation(lin, ops.GELU_TANH)); grab("silu", be.activation(lin, ops.SILU))
+            grab("gated", ops.fused_gated_residual(be, p, ins["res"], lin, ins["gate"]))
+            grab("added", ops.fused_gated_residual(be, p, ins["res"], lin, None))
+            grab("swiglu", ops.fused_swiglu(be, lin))
     return out

@@ -57,6 +57,12 @@ constexpr int64_t kLutMinElements = int64_t{4} << 20;
 bool unary_lut_applicable(int dtype, int64_t count, const void* x, const void* out);
 int launch_unary_lut(int op, const void* x, void* out, int64_t count, float p0, float p1, cudaStream_t stream);
 int launch_swiglu_lut(const void* proj, void* out, int64_t rows, int64_t hidden, cudaStream_t stream);
+// Linear epilogue + activation / SwiGLU through the table: width (hidden) % 8 == 0, 16-byte aligned
+// operands, fewer than 2^32 chunks of 8 output elements.
+int launch_linear_output_lut(int kind, const float* accumulation, const void* bias, void* out, int64_t rows, int64_t width,
+                             cudaStream_t stream);
+int launch_linear_output_swiglu_lut(const float* accumulation, const void* bias, void* out, int64_t rows, int64_t hidden,
+                                    cudaStream_t stream);
 // Where the GroupNorm normalise pass writes.  count == 0: `out`, laid out like x.  count > 0: the
 // same values go to every dst[k] (this GPU's and peer-mapped full-size tensors), plane p of x
 // landing at element p * plane_stride + plane_offset -- the all-gather of an H-sharded feature map

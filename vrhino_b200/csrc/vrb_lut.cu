@@ -137,6 +137,99 @@ __global__ void __launch_bounds__(kLutThreads, 1) swiglu_lut_kernel(const uint4*
     }
 }
 
+// The bf16 linear epilogue (fused_bf16_linear_output_kernel, native/src/backend/cuda/cuda_backend.cu:
+// 754-764) followed by an activation: y = bf16(accumulation + float(bias)) is a bf16 value, so
+// activation(y) is read from the table.  8 accumulators -> 4 packed bf16 pairs:
+__device__ __forceinline__ uint4 biased_pack(const float4& lo, const float4& hi, const uint4& bias, bool has_bias) {
+    float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    if (has_bias) {
+        const uint32_t bw[4] = {bias.x, bias.y, bias.z, bias.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            v[2 * k] = __fadd_rn(v[2 * k], __uint_as_float(bw[k] << 16));
+            v[2 * k + 1] = __fadd_rn(v[2 * k + 1], __uint_as_float(bw[k] & 0xffff0000u));
+        }
+    }
+    return make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+}
+
+template <int OP>
+__global__ void __launch_bounds__(kLutThreads, 1) linear_output_lut_kernel(const float4* __restrict__ accumulation,
+                                                                          const uint4* __restrict__ bias,
+                                                                          uint4* __restrict__ out, int64_t chunks,
+                                                                          unsigned width_chunks,
+                                                                          const uint4* __restrict__ ready) {
+    extern __shared__ __align__(16) uint16_t table[];
+    constexpr int U = 2;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kLutThreads;
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * kLutThreads + threadIdx.x;
+    const bool has_bias = bias != nullptr;
+    float4 a[U][2];
+    uint4 b[U];
+    auto request = [&](int64_t i) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t c = i + u * stride;
+            if (c >= chunks) break;
+            a[u][0] = __ldcs(accumulation + 2 * c);
+            a[u][1] = __ldcs(accumulation + 2 * c + 1);
+            if (has_bias) b[u] = __ldg(bias + static_cast<unsigned>(c) % width_chunks);   // chunks < 2^32
+        }
+    };
+    request(first);   // before the table copy, so HBM is busy while the table arrives
+    fill_table<OP>(table, ready, 0.f, 0.f);
+    for (int64_t i = first; i < chunks; i += stride * U) {
+        if (i != first) request(i);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (i + u * stride >= chunks) break;
+            const uint4 y = biased_pack(a[u][0], a[u][1], b[u], has_bias);
+            __stcs(out + i + u * stride,
+                   make_uint4(lookup2(table, y.x), lookup2(table, y.y), lookup2(table, y.z), lookup2(table, y.w)));
+        }
+    }
+}
+
+// ... followed by SwiGLU (mochi.cpp:195-202): accumulation is [rows, 2 * hidden]; the value half and
+// the gate half are each rounded to bf16 as the linear output would be, silu(gate) comes from the
+// table, the product is one bf16 multiply.
+__global__ void __launch_bounds__(kLutThreads, 1) linear_output_swiglu_lut_kernel(const float4* __restrict__ accumulation,
+                                                                                 const uint4* __restrict__ bias,
+                                                                                 uint4* __restrict__ out, int64_t chunks,
+                                                                                 unsigned hidden_chunks,
+                                                                                 const uint4* __restrict__ ready) {
+    extern __shared__ __align__(16) uint16_t table[];
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kLutThreads;
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * kLutThreads + threadIdx.x;
+    const bool has_bias = bias != nullptr;
+    float4 a[2], g[2];
+    uint4 ba, bg;
+    auto request = [&](int64_t c) {
+        if (c >= chunks) return;
+        const unsigned row = static_cast<unsigned>(c) / hidden_chunks, chunk = static_cast<unsigned>(c) - row * hidden_chunks;
+        const float4* src = accumulation + (static_cast<int64_t>(row) * 2 * hidden_chunks + chunk) * 2;
+        a[0] = __ldcs(src); a[1] = __ldcs(src + 1);
+        g[0] = __ldcs(src + 2 * hidden_chunks); g[1] = __ldcs(src + 2 * hidden_chunks + 1);
+        if (has_bias) { ba = __ldg(bias + chunk); bg = __ldg(bias + hidden_chunks + chunk); }
+    };
+    request(first);
+    fill_table<VRB_SILU>(table, ready, 0.f, 0.f);
+    for (int64_t i = first; i < chunks; i += stride) {
+        if (i != first) request(i);
+        const uint4 value = biased_pack(a[0], a[1], ba, has_bias), gate = biased_pack(g[0], g[1], bg, has_bias);
+        const uint32_t vw[4] = {value.x, value.y, value.z, value.w}, gw[4] = {gate.x, gate.y, gate.z, gate.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t s = lookup2(table, gw[k]);
+            const __nv_bfloat162 prod = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&vw[k]),
+                                                *reinterpret_cast<const __nv_bfloat162*>(&s));
+            ow[k] = *reinterpret_cast<const uint32_t*>(&prod);
+        }
+        __stcs(out + i, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+    }
+}
+
 // GroupNorm normalise pass + SiLU on bf16 (CudaBackend::group_norm :4919-5008 followed by
 // activation(Silu), native/src/components/autoencoder_kl.cpp:40-41): y = bf16((x - mean) * inv *
 // gamma + beta) with the reference's rounding order, then silu(y) read from the table, since y is
@@ -285,6 +378,43 @@ int launch_unary_lut(int op, const void* x, void* out, int64_t count, float p0, 
         case 6: return launch_lut<6>(x, out, count, p0, p1, stream);
         default: return launch_lut<7>(x, out, count, p0, p1, stream);
     }
+}
+
+template <int OP>
+int launch_linear_lut(const float* accumulation, const void* bias, void* out, int64_t rows, int64_t width, cudaStream_t stream) {
+    static bool done[64] = {false};
+    if (int rc = reserve_table(linear_output_lut_kernel<OP>, done)) return rc;
+    const int64_t chunks = rows * (width / 8);
+    const int64_t per_cta = (chunks + kLutThreads - 1) / kLutThreads;
+    const int grid = static_cast<int>(per_cta < sm_count() ? per_cta : sm_count());
+    linear_output_lut_kernel<OP><<<grid, kLutThreads, kTableBytes, stream>>>(
+        reinterpret_cast<const float4*>(accumulation), static_cast<const uint4*>(bias), static_cast<uint4*>(out), chunks,
+        static_cast<unsigned>(width / 8), ready_table<OP>(0.f, 0.f, stream));
+    return after_launch("linear_output_activation (table)");
+}
+
+int launch_linear_output_lut(int kind, const float* accumulation, const void* bias, void* out, int64_t rows, int64_t width,
+                             cudaStream_t stream) {
+    switch (kind) {
+        case 0: return launch_linear_lut<0>(accumulation, bias, out, rows, width, stream);
+        case 1: return launch_linear_lut<1>(accumulation, bias, out, rows, width, stream);
+        case 2: return launch_linear_lut<2>(accumulation, bias, out, rows, width, stream);
+        case 3: return launch_linear_lut<3>(accumulation, bias, out, rows, width, stream);
+        default: return launch_linear_lut<4>(accumulation, bias, out, rows, width, stream);
+    }
+}
+
+int launch_linear_output_swiglu_lut(const float* accumulation, const void* bias, void* out, int64_t rows, int64_t hidden,
+                                    cudaStream_t stream) {
+    static bool done[64] = {false};
+    if (int rc = reserve_table(linear_output_swiglu_lut_kernel, done)) return rc;
+    const int64_t chunks = rows * (hidden / 8);
+    const int64_t per_cta = (chunks + kLutThreads - 1) / kLutThreads;
+    const int grid = static_cast<int>(per_cta < sm_count() ? per_cta : sm_count());
+    linear_output_swiglu_lut_kernel<<<grid, kLutThreads, kTableBytes, stream>>>(
+        reinterpret_cast<const float4*>(accumulation), static_cast<const uint4*>(bias), static_cast<uint4*>(out), chunks,
+        static_cast<unsigned>(hidden / 8), ready_table<VRB_SILU>(0.f, 0.f, stream));
+    return after_launch("linear_output_swiglu (table)");
 }
 
 int launch_swiglu_lut(const void* proj, void* out, int64_t rows, int64_t hidden, cudaStream_t stream) {

@@ -539,6 +539,62 @@ def fused_swiglu(be, projected, out=None):
     return out
 
 
+def _linear_operands(accumulation, bias):
+    accumulation = _dense(accumulation)
+    if accumulation.dtype != F32:
+        raise VrbError("linear_output: the accumulation must be F32")
+    if bias is not None:
+        bias = _dense(bias)
+        if bias.dtype != BF16 or bias.numel() != accumulation.shape[-1]:
+            raise VrbError("linear bias mismatch")
+    width = accumulation.shape[-1]
+    return accumulation, bias, accumulation.numel() // width, width
+
+
+def linear_output(be, accumulation, bias, out=None):
+    """The epilogue of the reference's bf16 linear (fused_bf16_linear_output_kernel,
+    native/src/backend/cuda/cuda_backend.cu:754-764): bf16(accumulation + float(bias))."""
+    accumulation, bias, rows, width = _linear_operands(accumulation, bias)
+    out = _result(out, accumulation.shape, BF16, accumulation.device)
+    call("vrb_linear_output", _ptr(accumulation), _ptr(bias), _ptr(out), rows, width, _stream())
+    return out
+
+
+def linear_output_activation(be, accumulation, bias, kind, out=None):
+    """activation(linear_output(accumulation, bias), kind) without writing the linear output
+    (wan.cpp:109-112)."""
+    accumulation, bias, rows, width = _linear_operands(accumulation, bias)
+    out = _result(out, accumulation.shape, BF16, accumulation.device)
+    call("vrb_linear_output_activation", _ptr(accumulation), _ptr(bias), int(kind), _ptr(out), rows, width, _stream())
+    return out
+
+
+def linear_output_gated_residual(be, policy, residual, accumulation, bias, gate, out=None):
+    """gated_residual(residual, linear_output(accumulation, bias), gate) (residual_add when gate is
+    None) without writing the linear output (wan.cpp:99-103, 114-116)."""
+    accumulation, bias, rows, width = _linear_operands(accumulation, bias)
+    residual = _dense(residual)
+    if tuple(residual.shape) != tuple(accumulation.shape):
+        raise VrbError("Incompatible broadcast shapes")
+    rpv, nvec = (1, 1) if gate is None else _vec_layout(rows, residual.shape, gate)
+    out = _result(out, residual.shape, policy.residual, residual.device)
+    call("vrb_linear_output_gated_residual", _ptr(accumulation), _ptr(bias), _ptr(residual), _code(residual),
+         _ptr(_dense(gate)) if gate is not None else None, _code(gate) if gate is not None else 0, rpv, nvec, _ptr(out),
+         _code(policy.residual), rows, width, _stream())
+    return out
+
+
+def linear_output_swiglu(be, accumulation, bias, out=None):
+    """fused_swiglu(linear_output(accumulation, bias)) without writing the linear output
+    (mochi.cpp:195-202)."""
+    accumulation, bias, rows, width = _linear_operands(accumulation, bias)
+    if width % 2:
+        raise VrbError("split sections mismatch")
+    out = _result(out, accumulation.shape[:-1] + (width // 2,), BF16, accumulation.device)
+    call("vrb_linear_output_swiglu", _ptr(accumulation), _ptr(bias), _ptr(out), rows, width // 2, _stream())
+    return out
+
+
 def fused_cfg_combine(be, policy, unconditional, conditional, scale, out=None):
     out = _result(out, unconditional.shape, unconditional.dtype, unconditional.device)
     call("vrb_cfg_combine", _ptr(_dense(unconditional)), _ptr(_dense(conditional)), _ptr(out), _code(out),
