@@ -270,7 +270,8 @@ class RefDropin(RefCuda):
     def __init__(self, execution_dtype=BF16):
         super().__init__(execution_dtype)
         for name in ("refd_layer_norm_modulate", "refd_rms_norm_rope", "refd_gated_residual", "refd_swiglu",
-                     "refd_group_norm_silu", "refd_cfg_euler", "refd_gated_residual_layer_norm"):
+                     "refd_group_norm_silu", "refd_cfg_euler", "refd_gated_residual_layer_norm",
+                     "refd_linear_activation", "refd_linear_gated_residual", "refd_linear_swiglu"):
             getattr(self.lib, name).restype = _c.c_int64
 
     def name(self): return self.lib.refc_backend_name().decode()
@@ -289,6 +290,12 @@ class RefDropin(RefCuda):
                                                                  self._i(bias), _c.c_float(eps), self._i(shift), self._i(scale),
                                                                  int(out_dtype), _c.byref(state)))
         return state.value, normed
+    def fused_linear_activation(self, x, w, bias, kind):
+        return self._h(self.lib.refd_linear_activation(self._i(x), self._i(w), self._i(bias), int(kind)))
+    def fused_linear_gated_residual(self, policy, r, x, w, bias, g):
+        return self._h(self.lib.refd_linear_gated_residual(int(policy), self._i(r), self._i(x), self._i(w), self._i(bias), self._i(g)))
+    def fused_linear_swiglu(self, x, w, bias):
+        return self._h(self.lib.refd_linear_swiglu(self._i(x), self._i(w), self._i(bias)))
     def fused_swiglu(self, x): return self._h(self.lib.refd_swiglu(self._i(x)))
     def fused_group_norm_silu(self, x, groups, w, b, eps):
         return self._h(self.lib.refd_group_norm_silu(self._i(x), int(groups), self._i(w), self._i(b), _c.c_float(eps)))

@@ -247,6 +247,19 @@ int64_t refd_gated_residual_layer_norm(int policy, int64_t r, int64_t b, int64_t
         return keep(both.second);
     });
 }
+int64_t refd_linear_activation(int64_t x, int64_t w, int64_t bias, int kind) {
+    return guarded([&] {
+        return keep(vrhino_b200::linear_activation(*g_backend, at(x), at(w), opt(bias), static_cast<Activation>(kind)));
+    });
+}
+int64_t refd_linear_gated_residual(int policy, int64_t r, int64_t x, int64_t w, int64_t bias, int64_t g) {
+    return guarded([&] {
+        return keep(vrhino_b200::linear_gated_residual(*g_backend, policy_of(policy), at(r), at(x), at(w), opt(bias), opt(g)));
+    });
+}
+int64_t refd_linear_swiglu(int64_t x, int64_t w, int64_t bias) {
+    return guarded([&] { return keep(vrhino_b200::linear_swiglu(*g_backend, at(x), at(w), opt(bias))); });
+}
 int64_t refd_swiglu(int64_t x) { return guarded([&] { return keep(vrhino_b200::swiglu(*g_backend, at(x))); }); }
 int64_t refd_group_norm_silu(int64_t x, int groups, int64_t w, int64_t b, float eps) {
     return guarded([&] { return keep(vrhino_b200::group_norm_silu(*g_backend, at(x), groups, opt(w), opt(b), eps)); });

@@ -60,7 +60,7 @@ def _grab(rd, case, handle, shape):
 
 
 @pytest.mark.parametrize("case", [c for c in cases.CASES if c["kind"] in
-                                  ("ln_modulate", "rms_rope", "gated_residual", "mochi", "group_norm", "sampler")],
+                                  ("ln_modulate", "rms_rope", "gated_residual", "mochi", "group_norm", "sampler", "linear_output")],
                          ids=lambda c: c["name"])
 def test_fused_call_site_forms(orc, golden, dropin, case):
     """One kernel per chain through vrhino_b200::layer_norm_modulate / rms_norm_rope / ... ."""
@@ -110,6 +110,20 @@ def test_fused_call_site_forms(orc, golden, dropin, case):
                         assert np.array_equal(got_bits, want_bits)
                     else:   # the one-kernel modulate rounds once where the chain rounds per operator
                         compare(orc, case, "normed", (cases._sub(case, got_bits), "bf16"), (cases._sub(case, want_bits), "bf16"))
+        elif k == "linear_output":
+            # the device runtime's GEMM (exact accumulators in this case) + the merged epilogue kernels,
+            # bit for bit against the reference's linear -> consumer chain
+            M, N = case["m"], case["n"]
+            p = ref.POLICY_BF16 if case["state"] == "bf16" else ref.POLICY_FP32
+            for kind, name in ((2, "gelu_tanh"), (0, "silu")):
+                got = rd.fused_linear_activation(h["x"], h["w"], h["bias"], kind)
+                compare(orc, case, name, _grab(rd, case, got, (1, M, N)), want[name], strict_tables=True)
+            compare(orc, case, "gated", _grab(rd, case, rd.fused_linear_gated_residual(p, h["res"], h["x"], h["w"], h["bias"], h["gate"]),
+                                              (1, M, N)), want["gated"])
+            compare(orc, case, "added", _grab(rd, case, rd.fused_linear_gated_residual(p, h["res"], h["x"], h["w"], h["bias"], 0),
+                                              (1, M, N)), want["added"])
+            compare(orc, case, "swiglu", _grab(rd, case, rd.fused_linear_swiglu(h["x"], h["w"], h["bias"]), (1, M, N // 2)),
+                    want["swiglu"], strict_tables=True)
         elif k == "mochi":
             B, S, D = case["shape"]
             compare(orc, case, "swiglu", _grab(rd, case, rd.fused_swiglu(h["proj"]), (B, S, case["hidden"])), want["swiglu"])
@@ -315,3 +329,37 @@ def test_errors_and_session_semantics(dropin):
     finally:
         rd.lib.refc_shutdown()          # a fresh backend for whoever uses the library next
         rd.lib.refc_init(ref.BF16)
+
+
+def test_merged_linear_forms_on_a_dense_gemm(orc, dropin):
+    """A dense K=512 GEMM: the merged forms take the device runtime's F32 accumulation, the stock chain
+    takes whichever plan the reference's linear picks for a bf16 result, so accumulators may differ in
+    their last bits: <= 2 bf16 ulp (activation, SwiGLU) and the gated residual within one bf16 ulp of
+    the branch."""
+    from oracle import ref
+    rd = dropin
+    rng = np.random.default_rng(3)
+    M, N, K = 256, 1536, 512
+    up = lambda a, dt=ref.BF16: rd.upload(cases.to_bits(a.astype(np.float32), "bf16" if dt == ref.BF16 else "f32"), dt)
+    x, w = up(rng.normal(0, 1, (1, M, K))), up(rng.normal(0, K ** -0.5, (N, K)))
+    bias, res, gate = up(rng.normal(0, 0.5, (N,))), up(rng.normal(0, 1, (1, M, N))), up(rng.normal(0, 0.3, (1, 1, N)), ref.F32)
+    case = {"name": "dense_gemm", "kind": "dense_linear"}
+    try:
+        lin = rd.linear(x, w, bias)
+        pairs = [
+            ("gelu_tanh", rd.fused_linear_activation(x, w, bias, 2), rd.activation(lin, 2), (1, M, N)),
+            ("gated", rd.fused_linear_gated_residual(ref.POLICY_BF16, res, x, w, bias, gate),
+             rd.gated_residual(ref.POLICY_BF16, res, lin, gate), (1, M, N)),
+            ("swiglu", rd.fused_linear_swiglu(x, w, bias),
+             rd.binary(1, rd.slice(lin, 2, 0, N // 2), rd.activation(rd.slice(lin, 2, N // 2, N), 0)), (1, M, N // 2)),
+        ]
+        for name, got, want, shape in pairs:
+            g, gdt = rd.download(got, shape)
+            w_, wdt = rd.download(want, shape)
+            assert gdt == wdt == ref.BF16
+            d = orc.bf16_ulp_distance(g, w_)
+            assert (d <= 2).mean() >= 0.998, f"{name}: {(d > 2).sum()} of {d.size} beyond 2 ulp"
+            diff = np.abs(orc.bf16_bits_to_f32(g).astype(np.float64) - orc.bf16_bits_to_f32(w_).astype(np.float64))
+            assert diff.max() <= 2.0 ** -8 * 8.0, f"{name}: max difference {diff.max()}"
+    finally:
+        rd.clear()

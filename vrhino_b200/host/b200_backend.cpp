@@ -431,6 +431,65 @@ std::pair<Tensor, Tensor> B200Backend::gated_residual_layer_norm(const Tensor& r
     return result;
 }
 
+namespace {
+// The merged epilogue applies where the reference's linear would run fused_bf16_linear_output_kernel:
+// bf16 compute and bf16 output, weights not quantised (cuda_backend.cu:3678-3790 take another route).
+bool merged_linear_applies(const B200Backend& backend, const Tensor& weight) {
+    return backend.execution_dtype() == DType::BF16 && !weight.is_quantized();
+}
+}  // namespace
+
+Tensor B200Backend::linear_activation(const Tensor& x, const Tensor& weight, const Tensor* bias_raw, vrhino::Activation kind) {
+    if (!merged_linear_applies(*this, weight)) return activation(linear(x, weight, bias_raw), kind);
+    return guarded([&] {
+        Tensor accumulation = rt_->linear(x, weight, nullptr, DType::BF16, DType::F32);
+        const int64_t width = accumulation.dim(-1), rows = accumulation.numel() / width;
+        Tensor bias;
+        if (bias_raw) { bias = copy_to_device(*bias_raw, DType::BF16); require(bias.numel() == width, "linear bias mismatch"); }
+        Tensor out = rt_->allocate_device(accumulation.shape(), DType::BF16);
+        check(vrb_linear_output_activation(accumulation.data_as<float>(), bias_raw ? bias.data() : nullptr, static_cast<int>(kind),
+                                           out.data(), rows, width, kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::linear_gated_residual(const Tensor& residual_raw, const Tensor& x, const Tensor& weight,
+                                          const Tensor* bias_raw, const Tensor* gate_raw, DType state) {
+    if (!merged_linear_applies(*this, weight)) return gated_residual(residual_raw, linear(x, weight, bias_raw), gate_raw, state);
+    return guarded([&] {
+        Tensor accumulation = rt_->linear(x, weight, nullptr, DType::BF16, DType::F32);
+        Tensor residual = copy_to_device(residual_raw, operand_dtype(residual_raw)), bias, gate;
+        require(residual.shape() == accumulation.shape(), "Incompatible broadcast shapes");
+        const int64_t width = accumulation.dim(-1), rows = accumulation.numel() / width;
+        if (bias_raw) { bias = copy_to_device(*bias_raw, DType::BF16); require(bias.numel() == width, "linear bias mismatch"); }
+        int64_t rows_per_vector = 1, vectors = 1;
+        if (gate_raw) { gate = parameter(*gate_raw); vector_layout(residual, gate, rows_per_vector, vectors); }
+        Tensor out = rt_->allocate_device(residual.shape(), state);
+        check(vrb_linear_output_gated_residual(accumulation.data_as<float>(), bias_raw ? bias.data() : nullptr, residual.data(),
+                                               code(residual.dtype()), gate_raw ? gate.data() : nullptr,
+                                               gate_raw ? code(gate.dtype()) : 0, rows_per_vector, vectors, out.data(),
+                                               code(state), rows, width, kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::linear_swiglu(const Tensor& x, const Tensor& weight, const Tensor* bias_raw) {
+    if (!merged_linear_applies(*this, weight)) return swiglu(linear(x, weight, bias_raw));
+    return guarded([&] {
+        Tensor accumulation = rt_->linear(x, weight, nullptr, DType::BF16, DType::F32);
+        const int64_t width = accumulation.dim(-1), rows = accumulation.numel() / width;
+        require(width % 2 == 0, "split sections mismatch");
+        Tensor bias;
+        if (bias_raw) { bias = copy_to_device(*bias_raw, DType::BF16); require(bias.numel() == width, "linear bias mismatch"); }
+        std::vector<int64_t> shape = accumulation.shape();
+        shape.back() = width / 2;
+        Tensor out = rt_->allocate_device(shape, DType::BF16);
+        check(vrb_linear_output_swiglu(accumulation.data_as<float>(), bias_raw ? bias.data() : nullptr, out.data(), rows,
+                                       width / 2, kLegacyStream));
+        return out;
+    });
+}
+
 Tensor B200Backend::swiglu(const Tensor& raw) {
     return guarded([&] {
         const DType dtype = operand_dtype(raw);
@@ -499,6 +558,27 @@ std::pair<Tensor, Tensor> fused_gated_residual_layer_norm(vrhino::Backend& backe
     Tensor normed = backend.layer_norm(state, weight, bias, eps);
     if (scale) normed = vrhino::modulate(backend, policy, normed, *shift, *scale);
     return {state, backend.cast(normed, output)};
+}
+
+Tensor linear_activation(vrhino::Backend& backend, const Tensor& x, const Tensor& weight, const Tensor* bias,
+                         vrhino::Activation kind) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend)) return b200->linear_activation(x, weight, bias, kind);
+    return backend.activation(backend.linear(x, weight, bias), kind);
+}
+
+Tensor linear_gated_residual(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy, const Tensor& residual,
+                             const Tensor& x, const Tensor& weight, const Tensor* bias, const Tensor* gate) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend))
+        return b200->linear_gated_residual(residual, x, weight, bias, gate,
+                                           policy.persistent_state_dtype(vrhino::PrecisionSemantic::ResidualState));
+    Tensor branch = backend.linear(x, weight, bias);
+    return gate ? vrhino::gated_residual(backend, policy, residual, branch, *gate)
+                : vrhino::residual_add(backend, policy, residual, branch);
+}
+
+Tensor linear_swiglu(vrhino::Backend& backend, const Tensor& x, const Tensor& weight, const Tensor* bias) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend)) return b200->linear_swiglu(x, weight, bias);
+    return swiglu(backend, backend.linear(x, weight, bias));
 }
 
 Tensor swiglu(vrhino::Backend& backend, const Tensor& projected) {

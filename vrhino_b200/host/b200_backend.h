@@ -70,6 +70,14 @@ public:
     std::pair<Tensor, Tensor> gated_residual_layer_norm(const Tensor& residual, const Tensor& branch, const Tensor* gate,
                                                         DType state, const Tensor* weight, const Tensor* bias, float eps,
                                                         const Tensor* shift, const Tensor* scale, DType output);
+    // ---- linear + the operator that reads its result: the GEMM is the device runtime's, asked for
+    // its F32 accumulation (linear(x, w, no bias, BF16 compute, F32 output)); the bf16 epilogue
+    // (cuda_backend.cu:754-764) and the consumer run as ONE kernel, so the rounded linear output is
+    // never written.  BF16 execution and unquantised weights only; otherwise the operators compose.
+    Tensor linear_activation(const Tensor& x, const Tensor& weight, const Tensor* bias, vrhino::Activation kind);
+    Tensor linear_gated_residual(const Tensor& residual, const Tensor& x, const Tensor& weight, const Tensor* bias,
+                                 const Tensor* gate, DType state);
+    Tensor linear_swiglu(const Tensor& x, const Tensor& weight, const Tensor* bias);
     Tensor swiglu(const Tensor& projected);
     Tensor group_norm_silu(const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps);
     // x [B, C, T, H, W]: statistics per (batch entry, frame, group), no permutes
@@ -197,6 +205,16 @@ std::pair<vrhino::Tensor, vrhino::Tensor> fused_gated_residual_layer_norm(
     vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy, const vrhino::Tensor& residual,
     const vrhino::Tensor& branch, const vrhino::Tensor* gate, const vrhino::Tensor* weight, const vrhino::Tensor* bias,
     float eps, const vrhino::Tensor* shift, const vrhino::Tensor* scale, vrhino::DType output = vrhino::DType::BF16);
+// activation(linear(x, weight, bias), kind)   (wan.cpp:109-112)
+vrhino::Tensor linear_activation(vrhino::Backend& backend, const vrhino::Tensor& x, const vrhino::Tensor& weight,
+                                 const vrhino::Tensor* bias, vrhino::Activation kind);
+// gated_residual / residual_add (gate == nullptr) of residual and linear(x, weight, bias)   (wan.cpp:113-116)
+vrhino::Tensor linear_gated_residual(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy,
+                                     const vrhino::Tensor& residual, const vrhino::Tensor& x,
+                                     const vrhino::Tensor& weight, const vrhino::Tensor* bias, const vrhino::Tensor* gate);
+// the SwiGLU of linear(x, weight, bias): split -> silu -> mul   (mochi.cpp:197-200)
+vrhino::Tensor linear_swiglu(vrhino::Backend& backend, const vrhino::Tensor& x, const vrhino::Tensor& weight,
+                             const vrhino::Tensor* bias);
 // mul(parts[0], silu(parts[1])), parts = split(projected, {H, H}, -1)   (mochi.cpp:195-202)
 vrhino::Tensor swiglu(vrhino::Backend& backend, const vrhino::Tensor& projected);
 // activation(group_norm(x, groups, weight, bias, eps), Silu)   (autoencoder_kl.cpp:31-41)
