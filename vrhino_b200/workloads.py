@@ -252,8 +252,51 @@ class VaeGroupNorm:
         return [Launch("group_norm_silu", gn, self.x.numel() * 6, kernels=4)]
 
 
+class LinearEpilogues:
+    """The bf16 linear's epilogue merged with the operator that reads its result, at the sizes of the
+    DiT blocks: FFN up-projection -> GELU-tanh [B*S, 8960] (wan.cpp:109-112), FFN down-projection ->
+    gated residual [B, S, 1536] (wan.cpp:113-116), Mochi FFN -> SwiGLU [S, 2*8192] (mochi.cpp:197-200).
+    Inputs are F32 "GEMM accumulators" ~N(0,1); algorithmic bytes = accumulation + bias (+ residual)
+    read once, result written once.  merged=False runs epilogue and consumer as two launches."""
+
+    def __init__(self, be, tokens=32760, batch=2, dim=1536, ffn=8960, swiglu_hidden=8192, seed=0, merged=True):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        self.be, self.merged = be, merged
+        self.policy = ops.Policy(BF16, BF16)
+        self.acc_up = _randn((batch, tokens, ffn), F32, g)
+        self.bias_up = _randn((ffn,), BF16, g, 0.0, 0.5)
+        self.acc_down = _randn((batch, tokens, dim), F32, g)
+        self.bias_down = _randn((dim,), BF16, g, 0.0, 0.5)
+        self.res = _randn((batch, tokens, dim), BF16, g)
+        self.gate = _randn((batch, 1, dim), F32, g, std=0.3)
+        self.acc_glu = _randn((1, tokens, 2 * swiglu_hidden), F32, g)
+        self.out = {}
+
+    def launches(self) -> List[Launch]:
+        be, p, o = self.be, self.policy, self.out
+        up, down, glu = self.acc_up.numel(), self.acc_down.numel(), self.acc_glu.numel()
+
+        def gelu(): o["gelu"] = ops.linear_output_activation(be, self.acc_up, self.bias_up, ops.GELU_TANH, out=o.get("gelu"))
+        def gated(): o["gated"] = ops.linear_output_gated_residual(be, p, self.res, self.acc_down, self.bias_down, self.gate, out=o.get("gated"))
+        def swiglu(): o["swiglu"] = ops.linear_output_swiglu(be, self.acc_glu, None, out=o.get("swiglu"))
+        def lin_up(): o["lin_up"] = ops.linear_output(be, self.acc_up, self.bias_up, out=o.get("lin_up"))
+        def lin_down(): o["lin_down"] = ops.linear_output(be, self.acc_down, self.bias_down, out=o.get("lin_down"))
+        def lin_glu(): o["lin_glu"] = ops.linear_output(be, self.acc_glu, None, out=o.get("lin_glu"))
+        def gelu2(): o["gelu"] = be.activation(o["lin_up"], ops.GELU_TANH, out=o.get("gelu"))
+        def gated2(): o["gated"] = ops.fused_gated_residual(be, p, self.res, o["lin_down"], self.gate, out=o.get("gated"))
+        def swiglu2(): o["swiglu"] = ops.fused_swiglu(be, o["lin_glu"], out=o.get("swiglu"))
+
+        if self.merged:
+            return [Launch("linear_output gelu_tanh", gelu, up * 6), Launch("linear_output gated_residual", gated, down * 8),
+                    Launch("linear_output swiglu", swiglu, glu * 4 + glu)]
+        return [Launch("epilogue up", lin_up, up * 6), Launch("gelu_tanh", gelu2, up * 4),
+                Launch("epilogue down", lin_down, down * 6), Launch("gated_residual", gated2, down * 6),
+                Launch("epilogue glu", lin_glu, glu * 6), Launch("swiglu", swiglu2, glu * 3)]
+
+
 def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, batch=1):
-    """The launch list of headline configuration 2..5 (optionally at a reduced token / frame count)."""
+    """The launch list of headline configuration 2..5 (optionally at a reduced token / frame count),
+    or of the additional measurement configurations 6..9."""
     if config == 2:
         t = tokens or 32760
         return WanBlock(be, tokens=t, grid=(21, 30, 52) if t == 32760 else (1, 1, t), hidden_dtype=hidden_dtype, batch=batch)
@@ -267,8 +310,11 @@ def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, b
         return VaeGroupNorm(be, shape=(frames or 28, 256, 1, 240, 424))
     if config == 7:
         return VaeGroupNorm(be, shape=(1, 256, frames or 28, 240, 424), per_frame=True)
-    raise ValueError("config must be 2..7 (6 = config 5 as a pre-permuted per-frame tensor, 7 = per-frame statistics "
-                     "on the unpermuted [N,C,T,H,W] tensor)")
+    if config in (8, 9):
+        return LinearEpilogues(be, tokens=tokens or 32760, batch=batch, merged=config == 8)
+    raise ValueError("config must be 2..9 (6 = config 5 as a pre-permuted per-frame tensor, 7 = per-frame statistics "
+                     "on the unpermuted [N,C,T,H,W] tensor, 8 = linear epilogues merged with their consumers, "
+                     "9 = the same as separate launches)")
 
 
 def _main():
