@@ -249,7 +249,7 @@ class RefCuda:
     def wan_chain_graph(self, tokens, width, heads, hidden_dtype, eps, handles, fused=False):
         """Evaluates the non-GEMM part of the Wan self-attention graph (built node for node in
         ref_cuda.cpp) through neural_graph::evaluate, or -- drop-in build, fused=True -- through
-        vrhino_b200::evaluate_fused.  handles: hidden, modulation, cos, sin, q, k, projection,
+        vrhino_b200::evaluate_fused (fused=2: without its per-graph synchronisation).  handles: hidden, modulation, cos, sin, q, k, projection,
         table, norm_q, norm_k.  Returns ([attention input, q operand, k operand, residual], stats)."""
         h = (_c.c_int64 * 10)(*handles)
         out = (_c.c_int64 * 4)()

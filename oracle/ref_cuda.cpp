@@ -345,7 +345,8 @@ neural_graph::Graph wan_chain_graph(int64_t s, int64_t width, int64_t heads_coun
 }  // namespace
 
 // handles: hidden, modulation, cos, sin, q, k, projection, table, norm_q, norm_k (10); out: 4 handles.
-// fused != 0 (drop-in build only) runs vrhino_b200::evaluate_fused; stats (may be null) receives
+// fused != 0 (drop-in build only) runs vrhino_b200::evaluate_fused (fused == 2: without the per-graph
+// device synchronisation); stats (may be null) receives
 // {layer_norm_modulate, rms_norm_rope, gated_residual, nodes_total, nodes_absorbed}.
 int refc_wan_chain_graph(int64_t s, int64_t width, int64_t heads, int hidden_dtype, float eps, const int64_t* handles,
                          int fused, int64_t* out, int* stats) {
@@ -358,7 +359,7 @@ int refc_wan_chain_graph(int64_t s, int64_t width, int64_t heads, int hidden_dty
         if (fused) {
 #ifdef VRB_DROPIN
             vrhino_b200::FusionStats fs;
-            results = vrhino_b200::evaluate_fused(*g_backend, graph, inputs, parameters, &fs);
+            results = vrhino_b200::evaluate_fused(*g_backend, graph, inputs, parameters, &fs, fused != 2);
             if (stats) { stats[0] = fs.layer_norm_modulate; stats[1] = fs.rms_norm_rope; stats[2] = fs.gated_residual;
                          stats[3] = fs.nodes_total; stats[4] = fs.nodes_absorbed; }
 #else

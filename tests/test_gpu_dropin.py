@@ -181,6 +181,9 @@ def test_graph_fusion_pass(orc, dropin, hidden):
     fused, stats = run(dropin, True)
     assert stats[:3] == [1, 2, 1], stats
     assert stats[4] >= 9, stats            # LN, (cast), mul, add, 1+scale; 2 x (rms, reshape, rope); casts, mul
+    undrained, _ = run(dropin, 2)          # no per-graph device synchronisation: same stream order, same bits
+    for (g, _), (w, _) in zip(undrained, fused):
+        assert np.array_equal(g, w)
     for got in (node_by_node, fused):
         for (g, gdt), (w, wdt), name in zip(got, want, ("attention input", "q operand", "k operand", "residual")):
             assert gdt == wdt and g.shape == w.shape, name

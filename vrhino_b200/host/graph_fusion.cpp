@@ -57,7 +57,7 @@ struct Dispatch {
 }  // namespace
 
 std::vector<Tensor> evaluate_fused(B200Backend& backend, const ng::Graph& graph, const std::vector<Tensor>& inputs,
-                                   const std::vector<Tensor>& parameters, FusionStats* stats) {
+                                   const std::vector<Tensor>& parameters, FusionStats* stats, bool drain) {
     const ng::Description& d = graph.description();
     require(inputs.size() == d.inputs.size(), "Input slot count mismatch");
     require(parameters.size() == d.parameters.size(), "Parameter slot count mismatch");
@@ -114,7 +114,7 @@ std::vector<Tensor> evaluate_fused(B200Backend& backend, const ng::Graph& graph,
                 "Backend returned invalid tensor metadata");
         values[n.result] = std::move(result);
     }
-    backend.synchronize();
+    if (drain) backend.synchronize();
     std::vector<Tensor> outputs;
     outputs.reserve(d.outputs.size());
     for (ng::ValueId id : d.outputs) {

@@ -52,9 +52,14 @@ FusionPlan plan_fusion(const vrhino::neural_graph::Description& description);
 
 // Same contract as neural_graph::evaluate: inputs / parameters bound in slot order, host
 // tensors uploaded on demand, outputs in d.outputs order after a synchronize().
+// drain = false leaves out that per-graph device synchronisation
+// (native/src/runtime/neural_graph_evaluator.cpp:151): every operator of the backend is enqueued on
+// the same stream, so a caller that keeps enqueueing (the next block's graph) needs no host
+// wait between graphs; a device fault then surfaces at the caller's next synchronising call
+// instead of as this graph's completion failure.
 std::vector<vrhino::Tensor> evaluate_fused(B200Backend& backend, const vrhino::neural_graph::Graph& graph,
                                            const std::vector<vrhino::Tensor>& inputs,
                                            const std::vector<vrhino::Tensor>& parameters,
-                                           FusionStats* stats = nullptr);
+                                           FusionStats* stats = nullptr, bool drain = true);
 
 }  // namespace vrhino_b200
