@@ -91,6 +91,17 @@ int vrb_rms_norm_axis(const void* x, int dtype, const void* weight, int weight_d
                       int64_t outer, int64_t axis, int64_t inner, float eps, int fuse_silu,
                       vrb_stream stream);
 
+/* CudaBackend::pixel_norm (:5048-5086) over the middle axis of x [outer, channels, inner]:
+ *   y = x / sqrtf(mean_c(x^2) + eps)  in x's dtype, the kernels' F32 summation schedules (:2097-2165).
+ * With scale / shift ([outer, channels], both or neither) the result continues as the head of LTX's
+ * decoder_residual (native/src/architectures/ltx.cpp:221-227):
+ *   out = cast(F32(y) * (1 + F32(scale)) + F32(shift), out_dtype)     modulate, common.cpp:51-61
+ * and with fuse_silu the activation (activation(Silu)) is applied before the final cast.
+ * Without scale / shift out_dtype must equal dtype. */
+int vrb_pixel_norm(const void* x, int dtype, const void* scale, const void* shift, int mod_dtype,
+                   int fuse_silu, void* out, int out_dtype, int64_t outer, int64_t channels,
+                   int64_t inner, float eps, vrb_stream stream);
+
 /* CudaBackend::rope_nd (:4198-4213).  cos/sin have f_shape and broadcast against x_shape. */
 int vrb_rope(const void* x, int x_dtype, const int64_t* x_shape, int x_rank,
              const void* cosine, const void* sine, int f_dtype, const int64_t* f_shape, int f_rank,

@@ -274,6 +274,20 @@ class OracleBackend:
                                     ctypes.c_int64(inner), ctypes.c_float(eps))
         return T(out, out_dtype)
 
+    def pixel_norm(self, raw: T, dim: int = 1, eps: float = 1e-8) -> T:
+        """CudaBackend::pixel_norm (native/src/backend/cuda/cuda_backend.cu:5048-5086): x / sqrt(mean(x^2)
+        over `dim` + eps) in x's dtype, with the kernels' F32 summation schedules."""
+        dtype = self._dtype_of(raw)
+        x = self.copy_to_device(raw, dtype)
+        dim = dim + len(x.shape) if dim < 0 else dim
+        channels = x.shape[dim]
+        inner = int(np.prod(x.shape[dim + 1:]))
+        outer = x.numel // (channels * inner)
+        out = np.empty(x.shape, dtype=_NP[dtype])
+        lib().orc_pixel_norm(_p(x.data), _p(out), _CODE[dtype], ctypes.c_int64(outer), ctypes.c_int64(channels),
+                             ctypes.c_int64(inner), ctypes.c_float(eps))
+        return T(out, dtype)
+
     def activation(self, raw: T, kind: int) -> T:
         dtype = self._dtype_of(raw)
         x = self.copy_to_device(raw, dtype)
@@ -456,6 +470,12 @@ def flow_to_x0(be, policy, sample, model_output, sigma):
 def group_norm_silu(be, x, groups, weight, bias, eps):
     """autoencoder_kl.cpp:40-41 / mochi.cpp:373-377: GroupNorm, then a separate SiLU kernel."""
     return be.activation(be.group_norm(x, groups, weight, bias, eps), SILU)
+
+
+def pixel_norm_modulate_silu(be, policy, x, shift, scale, eps=1e-8):
+    """LTX decoder_residual (native/src/architectures/ltx.cpp:221-227): silu(modulate(pixel_norm(x), shift,
+    scale)) with shift / scale [B, C, 1, 1, 1]; the result is F32 (modulate's contract output)."""
+    return be.activation(modulate(be, policy, be.pixel_norm(x, 1, eps), shift, scale), SILU)
 
 
 def rms_channel_silu(be, x, gamma, eps=1e-12):

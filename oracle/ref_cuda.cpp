@@ -156,6 +156,9 @@ int64_t refc_rms_norm(int64_t x, int64_t w, float eps, int64_t axis, int out_dty
 int64_t refc_linear(int64_t x, int64_t w, int64_t bias) {
     return guarded([&] { return keep(g_backend->linear(at(x), at(w), opt(bias))); });
 }
+int64_t refc_pixel_norm(int64_t x, int64_t dim, float eps) {
+    return guarded([&] { return keep(g_backend->pixel_norm(at(x), dim, eps)); });
+}
 int64_t refc_activation(int64_t x, int kind) {
     return guarded([&] { return keep(g_backend->activation(at(x), static_cast<Activation>(kind))); });
 }
@@ -259,6 +262,12 @@ int64_t refd_linear_gated_residual(int policy, int64_t r, int64_t x, int64_t w, 
 }
 int64_t refd_linear_swiglu(int64_t x, int64_t w, int64_t bias) {
     return guarded([&] { return keep(vrhino_b200::linear_swiglu(*g_backend, at(x), at(w), opt(bias))); });
+}
+int64_t refd_pixel_norm_modulate_silu(int policy, int64_t x, int64_t shift, int64_t scale, float eps, int out_dtype) {
+    return guarded([&] {
+        return keep(vrhino_b200::pixel_norm_modulate_silu(*g_backend, policy_of(policy), at(x), at(shift), at(scale), eps,
+                                                          static_cast<DType>(out_dtype)));
+    });
 }
 int64_t refd_swiglu(int64_t x) { return guarded([&] { return keep(vrhino_b200::swiglu(*g_backend, at(x))); }); }
 int64_t refd_group_norm_silu(int64_t x, int groups, int64_t w, int64_t b, float eps) {

@@ -310,6 +310,52 @@ void orc_rms_norm_axis(const void* x, const void* w, void* out, int dt,
         }
 }
 
+/* ---- pixel_norm (CudaBackend::pixel_norm :5048-5086) over axis 1 of x [outer, channels, inner] ----
+ * inner > 1: pixel_norm_strided_axis_kernel :2131-2165 -- 8 channel lanes per position, lane a
+ * accumulates channels a, a+8, ... with `square += value * value` (one FFMA after nvcc's
+ * contraction), then the shared-memory tree with strides 4, 2, 1.
+ * inner == 1: pixel_norm_contiguous_axis_kernel :2097-2126 -- 256 thread partials (thread t takes
+ * channels t, t+256, ...), then group_norm_block_sum's tree (:1884-1893, strides 128 ... 1).
+ * denominator = sqrtf(total / channels + eps); out = x / denominator, rounded to x's dtype. */
+void orc_pixel_norm(const void* x, void* out, int dt, int64_t outer, int64_t channels, int64_t inner, float eps) {
+#pragma omp parallel for schedule(static)
+    for (int64_t o = 0; o < outer; ++o)
+        for (int64_t i = 0; i < inner; ++i) {
+            const int64_t base = o * channels * inner + i;
+            float total;
+            if (inner > 1) {
+                float lane[8];
+                for (int a = 0; a < 8; ++a) {
+                    float q = 0.0f;
+                    for (int64_t c = a; c < channels; c += 8) {
+                        const float v = ld(x, dt, base + c * inner);
+                        q = fmaf(v, v, q);
+                    }
+                    lane[a] = q;
+                }
+                for (int stride = 4; stride > 0; stride /= 2)
+                    for (int a = 0; a < stride; ++a) lane[a] += lane[a + stride];
+                total = lane[0];
+            } else {
+                float part[256];
+                for (int t = 0; t < 256; ++t) {
+                    float q = 0.0f;
+                    for (int64_t c = t; c < channels; c += 256) {
+                        const float v = ld(x, dt, base + c);
+                        q = fmaf(v, v, q);
+                    }
+                    part[t] = q;
+                }
+                for (int stride = 128; stride > 0; stride /= 2)
+                    for (int t = 0; t < stride; ++t) part[t] += part[t + stride];
+                total = part[0];
+            }
+            const float denominator = sqrtf(total / (float)channels + eps);
+            for (int64_t c = 0; c < channels; ++c)
+                st(out, dt, base + c * inner, ld(x, dt, base + c * inner) / denominator);
+        }
+}
+
 /* ---- RoPE (rope_kernel :1200-1215): adjacent pairs, two separately rounded products ---- */
 int orc_rope(const void* x, int x_dt, int x_rank, const int64_t* x_shape,
              const void* cosine, const void* sine, int f_dt, int f_rank, const int64_t* f_shape,

@@ -55,6 +55,10 @@ def _inputs(case):
         return {"packed": (codes.reshape(rows, inner), "u8"), "scales": (synth.uniform_range((rows, groups), 1e-3, 1e-2, seed=s, stream=1), "f32")}
     if k == "binary":
         return {"a": (n(case["a"], 0), case["dt"]), "b": (n(case["b"], 1), case["dt"])}
+    if k == "pixel_norm":
+        shape = case["shape"]
+        vec = (shape[0], shape[1]) + (1,) * (len(shape) - 2)
+        return {"x": (n(shape, 0, 0.2, 1.5), case["dt"]), "shift": (n(vec, 1, 0, 0.2), "f32"), "scale": (n(vec, 2, 0, 0.2), "f32")}
     if k == "linear_output":
         # A GEMM whose F32 accumulators are exact whatever the summation order: only column 0 of x
         # is non-zero, so accumulation[m, n] = x[m, 0] * w[n, 0], the exact product of two bf16 values.
@@ -99,6 +103,11 @@ CASES = [
     {"name": "dequant_fp8_all_codes", "kind": "dequant", "rows": 8, "inner": 256, "group": 256, "all_codes": True, "seed": 19},
     {"name": "dequant_fp8_groups", "kind": "dequant", "rows": 16, "inner": 96, "group": 32, "seed": 20},
     {"name": "binary_internal_broadcast", "kind": "binary", "a": (3, 1, 7), "b": (1, 5, 1), "dt": "bf16", "seed": 21},
+    {"name": "pixel_norm_ltx_bf16", "kind": "pixel_norm", "shape": (2, 128, 3, 8, 16), "dt": "bf16", "seed": 24, "subsample": 7},
+    {"name": "pixel_norm_wide_bf16", "kind": "pixel_norm", "shape": (1, 1024, 2, 4, 12), "dt": "bf16", "seed": 25, "subsample": 5},
+    {"name": "pixel_norm_f32_odd", "kind": "pixel_norm", "shape": (1, 20, 2, 3, 5), "dt": "f32", "seed": 26},
+    {"name": "pixel_norm_f32_tiles", "kind": "pixel_norm", "shape": (2, 96, 2, 6, 10), "dt": "f32", "seed": 27, "subsample": 3},
+    {"name": "pixel_norm_rows_f32", "kind": "pixel_norm", "shape": (6, 300), "dt": "f32", "seed": 28},
     {"name": "linear_output_bf16_state", "kind": "linear_output", "m": 72, "n": 1536, "k": 16, "state": "bf16", "seed": 22, "subsample": 3},
     {"name": "linear_output_f32_state", "kind": "linear_output", "m": 40, "n": 3072, "k": 32, "state": "f32", "seed": 23, "subsample": 5},
 ]
@@ -196,6 +205,15 @@ def run_reference(rc, case):
         shape = np.broadcast_shapes(case["a"], case["b"])
         for kind, name in enumerate(("add", "mul", "div", "max")):
             grab(name, rc.binary(kind, h["a"], h["b"]), shape)
+    elif k == "pixel_norm":
+        shape = case["shape"]
+        normed = rc.pixel_norm(h["x"], 1, 1e-8)
+        grab("pnorm", normed, shape)
+        mod = rc.modulate(pol, normed, h["shift"], h["scale"])
+        grab("pmod", mod, shape)
+        act = rc.activation(mod, 0)
+        grab("silu", act, shape)
+        grab("cast", rc.cast(act, ref.BF16), shape)
     elif k == "linear_output":
         M, N = case["m"], case["n"]
         p = ref.POLICY_BF16 if case["state"] == "bf16" else ref.POLICY_FP32
@@ -270,6 +288,11 @@ def run_oracle(orc, case):
     elif k == "binary":
         for kind, name in enumerate(("add", "mul", "div", "max")):
             grab(name, be._binary(kind, ins["a"], ins["b"]))
+    elif k == "pixel_norm":
+        normed = be.pixel_norm(ins["x"], 1, 1e-8)
+        mod = orc.modulate(be, pol, normed, ins["shift"], ins["scale"])
+        act = be.activation(mod, 0)
+        grab("pnorm", normed); grab("pmod", mod); grab("silu", act); grab("cast", be.cast(act, "bf16"))
     elif k == "linear_output":
         p = orc.Policy(residual=case["state"])
         acc = orc.T(linear_accumulation(case), "f32")
@@ -390,6 +413,16 @@ def run_library(be, ops, case, fused=True):
     elif k == "binary":
         for name in ("add", "mul", "div", "maximum"):
             grab("max" if name == "maximum" else name, getattr(be, name)(ins["a"], ins["b"]))
+    elif k == "pixel_norm":
+        grab("pnorm", be.pixel_norm(ins["x"], 1, 1e-8))
+        if fused:
+            grab("pmod", ops.fused_pixel_norm_modulate(be, ins["x"], ins["shift"], ins["scale"], 1e-8, silu=False))
+            grab("silu", ops.fused_pixel_norm_modulate(be, ins["x"], ins["shift"], ins["scale"], 1e-8))
+            grab("cast", ops.fused_pixel_norm_modulate(be, ins["x"], ins["shift"], ins["scale"], 1e-8, out_dtype=torch.bfloat16))
+        else:
+            mod = ops.modulate(be, pol, be.pixel_norm(ins["x"], 1, 1e-8), ins["shift"], ins["scale"])
+            act = be.activation(mod, ops.SILU)
+            grab("pmod", mod); grab("silu", act); grab("cast", be.cast(act, torch.bfloat16))
     elif k == "linear_output":
         p = ops.Policy(residual=tdt[case["state"]])
         acc = torch.from_numpy(linear_accumulation(case)).cuda()

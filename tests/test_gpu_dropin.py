@@ -60,7 +60,8 @@ def _grab(rd, case, handle, shape):
 
 
 @pytest.mark.parametrize("case", [c for c in cases.CASES if c["kind"] in
-                                  ("ln_modulate", "rms_rope", "gated_residual", "mochi", "group_norm", "sampler", "linear_output")],
+                                  ("ln_modulate", "rms_rope", "gated_residual", "mochi", "group_norm", "sampler", "linear_output",
+                                   "pixel_norm")],
                          ids=lambda c: c["name"])
 def test_fused_call_site_forms(orc, golden, dropin, case):
     """One kernel per chain through vrhino_b200::layer_norm_modulate / rms_norm_rope / ... ."""
@@ -110,6 +111,11 @@ def test_fused_call_site_forms(orc, golden, dropin, case):
                         assert np.array_equal(got_bits, want_bits)
                     else:   # the one-kernel modulate rounds once where the chain rounds per operator
                         compare(orc, case, "normed", (cases._sub(case, got_bits), "bf16"), (cases._sub(case, want_bits), "bf16"))
+        elif k == "pixel_norm":
+            got = rd.fused_pixel_norm_modulate_silu(pol, h["x"], h["shift"], h["scale"], 1e-8)
+            compare(orc, case, "silu", _grab(rd, case, got, case["shape"]), want["silu"], strict_tables=True)
+            got = rd.fused_pixel_norm_modulate_silu(pol, h["x"], h["shift"], h["scale"], 1e-8, ref.BF16)
+            compare(orc, case, "cast", _grab(rd, case, got, case["shape"]), want["cast"], strict_tables=True)
         elif k == "linear_output":
             # the device runtime's GEMM (exact accumulators in this case) + the merged epilogue kernels,
             # bit for bit against the reference's linear -> consumer chain

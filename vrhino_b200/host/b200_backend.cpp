@@ -306,7 +306,39 @@ Tensor B200Backend::group_norm_frames(const Tensor& raw, int groups, const Tenso
     });
 }
 
+Tensor B200Backend::pixel_norm(const Tensor& raw, int64_t dim, float eps) {
+    return guarded([&] {   // VRHINO_PROFILE("norm.pixel") carries the failure guard (cuda_backend.cu:3064, :5050)
+        if (dim < 0) dim += static_cast<int64_t>(raw.ndim());
+        require(dim >= 0 && dim < static_cast<int64_t>(raw.ndim()), "pixel norm dim invalid");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype);
+        const int64_t channels = x.dim(dim);
+        int64_t inner = 1;
+        for (int64_t d = dim + 1; d < static_cast<int64_t>(x.ndim()); ++d) inner *= x.dim(d);
+        Tensor out = rt_->allocate_device(x.shape(), dtype);
+        check(vrb_pixel_norm(x.data(), code(dtype), nullptr, nullptr, 0, 0, out.data(), code(dtype),
+                             x.numel() / (channels * inner), channels, inner, eps, kLegacyStream));
+        return out;
+    });
+}
+
 // ---- fused forms --------------------------------------------------------------------------------
+
+Tensor B200Backend::pixel_norm_modulate(const Tensor& raw, const Tensor& shift_raw, const Tensor& scale_raw, float eps,
+                                        bool silu, DType output) {
+    return guarded([&] {
+        require(raw.ndim() >= 2, "pixel norm dim invalid");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype);
+        const int64_t batch = x.dim(0), channels = x.dim(1), inner = x.numel() / (batch * channels);
+        Tensor scale = parameter(scale_raw), shift = copy_to_device(shift_raw, scale.dtype());
+        require(scale.numel() == batch * channels && shift.numel() == scale.numel(), "Incompatible broadcast shapes");
+        Tensor out = rt_->allocate_device(x.shape(), output);
+        check(vrb_pixel_norm(x.data(), code(dtype), scale.data(), shift.data(), code(scale.dtype()), silu ? 1 : 0, out.data(),
+                             code(output), batch, channels, inner, eps, kLegacyStream));
+        return out;
+    });
+}
 
 Tensor B200Backend::layer_norm_modulate(const Tensor& raw, const Tensor* weight_raw, const Tensor* bias_raw, float eps,
                                         const Tensor& shift_raw, const Tensor& scale_raw, DType output) {
@@ -579,6 +611,14 @@ Tensor linear_gated_residual(vrhino::Backend& backend, const vrhino::PrecisionPo
 Tensor linear_swiglu(vrhino::Backend& backend, const Tensor& x, const Tensor& weight, const Tensor* bias) {
     if (auto* b200 = dynamic_cast<B200Backend*>(&backend)) return b200->linear_swiglu(x, weight, bias);
     return swiglu(backend, backend.linear(x, weight, bias));
+}
+
+Tensor pixel_norm_modulate_silu(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy, const Tensor& x,
+                                const Tensor& shift, const Tensor& scale, float eps, DType output) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend)) return b200->pixel_norm_modulate(x, shift, scale, eps, true, output);
+    Tensor y = backend.activation(vrhino::modulate(backend, policy, backend.pixel_norm(x, 1, eps), shift, scale),
+                                  vrhino::Activation::Silu);
+    return y.dtype() == output ? y : backend.cast(y, output);
 }
 
 Tensor swiglu(vrhino::Backend& backend, const Tensor& projected) {

@@ -55,6 +55,7 @@ public:
     Tensor exp(const Tensor& x) override;
     Tensor sqrt(const Tensor& x) override;
     Tensor copy_to_device(const Tensor& input, DType dtype) override;
+    Tensor pixel_norm(const Tensor& x, int64_t dim, float eps) override;
 
     // ---- fused forms (one kernel each); see the free functions below for the call-site view --
     Tensor layer_norm_modulate(const Tensor& x, const Tensor* weight, const Tensor* bias, float eps,
@@ -78,6 +79,8 @@ public:
     Tensor linear_gated_residual(const Tensor& residual, const Tensor& x, const Tensor& weight, const Tensor* bias,
                                  const Tensor* gate, DType state);
     Tensor linear_swiglu(const Tensor& x, const Tensor& weight, const Tensor* bias);
+    // [silu](modulate(pixel_norm(x, 1, eps), shift, scale)) cast to `output`; shift / scale [B, C, 1, ...]
+    Tensor pixel_norm_modulate(const Tensor& x, const Tensor& shift, const Tensor& scale, float eps, bool silu, DType output);
     Tensor swiglu(const Tensor& projected);
     Tensor group_norm_silu(const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps);
     // x [B, C, T, H, W]: statistics per (batch entry, frame, group), no permutes
@@ -156,7 +159,6 @@ public:
     Tensor max_pool2d(const Tensor& x, const std::vector<int>& k, const std::vector<int>& s, const std::vector<int>& p = {0, 0}) override { return rt_->max_pool2d(x, k, s, p); }
     Tensor interpolate_nearest(const Tensor& x, const std::vector<double>& f) override { return rt_->interpolate_nearest(x, f); }
     Tensor interpolate_bilinear_2d(const Tensor& x, int64_t h, int64_t w, bool a) override { return rt_->interpolate_bilinear_2d(x, h, w, a); }
-    Tensor pixel_norm(const Tensor& x, int64_t d, float e) override { return rt_->pixel_norm(x, d, e); }
     Tensor l2_normalize(const Tensor& x, int64_t d, float e) override { return rt_->l2_normalize(x, d, e); }
     Tensor pixel_shuffle_nd(const Tensor& x, const std::vector<int64_t>& f) override { return rt_->pixel_shuffle_nd(x, f); }
     Tensor rng_normal(vrhino::RngState& s, const std::vector<int64_t>& shape, DType d) override { return rt_->rng_normal(s, shape, d); }
@@ -215,6 +217,11 @@ vrhino::Tensor linear_gated_residual(vrhino::Backend& backend, const vrhino::Pre
 // the SwiGLU of linear(x, weight, bias): split -> silu -> mul   (mochi.cpp:197-200)
 vrhino::Tensor linear_swiglu(vrhino::Backend& backend, const vrhino::Tensor& x, const vrhino::Tensor& weight,
                              const vrhino::Tensor* bias);
+// executor.silu(modulate(backend, policy, executor.pixel_norm(x), shift, scale))   (ltx.cpp:221-227), with the
+// cast to the consumer's operand dtype when output is BF16 (F32 = modulate's contract output)
+vrhino::Tensor pixel_norm_modulate_silu(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy,
+                                        const vrhino::Tensor& x, const vrhino::Tensor& shift, const vrhino::Tensor& scale,
+                                        float eps = 1e-8f, vrhino::DType output = vrhino::DType::F32);
 // mul(parts[0], silu(parts[1])), parts = split(projected, {H, H}, -1)   (mochi.cpp:195-202)
 vrhino::Tensor swiglu(vrhino::Backend& backend, const vrhino::Tensor& projected);
 // activation(group_norm(x, groups, weight, bias, eps), Silu)   (autoencoder_kl.cpp:31-41)

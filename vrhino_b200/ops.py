@@ -194,6 +194,23 @@ class B200Backend:
                  x.numel() // (width * inner), width, inner, ctypes.c_float(eps), 0, _stream())
         return out
 
+    def pixel_norm(self, raw, dim=1, eps=1e-8, out=None):
+        """CudaBackend::pixel_norm (native/src/backend/cuda/cuda_backend.cu:5048-5086)."""
+        rank = raw.dim()
+        if dim < 0:
+            dim += rank
+        if not 0 <= dim < rank:
+            raise VrbError("pixel norm dim invalid")
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        channels, inner = x.shape[dim], 1
+        for d in x.shape[dim + 1:]:
+            inner *= d
+        out = _result(out, x.shape, dtype, x.device)
+        call("vrb_pixel_norm", _ptr(x), _code(x), None, None, 0, 0, _ptr(out), _code(dtype),
+             x.numel() // (channels * inner), channels, inner, ctypes.c_float(eps), _stream())
+        return out
+
     def activation(self, raw, kind, out=None):
         dtype = self._dtype_of(raw)
         x = _dense(self.copy_to_device(raw, dtype))
@@ -536,6 +553,22 @@ def fused_swiglu(be, projected, out=None):
     rows = projected.numel() // (2 * hidden)
     out = _result(out, projected.shape[:-1] + (hidden,), projected.dtype, projected.device)
     call("vrb_swiglu", _ptr(projected), _ptr(out), _code(projected), rows, hidden, _stream())
+    return out
+
+
+def fused_pixel_norm_modulate(be, x, shift, scale, eps=1e-8, silu=True, out_dtype=F32, out=None):
+    """[silu](modulate(pixel_norm(x, 1, eps), shift, scale)) for x [B, C, ...] and shift / scale
+    [B, C, 1, ...] -- the head of LTX's decoder_residual (native/src/architectures/ltx.cpp:221-227) in one
+    pass.  out_dtype F32 is modulate's contract output; BF16 also folds the consumer's operand cast."""
+    x = _dense(x)
+    channels, inner = x.shape[1], 1
+    for d in x.shape[2:]:
+        inner *= d
+    if shift.dtype != scale.dtype or shift.numel() != x.shape[0] * channels or scale.numel() != shift.numel():
+        raise VrbError("Incompatible broadcast shapes")
+    out = _result(out, x.shape, out_dtype, x.device)
+    call("vrb_pixel_norm", _ptr(x), _code(x), _ptr(_dense(scale)), _ptr(_dense(shift)), _code(scale), int(bool(silu)),
+         _ptr(out), _code(out_dtype), x.shape[0], channels, inner, ctypes.c_float(eps), _stream())
     return out
 
 
