@@ -1,0 +1,69 @@
+"""pixel_norm over the channel axis and its merged form with modulate + SiLU: every path of the
+launcher (shared-memory tiles of 8 / 4 / 2 / 1 chunks, ragged last tile, the strided fallback for odd
+extents, the row kernel for inner == 1) against the oracle -- bit for bit up to the modulation, and
+within F32 tolerance after expf."""
+import numpy as np
+import pytest
+
+from conftest import assert_bits_equal, assert_close, to_torch
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [
+    (2, 128, 3, 8, 16),     # tiles of 8 chunks
+    (1, 64, 1, 5, 8),       # inner 40: one ragged tile (5 chunks of bf16, 10 of f32)
+    (1, 1024, 2, 4, 12),    # 1024 channels: narrower tiles
+    (1, 2048, 1, 2, 16),    # 2 chunks per row
+    (1, 4000, 1, 1, 16),    # one CTA per SM
+    (1, 20, 2, 3, 5),       # odd inner: strided fallback
+    (3, 7, 1, 1, 24),       # channels not a multiple of the 8 lanes
+    (6, 300),               # inner == 1: row kernel
+    (2, 9, 1),              # inner == 1, fewer channels than threads
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_pixel_norm_bit_exact(orc, gpu, shape, dt):
+    be, ops = gpu
+    from vrhino_b200 import synth
+    x = orc.tensor(synth.normal(shape, 0.2, 1.5, seed=len(shape) + shape[1]), dt)
+    want = orc.OracleBackend().pixel_norm(x, 1, 1e-8)
+    assert_bits_equal(be.pixel_norm(to_torch(x), 1, 1e-8), want, "pixel_norm")
+
+
+@pytest.mark.parametrize("shape", [s for s in SHAPES if len(s) == 5])
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_pixel_norm_modulate_silu(orc, gpu, shape, dt):
+    import torch
+    be, ops = gpu
+    from vrhino_b200 import synth
+    obe, pol = orc.OracleBackend(), orc.Policy()
+    vec = (shape[0], shape[1], 1, 1, 1)
+    x = orc.tensor(synth.normal(shape, 0.2, 1.5, seed=shape[1]), dt)
+    shift, scale = orc.tensor(synth.normal(vec, 0, 0.2, seed=1)), orc.tensor(synth.normal(vec, 0, 0.2, seed=2))
+    mod = orc.modulate(obe, pol, obe.pixel_norm(x, 1, 1e-8), shift, scale)
+    got = ops.fused_pixel_norm_modulate(be, to_torch(x), to_torch(shift), to_torch(scale), 1e-8, silu=False)
+    assert_bits_equal(got, mod, "pixel_norm + modulate")
+    act = obe.activation(mod, orc.SILU)
+    got = ops.fused_pixel_norm_modulate(be, to_torch(x), to_torch(shift), to_torch(scale), 1e-8)
+    assert_close(orc, got, act, rel=1e-5, atol=2e-6, what="pixel_norm + modulate + silu")
+    # the merged form equals this library's own operator chain bit for bit, in both output dtypes
+    chain = be.activation(ops.modulate(be, ops.Policy(), be.pixel_norm(to_torch(x), 1, 1e-8), to_torch(shift), to_torch(scale)), ops.SILU)
+    assert torch.equal(got.view(torch.int32), chain.view(torch.int32))
+    got16 = ops.fused_pixel_norm_modulate(be, to_torch(x), to_torch(shift), to_torch(scale), 1e-8, out_dtype=torch.bfloat16)
+    assert torch.equal(got16.view(torch.int16), be.cast(chain, torch.bfloat16).view(torch.int16))
+
+
+def test_pixel_norm_other_axes_and_errors(orc, gpu):
+    import torch
+    be, ops = gpu
+    from vrhino_b200 import synth
+    x = orc.tensor(synth.normal((4, 6, 40), seed=3), "f32")
+    obe = orc.OracleBackend()
+    assert_bits_equal(be.pixel_norm(to_torch(x), -1, 1e-8), obe.pixel_norm(x, -1, 1e-8), "last axis")
+    assert_bits_equal(be.pixel_norm(to_torch(x), 0, 1e-6), obe.pixel_norm(x, 0, 1e-6), "first axis")
+    with pytest.raises(ops.VrbError):
+        be.pixel_norm(to_torch(x), 3, 1e-8)
+    with pytest.raises(ops.VrbError):
+        ops.fused_pixel_norm_modulate(be, to_torch(x), torch.zeros(4, 5, 1, device="cuda"), torch.zeros(4, 5, 1, device="cuda"))

@@ -17,7 +17,8 @@
 // Tile kernel: a CTA stages [channels x P positions] of the input in shared memory with 16-byte
 // asynchronous copies (the whole tile is in flight at once and costs no registers), reduces it from
 // there, and writes the finished elements: the tensor is read from HBM once, where statistics pass +
-// normalise pass of the reference read it twice.  P is chosen so that three CTAs fit on an SM.
+// normalise pass of the reference read it twice.  Two tile buffers: the next tile's copies are in
+// flight while the current tile is reduced and written.  P is chosen so that three CTAs fit on an SM.
 #include "vrb_common.cuh"
 
 #include <mutex>
@@ -59,55 +60,93 @@ __device__ __forceinline__ void async_copy16(void* shared_dst, const void* globa
     const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(shared_dst));
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(global_src) : "memory");
 }
-__device__ __forceinline__ void async_copy_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void async_copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// waits until at most `pending` of this thread's committed groups are still in flight
+template <int pending>
+__device__ __forceinline__ void async_copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(pending) : "memory"); }
 
-// Tile kernel: inner % EPC == 0, 16-byte aligned tensors; `cols` (a power of two) 16-byte chunks per channel.
-template <bool X_BF16>
+// Epilogue variants of the tile kernel, fixed at compile time.
+enum Mode { kNormOnly = 0, kModulate = 1, kModulateSilu = 2 };
+
+// One normalised element to the stored value with everything known at compile time.
+template <bool X_BF16, int MODE>
+__device__ __forceinline__ float finish_tile(float x, float denominator, float one_plus_scale, float shift) {
+    float v = __fdiv_rn(x, denominator);
+    if constexpr (X_BF16 && MODE != kNormOnly) v = round_to_bf16(v);   // kNormOnly: the bf16 store rounds
+    if constexpr (MODE != kNormOnly) v = __fadd_rn(__fmul_rn(v, one_plus_scale), shift);
+    if constexpr (MODE == kModulateSilu) v = activation_value(VRB_SILU, v);
+    return v;
+}
+
+// Tile kernel: inner % EPC == 0, 16-byte aligned tensors; `cols` (a power of two) 16-byte chunks per
+// channel.  kNormOnly stores x's dtype; the modulated forms store F32 or (OUT_BF16) bf16.
+template <bool X_BF16, int MODE, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNormParams p, int cols, int cols_log2) {
     constexpr int EPC = X_BF16 ? 8 : 4;   // elements per 16-byte chunk
-    extern __shared__ __align__(16) uint4 tile[];   // [channels][cols]
+    extern __shared__ __align__(16) uint4 tiles_buffer[];   // two tiles of [channels][cols], then the reduction scratch
     const int channels = static_cast<int>(p.channels);
     const int positions = cols * EPC;
-    float* const partial = reinterpret_cast<float*>(tile + static_cast<size_t>(channels) * cols);   // [kLanes][positions]
-    float* const denominator = partial + kLanes * positions;                                        // [positions]
+    const int tile_chunks = channels * cols;
+    float* const partial = reinterpret_cast<float*>(tiles_buffer + 2 * static_cast<size_t>(tile_chunks));   // [kLanes][positions]
+    float* const denominator = partial + kLanes * positions;                                              // [positions]
     const int64_t inner_chunks = p.inner / EPC;
     const int64_t tiles_per_outer = (inner_chunks + cols - 1) / cols;
     const int64_t tiles = p.outer * tiles_per_outer;
-    const int tile_chunks = channels * cols;
-    const bool modulated = p.scale != nullptr;
     const float channel_count = static_cast<float>(p.channels);
     const uint4* const x = static_cast<const uint4*>(p.x);
 
-    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+    // asynchronous copy of tile t into buffer b (one committed group per tile and thread)
+    auto request = [&](int64_t t, int b) {
+        if (t < tiles) {
+            const int64_t o = t / tiles_per_outer;
+            const int64_t chunk0 = (t - o * tiles_per_outer) * cols;
+            const int valid = static_cast<int>(inner_chunks - chunk0 < cols ? inner_chunks - chunk0 : cols);
+            const uint4* const src = x + o * p.channels * inner_chunks + chunk0;
+            uint4* const dst = tiles_buffer + static_cast<size_t>(b) * tile_chunks;
+            for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads) {
+                const int c = idx >> cols_log2, k = idx & (cols - 1);
+                if (k < valid) async_copy16(dst + idx, src + static_cast<int64_t>(c) * inner_chunks + k);
+                else dst[idx] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        async_copy_commit();
+    };
+
+    int buffer = 0;
+    request(blockIdx.x, 0);
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, buffer ^= 1) {
         const int64_t o = t / tiles_per_outer;
         const int64_t chunk0 = (t - o * tiles_per_outer) * cols;
         const int valid = static_cast<int>(inner_chunks - chunk0 < cols ? inner_chunks - chunk0 : cols);
-        const uint4* const src = x + o * p.channels * inner_chunks + chunk0;
-        for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads) {
-            const int c = idx >> cols_log2, k = idx & (cols - 1);
-            if (k < valid) async_copy16(tile + idx, src + static_cast<int64_t>(c) * inner_chunks + k);
-            else tile[idx] = make_uint4(0, 0, 0, 0);
-        }
-        async_copy_wait();
+        const uint4* const tile = tiles_buffer + static_cast<size_t>(buffer) * tile_chunks;
+        request(t + gridDim.x, buffer ^ 1);   // the next tile arrives while this one is reduced and written
+        async_copy_wait<1>();
         __syncthreads();
-        // (position, lane) partial sums in the reference's order
-        for (int pair = threadIdx.x; pair < positions * kLanes; pair += kThreads) {
-            const int lane = pair / positions, pos = pair - lane * positions;
-            float q = 0.0f;
-            if constexpr (X_BF16) {
-                const uint16_t* e = reinterpret_cast<const uint16_t*>(tile) + pos;
-                for (int c = lane; c < channels; c += kLanes) {
-                    const float v = bf16_bits_to_float(e[c * positions]);
-                    q = __fmaf_rn(v, v, q);
-                }
-            } else {
-                const float* e = reinterpret_cast<const float*>(tile) + pos;
-                for (int c = lane; c < channels; c += kLanes) {
-                    const float v = e[c * positions];
-                    q = __fmaf_rn(v, v, q);
+        // (lane, position) partial sums in the reference's order; a thread takes the positions of one
+        // 32-bit shared-memory word (two bf16 positions, one F32 position)
+        constexpr int PPW = X_BF16 ? 2 : 1;
+        const int words = positions / PPW;
+        const uint32_t* const tile_words = reinterpret_cast<const uint32_t*>(tile);
+        for (int item = threadIdx.x; item < words * kLanes; item += kThreads) {
+            const int lane = item / words, word = item - lane * words;
+            float q0 = 0.0f, q1 = 0.0f;
+            const uint32_t* e = tile_words + lane * words + word;
+            const int step = kLanes * words;
+            int c = lane;
+#pragma unroll 4
+            for (; c < channels; c += kLanes, e += step) {
+                const uint32_t w = *e;
+                if constexpr (X_BF16) {
+                    const float lo = __uint_as_float(w << 16), hi = __uint_as_float(w & 0xffff0000u);
+                    q0 = __fmaf_rn(lo, lo, q0);
+                    q1 = __fmaf_rn(hi, hi, q1);
+                } else {
+                    const float v = __uint_as_float(w);
+                    q0 = __fmaf_rn(v, v, q0);
                 }
             }
-            partial[pair] = q;
+            partial[lane * positions + word * PPW] = q0;
+            if constexpr (X_BF16) partial[lane * positions + word * PPW + 1] = q1;
         }
         __syncthreads();
         if (threadIdx.x < positions) {
@@ -117,42 +156,54 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
             denominator[threadIdx.x] = __fsqrt_rn(__fadd_rn(__fdiv_rn(tree8(s), channel_count), p.eps));
         }
         __syncthreads();
+        const int64_t out_chunk0 = o * p.channels * inner_chunks + chunk0;
         for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads) {
             const int c = idx >> cols_log2, k = idx & (cols - 1);
             if (k >= valid) continue;
             float ops = 1.0f, sh = 0.0f;
-            if (modulated) {
+            if constexpr (MODE != kNormOnly) {
                 const int64_t at = o * p.channels + c;
                 ops = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, at));
                 sh = load1(p.shift, p.mod_dt, at);
             }
             const uint4 raw = tile[idx];
-            const int64_t element = ((o * p.channels + c) * inner_chunks + chunk0 + k) * EPC;
-            const float* d = denominator + k * EPC;
+            const int64_t chunk = out_chunk0 + static_cast<int64_t>(c) * inner_chunks + k;   // in units of EPC elements
+            const float4* d4 = reinterpret_cast<const float4*>(denominator + k * EPC);
             if constexpr (X_BF16) {
+                const float4 da = d4[0], db = d4[1];
+                const float d[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
                 const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
                 float v[8];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    v[2 * j] = finish(p, __uint_as_float(w[j] << 16), d[2 * j], modulated, ops, sh);
-                    v[2 * j + 1] = finish(p, __uint_as_float(w[j] & 0xffff0000u), d[2 * j + 1], modulated, ops, sh);
+                    v[2 * j] = finish_tile<true, MODE>(__uint_as_float(w[j] << 16), d[2 * j], ops, sh);
+                    v[2 * j + 1] = finish_tile<true, MODE>(__uint_as_float(w[j] & 0xffff0000u), d[2 * j + 1], ops, sh);
                 }
-                store8(p.out, p.out_dt, element, v);
+                if constexpr (MODE == kNormOnly || OUT_BF16) {
+                    __stcs(static_cast<uint4*>(p.out) + chunk, make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                                                          pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])));
+                } else {
+                    float4* dst = static_cast<float4*>(p.out) + 2 * chunk;
+                    __stcs(dst, make_float4(v[0], v[1], v[2], v[3]));
+                    __stcs(dst + 1, make_float4(v[4], v[5], v[6], v[7]));
+                }
             } else {
+                const float4 da = d4[0];
+                const float d[4] = {da.x, da.y, da.z, da.w};
                 const float in[4] = {__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w)};
                 float v[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = finish(p, in[j], d[j], modulated, ops, sh);
-                if (p.out_dt == VRB_BF16) {
-                    __stcs(reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.out) + element),
-                           make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3])));
+                for (int j = 0; j < 4; ++j) v[j] = finish_tile<false, MODE>(in[j], d[j], ops, sh);
+                if constexpr (MODE != kNormOnly && OUT_BF16) {
+                    __stcs(static_cast<uint2*>(p.out) + chunk, make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3])));
                 } else {
-                    __stcs(reinterpret_cast<float4*>(static_cast<float*>(p.out) + element), make_float4(v[0], v[1], v[2], v[3]));
+                    __stcs(static_cast<float4*>(p.out) + chunk, make_float4(v[0], v[1], v[2], v[3]));
                 }
             }
         }
-        __syncthreads();   // the tile is overwritten by the next iteration's copies
+        __syncthreads();   // this buffer is the target of the next iteration's copies
     }
+    async_copy_wait<0>();
 }
 
 // Any inner extent / alignment / channel count, inner > 1: one thread per position, two passes over
@@ -219,26 +270,34 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_rows_kernel(const PixelNo
     }
 }
 
-// Resident CTAs per SM of a tile kernel for a dynamic shared-memory size (opted into above 48 KB);
-// remembered per (device, size), guarded for concurrent callers.
+// Resident CTAs per SM of a tile kernel for a dynamic shared-memory size; remembered per (kernel,
+// device, size), guarded for concurrent callers.  The kernel is opted into the largest tile the
+// launcher ever asks for the first time it is seen on a device (the attribute is a limit that a
+// later, smaller request must not lower).
+constexpr size_t kMaxTileBytes = 208 * 1024;
 template <typename K>
 int tile_ctas_per_sm(K kernel, size_t smem) {
-    struct Entry { int device; size_t smem; int per_sm; };
+    struct Entry { const void* kernel; int device; size_t smem; int per_sm; };
     static std::mutex mutex;
     static std::vector<Entry> known;
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    const void* const key = reinterpret_cast<const void*>(kernel);
     std::lock_guard<std::mutex> lock(mutex);
-    for (const Entry& e : known)
-        if (e.device == device && e.smem == smem) return e.per_sm;
+    bool opted = false;
+    for (const Entry& e : known) {
+        if (e.kernel != key || e.device != device) continue;
+        if (e.smem == smem) return e.per_sm;
+        opted = true;
+    }
     int n = 0;
-    if ((smem > 40 * 1024 &&
-         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) ||
+    if ((!opted && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kMaxTileBytes)) != cudaSuccess) ||
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, smem) != cudaSuccess) {
         cudaGetLastError();
         n = 0;
     }
-    if (known.size() < 256) known.push_back({device, smem, n});
+    if (known.size() < 1024) known.push_back({key, device, smem, n});
     return n;
 }
 
@@ -272,15 +331,33 @@ extern "C" int vrb_pixel_norm(const void* x, int dtype, const void* scale, const
         for (int budget_ctas : {3, 1}) {
             for (int cols = 8, log2 = 3; cols >= 1; cols >>= 1, --log2) {
                 if (cols > 1 && cols / 2 >= inner_chunks) continue;
-                const size_t smem = static_cast<size_t>(channels) * cols * 16 + static_cast<size_t>(kLanes + 1) * cols * epc * 4;
-                if (smem > (budget_ctas == 3 ? 72 * 1024 : 200 * 1024)) continue;
-                const int per_sm = dtype == VRB_BF16 ? tile_ctas_per_sm(pixel_norm_tile_kernel<true>, smem)
-                                                    : tile_ctas_per_sm(pixel_norm_tile_kernel<false>, smem);
-                if (per_sm < 1) continue;
+                const size_t smem = 2 * static_cast<size_t>(channels) * cols * 16 + static_cast<size_t>(kLanes + 1) * cols * epc * 4;
+                if (smem > (budget_ctas == 3 ? 72 * 1024 : 200 * 1024) || smem > kMaxTileBytes) continue;
+                const int mode = !scale ? kNormOnly : fuse_silu ? kModulateSilu : kModulate;
+                const int variant = (dtype == VRB_BF16 ? 8 : 0) | (mode << 1) | (out_dtype == VRB_BF16 ? 1 : 0);
                 const int64_t tiles = outer * ((inner_chunks + cols - 1) / cols);
-                const int grid = grid_for(tiles, per_sm);
-                if (dtype == VRB_BF16) pixel_norm_tile_kernel<true><<<grid, kThreads, smem, s>>>(p, cols, log2);
-                else pixel_norm_tile_kernel<false><<<grid, kThreads, smem, s>>>(p, cols, log2);
+                bool launched = true;
+#define VRB_PN(XB, M, OB)                                                                               \
+    {                                                                                                   \
+        const int per_sm = tile_ctas_per_sm(pixel_norm_tile_kernel<XB, M, OB>, smem);                   \
+        if (per_sm < 1) { launched = false; break; }                                                    \
+        pixel_norm_tile_kernel<XB, M, OB><<<grid_for(tiles, per_sm), kThreads, smem, s>>>(p, cols, log2); \
+    }                                                                                                   \
+    break
+                switch (variant) {
+                    case 0: case 1: VRB_PN(false, kNormOnly, false);
+                    case 2: VRB_PN(false, kModulate, false);
+                    case 3: VRB_PN(false, kModulate, true);
+                    case 4: VRB_PN(false, kModulateSilu, false);
+                    case 5: VRB_PN(false, kModulateSilu, true);
+                    case 8: case 9: VRB_PN(true, kNormOnly, true);
+                    case 10: VRB_PN(true, kModulate, false);
+                    case 11: VRB_PN(true, kModulate, true);
+                    case 12: VRB_PN(true, kModulateSilu, false);
+                    default: VRB_PN(true, kModulateSilu, true);
+                }
+#undef VRB_PN
+                if (!launched) continue;
                 return after_launch("pixel_norm");
             }
         }

@@ -294,6 +294,32 @@ class LinearEpilogues:
                 Launch("epilogue glu", lin_glu, glu * 6), Launch("swiglu", swiglu2, glu * 3)]
 
 
+class LtxVaeNorm:
+    """The head of LTX's decoder_residual (native/src/architectures/ltx.cpp:221-227) on a VAE decoder
+    feature map [1, C, T, H, W] bf16 ~N(0.2, 1.5): pixel_norm over the channels, then modulate with
+    per-channel (shift, scale) ~N(0, 0.2) and SiLU.  Algorithmic bytes: input read once, result
+    written once (F32 as modulate's contract gives it, or bf16 with the consumer's operand cast)."""
+
+    def __init__(self, be, shape=(1, 128, 16, 256, 384), dtype=BF16, seed=0):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        self.be = be
+        self.x = _randn(shape, dtype, g, 0.2, 1.5)
+        vec = (shape[0], shape[1], 1, 1, 1)
+        self.shift, self.scale = _randn(vec, F32, g, 0.0, 0.2), _randn(vec, F32, g, 0.0, 0.2)
+        self.out = {}
+
+    def launches(self) -> List[Launch]:
+        be, o, x = self.be, self.out, self.x
+        n, eb = x.numel(), x.element_size()
+
+        def norm(): o["norm"] = be.pixel_norm(x, 1, 1e-8, out=o.get("norm"))
+        def f32(): o["f32"] = ops.fused_pixel_norm_modulate(be, x, self.shift, self.scale, 1e-8, out=o.get("f32"))
+        def bf16(): o["bf16"] = ops.fused_pixel_norm_modulate(be, x, self.shift, self.scale, 1e-8, out_dtype=BF16, out=o.get("bf16"))
+
+        return [Launch("pixel_norm", norm, n * 2 * eb), Launch("pixel_norm modulate silu f32", f32, n * (eb + 4)),
+                Launch("pixel_norm modulate silu bf16", bf16, n * (eb + 2))]
+
+
 def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, batch=1):
     """The launch list of headline configuration 2..5 (optionally at a reduced token / frame count),
     or of the additional measurement configurations 6..9."""
@@ -312,9 +338,11 @@ def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, b
         return VaeGroupNorm(be, shape=(1, 256, frames or 28, 240, 424), per_frame=True)
     if config in (8, 9):
         return LinearEpilogues(be, tokens=tokens or 32760, batch=batch, merged=config == 8)
-    raise ValueError("config must be 2..9 (6 = config 5 as a pre-permuted per-frame tensor, 7 = per-frame statistics "
+    if config == 10:
+        return LtxVaeNorm(be, shape=(1, 128, frames or 16, 256, 384), dtype=hidden_dtype)
+    raise ValueError("config must be 2..10 (6 = config 5 as a pre-permuted per-frame tensor, 7 = per-frame statistics "
                      "on the unpermuted [N,C,T,H,W] tensor, 8 = linear epilogues merged with their consumers, "
-                     "9 = the same as separate launches)")
+                     "9 = the same as separate launches, 10 = LTX VAE pixel_norm -> modulate -> SiLU)")
 
 
 def _main():
