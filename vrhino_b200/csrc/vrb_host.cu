@@ -21,7 +21,7 @@ namespace vrb {
 namespace {
 
 constexpr int kSlots = 3;
-constexpr size_t kBlockBytes = size_t{8} << 20;   // per-row-stream bytes per block, about
+constexpr size_t kBlockBytes = size_t{16} << 20;   // per-row-stream bytes per full block, about
 
 struct Arena {
     void* base = nullptr;
@@ -96,11 +96,28 @@ int run_pipeline(std::vector<Operand>& ops, int64_t rows, Launch launch) {
     VRB_CUDA(cudaEventRecord(g_pipe.shared_ready, g_pipe.streams[0]), "event record");
     for (int s = 1; s < kSlots; ++s) VRB_CUDA(cudaStreamWaitEvent(g_pipe.streams[s], g_pipe.shared_ready, 0), "event wait");
 
-    const int64_t blocks = (rows + block_rows - 1) / block_rows;
-    for (int64_t b = 0; b < blocks; ++b) {
+    // Block sizes ramp up at the start and down at the end (1/8, 1/4, 1/2 of a full block): the call
+    // returns only when everything is back on the host, so the first upload and the last download
+    // overlap nothing, and they should be short.
+    std::vector<int64_t> sizes;
+    {
+        int64_t head[3], tail[3], left = rows;
+        int heads = 0, tails = 0;
+        for (int shift = 3; shift >= 1 && left > 2 * block_rows; --shift) {
+            const int64_t n = block_rows >> shift;
+            if (n < 1) continue;
+            head[heads++] = n; tail[tails++] = n;
+            left -= 2 * n;
+        }
+        for (int i = 0; i < heads; ++i) sizes.push_back(head[i]);
+        for (; left > 0; left -= block_rows) sizes.push_back(left < block_rows ? left : block_rows);
+        for (int i = tails - 1; i >= 0; --i) sizes.push_back(tail[i]);
+    }
+    int64_t r0 = 0;
+    for (size_t b = 0; b < sizes.size(); r0 += sizes[b], ++b) {
         const int slot = static_cast<int>(b % kSlots);
         cudaStream_t st = g_pipe.streams[slot];
-        const int64_t r0 = b * block_rows, n = (r0 + block_rows <= rows) ? block_rows : rows - r0;
+        const int64_t n = sizes[b];
         size_t so = 0;
         for (size_t k = 0; k < ops.size(); ++k) {
             if (!ops[k].row_bytes) continue;
