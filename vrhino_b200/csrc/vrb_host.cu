@@ -20,8 +20,8 @@
 namespace vrb {
 namespace {
 
-constexpr int kSlots = 3;
-constexpr size_t kBlockBytes = size_t{16} << 20;   // per-row-stream bytes per full block, about
+constexpr int kSlots = 3;                          // 2, 4 and 6 slots measured no faster
+constexpr size_t kBlockBytes = size_t{16} << 20;   // per-row-stream bytes per full block, about (8 and 32 MiB: the same)
 
 struct Arena {
     void* base = nullptr;
@@ -30,7 +30,7 @@ struct Arena {
 
 struct HostPipe {
     std::mutex mutex;
-    cudaStream_t streams[kSlots] = {nullptr, nullptr, nullptr};
+    cudaStream_t streams[kSlots] = {};
     cudaEvent_t shared_ready = nullptr;
     Arena slots[kSlots];
     Arena shared;
