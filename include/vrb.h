@@ -102,6 +102,22 @@ int vrb_pixel_norm(const void* x, int dtype, const void* scale, const void* shif
                    int fuse_silu, void* out, int out_dtype, int64_t outer, int64_t channels,
                    int64_t inner, float eps, vrb_stream stream);
 
+/* CudaBackend::pixel_shuffle_nd (:5112-5118, pixel_shuffle_kernel :2170-2186):
+ * x [batch, channels*ft*fh*fw, frames, height, width] -> out [batch, channels, frames*ft, height*fh, width*fw],
+ * out[b, c, t*ft+pt, h*fh+ph, w*fw+pw] = x[b, ((c*ft+pt)*fh+ph)*fw+pw, t, h, w]. */
+int vrb_pixel_shuffle(const void* x, void* out, int dtype, int64_t batch, int64_t channels,
+                      int64_t frames, int64_t height, int64_t width, int factor_t, int factor_h,
+                      int factor_w, vrb_stream stream);
+
+/* LTX depth_to_space (native/src/architectures/ltx.cpp:250-259) after its convolution, in one pass:
+ * projected [batch, 4*C, T, H, W] (the convolution output), input [batch, C, T, H, W] ->
+ *   out = slice(pixel_shuffle(projected, {2,2,2}), 2, 1, 2T)
+ *       + slice(concat(4 x pixel_shuffle(input, {2,2,2}), 1), 2, 1, 2T)        [batch, C/2, 2T-1, 2H, 2W]
+ * all tensors in `dtype`; C a multiple of 8. */
+int vrb_depth_to_space_residual(const void* projected, const void* input, void* out, int dtype,
+                                int64_t batch, int64_t input_channels, int64_t frames,
+                                int64_t height, int64_t width, vrb_stream stream);
+
 /* CudaBackend::rope_nd (:4198-4213).  cos/sin have f_shape and broadcast against x_shape. */
 int vrb_rope(const void* x, int x_dtype, const int64_t* x_shape, int x_rank,
              const void* cosine, const void* sine, int f_dtype, const int64_t* f_shape, int f_rank,

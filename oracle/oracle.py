@@ -288,6 +288,17 @@ class OracleBackend:
                              ctypes.c_int64(inner), ctypes.c_float(eps))
         return T(out, dtype)
 
+    def pixel_shuffle_nd(self, raw: T, factors) -> T:
+        """CudaBackend::pixel_shuffle_nd (native/src/backend/cuda/cuda_backend.cu:5112-5118) with the index map of
+        pixel_shuffle_kernel (:2170-2186): packed channel ((c*ft+pt)*fh+ph)*fw+pw."""
+        dtype = self._dtype_of(raw)
+        x = self.copy_to_device(raw, dtype)
+        ft, fh, fw = (int(f) for f in factors)
+        b, cp, t, h, w = x.shape
+        c = cp // (ft * fh * fw)
+        v = x.data.reshape(b, c, ft, fh, fw, t, h, w).transpose(0, 1, 5, 2, 6, 3, 7, 4)   # b c t pt h ph w pw
+        return T(np.ascontiguousarray(v).reshape(b, c, t * ft, h * fh, w * fw), dtype)
+
     def activation(self, raw: T, kind: int) -> T:
         dtype = self._dtype_of(raw)
         x = self.copy_to_device(raw, dtype)
@@ -476,6 +487,17 @@ def pixel_norm_modulate_silu(be, policy, x, shift, scale, eps=1e-8):
     """LTX decoder_residual (native/src/architectures/ltx.cpp:221-227): silu(modulate(pixel_norm(x), shift,
     scale)) with shift / scale [B, C, 1, 1, 1]; the result is F32 (modulate's contract output)."""
     return be.activation(modulate(be, policy, be.pixel_norm(x, 1, eps), shift, scale), SILU)
+
+
+def depth_to_space_residual(be, projected, x):
+    """LTX depth_to_space (native/src/architectures/ltx.cpp:250-259) after its convolution `projected`:
+    pixel_shuffle of the input repeated four times along the channels, both shuffles without their
+    first frame, one add."""
+    residual = be.pixel_shuffle_nd(x, (2, 2, 2))
+    residual = T(np.concatenate([residual.data] * 4, axis=1), residual.dtype)
+    residual = be.slice(residual, 2, 1, residual.shape[2])
+    y = be.pixel_shuffle_nd(projected, (2, 2, 2))
+    return be.add(be.slice(y, 2, 1, y.shape[2]), residual)
 
 
 def rms_channel_silu(be, x, gamma, eps=1e-12):

@@ -148,7 +148,7 @@ class RefCuda:
                      "refc_layer_norm", "refc_rms_norm", "refc_activation", "refc_rope", "refc_group_norm", "refc_clamp",
                      "refc_exp", "refc_sqrt", "refc_dequantize", "refc_modulate", "refc_attention_norm", "refc_operation_rope",
                      "refc_residual_add", "refc_gated_residual", "refc_cfg_combine", "refc_euler_update", "refc_flow_to_x0",
-                     "refc_frame_group_norm", "refc_linear", "refc_pixel_norm"):
+                     "refc_frame_group_norm", "refc_linear", "refc_pixel_norm", "refc_pixel_shuffle", "refc_repeat"):
             getattr(lib, name).restype = _c.c_int64
         lib.refc_profile_total_ms.restype = _c.c_double
         self.lib = lib
@@ -200,6 +200,9 @@ class RefCuda:
         return self._h(self.lib.refc_rms_norm(self._i(x), self._i(w), _c.c_float(eps), _c.c_int64(axis), int(out_dtype)))
     def linear(self, x, w, bias): return self._h(self.lib.refc_linear(self._i(x), self._i(w), self._i(bias)))
     def pixel_norm(self, x, dim, eps): return self._h(self.lib.refc_pixel_norm(self._i(x), _c.c_int64(dim), _c.c_float(eps)))
+    def pixel_shuffle(self, x, factors):
+        return self._h(self.lib.refc_pixel_shuffle(self._i(x), *(_c.c_int64(int(f)) for f in factors)))
+    def repeat(self, x, copies, dim): return self._h(self.lib.refc_repeat(self._i(x), int(copies), _c.c_int64(dim)))
     def activation(self, x, kind): return self._h(self.lib.refc_activation(self._i(x), int(kind)))
     def rope(self, x, c, s): return self._h(self.lib.refc_rope(self._i(x), self._i(c), self._i(s)))
     def group_norm(self, x, groups, w, b, eps): return self._h(self.lib.refc_group_norm(self._i(x), int(groups), self._i(w), self._i(b), _c.c_float(eps)))
@@ -273,7 +276,7 @@ class RefDropin(RefCuda):
         for name in ("refd_layer_norm_modulate", "refd_rms_norm_rope", "refd_gated_residual", "refd_swiglu",
                      "refd_group_norm_silu", "refd_cfg_euler", "refd_gated_residual_layer_norm",
                      "refd_linear_activation", "refd_linear_gated_residual", "refd_linear_swiglu",
-                     "refd_pixel_norm_modulate_silu"):
+                     "refd_pixel_norm_modulate_silu", "refd_depth_to_space_residual"):
             getattr(self.lib, name).restype = _c.c_int64
 
     def name(self): return self.lib.refc_backend_name().decode()
@@ -301,6 +304,8 @@ class RefDropin(RefCuda):
     def fused_pixel_norm_modulate_silu(self, policy, x, shift, scale, eps=1e-8, out_dtype=F32):
         return self._h(self.lib.refd_pixel_norm_modulate_silu(int(policy), self._i(x), self._i(shift), self._i(scale),
                                                               _c.c_float(eps), int(out_dtype)))
+    def fused_depth_to_space_residual(self, projected, x):
+        return self._h(self.lib.refd_depth_to_space_residual(self._i(projected), self._i(x)))
     def fused_swiglu(self, x): return self._h(self.lib.refd_swiglu(self._i(x)))
     def fused_group_norm_silu(self, x, groups, w, b, eps):
         return self._h(self.lib.refd_group_norm_silu(self._i(x), int(groups), self._i(w), self._i(b), _c.c_float(eps)))

@@ -159,6 +159,13 @@ int64_t refc_linear(int64_t x, int64_t w, int64_t bias) {
 int64_t refc_pixel_norm(int64_t x, int64_t dim, float eps) {
     return guarded([&] { return keep(g_backend->pixel_norm(at(x), dim, eps)); });
 }
+int64_t refc_pixel_shuffle(int64_t x, int64_t ft, int64_t fh, int64_t fw) {
+    return guarded([&] { return keep(g_backend->pixel_shuffle_nd(at(x), {ft, fh, fw})); });
+}
+// concat of `copies` references to the same tensor along `dim`
+int64_t refc_repeat(int64_t x, int copies, int64_t dim) {
+    return guarded([&] { return keep(g_backend->concat(std::vector<Tensor>(static_cast<size_t>(copies), at(x)), dim)); });
+}
 int64_t refc_activation(int64_t x, int kind) {
     return guarded([&] { return keep(g_backend->activation(at(x), static_cast<Activation>(kind))); });
 }
@@ -268,6 +275,9 @@ int64_t refd_pixel_norm_modulate_silu(int policy, int64_t x, int64_t shift, int6
         return keep(vrhino_b200::pixel_norm_modulate_silu(*g_backend, policy_of(policy), at(x), at(shift), at(scale), eps,
                                                           static_cast<DType>(out_dtype)));
     });
+}
+int64_t refd_depth_to_space_residual(int64_t projected, int64_t input) {
+    return guarded([&] { return keep(vrhino_b200::depth_to_space_residual(*g_backend, at(projected), at(input))); });
 }
 int64_t refd_swiglu(int64_t x) { return guarded([&] { return keep(vrhino_b200::swiglu(*g_backend, at(x))); }); }
 int64_t refd_group_norm_silu(int64_t x, int groups, int64_t w, int64_t b, float eps) {

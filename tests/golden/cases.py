@@ -59,6 +59,9 @@ def _inputs(case):
         shape = case["shape"]
         vec = (shape[0], shape[1]) + (1,) * (len(shape) - 2)
         return {"x": (n(shape, 0, 0.2, 1.5), case["dt"]), "shift": (n(vec, 1, 0, 0.2), "f32"), "scale": (n(vec, 2, 0, 0.2), "f32")}
+    if k == "depth_to_space":
+        b, c, t, h, w = case["shape"]
+        return {"x": (n((b, c, t, h, w), 0), case["dt"]), "y": (n((b, 4 * c, t, h, w), 1), case["dt"])}
     if k == "linear_output":
         # A GEMM whose F32 accumulators are exact whatever the summation order: only column 0 of x
         # is non-zero, so accumulation[m, n] = x[m, 0] * w[n, 0], the exact product of two bf16 values.
@@ -108,6 +111,8 @@ CASES = [
     {"name": "pixel_norm_f32_odd", "kind": "pixel_norm", "shape": (1, 20, 2, 3, 5), "dt": "f32", "seed": 26},
     {"name": "pixel_norm_f32_tiles", "kind": "pixel_norm", "shape": (2, 96, 2, 6, 10), "dt": "f32", "seed": 27, "subsample": 3},
     {"name": "pixel_norm_rows_f32", "kind": "pixel_norm", "shape": (6, 300), "dt": "f32", "seed": 28},
+    {"name": "depth_to_space_bf16", "kind": "depth_to_space", "shape": (1, 32, 3, 6, 16), "dt": "bf16", "seed": 29, "subsample": 5},
+    {"name": "depth_to_space_f32_odd", "kind": "depth_to_space", "shape": (2, 8, 2, 3, 5), "dt": "f32", "seed": 30},
     {"name": "linear_output_bf16_state", "kind": "linear_output", "m": 72, "n": 1536, "k": 16, "state": "bf16", "seed": 22, "subsample": 3},
     {"name": "linear_output_f32_state", "kind": "linear_output", "m": 40, "n": 3072, "k": 32, "state": "f32", "seed": 23, "subsample": 5},
 ]
@@ -214,6 +219,15 @@ def run_reference(rc, case):
         act = rc.activation(mod, 0)
         grab("silu", act, shape)
         grab("cast", rc.cast(act, ref.BF16), shape)
+    elif k == "depth_to_space":
+        b, c, t, h_, w = case["shape"]
+        full = (b, c // 2, 2 * t, 2 * h_, 2 * w)
+        shuffled = rc.pixel_shuffle(h["y"], (2, 2, 2))
+        grab("shuffle", shuffled, full)
+        grab("shuffle_122", rc.pixel_shuffle(h["y"], (1, 2, 2)), (b, c, t, 2 * h_, 2 * w))
+        grab("shuffle_211", rc.pixel_shuffle(h["x"], (2, 1, 1)), (b, c // 2, 2 * t, h_, w))
+        residual = rc.slice(rc.repeat(rc.pixel_shuffle(h["x"], (2, 2, 2)), 4, 1), 2, 1, 2 * t)
+        grab("depth_to_space", rc.binary(0, rc.slice(shuffled, 2, 1, 2 * t), residual), (b, c // 2, 2 * t - 1, 2 * h_, 2 * w))
     elif k == "linear_output":
         M, N = case["m"], case["n"]
         p = ref.POLICY_BF16 if case["state"] == "bf16" else ref.POLICY_FP32
@@ -293,6 +307,11 @@ def run_oracle(orc, case):
         mod = orc.modulate(be, pol, normed, ins["shift"], ins["scale"])
         act = be.activation(mod, 0)
         grab("pnorm", normed); grab("pmod", mod); grab("silu", act); grab("cast", be.cast(act, "bf16"))
+    elif k == "depth_to_space":
+        grab("shuffle", be.pixel_shuffle_nd(ins["y"], (2, 2, 2)))
+        grab("shuffle_122", be.pixel_shuffle_nd(ins["y"], (1, 2, 2)))
+        grab("shuffle_211", be.pixel_shuffle_nd(ins["x"], (2, 1, 1)))
+        grab("depth_to_space", orc.depth_to_space_residual(be, ins["y"], ins["x"]))
     elif k == "linear_output":
         p = orc.Policy(residual=case["state"])
         acc = orc.T(linear_accumulation(case), "f32")
@@ -423,6 +442,16 @@ def run_library(be, ops, case, fused=True):
             mod = ops.modulate(be, pol, be.pixel_norm(ins["x"], 1, 1e-8), ins["shift"], ins["scale"])
             act = be.activation(mod, ops.SILU)
             grab("pmod", mod); grab("silu", act); grab("cast", be.cast(act, torch.bfloat16))
+    elif k == "depth_to_space":
+        shuffled = be.pixel_shuffle_nd(ins["y"], (2, 2, 2))
+        grab("shuffle", shuffled)
+        grab("shuffle_122", be.pixel_shuffle_nd(ins["y"], (1, 2, 2)))
+        grab("shuffle_211", be.pixel_shuffle_nd(ins["x"], (2, 1, 1)))
+        if fused:
+            grab("depth_to_space", ops.fused_depth_to_space_residual(be, ins["y"], ins["x"]))
+        else:
+            residual = torch.cat([be.pixel_shuffle_nd(ins["x"], (2, 2, 2))] * 4, dim=1)[:, :, 1:].contiguous()
+            grab("depth_to_space", be.add(shuffled[:, :, 1:].contiguous(), residual))
     elif k == "linear_output":
         p = ops.Policy(residual=tdt[case["state"]])
         acc = torch.from_numpy(linear_accumulation(case)).cuda()

@@ -61,7 +61,7 @@ def _grab(rd, case, handle, shape):
 
 @pytest.mark.parametrize("case", [c for c in cases.CASES if c["kind"] in
                                   ("ln_modulate", "rms_rope", "gated_residual", "mochi", "group_norm", "sampler", "linear_output",
-                                   "pixel_norm")],
+                                   "pixel_norm", "depth_to_space")],
                          ids=lambda c: c["name"])
 def test_fused_call_site_forms(orc, golden, dropin, case):
     """One kernel per chain through vrhino_b200::layer_norm_modulate / rms_norm_rope / ... ."""
@@ -111,6 +111,10 @@ def test_fused_call_site_forms(orc, golden, dropin, case):
                         assert np.array_equal(got_bits, want_bits)
                     else:   # the one-kernel modulate rounds once where the chain rounds per operator
                         compare(orc, case, "normed", (cases._sub(case, got_bits), "bf16"), (cases._sub(case, want_bits), "bf16"))
+        elif k == "depth_to_space":
+            b, c, t, h_, w = case["shape"]
+            got = rd.fused_depth_to_space_residual(h["y"], h["x"])
+            compare(orc, case, "depth_to_space", _grab(rd, case, got, (b, c // 2, 2 * t - 1, 2 * h_, 2 * w)), want["depth_to_space"])
         elif k == "pixel_norm":
             got = rd.fused_pixel_norm_modulate_silu(pol, h["x"], h["shift"], h["scale"], 1e-8)
             compare(orc, case, "silu", _grab(rd, case, got, case["shape"]), want["silu"], strict_tables=True)

@@ -322,7 +322,39 @@ Tensor B200Backend::pixel_norm(const Tensor& raw, int64_t dim, float eps) {
     });
 }
 
+Tensor B200Backend::pixel_shuffle_nd(const Tensor& raw, const std::vector<int64_t>& factors) {
+    return guarded([&] {   // VRHINO_PROFILE("pixel_shuffle") carries the failure guard (cuda_backend.cu:5114)
+        require(raw.ndim() == 5 && factors.size() == 3, "pixel_shuffle_nd requires 5D and 3 factors");
+        const int64_t product = factors[0] * factors[1] * factors[2];
+        require(product > 0 && raw.dim(1) % product == 0, "pixel shuffle channel mismatch");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype);
+        Tensor out = rt_->allocate_device({x.dim(0), x.dim(1) / product, x.dim(2) * factors[0], x.dim(3) * factors[1],
+                                           x.dim(4) * factors[2]}, dtype);
+        check(vrb_pixel_shuffle(x.data(), out.data(), code(dtype), x.dim(0), x.dim(1) / product, x.dim(2), x.dim(3), x.dim(4),
+                                static_cast<int>(factors[0]), static_cast<int>(factors[1]), static_cast<int>(factors[2]),
+                                kLegacyStream));
+        return out;
+    });
+}
+
 // ---- fused forms --------------------------------------------------------------------------------
+
+Tensor B200Backend::depth_to_space_residual(const Tensor& projected_raw, const Tensor& input_raw) {
+    return guarded([&] {
+        require(input_raw.ndim() == 5 && projected_raw.ndim() == 5, "pixel_shuffle_nd requires 5D and 3 factors");
+        const DType dtype = operand_dtype(projected_raw);
+        Tensor projected = copy_to_device(projected_raw, dtype), input = copy_to_device(input_raw, dtype);
+        require(input.dim(1) % 8 == 0 && projected.dim(1) == 4 * input.dim(1), "pixel shuffle channel mismatch");
+        require(projected.dim(0) == input.dim(0) && projected.dim(2) == input.dim(2) && projected.dim(3) == input.dim(3) &&
+                    projected.dim(4) == input.dim(4), "Incompatible broadcast shapes");
+        Tensor out = rt_->allocate_device({input.dim(0), input.dim(1) / 2, 2 * input.dim(2) - 1, 2 * input.dim(3),
+                                           2 * input.dim(4)}, dtype);
+        check(vrb_depth_to_space_residual(projected.data(), input.data(), out.data(), code(dtype), input.dim(0), input.dim(1),
+                                          input.dim(2), input.dim(3), input.dim(4), kLegacyStream));
+        return out;
+    });
+}
 
 Tensor B200Backend::pixel_norm_modulate(const Tensor& raw, const Tensor& shift_raw, const Tensor& scale_raw, float eps,
                                         bool silu, DType output) {
@@ -619,6 +651,15 @@ Tensor pixel_norm_modulate_silu(vrhino::Backend& backend, const vrhino::Precisio
     Tensor y = backend.activation(vrhino::modulate(backend, policy, backend.pixel_norm(x, 1, eps), shift, scale),
                                   vrhino::Activation::Silu);
     return y.dtype() == output ? y : backend.cast(y, output);
+}
+
+Tensor depth_to_space_residual(vrhino::Backend& backend, const Tensor& projected, const Tensor& input) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend)) return b200->depth_to_space_residual(projected, input);
+    Tensor residual = backend.pixel_shuffle_nd(input, {2, 2, 2});
+    residual = backend.concat({residual, residual, residual, residual}, 1);
+    residual = backend.slice(residual, 2, 1, residual.dim(2));
+    Tensor x = backend.pixel_shuffle_nd(projected, {2, 2, 2});
+    return backend.add(backend.slice(x, 2, 1, x.dim(2)), residual);
 }
 
 Tensor swiglu(vrhino::Backend& backend, const Tensor& projected) {

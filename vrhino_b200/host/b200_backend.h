@@ -56,6 +56,7 @@ public:
     Tensor sqrt(const Tensor& x) override;
     Tensor copy_to_device(const Tensor& input, DType dtype) override;
     Tensor pixel_norm(const Tensor& x, int64_t dim, float eps) override;
+    Tensor pixel_shuffle_nd(const Tensor& x, const std::vector<int64_t>& factors) override;
 
     // ---- fused forms (one kernel each); see the free functions below for the call-site view --
     Tensor layer_norm_modulate(const Tensor& x, const Tensor* weight, const Tensor* bias, float eps,
@@ -81,6 +82,8 @@ public:
     Tensor linear_swiglu(const Tensor& x, const Tensor& weight, const Tensor* bias);
     // [silu](modulate(pixel_norm(x, 1, eps), shift, scale)) cast to `output`; shift / scale [B, C, 1, ...]
     Tensor pixel_norm_modulate(const Tensor& x, const Tensor& shift, const Tensor& scale, float eps, bool silu, DType output);
+    // slice(pixel_shuffle(projected, {2,2,2}), 2, 1, 2T) + slice(concat(4 x pixel_shuffle(input, {2,2,2}), 1), 2, 1, 2T)
+    Tensor depth_to_space_residual(const Tensor& projected, const Tensor& input);
     Tensor swiglu(const Tensor& projected);
     Tensor group_norm_silu(const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps);
     // x [B, C, T, H, W]: statistics per (batch entry, frame, group), no permutes
@@ -160,7 +163,6 @@ public:
     Tensor interpolate_nearest(const Tensor& x, const std::vector<double>& f) override { return rt_->interpolate_nearest(x, f); }
     Tensor interpolate_bilinear_2d(const Tensor& x, int64_t h, int64_t w, bool a) override { return rt_->interpolate_bilinear_2d(x, h, w, a); }
     Tensor l2_normalize(const Tensor& x, int64_t d, float e) override { return rt_->l2_normalize(x, d, e); }
-    Tensor pixel_shuffle_nd(const Tensor& x, const std::vector<int64_t>& f) override { return rt_->pixel_shuffle_nd(x, f); }
     Tensor rng_normal(vrhino::RngState& s, const std::vector<int64_t>& shape, DType d) override { return rt_->rng_normal(s, shape, d); }
 
 private:
@@ -222,6 +224,9 @@ vrhino::Tensor linear_swiglu(vrhino::Backend& backend, const vrhino::Tensor& x, 
 vrhino::Tensor pixel_norm_modulate_silu(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy,
                                         const vrhino::Tensor& x, const vrhino::Tensor& shift, const vrhino::Tensor& scale,
                                         float eps = 1e-8f, vrhino::DType output = vrhino::DType::F32);
+// LTX depth_to_space (ltx.cpp:250-259) after its convolution `projected` = edge_time_conv(input): the two
+// pixel_shuffles, the four-fold concat, the two slices and the add as one kernel
+vrhino::Tensor depth_to_space_residual(vrhino::Backend& backend, const vrhino::Tensor& projected, const vrhino::Tensor& input);
 // mul(parts[0], silu(parts[1])), parts = split(projected, {H, H}, -1)   (mochi.cpp:195-202)
 vrhino::Tensor swiglu(vrhino::Backend& backend, const vrhino::Tensor& projected);
 // activation(group_norm(x, groups, weight, bias, eps), Silu)   (autoencoder_kl.cpp:31-41)

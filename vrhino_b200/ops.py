@@ -211,6 +211,21 @@ class B200Backend:
              x.numel() // (channels * inner), channels, inner, ctypes.c_float(eps), _stream())
         return out
 
+    def pixel_shuffle_nd(self, raw, factors, out=None):
+        """CudaBackend::pixel_shuffle_nd (native/src/backend/cuda/cuda_backend.cu:5112-5118)."""
+        if raw.dim() != 5 or len(factors) != 3:
+            raise VrbError("pixel_shuffle_nd requires 5D and 3 factors")
+        ft, fh, fw = (int(f) for f in factors)
+        product = ft * fh * fw
+        if raw.shape[1] % product:
+            raise VrbError("pixel shuffle channel mismatch")
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        b, c, t, h, w = x.shape
+        out = _result(out, (b, c // product, t * ft, h * fh, w * fw), dtype, x.device)
+        call("vrb_pixel_shuffle", _ptr(x), _ptr(out), _code(dtype), b, c // product, t, h, w, ft, fh, fw, _stream())
+        return out
+
     def activation(self, raw, kind, out=None):
         dtype = self._dtype_of(raw)
         x = _dense(self.copy_to_device(raw, dtype))
@@ -569,6 +584,19 @@ def fused_pixel_norm_modulate(be, x, shift, scale, eps=1e-8, silu=True, out_dtyp
     out = _result(out, x.shape, out_dtype, x.device)
     call("vrb_pixel_norm", _ptr(x), _code(x), _ptr(_dense(scale)), _ptr(_dense(shift)), _code(scale), int(bool(silu)),
          _ptr(out), _code(out_dtype), x.shape[0], channels, inner, ctypes.c_float(eps), _stream())
+    return out
+
+
+def fused_depth_to_space_residual(be, projected, x, out=None):
+    """LTX depth_to_space (native/src/architectures/ltx.cpp:250-259) after its convolution: projected
+    [B, 4C, T, H, W] is the convolution output, x [B, C, T, H, W] the block input; returns
+    pixel_shuffle(projected)[:, :, 1:] + repeat4(pixel_shuffle(x))[:, :, 1:] as [B, C/2, 2T-1, 2H, 2W]."""
+    projected, x = _dense(projected), _dense(x)
+    b, c, t, h, w = x.shape
+    if projected.dtype != x.dtype or tuple(projected.shape) != (b, 4 * c, t, h, w):
+        raise VrbError("Incompatible broadcast shapes")
+    out = _result(out, (b, c // 2, 2 * t - 1, 2 * h, 2 * w), x.dtype, x.device)
+    call("vrb_depth_to_space_residual", _ptr(projected), _ptr(x), _ptr(out), _code(x), b, c, t, h, w, _stream())
     return out
 
 
