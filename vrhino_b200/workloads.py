@@ -320,6 +320,32 @@ class LtxVaeNorm:
                 Launch("pixel_norm modulate silu bf16", bf16, n * (eb + 2))]
 
 
+class LtxDepthToSpace:
+    """LTX decoder up-block tail (native/src/architectures/ltx.cpp:250-259) on a feature map [1, C, T, H, W]
+    bf16: the convolution output [1, 4C, T, H, W] and the block input, shuffled, repeated, sliced and
+    added in one pass; plus pixel_shuffle_nd alone.  Algorithmic bytes: inputs once + result once."""
+
+    def __init__(self, be, shape=(1, 256, 16, 128, 192), dtype=BF16, seed=0):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        b, c, t, h, w = shape
+        self.be = be
+        self.x = _randn(shape, dtype, g)
+        self.y = _randn((b, 4 * c, t, h, w), dtype, g)
+        self.out = {}
+
+    def launches(self) -> List[Launch]:
+        be, o = self.be, self.out
+        eb = self.x.element_size()
+        b, c, t, h, w = self.x.shape
+        out_elems = b * (c // 2) * (2 * t - 1) * 4 * h * w
+
+        def d2s(): o["d2s"] = ops.fused_depth_to_space_residual(be, self.y, self.x, out=o.get("d2s"))
+        def shuffle(): o["shuffle"] = be.pixel_shuffle_nd(self.y, (2, 2, 2), out=o.get("shuffle"))
+
+        return [Launch("depth_to_space residual", d2s, (self.y.numel() + self.x.numel() + out_elems) * eb),
+                Launch("pixel_shuffle 2x2x2", shuffle, self.y.numel() * 2 * eb)]
+
+
 def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, batch=1):
     """The launch list of headline configuration 2..5 (optionally at a reduced token / frame count),
     or of the additional measurement configurations 6..9."""
@@ -340,9 +366,12 @@ def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, b
         return LinearEpilogues(be, tokens=tokens or 32760, batch=batch, merged=config == 8)
     if config == 10:
         return LtxVaeNorm(be, shape=(1, 128, frames or 16, 256, 384), dtype=hidden_dtype)
-    raise ValueError("config must be 2..10 (6 = config 5 as a pre-permuted per-frame tensor, 7 = per-frame statistics "
+    if config == 11:
+        return LtxDepthToSpace(be, shape=(1, 256, frames or 16, 128, 192), dtype=hidden_dtype)
+    raise ValueError("config must be 2..11 (6 = config 5 as a pre-permuted per-frame tensor, 7 = per-frame statistics "
                      "on the unpermuted [N,C,T,H,W] tensor, 8 = linear epilogues merged with their consumers, "
-                     "9 = the same as separate launches, 10 = LTX VAE pixel_norm -> modulate -> SiLU)")
+                     "9 = the same as separate launches, 10 = LTX VAE pixel_norm -> modulate -> SiLU, "
+                     "11 = LTX VAE depth_to_space)")
 
 
 def _main():
