@@ -102,9 +102,11 @@ def test_rms_norm_rejections(gpu):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape,axis", [((2, 5, 3), 1), ((2, 7, 4, 5), 1), ((2, 3, 9, 5), 2), ((1, 17, 2, 3, 5), 1), ((1, 96, 2, 8, 16), 1)])
+@pytest.mark.parametrize("shape,axis", [((2, 5, 3), 1), ((2, 7, 4, 5), 1), ((2, 3, 9, 5), 2), ((1, 17, 2, 3, 5), 1), ((1, 96, 2, 8, 16), 1),
+                                        ((2, 384, 1, 5, 8), 1), ((1, 1024, 1, 3, 16), 1), ((1, 3000, 1, 1, 16), 1), ((3, 13, 1, 1, 24), 1)])
 def test_rms_norm_axis(orc, gpu, dtype, shape, axis):
-    """primitive_tests.cpp:406-424 shapes plus a Wan-VAE-like [1, C, T, H, W]."""
+    """primitive_tests.cpp:406-424 shapes plus Wan-VAE-like [1, C, T, H, W] tensors that take the
+    shared-memory tile path (full and ragged tiles, 8 / 4 / 2 / 1 chunks per channel row)."""
     be, ops = gpu
     from vrhino_b200 import synth
     x = orc.tensor(synth.normal(shape, seed=9), dtype)

@@ -67,6 +67,11 @@ int launch_linear_output_swiglu_lut(const float* accumulation, const void* bias,
 // same values go to every dst[k] (this GPU's and peer-mapped full-size tensors), plane p of x
 // landing at element p * plane_stride + plane_offset -- the all-gather of an H-sharded feature map
 // done by the kernel's own stores.
+// Axis RMSNorm through shared-memory tiles (vrb_pixel_norm.cu); false when the layout needs the
+// caller's two-pass kernel (inner extent not a multiple of a 16-byte chunk, misaligned tensors).
+bool launch_rms_axis_tiles(const void* x, int dtype, const void* weight, int weight_dtype, void* out, int64_t outer,
+                           int64_t channels, int64_t inner, float eps, int fuse_silu, cudaStream_t stream);
+
 struct GnScatter {
     void* dst[8];
     int count;

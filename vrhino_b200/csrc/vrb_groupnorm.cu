@@ -626,6 +626,8 @@ extern "C" int vrb_rms_norm_axis(const void* x, int dtype, const void* weight, i
     VRB_REQUIRE(outer > 0 && axis > 0 && inner > 0, VRB_ERR_INVALID, "rms_norm axis invalid");
     VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "rms_norm_axis: dtype must be F32 or BF16");
     cudaStream_t s = as_stream(stream);
+    if (inner > 1 && launch_rms_axis_tiles(x, dtype, weight, weight_dtype, out, outer, axis, inner, eps, fuse_silu, s))
+        return after_launch("rms_norm_axis");
     if (inner % 8 == 0 && aligned16(x) && aligned16(out)) {
         const int64_t items = outer * (inner / 8);
         rms_axis_kernel<true><<<grid_for((items + kThreads - 1) / kThreads, 8), kThreads, 0, s>>>(

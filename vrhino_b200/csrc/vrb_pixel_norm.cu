@@ -301,7 +301,164 @@ int tile_ctas_per_sm(K kernel, size_t smem) {
     return n;
 }
 
+// ---- RMSNorm over the channel axis with the same tile scheme ------------------------------------
+// CudaBackend::rms_norm over an inner axis (rms_norm_axis_parallel_kernel,
+// native/src/backend/cuda/cuda_backend.cu:1045-1095; the Wan VAE's rms_channel, components/executor.cpp:90-93):
+// per position 8 reduction lanes, lane a takes channels a, a+8, ... in double, lanes combined in
+// lane order; inverse = rsqrtf(float(total / channels) + eps); y = x * inverse rounded to x's
+// dtype, times the weight (converted to x's dtype), rounded; optionally SiLU of that value.
+struct RmsAxisParams {
+    const void* x;
+    void* out;
+    const void* weight;   // [channels] or nullptr
+    int w_dt;
+    int64_t outer, channels, inner;
+    float eps;
+};
+
+template <bool X_BF16, bool SILU>
+__global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisParams p, int cols, int cols_log2) {
+    constexpr int EPC = X_BF16 ? 8 : 4;
+    constexpr int X_DT = X_BF16 ? VRB_BF16 : VRB_F32;
+    extern __shared__ __align__(16) uint4 tiles_buffer[];   // two tiles of [channels][cols], then the reduction scratch
+    const int channels = static_cast<int>(p.channels);
+    const int positions = cols * EPC;
+    const int tile_chunks = channels * cols;
+    double* const partial = reinterpret_cast<double*>(tiles_buffer + 2 * static_cast<size_t>(tile_chunks));   // [kLanes][positions]
+    float* const inverse = reinterpret_cast<float*>(partial + kLanes * positions);                          // [positions]
+    const int64_t inner_chunks = p.inner / EPC;
+    const int64_t tiles_per_outer = (inner_chunks + cols - 1) / cols;
+    const int64_t tiles = p.outer * tiles_per_outer;
+    const uint4* const x = static_cast<const uint4*>(p.x);
+
+    auto request = [&](int64_t t, int b) {
+        if (t < tiles) {
+            const int64_t o = t / tiles_per_outer;
+            const int64_t chunk0 = (t - o * tiles_per_outer) * cols;
+            const int valid = static_cast<int>(inner_chunks - chunk0 < cols ? inner_chunks - chunk0 : cols);
+            const uint4* const src = x + o * p.channels * inner_chunks + chunk0;
+            uint4* const dst = tiles_buffer + static_cast<size_t>(b) * tile_chunks;
+            for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads) {
+                const int c = idx >> cols_log2, k = idx & (cols - 1);
+                if (k < valid) async_copy16(dst + idx, src + static_cast<int64_t>(c) * inner_chunks + k);
+                else dst[idx] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        async_copy_commit();
+    };
+
+    int buffer = 0;
+    request(blockIdx.x, 0);
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, buffer ^= 1) {
+        const int64_t o = t / tiles_per_outer;
+        const int64_t chunk0 = (t - o * tiles_per_outer) * cols;
+        const int valid = static_cast<int>(inner_chunks - chunk0 < cols ? inner_chunks - chunk0 : cols);
+        const uint4* const tile = tiles_buffer + static_cast<size_t>(buffer) * tile_chunks;
+        request(t + gridDim.x, buffer ^ 1);
+        async_copy_wait<1>();
+        __syncthreads();
+        constexpr int PPW = X_BF16 ? 2 : 1;
+        const int words = positions / PPW;
+        const uint32_t* const tile_words = reinterpret_cast<const uint32_t*>(tile);
+        for (int item = threadIdx.x; item < words * kLanes; item += kThreads) {
+            const int lane = item / words, word = item - lane * words;
+            double q0 = 0.0, q1 = 0.0;
+            const uint32_t* e = tile_words + lane * words + word;
+            const int step = kLanes * words;
+#pragma unroll 4
+            for (int c = lane; c < channels; c += kLanes, e += step) {
+                const uint32_t w = *e;
+                if constexpr (X_BF16) {
+                    const double lo = static_cast<double>(__uint_as_float(w << 16)), hi = static_cast<double>(__uint_as_float(w & 0xffff0000u));
+                    q0 = fma(lo, lo, q0);
+                    q1 = fma(hi, hi, q1);
+                } else {
+                    const double v = static_cast<double>(__uint_as_float(w));
+                    q0 = fma(v, v, q0);
+                }
+            }
+            partial[lane * positions + word * PPW] = q0;
+            if constexpr (X_BF16) partial[lane * positions + word * PPW + 1] = q1;
+        }
+        __syncthreads();
+        if (threadIdx.x < positions) {
+            double total = 0.0;
+#pragma unroll
+            for (int a = 0; a < kLanes; ++a) total += partial[a * positions + threadIdx.x];
+            inverse[threadIdx.x] = rsqrtf(__fadd_rn(static_cast<float>(total / static_cast<double>(p.channels)), p.eps));
+        }
+        __syncthreads();
+        const int64_t out_chunk0 = o * p.channels * inner_chunks + chunk0;
+        for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads) {
+            const int c = idx >> cols_log2, k = idx & (cols - 1);
+            if (k >= valid) continue;
+            const bool weighted = p.weight != nullptr;
+            const float w = weighted ? round_to(X_DT, load1(p.weight, p.w_dt, c)) : 1.0f;
+            const uint4 raw = tile[idx];
+            const int64_t chunk = out_chunk0 + static_cast<int64_t>(c) * inner_chunks + k;
+            const float4* i4 = reinterpret_cast<const float4*>(inverse + k * EPC);
+            auto finish_one = [&](float v, float inv) {
+                float y = __fmul_rn(v, inv);
+                if constexpr (X_BF16) y = round_to_bf16(y);
+                if (weighted) { y = __fmul_rn(y, w); if constexpr (X_BF16) y = round_to_bf16(y); }
+                if constexpr (SILU) y = activation_value(VRB_SILU, y);
+                return y;
+            };
+            if constexpr (X_BF16) {
+                const float4 ia = i4[0], ib = i4[1];
+                const float inv[8] = {ia.x, ia.y, ia.z, ia.w, ib.x, ib.y, ib.z, ib.w};
+                const uint32_t wd[4] = {raw.x, raw.y, raw.z, raw.w};
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    v[2 * j] = finish_one(__uint_as_float(wd[j] << 16), inv[2 * j]);
+                    v[2 * j + 1] = finish_one(__uint_as_float(wd[j] & 0xffff0000u), inv[2 * j + 1]);
+                }
+                __stcs(static_cast<uint4*>(p.out) + chunk, make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                                                      pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])));
+            } else {
+                const float4 ia = i4[0];
+                __stcs(static_cast<float4*>(p.out) + chunk,
+                       make_float4(finish_one(__uint_as_float(raw.x), ia.x), finish_one(__uint_as_float(raw.y), ia.y),
+                                   finish_one(__uint_as_float(raw.z), ia.z), finish_one(__uint_as_float(raw.w), ia.w)));
+            }
+        }
+        __syncthreads();
+    }
+    async_copy_wait<0>();
+}
+
 }  // namespace
+
+// Launches the tile form of the axis RMSNorm when the layout allows it; false = caller's fallback.
+bool launch_rms_axis_tiles(const void* x, int dtype, const void* weight, int weight_dtype, void* out, int64_t outer,
+                           int64_t channels, int64_t inner, float eps, int fuse_silu, cudaStream_t stream) {
+    const int epc = dtype == VRB_BF16 ? 8 : 4;
+    if (inner % epc != 0 || !aligned16(x) || !aligned16(out) || channels >= (int64_t{1} << 20)) return false;
+    const int64_t inner_chunks = inner / epc;
+    RmsAxisParams p{x, out, weight, weight_dtype, outer, channels, inner, eps};
+    for (int budget_ctas : {3, 1}) {
+        for (int cols = 8, log2 = 3; cols >= 1; cols >>= 1, --log2) {
+            if (cols > 1 && cols / 2 >= inner_chunks) continue;
+            const size_t smem = 2 * static_cast<size_t>(channels) * cols * 16 + static_cast<size_t>(cols) * epc * (kLanes * 8 + 4);
+            if (smem > (budget_ctas == 3 ? 72 * 1024 : 200 * 1024) || smem > kMaxTileBytes) continue;
+            const int64_t tiles = outer * ((inner_chunks + cols - 1) / cols);
+            bool launched = true;
+#define VRB_RA(XB, S)                                                                                     \
+    {                                                                                                     \
+        const int per_sm = tile_ctas_per_sm(rms_axis_tile_kernel<XB, S>, smem);                           \
+        if (per_sm < 1) launched = false;                                                                 \
+        else rms_axis_tile_kernel<XB, S><<<grid_for(tiles, per_sm), kThreads, smem, stream>>>(p, cols, log2); \
+    }
+            if (dtype == VRB_BF16) { if (fuse_silu) VRB_RA(true, true) else VRB_RA(true, false) }
+            else { if (fuse_silu) VRB_RA(false, true) else VRB_RA(false, false) }
+#undef VRB_RA
+            if (launched) return true;
+        }
+    }
+    return false;
+}
+
 }  // namespace vrb
 
 using namespace vrb;

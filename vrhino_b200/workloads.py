@@ -346,6 +346,28 @@ class LtxDepthToSpace:
                 Launch("pixel_shuffle 2x2x2", shuffle, self.y.numel() * 2 * eb)]
 
 
+class WanVaeRmsChannel:
+    """Wan VAE rms_channel (+ SiLU) (native/src/components/executor.cpp:90-93 as used by wan.cpp:225-297):
+    RMSNorm over the channel axis of [1, C, T, H, W] bf16 ~N(0,1) with gamma [C] ~N(1,0.1), eps 1e-12.
+    Algorithmic bytes: input once + result once."""
+
+    def __init__(self, be, shape=(1, 192, 4, 240, 416), dtype=BF16, seed=0):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        self.be = be
+        self.x = _randn(shape, dtype, g)
+        self.gamma = _randn((shape[1],), F32, g, 1.0, 0.1)
+        self.out = {}
+
+    def launches(self) -> List[Launch]:
+        be, x = self.be, self.x
+        n = x.numel() * x.element_size() * 2
+
+        def plain(): self.out["plain"] = be.rms_norm(x, self.gamma, 1e-12, 1)
+        def silu(): self.out["silu"] = ops.fused_rms_channel_silu(be, x, self.gamma, 1e-12)
+
+        return [Launch("rms_channel", plain, n), Launch("rms_channel silu", silu, n)]
+
+
 def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, batch=1):
     """The launch list of headline configuration 2..5 (optionally at a reduced token / frame count),
     or of the additional measurement configurations 6..9."""
@@ -368,10 +390,12 @@ def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, b
         return LtxVaeNorm(be, shape=(1, 128, frames or 16, 256, 384), dtype=hidden_dtype)
     if config == 11:
         return LtxDepthToSpace(be, shape=(1, 256, frames or 16, 128, 192), dtype=hidden_dtype)
-    raise ValueError("config must be 2..11 (6 = config 5 as a pre-permuted per-frame tensor, 7 = per-frame statistics "
+    if config == 12:
+        return WanVaeRmsChannel(be, shape=(1, 192, frames or 4, 240, 416), dtype=hidden_dtype)
+    raise ValueError("config must be 2..12 (6 = config 5 as a pre-permuted per-frame tensor, 7 = per-frame statistics "
                      "on the unpermuted [N,C,T,H,W] tensor, 8 = linear epilogues merged with their consumers, "
                      "9 = the same as separate launches, 10 = LTX VAE pixel_norm -> modulate -> SiLU, "
-                     "11 = LTX VAE depth_to_space)")
+                     "11 = LTX VAE depth_to_space, 12 = Wan VAE rms_channel + SiLU)")
 
 
 def _main():
