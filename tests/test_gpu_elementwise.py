@@ -53,6 +53,28 @@ def test_binary_indexing_bit_exact(orc, gpu, dtype, label, a_shape, b_shape):
         assert_bits_equal(got, want, f"{label}/{dtype}/{name}")
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("a_shape,b_shape", [
+    ((2, 16, 3, 4, 8), (2, 16, 1, 1, 1)),     # channel vector over [B, C, T, H, W]: two merged axes
+    ((1, 16, 1, 1, 1), (2, 16, 3, 4, 8)),     # the same with the operands swapped
+    ((2, 5, 64), (2, 1, 64)),                 # per-batch row vector: three merged axes
+    ((4, 6, 8), (4, 1, 1)),                   # one value per row
+    ((3, 5, 7, 16), (1, 5, 1, 16)),           # four merged axes: general indexing
+    ((2, 3, 24), (2, 3, 1)),                  # innermost run 24
+    ((2, 16, 3, 4, 8), (1, 1, 3, 1, 1)),      # vector along a middle axis
+    ((2, 1, 40), (1, 7, 1)),                  # both operands broadcast
+])
+def test_binary_inner_axis_broadcasts_bit_exact(orc, gpu, dtype, a_shape, b_shape):
+    """Broadcasts along inner axes (VAE per-channel statistics, per-batch modulation rows): the
+    merged-axes vector path and the general path must agree with the oracle bit for bit."""
+    be, ops = gpu
+    obe = orc.OracleBackend(execution_dtype=dtype)
+    a, b = indexing_input(orc, a_shape, dtype, 1), indexing_input(orc, b_shape, dtype, 3)
+    ta, tb = to_torch(a), to_torch(b)
+    for kind, name in enumerate(["add", "mul", "div", "maximum"]):
+        assert_bits_equal(getattr(be, name)(ta, tb), obe._binary(kind, a, b), f"{a_shape}x{b_shape}/{dtype}/{name}")
+
+
 def test_binary_rejections(gpu):
     be, ops = gpu
     import torch

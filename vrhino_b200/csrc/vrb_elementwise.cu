@@ -163,6 +163,76 @@ int64_t flat_period(const Meta& out, const Meta& in) {
     return remaining == 1 ? elements : 0;
 }
 
+// Broadcast along inner axes (a [B, C, T, H, W] tensor with a [B, C, 1, 1, 1] vector, [B, S, D] with
+// [B, 1, D], ...): the output's axes are merged wherever both operands stay dense or both stay
+// broadcast, and if at most three merged axes remain and the innermost run is a multiple of 8
+// elements, each operand is either read in 16-byte chunks along it or is one value per run.
+struct Collapsed {
+    int dims;            // 1..3, innermost last
+    int64_t shape[3];
+    int64_t a_stride[3], b_stride[3];   // in elements; 0 = broadcast
+};
+bool collapse(const Meta& om, const Meta& am, const Meta& bm, Collapsed& c) {
+    int64_t shape[8], as[8], bs[8];
+    int n = 0;
+    for (int d = 0; d < om.rank; ++d) {
+        if (om.shape[d] == 1) continue;
+        const int ad = d - (om.rank - am.rank), bd = d - (om.rank - bm.rank);
+        const int64_t sa = (ad >= 0 && am.shape[ad] != 1) ? am.strides[ad] : 0;
+        const int64_t sb = (bd >= 0 && bm.shape[bd] != 1) ? bm.strides[bd] : 0;
+        if (n > 0) {
+            // merge into the previous (outer) axis when it continues densely, or stays broadcast, in both operands
+            const bool a_ok = (as[n - 1] == sa * om.shape[d]) && (sa != 0 || as[n - 1] == 0);
+            const bool b_ok = (bs[n - 1] == sb * om.shape[d]) && (sb != 0 || bs[n - 1] == 0);
+            if (a_ok && b_ok) { shape[n - 1] *= om.shape[d]; as[n - 1] = sa; bs[n - 1] = sb; continue; }
+        }
+        shape[n] = om.shape[d]; as[n] = sa; bs[n] = sb; ++n;
+    }
+    if (n == 0 || n > 3) return false;
+    c.dims = 3;
+    for (int k = 0; k < 3; ++k) {
+        const int src = n - 3 + k;
+        c.shape[k] = src >= 0 ? shape[src] : 1;
+        c.a_stride[k] = src >= 0 ? as[src] : 0;
+        c.b_stride[k] = src >= 0 ? bs[src] : 0;
+    }
+    if (c.shape[2] % 8 != 0) return false;
+    for (int k = 0; k < 3; ++k) {
+        if (k < 2 && (c.a_stride[k] % 8 != 0 || c.b_stride[k] % 8 != 0) ) {
+            // an outer stride that is not a multiple of 8 elements is fine for an operand that is one
+            // value per run (its chunk loads are scalar), not for one read in chunks
+            if ((c.a_stride[k] % 8 != 0 && c.a_stride[2] != 0) || (c.b_stride[k] % 8 != 0 && c.b_stride[2] != 0)) return false;
+        }
+    }
+    return (c.a_stride[2] == 0 || c.a_stride[2] == 1) && (c.b_stride[2] == 0 || c.b_stride[2] == 1);
+}
+
+template <int KIND, typename I>
+__global__ void __launch_bounds__(kThreads) binary_collapsed_vec_kernel(const void* __restrict__ a, const void* __restrict__ b,
+                                                                        void* __restrict__ out, int dt, Collapsed c) {
+    const I n1 = static_cast<I>(c.shape[1]), n2 = static_cast<I>(c.shape[2] / 8);
+    const I total = static_cast<I>(c.shape[0]) * n1 * n2;
+    const I stride = static_cast<I>(gridDim.x) * blockDim.x;
+    for (I i = static_cast<I>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const I r = i / n2, i2 = i - r * n2;
+        const I i0 = r / n1, i1 = r - i0 * n1;
+        const int64_t ao = static_cast<int64_t>(i0) * c.a_stride[0] + static_cast<int64_t>(i1) * c.a_stride[1];
+        const int64_t bo = static_cast<int64_t>(i0) * c.b_stride[0] + static_cast<int64_t>(i1) * c.b_stride[1];
+        float av[8], bv[8];
+        if (c.a_stride[2]) load8<true>(a, dt, ao + static_cast<int64_t>(i2) * 8, av);
+        else { const float v = load1(a, dt, ao);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) av[e] = v; }
+        if (c.b_stride[2]) load8<true>(b, dt, bo + static_cast<int64_t>(i2) * 8, bv);
+        else { const float v = load1(b, dt, bo);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) bv[e] = v; }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) av[e] = binary_value<KIND>(av[e], bv[e]);
+        store8(out, dt, static_cast<int64_t>(i) * 8, av);
+    }
+}
+
 template <int KIND>
 int launch_binary(const void* a, const Meta& am, const void* b, const Meta& bm, void* out, const Meta& om,
                   int64_t count, int dt, cudaStream_t stream) {
@@ -172,6 +242,13 @@ int launch_binary(const void* a, const Meta& am, const void* b, const Meta& bm, 
         const int64_t chunks = count / 8;
         binary_flat_vec_kernel<KIND><<<grid_for((chunks + kThreads - 1) / kThreads, kPerSm), kThreads, 0, stream>>>(
             a, b, out, dt, chunks, ap, bp, count);
+    } else if (Collapsed c; vec8_ok(count, {a, b, out}) && collapse(om, am, bm, c)) {
+        const int64_t chunks = count / 8;
+        const int grid = grid_for((chunks + kThreads - 1) / kThreads, kPerSm);
+        if (chunks + static_cast<int64_t>(grid) * kThreads < (int64_t{1} << 32))
+            binary_collapsed_vec_kernel<KIND, unsigned><<<grid, kThreads, 0, stream>>>(a, b, out, dt, c);
+        else
+            binary_collapsed_vec_kernel<KIND, int64_t><<<grid, kThreads, 0, stream>>>(a, b, out, dt, c);
     } else {
         binary_general_kernel<KIND><<<grid_for((count + kThreads - 1) / kThreads, kPerSm), kThreads, 0, stream>>>(
             a, b, out, dt, count, om, am, bm);
