@@ -315,6 +315,14 @@ int vrb_linear_output_gated_residual(const float* accumulation, const void* bias
 int vrb_linear_output_swiglu(const float* accumulation, const void* bias, void* out, int64_t rows,
                              int64_t hidden, vrb_stream stream);
 
+/* SamplingPrimitives::linear_combine (native/src/sampling/sampling.cpp:173-179) in one pass, 1..4 terms:
+ *   out = ((v0 (x) c0  +  v1 (x) c1)  +  v2 (x) c2)  + ...
+ * (x) = precision_scalar_binary (native/src/precision/precision.cpp:196-223): scalar_role != 0 -> F32 product
+ * rounded to `dtype`; 0 -> coefficient rounded to `dtype` first; + = one add in `dtype`.
+ * v_to_x0 (:204-214) and affine_first_order (:229-239) are its two-term forms. */
+int vrb_linear_combine(const void* const* values, const float* coefficients, int terms, void* out,
+                       int dtype, int64_t count, int scalar_role, vrb_stream stream);
+
 /* SwiGLU (mochi.cpp:195-202) without the two slice copies: projected is [rows, 2*hidden],
  * out[r, j] = round(projected[r, j] * round(silu(projected[r, hidden + j]))). */
 int vrb_swiglu(const void* projected, void* out, int dtype, int64_t rows, int64_t hidden,

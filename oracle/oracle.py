@@ -460,6 +460,14 @@ def multiply_coefficient(be, policy, value, coefficient, role=SOLVER):
     return precision_scalar_binary(be, policy, role, "mul", value, scalar_f32(coefficient))
 
 
+def linear_combine(be, policy, values, coefficients, role=GUIDANCE):
+    """SamplingPrimitives::linear_combine (native/src/sampling/sampling.cpp:173-179)."""
+    result = multiply_coefficient(be, policy, values[0], coefficients[0], role)
+    for v, c in zip(values[1:], coefficients[1:]):
+        result = be.add(result, multiply_coefficient(be, policy, v, c, role))
+    return result
+
+
 def cfg_combine(be, policy, unconditional, conditional, scale):
     neg = multiply_coefficient(be, policy, unconditional, -1.0, GUIDANCE)
     diff = be.add(conditional, neg)

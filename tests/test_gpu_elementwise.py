@@ -369,3 +369,33 @@ def test_null_and_empty_arguments_are_rejected(gpu):
     assert lib.vrb_activation(0, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x.data_ptr()), 0, 0, None) == -1
     assert lib.vrb_activation(9, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x.data_ptr()), 0, 8, None) == -1
     assert lib.vrb_activation(0, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x.data_ptr()), 5, 8, None) == -2
+
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("roles", [False, True])
+@pytest.mark.parametrize("terms", [1, 2, 3, 4])
+@pytest.mark.parametrize("shape", [(16, 3, 10, 13), (1, 16, 4, 8, 16)])
+def test_linear_combine_one_pass(orc, gpu, dt, roles, terms, shape):
+    """linear_combine (and its two-term uses v_to_x0 / affine_first_order) in one launch: bit for bit
+    against the oracle's operator chain and against this library's own chain, under the legacy and
+    the declared-role scalar contracts."""
+    import torch
+    be, ops = gpu
+    from vrhino_b200 import synth
+    coefs = [0.877877295, -0.4786229, 1.5, -0.0625][:terms]
+    vals = [orc.tensor(synth.normal(shape, seed=20 + t), dt) for t in range(terms)]
+    obe = orc.OracleBackend(execution_dtype=dt)
+    opol = orc.Policy.fp32() if dt == "f32" else orc.Policy()
+    pol = ops.Policy.fp32() if dt == "f32" else ops.Policy()
+    if roles:
+        opol = opol.with_scalar_roles({orc.GUIDANCE})
+        pol = pol.with_scalar_roles({ops.GUIDANCE})
+    want = orc.linear_combine(obe, opol, vals, coefs)
+    tv = [to_torch(v) for v in vals]
+    be2 = ops.B200Backend(execution_dtype=torch.float32 if dt == "f32" else torch.bfloat16)
+    got = ops.fused_linear_combine(be2, pol, tv, coefs)
+    assert_bits_equal(got, want, "linear_combine")
+    chain = ops.linear_combine(be2, pol, tv, coefs)
+    view = torch.int16 if dt == "bf16" else torch.int32
+    assert torch.equal(got.view(view), chain.view(view))

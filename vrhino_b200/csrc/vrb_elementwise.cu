@@ -682,6 +682,43 @@ int launch_sampler(SamplerParams q, int64_t count, cudaStream_t stream, const ch
     }
     return after_launch(what);
 }
+// linear_combine (sampling.cpp:173-179): ((v0*c0 + v1*c1) + v2*c2) + ..., every product through
+// precision_scalar_binary, every sum one add in the storage dtype.  Also v_to_x0 (:204-214) and
+// affine_first_order (:229-239), which are two-term combinations.
+constexpr int kMaxTerms = 4;
+struct CombineParams {
+    const void* value[kMaxTerms];
+    float coefficient[kMaxTerms];
+    void* out;
+    int terms, dt, role;
+};
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads) linear_combine_kernel(CombineParams q, int64_t n) {
+    constexpr int W = VEC ? 8 : 1;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float v[kMaxTerms][8];
+#pragma unroll
+        for (int t = 0; t < kMaxTerms; ++t) {
+            if (t >= q.terms) break;
+            if constexpr (VEC) load8<true>(q.value[t], q.dt, i * 8, v[t]);
+            else v[t][0] = load1(q.value[t], q.dt, i);
+        }
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < W; ++e) {
+            y[e] = coef_mul(q.dt, q.role, v[0][e], q.coefficient[0]);
+#pragma unroll
+            for (int t = 1; t < kMaxTerms; ++t) {
+                if (t >= q.terms) break;
+                y[e] = round_to(q.dt, __fadd_rn(y[e], coef_mul(q.dt, q.role, v[t][e], q.coefficient[t])));
+            }
+        }
+        if constexpr (VEC) store8(q.out, q.dt, i * 8, y);
+        else store1(q.out, q.dt, i, y[0]);
+    }
+}
+
 // The Euler coefficient: k = delta (x) (+-1) is itself a product on a one-element F32 tensor
 // (exact), so k = +-delta in F32 for both scalar contracts.
 inline float euler_coefficient(float delta, int subtract) { return subtract ? -delta : delta; }
@@ -690,6 +727,31 @@ inline float euler_coefficient(float delta, int subtract) { return subtract ? -d
 }  // namespace vrb
 
 using namespace vrb;
+
+extern "C" int vrb_linear_combine(const void* const* values, const float* coefficients, int terms, void* out, int dtype,
+                                  int64_t count, int scalar_role, vrb_stream stream) {
+    VRB_REQUIRE(values && coefficients && out, VRB_ERR_INVALID, "linear_combine: null argument");
+    VRB_REQUIRE(terms >= 1 && terms <= kMaxTerms, VRB_ERR_INVALID, "linear combine arity mismatch");
+    VRB_REQUIRE(count > 0, VRB_ERR_INVALID, "linear_combine: empty tensor");
+    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "linear_combine: dtype must be F32 or BF16");
+    CombineParams q{};
+    bool vec = vec8_ok(count, {out});
+    for (int t = 0; t < terms; ++t) {
+        VRB_REQUIRE(values[t], VRB_ERR_INVALID, "linear_combine: null tensor");
+        q.value[t] = values[t];
+        q.coefficient[t] = coefficients[t];
+        vec = vec && aligned16(values[t]);
+    }
+    q.out = out; q.terms = terms; q.dt = dtype; q.role = scalar_role ? 1 : 0;
+    cudaStream_t s = as_stream(stream);
+    if (vec) {
+        const int64_t chunks = count / 8;
+        linear_combine_kernel<true><<<grid_for((chunks + kThreads - 1) / kThreads, kPerSm), kThreads, 0, s>>>(q, chunks);
+    } else {
+        linear_combine_kernel<false><<<grid_for((count + kThreads - 1) / kThreads, kPerSm), kThreads, 0, s>>>(q, count);
+    }
+    return after_launch("linear_combine");
+}
 
 extern "C" int vrb_cast(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t count, vrb_stream stream) {
     if (src_dtype == VRB_U8) {

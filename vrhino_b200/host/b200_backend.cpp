@@ -568,6 +568,25 @@ Tensor B200Backend::swiglu(const Tensor& raw) {
     });
 }
 
+Tensor B200Backend::linear_combine(const std::vector<Tensor>& values, const std::vector<float>& coefficients,
+                                   bool declared_role) {
+    return guarded([&] {
+        require(!values.empty() && values.size() == coefficients.size() && values.size() <= 4, "linear combine arity mismatch");
+        const DType dtype = operand_dtype(values[0]);
+        std::vector<Tensor> device;
+        std::vector<const void*> pointers;
+        for (const Tensor& v : values) {
+            device.push_back(copy_to_device(v, dtype));
+            require(device.back().shape() == device.front().shape(), "Incompatible broadcast shapes");
+            pointers.push_back(device.back().data());
+        }
+        Tensor out = rt_->allocate_device(device.front().shape(), dtype);
+        check(vrb_linear_combine(pointers.data(), coefficients.data(), static_cast<int>(values.size()), out.data(), code(dtype),
+                                 out.numel(), declared_role ? 1 : 0, kLegacyStream));
+        return out;
+    });
+}
+
 Tensor B200Backend::cfg_euler(const Tensor& sample_raw, const Tensor& u_raw, const Tensor& c_raw, float guidance,
                               float delta, bool subtract_prediction, bool guidance_role, bool solver_role) {
     return guarded([&] {

@@ -88,6 +88,9 @@ public:
     Tensor group_norm_silu(const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps);
     // x [B, C, T, H, W]: statistics per (batch entry, frame, group), no permutes
     Tensor group_norm_frames(const Tensor& x, int groups, const Tensor* weight, const Tensor* bias, float eps, bool silu);
+    // SamplingPrimitives::linear_combine (sampling.cpp:173-179; also v_to_x0, affine_first_order) in one
+    // kernel, 1..4 terms; declared_role: the policy declares the coefficient's scalar role
+    Tensor linear_combine(const std::vector<Tensor>& values, const std::vector<float>& coefficients, bool declared_role);
     Tensor cfg_euler(const Tensor& sample, const Tensor& unconditional, const Tensor& conditional,
                      float guidance, float delta, bool subtract_prediction, bool guidance_role, bool solver_role);
 

@@ -671,6 +671,31 @@ def fused_euler_update(be, policy, sample, prediction, delta, subtract_predictio
     return out
 
 
+def linear_combine(be, policy, values, coefficients, role=GUIDANCE):
+    """SamplingPrimitives::linear_combine (native/src/sampling/sampling.cpp:173-179) operator by operator."""
+    result = precision_scalar_binary(be, policy, role, values[0], coefficients[0])
+    for v, c in zip(values[1:], coefficients[1:]):
+        result = be.add(result, precision_scalar_binary(be, policy, role, v, c))
+    return result
+
+
+def fused_linear_combine(be, policy, values, coefficients, role=GUIDANCE, out=None):
+    """linear_combine / v_to_x0 / affine_first_order (sampling.cpp:173-179, 204-214, 229-239) in one pass,
+    1..4 terms of one shape and dtype."""
+    if not values or len(values) != len(coefficients) or len(values) > 4:
+        raise VrbError("linear combine arity mismatch")
+    first = _dense(values[0])
+    for v in values:
+        if v.dtype != first.dtype or tuple(v.shape) != tuple(first.shape):
+            raise VrbError("Incompatible broadcast shapes")
+    out = _result(out, first.shape, first.dtype, first.device)
+    pointers = (ctypes.c_void_p * len(values))(*[_dense(v).data_ptr() for v in values])
+    coefs = (ctypes.c_float * len(values))(*[float(c) for c in coefficients])
+    call("vrb_linear_combine", ctypes.cast(pointers, ctypes.c_void_p), ctypes.cast(coefs, ctypes.c_void_p), len(values),
+         _ptr(out), _code(out), out.numel(), int(role in policy.scalar_roles), _stream())
+    return out
+
+
 def fused_flow_to_x0(be, policy, sample, model_output, sigma):
     out = torch.empty_like(sample)
     call("vrb_flow_to_x0", _ptr(_dense(sample)), _ptr(_dense(model_output)), _ptr(out), _code(out), out.numel(),
