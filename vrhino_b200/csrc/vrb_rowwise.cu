@@ -121,6 +121,7 @@ bool launch_by_dtype(const RowParams& p, int geometry, int64_t ctas, size_t smem
     if (p.pre_branch != nullptr) {   // fused residual update: bf16 stream, LayerNorm, no / staged / plain modulate
         if constexpr (NORM == kNormLayer && (POST == kPostNone || POST == kPostModulate || POST == kPostModulateStaged)) {
             if (x_bf16 && n_bf16) { launch_row_variant<NORM, POST, kBf16Bf16Pre>(p, geometry, ctas, smem, s); return true; }
+            if (!x_bf16 && !n_bf16) { launch_row_variant<NORM, POST, kF32Pre>(p, geometry, ctas, smem, s); return true; }
         }
         return false;
     }
@@ -200,7 +201,8 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
     // The fused residual update with a modulating epilogue runs three CTAs per SM: smaller budget,
     // its gate vectors included.
     const bool pre = p.pre_branch != nullptr;
-    const size_t gate_bytes = pre && p.pre_gate ? static_cast<size_t>(p.pre_vectors) * (region / 2) : 0;
+    // gate vectors: bf16 pairs for a bf16 stream, F32 for an F32 stream
+    const size_t gate_bytes = pre && p.pre_gate ? static_cast<size_t>(p.pre_vectors) * (p.x_dt == VRB_BF16 ? region / 2 : region) : 0;
     if (gate_bytes > 48 * 1024) return kPreNotFused;
     const size_t budget = (pre && post != kPostNone ? 72 * 1024 : 100 * 1024) - gate_bytes;
     if (post == kPostModulate && p.vectors >= 1 && p.vectors <= 4 && sub == 1 &&
@@ -297,9 +299,10 @@ extern "C" int vrb_gated_residual_layer_norm_modulate(
                 VRB_ERR_UNSUPPORTED, "layer_norm: weight/bias must be F32 or BF16");
     if (gate) { if (int rc = check_vectors("gated_residual_layer_norm", gate_rows_per_vector, gate_vectors)) return rc; }
     if (scale) { if (int rc = check_vectors("gated_residual_layer_norm", rows_per_vector, mod_vectors)) return rc; }
-    if (residual_dtype == VRB_BF16 && branch_dtype == VRB_BF16 && state_dtype == VRB_BF16) {
+    // one pass for a bf16 stream, and for the production contract (F32 stream, bf16 branch)
+    if (branch_dtype == VRB_BF16 && residual_dtype == state_dtype) {
         RowParams p = blank();
-        p.x = residual; p.x_dt = p.norm_out_dt = VRB_BF16; p.out = out; p.out_dt = out_dtype;
+        p.x = residual; p.x_dt = p.norm_out_dt = residual_dtype; p.out = out; p.out_dt = out_dtype;
         p.pre_branch = branch; p.pre_gate = gate; p.pre_gate_dt = gate_dtype; p.state_out = state_out;
         p.pre_rows_per_vector = gate ? gate_rows_per_vector : 1; p.pre_vectors = gate ? gate_vectors : 0;
         p.weight = weight; p.w_dt = weight_dtype; p.bias = bias; p.b_dt = bias_dtype;

@@ -50,7 +50,9 @@ enum Post {
 // kBf16Bf16Pre: like kBf16Bf16, but the row the norm sees is first COMPUTED as the bf16 gated
 // residual  state = residual + branch * gate  (common.cpp:134-144 in a bf16 residual stream) and
 // stored to state_out -- the residual update and the norm that follows it in one pass.
-enum DtClass { kF32F32 = 0, kBf16Bf16 = 1, kBf16F32 = 2, kBf16Bf16Pre = 3 };
+enum DtClass { kF32F32 = 0, kBf16Bf16 = 1, kBf16F32 = 2, kBf16Bf16Pre = 3, kF32Pre = 4 };
+// kF32Pre: like kBf16Bf16Pre with an F32 residual stream (the production contract): x F32, branch bf16,
+// gate in F32, the updated stream stored F32, then the kF32F32 norm.
 
 struct RowParams {
     const void* x; void* out;
@@ -188,7 +190,7 @@ __host__ __device__ constexpr bool pre_prefetches(int nch, bool full, int post) 
     return prefetches(nch, true, full) && post == kPostNone;
 }
 __host__ __device__ constexpr int min_ctas_per_sm(int nch, bool x_bf16, bool full, bool pre = false, int post = kPostNone) {
-    if (pre && full && prefetches(nch, true, full) && !pre_prefetches(nch, full, post)) return 3;
+    if (pre && x_bf16 && full && prefetches(nch, true, full) && !pre_prefetches(nch, full, post)) return 3;
     const int sets = (prefetches(nch, x_bf16, full) ? 2 : 1) + (pre ? 1 : 0);
     const int row_regs = packed_regs(nch, x_bf16) * sets;
     return row_regs <= 16 ? 4 : row_regs <= 32 ? 3 : 2;
@@ -198,12 +200,14 @@ __host__ __device__ constexpr int min_ctas_per_sm(int nch, bool x_bf16, bool ful
 // TPR > 0 with FULL means the row is exactly NCH * TPR chunks wide, so chunk offsets are
 // compile-time constants and no chunk needs a bounds test (the production widths).
 template <int NCH, int TPR, bool FULL, int NORM, int POST, int DT>
-__global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F32, FULL, DT == kBf16Bf16Pre, POST))
+__global__ void __launch_bounds__(kRowThreads, min_ctas_per_sm(NCH, DT != kF32F32 && DT != kF32Pre, FULL,
+                                                              DT == kBf16Bf16Pre || DT == kF32Pre, POST))
 row_kernel(const RowParams p) {
-    constexpr bool X_BF16 = DT != kF32F32;
-    constexpr bool PRE = DT == kBf16Bf16Pre;
-    constexpr bool PF = PRE ? pre_prefetches(NCH, FULL, POST) : prefetches(NCH, X_BF16, FULL);
-    constexpr bool N_BF16 = DT == kBf16Bf16 || PRE;   // the unfused norm operator would store bf16
+    constexpr bool X_BF16 = DT != kF32F32 && DT != kF32Pre;
+    constexpr bool PRE = DT == kBf16Bf16Pre || DT == kF32Pre;
+    constexpr bool PRE_F32 = DT == kF32Pre;
+    constexpr bool PF = PRE ? (X_BF16 && pre_prefetches(NCH, FULL, POST)) : prefetches(NCH, X_BF16, FULL);
+    constexpr bool N_BF16 = DT == kBf16Bf16 || DT == kBf16Bf16Pre;   // the unfused norm operator would store bf16
     constexpr bool kStaged = POST == kPostModulateStaged;
     constexpr bool kModulate = POST == kPostModulate || kStaged;
     constexpr bool kRope = POST == kPostRope || POST == kPostRopeShared;
@@ -255,7 +259,18 @@ row_kernel(const RowParams p) {
     uint32_t* const s_gate = reinterpret_cast<uint32_t*>(s_mod + (kStaged ? static_cast<int>(p.vectors) * 2 * pad : 0));
     const bool has_pre_gate = PRE && p.pre_gate != nullptr;
     if constexpr (PRE) {
-        if (has_pre_gate) {
+        if (has_pre_gate && PRE_F32) {
+            // F32 stream: the gate stays F32, in the modulation vectors' layout, vector v at s_gate + v * pad
+            float* const gate_f32 = reinterpret_cast<float*>(s_gate);
+            const int gate_vectors = static_cast<int>(p.pre_vectors);
+            for (int cv = threadIdx.x; cv < width * gate_vectors; cv += kRowThreads) {
+                const int v = cv / width, c = cv - v * width;
+                const int chunk = c >> 3, e = c & 7, i = chunk / tpr, l = chunk - i * tpr;
+                gate_f32[v * pad + (((i * 2 + (e >> 2)) * tpr + l) << 2) + (e & 3)] =
+                    load1(p.pre_gate, p.pre_gate_dt, static_cast<int64_t>(v) * p.width + c);
+            }
+            __syncthreads();
+        } else if (has_pre_gate) {
             const int gate_vectors = static_cast<int>(p.pre_vectors);
             for (int cv = threadIdx.x; cv < (width / 2) * gate_vectors; cv += kRowThreads) {
                 const int v = cv / (width / 2), pair = cv - v * (width / 2);
@@ -292,12 +307,12 @@ row_kernel(const RowParams p) {
         for (int i = 0; i < NCH; ++i) {
             const int chunk = lane_in_row + i * tpr;
             const bool here = ok && (FULL || chunk < nchunks);
-            res[i] = here ? load_packed<true>(p.x, off + chunk * 8) : zero_packed<true>();
+            if constexpr (!PRE_F32) res[i] = here ? load_packed<true>(p.x, off + chunk * 8) : zero_packed<true>();
             br[i] = here ? load_packed<true>(p.pre_branch, off + chunk * 8) : zero_packed<true>();
         }
     };
     Packed<X_BF16> xr[NCH];
-    Packed<true> raw_res[PRE ? NCH : 1], raw_br[PRE ? NCH : 1];   // PRE: the row being combined next
+    Packed<true> raw_res[(PRE && !PRE_F32) ? NCH : 1], raw_br[PRE ? NCH : 1];   // PRE: the row being combined next
     if constexpr (PRE) {
         if constexpr (PF) load_raw(blockIdx.x * rows_per_cta, raw_res, raw_br);
     } else if constexpr (PF) {
@@ -310,7 +325,45 @@ row_kernel(const RowParams p) {
         const int64_t row_offset = static_cast<int64_t>(nrow) * width;
 
         Packed<X_BF16> xn[(PF && !PRE) ? NCH : 1];
-        if constexpr (PRE) {
+        if constexpr (PRE_F32) {
+            // F32 stream: state = residual + F32(branch) * gate, product and sum each rounded once in F32
+            // (common.cpp:134-144 with T = F32), stored F32 and normalised from the registers
+            load_row(base, xr);
+            (void)raw_res;
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) {
+                const int chunk = lane_in_row + i * tpr;
+                const bool here = valid && (FULL || chunk < nchunks);
+                raw_br[i] = here ? load_packed<true>(p.pre_branch, row_offset + chunk * 8) : zero_packed<true>();
+            }
+            unsigned gate_base = 0;
+            if (has_pre_gate && p.pre_vectors > 1)
+                gate_base = ((nrow / static_cast<unsigned>(p.pre_rows_per_vector)) % static_cast<unsigned>(p.pre_vectors)) *
+                            static_cast<unsigned>(pad);
+            const float* const gate_f32 = reinterpret_cast<const float*>(s_gate) + gate_base;
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) {
+                const int chunk = lane_in_row + i * tpr;
+                if (!FULL && chunk >= nchunks) continue;
+                const uint32_t bw[4] = {raw_br[i].r.x, raw_br[i].r.y, raw_br[i].r.z, raw_br[i].r.w};
+                float b[8];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { b[2 * k] = __uint_as_float(bw[k] << 16); b[2 * k + 1] = __uint_as_float(bw[k] & 0xffff0000u); }
+                if (has_pre_gate) {
+                    const float4 g0 = *reinterpret_cast<const float4*>(gate_f32 + (((i * 2) * tpr + lane_in_row) << 2));
+                    const float4 g1 = *reinterpret_cast<const float4*>(gate_f32 + (((i * 2 + 1) * tpr + lane_in_row) << 2));
+                    b[0] = __fmul_rn(b[0], g0.x); b[1] = __fmul_rn(b[1], g0.y); b[2] = __fmul_rn(b[2], g0.z); b[3] = __fmul_rn(b[3], g0.w);
+                    b[4] = __fmul_rn(b[4], g1.x); b[5] = __fmul_rn(b[5], g1.y); b[6] = __fmul_rn(b[6], g1.z); b[7] = __fmul_rn(b[7], g1.w);
+                }
+                xr[i].a = make_float4(__fadd_rn(xr[i].a.x, b[0]), __fadd_rn(xr[i].a.y, b[1]), __fadd_rn(xr[i].a.z, b[2]), __fadd_rn(xr[i].a.w, b[3]));
+                xr[i].b = make_float4(__fadd_rn(xr[i].b.x, b[4]), __fadd_rn(xr[i].b.y, b[5]), __fadd_rn(xr[i].b.z, b[6]), __fadd_rn(xr[i].b.w, b[7]));
+                if (valid) {
+                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.state_out) + row_offset + chunk * 8);
+                    __stcs(dst, xr[i].a);
+                    __stcs(dst + 1, xr[i].b);
+                }
+            }
+        } else if constexpr (PRE) {
             if constexpr (!PF) load_raw(base, raw_res, raw_br);
             // state = residual + branch * gate in packed bf16 (two roundings, as the reference's
             // F32 multiply and add each followed by the bf16 store), written back as the new stream

@@ -104,10 +104,10 @@ class WanBlock:
                 Launch("A ln_modulate", A, act * (hb + 2) + 2 * vec),
                 Launch("B rms_rope q", Bq, act * 4 + vec + table // 2),
                 Launch("B rms_rope k", Bk, act * 4 + vec + table // 2),
-                Launch("C+D gated_residual ln_affine", CD, act * (hb + 2 + hb + 2) + 3 * vec, 1 if hb == 2 else 2),
+                Launch("C+D gated_residual ln_affine", CD, act * (hb + 2 + hb + 2) + 3 * vec),
                 Launch("E rms cross q", Eq, act * 4 + vec),
                 Launch("E rms cross k", Ek, self.cross_k.numel() * 4 + vec),
-                Launch("F+G residual_add ln_modulate", FG, act * (hb + 2 + hb + 2) + 2 * vec, 1 if hb == 2 else 2),
+                Launch("F+G residual_add ln_modulate", FG, act * (hb + 2 + hb + 2) + 2 * vec),
                 Launch("H gelu_tanh", H, self.ffn_hidden.numel() * 4),
                 Launch("I gated_residual", I, act * (hb + 2 + hb) + vec),
             ]
