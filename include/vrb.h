@@ -223,6 +223,19 @@ int vrb_gated_residual_layer_norm_modulate(
     const void* scale, const void* shift, int mod_dtype, int64_t rows_per_vector, int64_t mod_vectors,
     void* out, int out_dtype, int64_t rows, int64_t width, float eps, vrb_stream stream);
 
+/* The same merge for the LTX block, whose next norm is RMSNorm without a weight
+ * (native/src/architectures/ltx.cpp:100-151; ltx_self_attention_graph.cpp:30-44):
+ *   state = vrb_gated_residual(residual, branch, gate);  out = vrb_rms_norm_modulate(state, scale, shift). */
+int vrb_gated_residual_rms_norm_modulate(const void* residual, int residual_dtype,
+                                         const void* branch, int branch_dtype,
+                                         const void* gate, int gate_dtype,
+                                         int64_t gate_rows_per_vector, int64_t gate_vectors,
+                                         void* state_out, int state_dtype,
+                                         const void* scale, const void* shift, int mod_dtype,
+                                         int64_t rows_per_vector, int64_t mod_vectors,
+                                         void* out, int out_dtype, int64_t rows, int64_t width,
+                                         float eps, vrb_stream stream);
+
 /* layer_norm (:4057) -> modulate (native/src/architectures/common.cpp:51-61) -> cast to
  * out_dtype (the consumer cast, :3674).  scale/shift are [mod_vectors, width]; row r uses
  * vector (r / rows_per_vector) % mod_vectors.  shift may be NULL.  weight/bias may be NULL. */

@@ -288,3 +288,36 @@ def test_gated_residual_layer_norm_one_pass(orc, gpu, width, batch, tokens, gate
     want = obe.cast(orc.modulate(obe, opol, normed, shift, scale), "bf16") if mode == "modulate" else obe.cast(normed, "bf16")
     flips = dict(flip_atol=2.0 ** -8 * 8.0, flip_frac=2e-3)
     assert_close(orc, got_norm, want, rel=1e-5, atol=2e-6, what="norm after residual update", **flips)
+
+
+
+@pytest.mark.parametrize("width,batch,tokens", [(2048, 2, 9), (2048, 1, 5), (1536, 3, 4), (264, 1, 7), (24, 2, 5)])
+@pytest.mark.parametrize("gated", [True, False])
+@pytest.mark.parametrize("state", ["bf16", "f32"])
+def test_gated_residual_rms_norm_modulate_one_pass(orc, gpu, width, batch, tokens, gated, state):
+    """The LTX form (residual update + RMSNorm without weight + modulate): bit-identical to this
+    library's two launches, the updated stream bit-exact and the output within tolerance of the
+    oracle's unfused chain."""
+    import torch
+    be, ops = gpu
+    from vrhino_b200 import synth
+    obe = orc.OracleBackend()
+    opol = orc.Policy.unqualified_default("bf16") if state == "bf16" else orc.Policy.fp32()
+    pol = ops.Policy.unqualified_default(torch.bfloat16) if state == "bf16" else ops.Policy.fp32()
+    shape = (batch, tokens, width)
+    res = orc.tensor(synth.normal(shape, seed=width + 1), state)
+    branch = orc.tensor(synth.normal(shape, seed=width + 2), "bf16")
+    gate = orc.tensor(synth.normal((batch, 1, width), std=0.3, seed=3)) if gated else None
+    shift = orc.tensor(synth.normal((batch, 1, width), std=0.1, seed=6))
+    scale = orc.tensor(synth.normal((batch, 1, width), std=0.1, seed=7))
+    T = lambda t: None if t is None else to_torch(t)
+    got_state, got_norm = ops.fused_gated_residual_rms_norm_modulate(be, pol, T(res), T(branch), T(gate), 1e-6, T(shift), T(scale))
+    sep_state = ops.fused_gated_residual(be, pol, T(res), T(branch), T(gate))
+    sep_norm = ops.fused_rms_norm_modulate(be, sep_state, 1e-6, T(shift), T(scale))
+    bits = lambda t: t.view(torch.int16 if t.dtype == torch.bfloat16 else torch.int32)
+    assert torch.equal(bits(got_state), bits(sep_state))
+    assert torch.equal(bits(got_norm), bits(sep_norm))
+    want_state = orc.gated_residual(obe, opol, res, branch, gate) if gated else orc.residual_add(obe, opol, res, branch)
+    assert_bits_equal(got_state, want_state, "state")
+    want = obe.cast(orc.modulate(obe, opol, obe.rms_norm(want_state, None, 1e-6), shift, scale), "bf16")
+    assert_close(orc, got_norm, want, rel=1e-5, atol=2e-6, what="rms norm after residual update", flip_atol=2.0 ** -8 * 8.0, flip_frac=2e-3)

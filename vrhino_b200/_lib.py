@@ -52,6 +52,8 @@ SIGNATURES = {
     "vrb_group_norm_apply": [_vp, _i, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i, _vp, _vp, _i, _vp],
     "vrb_group_norm_apply_scatter": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _vp, _vp, _i, _vp],
     "vrb_layer_norm_modulate": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i64, _i64, _vp, _i, _i64, _i64, _f, _vp],
+    "vrb_gated_residual_rms_norm_modulate": [_vp, _i, _vp, _i, _vp, _i, _i64, _i64, _vp, _i, _vp, _vp, _i, _i64, _i64,
+                                             _vp, _i, _i64, _i64, _f, _vp],
     "vrb_gated_residual_layer_norm_modulate": [_vp, _i, _vp, _i, _vp, _i, _i64, _i64, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i64, _i64,
                                                _vp, _i, _i64, _i64, _f, _vp],
     "vrb_layer_norm_cast": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i64, _i64, _f, _vp],

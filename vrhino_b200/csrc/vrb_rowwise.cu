@@ -123,6 +123,10 @@ bool launch_by_dtype(const RowParams& p, int geometry, int64_t ctas, size_t smem
             if (x_bf16 && n_bf16) { launch_row_variant<NORM, POST, kBf16Bf16Pre>(p, geometry, ctas, smem, s); return true; }
             if (!x_bf16 && !n_bf16) { launch_row_variant<NORM, POST, kF32Pre>(p, geometry, ctas, smem, s); return true; }
         }
+        if constexpr (NORM == kNormRms && (POST == kPostModulate || POST == kPostModulateStaged)) {   // the LTX block's form
+            if (x_bf16 && n_bf16) { launch_row_variant<NORM, POST, kBf16Bf16Pre>(p, geometry, ctas, smem, s); return true; }
+            if (!x_bf16 && !n_bf16) { launch_row_variant<NORM, POST, kF32Pre>(p, geometry, ctas, smem, s); return true; }
+        }
         return false;
     }
     if (!x_bf16 && !n_bf16) { launch_row_variant<NORM, POST, kF32F32>(p, geometry, ctas, smem, s); return true; }
@@ -372,6 +376,36 @@ extern "C" int vrb_rms_norm_modulate(const void* x, int x_dtype, const void* sca
     set_rms(p, rows);
     p.post = kPostModulate;
     return launch_rows(p, as_stream(stream), "rms_norm_modulate");
+}
+
+extern "C" int vrb_gated_residual_rms_norm_modulate(
+        const void* residual, int residual_dtype, const void* branch, int branch_dtype,
+        const void* gate, int gate_dtype, int64_t gate_rows_per_vector, int64_t gate_vectors,
+        void* state_out, int state_dtype,
+        const void* scale, const void* shift, int mod_dtype, int64_t rows_per_vector, int64_t mod_vectors,
+        void* out, int out_dtype, int64_t rows, int64_t width, float eps, vrb_stream stream) {
+    VRB_REQUIRE(residual && branch && state_out && out, VRB_ERR_INVALID, "gated_residual_rms_norm: null tensor");
+    VRB_REQUIRE(scale != nullptr, VRB_ERR_INVALID, "gated_residual_rms_norm: scale is null");
+    if (gate) { if (int rc = check_vectors("gated_residual_rms_norm", gate_rows_per_vector, gate_vectors)) return rc; }
+    if (int rc = check_vectors("gated_residual_rms_norm", rows_per_vector, mod_vectors)) return rc;
+    if (branch_dtype == VRB_BF16 && residual_dtype == state_dtype) {
+        RowParams p = blank();
+        p.x = residual; p.x_dt = p.norm_out_dt = residual_dtype; p.out = out; p.out_dt = out_dtype;
+        p.pre_branch = branch; p.pre_gate = gate; p.pre_gate_dt = gate_dtype; p.state_out = state_out;
+        p.pre_rows_per_vector = gate ? gate_rows_per_vector : 1; p.pre_vectors = gate ? gate_vectors : 0;
+        p.scale = scale; p.shift = shift; p.mod_dt = mod_dtype;
+        p.rows_per_vector = rows_per_vector; p.vectors = mod_vectors;
+        p.rows = rows; p.width = p.norm_width = width; p.eps = eps;
+        set_rms(p, rows);
+        p.post = kPostModulate;
+        const int rc = launch_rows(p, as_stream(stream), "gated_residual_rms_norm");
+        if (rc != kPreNotFused) return rc;
+    }
+    if (int rc = vrb_gated_residual(residual, residual_dtype, branch, branch_dtype, gate, gate_dtype, gate_rows_per_vector,
+                                    gate_vectors, state_out, state_dtype, rows, width, stream))
+        return rc;
+    return vrb_rms_norm_modulate(state_out, state_dtype, scale, shift, mod_dtype, rows_per_vector, mod_vectors, out, out_dtype,
+                                 rows, width, eps, stream);
 }
 
 extern "C" int vrb_rms_norm_scale(const void* x, int dtype, const void* scale, int scale_dtype,

@@ -374,7 +374,7 @@ row_kernel(const RowParams p) {
 #pragma unroll
             for (int i = 0; i < NCH; ++i) {
                 const int chunk = lane_in_row + i * tpr;
-                if (!FULL && chunk >= nchunks) continue;
+                if (!FULL && chunk >= nchunks) { xr[i] = zero_packed<X_BF16>(); continue; }   // statistics see zeros there
                 const uint32_t rw[4] = {raw_res[i].r.x, raw_res[i].r.y, raw_res[i].r.z, raw_res[i].r.w};
                 const uint32_t bw[4] = {raw_br[i].r.x, raw_br[i].r.y, raw_br[i].r.z, raw_br[i].r.w};
                 uint4 gw = make_uint4(0, 0, 0, 0);

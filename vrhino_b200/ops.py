@@ -547,6 +547,27 @@ def fused_gated_residual_layer_norm(be, policy, residual, branch, gate, weight, 
     return state, normed
 
 
+def fused_gated_residual_rms_norm_modulate(be, policy, residual, branch, gate, eps, shift, scale, out_dtype=BF16,
+                                           state_out=None, out=None):
+    """The LTX block's residual update and its next RMSNorm (no weight) -> modulate
+    (native/src/architectures/ltx.cpp:100-151), one pass when the branch is bf16 and the stream keeps its dtype.
+    Returns (state, normed)."""
+    residual, branch = _dense(residual), _dense(branch)
+    width = residual.shape[-1]
+    rows = residual.numel() // width
+    grpv, gvec = (1, 1) if gate is None else _vec_layout(rows, residual.shape, gate)
+    mrpv, mvec = _vec_layout(rows, residual.shape, scale)
+    if shift is not None and (shift.dtype != scale.dtype or shift.numel() != scale.numel()):
+        raise VrbError("modulate: shift and scale must share dtype and shape")
+    state = _result(state_out, residual.shape, policy.residual, residual.device)
+    normed = _result(out, residual.shape, out_dtype, residual.device)
+    call("vrb_gated_residual_rms_norm_modulate", _ptr(residual), _code(residual), _ptr(branch), _code(branch),
+         _ptr(gate), _code(gate) if gate is not None else 0, grpv, gvec, _ptr(state), _code(policy.residual),
+         _ptr(_dense(scale)), _ptr(shift), _code(scale), mrpv, mvec, _ptr(normed), _code(out_dtype), rows, width,
+         ctypes.c_float(eps), _stream())
+    return state, normed
+
+
 def fused_rms_norm_gated_residual(be, policy, residual, branch, bounded_gate, eps=1e-6, out=None):
     """gated_residual(residual, rms_norm(branch, None, eps), bounded_gate) -- mochi.cpp:204-211
     after the tanh on the [B, D] gate."""
