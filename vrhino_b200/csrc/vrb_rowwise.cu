@@ -188,6 +188,7 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
         case 5120: geometry = kExact5120; tpr = 128; break;
         case 2048: geometry = kExact2048; tpr = 64; break;
         case 128: geometry = kExact128; tpr = 8; break;
+        case 64: geometry = kExact64; tpr = 8; break;
         default: break;
     }
     p.tpr = tpr;

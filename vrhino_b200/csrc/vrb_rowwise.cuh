@@ -657,6 +657,7 @@ enum Geometry {
     kExact5120 = 9,      // 5 chunks x 128 threads  (Wan2.2-A14B)
     kExact2048 = 10,     // 4 chunks x 64 threads   (LTX)
     kExact128 = 11,      // 2 chunks x 8 threads    (per-head q/k norm)
+    kExact64 = 12,       // 1 chunk x 8 threads     (per-head q/k norm over 64: CogVideoX)
 };
 
 // Launches the row_kernel instantiation for `geometry`; one definition per (NORM, POST, DT)

@@ -61,6 +61,7 @@ void launch_one(const RowParams& p, int64_t ctas, size_t smem, cudaStream_t stre
             case kExact3072: launch_one<6, 64, true, NORM, POST, DT>(p, ctas, smem, s); break;                       \
             case kExact5120: launch_one<5, 128, true, NORM, POST, DT>(p, ctas, smem, s); break;                      \
             case kExact2048: launch_one<4, 64, true, NORM, POST, DT>(p, ctas, smem, s); break;                       \
+            case kExact64: launch_one<1, 8, true, NORM, POST, DT>(p, ctas, smem, s); break;                          \
             default: launch_one<2, 8, true, NORM, POST, DT>(p, ctas, smem, s); break;                                \
         }                                                                                                            \
     }
