@@ -333,7 +333,7 @@ template <bool RES_BF16, bool BR_BF16, bool STATE_BF16>
 __global__ void __launch_bounds__(kThreads) gated_residual_typed_kernel(
         const void* __restrict__ res, const void* __restrict__ branch, const void* __restrict__ gate, int gate_dt,
         void* __restrict__ out, unsigned total, unsigned width_chunks, unsigned rows_per_vector, unsigned vectors) {
-    constexpr int U = 2;
+        constexpr int U = 2;
     const unsigned stride = gridDim.x * blockDim.x;
     for (unsigned i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
         if constexpr (RES_BF16 && BR_BF16 && STATE_BF16) {
