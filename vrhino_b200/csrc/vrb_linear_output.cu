@@ -117,7 +117,9 @@ __global__ void __launch_bounds__(kThreads) linear_output_gated_typed_kernel(
         const float4* __restrict__ accumulation, const uint4* __restrict__ bias, const void* __restrict__ residual,
         const void* __restrict__ gate, int gate_dt, void* __restrict__ out, unsigned total, unsigned width_chunks,
         unsigned rows_per_vector, unsigned vectors) {
-    constexpr int U = 2;
+        // work items per thread and iteration, measured: with a bf16 stream one item (four to five 16-byte loads
+    // in flight already) beats two by 15 %; with an F32 stream two items beat one by 7 %
+    constexpr int U = (RES_BF16 && STATE_BF16) ? 1 : 2;
     const unsigned stride = gridDim.x * blockDim.x;
     const bool has_bias = bias != nullptr, has_gate = gate != nullptr;
     for (unsigned i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
