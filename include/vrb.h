@@ -2,10 +2,17 @@
  * vrb.h -- C ABI of the B200 (sm_100a) non-GEMM operator library for the vrhino runtime.
  *
  * This is the boundary a vrhino::Backend implementation binds to: every entry point takes
- * raw DEVICE pointers, sizes and a CUDA stream, allocates nothing, launches asynchronously
- * on the given stream and returns 0 or a negative vrb_status (text via vrb_last_error()).
- * The *_host entry points at the end take HOST pointers instead and stage through device
- * buffers the library owns.
+ * raw DEVICE pointers, sizes and a CUDA stream, allocates nothing, never synchronises, launches
+ * asynchronously on the given stream and returns 0 or a negative vrb_status (text via
+ * vrb_last_error()).  The *_host entry points at the end take HOST pointers instead and stage
+ * through device buffers the library owns; they are the only ones that allocate
+ * (vrb_device_allocation_count() counts their cudaMalloc calls).
+ *
+ * Device memory the library's image holds on every GPU that loads it, until the process exits:
+ * seven 128 KB function tables (896 KB) used by the bf16 unary kernels on large tensors, and the
+ * ~1 MiB scratch of vrb_group_norm_fixed_scratch.  The first large bf16 call per (device,
+ * operator) launches a small kernel on the caller's stream that fills the operator's table;
+ * vrb_prepare_tables() does that for all of them ahead of time.
  *
  * Each declaration cites the reference interface it replaces; paths are inside the
  * reference project and, when no file is named, mean
@@ -54,6 +61,16 @@ int vrb_abi_version(void);
 const char* vrb_last_error(void);
 /* Number of kernels this library has launched in the process (all threads, all streams). */
 uint64_t vrb_launch_count(void);
+/* Number of device allocations (cudaMalloc) the library has made in the process.  Only the
+ * *_host entry points allocate; every other entry point leaves this count unchanged. */
+uint64_t vrb_device_allocation_count(void);
+/* Fills the current device's function tables (activation kinds, exp, sqrt as bf16 -> bf16 maps,
+ * CudaBackend::activation :4179-4188 evaluated on all 65536 inputs) on `stream`: seven small
+ * kernels, no allocation, no synchronisation.  Optional -- the operators do it on first use -- but
+ * a caller that captures its first launches into a CUDA graph should call it once per device
+ * before the capture, otherwise the captured kernels evaluate their tables themselves on every
+ * replay (same results, about 10 us slower per launch).  VRB_ERR_INVALID on a capturing stream. */
+int vrb_prepare_tables(vrb_stream stream);
 
 /* ------------------------------------------------------------------ per-operator forms -- */
 
@@ -158,9 +175,11 @@ int vrb_group_norm_frames(const void* x, int dtype, const void* weight, int weig
  * library holds about 1 MiB for it until the process exits, and it limits the call to
  * batch * groups <= VRB_GROUP_NORM_FIXED_SCRATCH_MAX_UNITS; larger problems are refused with
  * VRB_ERR_WORKSPACE and must use vrb_group_norm.  No memory is allocated or freed, here or in
- * anything it calls.  The first call on a device looks up the array's device address (one
- * runtime query with that device current); make that first call before any stream capture
- * begins.  All calls on a device share the one array, which keeps whatever the previous call
+ * anything it calls (the SiLU table of the bf16 + fuse_silu path is part of the library's device
+ * image as well).  The first call on a device looks up the array's device address (one runtime
+ * query with that device current; the address is kept per device index and does not survive
+ * cudaDeviceReset) and, for bf16 + fuse_silu on large tensors, launches the table-fill kernel
+ * ahead of the operator's own; make that first call before any stream capture begins.  All calls on a device share the one array, which keeps whatever the previous call
  * wrote; this operator overwrites every slot it later reads, so nothing needs clearing, but
  * two calls whose kernels can overlap on the GPU (different streams, no ordering between them)
  * race on it -- order them on one stream or with events. */
@@ -374,8 +393,10 @@ int vrb_cfg_euler(const void* sample, const void* unconditional, const void* con
  * device buffers the library owns on three streams, so upload, kernel and download overlap;
  * operands shared by all rows (vectors of `width`, the norm weight) are uploaded once.
  * Full overlap needs page-locked host buffers (cudaMallocHost / cudaHostRegister).
- * Synchronous: when a call returns, `out` holds the result.  These are the only entry points
- * that allocate device memory; vrb_host_release() frees it. */
+ * Synchronous: when a call returns -- with success or with an error -- no copy to or from the
+ * caller's buffers is in flight, and on success `out` holds the result.  Buffers and streams are
+ * kept per device (the device current at the call).  These are the only entry points that allocate
+ * device memory; vrb_host_release() frees the current device's. */
 
 /* vrb_layer_norm_modulate on host buffers; scale == NULL gives vrb_layer_norm_cast. */
 int vrb_host_layer_norm_modulate(const void* x, int x_dtype, const void* weight, int weight_dtype,

@@ -15,6 +15,29 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 
 
+# ---- parity record ---------------------------------------------------------------------------
+# Every tolerance comparison records what it saw: the largest bf16-ulp distance (or the largest
+# relative F32 error), how many elements exceeded the tight bound, and how many of those were
+# admitted by a stated exception clause.  With VRB_PARITY_REPORT=<path> the records are written
+# there as JSON lines at the end of the session, so "<= 2 ulp" is a measured statement.
+PARITY_RECORDS = []
+
+
+def record_parity(what, dtype, count, worst, over, admitted, clause=""):
+    PARITY_RECORDS.append({"case": what, "dtype": dtype, "elements": int(count), "worst": float(worst),
+                           "over_tight_bound": int(over), "admitted_by_clause": int(admitted), "clause": clause})
+
+
+def pytest_sessionfinish(session, exitstatus):
+    path = os.environ.get("VRB_PARITY_REPORT")
+    if path and PARITY_RECORDS:
+        import json
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        with open(path, "a") as fh:
+            for r in PARITY_RECORDS:
+                fh.write(json.dumps(r) + "\n")
+
+
 @pytest.fixture(scope="session")
 def orc():
     from oracle import oracle
@@ -76,9 +99,12 @@ def assert_close(orc, got, want, max_ulp=2, rel=1e-5, atol=0.0, flip_atol=0.0, f
     if tag == "bf16":
         d = orc.bf16_ulp_distance(data, want.data)
         bad = d > max_ulp
+        over = int(bad.sum())
         if atol > 0 and bad.any():
             diff = np.abs(orc.bf16_bits_to_f32(data) - want.f32())
             bad &= ~(diff <= atol)
+        record_parity(what, "bf16", d.size, d.max() if d.size else 0, over, over - int(bad.sum()),
+                      f"|d| <= {atol:g} absolute" if atol > 0 else "")
         if bad.any():
             i = np.unravel_index(np.argmax(np.where(bad, d, 0)), d.shape)
             raise AssertionError(f"{what}: {int(bad.sum())} of {d.size} elements differ by more than {max_ulp} bf16 ulp; "
@@ -92,10 +118,16 @@ def assert_close(orc, got, want, max_ulp=2, rel=1e-5, atol=0.0, flip_atol=0.0, f
     same_inf = np.isinf(data) & (data == want.data)
     bad = ~(diff <= tol) & ~both_nan & ~same_inf
     bad |= nan_mismatch
+    over = int(bad.sum())
+    with np.errstate(invalid="ignore", divide="ignore"):
+        finite = np.isfinite(ref) & np.isfinite(data)
+        worst_rel = float(np.max(np.where(finite, diff / np.maximum(np.abs(ref), 1e-3), 0.0))) if diff.size else 0.0
     if bad.any() and flip_frac > 0:
         within_flip = bad & (diff <= flip_atol) & ~nan_mismatch
         if bad.mean() <= flip_frac and within_flip.sum() == bad.sum():
             bad[:] = False
+    record_parity(what, "f32 (worst = relative error, floor 1e-3)", diff.size, worst_rel, over, over - int(bad.sum()),
+                  f"<= {flip_frac:g} of the elements within {flip_atol:g} (one bf16 ulp of a mid-chain value)" if flip_frac > 0 else "")
     if bad.any():
         i = np.unravel_index(np.argmax(np.where(bad, diff, 0)), diff.shape)
         raise AssertionError(f"{what}: {int(bad.sum())} of {diff.size} f32 elements out of tolerance; "

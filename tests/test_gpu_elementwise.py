@@ -162,6 +162,58 @@ def test_table_path_equals_direct_path(gpu):
     assert torch.equal(whole.view(torch.int16), parts.view(torch.int16))
 
 
+_TABLE_STATES_SCRIPT = r"""
+import ctypes, sys, torch
+sys.path.insert(0, sys.argv[1])
+from vrhino_b200 import _lib
+lib = _lib.load()
+P = ctypes.c_void_p
+codes = torch.arange(65536, dtype=torch.int32, device="cuda").to(torch.int16).view(torch.bfloat16)
+big = codes.repeat(80)
+outs = [torch.empty_like(big) for _ in range(4)]
+direct = torch.empty_like(codes)
+def act(x, out, stream):
+    assert lib.vrb_activation(2, P(x.data_ptr()), P(out.data_ptr()), 2, x.numel(), P(stream)) == 0, lib.vrb_last_error()
+side = torch.cuda.Stream()
+graph = torch.cuda.CUDAGraph()
+# 1. the FIRST use of the library is captured: no table exists, none may be built inside a capture
+with torch.cuda.graph(graph, stream=side):
+    act(big, outs[0], side.cuda_stream)
+graph.replay(); torch.cuda.synchronize()
+first = outs[0].clone()
+outs[0].zero_()
+assert lib.vrb_prepare_tables(P(side.cuda_stream)) == 0
+act(big, outs[1], side.cuda_stream)            # 2. same stream as the build: ordered behind it
+act(big, outs[2], torch.cuda.current_stream().cuda_stream)   # 3. another stream: flag set or not, same bits
+torch.cuda.synchronize()
+act(big, outs[3], torch.cuda.current_stream().cuda_stream)   # 4. table certainly published
+graph.replay()                                 # 5. the captured kernel now finds the table
+act(codes, direct, torch.cuda.current_stream().cuda_stream)  # small tensor: the direct kernel
+torch.cuda.synchronize()
+want = direct.view(torch.int16).expand(80, 65536)
+for k, t in enumerate([first] + outs):
+    assert torch.equal(t.view(torch.int16).reshape(80, 65536), want), k
+with torch.cuda.graph(torch.cuda.CUDAGraph(), stream=side):
+    assert lib.vrb_prepare_tables(P(side.cuda_stream)) == -1
+assert lib.vrb_device_allocation_count() == 0
+print("ok")
+"""
+
+
+def test_function_table_states_in_a_fresh_process():
+    """The table kernels decide on the device whether the resident table may be read: captured
+    before any table was built (evaluates its own), right behind the build on the same stream,
+    on another stream, after publication, and the first graph replayed again.  All five give the
+    direct kernel's bits; the library allocates nothing; vrb_prepare_tables refuses a capturing
+    stream."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.run([sys.executable, "-c", _TABLE_STATES_SCRIPT, root], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0 and proc.stdout.strip().endswith("ok"), proc.stderr[-3000:]
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("kind", [0, 2, 3])
 @pytest.mark.parametrize("n", [37, 8 * 4096 + 8])

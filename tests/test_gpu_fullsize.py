@@ -37,10 +37,13 @@ def _cmp_rope(orc, got, want, what):
     """bf16 RoPE outputs: <= 2 ulp, except where the two products of the rotation cancel -- there the
     result inherits one bf16 ulp of the (much larger) rounded normalised operands; such elements
     must be rare (<= 0.2 %) and within 8 * 2^-8 absolutely (the bound test_golden.py uses)."""
+    from conftest import record_parity
     data, tag = from_torch(got)
     assert tag == "bf16" and tuple(data.shape) == tuple(want.shape), what
     d = orc.bf16_ulp_distance(data, want.data)
     bad = d > 2
+    record_parity(what, "bf16", d.size, d.max(), int(bad.sum()), int(bad.sum()),
+                  "<= 0.2 % of the elements within 8 * 2^-8 absolute (RoPE cancellation after the bf16-rounded norm)" if bad.any() else "")
     if bad.any():
         diff = np.abs(orc.bf16_bits_to_f32(data).astype(np.float64) - want.f32().astype(np.float64))
         assert bad.mean() <= 2e-3 and (diff[bad] <= 2.0 ** -8 * 8.0).all(), (what, int(bad.sum()), int(d.max()))
@@ -51,18 +54,17 @@ def _cmp_rows(orc, got, rows, want, what, **kw):
     assert_close(orc, sub, want, what=what, **kw)
 
 
-def test_wan21_chain_full_size_sampled_rows(orc, gpu):
-    """Config 2: the eleven launches on 32760 tokens; 48 sampled token rows per launch against
-    the oracle's unfused chain (the reference's operator sequence)."""
+def _check_wan_chain(orc, gpu, blk, tag):
+    """Runs the eleven launches of a Wan block and compares 48 sampled token rows per launch with the
+    oracle's unfused chain (the reference's operator sequence)."""
     import torch
-    from vrhino_b200 import workloads
     be, ops = gpu
-    blk = workloads.WanBlock(be, tokens=32760, seed=11)
+    S = blk.x.shape[1]
     for l in blk.launches():
         l.fn()
     torch.cuda.synchronize()
     rng = np.random.default_rng(0)
-    rows = np.sort(np.concatenate([[0, 1, 32759], rng.choice(32760, 45, replace=False)]))
+    rows = np.sort(np.concatenate([[0, 1, S - 1], rng.choice(S, 45, replace=False)]))
     rows_t = torch.from_numpy(rows).cuda()
     obe, pol = orc.OracleBackend(), orc.Policy.unqualified_default("bf16")
     f32 = lambda t: orc.T(t.detach().cpu().float().numpy(), "f32")
@@ -73,21 +75,21 @@ def test_wan21_chain_full_size_sampled_rows(orc, gpu):
     def chain_ln_mod(shift, scale):
         return obe.cast(orc.modulate(obe, pol, obe.layer_norm(x, None, None, eps), shift, scale), "bf16")
 
-    _cmp_rows(orc, blk.out["A"], rows_t, chain_ln_mod(mod[0], mod[1]), "A ln_modulate")
-    _cmp_rows(orc, blk.out["G"], rows_t, chain_ln_mod(mod[3], mod[4]), "G ln_modulate")
+    _cmp_rows(orc, blk.out["A"], rows_t, chain_ln_mod(mod[0], mod[1]), f"{tag} A ln_modulate")
+    _cmp_rows(orc, blk.out["G"], rows_t, chain_ln_mod(mod[3], mod[4]), f"{tag} G ln_modulate")
     d = blk.cos.shape[-1]
     cos = orc.T(blk.cos.reshape(-1, d)[rows_t].cpu().numpy().reshape(1, len(rows), 1, d), "f32")
     sin = orc.T(blk.sin.reshape(-1, d)[rows_t].cpu().numpy().reshape(1, len(rows), 1, d), "f32")
     for name, src, w in (("Bq", blk.q, blk.wq), ("Bk", blk.k, blk.wk)):
-        n = orc.attention_norm(obe, pol, _orc_rows(orc, src, rows_t), f32(w), eps, rows_for_schedule=32760)
+        n = orc.attention_norm(obe, pol, _orc_rows(orc, src, rows_t), f32(w), eps, rows_for_schedule=S)
         r = orc.operation_rope(obe, pol, obe.reshape(n, (1, len(rows), blk.heads, d)), cos, sin)
         want = obe.cast(r, "bf16")
         got = blk.out[name][0, rows_t].reshape(1, len(rows), blk.heads, d)
-        _cmp_rope(orc, got, want, name)
-    n = orc.attention_norm(obe, pol, _orc_rows(orc, blk.cross_q, rows_t), f32(blk.wcq), eps, rows_for_schedule=32760)
-    _cmp_rows(orc, blk.out["Eq"], rows_t, obe.cast(n, "bf16"), "E rms cross q")
+        _cmp_rope(orc, got, want, f"{tag} {name} rms_rope")
+    n = orc.attention_norm(obe, pol, _orc_rows(orc, blk.cross_q, rows_t), f32(blk.wcq), eps, rows_for_schedule=S)
+    _cmp_rows(orc, blk.out["Eq"], rows_t, obe.cast(n, "bf16"), f"{tag} E rms cross q")
     want = obe.layer_norm(x, f32(blk.gamma3), f32(blk.beta3), eps)
-    _cmp_rows(orc, blk.out["D"], rows_t, want, "D ln_affine")
+    _cmp_rows(orc, blk.out["D"], rows_t, want, f"{tag} D ln_affine")
     for name, branch, gate in (("C", blk.proj, mod[2]), ("I", blk.ffn_out, mod[5])):
         want = orc.gated_residual(obe, pol, x, _orc_rows(orc, branch, rows_t), gate)
         got = blk.out[name][0, rows_t]
@@ -95,6 +97,42 @@ def test_wan21_chain_full_size_sampled_rows(orc, gpu):
     want = orc.residual_add(obe, pol, x, _orc_rows(orc, blk.cross, rows_t))
     got = blk.out["F"][0, rows_t]
     assert torch.equal(_bits(got).cpu(), torch.from_numpy(want.data.view(np.int16).reshape(got.shape))), "F"
+    # size-independent: a second pass over the whole tensors is bit-identical (no order-dependent sums)
+    first = {k: v.clone() for k, v in blk.out.items() if k in ("A", "Bq", "D")}
+    for l in blk.launches():
+        if l.name.split()[0] in ("A", "B", "D"):
+            l.fn()
+    torch.cuda.synchronize()
+    for k, v in first.items():
+        assert torch.equal(_bits(v), _bits(blk.out[k])), f"{tag} {k}: repeated launch differs"
+
+
+def test_wan21_chain_full_size_sampled_rows(orc, gpu):
+    """Config 2: the eleven launches on 32760 tokens x 1536."""
+    from vrhino_b200 import workloads
+    _check_wan_chain(orc, gpu, workloads.WanBlock(gpu[0], tokens=32760, seed=11), "wan2.1")
+
+
+def test_wan22_chain_full_size_sampled_rows(orc, gpu):
+    """Config 3: the same chain at D = 5120 (40 heads x 128), FFN 13824, 32760 tokens on the real
+    21 x 30 x 52 RoPE grid.  A 5120-wide row spans several warps, so this is the full-size exercise of
+    the cross-warp reduction of the row kernels (layer_norm_parallel_kernel, native/src/backend/cuda/
+    cuda_backend.cu:910-943, and rms_norm_contiguous_f32_kernel, :853-907, are what it replaces)."""
+    import torch
+    from vrhino_b200 import workloads
+    blk = workloads.WanBlock(gpu[0], tokens=32760, dim=5120, heads=40, ffn=13824, seed=13)
+    _check_wan_chain(orc, gpu, blk, "wan2.2")
+    # GELU-tanh [32760, 13824]: every element equals the function table at the input's bit pattern
+    be = gpu[0]
+    codes = torch.arange(65536, dtype=torch.int32, device="cuda").to(torch.int16).view(torch.bfloat16)
+    table = be.activation(codes, 2).view(torch.int16)
+    x, out = blk.ffn_hidden[0], blk.out["H"][0]
+    bad = 0
+    for r0 in range(0, x.shape[0], 2048):
+        sl = slice(r0, min(r0 + 2048, x.shape[0]))
+        index = (x[sl].contiguous().view(torch.int16).to(torch.int32) & 0xFFFF).long()
+        bad += int((table[index.reshape(-1)].reshape(index.shape) != out[sl].view(torch.int16)).sum())
+    assert bad == 0
 
 
 def test_wan21_merged_residual_norm_full_size(orc, gpu):

@@ -31,6 +31,8 @@ SIGNATURES = {
     "vrb_abi_version": [],
     "vrb_last_error": [],
     "vrb_launch_count": [],
+    "vrb_device_allocation_count": [],
+    "vrb_prepare_tables": [_vp],
     "vrb_binary": [_i, _vp, _pi64, _i, _vp, _pi64, _i, _vp, _i, _vp],
     "vrb_cast": [_vp, _i, _vp, _i, _i64, _vp],
     "vrb_activation": [_i, _vp, _vp, _i, _i64, _vp],
@@ -85,6 +87,7 @@ SIGNATURES = {
 _RESTYPES = {
     "vrb_last_error": _c.c_char_p,
     "vrb_launch_count": _c.c_uint64,
+    "vrb_device_allocation_count": _c.c_uint64,
     "vrb_group_norm_workspace_bytes": _c.c_size_t,
     "vrb_group_norm_frames_workspace_bytes": _c.c_size_t,
     "vrb_host_release": None,

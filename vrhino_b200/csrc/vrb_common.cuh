@@ -16,6 +16,7 @@ namespace vrb {
 // ------------------------------------------------------------------ host-side plumbing --
 void set_error(const char* format, ...);
 extern std::atomic<uint64_t> g_launches;
+extern std::atomic<uint64_t> g_device_allocations;   // cudaMalloc calls made by the library (host-buffer entry points only)
 
 // SM count of the current device, cached per device index.
 int sm_count();

@@ -509,7 +509,8 @@ constexpr size_t kFixedScratchBytes =
 static __device__ __align__(256) unsigned char g_fixed_scratch[kFixedScratchBytes];
 
 // In host code `g_fixed_scratch` is only a handle for the symbol, not an address a kernel can
-// use; the device address has to be asked for, per device, with that device current.
+// use; the device address has to be asked for, per device, with that device current.  It is kept
+// per device index and is not asked for again, so it does not survive cudaDeviceReset.
 std::mutex g_fixed_mutex;
 void* g_fixed_address[64] = {nullptr};
 

@@ -8,8 +8,11 @@
 // one is computing and one is downloading, and both PCIe directions stay busy.  Operands that
 // are shared by all rows (modulation vectors, norm weights) are uploaded once.
 //
-// Device staging buffers are owned by the library, grown on demand and freed by
-// vrb_host_release(); these are the only entry points of the library that allocate.  Copies
+// Device staging buffers and streams are owned by the library, one set per device (the device that is
+// current when a call is made), grown on demand and freed by vrb_host_release(); these are the only
+// entry points of the library that allocate (vrb_device_allocation_count() counts them).  When
+// anything fails mid-pipeline the streams are drained before the call returns, so no copy to or
+// from the caller's host buffers is still in flight when the caller sees the error.  Copies
 // are asynchronous only if the host buffers are page-locked; with pageable memory the calls
 // still work but CUDA stages the copies itself and little overlaps.
 #include <mutex>
@@ -35,7 +38,8 @@ struct HostPipe {
     Arena slots[kSlots];
     Arena shared;
 };
-HostPipe g_pipe;
+constexpr int kMaxDevices = 64;
+HostPipe g_pipes[kMaxDevices];
 
 int cuda_fail(cudaError_t e, const char* what) {
     set_error("CUDA error: %s (%s)", cudaGetErrorString(e), what);
@@ -47,6 +51,7 @@ int ensure(Arena& a, size_t bytes) {
     if (a.bytes >= bytes) return VRB_OK;
     if (a.base) { VRB_CUDA(cudaDeviceSynchronize(), "drain before regrow"); cudaFree(a.base); a.base = nullptr; a.bytes = 0; }
     VRB_CUDA(cudaMalloc(&a.base, bytes), "device staging");
+    g_device_allocations.fetch_add(1, std::memory_order_relaxed);
     a.bytes = bytes;
     return VRB_OK;
 }
@@ -65,11 +70,10 @@ struct Operand {
 
 // launch(block_rows, dev_ptrs[], stream): dev_ptrs are in operand order.
 template <typename Launch>
-int run_pipeline(std::vector<Operand>& ops, int64_t rows, Launch launch) {
-    std::lock_guard<std::mutex> lock(g_pipe.mutex);
-    for (auto& s : g_pipe.streams)
+int enqueue_pipeline(HostPipe& pipe, std::vector<Operand>& ops, int64_t rows, Launch launch) {
+    for (auto& s : pipe.streams)
         if (!s) VRB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "stream create");
-    if (!g_pipe.shared_ready) VRB_CUDA(cudaEventCreateWithFlags(&g_pipe.shared_ready, cudaEventDisableTiming), "event create");
+    if (!pipe.shared_ready) VRB_CUDA(cudaEventCreateWithFlags(&pipe.shared_ready, cudaEventDisableTiming), "event create");
 
     size_t widest = 1, shared_bytes = 0;
     for (const auto& o : ops) {
@@ -81,20 +85,20 @@ int run_pipeline(std::vector<Operand>& ops, int64_t rows, Launch launch) {
     if (block_rows > rows) block_rows = rows;
     size_t slot_bytes = 0;
     for (const auto& o : ops) if (o.row_bytes) slot_bytes += align256(o.row_bytes * static_cast<size_t>(block_rows));
-    for (auto& a : g_pipe.slots) if (int rc = ensure(a, slot_bytes)) return rc;
-    if (int rc = ensure(g_pipe.shared, shared_bytes ? shared_bytes : 256)) return rc;
+    for (auto& a : pipe.slots) if (int rc = ensure(a, slot_bytes)) return rc;
+    if (int rc = ensure(pipe.shared, shared_bytes ? shared_bytes : 256)) return rc;
 
     // shared operands: once, on stream 0; the other streams wait for them
     std::vector<void*> dev(ops.size(), nullptr);
     size_t off = 0;
     for (size_t k = 0; k < ops.size(); ++k) {
         if (ops[k].row_bytes || !ops[k].host_in) continue;
-        dev[k] = static_cast<char*>(g_pipe.shared.base) + off;
+        dev[k] = static_cast<char*>(pipe.shared.base) + off;
         off += align256(ops[k].total_bytes);
-        VRB_CUDA(cudaMemcpyAsync(dev[k], ops[k].host_in, ops[k].total_bytes, cudaMemcpyHostToDevice, g_pipe.streams[0]), "upload shared operand");
+        VRB_CUDA(cudaMemcpyAsync(dev[k], ops[k].host_in, ops[k].total_bytes, cudaMemcpyHostToDevice, pipe.streams[0]), "upload shared operand");
     }
-    VRB_CUDA(cudaEventRecord(g_pipe.shared_ready, g_pipe.streams[0]), "event record");
-    for (int s = 1; s < kSlots; ++s) VRB_CUDA(cudaStreamWaitEvent(g_pipe.streams[s], g_pipe.shared_ready, 0), "event wait");
+    VRB_CUDA(cudaEventRecord(pipe.shared_ready, pipe.streams[0]), "event record");
+    for (int s = 1; s < kSlots; ++s) VRB_CUDA(cudaStreamWaitEvent(pipe.streams[s], pipe.shared_ready, 0), "event wait");
 
     // Block sizes ramp up at the start and down at the end (1/8, 1/4, 1/2 of a full block): the call
     // returns only when everything is back on the host, so the first upload and the last download
@@ -116,12 +120,12 @@ int run_pipeline(std::vector<Operand>& ops, int64_t rows, Launch launch) {
     int64_t r0 = 0;
     for (size_t b = 0; b < sizes.size(); r0 += sizes[b], ++b) {
         const int slot = static_cast<int>(b % kSlots);
-        cudaStream_t st = g_pipe.streams[slot];
+        cudaStream_t st = pipe.streams[slot];
         const int64_t n = sizes[b];
         size_t so = 0;
         for (size_t k = 0; k < ops.size(); ++k) {
             if (!ops[k].row_bytes) continue;
-            dev[k] = static_cast<char*>(g_pipe.slots[slot].base) + so;
+            dev[k] = static_cast<char*>(pipe.slots[slot].base) + so;
             so += align256(ops[k].row_bytes * static_cast<size_t>(block_rows));
             if (ops[k].host_in)
                 VRB_CUDA(cudaMemcpyAsync(dev[k], static_cast<const char*>(ops[k].host_in) + static_cast<size_t>(r0) * ops[k].row_bytes,
@@ -133,7 +137,26 @@ int run_pipeline(std::vector<Operand>& ops, int64_t rows, Launch launch) {
                 VRB_CUDA(cudaMemcpyAsync(static_cast<char*>(ops[k].host_out) + static_cast<size_t>(r0) * ops[k].row_bytes, dev[k],
                                          static_cast<size_t>(n) * ops[k].row_bytes, cudaMemcpyDeviceToHost, st), "download rows");
     }
-    for (auto& s : g_pipe.streams) VRB_CUDA(cudaStreamSynchronize(s), "pipeline drain");
+    return VRB_OK;
+}
+
+template <typename Launch>
+int run_pipeline(std::vector<Operand>& ops, int64_t rows, Launch launch) {
+    int device = 0;
+    VRB_CUDA(cudaGetDevice(&device), "current device");
+    VRB_REQUIRE(device >= 0 && device < kMaxDevices, VRB_ERR_UNSUPPORTED, "host pipeline: device index %d out of range", device);
+    HostPipe& pipe = g_pipes[device];
+    std::lock_guard<std::mutex> lock(pipe.mutex);
+    const int rc = enqueue_pipeline(pipe, ops, rows, launch);
+    // Drain on success and on failure alike: the caller's host buffers are its own again on return.
+    cudaError_t drained = cudaSuccess;
+    for (auto& s : pipe.streams) {
+        if (!s) continue;
+        const cudaError_t e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess && drained == cudaSuccess) drained = e;
+    }
+    if (rc != VRB_OK) return rc;   // the first failure's text stays
+    if (drained != cudaSuccess) return cuda_fail(drained, "pipeline drain");
     return VRB_OK;
 }
 
@@ -210,12 +233,16 @@ extern "C" int vrb_host_activation(int kind, const void* x, void* out, int dtype
     });
 }
 
+// Frees the current device's staging buffers and streams.
 extern "C" void vrb_host_release(void) {
-    std::lock_guard<std::mutex> lock(g_pipe.mutex);
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return;
+    HostPipe& pipe = g_pipes[device];
+    std::lock_guard<std::mutex> lock(pipe.mutex);
     cudaDeviceSynchronize();
-    for (auto& a : g_pipe.slots) { if (a.base) cudaFree(a.base); a = Arena{}; }
-    if (g_pipe.shared.base) cudaFree(g_pipe.shared.base);
-    g_pipe.shared = Arena{};
-    for (auto& s : g_pipe.streams) { if (s) cudaStreamDestroy(s); s = nullptr; }
-    if (g_pipe.shared_ready) { cudaEventDestroy(g_pipe.shared_ready); g_pipe.shared_ready = nullptr; }
+    for (auto& a : pipe.slots) { if (a.base) cudaFree(a.base); a = Arena{}; }
+    if (pipe.shared.base) cudaFree(pipe.shared.base);
+    pipe.shared = Arena{};
+    for (auto& s : pipe.streams) { if (s) cudaStreamDestroy(s); s = nullptr; }
+    if (pipe.shared_ready) { cudaEventDestroy(pipe.shared_ready); pipe.shared_ready = nullptr; }
 }

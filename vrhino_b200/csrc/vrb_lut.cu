@@ -9,16 +9,18 @@
 // activation_kernel expressions, native/src/backend/cuda/cuda_backend.cu:1098-1109) on every
 // possible input, so the result is bit-identical to the direct kernel by construction.
 //
-// Building the table costs about 10 us of an SM's time, so it is built ONCE per (device,
-// operator, parameters) into device memory by a small kernel and kept; every later launch
-// copies the 128 KB from L2 into its shared memory (about 1 us, issued behind the first tensor
-// loads).  When the table cannot be built ahead (the stream is being captured into a graph, or
-// the small cache is full) the kernel falls back to filling its shared table itself.
+// Building the table costs about 10 us of an SM's time, so the tables of the parameter-free
+// operators (five activation kinds, exp, sqrt) live in a file-scope __device__ array (7 x 128 KB
+// that every GPU loading the library holds until exit): nothing is allocated.  The first table
+// launch per (device, operator) is preceded by a small build kernel on the same stream; when its
+// last CTA has stored its entries it publishes a device-side flag.  Every table kernel reads that
+// flag: set -> it copies the 128 KB from L2 into its shared memory (about 1 us, issued behind the
+// first tensor loads); not set (another stream's build still running, a graph captured before any
+// build, clamp with its caller-chosen bounds) -> it evaluates the table itself.  Either way the
+// entries are the same bits, and no host-side synchronisation, event or allocation is involved.
 #include "vrb_common.cuh"
 
-#include <cstring>
-#include <mutex>
-#include <vector>
+#include <atomic>
 
 namespace vrb {
 namespace {
@@ -40,24 +42,53 @@ __device__ __forceinline__ uint16_t table_entry(int i, float p0, float p1) {
     return static_cast<uint16_t>(float_to_bf16_bits(lut_value<OP>(bf16_bits_to_float(static_cast<uint32_t>(i)), p0, p1)));
 }
 
-// Shared table from the prebuilt copy in device memory (ready != nullptr) or evaluated here.
+// Resident tables of the parameter-free operators: slot = operator code (0-4 activation kinds),
+// 5 = exp, 6 = sqrt.  g_table_done[slot] counts the build kernel's finished CTAs;
+// g_table_published[slot] becomes 1 once all of them have stored their entries.
+constexpr int kResidentTables = 7;
+constexpr int kBuildCtas = kTableEntries / kLutThreads;
+__device__ __align__(256) uint16_t g_resident_tables[kResidentTables][kTableEntries];
+__device__ unsigned g_table_done[kResidentTables];
+__device__ unsigned g_table_published[kResidentTables];
+
+__host__ __device__ constexpr int resident_slot(int op) { return op <= 4 ? op : op == 6 ? 5 : op == 7 ? 6 : -1; }
+
+// Shared table from the resident copy when `slot` has been published, evaluated here otherwise.
 template <int OP>
-__device__ __forceinline__ void fill_table(uint16_t* table, const uint4* __restrict__ ready, float p0, float p1) {
-    if (ready != nullptr) {
+__device__ __forceinline__ void fill_table(uint16_t* table, int slot, float p0, float p1) {
+    __shared__ unsigned published;
+    if (threadIdx.x == 0) {
+        unsigned flag = 0;
+        if (slot >= 0) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(flag) : "l"(&g_table_published[slot]) : "memory");
+        published = flag;
+    }
+    __syncthreads();
+    if (published != 0) {
+        const uint4* ready = reinterpret_cast<const uint4*>(g_resident_tables[slot]);
         uint4* dst = reinterpret_cast<uint4*>(table);
 #pragma unroll
         for (int i = 0; i < kTableBytes / 16 / kLutThreads; ++i)
-            dst[threadIdx.x + i * kLutThreads] = __ldg(ready + threadIdx.x + i * kLutThreads);
+            dst[threadIdx.x + i * kLutThreads] = __ldcg(ready + threadIdx.x + i * kLutThreads);
     } else {
         for (int i = threadIdx.x; i < kTableEntries; i += kLutThreads) table[i] = table_entry<OP>(i, p0, p1);
     }
     __syncthreads();
 }
 
+// kBuildCtas CTAs of kLutThreads threads; the CTA that finishes last publishes the slot.
 template <int OP>
-__global__ void __launch_bounds__(kLutThreads) build_table_kernel(uint16_t* __restrict__ table, float p0, float p1) {
+__global__ void __launch_bounds__(kLutThreads) build_table_kernel(int slot) {
     const int i = blockIdx.x * kLutThreads + threadIdx.x;
-    if (i < kTableEntries) table[i] = table_entry<OP>(i, p0, p1);
+    g_resident_tables[slot][i] = table_entry<OP>(i, 0.f, 0.f);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned finished = atomicAdd(&g_table_done[slot], 1u) + 1u;
+        if (finished % kBuildCtas == 0) {   // a repeated build rewrites the same bits: still complete
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(&g_table_published[slot]), "r"(1u) : "memory");
+        }
+    }
 }
 
 __device__ __forceinline__ uint32_t lookup2(const uint16_t* table, uint32_t word) {
@@ -66,7 +97,7 @@ __device__ __forceinline__ uint32_t lookup2(const uint16_t* table, uint32_t word
 
 template <int OP>
 __global__ void __launch_bounds__(kLutThreads, 1) unary_lut_kernel(const uint4* __restrict__ x, uint4* __restrict__ out,
-                                                                  int64_t chunks, const uint4* __restrict__ ready,
+                                                                  int64_t chunks, int slot,
                                                                   float p0, float p1) {
     extern __shared__ __align__(16) uint16_t table[];
     constexpr int U = 3;   // 16-byte loads in flight per thread; 3 measured 8 % faster than 2 or 4 (5 and more: slower)
@@ -77,7 +108,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) unary_lut_kernel(const uint4* 
 #pragma unroll
     for (int u = 0; u < U; ++u)
         if (first + u * stride < chunks) r[u] = __ldcs(x + first + u * stride);
-    fill_table<OP>(table, ready, p0, p1);
+    fill_table<OP>(table, slot, p0, p1);
     for (int64_t i = first; i < chunks; i += stride * U) {
         if (i != first) {
 #pragma unroll
@@ -101,9 +132,9 @@ __global__ void __launch_bounds__(kLutThreads, 1) unary_lut_kernel(const uint4* 
 // bf16 store produces).
 __global__ void __launch_bounds__(kLutThreads, 1) swiglu_lut_kernel(const uint4* __restrict__ proj, uint4* __restrict__ out,
                                                                    int64_t rows, int64_t hidden_chunks,
-                                                                   const uint4* __restrict__ ready) {
+                                                                   int slot) {
     extern __shared__ __align__(16) uint16_t table[];
-    fill_table<VRB_SILU>(table, ready, 0.f, 0.f);
+    fill_table<VRB_SILU>(table, slot, 0.f, 0.f);
     constexpr int U = 2;   // 3 measured slower here
     const int64_t total = rows * hidden_chunks;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kLutThreads;
@@ -158,7 +189,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) linear_output_lut_kernel(const
                                                                           const uint4* __restrict__ bias,
                                                                           uint4* __restrict__ out, int64_t chunks,
                                                                           unsigned width_chunks,
-                                                                          const uint4* __restrict__ ready) {
+                                                                          int slot) {
     extern __shared__ __align__(16) uint16_t table[];
         constexpr int U = 2;   // registers: U x (8 accumulators + 4 bias); 3 measured slower
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kLutThreads;
@@ -177,7 +208,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) linear_output_lut_kernel(const
         }
     };
     request(first);   // before the table copy, so HBM is busy while the table arrives
-    fill_table<OP>(table, ready, 0.f, 0.f);
+    fill_table<OP>(table, slot, 0.f, 0.f);
     for (int64_t i = first; i < chunks; i += stride * U) {
         if (i != first) request(i);
 #pragma unroll
@@ -197,7 +228,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) linear_output_swiglu_lut_kerne
                                                                                  const uint4* __restrict__ bias,
                                                                                  uint4* __restrict__ out, int64_t chunks,
                                                                                  unsigned hidden_chunks,
-                                                                                 const uint4* __restrict__ ready) {
+                                                                                 int slot) {
     extern __shared__ __align__(16) uint16_t table[];
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kLutThreads;
     const int64_t first = static_cast<int64_t>(blockIdx.x) * kLutThreads + threadIdx.x;
@@ -213,7 +244,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) linear_output_swiglu_lut_kerne
         if (has_bias) { ba = __ldg(bias + chunk); bg = __ldg(bias + hidden_chunks + chunk); }
     };
     request(first);
-    fill_table<VRB_SILU>(table, ready, 0.f, 0.f);
+    fill_table<VRB_SILU>(table, slot, 0.f, 0.f);
     for (int64_t i = first; i < chunks; i += stride) {
         if (i != first) request(i);
         const uint4 value = biased_pack(a[0], a[1], ba, has_bias), gate = biased_pack(g[0], g[1], bg, has_bias);
@@ -239,9 +270,9 @@ __global__ void __launch_bounds__(kLutThreads, 1) gn_apply_silu_lut_kernel(
     const uint4* __restrict__ x, uint4* __restrict__ out, const void* __restrict__ weight, int w_dt,
     const void* __restrict__ bias, int b_dt, const float* __restrict__ mean, const float* __restrict__ inverse,
     int64_t planes, int64_t channels, int channels_per, int groups, int64_t frames, int64_t stat_frames, int64_t plane_chunks,
-    int64_t tiles_per_plane, int64_t tile_chunks, GnScatter scatter, const uint4* __restrict__ ready) {
+    int64_t tiles_per_plane, int64_t tile_chunks, GnScatter scatter, int slot) {
     extern __shared__ __align__(16) uint16_t table[];
-    fill_table<VRB_SILU>(table, ready, 0.f, 0.f);
+    fill_table<VRB_SILU>(table, slot, 0.f, 0.f);
     constexpr int U = 4;   // 3 and 2 measured slower (760 / 840 us against 730 us on [1,256,28,240,424])
     // the launcher guarantees planes * tiles_per_plane < 2^31: 32-bit index arithmetic
     const unsigned tiles = static_cast<unsigned>(planes * tiles_per_plane), tpp = static_cast<unsigned>(tiles_per_plane);
@@ -303,50 +334,37 @@ int reserve_table(K kernel, bool* done) {
     return VRB_OK;
 }
 
-// Prebuilt tables, one per (device, operator, parameter bits); a handful exist in practice
-// (one per activation kind plus the clamp bounds a model uses), so the cache is a short list.
-struct ReadyTable {
-    int device, op;
-    uint32_t p0, p1;
-    uint16_t* table;
-};
-constexpr size_t kMaxReadyTables = 64;
-std::mutex g_tables_mutex;
-std::vector<ReadyTable> g_tables;
+// Host side of the resident tables: which (device, slot) build kernels have been launched.  The
+// state only avoids launching a build twice; whether a table may be READ is decided on the device
+// by the published flag, so a stale entry here (after cudaDeviceReset) costs speed, not results.
+constexpr int kMaxDevices = 64;
+std::atomic<int> g_build_launched[kMaxDevices][kResidentTables];
 
-// The device copy of the table, built on `stream` at first use (and waited for, so later
-// launches on any stream may read it).  nullptr when it cannot be prepared now: the caller's
-// kernel then fills its own shared table.
 template <int OP>
-const uint4* ready_table(float p0, float p1, cudaStream_t stream) {
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess) return nullptr;
-    uint32_t b0, b1;
-    std::memcpy(&b0, &p0, 4);
-    std::memcpy(&b1, &p1, 4);
-    std::lock_guard<std::mutex> lock(g_tables_mutex);
-    for (const ReadyTable& t : g_tables)
-        if (t.device == device && t.op == OP && t.p0 == b0 && t.p1 == b1) return reinterpret_cast<const uint4*>(t.table);
-    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
-        cudaGetLastError();
-        return nullptr;
+void launch_build(int slot, cudaStream_t stream) {
+    build_table_kernel<OP><<<kBuildCtas, kLutThreads, 0, stream>>>(slot);
+    if (cudaGetLastError() == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+// Slot of OP's resident table (-1: none, the kernel evaluates its own), making sure its build
+// kernel has been launched on this device -- on `stream`, ahead of the caller's kernel, unless
+// that stream is being captured (a captured build would be rebuilt by every replay).
+template <int OP>
+int ready_table(cudaStream_t stream) {
+    constexpr int slot = resident_slot(OP);
+    if constexpr (slot >= 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return slot;
+        std::atomic<int>& launched = g_build_launched[device][slot];
+        if (launched.load(std::memory_order_acquire) != 0) return slot;
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+            cudaGetLastError();
+            return slot;
+        }
+        if (launched.exchange(1, std::memory_order_acq_rel) == 0) launch_build<OP>(slot, stream);
     }
-    if (g_tables.size() >= kMaxReadyTables) return nullptr;
-    uint16_t* table = nullptr;
-    if (cudaMalloc(&table, kTableBytes) != cudaSuccess) {
-        cudaGetLastError();
-        return nullptr;
-    }
-    build_table_kernel<OP><<<kTableEntries / kLutThreads, kLutThreads, 0, stream>>>(table, p0, p1);
-    if (cudaGetLastError() != cudaSuccess || cudaStreamSynchronize(stream) != cudaSuccess) {
-        cudaGetLastError();
-        cudaFree(table);
-        return nullptr;
-    }
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    g_tables.push_back({device, OP, b0, b1, table});
-    return reinterpret_cast<const uint4*>(table);
+    return slot;
 }
 
 template <int OP>
@@ -357,7 +375,7 @@ int launch_lut(const void* x, void* out, int64_t count, float p0, float p1, cuda
     const int64_t per_cta = (chunks + kLutThreads - 1) / kLutThreads;
     const int grid = static_cast<int>(per_cta < sm_count() ? per_cta : sm_count());
     unary_lut_kernel<OP><<<grid, kLutThreads, kTableBytes, stream>>>(
-        static_cast<const uint4*>(x), static_cast<uint4*>(out), chunks, ready_table<OP>(p0, p1, stream), p0, p1);
+        static_cast<const uint4*>(x), static_cast<uint4*>(out), chunks, ready_table<OP>(stream), p0, p1);
     return after_launch("unary (table)");
 }
 
@@ -389,7 +407,7 @@ int launch_linear_lut(const float* accumulation, const void* bias, void* out, in
     const int grid = static_cast<int>(per_cta < sm_count() ? per_cta : sm_count());
     linear_output_lut_kernel<OP><<<grid, kLutThreads, kTableBytes, stream>>>(
         reinterpret_cast<const float4*>(accumulation), static_cast<const uint4*>(bias), static_cast<uint4*>(out), chunks,
-        static_cast<unsigned>(width / 8), ready_table<OP>(0.f, 0.f, stream));
+        static_cast<unsigned>(width / 8), ready_table<OP>(stream));
     return after_launch("linear_output_activation (table)");
 }
 
@@ -413,7 +431,7 @@ int launch_linear_output_swiglu_lut(const float* accumulation, const void* bias,
     const int grid = static_cast<int>(per_cta < sm_count() ? per_cta : sm_count());
     linear_output_swiglu_lut_kernel<<<grid, kLutThreads, kTableBytes, stream>>>(
         reinterpret_cast<const float4*>(accumulation), static_cast<const uint4*>(bias), static_cast<uint4*>(out), chunks,
-        static_cast<unsigned>(hidden / 8), ready_table<VRB_SILU>(0.f, 0.f, stream));
+        static_cast<unsigned>(hidden / 8), ready_table<VRB_SILU>(stream));
     return after_launch("linear_output_swiglu (table)");
 }
 
@@ -421,7 +439,7 @@ int launch_swiglu_lut(const void* proj, void* out, int64_t rows, int64_t hidden,
     static bool done[64] = {false};
     if (int rc = reserve_table(swiglu_lut_kernel, done)) return rc;
     swiglu_lut_kernel<<<sm_count(), kLutThreads, kTableBytes, stream>>>(
-        static_cast<const uint4*>(proj), static_cast<uint4*>(out), rows, hidden / 8, ready_table<VRB_SILU>(0.f, 0.f, stream));
+        static_cast<const uint4*>(proj), static_cast<uint4*>(out), rows, hidden / 8, ready_table<VRB_SILU>(stream));
     return after_launch("swiglu (table)");
 }
 
@@ -439,8 +457,30 @@ int launch_group_norm_apply_silu_lut(const void* x, const void* weight, int w_dt
     gn_apply_silu_lut_kernel<<<grid, kLutThreads, kTableBytes, stream>>>(
         static_cast<const uint4*>(x), static_cast<uint4*>(out), weight, w_dt, bias, b_dt, mean, inverse, planes, channels,
         channels_per, groups, frames, stat_frames, plane_chunks, tiles_per_plane, tile_chunks, scatter,
-        ready_table<VRB_SILU>(0.f, 0.f, stream));
+        ready_table<VRB_SILU>(stream));
     return after_launch("group_norm apply (table)");
 }
 
 }  // namespace vrb
+
+// Builds every resident table of the current device on `stream` (seven small kernels).  Optional:
+// the operator entry points do this on first use; a caller that captures its first launches into a
+// CUDA graph calls it once per device before the capture so the captured kernels find the tables.
+extern "C" int vrb_prepare_tables(vrb_stream stream) {
+    using namespace vrb;
+    cudaStream_t s = as_stream(stream);
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        set_error("prepare_tables: the stream is being captured; call it before the capture begins");
+        return VRB_ERR_INVALID;
+    }
+    ready_table<0>(s); ready_table<1>(s); ready_table<2>(s); ready_table<3>(s); ready_table<4>(s);
+    ready_table<6>(s); ready_table<7>(s);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("CUDA error: %s (function-table build)", cudaGetErrorString(e));
+        return VRB_ERR_CUDA;
+    }
+    return VRB_OK;
+}
