@@ -71,6 +71,14 @@ uint64_t vrb_device_allocation_count(void);
  * before the capture, otherwise the captured kernels evaluate their tables themselves on every
  * replay (same results, about 10 us slower per launch).  VRB_ERR_INVALID on a capturing stream. */
 int vrb_prepare_tables(vrb_stream stream);
+/* Overlapped launches (on by default).  The row-norm, gated-residual and table kernels are launched
+ * so that the GPU may begin scheduling them while the previous kernel of the stream drains
+ * (programmatic dependent launch); each of them waits for that kernel's completion before it
+ * touches any caller memory, so results and stream ordering are those of plain launches.  What it
+ * buys is the launch gap between short kernels (token shards of a block on 8 GPUs).  0 switches it
+ * off (plain launches), non-zero on; returns the previous setting.  Process-wide.  No counterpart
+ * in the reference, which launches everything on the legacy default stream. */
+int vrb_set_launch_overlap(int enabled);
 
 /* ------------------------------------------------------------------ per-operator forms -- */
 
@@ -212,8 +220,10 @@ int vrb_group_norm_apply(const void* x, int dtype, const void* weight, int weigh
  * the peer-mapped ones of the other ranks -- and receives the slice at element offset
  * spatial_offset of every (batch entry, channel, frame) plane.  mean / inverse are per
  * (batch entry, group) as vrb_group_norm_finalize produced them from the all-reduced moments.
- * Plain st.global to the peer pointers; the caller orders the ranks afterwards (any collective
- * or barrier on the stream).  spatial_local, spatial_full and spatial_offset must be multiples
+ * Plain st.global to the peer pointers; the caller orders the ranks on both sides: before the
+ * launch every rank must be done reading the previous contents of its destination, and after it
+ * every rank's stores must have landed before anyone reads (any collective or barrier on the
+ * stream does either).  spatial_local, spatial_full and spatial_offset must be multiples
  * of 8 elements.  No counterpart in the reference, which has no multi-GPU path. */
 int vrb_group_norm_apply_scatter(const void* x, int dtype, const void* weight, int weight_dtype,
                                  const void* bias, int bias_dtype, void* const* destinations, int destination_count,

@@ -7,13 +7,14 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("pinned", [True, False])
-def test_host_chain_matches_device_chain(gpu, pinned):
+@pytest.mark.parametrize("pinned,batch", [(True, 1), (False, 1), (True, 2)])
+def test_host_chain_matches_device_chain(gpu, pinned, batch):
     import torch
     be, ops = gpu
     from vrhino_b200 import _lib, workloads
-    # 3000 rows x 1536 bf16 = 9 MB per tensor: two row blocks, the second one partial
-    blk = workloads.WanBlock(be, tokens=3000, grid=(1, 30, 100), ffn=1024, text_tokens=40, seed=3)
+    # 3000 rows x 1536 bf16 = 9 MB per tensor: two row blocks, the second one partial; batch 2 = both
+    # CFG branches with their own modulation vectors, run branch by branch on the host side
+    blk = workloads.WanBlock(be, tokens=3000, grid=(1, 30, 100), ffn=1024, text_tokens=40, seed=3, batch=batch)
     for l in blk.launches():
         l.fn()
     torch.cuda.synchronize()

@@ -33,6 +33,7 @@ SIGNATURES = {
     "vrb_launch_count": [],
     "vrb_device_allocation_count": [],
     "vrb_prepare_tables": [_vp],
+    "vrb_set_launch_overlap": [_i],
     "vrb_binary": [_i, _vp, _pi64, _i, _vp, _pi64, _i, _vp, _i, _vp],
     "vrb_cast": [_vp, _i, _vp, _i, _i64, _vp],
     "vrb_activation": [_i, _vp, _vp, _i, _i64, _vp],

@@ -45,6 +45,40 @@ inline int after_launch(const char* what) {
     return VRB_OK;
 }
 
+// ---- overlapped launches (programmatic dependent launch) ------------------------------------
+// With overlap enabled (the default; vrb_set_launch_overlap) the hot kernels are launched with the
+// programmatic-stream-serialization attribute: the GPU may start scheduling their CTAs while the
+// previous kernel of the stream drains, which hides the launch gap between short kernels.  Such a
+// kernel calls pdl_wait() -- which returns once the previous kernel has completed and its writes
+// are visible -- before it touches ANY memory the caller passed in (inputs, outputs, vectors,
+// tables); only work on the library's own immutable data may precede it.  Every thread calls it
+// unconditionally, so "this kernel has finished" always implies "its predecessors have finished".
+// Without the attribute pdl_wait() returns at once.
+extern std::atomic<int> g_launch_overlap;
+
+template <typename... KArgs, typename... Args>
+inline void launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    if (g_launch_overlap.load(std::memory_order_relaxed) != 0) {
+        attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[0].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        if (cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...) == cudaSuccess) return;
+        // a driver / stream that refuses the attribute: plain launches from here on
+        cudaGetLastError();
+        g_launch_overlap.store(0, std::memory_order_relaxed);
+        config.attrs = nullptr;
+        config.numAttrs = 0;
+    }
+    cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);   // an error stays for after_launch()
+}
+
 // Persistent-style grid: enough CTAs to fill every SM `per_sm` times, never more than `work`.
 inline int grid_for(int64_t work_items, int per_sm) {
     const int64_t cap = static_cast<int64_t>(sm_count()) * per_sm;
@@ -89,6 +123,11 @@ int launch_group_norm_apply_silu_lut(const void* x, const void* weight, int w_dt
 
 // ------------------------------------------------------------------------ device side --
 #ifdef __CUDACC__
+
+// See launch_overlapped(): let the next kernel of the stream start being scheduled / wait for the
+// previous kernel of the stream to have completed.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
     return __uint_as_float(bits16 << 16);

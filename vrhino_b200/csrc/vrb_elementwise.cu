@@ -333,8 +333,10 @@ template <bool RES_BF16, bool BR_BF16, bool STATE_BF16>
 __global__ void __launch_bounds__(kThreads) gated_residual_typed_kernel(
         const void* __restrict__ res, const void* __restrict__ branch, const void* __restrict__ gate, int gate_dt,
         void* __restrict__ out, unsigned total, unsigned width_chunks, unsigned rows_per_vector, unsigned vectors) {
-        constexpr int U = 2;
+    constexpr int U = 2;
     const unsigned stride = gridDim.x * blockDim.x;
+    pdl_launch_dependents();
+    pdl_wait();
     for (unsigned i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
         if constexpr (RES_BF16 && BR_BF16 && STATE_BF16) {
             uint4 r[U], b[U];
@@ -850,7 +852,7 @@ extern "C" int vrb_gated_residual(const void* residual, int residual_dtype, cons
         const unsigned rpv = static_cast<unsigned>(gate ? rows_per_vector : 1), nv = static_cast<unsigned>(gate ? gate_vectors : 1);
         cudaStream_t s = as_stream(stream);
         const int key = (residual_dtype == VRB_BF16 ? 4 : 0) | (branch_dtype == VRB_BF16 ? 2 : 0) | (state_dtype == VRB_BF16 ? 1 : 0);
-#define VRB_GR(R, B, S) gated_residual_typed_kernel<R, B, S><<<grid, kThreads, 0, s>>>(residual, branch, gate, gate_dtype, out, total, wc, rpv, nv)
+#define VRB_GR(R, B, S) launch_overlapped(gated_residual_typed_kernel<R, B, S>, dim3(grid), dim3(kThreads), 0, s, residual, branch, gate, gate_dtype, out, total, wc, rpv, nv)
         switch (key) {
             case 0: VRB_GR(false, false, false); break;
             case 1: VRB_GR(false, false, true); break;

@@ -98,17 +98,22 @@ __device__ __forceinline__ uint32_t lookup2(const uint16_t* table, uint32_t word
 template <int OP>
 __global__ void __launch_bounds__(kLutThreads, 1) unary_lut_kernel(const uint4* __restrict__ x, uint4* __restrict__ out,
                                                                   int64_t chunks, int slot,
-                                                                  float p0, float p1) {
+                                                                  float p0, float p1, int overlapped) {
     extern __shared__ __align__(16) uint16_t table[];
     constexpr int U = 3;   // 16-byte loads in flight per thread; 3 measured 8 % faster than 2 or 4 (5 and more: slower)
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kLutThreads;
     const int64_t first = static_cast<int64_t>(blockIdx.x) * kLutThreads + threadIdx.x;
     uint4 r[U];
-    // The first tensor loads go out before the table copy so HBM is busy while the table arrives.
+    pdl_launch_dependents();
+    // Overlapped launch: the table (library data) is filled while the previous kernel drains, the
+    // tensor is touched only after it has completed.  Plain launch: the first tensor loads go out
+    // before the table copy so HBM is busy while the table arrives.
+    if (overlapped) fill_table<OP>(table, slot, p0, p1);
+    pdl_wait();
 #pragma unroll
     for (int u = 0; u < U; ++u)
         if (first + u * stride < chunks) r[u] = __ldcs(x + first + u * stride);
-    fill_table<OP>(table, slot, p0, p1);
+    if (!overlapped) fill_table<OP>(table, slot, p0, p1);
     for (int64_t i = first; i < chunks; i += stride * U) {
         if (i != first) {
 #pragma unroll
@@ -134,7 +139,9 @@ __global__ void __launch_bounds__(kLutThreads, 1) swiglu_lut_kernel(const uint4*
                                                                    int64_t rows, int64_t hidden_chunks,
                                                                    int slot) {
     extern __shared__ __align__(16) uint16_t table[];
-    fill_table<VRB_SILU>(table, slot, 0.f, 0.f);
+    pdl_launch_dependents();
+    fill_table<VRB_SILU>(table, slot, 0.f, 0.f);   // library data: may overlap the previous kernel's tail
+    pdl_wait();
     constexpr int U = 2;   // 3 measured slower here
     const int64_t total = rows * hidden_chunks;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kLutThreads;
@@ -189,7 +196,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) linear_output_lut_kernel(const
                                                                           const uint4* __restrict__ bias,
                                                                           uint4* __restrict__ out, int64_t chunks,
                                                                           unsigned width_chunks,
-                                                                          int slot) {
+                                                                          int slot, int overlapped) {
     extern __shared__ __align__(16) uint16_t table[];
         constexpr int U = 2;   // registers: U x (8 accumulators + 4 bias); 3 measured slower
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kLutThreads;
@@ -207,8 +214,11 @@ __global__ void __launch_bounds__(kLutThreads, 1) linear_output_lut_kernel(const
             if (has_bias) b[u] = __ldg(bias + static_cast<unsigned>(c) % width_chunks);   // chunks < 2^32
         }
     };
-    request(first);   // before the table copy, so HBM is busy while the table arrives
-    fill_table<OP>(table, slot, 0.f, 0.f);
+    pdl_launch_dependents();
+    if (overlapped) fill_table<OP>(table, slot, 0.f, 0.f);   // see unary_lut_kernel
+    pdl_wait();
+    request(first);   // plain launch: before the table copy, so HBM is busy while the table arrives
+    if (!overlapped) fill_table<OP>(table, slot, 0.f, 0.f);
     for (int64_t i = first; i < chunks; i += stride * U) {
         if (i != first) request(i);
 #pragma unroll
@@ -228,7 +238,7 @@ __global__ void __launch_bounds__(kLutThreads, 1) linear_output_swiglu_lut_kerne
                                                                                  const uint4* __restrict__ bias,
                                                                                  uint4* __restrict__ out, int64_t chunks,
                                                                                  unsigned hidden_chunks,
-                                                                                 int slot) {
+                                                                                 int slot, int overlapped) {
     extern __shared__ __align__(16) uint16_t table[];
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kLutThreads;
     const int64_t first = static_cast<int64_t>(blockIdx.x) * kLutThreads + threadIdx.x;
@@ -243,8 +253,11 @@ __global__ void __launch_bounds__(kLutThreads, 1) linear_output_swiglu_lut_kerne
         g[0] = __ldcs(src + 2 * hidden_chunks); g[1] = __ldcs(src + 2 * hidden_chunks + 1);
         if (has_bias) { ba = __ldg(bias + chunk); bg = __ldg(bias + hidden_chunks + chunk); }
     };
+    pdl_launch_dependents();
+    if (overlapped) fill_table<VRB_SILU>(table, slot, 0.f, 0.f);   // see unary_lut_kernel
+    pdl_wait();
     request(first);
-    fill_table<VRB_SILU>(table, slot, 0.f, 0.f);
+    if (!overlapped) fill_table<VRB_SILU>(table, slot, 0.f, 0.f);
     for (int64_t i = first; i < chunks; i += stride) {
         if (i != first) request(i);
         const uint4 value = biased_pack(a[0], a[1], ba, has_bias), gate = biased_pack(g[0], g[1], bg, has_bias);
@@ -367,6 +380,8 @@ int ready_table(cudaStream_t stream) {
     return slot;
 }
 
+inline int overlapped_now() { return g_launch_overlap.load(std::memory_order_relaxed); }
+
 template <int OP>
 int launch_lut(const void* x, void* out, int64_t count, float p0, float p1, cudaStream_t stream) {
     static bool done[64] = {false};   // one flag set per OP instantiation
@@ -374,8 +389,9 @@ int launch_lut(const void* x, void* out, int64_t count, float p0, float p1, cuda
     const int64_t chunks = count / 8;
     const int64_t per_cta = (chunks + kLutThreads - 1) / kLutThreads;
     const int grid = static_cast<int>(per_cta < sm_count() ? per_cta : sm_count());
-    unary_lut_kernel<OP><<<grid, kLutThreads, kTableBytes, stream>>>(
-        static_cast<const uint4*>(x), static_cast<uint4*>(out), chunks, ready_table<OP>(stream), p0, p1);
+    const int slot = ready_table<OP>(stream);
+    launch_overlapped(unary_lut_kernel<OP>, dim3(grid), dim3(kLutThreads), kTableBytes, stream,
+                      static_cast<const uint4*>(x), static_cast<uint4*>(out), chunks, slot, p0, p1, overlapped_now());
     return after_launch("unary (table)");
 }
 
@@ -405,9 +421,10 @@ int launch_linear_lut(const float* accumulation, const void* bias, void* out, in
     const int64_t chunks = rows * (width / 8);
     const int64_t per_cta = (chunks + kLutThreads - 1) / kLutThreads;
     const int grid = static_cast<int>(per_cta < sm_count() ? per_cta : sm_count());
-    linear_output_lut_kernel<OP><<<grid, kLutThreads, kTableBytes, stream>>>(
-        reinterpret_cast<const float4*>(accumulation), static_cast<const uint4*>(bias), static_cast<uint4*>(out), chunks,
-        static_cast<unsigned>(width / 8), ready_table<OP>(stream));
+    const int slot = ready_table<OP>(stream);
+    launch_overlapped(linear_output_lut_kernel<OP>, dim3(grid), dim3(kLutThreads), kTableBytes, stream,
+                      reinterpret_cast<const float4*>(accumulation), static_cast<const uint4*>(bias), static_cast<uint4*>(out), chunks,
+                      static_cast<unsigned>(width / 8), slot, overlapped_now());
     return after_launch("linear_output_activation (table)");
 }
 
@@ -429,17 +446,19 @@ int launch_linear_output_swiglu_lut(const float* accumulation, const void* bias,
     const int64_t chunks = rows * (hidden / 8);
     const int64_t per_cta = (chunks + kLutThreads - 1) / kLutThreads;
     const int grid = static_cast<int>(per_cta < sm_count() ? per_cta : sm_count());
-    linear_output_swiglu_lut_kernel<<<grid, kLutThreads, kTableBytes, stream>>>(
-        reinterpret_cast<const float4*>(accumulation), static_cast<const uint4*>(bias), static_cast<uint4*>(out), chunks,
-        static_cast<unsigned>(hidden / 8), ready_table<VRB_SILU>(stream));
+    const int slot = ready_table<VRB_SILU>(stream);
+    launch_overlapped(linear_output_swiglu_lut_kernel, dim3(grid), dim3(kLutThreads), kTableBytes, stream,
+                      reinterpret_cast<const float4*>(accumulation), static_cast<const uint4*>(bias), static_cast<uint4*>(out), chunks,
+                      static_cast<unsigned>(hidden / 8), slot, overlapped_now());
     return after_launch("linear_output_swiglu (table)");
 }
 
 int launch_swiglu_lut(const void* proj, void* out, int64_t rows, int64_t hidden, cudaStream_t stream) {
     static bool done[64] = {false};
     if (int rc = reserve_table(swiglu_lut_kernel, done)) return rc;
-    swiglu_lut_kernel<<<sm_count(), kLutThreads, kTableBytes, stream>>>(
-        static_cast<const uint4*>(proj), static_cast<uint4*>(out), rows, hidden / 8, ready_table<VRB_SILU>(stream));
+    const int slot = ready_table<VRB_SILU>(stream);
+    launch_overlapped(swiglu_lut_kernel, dim3(sm_count()), dim3(kLutThreads), kTableBytes, stream,
+                      static_cast<const uint4*>(proj), static_cast<uint4*>(out), rows, hidden / 8, slot);
     return after_launch("swiglu (table)");
 }
 

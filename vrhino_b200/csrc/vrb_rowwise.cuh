@@ -226,6 +226,11 @@ row_kernel(const RowParams p) {
     const bool f32_formula = NORM == kNormRms && !p.rms_f64;
     int parity = 0;
 
+    // nothing below this line may run before the previous kernel of the stream has completed: the
+    // vectors staged next are caller memory like the rows themselves
+    pdl_launch_dependents();
+    pdl_wait();
+
     // LayerNorm weight / bias, already converted to x's dtype, staged once per CTA (same
     // conflict-free layout as the modulation vectors, placed before them)
     const int pad = NCH * tpr * 8;

@@ -42,7 +42,7 @@ void launch_one(const RowParams& p, int64_t ctas, size_t smem, cudaStream_t stre
         }
         per_sm = cached_per_sm[device];
     }
-    row_kernel<NCH, TPR, FULL, NORM, POST, DT><<<grid_for(ctas, per_sm), kRowThreads, smem, stream>>>(p);
+    launch_overlapped(row_kernel<NCH, TPR, FULL, NORM, POST, DT>, dim3(grid_for(ctas, per_sm)), dim3(kRowThreads), smem, stream, p);
 }
 
 #define VRB_DEFINE_ROW_VARIANT(NORM, POST, DT)                                                                       \

@@ -6,6 +6,7 @@ namespace vrb {
 
 std::atomic<uint64_t> g_launches{0};
 std::atomic<uint64_t> g_device_allocations{0};
+std::atomic<int> g_launch_overlap{1};
 
 namespace {
 thread_local char t_error[512] = "";
@@ -38,3 +39,4 @@ extern "C" int vrb_abi_version(void) { return VRB_ABI_VERSION; }
 extern "C" const char* vrb_last_error(void) { return t_error; }
 extern "C" uint64_t vrb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 extern "C" uint64_t vrb_device_allocation_count(void) { return g_device_allocations.load(std::memory_order_relaxed); }
+extern "C" int vrb_set_launch_overlap(int enabled) { return g_launch_overlap.exchange(enabled != 0 ? 1 : 0, std::memory_order_relaxed); }

@@ -111,7 +111,10 @@ class KernelMoments:
 class PeerOutput:
     """The full output tensor of every rank, mapped into every rank (torch symmetric memory):
     the normalise kernel of each rank stores its H-slice straight into all of them, so no
-    all-gather and no placement copy follow.  `ready()` orders the ranks on the current stream."""
+    all-gather and no placement copy follow.  Two orderings, both on the current stream:
+    `acquire()` before the stores -- every rank has finished whatever it was doing with the previous
+    contents of its tensor (work it enqueued before its own acquire), so peers may overwrite it --
+    and `ready()` after them -- every rank's stores have landed before anyone reads the result."""
 
     def __init__(self, shape, dtype, device, group=None):
         import torch.distributed._symmetric_memory as symm
@@ -120,6 +123,9 @@ class PeerOutput:
         self.handle = symm.rendezvous(self.tensor, self.group)
         self.pointers = [int(p) for p in self.handle.buffer_ptrs]
         self._flag = torch.zeros(1, device=device)
+
+    def acquire(self):
+        dist.all_reduce(self._flag, group=self.group)   # every rank's earlier reads precede its contribution
 
     def ready(self):
         dist.all_reduce(self._flag, group=self.group)   # every rank's kernel precedes its contribution
@@ -144,7 +150,11 @@ def sharded_group_norm(pieces, x_local, groups, weight, bias, eps, silu=True, gr
         dist.all_reduce(moments, op=dist.ReduceOp.SUM, group=group)
     mean, inv = pieces.finalize(moments, shift, eps)
     if peer_out is not None:
-        # the "gather" happens in the normalise kernel's stores (peer memory over NVLink)
+        # the "gather" happens in the normalise kernel's stores (peer memory over NVLink).  The
+        # statistics all-reduce above already is the "acquire": no rank gets past it before every rank
+        # has reached it, i.e. has finished the reads of the previous result it enqueued earlier.
+        if world == 1:
+            peer_out.acquire()
         pieces.apply_scatter(x_local, groups, weight, bias, mean, inv, silu, peer_out.pointers, peer_out.tensor.shape[3], row0)
         peer_out.ready()
         return peer_out.tensor

@@ -69,6 +69,32 @@ class WanBlock:
         self.heads, self.eps = heads, 1e-6
         self.out = {}
 
+    # DRAM bytes (read + write) per element the table-driven GELU-tanh kernel moves, from an ncu
+    # capture of one [32760, 8960] bf16 launch (1 124.7 MB for 293.5 M elements: the 4 algorithmic
+    # bytes minus the part of the output still dirty in L2 when the kernel ends); the kernel streams,
+    # so its traffic grows in proportion to the element count.
+    GELU_DRAM_BYTES_PER_ELEMENT = 1_124_700_000 / (32760 * 8960)
+
+    def token_shard(self, rank: int, world: int) -> "WanBlock":
+        """The same block restricted to rank `rank`'s contiguous token rows [r*S/world, (r+1)*S/world)
+        of every per-token tensor (and its rows of the RoPE tables and of the text tokens); vectors
+        shared by all rows are shared with the parent.  The operators are row-independent, so the
+        shard's outputs are the parent's outputs on those rows, bit for bit."""
+        S, T = self.x.shape[1], self.cross_k.shape[1]
+        r0, r1 = rank * S // world, (rank + 1) * S // world
+        t0, t1 = rank * T // world, (rank + 1) * T // world
+        blk = object.__new__(WanBlock)
+        blk.__dict__.update(self.__dict__)
+        for name in ("x", "q", "k", "proj", "cross_q", "cross", "ffn_out", "ffn_hidden"):
+            setattr(blk, name, getattr(self, name)[:, r0:r1].contiguous())
+        blk.cross_k = self.cross_k[:, t0:t1].contiguous()
+        d = self.cos.shape[-1]
+        blk.cos = self.cos.reshape(S, d)[r0:r1].reshape(1, r1 - r0, 1, d).contiguous()
+        blk.sin = self.sin.reshape(S, d)[r0:r1].reshape(1, r1 - r0, 1, d).contiguous()
+        blk.out = {}
+        blk.token_rows, blk.text_rows = (r0, r1), (t0, t1)
+        return blk
+
     def launches(self, fuse_residual_norm: bool = False) -> List[Launch]:
         """fuse_residual_norm: C+D and F+G each as ONE launch (residual update + the LayerNorm that
         reads the updated stream, wan.cpp:95-107 of the reference) -- 9 launches instead of 11.  Such a
@@ -124,6 +150,38 @@ class WanBlock:
             Launch("H gelu_tanh", H, self.ffn_hidden.numel() * 4),
             Launch("I gated_residual", I, act * (hb + 2 + hb) + vec),
         ]
+
+
+def compile_launches(launches: List[Launch]) -> List[Launch]:
+    """The same launches with the Python above the C ABI taken out of the loop: every launch is run
+    once while the C-ABI calls it makes are recorded (entry point + argument objects, the current
+    stream included), and the returned launches replay exactly those calls.  Outputs must already
+    exist (run every launch once before), so that the recorded pointers stay valid; the tensors are
+    kept alive by the original launches' closures.  Replay on the stream that was current here."""
+    from . import _lib
+    lib = _lib.load()
+    compiled = []
+    for l in launches:
+        calls = []
+        original = ops.call
+
+        def recording(name, *args, _calls=calls):
+            _calls.append((getattr(lib, name), args, name))
+            original(name, *args)
+
+        ops.call = recording
+        try:
+            l.fn()
+        finally:
+            ops.call = original
+
+        def replay(_calls=calls, _keep=l.fn):
+            for fn, args, name in _calls:
+                if fn(*args) != 0:
+                    _lib.check(-1)
+
+        compiled.append(Launch(l.name, replay, l.bytes, l.kernels))
+    return compiled
 
 
 def time_launches(launches: List[Launch], steps: int, warmup: int):
@@ -429,7 +487,9 @@ def _main():
 
 class WanBlockHost:
     """The same chain with every operand in page-locked HOST memory, run through the host-buffer
-    entry points of the C ABI (upload, kernel, download pipelined inside each call)."""
+    entry points of the C ABI (upload, kernel, download pipelined inside each call).  A batched block
+    (both CFG branches) is run branch by branch: each branch has its own modulation vectors, and the
+    host entry points take one vector set per call."""
 
     def __init__(self, blk: WanBlock):
         import ctypes
@@ -446,7 +506,7 @@ class WanBlockHost:
         self.rows = [pin(r) for r in blk.rows]
         self.wq, self.wk, self.wcq, self.wck = pin(blk.wq), pin(blk.wk), pin(blk.wcq), pin(blk.wck)
         self.gamma3, self.beta3 = pin(blk.gamma3), pin(blk.beta3)
-        S = blk.x.shape[1]
+        B, S = blk.x.shape[0], blk.x.shape[1]
         self.cos, self.sin = pin(blk.cos.reshape(S, -1)), pin(blk.sin.reshape(S, -1))
         hd = blk.x.dtype
 
@@ -457,9 +517,9 @@ class WanBlockHost:
         self.out.update({k: out_like(self.x, hd) for k in ("C", "F", "I")})
         self.out["Ek"] = out_like(self.cross_k)
         self.out["H"] = out_like(self.ffn_hidden)
-        ins = [self.x] * 6 + [self.q, self.k, self.proj, self.cross_q, self.cross_k, self.cross, self.ffn_out, self.ffn_hidden,
-                              self.cos, self.sin, self.cos, self.sin]
-        self.h2d_bytes = _nbytes(*ins) + 6 * self.rows[0].numel() * 4 + 6 * self.wq.numel() * 4
+        ins = [self.x] * 6 + [self.q, self.k, self.proj, self.cross_q, self.cross_k, self.cross, self.ffn_out, self.ffn_hidden] + \
+              [self.cos, self.sin, self.cos, self.sin] * B
+        self.h2d_bytes = _nbytes(*ins) + B * (6 * self.rows[0][0].numel() * 4 + 6 * self.wq.numel() * 4)
         self.d2h_bytes = _nbytes(*self.out.values())
         self.bytes_per_step = sum(l.bytes for l in blk.launches())
 
@@ -467,34 +527,38 @@ class WanBlockHost:
         P = lambda t: None if t is None else self._c.c_void_p(t.data_ptr())
         code = lambda t: 0 if t is None else (2 if t.dtype == BF16 else 0)
         call, o, r = self._lib.call, self.out, self.rows
-        S, D = self.x.shape[1], self.x.shape[2]
+        B, S, D = self.x.shape
         eps = self._c.c_float(1e-6)
         F = self.ffn_hidden.shape[-1]
         T = self.cross_k.shape[1]
         d = self.cos.shape[-1]
+        for b in range(B):
+            x = self.x[b]
 
-        def ln_mod(out, shift, scale, w=None, b=None):
-            call("vrb_host_layer_norm_modulate", P(self.x), code(self.x), P(w), code(w), P(b), code(b), P(scale), P(shift), 0,
-                 P(out), code(out), S, D, eps)
+            def ln_mod(out, shift, scale, w=None, bias=None):
+                call("vrb_host_layer_norm_modulate", P(x), code(x), P(w), code(w), P(bias), code(bias),
+                     None if scale is None else P(scale[b]), None if shift is None else P(shift[b]), 0,
+                     P(out[b]), code(out), S, D, eps)
 
-        def rms_rope(x, w, out, rows, rope=True):
-            call("vrb_host_rms_norm_rope", P(x), code(x), P(w), 0, P(self.cos) if rope else None, P(self.sin) if rope else None,
-                 d, P(out), code(out), rows, D, D, eps)
+            def rms_rope(src, w, out, rows, rope=True):
+                call("vrb_host_rms_norm_rope", P(src[b]), code(src), P(w), 0, P(self.cos) if rope else None, P(self.sin) if rope else None,
+                     d, P(out[b]), code(out), rows, D, D, eps)
 
-        def gated(branch, gate, out):
-            call("vrb_host_gated_residual", P(self.x), code(self.x), P(branch), code(branch), P(gate), 0, P(out), code(out), S, D)
+            def gated(branch, gate, out):
+                call("vrb_host_gated_residual", P(x), code(x), P(branch[b]), code(branch), None if gate is None else P(gate[b]), 0,
+                     P(out[b]), code(out), S, D)
 
-        ln_mod(o["A"], r[0], r[1])
-        rms_rope(self.q, self.wq, o["Bq"], S)
-        rms_rope(self.k, self.wk, o["Bk"], S)
-        gated(self.proj, r[2], o["C"])
-        ln_mod(o["D"], None, None, self.gamma3, self.beta3)
-        rms_rope(self.cross_q, self.wcq, o["Eq"], S, rope=False)
-        rms_rope(self.cross_k, self.wck, o["Ek"], T, rope=False)
-        gated(self.cross, None, o["F"])
-        ln_mod(o["G"], r[3], r[4])
-        call("vrb_host_activation", 2, P(self.ffn_hidden), P(o["H"]), 2, S, F)
-        gated(self.ffn_out, r[5], o["I"])
+            ln_mod(o["A"], r[0], r[1])
+            rms_rope(self.q, self.wq, o["Bq"], S)
+            rms_rope(self.k, self.wk, o["Bk"], S)
+            gated(self.proj, r[2], o["C"])
+            ln_mod(o["D"], None, None, self.gamma3, self.beta3)
+            rms_rope(self.cross_q, self.wcq, o["Eq"], S, rope=False)
+            rms_rope(self.cross_k, self.wck, o["Ek"], T, rope=False)
+            gated(self.cross, None, o["F"])
+            ln_mod(o["G"], r[3], r[4])
+            call("vrb_host_activation", 2, P(self.ffn_hidden[b]), P(o["H"][b]), 2, S, F)
+            gated(self.ffn_out, r[5], o["I"])
 
 
 if __name__ == "__main__":
