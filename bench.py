@@ -6,7 +6,7 @@
 N > 1 is launched with torch.distributed.run, one rank per GPU (NCCL).
 
 A step = one pass of the chain over ONE batch: both classifier-free-guidance branches of one DiT
-block (11 fused launches over [2, 32760, 1536], FFN 8960; synthetic, seeded data).  The path
+block (9 fused launches over [2, 32760, 1536], FFN 8960; synthetic, seeded data).  The path
 partitions by token rows and needs no collective: with N ranks the SAME batch is split into N
 contiguous token ranges, one per rank ("scaling": "strong"), and `value` is the batch's algorithmic
 bytes divided by the slowest rank's time.  Outside the timed region every rank also runs the whole
@@ -44,7 +44,9 @@ METRIC = "fused-op HBM GB/s (Wan2.1-1.3B DiT-block non-GEMM chain)"
 UNIT = "GB/s"
 WORKLOAD = {
     "workload": "wan2.1-1.3b dit block non-gemm chain, batch 2 (cfg)", "tokens": 32760, "dim": 1536, "heads": 12,
-    "head_dim": 128, "ffn": 8960, "hidden_dtype": "bf16", "launches_per_step": 11,
+    "head_dim": 128, "ffn": 8960, "hidden_dtype": "bf16", "launches_per_step": 9,
+    "launches": "LN+modulate, RMS+RoPE(q,k as one launch), gated residual, LN affine, RMS(cross q, text k as one launch), "
+                "residual add, LN+modulate, GELU-tanh, gated residual",
     "batching": "both CFG branches as one [2, 32760, 1536] batch, one modulation vector set per branch",
     "sharding": "N ranks: the same batch split into N contiguous token ranges, no collective on the data path",
     "l2": "every launch streams 0.2-1.2 GB of distinct tensors (> 126 MB L2) at N=1; no flush needed",
@@ -230,8 +232,8 @@ def main():
     # ---- the batch: identical on every rank (same seed); rank r works on its token rows ----------
     whole = workloads.WanBlock(be, seed=0, batch=2)
     work = whole if world == 1 else whole.token_shard(rank, world)
-    step_bytes = sum(l.bytes for l in whole.launches())          # the whole batch, whatever N
-    python_launches = work.launches()
+    step_bytes = sum(l.bytes for l in whole.launches(pair_qk=True))          # the whole batch, whatever N
+    python_launches = work.launches(pair_qk=True)
     for l in python_launches:
         l.fn()                                                   # allocates the outputs
     torch.cuda.synchronize()
@@ -327,7 +329,7 @@ def main():
     e2e_obj = {"value": step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
                "h2d_bytes_per_step": total_over_ranks(e2e.h2d_bytes), "d2h_bytes_per_step": total_over_ranks(e2e.d2h_bytes),
                "ms_per_step": e2e_ms,
-               "note": "the same step (both CFG branches, 22 host-buffer calls; each rank its token rows), pinned host buffers, "
+               "note": "the same step's operators (both CFG branches, 22 host-buffer calls; each rank its token rows), pinned host buffers, "
                        "3-stream upload/kernel/download pipeline per call"}
     lib.vrb_host_release()
 

@@ -316,6 +316,18 @@ int vrb_rms_norm_rope_tables(const void* x, int x_dtype, const void* weight, int
                              int64_t f_width, int64_t rows_per_f_row, void* out, int out_dtype,
                              int64_t rows, int64_t width, int64_t norm_width, float eps, vrb_stream stream);
 
+/* vrb_rms_norm_rope_tables on TWO tensors in one launch: the q and k projections of an attention block
+ * (native/src/architectures/wan.cpp:38-52 normalises and rotates q, then k; the cross-attention q and
+ * its text-token k at :38-46 are the cosine == NULL form with different row counts).  Both share
+ * dtypes, widths, eps and tables; each has its own tensor, norm weight and row count, and row r of
+ * either uses table row (r / rows_per_f_row) % f_rows.  Results are bit-identical to two calls of
+ * vrb_rms_norm_rope_tables; what is saved is a launch, and the tables are fetched from HBM once. */
+int vrb_rms_norm_rope_pair(const void* x_a, const void* weight_a, void* out_a, int64_t rows_a,
+                           const void* x_b, const void* weight_b, void* out_b, int64_t rows_b,
+                           int x_dtype, int weight_dtype, const void* cosine, const void* sine, int table_dtype,
+                           int64_t f_rows, int64_t f_width, int64_t rows_per_f_row, int out_dtype,
+                           int64_t width, int64_t norm_width, float eps, vrb_stream stream);
+
 /* gated_residual (common.cpp:139-144) and, with gate == NULL, residual_add (:134-138):
  * out = T(residual) + round_T(T(branch) * T(gate)), T = state_dtype.  gate is
  * [gate_vectors, width]; row r uses vector (r / rows_per_vector) % gate_vectors. */

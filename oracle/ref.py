@@ -111,6 +111,24 @@ class RefHost:
         keys = ("layer_norm_modulate", "rms_norm_modulate", "rms_norm_rope", "gated_residual", "nodes_total", "nodes_absorbed")
         return dict(zip(keys, out))
 
+    CODES = ("UnsupportedSchema", "UnsupportedPrimitive", "InvalidOperation", "LimitExceeded", "InvalidShape", "InvalidDType",
+             "InvalidValue", "InvalidDependency", "InvalidInputBinding", "InvalidParameterBinding", "InvalidContext",
+             "BackendFailure", "InvalidNodeOutput", "CompletionFailure", "InvalidOutput")
+    PHASES = ("Admit", "Bind", "Run", "Drain", "Capture")
+
+    def fused_faults(self, scenario, tokens=4, n=0):
+        """vrhino_b200::evaluate_fused under a failure injected on the host (see refh_fused_faults in
+        ref_host.cpp).  Returns a dict: threw, code, phase, node, value, primitive, syncs,
+        secondary_completion, calls, outputs, text."""
+        report = (_c.c_int64 * 10)()
+        if self.lib.refh_fused_faults(int(scenario), _c.c_int64(tokens), int(n), report) != 0:
+            raise RuntimeError(self.lib.refh_last_error().decode())
+        r = list(report)
+        loc = lambda v: None if v < 0 else v
+        return {"threw": bool(r[0]), "code": self.CODES[r[1]] if r[0] else None, "phase": self.PHASES[r[2]] if r[0] else None,
+                "node": loc(r[3]), "value": loc(r[4]), "primitive": loc(r[5]), "syncs": r[6], "secondary_completion": bool(r[7]),
+                "calls": r[8], "outputs": r[9], "text": self.lib.refh_last_error().decode() if r[0] else ""}
+
     def wan_chain_seconds(self, tokens, threads, steps, dim=1536, heads=12, ffn=8960, text=512, seed=0):
         """Seconds per step of the Wan block chain on `tokens` rows, and its algorithmic bytes
         (same accounting as the GPU arm, bf16-hidden contract, so the GB/s are comparable)."""
@@ -276,8 +294,29 @@ class RefDropin(RefCuda):
         for name in ("refd_layer_norm_modulate", "refd_rms_norm_rope", "refd_gated_residual", "refd_swiglu",
                      "refd_group_norm_silu", "refd_cfg_euler", "refd_gated_residual_layer_norm",
                      "refd_linear_activation", "refd_linear_gated_residual", "refd_linear_swiglu",
-                     "refd_pixel_norm_modulate_silu", "refd_depth_to_space_residual"):
+                     "refd_pixel_norm_modulate_silu", "refd_depth_to_space_residual", "refd_profile_report",
+                     "refd_dequantize_repeated", "refd_release_cached"):
             getattr(self.lib, name).restype = _c.c_int64
+
+    def profile(self, enabled): self.lib.refc_profile(int(enabled))
+    def profile_report(self):
+        """{name: (calls, device ms, bytes moved)} of the wrapped backend's profile_stats()."""
+        buf = _c.create_string_buffer(1 << 20)
+        self._h(self.lib.refd_profile_report(buf, _c.c_int64(len(buf))))
+        out = {}
+        for line in buf.value.decode().splitlines():
+            name, calls, ms, nbytes = line.split("\t")
+            out[name] = (int(calls), float(ms), int(nbytes))
+        return out
+    def dequantize_repeated(self, kind, packed, scales, rows, inner, group_size, out_dtype, repeats, budget=-1):
+        """(handle of the last result, {hits, misses, resident_bytes})"""
+        p = np.ascontiguousarray(packed, dtype=np.uint8); s = _f(scales)
+        stats = (_c.c_int64 * 3)()
+        h = self._h(self.lib.refd_dequantize_repeated(int(kind), _c.c_void_p(p.ctypes.data), _c.c_int64(p.nbytes), _ptr(s),
+                                                      _c.c_int64(rows), _c.c_int64(inner), _c.c_int64(group_size), int(out_dtype),
+                                                      int(repeats), _c.c_int64(budget), stats))
+        return h, {"hits": stats[0], "misses": stats[1], "resident_bytes": stats[2]}
+    def release_cached(self): return self._h(self.lib.refd_release_cached())
 
     def name(self): return self.lib.refc_backend_name().decode()
     def session_terminal(self): return bool(self.lib.refd_session_terminal())

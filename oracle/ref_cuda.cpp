@@ -288,6 +288,58 @@ int64_t refd_cfg_euler(int64_t x, int64_t u, int64_t c, float guidance, float de
         return keep(g_backend->cfg_euler(at(x), at(u), at(c), guidance, delta, subtract != 0, guidance_role != 0, solver_role != 0));
     });
 }
+// profile_stats() of the wrapped backend as text, one "name\tcalls\tdevice ms\tbytes" line per entry
+// (bytes from B200Backend::profile_bytes(), 0 for entries the device runtime recorded itself).
+int64_t refd_profile_report(char* buffer, int64_t capacity) {
+    return guarded([&] {
+        std::string text;
+        const auto& bytes = g_backend->profile_bytes();
+        for (const auto& [name, stat] : g_backend->profile_stats()) {
+            const auto found = bytes.find(name);
+            text += name + "\t" + std::to_string(stat.calls) + "\t" + std::to_string(stat.device_milliseconds) + "\t" +
+                    std::to_string(found == bytes.end() ? 0 : found->second) + "\n";
+        }
+        require(static_cast<int64_t>(text.size()) < capacity, "profile report buffer too small");
+        std::memcpy(buffer, text.c_str(), text.size() + 1);
+        return static_cast<int64_t>(text.size());
+    });
+}
+// ONE quantised host weight uploaded `repeats` times (what linear() does with a quantised weight on
+// every call, cuda_backend.cu:3276-3295); stats = {cache hits, misses, resident bytes} of the
+// dequantised-weight cache afterwards.  budget < 0 keeps the current budget.
+int64_t refd_dequantize_repeated(int type, const uint8_t* packed, int64_t packed_bytes, const float* scales, int64_t rows,
+                                 int64_t inner, int64_t group_size, int out_dtype, int repeats, int64_t budget, int64_t* stats) {
+    return guarded([&] {
+        if (budget >= 0) g_backend->set_dequantized_cache_budget(static_cast<size_t>(budget));
+        static std::vector<std::shared_ptr<std::vector<uint8_t>>> payloads;   // host weights outlive their cache entries
+        auto payload = std::make_shared<std::vector<uint8_t>>(packed, packed + packed_bytes);
+        payloads.push_back(payload);
+        Tensor weight = Tensor::borrowed(payload->data(), payload->size(), {rows, inner}, DType::U8);
+        auto info = std::make_shared<QuantizationInfo>();
+        info->type = type == 0 ? QuantType::FP8E4M3FN : type == 1 ? QuantType::INT8Symmetric : QuantType::INT4Symmetric;
+        info->logical_dtype = DType::BF16; info->compute_dtype = DType::BF16; info->accumulation_dtype = DType::F32;
+        info->group_size = group_size; info->axis = 1; info->symmetric = true;
+        info->granularity = group_size == inner ? "per_channel" : "per_group";
+        info->zero_point_mode = "none";
+        info->packing_layout = type == 0 ? "byte_e4m3fn" : type == 1 ? "byte_twos_complement" : "nibble_low_first_twos_complement";
+        const int64_t groups = (inner + group_size - 1) / group_size;
+        info->scales = host_f32({rows, groups}, std::vector<float>(scales, scales + rows * groups));
+        weight.set_quantization(info);
+        Tensor out;
+        for (int i = 0; i < repeats; ++i) out = g_backend->copy_to_device(weight, static_cast<DType>(out_dtype));
+        g_backend->synchronize();
+        stats[0] = static_cast<int64_t>(g_backend->dequantized_cache_hits());
+        stats[1] = static_cast<int64_t>(g_backend->dequantized_cache_misses());
+        stats[2] = static_cast<int64_t>(g_backend->dequantized_cache_resident_bytes());
+        return keep(out);
+    });
+}
+int64_t refd_release_cached() {
+    return guarded([&] {
+        g_backend->release_cached_device_memory();
+        return static_cast<int64_t>(g_backend->dequantized_cache_resident_bytes());
+    });
+}
 // An operator failure must leave the session terminal, like the reference's (memory.h:225-236).
 int refd_session_terminal() { return g_backend && g_backend->resource_session_terminal() ? 1 : 0; }
 #else

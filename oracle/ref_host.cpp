@@ -181,4 +181,107 @@ int refh_fusion_plan(int which, int contract, int diagnostics, int64_t tokens, i
     } catch (const std::exception& e) { g_error = e.what(); return -1; }
 }
 
+
+// ---- failure semantics of vrhino_b200::evaluate_fused, exercised on the host --------------------
+// The fused chains are stood in for by compositions of the reference's own seams over the test
+// backends, so a failure can be injected into any backend call -- inside a fused chain too --
+// without a GPU: TinyBackend (native/tests/neural_graph_test_backend.h) throws at its fail_call-th
+// primitive, returns broken metadata at its fault_call-th, and fails its synchronize() on request.
+namespace {
+struct SeamFused final : vrhino_b200::FusedOperators {
+    Backend& be;
+    std::vector<Tensor> interior;   // the test backends want every tensor they produced alive until the drain
+    Tensor hold(Tensor t) { interior.push_back(t); return t; }
+    PrecisionPolicy policy = PrecisionPolicy::fp32();
+    explicit SeamFused(Backend& b) : be(b) {}
+    Backend& backend() override { return be; }
+    Tensor layer_norm_modulate(const Tensor& x, const Tensor* w, const Tensor* b, float eps, const Tensor& shift, const Tensor& scale,
+                               DType output) override {
+        return be.cast(hold(modulate(be, policy, hold(be.layer_norm(x, w, b, eps)), shift, scale)), output);
+    }
+    Tensor rms_norm_modulate(const Tensor& x, float eps, const Tensor& shift, const Tensor& scale, DType output) override {
+        return be.cast(hold(modulate(be, policy, hold(be.rms_norm(x, nullptr, eps, -1, DType::F16)), shift, scale)), output);
+    }
+    Tensor rms_norm_rope(const Tensor& x, const Tensor* w, float eps, const Tensor* c, const Tensor* s, int heads, DType output) override {
+        Tensor n = hold(be.rms_norm(x, w, eps, -1, DType::F16));
+        Tensor split = hold(be.reshape(n, {x.dim(0), x.dim(1), heads, x.dim(2) / heads}));
+        return be.cast(hold(be.reshape(hold(be.rope_nd(split, *c, *s)), x.shape())), output);
+    }
+    Tensor gated_residual(const Tensor& residual, const Tensor& branch, const Tensor* gate, DType state) override {
+        Tensor update = gate ? hold(be.mul(branch, *gate)) : branch;
+        Tensor sum = hold(be.add(residual, update));
+        return sum.dtype() == state ? sum : be.cast(sum, state);
+    }
+};
+
+Tensor filled(const std::vector<int64_t>& shape, float value) {
+    Tensor t = Tensor::host(shape, DType::F32);
+    for (int64_t i = 0; i < t.numel(); ++i) t.data_as<float>()[i] = value + 0.001f * static_cast<float>(i % 7);
+    return t;
+}
+}  // namespace
+
+// scenario 0: the reference's Wan self-attention graph (F32 contract, dim 64, 2 heads, `tokens` rows) on
+//             family_test::Backend, its `n`-th primitive call throwing (n == 0: no failure);
+// scenario 1: res + branch * gate (one fused gated residual) on TinyBackend with a failing drain;
+// scenario 2: the same, first primitive throwing AND the drain failing;
+// scenario 3: the same, the fused result coming back with the wrong shape;
+// scenario 4: the same, first primitive throwing something that is not a std::exception.
+// report: {threw, code, phase, node, value, primitive, synchronize calls, secondary completion recorded,
+//          primitive calls made, outputs returned}; -1 stands for "no location".
+int refh_fused_faults(int scenario, int64_t tokens, int n, int64_t* report) {
+    namespace ng = neural_graph;
+    for (int i = 0; i < 10; ++i) report[i] = 0;
+    auto note = [&](const ng::GraphError& e) {
+        report[0] = 1; report[1] = static_cast<int64_t>(e.code); report[2] = static_cast<int64_t>(e.phase);
+        report[3] = e.node ? static_cast<int64_t>(*e.node) : -1;
+        report[4] = e.value ? static_cast<int64_t>(*e.value) : -1;
+        report[5] = e.primitive ? static_cast<int64_t>(*e.primitive) : -1;
+        report[7] = e.secondary_completion.empty() ? 0 : 1;
+        g_error = e.what();
+    };
+    try {
+        if (scenario == 0) {
+            wan_family::Config config;
+            config.dim = 64; config.heads = 2;
+            const ng::Graph graph = wan_internal::self_attention_graph(1, tokens, DType::F32, DType::F32, false, config);
+            const ng::Description& d = graph.description();
+            std::vector<Tensor> inputs, parameters;
+            for (ng::ValueId id : d.inputs) inputs.push_back(filled(d.values[id].shape, 0.05f));
+            for (ng::ValueId id : d.parameters) parameters.push_back(filled(d.values[id].shape, 0.01f));
+            family_test::Backend be;
+            be.fail_call = static_cast<size_t>(n);
+            SeamFused fused(be);
+            try {
+                report[9] = static_cast<int64_t>(vrhino_b200::evaluate_fused(fused, graph, inputs, parameters).size());
+            } catch (const ng::GraphError& e) { note(e); }
+            report[6] = static_cast<int64_t>(be.syncs);
+            report[8] = static_cast<int64_t>(be.calls.size());
+            return 0;
+        }
+        ng::Description d;
+        d.schema = ng::schema_v1;
+        d.execution_dtype = DType::F32;
+        d.values = {{{1, 4, 8}}, {{1, 4, 8}}, {{1, 1, 8}}, {{1, 4, 8}}, {{1, 4, 8}}};
+        d.inputs = {0, 1};
+        d.parameters = {2};
+        d.nodes = {{3, ng::Mul{1, 2}}, {4, ng::Add{0, 3}}};
+        d.outputs = {4};
+        const ng::Graph graph = ng::admit(d);
+        ng::test::TinyBackend be;
+        be.fail_sync = scenario == 1 || scenario == 2;
+        if (scenario == 2 || scenario == 4) be.fail_call = 1;
+        be.throw_nonstandard = scenario == 4;
+        if (scenario == 3) { be.fault = ng::test::TinyBackend::Fault::Shape; be.fault_call = 2; }
+        SeamFused fused(be);
+        try {
+            report[9] = static_cast<int64_t>(
+                vrhino_b200::evaluate_fused(fused, graph, {filled({1, 4, 8}, 1.f), filled({1, 4, 8}, 2.f)}, {filled({1, 1, 8}, 3.f)}).size());
+        } catch (const ng::GraphError& e) { note(e); }
+        report[6] = static_cast<int64_t>(be.syncs);
+        report[8] = static_cast<int64_t>(be.calls.size());
+        return 0;
+    } catch (const std::exception& e) { g_error = e.what(); return -1; }
+}
+
 }  // extern "C"

@@ -44,7 +44,7 @@ def test_reference_call_sites_on_the_replaced_backend(orc, golden, dropin, case)
     got = cases.run_reference(dropin, case)
     assert set(got) == set(want)
     for name in want:
-        compare(orc, case, name, got[name], want[name], strict_tables=True)
+        compare(orc, case, name, got[name], want[name], strict_tables=True, who="library (C++ drop-in backend)")
 
 
 def _upload(rd, case):
@@ -376,3 +376,67 @@ def test_merged_linear_forms_on_a_dense_gemm(orc, dropin):
             assert diff.max() <= 2.0 ** -8 * 8.0, f"{name}: max difference {diff.max()}"
     finally:
         rd.clear()
+
+
+def test_replaced_operators_appear_in_profile_stats_under_the_reference_names(dropin):
+    """The reference's operators record themselves in profile_stats() (cuda_backend.cu:3011-3064, e.g.
+    "norm.layer|rows=..|width=..|dtype=.." :4073-4076).  The replaced operators keep those names, and
+    the backend adds the bytes each one moved."""
+    from oracle import ref
+    rd = dropin
+    rng = np.random.default_rng(5)
+    x = rd.upload(cases.to_bits(rng.standard_normal((1, 40, 1536)).astype(np.float32), "bf16"), ref.BF16)
+    w = rd.upload(rng.standard_normal(1536).astype(np.float32), ref.F32)
+    rd.profile(True)
+    try:
+        made = [rd.layer_norm(x, None, None, 1e-6), rd.rms_norm(x, w, 1e-6), rd.activation(x, 2), rd.binary(0, x, x),
+                rd.cast(x, ref.F32), rd.clamp(x, -1.0, 1.0),
+                rd.fused_layer_norm_modulate(ref.POLICY_BF16, x, None, None, 1e-6,
+                                             rd.upload(rng.standard_normal((1, 1, 1536)).astype(np.float32), ref.F32),
+                                             rd.upload(rng.standard_normal((1, 1, 1536)).astype(np.float32), ref.F32))]
+        report = rd.profile_report()
+    finally:
+        rd.profile(False)
+    nbytes = 40 * 1536 * 2
+    expected = {
+        "norm.layer|rows=40|width=1536|dtype=bfloat16": 2 * nbytes,
+        "norm.rms|rows=40|width=1536|axis=2|dtype=bfloat16": 2 * nbytes,
+        "activation|elements=61440|kind=2|dtype=bfloat16": 2 * nbytes,
+        "elementwise.add": 3 * nbytes,
+        "cast": 3 * nbytes,
+        "clamp": 2 * nbytes,
+        "fused.norm.layer+modulate": 2 * nbytes,
+    }
+    for name, moved in expected.items():
+        assert name in report, (name, sorted(report))
+        calls, ms, recorded = report[name]
+        assert calls >= 1 and ms > 0.0 and recorded >= moved, (name, report[name])
+    for h in made:
+        rd.free(h)
+
+
+def test_dequantised_weight_is_decoded_once(dropin):
+    """linear() on a quantised weight uploads and decodes it on every call in the reference
+    (cuda_backend.cu:3276-3295); the replaced backend keeps the decoded weight, within a byte budget,
+    until release_cached_device_memory()."""
+    from oracle import ref
+    rd = dropin
+    rng = np.random.default_rng(6)
+    rows, inner = 64, 256
+    packed = rng.integers(0, 254, size=(rows, inner)).astype(np.uint8)
+    scales = rng.uniform(1e-3, 1e-2, size=(rows, 1)).astype(np.float32)
+    once = rd.dequantize(0, packed, scales, rows, inner, inner, ref.BF16)
+    want, _ = rd.download(once, (rows, inner))
+    _, before = rd.dequantize_repeated(0, packed, scales, rows, inner, inner, ref.BF16, repeats=0)
+    h, after = rd.dequantize_repeated(0, packed, scales, rows, inner, inner, ref.BF16, repeats=3)
+    got, _ = rd.download(h, (rows, inner))
+    assert np.array_equal(got, want)
+    assert after["misses"] - before["misses"] == 1 and after["hits"] - before["hits"] == 2
+    assert after["resident_bytes"] >= rows * inner * 2
+    assert rd.release_cached() == 0
+    # a budget smaller than the weight: decoded per call, nothing kept
+    h2, small = rd.dequantize_repeated(0, packed, scales, rows, inner, inner, ref.BF16, repeats=2, budget=1024)
+    assert small["hits"] == after["hits"] and small["misses"] - after["misses"] == 2 and small["resident_bytes"] == 0
+    got2, _ = rd.download(h2, (rows, inner))
+    assert np.array_equal(got2, want)
+    rd.dequantize_repeated(0, packed, scales, rows, inner, inner, ref.BF16, repeats=0, budget=48 << 30)

@@ -81,3 +81,41 @@ def test_token_shards_concatenate_to_the_whole_block(gpu, world):
             want = whole[k][:, t0:t1] if k == "Ek" else whole[k][:, r0:r1]
             view = torch.int16 if v.dtype == torch.bfloat16 else torch.int32
             assert torch.equal(v.view(view), want.contiguous().view(view)), (rank, k)
+
+
+def test_pair_launch_equals_two_launches(gpu):
+    """q and k (and the cross-attention q and text-token k, whose row counts differ) normalised and
+    rotated by one launch: the same bits as one launch each; so is the whole chain with pairs."""
+    import torch
+    from vrhino_b200 import workloads
+    be, ops = gpu
+    blk = workloads.WanBlock(be, tokens=2080, grid=(2, 26, 40), ffn=1024, text_tokens=77, seed=23, batch=2)
+    for l in blk.launches():
+        l.fn()
+    separate = _outputs(blk)
+    for v in blk.out.values():
+        v.zero_()
+    names = [l.name for l in blk.launches(pair_qk=True)]
+    assert len(names) == 9 and "B rms_rope q+k" in names and "E rms cross q+k" in names
+    for l in blk.launches(pair_qk=True):
+        l.fn()
+    _same(separate, _outputs(blk), "pair launches")
+    # per-head norm with per-head tables (the Mochi form), F32 output
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q, k = (torch.randn((1, 300, 24 * 128), device="cuda", generator=g).to(torch.bfloat16) for _ in range(2))
+    wq, wk = (torch.randn(128, device="cuda", generator=g) * 0.1 + 1 for _ in range(2))
+    phase = torch.rand((1, 300, 24, 128), device="cuda", generator=g) * 6.28
+    cos, sin = torch.cos(phase), torch.sin(phase)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        a = ops.fused_rms_norm_rope(be, q, wq, 1e-5, cos, sin, heads=24, per_head_norm=True, out_dtype=out_dtype)
+        b = ops.fused_rms_norm_rope(be, k, wk, 1e-5, cos, sin, heads=24, per_head_norm=True, out_dtype=out_dtype)
+        pa, pb = ops.fused_rms_norm_rope_pair(be, q, wq, k, wk, 1e-5, cos, sin, heads=24, per_head_norm=True, out_dtype=out_dtype)
+        view = torch.int16 if out_dtype == torch.bfloat16 else torch.int32
+        assert torch.equal(a.view(view), pa.view(view)) and torch.equal(b.view(view), pb.view(view)), out_dtype
+    # one row against many rows: the reference would pick different summation formulas, so the entry
+    # point falls back to two launches -- still the same results
+    one = q[:, :1].contiguous()
+    a = ops.fused_rms_norm_rope(be, one, wq.repeat(24), 1e-6, None, None)
+    pa, pb = ops.fused_rms_norm_rope_pair(be, one, wq.repeat(24), k, wk.repeat(24), 1e-6, None, None)
+    assert torch.equal(a.view(torch.int16), pa.view(torch.int16))
+    assert torch.equal(ops.fused_rms_norm_rope(be, k, wk.repeat(24), 1e-6, None, None).view(torch.int16), pb.view(torch.int16))

@@ -38,3 +38,32 @@ def test_ltx_production_graph(host, contract):
     diag = host.fusion_plan("ltx", contract, diagnostics=True)
     # the diagnostics graph exports the norm, the modulated input and the positioned q / k
     assert diag["rms_norm_modulate"] == 0 and diag["rms_norm_rope"] == 0
+
+
+def test_evaluate_fused_reports_failures_like_the_reference_evaluator(host):
+    """neural_graph::evaluate reports every failure as a GraphError with code, phase and the node /
+    value / primitive at work, and drains the device once if work may be in flight
+    (native/src/runtime/neural_graph_evaluator.cpp:84-93, :162-175).  evaluate_fused does the same;
+    the failures are injected on the host through the reference's own test backends."""
+    clean = host.fused_faults(0, tokens=4, n=0)
+    assert not clean["threw"] and clean["outputs"] == 2 and clean["syncs"] == 1
+    calls = clean["calls"]
+    assert calls > 10
+    seen_nodes = set()
+    for n in range(1, calls + 1):                       # a failure in every single backend call of the graph
+        r = host.fused_faults(0, tokens=4, n=n)
+        assert r["threw"] and r["code"] == "BackendFailure" and r["phase"] == "Run", (n, r)
+        assert r["node"] is not None and r["value"] is not None and r["primitive"] is not None, (n, r)
+        assert r["syncs"] == 1, (n, r)                   # drained exactly once after the failure
+        assert "injected primitive failure" in r["text"]
+        seen_nodes.add(r["node"])
+    assert len(seen_nodes) >= 8                          # failures were attributed to many different nodes
+    r = host.fused_faults(1)                             # the drain itself fails
+    assert r["threw"] and r["code"] == "CompletionFailure" and r["phase"] == "Drain" and r["node"] is None and r["syncs"] == 1
+    r = host.fused_faults(2)                             # a primitive fails, then the drain after it fails too
+    assert r["code"] == "BackendFailure" and r["phase"] == "Run" and r["secondary_completion"] and r["syncs"] == 1
+    assert r["node"] == 1                                # the fused chain runs at its last node (the Add)
+    r = host.fused_faults(3)                             # the fused result has the wrong shape
+    assert r["code"] == "InvalidNodeOutput" and r["phase"] == "Run" and r["node"] == 1 and r["syncs"] == 1
+    r = host.fused_faults(4)                             # something that is not a std::exception
+    assert r["code"] == "BackendFailure" and "Non-standard" in r["text"] and r["syncs"] == 1

@@ -64,6 +64,7 @@ SIGNATURES = {
     "vrb_rms_norm_scale": [_vp, _i, _vp, _i, _i64, _i64, _vp, _i64, _i64, _f, _vp],
     "vrb_rms_norm_rope": [_vp, _i, _vp, _i, _vp, _vp, _i64, _i64, _i64, _vp, _i, _i64, _i64, _i64, _f, _vp],
     "vrb_rms_norm_rope_tables": [_vp, _i, _vp, _i, _vp, _vp, _i, _i64, _i64, _i64, _vp, _i, _i64, _i64, _i64, _f, _vp],
+    "vrb_rms_norm_rope_pair": [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i, _i, _vp, _vp, _i, _i64, _i64, _i64, _i, _i64, _i64, _f, _vp],
     "vrb_gated_residual": [_vp, _i, _vp, _i, _vp, _i, _i64, _i64, _vp, _i, _i64, _i64, _vp],
     "vrb_rms_norm_gated_residual": [_vp, _i, _vp, _i, _vp, _i, _i64, _i64, _vp, _i, _i64, _i64, _f, _vp],
     "vrb_swiglu": [_vp, _vp, _i, _i64, _i64, _vp],

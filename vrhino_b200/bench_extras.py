@@ -22,7 +22,7 @@ def check_shard_against_whole(whole, shard, dist):
     outputs on the shard's rows, element for element; then checks across ranks that every rank's
     whole-batch outputs are the same tensors (checksums), so the N shards together ARE the N=1
     result.  Returns a dict for the bench line; all ranks call it."""
-    for l in whole.launches():
+    for l in whole.launches(pair_qk=True):
         l.fn()
     torch.cuda.synchronize()
     (r0, r1), (t0, t1) = shard.token_rows, shard.text_rows
@@ -196,12 +196,12 @@ def run(be, whole, work, world, rank, dist, timed, barrier, max_over_ranks, peak
     out = {}
     # the residual updates merged into the LayerNorm that follows (9 launches): fewer bytes to move
     try:
-        merged = work.launches(fuse_residual_norm=True)
+        merged = work.launches(fuse_residual_norm=True, pair_qk=True)
         for l in merged:
             l.fn()
         compiled = workloads.compile_launches(merged)
         ms = timed([l.fn for l in compiled], args.steps)
-        nbytes = sum(l.bytes for l in whole.launches(fuse_residual_norm=True))
+        nbytes = sum(l.bytes for l in whole.launches(fuse_residual_norm=True, pair_qk=True))
         out["residual_norm_merged"] = {"ms_per_step": ms, "us_per_dit_block": ms * 1e3, "launches_per_step": len(merged),
                                        "bytes_per_step": nbytes, "value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s"}
         del merged, compiled
@@ -210,9 +210,9 @@ def run(be, whole, work, world, rank, dist, timed, barrier, max_over_ranks, peak
     if world > 1:
         # every rank running the whole batch on its own data path: N independent replicas
         try:
-            fns = [l.fn for l in workloads.compile_launches(_ran(whole.launches()))]
+            fns = [l.fn for l in workloads.compile_launches(_ran(whole.launches(pair_qk=True)))]
             ms = timed(fns, max(args.steps // 4, 5))
-            nbytes = sum(l.bytes for l in whole.launches())
+            nbytes = sum(l.bytes for l in whole.launches(pair_qk=True))
             out["replicas"] = {"ms_per_step": ms, "value": world * nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s",
                                "note": "weak scaling: every rank runs the whole batch, no communication"}
             whole.out.clear()

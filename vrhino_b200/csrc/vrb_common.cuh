@@ -202,6 +202,68 @@ __device__ __forceinline__ void store1(void* base, int dt, int64_t e, float v) {
     else static_cast<float*>(base)[e] = v;
 }
 
+// ---- packed F32 arithmetic (two IEEE round-to-nearest operations per instruction) ------------
+// sm_100 has add / sub / mul / fma on pairs of F32 values held in a 64-bit register; each half is
+// rounded exactly like the scalar _rn operation, so results are bit-identical to per-element
+// __fadd_rn / __fmul_rn / __fmaf_rn (no contraction either: these are explicit instructions).  The row
+// kernels are bound by issue slots, and these halve the arithmetic's share of them.
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long sub_f32x2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long mul_f32x2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+// Eight-element forms over float[8] register arrays: pairs (0,1) (2,3) (4,5) (6,7).
+#define VRB_PAIRWISE8(EXPR)                                              \
+    _Pragma("unroll") for (int e = 0; e < 8; e += 2) {                   \
+        const unsigned long long r_ = (EXPR);                            \
+        unpack_f32x2(r_, y[e], y[e + 1]);                                \
+    }
+__device__ __forceinline__ void sub8_scalar(float (&y)[8], float s) {
+    const unsigned long long ss = pack_f32x2(s, s);
+    VRB_PAIRWISE8(sub_f32x2(pack_f32x2(y[e], y[e + 1]), ss))
+}
+__device__ __forceinline__ void mul8_scalar(float (&y)[8], float s) {
+    const unsigned long long ss = pack_f32x2(s, s);
+    VRB_PAIRWISE8(mul_f32x2(pack_f32x2(y[e], y[e + 1]), ss))
+}
+__device__ __forceinline__ void add8_scalar(float (&y)[8], float s) {
+    const unsigned long long ss = pack_f32x2(s, s);
+    VRB_PAIRWISE8(add_f32x2(pack_f32x2(y[e], y[e + 1]), ss))
+}
+__device__ __forceinline__ void mul8(float (&y)[8], const float (&b)[8]) {
+    VRB_PAIRWISE8(mul_f32x2(pack_f32x2(y[e], y[e + 1]), pack_f32x2(b[e], b[e + 1])))
+}
+__device__ __forceinline__ void add8(float (&y)[8], const float (&b)[8]) {
+    VRB_PAIRWISE8(add_f32x2(pack_f32x2(y[e], y[e + 1]), pack_f32x2(b[e], b[e + 1])))
+}
+__device__ __forceinline__ void fma8(float (&y)[8], const float (&b)[8], const float (&c)[8]) {   // y = y * b + c
+    VRB_PAIRWISE8(fma_f32x2(pack_f32x2(y[e], y[e + 1]), pack_f32x2(b[e], b[e + 1]), pack_f32x2(c[e], c[e + 1])))
+}
+#undef VRB_PAIRWISE8
+
 // The reference's activation_kernel expressions (cuda_backend.cu:1098-1109), written so the
 // compiler sees the same operations in the same order.
 __device__ __forceinline__ float activation_value(int kind, float x) {

@@ -112,6 +112,8 @@ constexpr int kMaxChunks = 8;
 // launch_rows() result when a fused residual update was asked for but the vector kernel cannot
 // take it (alignment, width, too many gate vectors): the caller then runs the two operators.
 constexpr int kPreNotFused = 1;
+// ... and when a two-problem launch was asked for but needs the scalar kernel: the caller launches twice.
+constexpr int kPairNotFused = 2;
 
 // Which dtype classes exist for a (norm, post) pair; anything else takes the scalar kernel.
 template <int NORM, int POST>
@@ -139,7 +141,9 @@ bool launch_by_dtype(const RowParams& p, int geometry, int64_t ctas, size_t smem
     return false;
 }
 
-int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
+// second_rows > 0: (p.x_b, p.out_b, p.weight_b) is a second problem of second_rows storage rows that
+// runs in the same launch; the caller has checked that both problems take the same kernel.
+int launch_rows(RowParams p, cudaStream_t stream, const char* what, int64_t second_rows = 0) {
     VRB_REQUIRE(p.x && p.out, VRB_ERR_INVALID, "%s: null tensor", what);
     VRB_REQUIRE(p.rows > 0 && p.width > 0 && p.norm_width > 0 && p.width % p.norm_width == 0,
                 VRB_ERR_INVALID, "%s: rows/width must be positive and norm_width must divide width", what);
@@ -152,6 +156,12 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
                      (!p.scale || aligned16(p.scale)) && (!p.shift || aligned16(p.shift)) &&
                      (!p.cosine || (aligned16(p.cosine) && aligned16(p.sine) && p.f_width % 8 == 0)) &&
                      (!p.residual || aligned16(p.residual)) && (!p.gate || aligned16(p.gate));
+    if (second_rows > 0) {
+        VRB_REQUIRE(p.x_b && p.out_b, VRB_ERR_INVALID, "%s: null tensor", what);
+        vector_ok = vector_ok && aligned16(p.x_b) && aligned16(p.out_b) && (!p.weight_b || aligned16(p.weight_b)) &&
+                    second_rows * sub < (1LL << 31);
+        if (!vector_ok) return kPairNotFused;
+    }
     const int64_t chunks = p.norm_width / 8;
     if (chunks > static_cast<int64_t>(kMaxChunks) * kRowThreads) vector_ok = false;
     // The vector kernel indexes rows and table rows in 32 bits.
@@ -196,7 +206,11 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
     p.sub32 = static_cast<unsigned>(sub);
     p.inv_width = 1.0 / static_cast<double>(p.norm_width);
     const int rows_per_cta = kRowThreads / tpr;
-    const int64_t ctas = (nrows + rows_per_cta - 1) / rows_per_cta;
+    int64_t ctas = (nrows + rows_per_cta - 1) / rows_per_cta;
+    if (second_rows > 0) {
+        p.nrows_b = static_cast<unsigned>(second_rows * sub);
+        ctas += (second_rows * sub + rows_per_cta - 1) / rows_per_cta;
+    }
     size_t smem = 0;
     int post = p.post;
     const size_t region = static_cast<size_t>(geometry <= 6 ? nch : (chunks / tpr)) * tpr * 8 * sizeof(float);
@@ -243,7 +257,7 @@ int launch_rows(RowParams p, cudaStream_t stream, const char* what) {
             default: launched = launch_by_dtype<kNormRms, kPostNone>(p, geometry, ctas, smem, stream); break;
         }
     }
-    if (!launched) return p.pre_branch != nullptr ? kPreNotFused : scalar_path();
+    if (!launched) return p.pre_branch != nullptr ? kPreNotFused : second_rows > 0 ? kPairNotFused : scalar_path();
     return after_launch(what);
 }
 
@@ -456,6 +470,43 @@ extern "C" int vrb_rms_norm_rope_tables(const void* x, int x_dtype, const void* 
         p.post = kPostRope;
     }
     return launch_rows(p, as_stream(stream), "rms_norm_rope");
+}
+
+extern "C" int vrb_rms_norm_rope_pair(const void* x_a, const void* weight_a, void* out_a, int64_t rows_a,
+                                      const void* x_b, const void* weight_b, void* out_b, int64_t rows_b,
+                                      int x_dtype, int weight_dtype, const void* cosine, const void* sine, int table_dtype,
+                                      int64_t f_rows, int64_t f_width, int64_t rows_per_f_row, int out_dtype,
+                                      int64_t width, int64_t norm_width, float eps, vrb_stream stream) {
+    VRB_REQUIRE(x_a && x_b && out_a && out_b && weight_a && weight_b, VRB_ERR_INVALID, "rms_norm_rope_pair: null tensor");
+    VRB_REQUIRE(rows_a > 0 && rows_b > 0, VRB_ERR_INVALID, "rms_norm_rope_pair: extents must be positive");
+    VRB_REQUIRE(norm_width > 0 && width % norm_width == 0, VRB_ERR_INVALID, "rms_norm_rope: norm_width must divide width");
+    const int64_t sub = width / norm_width;
+    // One launch only if both problems take the same kernel: the reference picks its summation formula
+    // from the row count (rms_contiguous_reduction_lanes, :838-850).
+    if (rms_uses_f32_accumulation(norm_width, rows_a * sub) == rms_uses_f32_accumulation(norm_width, rows_b * sub)) {
+        VRB_REQUIRE(is_float_dtype(table_dtype), VRB_ERR_UNSUPPORTED, "rms_norm_rope: tables must be F32 or BF16");
+        VRB_REQUIRE((cosine == nullptr) == (sine == nullptr), VRB_ERR_INVALID, "RoPE frequency mismatch");
+        RowParams p = blank();
+        p.x = x_a; p.out = out_a; p.weight = weight_a;
+        p.x_b = x_b; p.out_b = out_b; p.weight_b = weight_b;
+        p.x_dt = x_dtype; p.out_dt = out_dtype; p.norm_out_dt = VRB_F32; p.w_dt = weight_dtype;
+        p.rows = rows_a; p.width = width; p.norm_width = norm_width; p.eps = eps;
+        set_rms(p, rows_a * sub);
+        if (cosine) {
+            VRB_REQUIRE(f_rows > 0 && f_width > 0 && rows_per_f_row > 0 && width % f_width == 0 && (norm_width % 2) == 0,
+                        VRB_ERR_INVALID, "rms_norm_rope: table extents must be positive, f_width must divide width, width even");
+            p.cosine = cosine; p.sine = sine; p.f_dt = table_dtype;
+            p.f_rows = f_rows; p.f_width = f_width; p.rows_per_f_row = rows_per_f_row;
+            p.post = kPostRope;
+        }
+        const int rc = launch_rows(p, as_stream(stream), "rms_norm_rope_pair", rows_b);
+        if (rc != kPairNotFused) return rc;
+    }
+    if (int rc = vrb_rms_norm_rope_tables(x_a, x_dtype, weight_a, weight_dtype, cosine, sine, table_dtype, f_rows, f_width,
+                                          rows_per_f_row, out_a, out_dtype, rows_a, width, norm_width, eps, stream))
+        return rc;
+    return vrb_rms_norm_rope_tables(x_b, x_dtype, weight_b, weight_dtype, cosine, sine, table_dtype, f_rows, f_width,
+                                    rows_per_f_row, out_b, out_dtype, rows_b, width, norm_width, eps, stream);
 }
 
 extern "C" int vrb_rms_norm_gated_residual(const void* residual, int residual_dtype,

@@ -77,6 +77,11 @@ struct RowParams {
     const void* pre_branch; const void* pre_gate; void* state_out;
     int pre_gate_dt;
     int64_t pre_rows_per_vector, pre_vectors;
+    // Two problems in one launch (q and k of an attention block: same geometry, dtypes, tables and
+    // epilogue, their own tensors, weights and row counts): CTAs [0, blocks_a) work on (x, out, weight,
+    // nrows32), the others on (x_b, out_b, weight_b, nrows_b).  blocks_a == 0: a single problem.
+    const void* x_b; void* out_b; const void* weight_b;
+    unsigned nrows_b, blocks_a;
 };
 
 constexpr int kRowThreads = 256;
@@ -175,6 +180,29 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Staging of per-CTA vectors: `groups` float4 groups, up to four loads in flight per thread before
+// the first store, so a CTA pays the L2 / DRAM latency once instead of once per loop iteration (the
+// staging is a fixed cost of every launch; it is what a short launch on a token shard feels most).
+template <typename Load, typename Store>
+__device__ __forceinline__ void stage_groups(int groups, Load load, Store store) {
+    for (int g0 = threadIdx.x; g0 < groups; g0 += 4 * kRowThreads) {
+        float4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int g = g0 + k * kRowThreads;
+            if (g < groups) v[k] = load(g);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int g = g0 + k * kRowThreads;
+            if (g < groups) store(g, v[k]);
+        }
+    }
+}
+__device__ __forceinline__ bool f32_vector_ok(const void* p, int dt) {
+    return dt == VRB_F32 && (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
 // ---- vector kernel: norm_width % 8 == 0, 16-byte aligned operands ------------------------
 // CTAs per SM the register allocator must leave room for: the packed row takes 4 (bf16) or 8
 // (f32) registers per chunk; the rest of the budget is working state.
@@ -219,9 +247,21 @@ row_kernel(const RowParams p) {
     const int rows_per_cta = kRowThreads / tpr;
     const int nchunks = FULL ? NCH * TPR : static_cast<int>(p.norm_width >> 3);
     const int width = nchunks * 8;
-    const unsigned nrows = p.nrows32;
     const int warps_per_row = tpr >> 5;
-    const bool has_w = p.weight != nullptr, has_b = p.bias != nullptr;
+    // this CTA's problem: the only one, or one of a pair
+    unsigned block = blockIdx.x, blocks = gridDim.x, nrows = p.nrows32;
+    const void* x_base = p.x;
+    void* out_base = p.out;
+    const void* weight_base = p.weight;
+    if (p.blocks_a != 0) {
+        if (block >= p.blocks_a) {
+            block -= p.blocks_a; blocks -= p.blocks_a;
+            nrows = p.nrows_b; x_base = p.x_b; out_base = p.out_b; weight_base = p.weight_b;
+        } else {
+            blocks = p.blocks_a;
+        }
+    }
+    const bool has_w = weight_base != nullptr, has_b = p.bias != nullptr;
     const bool has_shift = p.shift != nullptr;
     const bool f32_formula = NORM == kNormRms && !p.rms_f64;
     int parity = 0;
@@ -235,12 +275,32 @@ row_kernel(const RowParams p) {
     // conflict-free layout as the modulation vectors, placed before them)
     const int pad = NCH * tpr * 8;
     float* const s_mod = s_vec + (p.affine_staged ? 2 * pad : 0);
+    // float4 group g of a staged vector (elements 4g .. 4g+3 of the row) -> float4 slot in shared memory
+    auto group_slot = [&](int g) {
+        const int chunk = g >> 1, i = chunk / tpr, l = chunk - i * tpr;
+        return (i * 2 + (g & 1)) * tpr + l;
+    };
     if (NORM == kNormLayer && p.affine_staged) {
-        for (int c = threadIdx.x; c < width; c += kRowThreads) {
-            const int chunk = c >> 3, e = c & 7, i = chunk / tpr, l = chunk - i * tpr;
-            const int pos = (((i * 2 + (e >> 2)) * tpr + l) << 2) + (e & 3);
-            s_vec[pos] = has_w ? round_to(p.x_dt, load1(p.weight, p.w_dt, c)) : 1.0f;
-            s_vec[pad + pos] = has_b ? round_to(p.x_dt, load1(p.bias, p.b_dt, c)) : 0.0f;
+        const bool fast_w = !has_w || f32_vector_ok(p.weight, p.w_dt), fast_b = !has_b || f32_vector_ok(p.bias, p.b_dt);
+        if (fast_w && fast_b && (width & 3) == 0) {
+            const bool to_bf16 = p.x_dt == VRB_BF16;
+            auto rounded = [&](float4 v) {
+                if (to_bf16) { v.x = round_to_bf16(v.x); v.y = round_to_bf16(v.y); v.z = round_to_bf16(v.z); v.w = round_to_bf16(v.w); }
+                return v;
+            };
+            stage_groups(width >> 2,
+                         [&](int g) { return has_w ? __ldg(static_cast<const float4*>(p.weight) + g) : make_float4(1.f, 1.f, 1.f, 1.f); },
+                         [&](int g, float4 v) { reinterpret_cast<float4*>(s_vec)[group_slot(g)] = rounded(v); });
+            stage_groups(width >> 2,
+                         [&](int g) { return has_b ? __ldg(static_cast<const float4*>(p.bias) + g) : make_float4(0.f, 0.f, 0.f, 0.f); },
+                         [&](int g, float4 v) { reinterpret_cast<float4*>(s_vec + pad)[group_slot(g)] = rounded(v); });
+        } else {
+            for (int c = threadIdx.x; c < width; c += kRowThreads) {
+                const int chunk = c >> 3, e = c & 7, i = chunk / tpr, l = chunk - i * tpr;
+                const int pos = (((i * 2 + (e >> 2)) * tpr + l) << 2) + (e & 3);
+                s_vec[pos] = has_w ? round_to(p.x_dt, load1(p.weight, p.w_dt, c)) : 1.0f;
+                s_vec[pad + pos] = has_b ? round_to(p.x_dt, load1(p.bias, p.b_dt, c)) : 0.0f;
+            }
         }
         if constexpr (!kStaged) __syncthreads();
     }
@@ -250,12 +310,30 @@ row_kernel(const RowParams p) {
         // layout: for chunk (l + i*tpr) the two float4 halves sit at float4 index (2i + half)*tpr + l,
         // so the lanes of a warp read consecutive 16-byte words (no bank conflicts)
         const int staged_vectors = static_cast<int>(p.vectors);
-        for (int cv = threadIdx.x; cv < width * staged_vectors; cv += kRowThreads) {
-            const int v = cv / width, c = cv - v * width;
-            const int chunk = c >> 3, e = c & 7, i = chunk / tpr, l = chunk - i * tpr;
-            const int pos = v * 2 * pad + (((i * 2 + (e >> 2)) * tpr + l) << 2) + (e & 3);
-            s_mod[pos] = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, static_cast<int64_t>(v) * p.width + c));
-            s_mod[pad + pos] = has_shift ? load1(p.shift, p.mod_dt, static_cast<int64_t>(v) * p.width + c) : 0.0f;
+        if (f32_vector_ok(p.scale, p.mod_dt) && (!has_shift || f32_vector_ok(p.shift, p.mod_dt)) && p.width == width) {
+            // vector v's groups follow vector v-1's (the vectors are contiguous rows of `width` elements)
+            const int per_vector = width >> 2;
+            auto slot = [&](int g) {
+                const int v = g / per_vector;
+                return v * (2 * pad / 4) + group_slot(g - v * per_vector);
+            };
+            stage_groups(per_vector * staged_vectors,
+                         [&](int g) { return __ldg(static_cast<const float4*>(p.scale) + g); },
+                         [&](int g, float4 v) {
+                             reinterpret_cast<float4*>(s_mod)[slot(g)] =
+                                 make_float4(__fadd_rn(1.0f, v.x), __fadd_rn(1.0f, v.y), __fadd_rn(1.0f, v.z), __fadd_rn(1.0f, v.w));
+                         });
+            stage_groups(per_vector * staged_vectors,
+                         [&](int g) { return has_shift ? __ldg(static_cast<const float4*>(p.shift) + g) : make_float4(0.f, 0.f, 0.f, 0.f); },
+                         [&](int g, float4 v) { reinterpret_cast<float4*>(s_mod + pad)[slot(g)] = v; });
+        } else {
+            for (int cv = threadIdx.x; cv < width * staged_vectors; cv += kRowThreads) {
+                const int v = cv / width, c = cv - v * width;
+                const int chunk = c >> 3, e = c & 7, i = chunk / tpr, l = chunk - i * tpr;
+                const int pos = v * 2 * pad + (((i * 2 + (e >> 2)) * tpr + l) << 2) + (e & 3);
+                s_mod[pos] = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, static_cast<int64_t>(v) * p.width + c));
+                s_mod[pad + pos] = has_shift ? load1(p.shift, p.mod_dt, static_cast<int64_t>(v) * p.width + c) : 0.0f;
+            }
         }
         __syncthreads();
     }
@@ -292,7 +370,7 @@ row_kernel(const RowParams p) {
 #pragma unroll
     for (int i = 0; i < NCH; ++i) own += (FULL || lane_in_row + i * tpr < nchunks) ? 8 : 0;
 
-    const unsigned row_step = gridDim.x * rows_per_cta;
+    const unsigned row_step = blocks * rows_per_cta;
     auto load_row = [&](unsigned first_row, Packed<X_BF16> (&dst)[NCH]) {
         const unsigned r = first_row + row_in_cta;
         const bool ok = r < nrows;
@@ -300,7 +378,7 @@ row_kernel(const RowParams p) {
 #pragma unroll
         for (int i = 0; i < NCH; ++i) {
             const int chunk = lane_in_row + i * tpr;
-            dst[i] = (ok && (FULL || chunk < nchunks)) ? load_packed<X_BF16>(p.x, off + chunk * 8) : zero_packed<X_BF16>();
+            dst[i] = (ok && (FULL || chunk < nchunks)) ? load_packed<X_BF16>(x_base, off + chunk * 8) : zero_packed<X_BF16>();
         }
     };
     // kBf16Bf16Pre: the raw residual-stream row and branch row of a normalised row
@@ -312,19 +390,19 @@ row_kernel(const RowParams p) {
         for (int i = 0; i < NCH; ++i) {
             const int chunk = lane_in_row + i * tpr;
             const bool here = ok && (FULL || chunk < nchunks);
-            if constexpr (!PRE_F32) res[i] = here ? load_packed<true>(p.x, off + chunk * 8) : zero_packed<true>();
+            if constexpr (!PRE_F32) res[i] = here ? load_packed<true>(x_base, off + chunk * 8) : zero_packed<true>();
             br[i] = here ? load_packed<true>(p.pre_branch, off + chunk * 8) : zero_packed<true>();
         }
     };
     Packed<X_BF16> xr[NCH];
     Packed<true> raw_res[(PRE && !PRE_F32) ? NCH : 1], raw_br[PRE ? NCH : 1];   // PRE: the row being combined next
     if constexpr (PRE) {
-        if constexpr (PF) load_raw(blockIdx.x * rows_per_cta, raw_res, raw_br);
+        if constexpr (PF) load_raw(block * rows_per_cta, raw_res, raw_br);
     } else if constexpr (PF) {
-        load_row(blockIdx.x * rows_per_cta, xr);
+        load_row(block * rows_per_cta, xr);
     }
 
-    for (unsigned base = blockIdx.x * rows_per_cta; base < nrows; base += row_step) {
+    for (unsigned base = block * rows_per_cta; base < nrows; base += row_step) {
         const unsigned nrow = base + row_in_cta;
         const bool valid = nrow < nrows;
         const int64_t row_offset = static_cast<int64_t>(nrow) * width;
@@ -457,7 +535,10 @@ row_kernel(const RowParams p) {
         // LayerNorm sums x - K and (x - K)^2 with K = the thread's first element, so the
         // partials stay small and accurate however large the row's common offset is; the exact
         // sums are rebuilt in double: S = s1 + n K, Q = s2 + 2 K s1 + n K^2.
+        // Two elements per instruction: the partial sums are kept as (even, odd) pairs and folded once
+        // at the end.
         float s1 = 0.0f, s2 = 0.0f, pivot = 0.0f;
+        unsigned long long s1_pair = 0ull, s2_pair = 0ull;   // +0.0f in both halves
 #pragma unroll
         for (int i = 0; i < NCH; ++i) {
             float v[8];
@@ -465,19 +546,26 @@ row_kernel(const RowParams p) {
             if constexpr (NORM == kNormLayer) {
                 if (i == 0) pivot = v[0];
                 if (FULL || lane_in_row + i * tpr < nchunks) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) v[e] -= pivot;
-                    s1 += ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+                    sub8_scalar(v, pivot);
+                    const unsigned long long p0 = pack_f32x2(v[0], v[1]), p1 = pack_f32x2(v[2], v[3]);
+                    const unsigned long long p2 = pack_f32x2(v[4], v[5]), p3 = pack_f32x2(v[6], v[7]);
+                    s1_pair = add_f32x2(s1_pair, add_f32x2(add_f32x2(p0, p1), add_f32x2(p2, p3)));
                 } else {
 #pragma unroll
                     for (int e = 0; e < 8; ++e) v[e] = 0.0f;
                 }
             }
-            float qa = v[0] * v[0], qb = v[4] * v[4];
-            qa = fmaf(v[1], v[1], qa); qb = fmaf(v[5], v[5], qb);
-            qa = fmaf(v[2], v[2], qa); qb = fmaf(v[6], v[6], qb);
-            qa = fmaf(v[3], v[3], qa); qb = fmaf(v[7], v[7], qb);
-            s2 += qa + qb;
+            const unsigned long long p0 = pack_f32x2(v[0], v[1]), p1 = pack_f32x2(v[2], v[3]);
+            const unsigned long long p2 = pack_f32x2(v[4], v[5]), p3 = pack_f32x2(v[6], v[7]);
+            unsigned long long qa = mul_f32x2(p0, p0), qb = mul_f32x2(p2, p2);
+            qa = fma_f32x2(p1, p1, qa);
+            qb = fma_f32x2(p3, p3, qb);
+            s2_pair = add_f32x2(s2_pair, add_f32x2(qa, qb));
+        }
+        {
+            float lo, hi;
+            unpack_f32x2(s1_pair, lo, hi); s1 = lo + hi;
+            unpack_f32x2(s2_pair, lo, hi); s2 = lo + hi;
         }
         const int span = tpr < 32 ? tpr : 32;
         double acc0 = 0.0, acc1 = 0.0;
@@ -535,8 +623,8 @@ row_kernel(const RowParams p) {
             float y[8];
             unpack<X_BF16>(xr[i], y);
             if constexpr (NORM == kNormLayer) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(__fsub_rn(y[e], mean), inv);
+                sub8_scalar(y, mean);
+                mul8_scalar(y, inv);
                 if (has_w || has_b) {
                     // weight / bias are converted to x's dtype first (:4069-4070)
                     float w[8], b[8];
@@ -547,34 +635,25 @@ row_kernel(const RowParams p) {
                         w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w; w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
                         b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
                     } else {
-                        if (has_w) { load8<false>(p.weight, p.w_dt, c, w); round8<X_BF16>(w); }
+                        if (has_w) { load8<false>(weight_base, p.w_dt, c, w); round8<X_BF16>(w); }
                         if (has_b) { load8<false>(p.bias, p.b_dt, c, b); round8<X_BF16>(b); }
                     }
                     if (has_w && has_b && p.affine_fma) {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) y[e] = __fmaf_rn(y[e], w[e], b[e]);
+                        fma8(y, w, b);
                     } else {
-                        if (has_w) {
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(y[e], w[e]);
-                        }
-                        if (has_b) {
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) y[e] = __fadd_rn(y[e], b[e]);
-                        }
+                        if (has_w) mul8(y, w);
+                        if (has_b) add8(y, b);
                     }
                 }
             } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(y[e], inv);
+                mul8_scalar(y, inv);
                 round8<X_BF16>(y);   // the normalised value is stored in the input dtype first (:900-902)
                 if (has_w) {
                     // the weight is converted to the norm's output dtype (:4115)
                     float w[8];
-                    load8<false>(p.weight, p.w_dt, c, w);
+                    load8<false>(weight_base, p.w_dt, c, w);
                     round8<N_BF16>(w);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(y[e], w[e]);
+                    mul8(y, w);
                 }
             }
             round8<N_BF16>(y);       // what the unfused norm operator stores
@@ -590,23 +669,17 @@ row_kernel(const RowParams p) {
                     sh[0] = b0.x; sh[1] = b0.y; sh[2] = b0.z; sh[3] = b0.w; sh[4] = b1.x; sh[5] = b1.y; sh[6] = b1.z; sh[7] = b1.w;
                 } else {
                     load8<false>(p.scale, p.mod_dt, vec_offset + c, t1);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) t1[e] = __fadd_rn(1.0f, t1[e]);
+                    add8_scalar(t1, 1.0f);
                     if (has_shift) load8<false>(p.shift, p.mod_dt, vec_offset + c, sh);
                 }
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    y[e] = __fmul_rn(y[e], t1[e]);
-                    if (has_shift) y[e] = __fadd_rn(y[e], sh[e]);
-                }
+                mul8(y, t1);
+                if (has_shift) add8(y, sh);
             } else if constexpr (POST == kPostScaleX) {
                 float sc[8];
                 load8<false>(p.scale, p.mod_dt, vec_offset + c, sc);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) sc[e] = __fadd_rn(1.0f, sc[e]);
+                add8_scalar(sc, 1.0f);
                 round8<N_BF16>(sc);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(y[e], sc[e]);
+                mul8(y, sc);
                 round8<N_BF16>(y);
             } else if constexpr (kRope) {
                 float r[8];
@@ -615,10 +688,13 @@ row_kernel(const RowParams p) {
                     load8<false>(p.cosine, p.f_dt, f_offset + fc, co);
                     load8<false>(p.sine, p.f_dt, f_offset + fc, si);
                 }
+                // pair (e, e+1): out = (y_e, y_e+1) * (cos_e, cos_e+1) + (-y_e+1, y_e) * (sin_e, sin_e+1), each
+                // product and the sum rounded separately (rope_kernel uses __fmul_rn / __fadd_rn)
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float rotated = (e & 1) ? y[e ^ 1] : -y[e ^ 1];
-                    r[e] = __fadd_rn(__fmul_rn(y[e], co[e]), __fmul_rn(rotated, si[e]));
+                for (int e = 0; e < 8; e += 2) {
+                    const unsigned long long direct = mul_f32x2(pack_f32x2(y[e], y[e + 1]), pack_f32x2(co[e], co[e + 1]));
+                    const unsigned long long turned = mul_f32x2(pack_f32x2(-y[e + 1], y[e]), pack_f32x2(si[e], si[e + 1]));
+                    unpack_f32x2(add_f32x2(direct, turned), r[e], r[e + 1]);
                 }
 #pragma unroll
                 for (int e = 0; e < 8; ++e) y[e] = r[e];
@@ -633,14 +709,12 @@ row_kernel(const RowParams p) {
                 if (has_gate) {
                     load8<false>(p.gate, p.gate_dt, vec_offset + c, g);
                     round8_rt(sd, g);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(y[e], g[e]);
+                    mul8(y, g);
                     round8_rt(sd, y);
                 }
-#pragma unroll
-                for (int e = 0; e < 8; ++e) y[e] = __fadd_rn(res[e], y[e]);
+                add8(y, res);
             }
-            store8(p.out, p.out_dt, row_offset + c, y);
+            store8(out_base, p.out_dt, row_offset + c, y);
         }
         }  // valid
         if constexpr (PF && !PRE) {

@@ -42,7 +42,20 @@ void launch_one(const RowParams& p, int64_t ctas, size_t smem, cudaStream_t stre
         }
         per_sm = cached_per_sm[device];
     }
-    launch_overlapped(row_kernel<NCH, TPR, FULL, NORM, POST, DT>, dim3(grid_for(ctas, per_sm)), dim3(kRowThreads), smem, stream, p);
+    const int grid = grid_for(ctas, per_sm);
+    if (p.nrows_b != 0) {
+        // two problems: CTAs in proportion to the rows, at least one each
+        RowParams pair = p;
+        const double share = static_cast<double>(p.nrows32) / (static_cast<double>(p.nrows32) + static_cast<double>(p.nrows_b));
+        int first = static_cast<int>(share * grid + 0.5);
+        first = first < 1 ? 1 : first;
+        const int total = grid < 2 ? 2 : grid;
+        if (first > total - 1) first = total - 1;
+        pair.blocks_a = static_cast<unsigned>(first);
+        launch_overlapped(row_kernel<NCH, TPR, FULL, NORM, POST, DT>, dim3(total), dim3(kRowThreads), smem, stream, pair);
+        return;
+    }
+    launch_overlapped(row_kernel<NCH, TPR, FULL, NORM, POST, DT>, dim3(grid), dim3(kRowThreads), smem, stream, p);
 }
 
 #define VRB_DEFINE_ROW_VARIANT(NORM, POST, DT)                                                                       \

@@ -65,6 +65,38 @@ void vector_layout(const Tensor& x, const Tensor& vec, int64_t& rows_per_vector,
 
 }  // namespace
 
+// One profiled operator: a region in the device runtime's profiler (events on the legacy stream the
+// kernels run on) under the reference's name for that operator, plus the bytes it moves.  The name is
+// only built when profiling is on.  Closing never throws: a failing profiler must not mask the
+// operator's own outcome.
+class B200Backend::ProfileRegion {
+public:
+    template <typename Name>
+    ProfileRegion(B200Backend& backend, Name&& name, uint64_t bytes) : backend_(backend) {
+        if (!backend_.rt_->profiling_enabled()) return;
+        const std::string text = name();
+        backend_.rt_->profile_region_begin(text);
+        backend_.profile_bytes_[text] += bytes;
+        open_ = true;
+    }
+    ~ProfileRegion() {
+        if (!open_) return;
+        try { backend_.rt_->profile_region_end(); } catch (...) {}
+    }
+    ProfileRegion(const ProfileRegion&) = delete;
+    ProfileRegion& operator=(const ProfileRegion&) = delete;
+private:
+    B200Backend& backend_;
+    bool open_ = false;
+};
+
+namespace {
+std::string sized(const char* head, int64_t rows, int64_t width, DType dtype) {
+    return std::string(head) + "|rows=" + std::to_string(rows) + "|width=" + std::to_string(width) + "|dtype=" + vrhino::dtype_name(dtype);
+}
+uint64_t bytes_of(const Tensor& t) { return t.defined() ? static_cast<uint64_t>(t.bytes()) : 0; }
+}  // namespace
+
 B200Backend::B200Backend(std::unique_ptr<vrhino::Backend> device_runtime) : rt_(std::move(device_runtime)) {
     require(rt_ != nullptr, "B200Backend needs a device runtime backend");
     require(vrb_abi_version() == VRB_ABI_VERSION, "libvrb.so ABI version mismatch");
@@ -132,6 +164,16 @@ Tensor B200Backend::dequantize(const Tensor& input, DType dtype) {
         else if (q.type == vrhino::QuantType::INT8Symmetric && q.packing_layout == "byte_twos_complement") kind = VRB_Q_INT8;
         else if (q.type == vrhino::QuantType::INT4Symmetric && q.packing_layout == "nibble_low_first_twos_complement") kind = VRB_Q_INT4;
         require(kind >= 0, "Unsupported quantized tensor packing");
+        const auto key = std::make_pair(static_cast<const void*>(input.data()), code(dtype));
+        if (weight_cache_enabled_) {
+            const auto found = dequant_cache_.find(key);
+            if (found != dequant_cache_.end() && found->second.value.shape() == input.shape()) {
+                ++dequant_hits_;
+                found->second.last_use = ++dequant_clock_;
+                return found->second.value;
+            }
+        }
+        ++dequant_misses_;
         Tensor host_bytes = Tensor::borrowed(input.data(), input.bytes(), {static_cast<int64_t>(input.bytes())}, DType::U8);
         Tensor packed = rt_->allocate_device(host_bytes.shape(), DType::U8);
         Tensor scales = rt_->allocate_device(q.scales.shape(), DType::F32);
@@ -139,10 +181,40 @@ Tensor B200Backend::dequantize(const Tensor& input, DType dtype) {
         rt_->copy(q.scales, scales);
         Tensor output = rt_->allocate_device(input.shape(), dtype);
         const int64_t rows = input.dim(0), inner = input.numel() / rows;
-        check(vrb_dequantize(kind, packed.data(), scales.data_as<float>(), output.data(), code(dtype), rows, inner,
-                             q.group_size, kLegacyStream));
+        {
+            ProfileRegion region(*this, [] { return std::string("quantized_dequant"); },
+                                 bytes_of(packed) + bytes_of(scales) + bytes_of(output));
+            check(vrb_dequantize(kind, packed.data(), scales.data_as<float>(), output.data(), code(dtype), rows, inner,
+                                 q.group_size, kLegacyStream));
+        }
+        const size_t resident = output.bytes();
+        if (weight_cache_enabled_ && resident <= dequant_budget_) {
+            while (dequant_resident_ + resident > dequant_budget_ && !dequant_cache_.empty()) {
+                auto oldest = dequant_cache_.begin();
+                for (auto it = dequant_cache_.begin(); it != dequant_cache_.end(); ++it)
+                    if (it->second.last_use < oldest->second.last_use) oldest = it;
+                dequant_resident_ -= oldest->second.bytes;
+                dequant_cache_.erase(oldest);
+            }
+            dequant_cache_[key] = DequantizedEntry{output, resident, ++dequant_clock_};
+            dequant_resident_ += resident;
+        }
         return output;
     });
+}
+
+void B200Backend::drop_dequantized_cache() {
+    dequant_cache_.clear();
+    dequant_resident_ = 0;
+}
+void B200Backend::set_dequantized_cache_budget(size_t bytes) {
+    dequant_budget_ = bytes;
+    if (dequant_resident_ > bytes) drop_dequantized_cache();
+}
+void B200Backend::release_cached_device_memory() {
+    require_active_session();
+    drop_dequantized_cache();
+    rt_->release_cached_device_memory();
 }
 
 Tensor B200Backend::cast(const Tensor& x, DType dtype) {
@@ -152,6 +224,7 @@ Tensor B200Backend::cast(const Tensor& x, DType dtype) {
     if (!is_float(dtype) || !(is_float(x.dtype()) || x.dtype() == DType::U8)) return rt_->cast(x, dtype);
     return guarded([&] {
         Tensor out = rt_->allocate_device(x.shape(), dtype);
+        ProfileRegion region(*this, [] { return std::string("cast"); }, bytes_of(x) + bytes_of(out));
         if (x.numel() > 0) check(vrb_cast(x.data(), code(x.dtype()), out.data(), code(dtype), x.numel(), kLegacyStream));
         return out;
     });
@@ -163,6 +236,8 @@ Tensor B200Backend::binary(int kind, const Tensor& a_raw, const Tensor& b_raw) {
         Tensor a = copy_to_device(a_raw, dtype), b = copy_to_device(b_raw, dtype);
         Tensor out = rt_->allocate_device(broadcast_shape(a.shape(), b.shape()), dtype);
         const int64_t one = 1;
+        static const char* const names[] = {"elementwise.add", "elementwise.mul", "elementwise.div", "elementwise.maximum"};
+        ProfileRegion region(*this, [&] { return std::string(names[kind]); }, bytes_of(a) + bytes_of(b) + bytes_of(out));
         check(vrb_binary(kind, a.data(), a.ndim() ? a.shape().data() : &one, static_cast<int>(a.ndim()),
                          b.data(), b.ndim() ? b.shape().data() : &one, static_cast<int>(b.ndim()),
                          out.data(), code(dtype), kLegacyStream));
@@ -182,6 +257,7 @@ Tensor B200Backend::layer_norm(const Tensor& raw, const Tensor* weight_raw, cons
         if (weight_raw) { weight = parameter(*weight_raw); require(weight.numel() == width, "layer norm weight mismatch"); }
         if (bias_raw) { bias = parameter(*bias_raw); require(bias.numel() == width, "layer norm bias mismatch"); }
         Tensor out = rt_->allocate_device(x.shape(), dtype);
+        ProfileRegion region(*this, [&] { return sized("norm.layer", x.numel() / width, width, dtype); }, bytes_of(x) + bytes_of(out));
         check(vrb_layer_norm(x.data(), code(dtype), weight_raw ? weight.data() : nullptr, weight_raw ? code(weight.dtype()) : 0,
                              bias_raw ? bias.data() : nullptr, bias_raw ? code(bias.dtype()) : 0, out.data(),
                              x.numel() / width, width, eps, kLegacyStream));
@@ -201,6 +277,11 @@ Tensor B200Backend::rms_norm(const Tensor& raw, const Tensor* weight_raw, float 
         const void* w = weight_raw ? weight.data() : nullptr;
         const int wcode = weight_raw ? code(weight.dtype()) : 0;
         Tensor out = rt_->allocate_device(x.shape(), out_dtype);
+        ProfileRegion region(*this, [&] {
+            const int64_t w = x.dim(axis);
+            return std::string("norm.rms|rows=") + std::to_string(x.numel() / w) + "|width=" + std::to_string(w) + "|axis=" +
+                   std::to_string(axis) + "|dtype=" + vrhino::dtype_name(dtype);
+        }, bytes_of(x) + bytes_of(out));
         if (axis == x.ndim() - 1) {
             if (dtype == DType::BF16 && out_dtype == DType::F32)
                 require(weight_raw != nullptr, "BF16-to-FP32 rms_norm requires affine weight");
@@ -226,6 +307,12 @@ Tensor B200Backend::unary(int which, const Tensor& raw, int kind, float p0, floa
         const DType dtype = operand_dtype(raw);
         Tensor x = copy_to_device(raw, dtype), out = rt_->allocate_device(x.shape(), dtype);
         const int64_t n = x.numel();
+        ProfileRegion region(*this, [&] {
+            if (which == 0)
+                return std::string("activation|elements=") + std::to_string(n) + "|kind=" + std::to_string(kind) + "|dtype=" +
+                       vrhino::dtype_name(dtype);
+            return std::string(which == 1 ? "clamp" : which == 2 ? "exp" : "sqrt");
+        }, bytes_of(x) + bytes_of(out));
         switch (which) {
             case 0: check(vrb_activation(kind, x.data(), out.data(), code(dtype), n, kLegacyStream)); break;
             case 1: check(vrb_clamp(x.data(), out.data(), code(dtype), n, p0, p1, kLegacyStream)); break;
@@ -250,6 +337,10 @@ Tensor B200Backend::rope_nd(const Tensor& raw, const Tensor& cos_raw, const Tens
         require(c.shape() == s.shape(), "RoPE frequency mismatch");
         broadcast_shape(x.shape(), c.shape());
         Tensor out = rt_->allocate_device(x.shape(), dtype);
+        ProfileRegion region(*this, [&] {
+            return std::string("rope|elements=") + std::to_string(x.numel()) + "|width=" + std::to_string(x.dim(-1)) + "|dtype=" +
+                   vrhino::dtype_name(dtype);
+        }, bytes_of(x) + bytes_of(c) + bytes_of(s) + bytes_of(out));
         check(vrb_rope(x.data(), code(dtype), x.shape().data(), static_cast<int>(x.ndim()), c.data(), s.data(), code(f_dtype),
                        c.shape().data(), static_cast<int>(c.ndim()), out.data(), kLegacyStream));
         return out;
@@ -274,6 +365,8 @@ Tensor B200Backend::group_norm_impl(const Tensor& raw, int groups, const Tensor*
         require(batch * groups <= std::numeric_limits<int>::max(), "group norm launch extent exceeds CUDA grid capacity");
         const size_t need = vrb_group_norm_workspace_bytes(batch, groups);
         Tensor out = rt_->allocate_device(x.shape(), dtype);
+        ProfileRegion region(*this, [&] { return std::string(silu ? "fused.norm.group+silu" : "norm.group"); },
+                             2 * bytes_of(x) + bytes_of(out));   // statistics pass + normalise pass
         check(vrb_group_norm(x.data(), code(dtype), weight_raw ? weight.data() : nullptr, weight_raw ? code(weight.dtype()) : 0,
                              bias_raw ? bias.data() : nullptr, bias_raw ? code(bias.dtype()) : 0, out.data(), batch, channels,
                              spatial, groups, eps, silu ? 1 : 0, workspace(need), need, kLegacyStream));
@@ -298,6 +391,8 @@ Tensor B200Backend::group_norm_frames(const Tensor& raw, int groups, const Tenso
         const int64_t batch = x.dim(0), channels = x.dim(1), frames = x.dim(2), spatial = x.dim(3) * x.dim(4);
         const size_t need = vrb_group_norm_frames_workspace_bytes(batch, frames, groups);
         Tensor out = rt_->allocate_device(x.shape(), dtype);
+        ProfileRegion region(*this, [&] { return std::string(silu ? "fused.norm.group_frames+silu" : "fused.norm.group_frames"); },
+                             2 * bytes_of(x) + bytes_of(out));
         check(vrb_group_norm_frames(x.data(), code(dtype), weight_raw ? weight.data() : nullptr,
                                     weight_raw ? code(weight.dtype()) : 0, bias_raw ? bias.data() : nullptr,
                                     bias_raw ? code(bias.dtype()) : 0, out.data(), batch, channels, frames, spatial, groups,
@@ -316,6 +411,7 @@ Tensor B200Backend::pixel_norm(const Tensor& raw, int64_t dim, float eps) {
         int64_t inner = 1;
         for (int64_t d = dim + 1; d < static_cast<int64_t>(x.ndim()); ++d) inner *= x.dim(d);
         Tensor out = rt_->allocate_device(x.shape(), dtype);
+        ProfileRegion region(*this, [] { return std::string("norm.pixel"); }, bytes_of(x) + bytes_of(out));
         check(vrb_pixel_norm(x.data(), code(dtype), nullptr, nullptr, 0, 0, out.data(), code(dtype),
                              x.numel() / (channels * inner), channels, inner, eps, kLegacyStream));
         return out;
@@ -331,6 +427,7 @@ Tensor B200Backend::pixel_shuffle_nd(const Tensor& raw, const std::vector<int64_
         Tensor x = copy_to_device(raw, dtype);
         Tensor out = rt_->allocate_device({x.dim(0), x.dim(1) / product, x.dim(2) * factors[0], x.dim(3) * factors[1],
                                            x.dim(4) * factors[2]}, dtype);
+        ProfileRegion region(*this, [] { return std::string("pixel_shuffle"); }, bytes_of(x) + bytes_of(out));
         check(vrb_pixel_shuffle(x.data(), out.data(), code(dtype), x.dim(0), x.dim(1) / product, x.dim(2), x.dim(3), x.dim(4),
                                 static_cast<int>(factors[0]), static_cast<int>(factors[1]), static_cast<int>(factors[2]),
                                 kLegacyStream));
@@ -350,6 +447,7 @@ Tensor B200Backend::depth_to_space_residual(const Tensor& projected_raw, const T
                     projected.dim(4) == input.dim(4), "Incompatible broadcast shapes");
         Tensor out = rt_->allocate_device({input.dim(0), input.dim(1) / 2, 2 * input.dim(2) - 1, 2 * input.dim(3),
                                            2 * input.dim(4)}, dtype);
+        ProfileRegion region(*this, [] { return std::string("fused.depth_to_space_residual"); }, bytes_of(projected) + bytes_of(input) + bytes_of(out));
         check(vrb_depth_to_space_residual(projected.data(), input.data(), out.data(), code(dtype), input.dim(0), input.dim(1),
                                           input.dim(2), input.dim(3), input.dim(4), kLegacyStream));
         return out;
@@ -366,6 +464,7 @@ Tensor B200Backend::pixel_norm_modulate(const Tensor& raw, const Tensor& shift_r
         Tensor scale = parameter(scale_raw), shift = copy_to_device(shift_raw, scale.dtype());
         require(scale.numel() == batch * channels && shift.numel() == scale.numel(), "Incompatible broadcast shapes");
         Tensor out = rt_->allocate_device(x.shape(), output);
+        ProfileRegion region(*this, [] { return std::string("fused.norm.pixel+modulate"); }, bytes_of(x) + bytes_of(out));
         check(vrb_pixel_norm(x.data(), code(dtype), scale.data(), shift.data(), code(scale.dtype()), silu ? 1 : 0, out.data(),
                              code(output), batch, channels, inner, eps, kLegacyStream));
         return out;
@@ -385,6 +484,7 @@ Tensor B200Backend::layer_norm_modulate(const Tensor& raw, const Tensor* weight_
         int64_t rows_per_vector = 0, vectors = 0;
         vector_layout(x, scale, rows_per_vector, vectors);
         Tensor out = rt_->allocate_device(x.shape(), output);
+        ProfileRegion region(*this, [] { return std::string("fused.norm.layer+modulate"); }, bytes_of(x) + bytes_of(out));
         check(vrb_layer_norm_modulate(x.data(), code(dtype), weight_raw ? weight.data() : nullptr,
                                       weight_raw ? code(weight.dtype()) : 0, bias_raw ? bias.data() : nullptr,
                                       bias_raw ? code(bias.dtype()) : 0, scale.data(), shift.data(), code(scale.dtype()),
@@ -403,6 +503,7 @@ Tensor B200Backend::rms_norm_modulate(const Tensor& raw, float eps, const Tensor
         int64_t rows_per_vector = 0, vectors = 0;
         vector_layout(x, scale, rows_per_vector, vectors);
         Tensor out = rt_->allocate_device(x.shape(), output);
+        ProfileRegion region(*this, [] { return std::string("fused.norm.rms+modulate"); }, bytes_of(x) + bytes_of(out));
         check(vrb_rms_norm_modulate(x.data(), code(dtype), scale.data(), shift.data(), code(scale.dtype()), rows_per_vector,
                                     vectors, out.data(), code(output), rows, width, eps, kLegacyStream));
         return out;
@@ -436,6 +537,7 @@ Tensor B200Backend::rms_norm_rope(const Tensor& raw, const Tensor* weight_raw, f
             require(f_rows == rows || f_rows == rows / x.dim(0), "Incompatible broadcast shapes");
         }
         Tensor out = rt_->allocate_device(x.shape(), output);
+        ProfileRegion region(*this, [] { return std::string("fused.norm.rms+rope"); }, bytes_of(x) + bytes_of(out));
         check(vrb_rms_norm_rope_tables(x.data(), code(dtype), weight_raw ? weight.data() : nullptr,
                                        weight_raw ? code(weight.dtype()) : 0, cos_raw ? c.data() : nullptr,
                                        cos_raw ? s.data() : nullptr, code(table_dtype), f_rows, f_width, 1, out.data(),
@@ -453,6 +555,7 @@ Tensor B200Backend::gated_residual(const Tensor& residual_raw, const Tensor& bra
         int64_t rows_per_vector = 1, vectors = 1;
         if (gate_raw) { gate = parameter(*gate_raw); vector_layout(residual, gate, rows_per_vector, vectors); }
         Tensor out = rt_->allocate_device(residual.shape(), state);
+        ProfileRegion region(*this, [] { return std::string("fused.gated_residual"); }, bytes_of(residual) + bytes_of(branch) + bytes_of(out));
         check(vrb_gated_residual(residual.data(), code(residual.dtype()), branch.data(), code(branch.dtype()),
                                  gate_raw ? gate.data() : nullptr, gate_raw ? code(gate.dtype()) : 0, rows_per_vector,
                                  vectors, out.data(), code(state), rows, width, kLegacyStream));
@@ -483,6 +586,7 @@ std::pair<Tensor, Tensor> B200Backend::gated_residual_layer_norm(const Tensor& r
         }
         result.first = rt_->allocate_device(residual.shape(), state);
         result.second = rt_->allocate_device(residual.shape(), output);
+        ProfileRegion region(*this, [] { return std::string("fused.gated_residual+norm.layer"); }, bytes_of(residual) + bytes_of(branch) + bytes_of(result.first) + bytes_of(result.second));
         check(vrb_gated_residual_layer_norm_modulate(
             residual.data(), code(residual.dtype()), branch.data(), code(branch.dtype()), gate_raw ? gate.data() : nullptr,
             gate_raw ? code(gate.dtype()) : 0, gate_rows_per_vector, gate_vectors, result.first.data(), code(state),
@@ -511,6 +615,7 @@ Tensor B200Backend::linear_activation(const Tensor& x, const Tensor& weight, con
         Tensor bias;
         if (bias_raw) { bias = copy_to_device(*bias_raw, DType::BF16); require(bias.numel() == width, "linear bias mismatch"); }
         Tensor out = rt_->allocate_device(accumulation.shape(), DType::BF16);
+        ProfileRegion region(*this, [] { return std::string("fused.linear_output+activation"); }, bytes_of(accumulation) + bytes_of(out));
         check(vrb_linear_output_activation(accumulation.data_as<float>(), bias_raw ? bias.data() : nullptr, static_cast<int>(kind),
                                            out.data(), rows, width, kLegacyStream));
         return out;
@@ -529,6 +634,7 @@ Tensor B200Backend::linear_gated_residual(const Tensor& residual_raw, const Tens
         int64_t rows_per_vector = 1, vectors = 1;
         if (gate_raw) { gate = parameter(*gate_raw); vector_layout(residual, gate, rows_per_vector, vectors); }
         Tensor out = rt_->allocate_device(residual.shape(), state);
+        ProfileRegion region(*this, [] { return std::string("fused.linear_output+gated_residual"); }, bytes_of(accumulation) + bytes_of(residual) + bytes_of(out));
         check(vrb_linear_output_gated_residual(accumulation.data_as<float>(), bias_raw ? bias.data() : nullptr, residual.data(),
                                                code(residual.dtype()), gate_raw ? gate.data() : nullptr,
                                                gate_raw ? code(gate.dtype()) : 0, rows_per_vector, vectors, out.data(),
@@ -548,6 +654,7 @@ Tensor B200Backend::linear_swiglu(const Tensor& x, const Tensor& weight, const T
         std::vector<int64_t> shape = accumulation.shape();
         shape.back() = width / 2;
         Tensor out = rt_->allocate_device(shape, DType::BF16);
+        ProfileRegion region(*this, [] { return std::string("fused.linear_output+swiglu"); }, bytes_of(accumulation) + bytes_of(out));
         check(vrb_linear_output_swiglu(accumulation.data_as<float>(), bias_raw ? bias.data() : nullptr, out.data(), rows,
                                        width / 2, kLegacyStream));
         return out;
@@ -563,6 +670,7 @@ Tensor B200Backend::swiglu(const Tensor& raw) {
         std::vector<int64_t> shape = projected.shape();
         shape.back() = hidden;
         Tensor out = rt_->allocate_device(shape, dtype);
+        ProfileRegion region(*this, [] { return std::string("fused.swiglu"); }, bytes_of(projected) + bytes_of(out));
         check(vrb_swiglu(projected.data(), out.data(), code(dtype), rows, hidden, kLegacyStream));
         return out;
     });
@@ -581,6 +689,7 @@ Tensor B200Backend::linear_combine(const std::vector<Tensor>& values, const std:
             pointers.push_back(device.back().data());
         }
         Tensor out = rt_->allocate_device(device.front().shape(), dtype);
+        ProfileRegion region(*this, [] { return std::string("fused.sampler.linear_combine"); }, bytes_of(out) * (values.size() + 1));
         check(vrb_linear_combine(pointers.data(), coefficients.data(), static_cast<int>(values.size()), out.data(), code(dtype),
                                  out.numel(), declared_role ? 1 : 0, kLegacyStream));
         return out;
@@ -594,6 +703,7 @@ Tensor B200Backend::cfg_euler(const Tensor& sample_raw, const Tensor& u_raw, con
         Tensor sample = copy_to_device(sample_raw, dtype), u = copy_to_device(u_raw, dtype), c = copy_to_device(c_raw, dtype);
         require(sample.shape() == u.shape() && u.shape() == c.shape(), "Incompatible broadcast shapes");
         Tensor out = rt_->allocate_device(sample.shape(), dtype);
+        ProfileRegion region(*this, [] { return std::string("fused.sampler.cfg+euler"); }, bytes_of(out) * 4);
         check(vrb_cfg_euler(sample.data(), u.data(), c.data(), nullptr, out.data(), code(dtype), sample.numel(), guidance,
                             delta, subtract_prediction ? 1 : 0, guidance_role ? 1 : 0, solver_role ? 1 : 0, kLegacyStream));
         return out;

@@ -5,7 +5,7 @@
 // native/src/backend/cuda/cuda_backend.cu.
 //
 // Everything that is not on this path -- allocation and the temporary pool, host<->device
-// transfers and fences, GEMM, attention, convolutions, the memory runtime, profiling -- is
+// transfers and fences, GEMM, attention, convolutions, the memory runtime, the profiler itself -- is
 // forwarded to the device runtime backend given at construction (normally the reference's own
 // CudaBackend), so call sites that hold a `Backend&` (native/include/vrhino/architecture.h:33-42)
 // need no change: construct B200Backend(std::make_unique<CudaBackend>()) where they used to
@@ -112,20 +112,36 @@ public:
     void destroy_fence(vrhino::TransferFence f) override { rt_->destroy_fence(f); }
     Tensor copy_to_host(const Tensor& input) override { return rt_->copy_to_host(input); }
     void synchronize() override { rt_->synchronize(); }
-    void release_cached_device_memory() override { require_active_session(); rt_->release_cached_device_memory(); }
+    void release_cached_device_memory() override;   // also drops the dequantised-weight cache below
     size_t peak_device_bytes() const override { return rt_->peak_device_bytes(); }
     size_t weight_upload_bytes() const override { return rt_->weight_upload_bytes(); }
     double weight_upload_seconds() const override { return rt_->weight_upload_seconds(); }
+    // Profiling: the replaced operators record themselves in the device runtime's profiler through
+    // its region interface under the names the reference's own operators use
+    // (cuda_backend.cu:3011-3064: "norm.layer|rows=..|width=..|dtype=..", "norm.rms|..", "activation|..",
+    // "rope|..", "elementwise.add", "cast", "norm.group", "norm.pixel", "pixel_shuffle", "clamp", "exp",
+    // "sqrt", "quantized_dequant"), so profile_stats() shows them beside the forwarded ones; the fused
+    // forms appear as "fused.<name>".  profile_bytes() adds what the reference does not record: the
+    // algorithmic bytes (inputs read once + output written once) each profiled name has moved.
     void enable_profiling(bool e) override { rt_->enable_profiling(e); }
     bool profiling_enabled() const override { return rt_->profiling_enabled(); }
     std::map<std::string, vrhino::ProfileStat> profile_stats() override { return rt_->profile_stats(); }
+    const std::map<std::string, uint64_t>& profile_bytes() const { return profile_bytes_; }
     void profile_region_begin(const std::string& n) override { rt_->profile_region_begin(n); }
     void profile_region_end() override { rt_->profile_region_end(); }
     uint64_t weight_cache_hits() const override { return rt_->weight_cache_hits(); }
     uint64_t weight_cache_misses() const override { return rt_->weight_cache_misses(); }
     size_t weight_cache_resident_bytes() const override { return rt_->weight_cache_resident_bytes(); }
     size_t weight_cache_capacity_bytes() const override { return rt_->weight_cache_capacity_bytes(); }
-    void enable_weight_cache(bool e) override { rt_->enable_weight_cache(e); }
+    void enable_weight_cache(bool e) override { weight_cache_enabled_ = e; if (!e) drop_dequantized_cache(); rt_->enable_weight_cache(e); }
+    // Dequantised weights are kept on the device, keyed by the host payload like the reference's
+    // packed-byte cache (cuda_backend.cu:3236-3275), so a quantised weight is decoded once instead of
+    // once per linear() call (:3276-3295).  Least-recently-used entries go when the budget is exceeded;
+    // a weight larger than the budget is decoded per call as before.  Default budget: 48 GiB.
+    void set_dequantized_cache_budget(size_t bytes);
+    size_t dequantized_cache_resident_bytes() const { return dequant_resident_; }
+    uint64_t dequantized_cache_hits() const { return dequant_hits_; }
+    uint64_t dequantized_cache_misses() const { return dequant_misses_; }
     void enable_true_quant_compute(bool e) override { rt_->enable_true_quant_compute(e); }
     bool true_quant_compute_enabled() const override { return rt_->true_quant_compute_enabled(); }
     vrhino::QuantComputeStats quant_compute_stats() const override { return rt_->quant_compute_stats(); }
@@ -180,8 +196,18 @@ private:
     template <typename F> Tensor guarded(F&& body);
     template <typename F> Tensor unguarded(F&& body);
 
+    class ProfileRegion;
+    friend class ProfileRegion;
+    void drop_dequantized_cache();
+
     std::unique_ptr<vrhino::Backend> rt_;
     Tensor workspace_;
+    std::map<std::string, uint64_t> profile_bytes_;
+    struct DequantizedEntry { Tensor value; size_t bytes = 0; uint64_t last_use = 0; };
+    std::map<std::pair<const void*, int>, DequantizedEntry> dequant_cache_;
+    size_t dequant_resident_ = 0, dequant_budget_ = size_t{48} << 30;
+    uint64_t dequant_clock_ = 0, dequant_hits_ = 0, dequant_misses_ = 0;
+    bool weight_cache_enabled_ = true;
 };
 
 // ---- call-site view ---------------------------------------------------------------------------

@@ -50,13 +50,40 @@ struct FusionPlan {
 };
 FusionPlan plan_fusion(const vrhino::neural_graph::Description& description);
 
+// What evaluate_fused needs from a backend beyond vrhino::Backend: the four one-kernel chains.
+// B200Backend provides them; a test can provide stand-ins (fault injection on the host, no GPU).
+class FusedOperators {
+public:
+    virtual ~FusedOperators() = default;
+    virtual vrhino::Backend& backend() = 0;
+    virtual vrhino::Tensor layer_norm_modulate(const vrhino::Tensor& x, const vrhino::Tensor* weight, const vrhino::Tensor* bias,
+                                               float eps, const vrhino::Tensor& shift, const vrhino::Tensor& scale,
+                                               vrhino::DType output) = 0;
+    virtual vrhino::Tensor rms_norm_modulate(const vrhino::Tensor& x, float eps, const vrhino::Tensor& shift,
+                                             const vrhino::Tensor& scale, vrhino::DType output) = 0;
+    virtual vrhino::Tensor rms_norm_rope(const vrhino::Tensor& x, const vrhino::Tensor* weight, float eps,
+                                         const vrhino::Tensor* cosine, const vrhino::Tensor* sine, int heads,
+                                         vrhino::DType output) = 0;
+    virtual vrhino::Tensor gated_residual(const vrhino::Tensor& residual, const vrhino::Tensor& branch,
+                                          const vrhino::Tensor* gate, vrhino::DType state) = 0;
+};
+
 // Same contract as neural_graph::evaluate: inputs / parameters bound in slot order, host
-// tensors uploaded on demand, outputs in d.outputs order after a synchronize().
+// tensors uploaded on demand, outputs in d.outputs order after a synchronize().  Failures are
+// reported the way the reference evaluator reports them (neural_graph_evaluator.cpp:84-93, :162-175):
+// always a neural_graph::GraphError carrying code, phase (Bind / Run / Drain / Capture) and the node,
+// value and primitive being worked on; a backend exception becomes BackendFailure (CompletionFailure
+// while draining); and after a failure that may have left work enqueued the device is drained exactly
+// once, a failure of that drain being kept in secondary_completion instead of replacing the error.
 // drain = false leaves out that per-graph device synchronisation
 // (native/src/runtime/neural_graph_evaluator.cpp:151): every operator of the backend is enqueued on
 // the same stream, so a caller that keeps enqueueing (the next block's graph) needs no host
 // wait between graphs; a device fault then surfaces at the caller's next synchronising call
 // instead of as this graph's completion failure.
+std::vector<vrhino::Tensor> evaluate_fused(FusedOperators& operators, const vrhino::neural_graph::Graph& graph,
+                                           const std::vector<vrhino::Tensor>& inputs,
+                                           const std::vector<vrhino::Tensor>& parameters,
+                                           FusionStats* stats = nullptr, bool drain = true);
 std::vector<vrhino::Tensor> evaluate_fused(B200Backend& backend, const vrhino::neural_graph::Graph& graph,
                                            const std::vector<vrhino::Tensor>& inputs,
                                            const std::vector<vrhino::Tensor>& parameters,

@@ -509,6 +509,42 @@ def fused_rms_norm_rope(be, x, weight, eps, cosine, sine, heads=1, per_head_norm
     return out
 
 
+def fused_rms_norm_rope_pair(be, x_a, weight_a, x_b, weight_b, eps, cosine, sine, heads=1, per_head_norm=False,
+                             out_dtype=BF16, out=None):
+    """fused_rms_norm_rope on two tensors in ONE launch: the q and k projections of an attention
+    block (wan.cpp:38-52), or -- cosine None -- the cross-attention q and its text-token k, whose row
+    counts differ.  Same width, dtype and tables for both; each has its own norm weight.  Returns
+    (out_a, out_b), bit-identical to two fused_rms_norm_rope calls."""
+    x_a, x_b = _dense(x_a), _dense(x_b)
+    width = x_a.shape[-1]
+    if x_b.shape[-1] != width or x_a.dtype != x_b.dtype or weight_a.dtype != weight_b.dtype:
+        raise VrbError("Incompatible broadcast shapes")
+    rows_a, rows_b = x_a.numel() // width, x_b.numel() // width
+    head_width = width // heads
+    norm_width = head_width if per_head_norm else width
+    out_a, out_b = out if out is not None else (None, None)
+    out_a = _result(out_a, x_a.shape, out_dtype, x_a.device)
+    out_b = _result(out_b, x_b.shape, out_dtype, x_b.device)
+    if cosine is None:
+        f_rows, f_width, cp, sp = 0, 8, None, None
+    else:
+        if cosine.dtype != F32 or cosine.shape != sine.shape:
+            raise VrbError("RoPE frequency mismatch")
+        cosine, sine = _dense(cosine), _dense(sine)
+        f_width = cosine.shape[-1] * cosine.shape[-2] if cosine.dim() >= 2 else cosine.shape[-1]
+        if cosine.shape[-1] != head_width or f_width not in (head_width, width):
+            raise VrbError("Incompatible broadcast shapes")
+        f_rows = cosine.numel() // f_width
+        for x, rows in ((x_a, rows_a), (x_b, rows_b)):
+            if f_rows not in (rows, rows // x.shape[0]):
+                raise VrbError("Incompatible broadcast shapes")
+        cp, sp = _ptr(cosine), _ptr(sine)
+    call("vrb_rms_norm_rope_pair", _ptr(x_a), _ptr(weight_a), _ptr(out_a), rows_a, _ptr(x_b), _ptr(weight_b), _ptr(out_b), rows_b,
+         _code(x_a), _code(weight_a), cp, sp, _lib.F32, f_rows, f_width, 1, _code(out_dtype), width, norm_width,
+         ctypes.c_float(eps), _stream())
+    return out_a, out_b
+
+
 def fused_gated_residual(be, policy, residual, branch, gate, out=None):
     """gated_residual(...) / residual_add(...) (gate None) of common.cpp:134-144 in one pass."""
     residual, branch = _dense(residual), _dense(branch)

@@ -95,8 +95,11 @@ class WanBlock:
         blk.token_rows, blk.text_rows = (r0, r1), (t0, t1)
         return blk
 
-    def launches(self, fuse_residual_norm: bool = False) -> List[Launch]:
-        """fuse_residual_norm: C+D and F+G each as ONE launch (residual update + the LayerNorm that
+    def launches(self, fuse_residual_norm: bool = False, pair_qk: bool = False) -> List[Launch]:
+        """pair_qk: the q and k projections normalised and rotated by ONE launch (they are independent
+        and share the RoPE tables, which then cross HBM once), likewise the cross-attention q and k: two
+        launches fewer, bit-identical outputs.
+        fuse_residual_norm: C+D and F+G each as ONE launch (residual update + the LayerNorm that
         reads the updated stream, wan.cpp:95-107 of the reference) -- 9 launches instead of 11.  Such a
         launch reads residual and branch and writes stream and normalised output: 4 passes where
         the two launches it replaces make 5."""
@@ -119,32 +122,35 @@ class WanBlock:
         def H(): o["H"] = be.activation(self.ffn_hidden, ops.GELU_TANH, out=o.get("H"))
         def I(): o["I"] = ops.fused_gated_residual(be, p, self.x, self.ffn_out, r[5], out=o.get("I"))
 
+        def Bqk(): o["Bq"], o["Bk"] = ops.fused_rms_norm_rope_pair(be, self.q, self.wq, self.k, self.wk, e, self.cos, self.sin,
+                                                                   heads=self.heads, out=(o.get("Bq"), o.get("Bk")))
+        def Eqk(): o["Eq"], o["Ek"] = ops.fused_rms_norm_rope_pair(be, self.cross_q, self.wcq, self.cross_k, self.wck, e, None, None,
+                                                                   heads=self.heads, out=(o.get("Eq"), o.get("Ek")))
+
         def CD(): o["C"], o["D"] = ops.fused_gated_residual_layer_norm(be, p, self.x, self.proj, r[2], self.gamma3, self.beta3, e,
                                                                        state_out=o.get("C"), out=o.get("D"))
         def FG(): o["F"], o["G"] = ops.fused_gated_residual_layer_norm(be, p, self.x, self.cross, None, None, None, e, r[3], r[4],
                                                                        state_out=o.get("F"), out=o.get("G"))
 
         table = self.cos.numel() * 4 * 2
+        # q / k norm + RoPE and the cross-attention norms: two launches each, or one pair launch that reads
+        # the RoPE tables once
+        if pair_qk:
+            b_launches = [Launch("B rms_rope q+k", Bqk, 2 * (act * 4 + vec) + table // 2)]
+            e_launches = [Launch("E rms cross q+k", Eqk, act * 4 + self.cross_k.numel() * 4 + 2 * vec)]
+        else:
+            b_launches = [Launch("B rms_rope q", Bq, act * 4 + vec + table // 2), Launch("B rms_rope k", Bk, act * 4 + vec + table // 2)]
+            e_launches = [Launch("E rms cross q", Eq, act * 4 + vec), Launch("E rms cross k", Ek, self.cross_k.numel() * 4 + vec)]
         if fuse_residual_norm:
-            return [
-                Launch("A ln_modulate", A, act * (hb + 2) + 2 * vec),
-                Launch("B rms_rope q", Bq, act * 4 + vec + table // 2),
-                Launch("B rms_rope k", Bk, act * 4 + vec + table // 2),
-                Launch("C+D gated_residual ln_affine", CD, act * (hb + 2 + hb + 2) + 3 * vec),
-                Launch("E rms cross q", Eq, act * 4 + vec),
-                Launch("E rms cross k", Ek, self.cross_k.numel() * 4 + vec),
+            return [Launch("A ln_modulate", A, act * (hb + 2) + 2 * vec)] + b_launches + [
+                Launch("C+D gated_residual ln_affine", CD, act * (hb + 2 + hb + 2) + 3 * vec)] + e_launches + [
                 Launch("F+G residual_add ln_modulate", FG, act * (hb + 2 + hb + 2) + 2 * vec),
                 Launch("H gelu_tanh", H, self.ffn_hidden.numel() * 4),
                 Launch("I gated_residual", I, act * (hb + 2 + hb) + vec),
             ]
-        return [
-            Launch("A ln_modulate", A, act * (hb + 2) + 2 * vec),
-            Launch("B rms_rope q", Bq, act * 4 + vec + table // 2),
-            Launch("B rms_rope k", Bk, act * 4 + vec + table // 2),
+        return [Launch("A ln_modulate", A, act * (hb + 2) + 2 * vec)] + b_launches + [
             Launch("C gated_residual", C, act * (hb + 2 + hb) + vec),
-            Launch("D ln_affine", Dn, act * (hb + 2) + 2 * vec),
-            Launch("E rms cross q", Eq, act * 4 + vec),
-            Launch("E rms cross k", Ek, self.cross_k.numel() * 4 + vec),
+            Launch("D ln_affine", Dn, act * (hb + 2) + 2 * vec)] + e_launches + [
             Launch("F residual_add", Fr, act * (hb + 2 + hb)),
             Launch("G ln_modulate", G, act * (hb + 2) + 2 * vec),
             Launch("H gelu_tanh", H, self.ffn_hidden.numel() * 4),
