@@ -32,6 +32,25 @@ def test_binding_table_matches_header(cuda_lib):
     assert sorted(_lib.SIGNATURES) == declared_symbols()
 
 
+def test_sharded_library_exports_its_header(cuda_lib):
+    """libvrb_sharded.so (the C++ multi-GPU host layer) exports what include/vrb_sharded.h declares, and its
+    bounded wait works on the host: with a peer that never joins, vrbs_wait's loop gives up after the
+    timeout, aborts the communicator once, and later calls are refused."""
+    from vrhino_b200 import _lib, build
+    if not os.path.exists(_lib.SHARDED_LIB_PATH):
+        build.build_sharded()
+    lib = _lib.load_sharded()
+    text = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "vrb_sharded.h")).read(), flags=re.S)
+    declared = sorted(set(re.findall(r"\b(vrbs_[a-z0-9_]+)\s*\(", text)))
+    assert declared == sorted(_lib.SHARDED_SIGNATURES)
+    assert not [n for n in declared if not hasattr(lib, n)]
+    report = (ctypes.c_int64 * 4)()
+    assert lib.vrbs_watchdog_selftest(120, report) == 0
+    status, waited_ms, aborts, later = list(report)
+    assert status == -6 and 120 <= waited_ms < 2000 and aborts == 1 and later == -7
+    assert b"aborted" in lib.vrbs_last_error()
+
+
 def test_exports_are_plain_c(cuda_lib):
     from vrhino_b200 import _lib
     out = subprocess.run(["nm", "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True, check=True).stdout

@@ -95,7 +95,43 @@ _RESTYPES = {
     "vrb_host_release": None,
 }
 
+# the multi-GPU host layer (include/vrb_sharded.h)
+SHARDED_LIB_PATH = os.path.join(_PKG, "libvrb_sharded.so")
+_pp = _c.POINTER(_c.c_void_p)
+SHARDED_SIGNATURES = {
+    "vrbs_last_error": [],
+    "vrbs_unique_id": [_vp],
+    "vrbs_create": [_pp, _i, _i, _vp, _i],
+    "vrbs_destroy": [_vp],
+    "vrbs_rank": [_vp],
+    "vrbs_world": [_vp],
+    "vrbs_aborted": [_vp],
+    "vrbs_group_norm_workspace_bytes": [_vp, _i64, _i, _i, _sz],
+    "vrbs_group_norm": [_vp, _vp, _i, _vp, _i, _vp, _i, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _f, _i, _i, _vp, _vp, _sz, _vp],
+    "vrbs_cfg_euler": [_vp, _vp, _vp, _vp, _vp, _i, _i64, _f, _f, _i, _i, _i, _vp],
+    "vrbs_wait": [_vp, _vp],
+    "vrbs_watchdog_selftest": [_i, _c.POINTER(_c.c_int64)],
+}
+_SHARDED_RESTYPES = {"vrbs_last_error": _c.c_char_p, "vrbs_group_norm_workspace_bytes": _c.c_size_t}
+
 _lib = None
+_sharded = None
+
+
+def load_sharded() -> ctypes.CDLL:
+    """Load libvrb_sharded.so (C++ over NCCL and libvrb.so).  Raises if it was not built."""
+    global _sharded
+    if _sharded is None:
+        load()
+        if not os.path.exists(SHARDED_LIB_PATH):
+            raise VrbError(f"{SHARDED_LIB_PATH} is missing: build it with `python -m vrhino_b200.build`")
+        lib = ctypes.CDLL(SHARDED_LIB_PATH)
+        for name, argtypes in SHARDED_SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = _SHARDED_RESTYPES.get(name, _c.c_int)
+        _sharded = lib
+    return _sharded
 
 
 def load() -> ctypes.CDLL:

@@ -1,4 +1,5 @@
-"""Build the CUDA operator library (``libvrb.so``) in-tree with nvcc for sm_100a.
+"""Build the CUDA operator library (``libvrb.so``) in-tree with nvcc for sm_100a, and the
+multi-GPU host layer (``libvrb_sharded.so``: C++ over NCCL and libvrb.so) with the host compiler.
 
 ``python -m vrhino_b200.build`` compiles every ``csrc/*.cu`` to an object file (in parallel)
 and links them into ``vrhino_b200/libvrb.so``.  nvcc cross-compiles, so no GPU is needed.
@@ -18,6 +19,8 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(PKG, "libvrb.so")
+SHARDED_SRC = os.path.join(PKG, "host", "sharded_ops.cpp")
+SHARDED_LIB = os.path.join(PKG, "libvrb_sharded.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -73,7 +76,22 @@ def build(force: bool = False, verbose: bool = False) -> str:
     objects = [os.path.join(OBJ, os.path.basename(s)[:-3] + ".o") for s in _sources()]
     if force or jobs or _stale(LIB, objects):
         subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB, *objects, "-lcudart"], check=True)
+    build_sharded(force)
     return LIB
+
+
+def build_sharded(force: bool = False) -> str:
+    """libvrb_sharded.so: needs nccl.h / libnccl (the system's) next to the CUDA toolkit."""
+    headers = glob.glob(os.path.join(ROOT, "include", "*.h"))
+    if not (force or _stale(SHARDED_LIB, [SHARDED_SRC, LIB] + headers)):
+        return SHARDED_LIB
+    cuda_home = os.path.dirname(os.path.dirname(_nvcc()))
+    cxx = shutil.which("g++") or "g++"
+    subprocess.run([cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-I", os.path.join(ROOT, "include"),
+                    "-I", os.path.join(cuda_home, "include"), "-o", SHARDED_LIB, SHARDED_SRC,
+                    "-L", PKG, "-lvrb", "-Wl,-rpath,$ORIGIN", "-L", os.path.join(cuda_home, "lib64"), "-lcudart", "-lnccl",
+                    "-lpthread"], check=True)
+    return SHARDED_LIB
 
 
 if __name__ == "__main__":
