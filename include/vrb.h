@@ -127,6 +127,13 @@ int vrb_pixel_norm(const void* x, int dtype, const void* scale, const void* shif
                    int fuse_silu, void* out, int out_dtype, int64_t outer, int64_t channels,
                    int64_t inner, float eps, vrb_stream stream);
 
+/* CudaBackend::l2_normalize (:5088-5110, l2_normalize_kernel :1142-1176) over the middle axis of
+ * x [outer, channels, inner]:  y = x / (sqrtf(sum_c(x^2)) + eps)  in x's dtype; eps >= 0.  Same tiles and
+ * F32 summation as vrb_pixel_norm (the reference's 256-thread tree adds the same squares in another
+ * order: results agree to the last bits of the sum). */
+int vrb_l2_normalize(const void* x, void* out, int dtype, int64_t outer, int64_t channels, int64_t inner,
+                     float eps, vrb_stream stream);
+
 /* CudaBackend::pixel_shuffle_nd (:5112-5118, pixel_shuffle_kernel :2170-2186):
  * x [batch, channels*ft*fh*fw, frames, height, width] -> out [batch, channels, frames*ft, height*fh, width*fw],
  * out[b, c, t*ft+pt, h*fh+ph, w*fw+pw] = x[b, ((c*ft+pt)*fh+ph)*fw+pw, t, h, w]. */
@@ -343,6 +350,20 @@ int vrb_rms_norm_gated_residual(const void* residual, int residual_dtype,
                                 int64_t rows_per_vector, int64_t gate_vectors,
                                 void* out, int state_dtype, int64_t rows, int64_t width,
                                 float eps, vrb_stream stream);
+
+/* The Mochi block's residual update and the pre-norm of the layer that follows it, in one pass
+ * (native/src/architectures/mochi.cpp:204-211 then :228-231):
+ *   state_out = vrb_rms_norm_gated_residual(residual, branch, gate', branch_eps),  gate' = tanh(gate) if gate_tanh
+ *               (activation(gate, Tanh) in the gate's dtype, as the block computes it) else gate
+ *   out       = vrb_rms_norm_scale(state_out, scale, eps)                          in the stream's dtype
+ * One kernel when residual, branch and the updated stream are BF16 (each tensor crosses HBM once: 8 B
+ * per element instead of 6 + 4, and the tanh of the [vectors, width] gate costs no launch); other dtype
+ * contracts run the two operators (then gate_tanh must be 0: apply vrb_activation to the gate first). */
+int vrb_rms_norm_gated_residual_rms_norm_scale(
+    const void* residual, int residual_dtype, const void* branch, int branch_dtype, float branch_eps,
+    const void* gate, int gate_dtype, int gate_tanh, int64_t gate_rows_per_vector, int64_t gate_vectors,
+    void* state_out, int state_dtype, const void* scale, int scale_dtype, int64_t rows_per_vector, int64_t scale_vectors,
+    void* out, int64_t rows, int64_t width, float eps, vrb_stream stream);
 
 /* ---- the bf16 linear's epilogue and the operator that reads its result --------------------
  * CudaBackend::linear (native/src/backend/cuda/cuda_backend.cu:3661-3866) leaves the GEMM result in an

@@ -288,6 +288,22 @@ class OracleBackend:
                              ctypes.c_int64(inner), ctypes.c_float(eps))
         return T(out, dtype)
 
+    def l2_normalize(self, raw: T, dim: int, eps: float) -> T:
+        """CudaBackend::l2_normalize (native/src/backend/cuda/cuda_backend.cu:5088-5110): x / (sqrt(sum(x^2)
+        over `dim`) + eps) in x's dtype, the kernel's 256-partial summation schedule (:1142-1176)."""
+        dtype = self._dtype_of(raw)
+        x = self.copy_to_device(raw, dtype)
+        dim = dim + len(x.shape) if dim < 0 else dim
+        if not (0 <= dim < len(x.shape)) or eps < 0:
+            raise ValueError("l2 normalize contract violation")
+        channels = x.shape[dim]
+        inner = int(np.prod(x.shape[dim + 1:]))
+        outer = x.numel // (channels * inner)
+        out = np.empty(x.shape, dtype=_NP[dtype])
+        lib().orc_l2_normalize(_p(x.data), _p(out), _CODE[dtype], ctypes.c_int64(outer), ctypes.c_int64(channels),
+                               ctypes.c_int64(inner), ctypes.c_float(eps))
+        return T(out, dtype)
+
     def pixel_shuffle_nd(self, raw: T, factors) -> T:
         """CudaBackend::pixel_shuffle_nd (native/src/backend/cuda/cuda_backend.cu:5112-5118) with the index map of
         pixel_shuffle_kernel (:2170-2186): packed channel ((c*ft+pt)*fh+ph)*fw+pw."""

@@ -166,7 +166,8 @@ class RefCuda:
                      "refc_layer_norm", "refc_rms_norm", "refc_activation", "refc_rope", "refc_group_norm", "refc_clamp",
                      "refc_exp", "refc_sqrt", "refc_dequantize", "refc_modulate", "refc_attention_norm", "refc_operation_rope",
                      "refc_residual_add", "refc_gated_residual", "refc_cfg_combine", "refc_euler_update", "refc_flow_to_x0",
-                     "refc_frame_group_norm", "refc_linear", "refc_pixel_norm", "refc_pixel_shuffle", "refc_repeat"):
+                     "refc_frame_group_norm", "refc_linear", "refc_pixel_norm", "refc_pixel_shuffle", "refc_repeat",
+                     "refc_l2_normalize"):
             getattr(lib, name).restype = _c.c_int64
         lib.refc_profile_total_ms.restype = _c.c_double
         self.lib = lib
@@ -218,6 +219,7 @@ class RefCuda:
         return self._h(self.lib.refc_rms_norm(self._i(x), self._i(w), _c.c_float(eps), _c.c_int64(axis), int(out_dtype)))
     def linear(self, x, w, bias): return self._h(self.lib.refc_linear(self._i(x), self._i(w), self._i(bias)))
     def pixel_norm(self, x, dim, eps): return self._h(self.lib.refc_pixel_norm(self._i(x), _c.c_int64(dim), _c.c_float(eps)))
+    def l2_normalize(self, x, dim, eps): return self._h(self.lib.refc_l2_normalize(self._i(x), _c.c_int64(dim), _c.c_float(eps)))
     def pixel_shuffle(self, x, factors):
         return self._h(self.lib.refc_pixel_shuffle(self._i(x), *(_c.c_int64(int(f)) for f in factors)))
     def repeat(self, x, copies, dim): return self._h(self.lib.refc_repeat(self._i(x), int(copies), _c.c_int64(dim)))

@@ -159,6 +159,9 @@ int64_t refc_linear(int64_t x, int64_t w, int64_t bias) {
 int64_t refc_pixel_norm(int64_t x, int64_t dim, float eps) {
     return guarded([&] { return keep(g_backend->pixel_norm(at(x), dim, eps)); });
 }
+int64_t refc_l2_normalize(int64_t x, int64_t dim, float eps) {
+    return guarded([&] { return keep(g_backend->l2_normalize(at(x), dim, eps)); });
+}
 int64_t refc_pixel_shuffle(int64_t x, int64_t ft, int64_t fh, int64_t fw) {
     return guarded([&] { return keep(g_backend->pixel_shuffle_nd(at(x), {ft, fh, fw})); });
 }

@@ -356,6 +356,32 @@ void orc_pixel_norm(const void* x, void* out, int dt, int64_t outer, int64_t cha
         }
 }
 
+/* ---- l2_normalize (CudaBackend::l2_normalize :5088-5110, l2_normalize_kernel :1142-1176) ----
+ * x [outer, channels, inner], one 256-thread block per (outer, inner) position: thread t adds the squares of
+ * channels t, t+256, ... with one FMA each, the block tree (strides 128 ... 1) adds the partials;
+ * denominator = sqrtf(total) + eps; out = x / denominator, rounded to x's dtype. */
+void orc_l2_normalize(const void* x, void* out, int dt, int64_t outer, int64_t channels, int64_t inner, float eps) {
+#pragma omp parallel for schedule(static)
+    for (int64_t o = 0; o < outer; ++o)
+        for (int64_t i = 0; i < inner; ++i) {
+            const int64_t base = o * channels * inner + i;
+            float part[256];
+            for (int t = 0; t < 256; ++t) {
+                float q = 0.0f;
+                for (int64_t c = t; c < channels; c += 256) {
+                    const float v = ld(x, dt, base + c * inner);
+                    q = fmaf(v, v, q);
+                }
+                part[t] = q;
+            }
+            for (int stride = 128; stride > 0; stride /= 2)
+                for (int t = 0; t < stride; ++t) part[t] += part[t + stride];
+            const float denominator = sqrtf(part[0]) + eps;
+            for (int64_t c = 0; c < channels; ++c)
+                st(out, dt, base + c * inner, ld(x, dt, base + c * inner) / denominator);
+        }
+}
+
 /* ---- RoPE (rope_kernel :1200-1215): adjacent pairs, two separately rounded products ---- */
 int orc_rope(const void* x, int x_dt, int x_rank, const int64_t* x_shape,
              const void* cosine, const void* sine, int f_dt, int f_rank, const int64_t* f_shape,

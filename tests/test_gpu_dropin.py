@@ -440,3 +440,30 @@ def test_dequantised_weight_is_decoded_once(dropin):
     got2, _ = rd.download(h2, (rows, inner))
     assert np.array_equal(got2, want)
     rd.dequantize_repeated(0, packed, scales, rows, inner, inner, ref.BF16, repeats=0, budget=48 << 30)
+
+
+def test_l2_normalize_reference_kernel_oracle_and_drop_in_agree(orc, dropin):
+    """No golden vector exists for l2_normalize, so the three are compared live: the reference's own kernel
+    (its CUDA backend compiled for sm_100a), the CPU oracle that restates it (bit for bit on F32: same
+    summation order), and the replaced backend (other summation order: <= 2 bf16 ulp / 1e-5)."""
+    from oracle import ref
+    if not ref.available_cuda():
+        pytest.skip("oracle/_ref/libvrhino_ref_cuda.so has not been built")
+    rc = ref.RefCuda()
+    rng = np.random.default_rng(8)
+    try:
+        for shape, dt in (((1, 512, 6, 10), "f32"), ((2, 256, 5, 8), "bf16"), ((3, 40), "f32")):
+            x = (rng.standard_normal(shape) * 1.5 + 0.2).astype(np.float32)
+            bits = cases.to_bits(x, dt)
+            code = {"f32": ref.F32, "bf16": ref.BF16}[dt]
+            reference, _ = rc.download(rc.l2_normalize(rc.upload(bits, code), 1, 1e-10), shape)
+            mine, _ = dropin.download(dropin.l2_normalize(dropin.upload(bits, code), 1, 1e-10), shape)
+            want = orc.OracleBackend().l2_normalize(orc.T(bits, dt), 1, 1e-10)
+            if dt == "f32":
+                assert np.array_equal(want.data.view(np.uint32), reference.view(np.uint32)), "oracle vs the reference's kernel"
+                assert np.allclose(mine, reference, rtol=1e-5, atol=1e-8)
+            else:
+                assert orc.bf16_ulp_distance(want.data, reference).max() <= 1
+                assert orc.bf16_ulp_distance(mine, reference).max() <= 2
+    finally:
+        rc.lib.refc_shutdown()

@@ -67,3 +67,21 @@ def test_pixel_norm_other_axes_and_errors(orc, gpu):
         be.pixel_norm(to_torch(x), 3, 1e-8)
     with pytest.raises(ops.VrbError):
         ops.fused_pixel_norm_modulate(be, to_torch(x), torch.zeros(4, 5, 1, device="cuda"), torch.zeros(4, 5, 1, device="cuda"))
+
+
+@pytest.mark.parametrize("shape", SHAPES + [(1, 512, 38, 38), (2, 256, 19, 24)])      # + the detector's feature maps
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_l2_normalize(orc, gpu, shape, dt):
+    """CudaBackend::l2_normalize: x / (sqrt(sum of squares over the channels) + eps).  The kernels add the
+    squares in the tile kernels' order, the reference (and the oracle) in its 256-thread tree: <= 2 bf16 ulp /
+    1e-5 relative, and within this library inner == 1 and inner > 1 must agree with a permuted call."""
+    be, ops = gpu
+    from vrhino_b200 import synth
+    x = orc.tensor(synth.normal(shape, 0.2, 1.5, seed=shape[1]), dt)
+    want = orc.OracleBackend().l2_normalize(x, 1, 1e-10)
+    got = be.l2_normalize(to_torch(x), 1, 1e-10)
+    assert_close(orc, got, want, max_ulp=2, rel=1e-5, what=f"l2_normalize {shape} {dt}")
+    with pytest.raises(ops.VrbError, match="l2 normalize contract violation"):
+        be.l2_normalize(to_torch(x), len(shape), 1e-10)
+    with pytest.raises(ops.VrbError, match="l2 normalize contract violation"):
+        be.l2_normalize(to_torch(x), 1, -1.0)

@@ -252,6 +252,37 @@ def test_rms_norm_gated_residual_mochi(orc, gpu, state, width, batch):
     assert_close(orc, got, want, rel=1e-5, atol=1e-6, what="mochi normalized gated residual")
 
 
+@pytest.mark.parametrize("state", DTYPES)
+@pytest.mark.parametrize("width,batch,tokens", [(3072, 1, 37), (3072, 2, 9), (1536, 2, 300), (264, 1, 11), (24, 3, 5)])
+def test_mochi_residual_update_merged_with_the_next_pre_norm(orc, gpu, state, width, batch, tokens):
+    """mochi.cpp:204-211 then :228-231: x' = x + rms_norm(branch) * tanh(gate);  y = rms_norm(x') * (1 + scale).
+    The one-kernel form (bf16 stream) gives the bits of this library's three launches (tanh, residual update,
+    pre-norm), and both agree with the oracle's operator chain; an F32 stream takes the separate launches."""
+    import torch
+    be, ops = gpu
+    from vrhino_b200 import synth
+    obe = orc.OracleBackend()
+    opol = orc.Policy(residual=state)
+    pol = ops.Policy(residual=_torch_dtype(state))
+    res = orc.tensor(synth.normal((batch, tokens, width), seed=1), state)
+    branch = orc.tensor(synth.normal((batch, tokens, width), seed=2), "bf16")
+    gate = orc.tensor(synth.normal((batch, width), std=0.5, seed=3), "f32")
+    scale = orc.tensor(synth.normal((batch, 1, width), std=0.1, seed=4), "f32")
+    want_state = orc.normalized_gated_residual(obe, opol, res, branch, gate)
+    want_out = orc.mochi_norm_scale(obe, want_state, scale)
+    got_state, got_out = ops.fused_rms_norm_gated_residual_norm_scale(be, pol, to_torch(res), to_torch(branch), to_torch(gate),
+                                                                      to_torch(scale))
+    bounded = be.activation(to_torch(gate), ops.TANH)
+    sep_state = ops.fused_rms_norm_gated_residual(be, pol, to_torch(res), to_torch(branch), bounded, 1e-6)
+    sep_out = ops.fused_rms_norm_scale(be, sep_state, to_torch(scale), 1e-6)
+    view = torch.int16 if state == "bf16" else torch.int32
+    assert torch.equal(got_state.view(view), sep_state.view(view)), "merged stream differs from the separate launches"
+    assert torch.equal(got_out.view(view), sep_out.view(view)), "merged pre-norm differs from the separate launches"
+    assert_close(orc, got_state, want_state, rel=1e-5, atol=1e-6, what=f"mochi merged: stream {state} {width}")
+    assert_close(orc, got_out, want_out, rel=1e-5, atol=1e-6, flip_atol=2.0 ** -8 * 8.0, flip_frac=2e-3,
+                 what=f"mochi merged: pre-norm {state} {width}")
+
+
 @pytest.mark.parametrize("width,batch,tokens", [(1536, 1, 21), (1536, 2, 9), (5120, 1, 5), (3072, 2, 6), (2048, 1, 7), (128, 1, 40),
                                                 (264, 1, 11), (24, 3, 5)])
 @pytest.mark.parametrize("gated", [True, False])

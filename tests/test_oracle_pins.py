@@ -217,6 +217,18 @@ def test_group_norm_groups_equal_channels(orc, be, shape):
     close(got.reshape(flat.shape), (flat - mean) / np.sqrt(var + 1e-5), 5e-5)
 
 
+@pytest.mark.parametrize("shape", [(1, 2, 2), (1, 3, 1, 2)])
+def test_l2_normalize(orc, be, shape):
+    """primitive_tests.cpp:546: x / (sqrt(sum over channels of x^2) + 1e-10), channels = axis 1."""
+    x = sequence(int(np.prod(shape)), 0.2, 0.2).reshape(shape)
+    got = be.l2_normalize(orc.tensor(x), 1, 1e-10).data
+    flat = x.reshape(shape[0], shape[1], -1)
+    expected = flat / (np.sqrt((flat.astype(np.float32) ** 2).sum(axis=1, keepdims=True, dtype=np.float32)) + np.float32(1e-10))
+    close(got.reshape(flat.shape), expected)
+    with pytest.raises(ValueError, match="l2 normalize contract violation"):
+        be.l2_normalize(orc.tensor(x), 7, 1e-10)
+
+
 def test_clamp_exp_sqrt(orc, be):
     close(be.clamp(orc.tensor([-2, -1, 0, 1, 2]), -0.5, 0.75).data, [-0.5, -0.5, 0, 0.75, 0.75])
     close(be.clamp(orc.tensor([[-3, 0.2], [4, 0.8]]), 0, 1).data, [0, 0.2, 1, 0.8])

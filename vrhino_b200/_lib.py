@@ -67,10 +67,13 @@ SIGNATURES = {
     "vrb_rms_norm_rope_pair": [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i, _i, _vp, _vp, _i, _i64, _i64, _i64, _i, _i64, _i64, _f, _vp],
     "vrb_gated_residual": [_vp, _i, _vp, _i, _vp, _i, _i64, _i64, _vp, _i, _i64, _i64, _vp],
     "vrb_rms_norm_gated_residual": [_vp, _i, _vp, _i, _vp, _i, _i64, _i64, _vp, _i, _i64, _i64, _f, _vp],
+    "vrb_rms_norm_gated_residual_rms_norm_scale": [_vp, _i, _vp, _i, _f, _vp, _i, _i, _i64, _i64, _vp, _i, _vp, _i, _i64, _i64,
+                                                   _vp, _i64, _i64, _f, _vp],
     "vrb_swiglu": [_vp, _vp, _i, _i64, _i64, _vp],
     "vrb_linear_combine": [_vp, _vp, _i, _vp, _i, _i64, _i, _vp],
     "vrb_pixel_shuffle": [_vp, _vp, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _vp],
     "vrb_depth_to_space_residual": [_vp, _vp, _vp, _i, _i64, _i64, _i64, _i64, _i64, _vp],
+    "vrb_l2_normalize": [_vp, _vp, _i, _i64, _i64, _i64, _f, _vp],
     "vrb_pixel_norm": [_vp, _i, _vp, _vp, _i, _i, _vp, _i, _i64, _i64, _i64, _f, _vp],
     "vrb_linear_output": [_vp, _vp, _vp, _i64, _i64, _vp],
     "vrb_linear_output_activation": [_vp, _vp, _i, _vp, _i64, _i64, _vp],

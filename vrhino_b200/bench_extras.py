@@ -50,16 +50,19 @@ def _launch_table(launches, steps, warmup, peak):
              "frac_of_measured_peak": l.bytes / per[l.name] / 1e6 / peak} for l in launches]
     nbytes = sum(l.bytes for l in launches)
     return {"us": total * 1e3, "gbs": nbytes / total / 1e6, "algorithmic_mb": nbytes / 1e6,
-            "frac_of_measured_peak": nbytes / total / 1e6 / peak, "launches": rows}
+            "frac_of_measured_peak": nbytes / total / 1e6 / peak, "launches": rows,
+            "timing": "whole list back to back; each launch back to back with itself (tensors under 126 MB stay in L2 then)"}
 
 
-def single_gpu_configs(be, peak, steps=5, warmup=2):
+def single_gpu_configs(be, peak, steps=10, warmup=2):
     """Headline configurations 3, 4 and 5 at full size on one GPU: per-launch device times."""
     out = {}
     builders = {
         "wan22_step (config 3: D=5120 block chain, FP8 dequant 5120x13824, CFG + Euler on the F32 latent)":
             lambda: workloads.Wan22Step(be, tokens=32760).launches(),
         "mochi_block (config 4: 44520 tokens x 3072, SwiGLU 8192)": lambda: workloads.MochiBlock(be, tokens=44520).launches(),
+        "mochi_block, fewest launches (q+k as one launch, residual update + next pre-norm + tanh(gate) as one)":
+            lambda: workloads.MochiBlock(be, tokens=44520).launches(merge_tail=True),
         "vae_group_norm_silu (config 5: [1,256,28,240,424] bf16, 32 groups)": lambda: workloads.VaeGroupNorm(be).launches(),
     }
     for name, build in builders.items():
@@ -94,15 +97,18 @@ def sharded_forms(be, world, rank, dist, barrier, max_over_ranks, peak, steps=10
         tokens = 44520
         t0, t1 = sharded.token_range(tokens, rank, world)
         blk = workloads.MochiBlock(be, tokens=t1 - t0, seed=100 + rank)
-        launches = blk.launches()
-        for l in launches:
-            l.fn()
-        compiled = workloads.compile_launches(launches)
-        ms = _time_steps(lambda: [l.fn() for l in compiled], steps, warmup, barrier, max_over_ranks)
-        whole_bytes = sum(l.bytes for l in launches) * tokens / (t1 - t0)
-        out["mochi_block_token_sharded"] = {"us": ms * 1e3, "tokens_per_rank": t1 - t0, "aggregate_gbs": whole_bytes / ms / 1e6,
-                                            "collectives": "none (row-independent operators)"}
-        del blk, launches, compiled
+        entry = {"tokens_per_rank": t1 - t0, "collectives": "none (row-independent operators)"}
+        for label, merge in (("five_launches", False), ("three_launches", True)):
+            launches = blk.launches(merge_tail=True) if merge else blk.launches()
+            for l in launches:
+                l.fn()
+            compiled = workloads.compile_launches(launches)
+            ms = _time_steps(lambda: [l.fn() for l in compiled], steps, warmup, barrier, max_over_ranks)
+            whole_bytes = sum(l.bytes for l in launches) * tokens / (t1 - t0)
+            entry[label] = {"us": ms * 1e3, "aggregate_gbs": whole_bytes / ms / 1e6}
+            del launches, compiled
+        out["mochi_block_token_sharded"] = entry
+        del blk
     except Exception as exc:
         out["mochi_block_token_sharded"] = {"error": str(exc)[:200]}
     torch.cuda.empty_cache()

@@ -179,6 +179,25 @@ __device__ __forceinline__ void round8_bf16_inplace(float (&v)[8]) {
     }
 }
 
+// 32 consecutive bytes in ONE store instruction (sm_100 has 256-bit global accesses).  A thread that
+// writes 32 adjacent bytes as two 16-byte stores makes every store instruction of its warp touch each
+// 32-byte sector half: measured on B200 a 1-read : 2-write stream reaches 4.6 TB/s that way and 5.6 TB/s
+// with 32-byte stores (write-only: 5.9 TB/s either way).  `p` must be 32-byte aligned; store32() checks
+// and falls back to two 16-byte stores.
+__device__ __forceinline__ void store32_aligned(void* p, const uint4& a, const uint4& b) {
+    asm volatile("st.global.cs.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+                 "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+__device__ __forceinline__ void store32(void* p, const uint4& a, const uint4& b) {
+    if ((reinterpret_cast<uintptr_t>(p) & 31u) == 0) {
+        store32_aligned(p, a, b);
+    } else {
+        __stcs(static_cast<uint4*>(p), a);
+        __stcs(static_cast<uint4*>(p) + 1, b);
+    }
+}
+
 // Streaming store of 8 consecutive elements (RNE narrowing for bf16).
 __device__ __forceinline__ void store8(void* base, int dt, int64_t e, const float (&v)[8]) {
     if (dt == VRB_BF16) {
@@ -187,10 +206,16 @@ __device__ __forceinline__ void store8(void* base, int dt, int64_t e, const floa
         r.z = pack_bf16x2(v[4], v[5]); r.w = pack_bf16x2(v[6], v[7]);
         __stcs(reinterpret_cast<uint4*>(static_cast<uint16_t*>(base) + e), r);
     } else {
-        float4* p = reinterpret_cast<float4*>(static_cast<float*>(base) + e);
-        __stcs(p, make_float4(v[0], v[1], v[2], v[3]));
-        __stcs(p + 1, make_float4(v[4], v[5], v[6], v[7]));
+        store32(static_cast<float*>(base) + e,
+                make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3])),
+                make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7])));
     }
+}
+// Streaming store of 16 consecutive bf16 elements (32 bytes) from F32 values.
+__device__ __forceinline__ void store16_bf16(void* base, int64_t e, const float (&v)[16]) {
+    store32(static_cast<uint16_t*>(base) + e,
+            make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])),
+            make_uint4(pack_bf16x2(v[8], v[9]), pack_bf16x2(v[10], v[11]), pack_bf16x2(v[12], v[13]), pack_bf16x2(v[14], v[15])));
 }
 
 __device__ __forceinline__ float load1(const void* base, int dt, int64_t e) {

@@ -507,32 +507,35 @@ __device__ __forceinline__ float fp8_times(uint32_t word, int k, uint32_t scale_
     const uint32_t sign = (k == 3 ? word : word << (24 - 8 * k)) & 0x80000000u;
     return __fmul_rn(__uint_as_float(mag), __uint_as_float(scale_bits ^ sign));
 }
+// Flat persistent form: thread t takes 16-byte code chunks t, t + stride, ... of the whole [rows, inner] matrix
+// (U loads in flight), finds each chunk's row with one 32-bit division, and writes the chunk's 16 results
+// with ONE 32-byte store (bf16).  Every thread has the same amount of work whatever the row length.
 template <int KIND, bool OUT_BF16, bool ROW_SCALE>
 __global__ void __launch_bounds__(kThreads, 4) dequant_tile_kernel(const uint4* __restrict__ packed, const float* __restrict__ scales,
-                                                                  void* __restrict__ out, int64_t rows, int64_t inner_chunks,
-                                                                  int64_t groups, int group_chunks, int64_t tiles_per_row,
-                                                                  int64_t tile_chunks) {
-    constexpr int U = 2;
-    const int64_t tiles = rows * tiles_per_row;
-    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
-        const int64_t row = t / tiles_per_row;
-        const int64_t tile_begin = (t - row * tiles_per_row) * tile_chunks;
-        const int64_t tile_end = tile_begin + tile_chunks < inner_chunks ? tile_begin + tile_chunks : inner_chunks;
-        const int64_t c0 = tile_begin + threadIdx.x;
-        const uint4* src = packed + row * inner_chunks;
+                                                                  void* __restrict__ out, unsigned total_chunks, unsigned inner_chunks,
+                                                                  unsigned groups, unsigned group_chunks) {
+    constexpr int U = 4;
+    const unsigned stride = gridDim.x * kThreads;
+    for (unsigned i0 = blockIdx.x * kThreads + threadIdx.x; i0 < total_chunks; i0 += stride * U) {
         uint4 raw[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-            if (c0 + u * kThreads < tile_end) raw[u] = __ldcs(src + c0 + u * kThreads);
+        float scale[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int64_t c = c0 + u * kThreads;
-            if (c >= tile_end) break;
-            const float scale = __ldg(scales + (ROW_SCALE ? row : row * groups + static_cast<int>(c) / group_chunks));
+            const unsigned i = i0 + u * stride;
+            if (i < total_chunks) {
+                raw[u] = __ldcs(packed + i);
+                const unsigned row = i / inner_chunks;
+                scale[u] = __ldg(scales + (ROW_SCALE ? row : row * groups + (i - row * inner_chunks) / group_chunks));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const unsigned i = i0 + u * stride;
+            if (i >= total_chunks) break;
             const uint32_t words[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
             float v[16];
-            const float lifted = scale * 0x1p120f;
-            if (KIND == VRB_Q_FP8_E4M3FN && fabsf(scale) < 128.0f) {
+            const float lifted = scale[u] * 0x1p120f;
+            if (KIND == VRB_Q_FP8_E4M3FN && fabsf(scale[u]) < 128.0f) {
                 const uint32_t sb = __float_as_uint(lifted);
 #pragma unroll
                 for (int w = 0; w < 4; ++w)
@@ -546,15 +549,19 @@ __global__ void __launch_bounds__(kThreads, 4) dequant_tile_kernel(const uint4* 
                         const uint32_t code = (words[w] >> (8 * k)) & 0xffu;
                         const float q = KIND == VRB_Q_FP8_E4M3FN ? decode_fp8(code)
                                                                  : static_cast<float>(static_cast<int8_t>(code));
-                        v[w * 4 + k] = __fmul_rn(q, scale);
+                        v[w * 4 + k] = __fmul_rn(q, scale[u]);
                     }
             }
-            const int64_t e0 = (row * inner_chunks + c) * 16;
-            float lo[8], hi[8];
+            const int64_t e0 = static_cast<int64_t>(i) * 16;
+            if constexpr (OUT_BF16) {
+                store16_bf16(out, e0, v);
+            } else {
+                float lo[8], hi[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) { lo[e] = v[e]; hi[e] = v[8 + e]; }
-            store8(out, OUT_BF16 ? VRB_BF16 : VRB_F32, e0, lo);
-            store8(out, OUT_BF16 ? VRB_BF16 : VRB_F32, e0 + 8, hi);
+                for (int e = 0; e < 8; ++e) { lo[e] = v[e]; hi[e] = v[8 + e]; }
+                store8(out, VRB_F32, e0, lo);
+                store8(out, VRB_F32, e0 + 8, hi);
+            }
         }
     }
 }
@@ -606,14 +613,12 @@ void launch_dequant_int4_tiles(const uint8_t* packed, const float* scales, void*
 template <int KIND>
 void launch_dequant_tiles(const uint8_t* packed, const float* scales, void* out, int out_dtype, int64_t rows, int64_t inner,
                           int64_t groups, int64_t group_size, cudaStream_t s) {
-    const int64_t inner_chunks = inner / 16;
-    const int64_t tiles_per_row = (inner_chunks + kThreads * 2 - 1) / (kThreads * 2);
-    const int64_t tile_chunks = ((inner_chunks + tiles_per_row - 1) / tiles_per_row + 7) & ~int64_t{7};
-    const int grid = grid_for(rows * tiles_per_row, 8);
+    const int64_t inner_chunks = inner / 16, total = rows * inner_chunks;   // the caller checked total < 2^32
+    const int grid = grid_for((total + kThreads - 1) / kThreads, 8);
     const uint4* p = reinterpret_cast<const uint4*>(packed);
-    const int gc = static_cast<int>(group_size / 16);
+    const unsigned gc = static_cast<unsigned>(group_size / 16);
 #define VRB_DQ(BF, ROW) dequant_tile_kernel<KIND, BF, ROW><<<grid, kThreads, 0, s>>>( \
-        p, scales, out, rows, inner_chunks, groups, gc, tiles_per_row, tile_chunks)
+        p, scales, out, static_cast<unsigned>(total), static_cast<unsigned>(inner_chunks), static_cast<unsigned>(groups), gc)
     if (out_dtype == VRB_BF16) { if (groups == 1) VRB_DQ(true, true); else VRB_DQ(true, false); }
     else { if (groups == 1) VRB_DQ(false, true); else VRB_DQ(false, false); }
 #undef VRB_DQ
@@ -933,8 +938,8 @@ extern "C" int vrb_dequantize(int kind, const void* packed, const float* scales,
     const int64_t count = rows * inner, groups = (inner + group_size - 1) / group_size;
     const uint8_t* p = static_cast<const uint8_t*>(packed);
     cudaStream_t s = as_stream(stream);
-    const bool vec = kind != VRB_Q_INT4 && inner % 16 == 0 && group_size % 16 == 0 && inner / 16 < 0x7fffffff && aligned16(packed) &&
-                     aligned16(out);
+    const bool vec = kind != VRB_Q_INT4 && inner % 16 == 0 && group_size % 16 == 0 && rows * (inner / 16) < 0xffffffffLL &&
+                     groups * rows < 0xffffffffLL && aligned16(packed) && aligned16(out);
     const bool vec4 = kind == VRB_Q_INT4 && inner % 32 == 0 && group_size % 32 == 0 && inner / 32 < 0x7fffffff &&
                       aligned16(packed) && aligned16(out);
     if (vec4) {

@@ -39,7 +39,15 @@ struct PixelNormParams {
     int64_t outer, channels, inner;
     float eps;
     int silu;
+    int l2;              // l2_normalize: denominator = sqrtf(sum) + eps instead of sqrtf(sum / channels + eps)
 };
+
+// The denominator of one position from the sum of its channels' squares: pixel_norm (:2121, :2160) or
+// l2_normalize (l2_normalize_kernel :1170).
+__device__ __forceinline__ float denominator_of(const PixelNormParams& p, float total, float channel_count) {
+    if (p.l2) return __fadd_rn(__fsqrt_rn(total), p.eps);
+    return __fsqrt_rn(__fadd_rn(__fdiv_rn(total, channel_count), p.eps));
+}
 
 // One normalised element to the stored result; `one_plus_scale` / `shift` are ignored without modulation.
 __device__ __forceinline__ float finish(const PixelNormParams& p, float x, float denominator, bool modulated,
@@ -153,7 +161,7 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
             float s[kLanes];
 #pragma unroll
             for (int a = 0; a < kLanes; ++a) s[a] = partial[a * positions + threadIdx.x];
-            denominator[threadIdx.x] = __fsqrt_rn(__fadd_rn(__fdiv_rn(tree8(s), channel_count), p.eps));
+            denominator[threadIdx.x] = denominator_of(p, tree8(s), channel_count);
         }
         __syncthreads();
         const int64_t out_chunk0 = o * p.channels * inner_chunks + chunk0;
@@ -183,9 +191,7 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
                     __stcs(static_cast<uint4*>(p.out) + chunk, make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
                                                                           pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])));
                 } else {
-                    float4* dst = static_cast<float4*>(p.out) + 2 * chunk;
-                    __stcs(dst, make_float4(v[0], v[1], v[2], v[3]));
-                    __stcs(dst + 1, make_float4(v[4], v[5], v[6], v[7]));
+                    store8(p.out, VRB_F32, static_cast<int64_t>(chunk) * 8, v);
                 }
             } else {
                 const float4 da = d4[0];
@@ -227,7 +233,7 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_strided_kernel(const Pixe
                 }
             }
         }
-        const float denominator = __fsqrt_rn(__fadd_rn(__fdiv_rn(tree8(s), static_cast<float>(p.channels)), p.eps));
+        const float denominator = denominator_of(p, tree8(s), static_cast<float>(p.channels));
         for (int64_t c = 0; c < p.channels; ++c) {
             float ops = 1.0f, sh = 0.0f;
             if (modulated) {
@@ -257,7 +263,7 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_rows_kernel(const PixelNo
             if (threadIdx.x < stride) workspace[threadIdx.x] = __fadd_rn(workspace[threadIdx.x], workspace[threadIdx.x + stride]);
             __syncthreads();
         }
-        const float denominator = __fsqrt_rn(__fadd_rn(__fdiv_rn(workspace[0], static_cast<float>(p.channels)), p.eps));
+        const float denominator = denominator_of(p, workspace[0], static_cast<float>(p.channels));
         __syncthreads();   // workspace is rewritten by the next row
         for (int64_t c = threadIdx.x; c < p.channels; c += kThreads) {
             float ops = 1.0f, sh = 0.0f;
@@ -489,9 +495,26 @@ bool launch_rms_axis_tiles(const void* x, int dtype, const void* weight, int wei
 
 using namespace vrb;
 
+namespace {
+int pixel_norm_family(const void* x, int dtype, const void* scale, const void* shift, int mod_dtype, int fuse_silu, void* out,
+                      int out_dtype, int64_t outer, int64_t channels, int64_t inner, float eps, int l2, vrb_stream stream);
+}
+
 extern "C" int vrb_pixel_norm(const void* x, int dtype, const void* scale, const void* shift, int mod_dtype, int fuse_silu,
                               void* out, int out_dtype, int64_t outer, int64_t channels, int64_t inner, float eps,
                               vrb_stream stream) {
+    return pixel_norm_family(x, dtype, scale, shift, mod_dtype, fuse_silu, out, out_dtype, outer, channels, inner, eps, 0, stream);
+}
+
+extern "C" int vrb_l2_normalize(const void* x, void* out, int dtype, int64_t outer, int64_t channels, int64_t inner, float eps,
+                                vrb_stream stream) {
+    VRB_REQUIRE(eps >= 0.0f, VRB_ERR_INVALID, "l2 normalize contract violation");
+    return pixel_norm_family(x, dtype, nullptr, nullptr, 0, 0, out, dtype, outer, channels, inner, eps, 1, stream);
+}
+
+namespace {
+int pixel_norm_family(const void* x, int dtype, const void* scale, const void* shift, int mod_dtype, int fuse_silu, void* out,
+                      int out_dtype, int64_t outer, int64_t channels, int64_t inner, float eps, int l2, vrb_stream stream) {
     VRB_REQUIRE(x && out, VRB_ERR_INVALID, "pixel_norm: null tensor");
     VRB_REQUIRE(outer > 0 && channels > 0 && inner > 0, VRB_ERR_INVALID, "pixel_norm: extents must be positive");
     VRB_REQUIRE(is_float_dtype(dtype) && is_float_dtype(out_dtype), VRB_ERR_UNSUPPORTED, "pixel_norm: tensors must be F32 or BF16");
@@ -500,7 +523,7 @@ extern "C" int vrb_pixel_norm(const void* x, int dtype, const void* scale, const
     VRB_REQUIRE(scale || out_dtype == dtype, VRB_ERR_UNSUPPORTED, "pixel_norm: without modulation the result has x's dtype");
     PixelNormParams p{};
     p.x = x; p.out = out; p.scale = scale; p.shift = shift; p.x_dt = dtype; p.out_dt = out_dtype; p.mod_dt = mod_dtype;
-    p.outer = outer; p.channels = channels; p.inner = inner; p.eps = eps; p.silu = fuse_silu ? 1 : 0;
+    p.outer = outer; p.channels = channels; p.inner = inner; p.eps = eps; p.silu = fuse_silu ? 1 : 0; p.l2 = l2;
     cudaStream_t s = as_stream(stream);
     if (inner == 1) {
         pixel_norm_rows_kernel<<<grid_for(outer, 8), kThreads, 0, s>>>(p);
@@ -549,3 +572,4 @@ extern "C" int vrb_pixel_norm(const void* x, int dtype, const void* scale, const
     pixel_norm_strided_kernel<<<grid_for((units + kThreads - 1) / kThreads, 8), kThreads, 0, s>>>(p);
     return after_launch("pixel_norm");
 }
+}  // namespace

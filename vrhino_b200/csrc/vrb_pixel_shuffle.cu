@@ -154,8 +154,7 @@ __global__ void __launch_bounds__(kThreads) shuffle_rows_kernel(const uint4* __r
             } else {
                 uint4 lo, hi;
                 interleave<ELEM>(v[u][0], v[u][1], lo, hi);
-                __stcs(dst, lo);
-                __stcs(dst + 1, hi);
+                store32(dst, lo, hi);
             }
         }
     }
@@ -201,8 +200,7 @@ __global__ void __launch_bounds__(kThreads) depth_to_space_rows_kernel(const uin
             interleave<ELEM>(add_chunks(v[rep][0], w0, ELEM == 2), add_chunks(v[rep][1], w1, ELEM == 2), lo, hi);
             uint4* dst = out + (static_cast<int64_t>(b) * g.channels + c) * out_channel_chunks +
                          ((static_cast<int64_t>(frame) * out_h + oh) * row_chunks + k) * 2;
-            __stcs(dst, lo);
-            __stcs(dst + 1, hi);
+            store32(dst, lo, hi);
         }
     }
 }

@@ -129,6 +129,9 @@ bool launch_by_dtype(const RowParams& p, int geometry, int64_t ctas, size_t smem
             if (x_bf16 && n_bf16) { launch_row_variant<NORM, POST, kBf16Bf16Pre>(p, geometry, ctas, smem, s); return true; }
             if (!x_bf16 && !n_bf16) { launch_row_variant<NORM, POST, kF32Pre>(p, geometry, ctas, smem, s); return true; }
         }
+        if constexpr (NORM == kNormRms && POST == kPostScaleX) {   // the Mochi block's form
+            if (x_bf16 && n_bf16) { launch_row_variant<NORM, POST, kBf16Bf16Pre>(p, geometry, ctas, smem, s); return true; }
+        }
         return false;
     }
     if (!x_bf16 && !n_bf16) { launch_row_variant<NORM, POST, kF32F32>(p, geometry, ctas, smem, s); return true; }
@@ -470,6 +473,41 @@ extern "C" int vrb_rms_norm_rope_tables(const void* x, int x_dtype, const void* 
         p.post = kPostRope;
     }
     return launch_rows(p, as_stream(stream), "rms_norm_rope");
+}
+
+extern "C" int vrb_rms_norm_gated_residual_rms_norm_scale(
+        const void* residual, int residual_dtype, const void* branch, int branch_dtype, float branch_eps,
+        const void* gate, int gate_dtype, int gate_tanh, int64_t gate_rows_per_vector, int64_t gate_vectors,
+        void* state_out, int state_dtype, const void* scale, int scale_dtype, int64_t rows_per_vector, int64_t scale_vectors,
+        void* out, int64_t rows, int64_t width, float eps, vrb_stream stream) {
+    VRB_REQUIRE(residual && branch && state_out && out && scale, VRB_ERR_INVALID, "rms_norm_gated_residual_rms_norm_scale: null tensor");
+    if (gate) { if (int rc = check_vectors("rms_norm_gated_residual_rms_norm_scale", gate_rows_per_vector, gate_vectors)) return rc; }
+    if (int rc = check_vectors("rms_norm_gated_residual_rms_norm_scale", rows_per_vector, scale_vectors)) return rc;
+    VRB_REQUIRE(is_float_dtype(residual_dtype) && is_float_dtype(branch_dtype) && is_float_dtype(state_dtype) &&
+                    is_float_dtype(scale_dtype) && (!gate || is_float_dtype(gate_dtype)),
+                VRB_ERR_UNSUPPORTED, "rms_norm_gated_residual_rms_norm_scale: dtypes must be F32 or BF16");
+    // one pass for a bf16 stream (residual, branch, updated stream and normalised output all bf16)
+    if (residual_dtype == VRB_BF16 && branch_dtype == VRB_BF16 && state_dtype == VRB_BF16) {
+        RowParams p = blank();
+        p.x = residual; p.x_dt = p.norm_out_dt = p.out_dt = VRB_BF16; p.out = out;
+        p.pre_branch = branch; p.pre_gate = gate; p.pre_gate_dt = gate_dtype; p.state_out = state_out;
+        p.pre_rows_per_vector = gate ? gate_rows_per_vector : 1; p.pre_vectors = gate ? gate_vectors : 0;
+        p.pre_norm = 1; p.pre_eps = branch_eps; p.pre_gate_tanh = gate && gate_tanh ? 1 : 0;
+        p.scale = scale; p.mod_dt = scale_dtype; p.rows_per_vector = rows_per_vector; p.vectors = scale_vectors;
+        p.post = kPostScaleX;
+        p.rows = rows; p.width = p.norm_width = width; p.eps = eps;
+        set_rms(p, rows);
+        const int rc = launch_rows(p, as_stream(stream), "rms_norm_gated_residual_rms_norm_scale");
+        if (rc != kPreNotFused) return rc;
+    }
+    // otherwise the two operators; tanh(gate) would need a temporary, which an entry point does not allocate
+    VRB_REQUIRE(!(gate && gate_tanh), VRB_ERR_UNSUPPORTED,
+                "rms_norm_gated_residual_rms_norm_scale: for this dtype contract or geometry apply tanh to the gate first "
+                "(vrb_activation) and pass gate_tanh = 0");
+    if (int rc = vrb_rms_norm_gated_residual(residual, residual_dtype, branch, branch_dtype, gate, gate_dtype, gate_rows_per_vector,
+                                             gate_vectors, state_out, state_dtype, rows, width, branch_eps, stream))
+        return rc;
+    return vrb_rms_norm_scale(state_out, state_dtype, scale, scale_dtype, rows_per_vector, scale_vectors, out, rows, width, eps, stream);
 }
 
 extern "C" int vrb_rms_norm_rope_pair(const void* x_a, const void* weight_a, void* out_a, int64_t rows_a,

@@ -77,6 +77,10 @@ struct RowParams {
     const void* pre_branch; const void* pre_gate; void* state_out;
     int pre_gate_dt;
     int64_t pre_rows_per_vector, pre_vectors;
+    // kBf16Bf16Pre, Mochi's form (mochi.cpp:204-211): the branch is RMS-normalised (no weight, pre_eps) before
+    // it is gated and added, and the gate is tanh(pre_gate)
+    int pre_norm, pre_gate_tanh;
+    float pre_eps;
     // Two problems in one launch (q and k of an attention block: same geometry, dtypes, tables and
     // epilogue, their own tensors, weights and row counts): CTAs [0, blocks_a) work on (x, out, weight,
     // nrows32), the others on (x_b, out_b, weight_b, nrows_b).  blocks_a == 0: a single problem.
@@ -359,8 +363,12 @@ row_kernel(const RowParams p) {
                 const int v = cv / (width / 2), pair = cv - v * (width / 2);
                 const int c = pair * 2, chunk = c >> 3, i = chunk / tpr, l = chunk - i * tpr;
                 const int64_t at = static_cast<int64_t>(v) * p.width + c;
-                s_gate[v * (pad / 2) + ((i * tpr + l) << 2) + ((c & 7) >> 1)] =
-                    pack_bf16x2(load1(p.pre_gate, p.pre_gate_dt, at), load1(p.pre_gate, p.pre_gate_dt, at + 1));
+                float g0 = load1(p.pre_gate, p.pre_gate_dt, at), g1 = load1(p.pre_gate, p.pre_gate_dt, at + 1);
+                if (p.pre_gate_tanh) {   // activation(gate, Tanh) in the gate's dtype, then the cast to the stream's
+                    g0 = round_to(p.pre_gate_dt, tanhf(g0));
+                    g1 = round_to(p.pre_gate_dt, tanhf(g1));
+                }
+                s_gate[v * (pad / 2) + ((i * tpr + l) << 2) + ((c & 7) >> 1)] = pack_bf16x2(g0, g1);
             }
             __syncthreads();
         }
@@ -393,6 +401,29 @@ row_kernel(const RowParams p) {
             if constexpr (!PRE_F32) res[i] = here ? load_packed<true>(x_base, off + chunk * 8) : zero_packed<true>();
             br[i] = here ? load_packed<true>(p.pre_branch, off + chunk * 8) : zero_packed<true>();
         }
+    };
+    // RMS statistics of one row from this thread's sum of squares: warp shuffles, one partial per warp
+    // through shared memory for rows wider than a warp, then the reference's formula (:853-907 / :963-991).
+    auto rms_inverse = [&](float squares, float eps) -> float {
+        const int span = tpr < 32 ? tpr : 32;
+        double wide = static_cast<double>(squares);
+        for (int offset = span >> 1; offset > 0; offset >>= 1) {
+            if (f32_formula) squares = __fadd_rn(squares, __shfl_xor_sync(0xffffffffu, squares, offset));
+            else wide += __shfl_xor_sync(0xffffffffu, wide, offset);
+        }
+        if (warps_per_row > 1) {
+            if ((threadIdx.x & 31) == 0) s_red[parity][threadIdx.x >> 5][1] = f32_formula ? static_cast<double>(squares) : wide;
+            named_barrier(1 + row_in_cta, tpr);
+            const int first = row_in_cta * warps_per_row;
+            squares = 0.0f; wide = 0.0;
+            for (int w = 0; w < warps_per_row; ++w) {
+                if (f32_formula) squares = __fadd_rn(squares, static_cast<float>(s_red[parity][first + w][1]));
+                else wide += s_red[parity][first + w][1];
+            }
+            parity ^= 1;
+        }
+        if (f32_formula) return rsqrtf(__fadd_rn(__fmul_rn(squares, __fdiv_rn(1.0f, static_cast<float>(width))), eps));
+        return rsqrtf(static_cast<float>(wide * p.inv_width) + eps);
     };
     Packed<X_BF16> xr[NCH];
     Packed<true> raw_res[(PRE && !PRE_F32) ? NCH : 1], raw_br[PRE ? NCH : 1];   // PRE: the row being combined next
@@ -441,9 +472,9 @@ row_kernel(const RowParams p) {
                 xr[i].a = make_float4(__fadd_rn(xr[i].a.x, b[0]), __fadd_rn(xr[i].a.y, b[1]), __fadd_rn(xr[i].a.z, b[2]), __fadd_rn(xr[i].a.w, b[3]));
                 xr[i].b = make_float4(__fadd_rn(xr[i].b.x, b[4]), __fadd_rn(xr[i].b.y, b[5]), __fadd_rn(xr[i].b.z, b[6]), __fadd_rn(xr[i].b.w, b[7]));
                 if (valid) {
-                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.state_out) + row_offset + chunk * 8);
-                    __stcs(dst, xr[i].a);
-                    __stcs(dst + 1, xr[i].b);
+                    store32(static_cast<float*>(p.state_out) + row_offset + chunk * 8,
+                            make_uint4(__float_as_uint(xr[i].a.x), __float_as_uint(xr[i].a.y), __float_as_uint(xr[i].a.z), __float_as_uint(xr[i].a.w)),
+                            make_uint4(__float_as_uint(xr[i].b.x), __float_as_uint(xr[i].b.y), __float_as_uint(xr[i].b.z), __float_as_uint(xr[i].b.w)));
                 }
             }
         } else if constexpr (PRE) {
@@ -454,12 +485,35 @@ row_kernel(const RowParams p) {
             if (has_pre_gate && p.pre_vectors > 1)
                 gate_base = ((nrow / static_cast<unsigned>(p.pre_rows_per_vector)) % static_cast<unsigned>(p.pre_vectors)) *
                             static_cast<unsigned>(pad / 2);
+            // Mochi: the branch enters as rms_norm(branch, no weight, pre_eps), rounded to bf16 like the
+            // operator's own store (absent chunks were loaded as zeros)
+            float branch_inverse = 1.0f;
+            if (p.pre_norm) {
+                unsigned long long squares = 0ull;
+#pragma unroll
+                for (int i = 0; i < NCH; ++i) {
+                    float v[8];
+                    unpack<true>(raw_br[i], v);
+                    const unsigned long long p0 = pack_f32x2(v[0], v[1]), p1 = pack_f32x2(v[2], v[3]);
+                    const unsigned long long p2 = pack_f32x2(v[4], v[5]), p3 = pack_f32x2(v[6], v[7]);
+                    squares = add_f32x2(squares, add_f32x2(fma_f32x2(p1, p1, mul_f32x2(p0, p0)), fma_f32x2(p3, p3, mul_f32x2(p2, p2))));
+                }
+                float lo, hi;
+                unpack_f32x2(squares, lo, hi);
+                branch_inverse = rms_inverse(lo + hi, p.pre_eps);
+            }
 #pragma unroll
             for (int i = 0; i < NCH; ++i) {
                 const int chunk = lane_in_row + i * tpr;
                 if (!FULL && chunk >= nchunks) { xr[i] = zero_packed<X_BF16>(); continue; }   // statistics see zeros there
                 const uint32_t rw[4] = {raw_res[i].r.x, raw_res[i].r.y, raw_res[i].r.z, raw_res[i].r.w};
-                const uint32_t bw[4] = {raw_br[i].r.x, raw_br[i].r.y, raw_br[i].r.z, raw_br[i].r.w};
+                uint32_t bw[4] = {raw_br[i].r.x, raw_br[i].r.y, raw_br[i].r.z, raw_br[i].r.w};
+                if (p.pre_norm) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        bw[k] = pack_bf16x2(__fmul_rn(__uint_as_float(bw[k] << 16), branch_inverse),
+                                            __fmul_rn(__uint_as_float(bw[k] & 0xffff0000u), branch_inverse));
+                }
                 uint4 gw = make_uint4(0, 0, 0, 0);
                 if (has_pre_gate) gw = *reinterpret_cast<const uint4*>(s_gate + gate_base + ((i * tpr + lane_in_row) << 2));
                 const uint32_t gws[4] = {gw.x, gw.y, gw.z, gw.w};

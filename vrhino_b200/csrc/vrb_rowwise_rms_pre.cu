@@ -9,5 +9,7 @@ VRB_DEFINE_ROW_VARIANT(kNormRms, kPostModulate, kBf16Bf16Pre)
 VRB_DEFINE_ROW_VARIANT(kNormRms, kPostModulateStaged, kBf16Bf16Pre)
 VRB_DEFINE_ROW_VARIANT(kNormRms, kPostModulate, kF32Pre)
 VRB_DEFINE_ROW_VARIANT(kNormRms, kPostModulateStaged, kF32Pre)
+// Mochi: residual + rms_norm(branch) * tanh(gate), then rms_norm(.) * (1 + scale) of the updated stream
+VRB_DEFINE_ROW_VARIANT(kNormRms, kPostScaleX, kBf16Bf16Pre)
 }  // namespace rowwise
 }  // namespace vrb

@@ -418,6 +418,23 @@ Tensor B200Backend::pixel_norm(const Tensor& raw, int64_t dim, float eps) {
     });
 }
 
+Tensor B200Backend::l2_normalize(const Tensor& raw, int64_t dim, float eps) {
+    return guarded([&] {   // VRHINO_PROFILE("norm.l2") carries the failure guard (cuda_backend.cu:3064, :5090)
+        if (dim < 0) dim += static_cast<int64_t>(raw.ndim());
+        require(dim >= 0 && dim < static_cast<int64_t>(raw.ndim()) && eps >= 0.0f, "l2 normalize contract violation");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype);
+        const int64_t channels = x.dim(dim);
+        int64_t inner = 1;
+        for (int64_t d = dim + 1; d < static_cast<int64_t>(x.ndim()); ++d) inner *= x.dim(d);
+        require(x.numel() / channels <= std::numeric_limits<int>::max(), "l2 normalize launch extent exceeds CUDA grid capacity");
+        Tensor out = rt_->allocate_device(x.shape(), dtype);
+        ProfileRegion region(*this, [] { return std::string("norm.l2"); }, bytes_of(x) + bytes_of(out));
+        check(vrb_l2_normalize(x.data(), out.data(), code(dtype), x.numel() / (channels * inner), channels, inner, eps, kLegacyStream));
+        return out;
+    });
+}
+
 Tensor B200Backend::pixel_shuffle_nd(const Tensor& raw, const std::vector<int64_t>& factors) {
     return guarded([&] {   // VRHINO_PROFILE("pixel_shuffle") carries the failure guard (cuda_backend.cu:5114)
         require(raw.ndim() == 5 && factors.size() == 3, "pixel_shuffle_nd requires 5D and 3 factors");

@@ -14,7 +14,8 @@
 // Replaced virtuals (same signatures, defaults, dtype rules and error texts as
 // native/src/backend/cuda/cuda_backend.cu): add, mul, div, maximum (:3871-3902), cast (:3978),
 // layer_norm (:4057), rms_norm (:4091), activation (:4179), rope_nd (:4198), group_norm (:4919),
-// clamp (:5128), exp, sqrt (:5134-5173) and the quantised branch of copy_to_device (:3214-3296).
+// clamp (:5128), exp, sqrt (:5134-5173), pixel_norm (:5048), l2_normalize (:5088), pixel_shuffle_nd (:5112)
+// and the quantised branch of copy_to_device (:3214-3296).
 // Kernels run on the legacy default stream, which the runtime's pool reuse relies on
 // (cuda_backend.cu:55-59).
 #pragma once
@@ -57,6 +58,7 @@ public:
     Tensor copy_to_device(const Tensor& input, DType dtype) override;
     Tensor pixel_norm(const Tensor& x, int64_t dim, float eps) override;
     Tensor pixel_shuffle_nd(const Tensor& x, const std::vector<int64_t>& factors) override;
+    Tensor l2_normalize(const Tensor& x, int64_t dim, float eps) override;
 
     // ---- fused forms (one kernel each); see the free functions below for the call-site view --
     Tensor layer_norm_modulate(const Tensor& x, const Tensor* weight, const Tensor* bias, float eps,
@@ -181,7 +183,6 @@ public:
     Tensor max_pool2d(const Tensor& x, const std::vector<int>& k, const std::vector<int>& s, const std::vector<int>& p = {0, 0}) override { return rt_->max_pool2d(x, k, s, p); }
     Tensor interpolate_nearest(const Tensor& x, const std::vector<double>& f) override { return rt_->interpolate_nearest(x, f); }
     Tensor interpolate_bilinear_2d(const Tensor& x, int64_t h, int64_t w, bool a) override { return rt_->interpolate_bilinear_2d(x, h, w, a); }
-    Tensor l2_normalize(const Tensor& x, int64_t d, float e) override { return rt_->l2_normalize(x, d, e); }
     Tensor rng_normal(vrhino::RngState& s, const std::vector<int64_t>& shape, DType d) override { return rt_->rng_normal(s, shape, d); }
 
 private:

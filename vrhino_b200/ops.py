@@ -211,6 +211,23 @@ class B200Backend:
              x.numel() // (channels * inner), channels, inner, ctypes.c_float(eps), _stream())
         return out
 
+    def l2_normalize(self, x, dim, eps, out=None):
+        """CudaBackend::l2_normalize (cuda_backend.cu:5088-5110): x / (sqrt(sum(x^2) over `dim`) + eps)."""
+        if dim < 0:
+            dim += x.dim()
+        if not (0 <= dim < x.dim()) or eps < 0:
+            raise VrbError("l2 normalize contract violation")
+        dtype = self._dtype_of(x)
+        x = _dense(self.copy_to_device(x, dtype))
+        channels = x.shape[dim]
+        inner = 1
+        for d in x.shape[dim + 1:]:
+            inner *= d
+        out = _result(out, x.shape, dtype, x.device)
+        call("vrb_l2_normalize", _ptr(x), _ptr(out), _code(dtype), x.numel() // (channels * inner), channels, inner,
+             ctypes.c_float(eps), _stream())
+        return out
+
     def pixel_shuffle_nd(self, raw, factors, out=None):
         """CudaBackend::pixel_shuffle_nd (native/src/backend/cuda/cuda_backend.cu:5112-5118)."""
         if raw.dim() != 5 or len(factors) != 3:
@@ -616,6 +633,29 @@ def fused_rms_norm_gated_residual(be, policy, residual, branch, bounded_gate, ep
          _ptr(_dense(bounded_gate)), _code(bounded_gate), rpv, nvec, _ptr(out), _code(policy.residual),
          rows, width, ctypes.c_float(eps), _stream())
     return out
+
+
+def fused_rms_norm_gated_residual_norm_scale(be, policy, residual, branch, gate, scale, branch_eps=1e-6, eps=1e-6, gate_tanh=True,
+                                             state_out=None, out=None):
+    """The Mochi block's residual update and the next layer's pre-norm in one pass (mochi.cpp:204-211, :228-231):
+        state = gated_residual(residual, rms_norm(branch, None, branch_eps), tanh(gate) if gate_tanh else gate)
+        out   = mul(rms_norm(state, None, eps), add(1, scale))
+    Returns (state, out).  Other contracts than an all-bf16 stream run tanh, the residual update and the
+    norm as separate launches."""
+    residual, branch = _dense(residual), _dense(branch)
+    width = residual.shape[-1]
+    rows = residual.numel() // width
+    grpv, gvec = _vec_layout(rows, residual.shape, gate)
+    rpv, nvec = _vec_layout(rows, residual.shape, scale)
+    state = _result(state_out, residual.shape, policy.residual, residual.device)
+    one_pass = residual.dtype == BF16 and branch.dtype == BF16 and policy.residual == BF16
+    if gate_tanh and not one_pass:
+        gate, gate_tanh = be.activation(gate, TANH), False
+    out = _result(out, residual.shape, policy.residual, residual.device)
+    call("vrb_rms_norm_gated_residual_rms_norm_scale", _ptr(residual), _code(residual), _ptr(branch), _code(branch),
+         ctypes.c_float(branch_eps), _ptr(_dense(gate)), _code(gate), int(bool(gate_tanh)), grpv, gvec, _ptr(state),
+         _code(policy.residual), _ptr(_dense(scale)), _code(scale), rpv, nvec, _ptr(out), rows, width, ctypes.c_float(eps), _stream())
+    return state, out
 
 
 def fused_swiglu(be, projected, out=None):

@@ -191,25 +191,37 @@ def compile_launches(launches: List[Launch]) -> List[Launch]:
 
 
 def time_launches(launches: List[Launch], steps: int, warmup: int):
-    """Per-launch device time with CUDA events on the current stream; returns
-    (total_ms_per_step, {name: mean_ms})."""
-    for _ in range(warmup):
-        for l in launches:
-            l.fn()
+    """Device times with CUDA events on the current stream, the C-ABI calls recorded once and replayed
+    so that no Python sits between two launches: the whole list back to back (`steps` repetitions,
+    one event pair), and every launch on its own, `steps` repetitions back to back -- a launch of a few
+    microseconds bracketed by its own event pair through the Python layer would mostly measure the
+    host.  Returns (list_ms_per_step, {name: ms_per_launch})."""
+    for l in launches:
+        l.fn()
     torch.cuda.synchronize()
-    per = {l.name: 0.0 for l in launches}
-    events = []
-    for _ in range(steps):
-        for l in launches:
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            l.fn()
-            b.record()
-            events.append((l.name, a, b))
+    compiled = compile_launches(launches)
+
+    def timed(fns, reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            for fn in fns:
+                fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    every = [l.fn for l in compiled]
+    for _ in range(max(warmup, 1)):
+        for fn in every:
+            fn()
     torch.cuda.synchronize()
-    for name, a, b in events:
-        per[name] += a.elapsed_time(b) / steps
-    return sum(per.values()), per
+    total = timed(every, steps)
+    per = {}
+    for l in compiled:
+        l.fn()
+        per[l.name] = timed([l.fn], steps)
+    return total, per
 
 
 class Wan22Step:
@@ -262,7 +274,8 @@ class MochiBlock:
         self.x = _randn((1, S, D), hidden_dtype, g)
         self.h, self.q, self.k, self.branch = (_randn((1, S, D), BF16, g) for _ in range(4))
         self.scale = _randn((1, 1, D), F32, g, std=0.1)
-        self.gate = torch.tanh(_randn((1, 1, D), F32, g, std=0.1))
+        self.raw_gate = _randn((1, 1, D), F32, g, std=0.1)
+        self.gate = torch.tanh(self.raw_gate)
         self.wq, self.wk = (_randn((D // heads,), F32, g, 1.0, 0.1) for _ in range(2))
         phase = torch.rand((1, S, heads, D // heads), device="cuda", generator=g) * 6.2831853
         self.cos, self.sin = torch.cos(phase), torch.sin(phase)
@@ -270,12 +283,25 @@ class MochiBlock:
         self.proj = _randn((1, S, 2 * hidden), BF16, g)
         self.out = {}
 
-    def launches(self) -> List[Launch]:
+    def launches(self, merge_tail: bool = False) -> List[Launch]:
+        """merge_tail: the residual update and the pre-norm of the layer that follows it (mochi.cpp:204-211,
+        :228-231) as ONE launch with the tanh of the gate folded in, q and k as one pair launch."""
         be, p, o = self.be, self.policy, self.out
         act = self.h.numel()
         hb = self.x.element_size()
         vec = self.scale.numel() * 4
         table = self.cos.numel() * 4 * 2
+        if merge_tail:
+            def qk(): o["q"], o["k"] = ops.fused_rms_norm_rope_pair(be, self.q, self.wq, self.k, self.wk, 1e-5, self.cos, self.sin,
+                                                                    heads=self.heads, per_head_norm=True, out=(o.get("q"), o.get("k")))
+            def sw2(): o["swiglu"] = ops.fused_swiglu(be, self.proj, out=o.get("swiglu"))
+            def tail(): o["res"], o["pre_next"] = ops.fused_rms_norm_gated_residual_norm_scale(
+                be, p, self.x, self.branch, self.raw_gate, self.scale, state_out=o.get("res"), out=o.get("pre_next"))
+            return [
+                Launch("head rms_rope q+k", qk, 2 * (act * 4 + 512) + table),
+                Launch("swiglu", sw2, self.proj.numel() * 2 + self.proj.numel()),
+                Launch("rms_gated_residual + next rms_scale", tail, act * (2 + 3 * hb) + 2 * vec),
+            ]
 
         def pre(): o["pre"] = ops.fused_rms_norm_scale(be, self.h, self.scale, 1e-6, out=o.get("pre"))
         def q(): o["q"] = ops.fused_rms_norm_rope(be, self.q, self.wq, 1e-5, self.cos, self.sin, heads=self.heads, per_head_norm=True, out=o.get("q"))
