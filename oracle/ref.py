@@ -24,6 +24,12 @@ F32, BF16, U8 = 0, 2, 5
 POLICY_BF16, POLICY_FP32, POLICY_BF16_ROLES, POLICY_BF16_GUIDANCE = 0, 1, 2, 3
 
 
+def reference_tree() -> str:
+    """The reference checkout's native/ directory: $VRHINO_REF, else a `reference` checkout beside this
+    repository.  Only the build recipes read it (oracle/Makefile); nothing does at run time."""
+    return os.environ.get("VRHINO_REF") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference", "native")
+
+
 def available_host() -> bool:
     return os.path.exists(HOST_LIB)
 

@@ -19,7 +19,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 @pytest.fixture(scope="module")
 def host(orc):
     from oracle import ref
-    if not ref.available_host() and os.path.isdir("/root/reference/native"):
+    if not ref.available_host() and os.path.isdir(ref.reference_tree()):
         subprocess.run(["make", "-C", os.path.join(ROOT, "oracle"), "-j4", "ref_host"], check=True, capture_output=True)
     if not ref.available_host():
         pytest.skip("oracle/_ref/libvrhino_ref_host.so is not built and the reference tree is not mounted")

@@ -125,6 +125,9 @@ def load_sharded() -> ctypes.CDLL:
     """Load libvrb_sharded.so (C++ over NCCL and libvrb.so).  Raises if it was not built."""
     global _sharded
     if _sharded is None:
+        # A process has ONE libnccl.so.2.  torch brings its own (newer than the system's this library is
+        # linked against) and fails to import if another one was loaded first, so torch goes first here.
+        import torch  # noqa: F401
         load()
         if not os.path.exists(SHARDED_LIB_PATH):
             raise VrbError(f"{SHARDED_LIB_PATH} is missing: build it with `python -m vrhino_b200.build`")
