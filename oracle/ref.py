@@ -303,7 +303,7 @@ class RefDropin(RefCuda):
                      "refd_group_norm_silu", "refd_cfg_euler", "refd_gated_residual_layer_norm",
                      "refd_linear_activation", "refd_linear_gated_residual", "refd_linear_swiglu",
                      "refd_pixel_norm_modulate_silu", "refd_depth_to_space_residual", "refd_profile_report",
-                     "refd_dequantize_repeated", "refd_release_cached"):
+                     "refd_dequantize_repeated", "refd_release_cached", "refd_rms_norm_rope_pair", "refd_mochi_residual_norm"):
             getattr(self.lib, name).restype = _c.c_int64
 
     def profile(self, enabled): self.lib.refc_profile(int(enabled))
@@ -334,6 +334,18 @@ class RefDropin(RefCuda):
     def fused_rms_norm_rope(self, policy, x, w, eps, c, s, heads, per_head=False, out_dtype=BF16):
         return self._h(self.lib.refd_rms_norm_rope(int(policy), self._i(x), self._i(w), _c.c_float(eps), self._i(c), self._i(s),
                                                    int(heads), int(per_head), int(out_dtype)))
+    def fused_rms_norm_rope_pair(self, policy, q, wq, k, wk, eps, c, s, heads, per_head=False, out_dtype=BF16):
+        second = _c.c_int64(0)
+        first = self._h(self.lib.refd_rms_norm_rope_pair(int(policy), self._i(q), self._i(wq), self._i(k), self._i(wk), _c.c_float(eps),
+                                                         self._i(c), self._i(s), int(heads), int(per_head), int(out_dtype),
+                                                         _c.byref(second)))
+        return first, second.value
+    def fused_mochi_residual_norm(self, policy, r, b, g, scale, eps=1e-6):
+        """(updated stream handle, next pre-norm handle)"""
+        normed = _c.c_int64(0)
+        state = self._h(self.lib.refd_mochi_residual_norm(int(policy), self._i(r), self._i(b), self._i(g), self._i(scale),
+                                                          _c.c_float(eps), _c.byref(normed)))
+        return state, normed.value
     def fused_gated_residual(self, policy, r, b, g): return self._h(self.lib.refd_gated_residual(int(policy), self._i(r), self._i(b), self._i(g)))
     def fused_gated_residual_layer_norm(self, policy, r, b, g, w, bias, eps, shift, scale, out_dtype=BF16):
         """(state handle, normalised handle)"""

@@ -246,6 +246,24 @@ int64_t refd_rms_norm_rope(int policy, int64_t x, int64_t w, float eps, int64_t 
                                                static_cast<DType>(out_dtype)));
     });
 }
+// {q operand, k operand} of one pair launch; returns the first handle, *second receives the other
+int64_t refd_rms_norm_rope_pair(int policy, int64_t q, int64_t wq, int64_t k, int64_t wk, float eps, int64_t c, int64_t s, int heads,
+                                int per_head, int out_dtype, int64_t* second) {
+    return guarded([&] {
+        auto both = vrhino_b200::rms_norm_rope_pair(*g_backend, policy_of(policy), at(q), at(wq), at(k), at(wk), eps, opt(c), opt(s),
+                                                    heads, per_head != 0, static_cast<DType>(out_dtype));
+        *second = keep(both.second);
+        return keep(both.first);
+    });
+}
+// Mochi's layer boundary: returns the updated stream's handle, *normed receives the next layer's pre-norm
+int64_t refd_mochi_residual_norm(int policy, int64_t r, int64_t b, int64_t g, int64_t scale, float eps, int64_t* normed) {
+    return guarded([&] {
+        auto both = vrhino_b200::normalized_gated_residual_norm_scale(*g_backend, policy_of(policy), at(r), at(b), at(g), at(scale), eps);
+        *normed = keep(both.second);
+        return keep(both.first);
+    });
+}
 int64_t refd_gated_residual(int policy, int64_t r, int64_t b, int64_t g) {
     return guarded([&] { return keep(vrhino_b200::fused_gated_residual(*g_backend, policy_of(policy), at(r), at(b), opt(g))); });
 }

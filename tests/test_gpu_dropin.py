@@ -81,6 +81,15 @@ def test_fused_call_site_forms(orc, golden, dropin, case):
             got = rd.fused_rms_norm_rope(pol, h["x"], h["w"], 1e-5 if case["per_head"] else cases.EPS, 0, 0, H,
                                          per_head=case["per_head"])
             compare(orc, case, "norm_cast", _grab(rd, case, got, (1, S, H, d)), want["norm_cast"])
+            # q and k of one attention in one launch: each half is what the single launch gives
+            eps = 1e-5 if case["per_head"] else cases.EPS
+            other = rd.upload(cases.to_bits(np.random.default_rng(5).normal(1.0, 0.1, cases._inputs(case)["w"][0].shape)
+                                            .astype(np.float32), "f32"), ref.F32)
+            first, second = rd.fused_rms_norm_rope_pair(pol, h["x"], h["w"], h["x"], other, eps, h["cos"], h["sin"], H,
+                                                        per_head=case["per_head"])
+            compare(orc, case, "cast", _grab(rd, case, first, (1, S, H, d)), want["cast"])
+            alone = rd.fused_rms_norm_rope(pol, h["x"], other, eps, h["cos"], h["sin"], H, per_head=case["per_head"])
+            assert np.array_equal(rd.download(second, (1, S, H, d))[0], rd.download(alone, (1, S, H, d))[0])
         elif k == "gated_residual":
             p = ref.POLICY_BF16 if case["state"] == "bf16" else ref.POLICY_FP32
             compare(orc, case, "gated", _grab(rd, case, rd.fused_gated_residual(p, h["res"], h["branch"], h["gate"]), case["shape"]),
@@ -137,6 +146,18 @@ def test_fused_call_site_forms(orc, golden, dropin, case):
         elif k == "mochi":
             B, S, D = case["shape"]
             compare(orc, case, "swiglu", _grab(rd, case, rd.fused_swiglu(h["proj"]), (B, S, case["hidden"])), want["swiglu"])
+            # the layer boundary in one kernel: the updated stream against the golden vector, the next
+            # layer's pre-norm against the replaced backend's own rms_norm -> (1 + scale) chain on that stream
+            p = ref.POLICY_BF16 if case["state"] == "bf16" else ref.POLICY_FP32
+            state, normed = rd.fused_mochi_residual_norm(p, h["x"], h["branch"], h["gate"], h["scale"], cases.EPS)
+            compare(orc, case, "norm_gated", _grab(rd, case, state, (B, S, D)), want["norm_gated"])
+            one = rd.host_f32(np.array(1.0, dtype=np.float32))
+            chain = rd.binary(1, rd.rms_norm(state, 0, cases.EPS), rd.binary(0, one, rd.reshape(h["scale"], (B, 1, D))))
+            got_bits, got_dt = rd.download(normed, (B, S, D))
+            want_bits, want_dt = rd.download(chain, (B, S, D))
+            assert got_dt == want_dt
+            compare(orc, case, "norm_scale", (cases._sub(case, got_bits), "bf16" if got_dt == ref.BF16 else "f32"),
+                    (cases._sub(case, want_bits), "bf16" if want_dt == ref.BF16 else "f32"))
         elif k == "group_norm":
             got = rd.fused_group_norm_silu(h["x"], case["groups"], h["w"], h["b"], case["eps"])
             compare(orc, case, "silu", _grab(rd, case, got, case["shape"]), want["silu"])

@@ -563,6 +563,77 @@ Tensor B200Backend::rms_norm_rope(const Tensor& raw, const Tensor* weight_raw, f
     });
 }
 
+std::pair<Tensor, Tensor> B200Backend::rms_norm_rope_pair(const Tensor& a_raw, const Tensor& weight_a_raw, const Tensor& b_raw,
+                                                          const Tensor& weight_b_raw, float eps, const Tensor* cos_raw,
+                                                          const Tensor* sin_raw, int heads, bool per_head_norm, DType output) {
+    std::pair<Tensor, Tensor> result;
+    guarded([&] {
+        require(a_raw.ndim() == 3 && b_raw.ndim() == 3 && heads > 0 && a_raw.dim(2) % heads == 0 && a_raw.dim(2) == b_raw.dim(2),
+                "split_heads shape mismatch");
+        const DType dtype = operand_dtype(a_raw);
+        require(operand_dtype(b_raw) == dtype, "Incompatible broadcast shapes");
+        Tensor a = copy_to_device(a_raw, dtype), b = copy_to_device(b_raw, dtype), c, s;
+        const int64_t width = a.dim(2), rows_a = a.numel() / width, rows_b = b.numel() / width, head_width = width / heads;
+        const int64_t norm_width = per_head_norm ? head_width : width;
+        Tensor weight_a = parameter(weight_a_raw), weight_b = copy_to_device(weight_b_raw, weight_a.dtype());
+        require(weight_a.numel() == norm_width && weight_b.numel() == norm_width, "rms norm weight mismatch");
+        int64_t f_rows = 0, f_width = 8;
+        DType table_dtype = DType::F32;
+        if (cos_raw) {
+            require(sin_raw != nullptr, "RoPE frequency mismatch");
+            table_dtype = device_float(*cos_raw) ? cos_raw->dtype() : DType::F32;
+            c = copy_to_device(*cos_raw, table_dtype);
+            s = copy_to_device(*sin_raw, table_dtype);
+            require(c.shape() == s.shape() && c.ndim() >= 2, "RoPE frequency mismatch");
+            f_width = c.dim(-1) == width ? width : c.dim(-1) * c.dim(-2);
+            require((c.dim(-1) == head_width || c.dim(-1) == width) && (f_width == head_width || f_width == width),
+                    "Incompatible broadcast shapes");
+            f_rows = c.numel() / f_width;
+            require((f_rows == rows_a || f_rows == rows_a / a.dim(0)) && (f_rows == rows_b || f_rows == rows_b / b.dim(0)),
+                    "Incompatible broadcast shapes");
+        }
+        result.first = rt_->allocate_device(a.shape(), output);
+        result.second = rt_->allocate_device(b.shape(), output);
+        ProfileRegion region(*this, [] { return std::string("fused.norm.rms+rope.pair"); },
+                             bytes_of(a) + bytes_of(b) + bytes_of(result.first) + bytes_of(result.second));
+        check(vrb_rms_norm_rope_pair(a.data(), weight_a.data(), result.first.data(), rows_a, b.data(), weight_b.data(),
+                                     result.second.data(), rows_b, code(dtype), code(weight_a.dtype()), cos_raw ? c.data() : nullptr,
+                                     cos_raw ? s.data() : nullptr, code(table_dtype), f_rows, f_width, 1, code(output), width,
+                                     norm_width, eps, kLegacyStream));
+        return result.first;
+    });
+    return result;
+}
+
+std::pair<Tensor, Tensor> B200Backend::normalized_gated_residual_norm_scale(const Tensor& residual_raw, const Tensor& branch_raw,
+                                                                            const Tensor& gate_raw, const Tensor& scale_raw,
+                                                                            DType state, float branch_eps, float eps) {
+    std::pair<Tensor, Tensor> result;
+    guarded([&] {
+        Tensor residual = copy_to_device(residual_raw, operand_dtype(residual_raw));
+        Tensor branch = copy_to_device(branch_raw, operand_dtype(branch_raw));
+        require(residual.shape() == branch.shape(), "Incompatible broadcast shapes");
+        Tensor gate = parameter(gate_raw), scale = parameter(scale_raw);
+        const int64_t width = residual.dim(-1), rows = residual.numel() / width;
+        int64_t gate_rows = 1, gate_vectors = 1, scale_rows = 1, scale_vectors = 1;
+        vector_layout(residual, gate, gate_rows, gate_vectors);
+        vector_layout(residual, scale, scale_rows, scale_vectors);
+        const bool one_pass = residual.dtype() == DType::BF16 && branch.dtype() == DType::BF16 && state == DType::BF16;
+        if (!one_pass) gate = activation(gate, vrhino::Activation::Tanh);   // a temporary of [B, D]
+        result.first = rt_->allocate_device(residual.shape(), state);
+        result.second = rt_->allocate_device(residual.shape(), state);
+        ProfileRegion region(*this, [] { return std::string("fused.mochi.residual+norm"); },
+                             bytes_of(residual) + bytes_of(branch) + bytes_of(result.first) + bytes_of(result.second));
+        check(vrb_rms_norm_gated_residual_rms_norm_scale(residual.data(), code(residual.dtype()), branch.data(), code(branch.dtype()),
+                                                         branch_eps, gate.data(), code(gate.dtype()), one_pass ? 1 : 0, gate_rows,
+                                                         gate_vectors, result.first.data(), code(state), scale.data(),
+                                                         code(scale.dtype()), scale_rows, scale_vectors, result.second.data(), rows,
+                                                         width, eps, kLegacyStream));
+        return result.first;
+    });
+    return result;
+}
+
 Tensor B200Backend::gated_residual(const Tensor& residual_raw, const Tensor& branch_raw, const Tensor* gate_raw, DType state) {
     return guarded([&] {
         Tensor residual = copy_to_device(residual_raw, operand_dtype(residual_raw));
@@ -745,6 +816,30 @@ Tensor rms_norm_rope(vrhino::Backend& backend, const vrhino::PrecisionPolicy& po
                              : vrhino::split_heads(backend, vrhino::attention_norm(backend, policy, x, weight, eps), heads);
     if (cosine) t = vrhino::operation_rope(backend, policy, t, *cosine, *sine);
     return backend.cast(vrhino::merge_heads(backend, t), output);
+}
+
+std::pair<Tensor, Tensor> rms_norm_rope_pair(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy, const Tensor& q,
+                                             const Tensor& weight_q, const Tensor& k, const Tensor& weight_k, float eps,
+                                             const Tensor* cosine, const Tensor* sine, int heads, bool per_head_norm, DType output) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend))
+        return b200->rms_norm_rope_pair(q, weight_q, k, weight_k, eps, cosine, sine, heads, per_head_norm, output);
+    return {rms_norm_rope(backend, policy, q, &weight_q, eps, cosine, sine, heads, per_head_norm, output),
+            rms_norm_rope(backend, policy, k, &weight_k, eps, cosine, sine, heads, per_head_norm, output)};
+}
+
+std::pair<Tensor, Tensor> normalized_gated_residual_norm_scale(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy,
+                                                               const Tensor& residual, const Tensor& branch, const Tensor& gate,
+                                                               const Tensor& scale, float eps) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend))
+        return b200->normalized_gated_residual_norm_scale(residual, branch, gate, scale,
+                                                          policy.persistent_state_dtype(vrhino::PrecisionSemantic::ResidualState),
+                                                          eps, eps);
+    // the block's own operator sequence (mochi.cpp:204-211, :228-231)
+    const std::vector<int64_t> row{residual.dim(0), 1, residual.dim(-1)};
+    Tensor bounded = backend.reshape(backend.activation(gate, vrhino::Activation::Tanh), row);
+    Tensor state = vrhino::gated_residual(backend, policy, residual, backend.rms_norm(branch, nullptr, eps), bounded);
+    Tensor factor = backend.add(vrhino::scalar_f32(1.0f), backend.reshape(scale, row));
+    return {state, backend.mul(backend.rms_norm(state, nullptr, eps), factor)};
 }
 
 Tensor fused_gated_residual(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy, const Tensor& residual,

@@ -67,7 +67,17 @@ public:
     Tensor rms_norm_modulate(const Tensor& x, float eps, const Tensor& shift, const Tensor& scale, DType output);
     Tensor rms_norm_rope(const Tensor& x, const Tensor* weight, float eps, const Tensor* cosine,
                          const Tensor* sine, int heads, bool per_head_norm, DType output);
+    // rms_norm_rope on two tensors (q and k) in one launch: same width, dtype and tables, own weights and
+    // row counts; {out_a, out_b}.  cosine / sine may be null (norm + cast only: cross-attention q and text k).
+    std::pair<Tensor, Tensor> rms_norm_rope_pair(const Tensor& x_a, const Tensor& weight_a, const Tensor& x_b, const Tensor& weight_b,
+                                                 float eps, const Tensor* cosine, const Tensor* sine, int heads, bool per_head_norm,
+                                                 DType output);
     Tensor gated_residual(const Tensor& residual, const Tensor& branch, const Tensor* gate, DType state);
+    // Mochi (mochi.cpp:204-211, :228-231): {state, normed} with state = residual + rms_norm(branch, none, branch_eps) *
+    // tanh(gate) in `state` dtype and normed = rms_norm(state, none, eps) * (1 + scale) in the stream's dtype; one
+    // kernel for a BF16 stream, tanh + the two operators otherwise
+    std::pair<Tensor, Tensor> normalized_gated_residual_norm_scale(const Tensor& residual, const Tensor& branch, const Tensor& gate,
+                                                                   const Tensor& scale, DType state, float branch_eps, float eps);
     // {state, normed}: state = gated_residual / residual_add (gate == nullptr) in `state` dtype,
     // normed = cast(layer_norm(state, weight, bias, eps) [modulated by shift, scale], output);
     // one kernel when the residual stream, the branch and both results are BF16
@@ -228,6 +238,18 @@ vrhino::Tensor rms_norm_rope(vrhino::Backend& backend, const vrhino::PrecisionPo
                              const vrhino::Tensor& x, const vrhino::Tensor* weight, float eps,
                              const vrhino::Tensor* cosine, const vrhino::Tensor* sine, int heads,
                              bool per_head_norm = false, vrhino::DType output = vrhino::DType::BF16);
+// the same for q and k together (wan.cpp:38-52 normalises and rotates one after the other): {q operand, k operand}
+std::pair<vrhino::Tensor, vrhino::Tensor> rms_norm_rope_pair(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy,
+                                                             const vrhino::Tensor& q, const vrhino::Tensor& weight_q,
+                                                             const vrhino::Tensor& k, const vrhino::Tensor& weight_k, float eps,
+                                                             const vrhino::Tensor* cosine, const vrhino::Tensor* sine, int heads,
+                                                             bool per_head_norm = false,
+                                                             vrhino::DType output = vrhino::DType::BF16);
+// Mochi's layer boundary (mochi.cpp:204-211 then :228-231): {x', y} with x' = x + rms_norm(branch) * tanh(gate) and
+// y = rms_norm(x') * (1 + scale); gate and scale are [B, D]
+std::pair<vrhino::Tensor, vrhino::Tensor> normalized_gated_residual_norm_scale(
+    vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy, const vrhino::Tensor& residual,
+    const vrhino::Tensor& branch, const vrhino::Tensor& gate, const vrhino::Tensor& scale, float eps = 1e-6f);
 // gated_residual / residual_add (gate == nullptr) of common.cpp:134-144.
 vrhino::Tensor fused_gated_residual(vrhino::Backend& backend, const vrhino::PrecisionPolicy& policy,
                                     const vrhino::Tensor& residual, const vrhino::Tensor& branch,
