@@ -134,6 +134,44 @@ int vrb_pixel_norm(const void* x, int dtype, const void* scale, const void* shif
 int vrb_l2_normalize(const void* x, void* out, int dtype, int64_t outer, int64_t channels, int64_t inner,
                      float eps, vrb_stream stream);
 
+/* ---- layout operators -------------------------------------------------------------------------
+ * Shapes are arrays of `rank` extents (rank <= 8), outermost first; tensors are contiguous; dtype is
+ * VRB_F32 or VRB_BF16; results are bit-exact copies.  A tensor with a zero extent launches nothing.
+ *
+ * CudaBackend::permute (:3936-3947, permute_kernel :767-780): out has shape[dims[d]] along d and
+ * out[c_0..c_{r-1}] = x[the coordinate whose axis dims[d] is c_d].  "Invalid permutation" unless dims is
+ * a permutation of 0..rank-1. */
+int vrb_permute(const void* x, void* out, int dtype, int rank, const int64_t* shape, const int64_t* dims,
+                vrb_stream stream);
+
+/* CudaBackend::slice (:3960-3970, slice_kernel :782-796): x[..., start:stop, ...] along `dim` of `shape`
+ * (x's shape).  As there: a negative dim counts from the end, negative start / stop are offset by the
+ * extent, start is clamped into [0, extent] and stop into [start, extent]; out must hold the clamped
+ * range. */
+int vrb_slice(const void* x, void* out, int dtype, int rank, const int64_t* shape, int dim, int64_t start,
+              int64_t stop, vrb_stream stream);
+
+/* CudaBackend::concat (:3949-3958, copy_into_concat_kernel :798-813): `count` tensors that differ only
+ * along `dim`, where input k has extents[k]; `shape` is the OUTPUT's shape and shape[dim] must equal the
+ * sum of extents ("concat shape mismatch" otherwise).  One launch per input, like the reference. */
+int vrb_concat(const void* const* inputs, const int64_t* extents, int count, void* out, int dtype, int rank,
+               const int64_t* shape, int dim, vrb_stream stream);
+
+/* CudaBackend::pad (:4875-4883, pad_kernel :1771-1788): out has shape[d] + before[d] + after[d] along
+ * every axis (per-axis arrays of `rank` entries; the reference's innermost-first pair vector is unpacked
+ * by the caller).  replicate == 0: positions outside x hold `value` rounded to dtype; replicate != 0:
+ * the nearest element of x (coordinates clamped per axis).  "Negative padding unsupported". */
+int vrb_pad(const void* x, void* out, int dtype, int rank, const int64_t* shape, const int64_t* before,
+            const int64_t* after, float value, int replicate, vrb_stream stream);
+
+/* CudaBackend::sinusoidal_embedding (:4190-4196, sinusoidal_kernel :1178-1198): positions [count] ->
+ * out [count, width].  half = width / 2; logical column l = flip ? (column + half) % (2 half) : column;
+ * out = (l < half ? sin : cos)(position * exp(-ln(10000) * (l % half) / (half - downscale))); an odd last
+ * column is 0.  frequency_f64 != 0 evaluates in double and rounds once; otherwise every step is single
+ * precision, in the reference kernel's order. */
+int vrb_sinusoidal_embedding(const void* positions, void* out, int dtype, int64_t count, int64_t width,
+                             int flip, double downscale, int frequency_f64, vrb_stream stream);
+
 /* CudaBackend::pixel_shuffle_nd (:5112-5118, pixel_shuffle_kernel :2170-2186):
  * x [batch, channels*ft*fh*fw, frames, height, width] -> out [batch, channels, frames*ft, height*fh, width*fw],
  * out[b, c, t*ft+pt, h*fh+ph, w*fw+pw] = x[b, ((c*ft+pt)*fh+ph)*fw+pw, t, h, w]. */

@@ -215,10 +215,90 @@ class OracleBackend:
     def reshape(self, x: T, shape) -> T:
         return self.copy_to_device(x, self._dtype_of(x)).reshape(shape)
 
-    def slice(self, x: T, dim: int, start: int, stop: int) -> T:
+    def slice(self, raw: T, dim: int, start: int, stop: int) -> T:
+        """CudaBackend::slice (native/src/backend/cuda/cuda_backend.cu:3960-3970): negative dim / start / stop count
+        from the end, start is clamped into [0, extent], stop into [start, extent]."""
+        x = self.copy_to_device(raw, self._dtype_of(raw))
+        if dim < 0:
+            dim += len(x.shape)
+        if not 0 <= dim < len(x.shape):
+            raise ValueError("slice dimension invalid")
+        size = x.shape[dim]
+        start = start + size if start < 0 else start
+        stop = stop + size if stop < 0 else stop
+        start = min(max(start, 0), size)
+        stop = min(max(stop, start), size)
         index = [slice(None)] * len(x.shape)
         index[dim] = slice(start, stop)
         return T(x.data[tuple(index)], x.dtype)
+
+    def permute(self, raw: T, dims) -> T:
+        """CudaBackend::permute (:3936-3947, permute_kernel :767-780): output axis d is input axis dims[d]."""
+        if len(dims) != len(raw.shape):
+            raise ValueError("permute rank mismatch")
+        if sorted(int(d) for d in dims) != list(range(len(raw.shape))):
+            raise ValueError("Invalid permutation")
+        x = self.copy_to_device(raw, self._dtype_of(raw))
+        return T(np.transpose(x.data, [int(d) for d in dims]), x.dtype)
+
+    def concat(self, tensors, dim: int) -> T:
+        """CudaBackend::concat (:3949-3958): dtype of the first input if it is a device F32 / BF16 tensor."""
+        if not tensors:
+            raise ValueError("concat requires inputs")
+        rank = len(tensors[0].shape)
+        if dim < 0:
+            dim += rank
+        if not 0 <= dim < rank:
+            raise ValueError("concat dimension invalid")
+        for t in tensors:
+            if len(t.shape) != rank:
+                raise ValueError("concat rank mismatch")
+            if any(t.shape[d] != tensors[0].shape[d] for d in range(rank) if d != dim):
+                raise ValueError("concat shape mismatch")
+        dtype = self._dtype_of(tensors[0])
+        return T(np.concatenate([self.copy_to_device(t, dtype).data for t in tensors], axis=dim), dtype)
+
+    def pad(self, raw: T, padding, value: float = 0.0, replicate: bool = False) -> T:
+        """CudaBackend::pad (:4875-4883, pad_kernel :1771-1788): `padding` holds (before, after) pairs from the
+        innermost axis outwards; constant mode stores `value` rounded to the dtype, replicate clamps the
+        source coordinate per axis."""
+        rank = len(raw.shape)
+        if len(padding) % 2 or len(padding) > 2 * rank:
+            raise ValueError("Invalid pad vector")
+        if any(p < 0 for p in padding):
+            raise ValueError("Negative padding unsupported")
+        x = self.copy_to_device(raw, self._dtype_of(raw))
+        widths = [(0, 0)] * rank
+        for pair in range(len(padding) // 2):
+            widths[rank - 1 - pair] = (int(padding[2 * pair]), int(padding[2 * pair + 1]))
+        if replicate:
+            return T(np.pad(x.data, widths, mode="edge"), x.dtype)
+        fill = tensor(np.array(value, dtype=np.float32), x.dtype).data.reshape(())
+        return T(np.pad(x.data, widths, mode="constant", constant_values=fill), x.dtype)
+
+    def sinusoidal_embedding(self, raw: T, width: int, flip: bool, downscale: float, frequency_f64: bool) -> T:
+        """CudaBackend::sinusoidal_embedding (:4190-4196, sinusoidal_kernel :1178-1198).  The single-precision path
+        rounds after every operation like the kernel; exp / sin / cos come from the host's libm, whose last bit
+        can differ from the device functions (the comparison with the reference's device output allows for it)."""
+        if len(raw.shape) != 1 or width <= 0:
+            raise ValueError("sinusoidal embedding contract violation")
+        x = self.copy_to_device(raw, self._dtype_of(raw))
+        positions = x.f32()
+        half = width // 2
+        out = np.zeros((x.numel, width), dtype=np.float32)
+        f32 = np.float32
+        for column in range(2 * half):
+            logical = (column + half) % (2 * half) if flip else column
+            frequency = logical % half
+            if frequency_f64:
+                exponent = -np.log(np.float64(10000.0)) * frequency / (half - np.float64(downscale))
+                phase = positions.astype(np.float64) * np.exp(exponent)
+                out[:, column] = (np.sin(phase) if logical < half else np.cos(phase)).astype(np.float32)
+            else:
+                exponent = f32(f32(-np.log(f32(10000.0))) * f32(frequency)) / f32(f32(half) - f32(downscale))
+                phase = positions * np.exp(f32(exponent)).astype(np.float32)
+                out[:, column] = (np.sin(phase) if logical < half else np.cos(phase)).astype(np.float32)
+        return tensor(out, x.dtype)
 
     def split(self, x: T, sections, dim: int):
         out, offset = [], 0

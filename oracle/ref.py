@@ -99,6 +99,35 @@ class RefHost:
                                                  _c.c_int64(res.size // res.shape[-1]), _c.c_int64(res.shape[-1])))
         return out
 
+    @staticmethod
+    def _i64(values):
+        return (_c.c_int64 * max(len(values), 1))(*[int(v) for v in values])
+
+    def permute(self, x, axes):
+        x = _f(x); out = np.empty([x.shape[a] for a in axes], dtype=np.float32)
+        self._check(self.lib.refh_permute(_ptr(x), x.ndim, self._i64(x.shape), self._i64(axes), _ptr(out)))
+        return out
+
+    def slice(self, x, axis, start, stop):
+        """The host backend takes the range as it is (no negative indices, no clamping)."""
+        x = _f(x); shape = list(x.shape); shape[axis] = stop - start
+        out = np.empty(shape, dtype=np.float32)
+        self._check(self.lib.refh_slice(_ptr(x), x.ndim, self._i64(x.shape), _c.c_int64(axis), _c.c_int64(start), _c.c_int64(stop), _ptr(out)))
+        return out
+
+    def sinusoidal_embedding(self, positions, width, flip, shift):
+        """The host backend always computes the phase in double; it has no zero column for an odd width."""
+        positions = _f(positions); out = np.zeros((positions.size, width), dtype=np.float32)
+        self._check(self.lib.refh_sinusoidal(_ptr(positions), _c.c_int64(positions.size), _c.c_int64(width), int(bool(flip)),
+                                             _c.c_double(shift), _ptr(out)))
+        return out
+
+    def pad_rows(self, x, after, value):
+        x = _f(x); out = np.empty((x.shape[0] + after, x.shape[1]), dtype=np.float32)
+        self._check(self.lib.refh_pad_rows(_ptr(x), _c.c_int64(x.shape[0]), _c.c_int64(x.shape[1]), _c.c_int64(after), _c.c_float(value),
+                                           _ptr(out)))
+        return out
+
     def cfg_euler(self, x, u, c, scale, delta):
         x, u, c = _f(x), _f(u), _f(c)
         guided, out = np.empty_like(x), np.empty_like(x)
@@ -173,7 +202,7 @@ class RefCuda:
                      "refc_exp", "refc_sqrt", "refc_dequantize", "refc_modulate", "refc_attention_norm", "refc_operation_rope",
                      "refc_residual_add", "refc_gated_residual", "refc_cfg_combine", "refc_euler_update", "refc_flow_to_x0",
                      "refc_frame_group_norm", "refc_linear", "refc_pixel_norm", "refc_pixel_shuffle", "refc_repeat",
-                     "refc_l2_normalize"):
+                     "refc_l2_normalize", "refc_permute", "refc_concat", "refc_pad", "refc_sinusoidal"):
             getattr(lib, name).restype = _c.c_int64
         lib.refc_profile_total_ms.restype = _c.c_double
         self.lib = lib
@@ -228,6 +257,18 @@ class RefCuda:
     def l2_normalize(self, x, dim, eps): return self._h(self.lib.refc_l2_normalize(self._i(x), _c.c_int64(dim), _c.c_float(eps)))
     def pixel_shuffle(self, x, factors):
         return self._h(self.lib.refc_pixel_shuffle(self._i(x), *(_c.c_int64(int(f)) for f in factors)))
+    def permute(self, x, dims):
+        d, r = self._shape(tuple(int(v) for v in dims))
+        return self._h(self.lib.refc_permute(self._i(x), r, d))
+    def concat(self, handles, dim):
+        h = (_c.c_int64 * len(handles))(*[int(v) for v in handles])
+        return self._h(self.lib.refc_concat(h, len(handles), _c.c_int64(dim)))
+    def pad(self, x, padding, value=0.0, replicate=False):
+        p = (_c.c_int64 * max(len(padding), 1))(*[int(v) for v in padding])
+        return self._h(self.lib.refc_pad(self._i(x), len(padding), p, _c.c_float(value), int(bool(replicate))))
+    def sinusoidal_embedding(self, positions, width, flip, downscale, frequency_f64):
+        return self._h(self.lib.refc_sinusoidal(self._i(positions), _c.c_int64(width), int(bool(flip)), _c.c_double(downscale),
+                                                int(bool(frequency_f64))))
     def repeat(self, x, copies, dim): return self._h(self.lib.refc_repeat(self._i(x), int(copies), _c.c_int64(dim)))
     def activation(self, x, kind): return self._h(self.lib.refc_activation(self._i(x), int(kind)))
     def rope(self, x, c, s): return self._h(self.lib.refc_rope(self._i(x), self._i(c), self._i(s)))

@@ -142,6 +142,26 @@ int64_t refc_reshape(int64_t x, int rank, const int64_t* shape) {
 int64_t refc_slice(int64_t x, int64_t dim, int64_t start, int64_t stop) {
     return guarded([&] { return keep(g_backend->slice(at(x), dim, start, stop)); });
 }
+int64_t refc_permute(int64_t x, int rank, const int64_t* dims) {
+    return guarded([&] { return keep(g_backend->permute(at(x), std::vector<int64_t>(dims, dims + rank))); });
+}
+int64_t refc_concat(const int64_t* handles, int count, int64_t dim) {
+    return guarded([&] {
+        std::vector<Tensor> parts;
+        for (int k = 0; k < count; ++k) parts.push_back(at(handles[k]));
+        return keep(g_backend->concat(parts, dim));
+    });
+}
+// padding: the reference's vector of (before, after) pairs from the innermost axis outwards
+int64_t refc_pad(int64_t x, int entries, const int64_t* padding, float value, int replicate) {
+    return guarded([&] {
+        return keep(g_backend->pad(at(x), std::vector<int64_t>(padding, padding + entries), value,
+                                   replicate ? vrhino::PadMode::Replicate : vrhino::PadMode::Constant));
+    });
+}
+int64_t refc_sinusoidal(int64_t positions, int64_t width, int flip, double downscale, int frequency_f64) {
+    return guarded([&] { return keep(g_backend->sinusoidal_embedding(at(positions), width, flip != 0, downscale, frequency_f64 != 0)); });
+}
 int64_t refc_layer_norm(int64_t x, int64_t w, int64_t b, float eps) {
     return guarded([&] { return keep(g_backend->layer_norm(at(x), opt(w), opt(b), eps)); });
 }

@@ -91,6 +91,32 @@ int refh_gated_residual(const float* res, const float* branch, const float* gate
         copy_out(gate ? gated_residual(be, policy, r, b, wrap(gate, {1, 1, width})) : residual_add(be, policy, r, b), out);
     });
 }
+// layout operators of the host backend (family_lowering_test_backend.h:77-88, :114-121, :150-154; it has no concat)
+int refh_permute(const float* x, int rank, const int64_t* shape, const int64_t* axes, float* out) {
+    return guarded([&] {
+        family_test::Backend be;
+        copy_out(be.permute(wrap(x, std::vector<int64_t>(shape, shape + rank)), std::vector<int64_t>(axes, axes + rank)), out);
+    });
+}
+int refh_slice(const float* x, int rank, const int64_t* shape, int64_t axis, int64_t start, int64_t stop, float* out) {
+    return guarded([&] {
+        family_test::Backend be;
+        copy_out(be.slice(wrap(x, std::vector<int64_t>(shape, shape + rank)), axis, start, stop), out);
+    });
+}
+int refh_sinusoidal(const float* positions, int64_t count, int64_t width, int flip, double shift, float* out) {
+    return guarded([&] {
+        family_test::Backend be;
+        copy_out(be.sinusoidal_embedding(wrap(positions, {count}), width, flip != 0, shift, true), out);
+    });
+}
+// the one padding the host backend implements: constant padding after axis 1 of a [1, rows, width] tensor
+int refh_pad_rows(const float* x, int64_t rows, int64_t width, int64_t after, float value, float* out) {
+    return guarded([&] {
+        family_test::Backend be;
+        copy_out(be.pad(wrap(x, {1, rows, width}), {0, 0, 0, after}, value, PadMode::Constant), out);
+    });
+}
 int refh_cfg_euler(const float* x, const float* u, const float* c, float* guided, float* out, int64_t count,
                    float scale, float delta) {
     return guarded([&] {

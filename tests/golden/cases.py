@@ -8,6 +8,8 @@ bf16 payloads as uint16 bits.
 """
 from __future__ import annotations
 
+import ctypes
+
 import numpy as np
 
 from vrhino_b200 import synth
@@ -62,6 +64,11 @@ def _inputs(case):
     if k == "depth_to_space":
         b, c, t, h, w = case["shape"]
         return {"x": (n((b, c, t, h, w), 0), case["dt"]), "y": (n((b, 4 * c, t, h, w), 1), case["dt"])}
+    if k == "layout":
+        made = {}
+        for index, (name, shape) in enumerate(case["inputs"].items()):
+            made[name] = (np.asarray(shape, dtype=np.float32) if name == "positions" else n(shape, index), case["dt"])
+        return made
     if k == "linear_output":
         # A GEMM whose F32 accumulators are exact whatever the summation order: only column 0 of x
         # is non-zero, so accumulation[m, n] = x[m, 0] * w[n, 0], the exact product of two bf16 values.
@@ -113,9 +120,66 @@ CASES = [
     {"name": "pixel_norm_rows_f32", "kind": "pixel_norm", "shape": (6, 300), "dt": "f32", "seed": 28},
     {"name": "depth_to_space_bf16", "kind": "depth_to_space", "shape": (1, 32, 3, 6, 16), "dt": "bf16", "seed": 29, "subsample": 5},
     {"name": "depth_to_space_f32_odd", "kind": "depth_to_space", "shape": (2, 8, 2, 3, 5), "dt": "f32", "seed": 30},
+    {"name": "layout_permute_bf16", "kind": "layout", "dt": "bf16", "seed": 31,
+     "inputs": {"frames": (2, 6, 3, 4, 16), "matrix": (1, 96, 200), "map": (1, 24, 2, 5, 7), "patches": (1, 2, 3, 4, 1, 2, 2, 16)},
+     "steps": [("frames_first", "permute", ["frames"], (0, 2, 1, 3, 4)), ("transposed", "permute", ["matrix"], (0, 2, 1)),
+               ("channels_last", "permute", ["map"], (0, 2, 3, 4, 1)), ("channels_first", "permute", ["channels_last"], (0, 4, 1, 2, 3)),
+               ("unpatchified", "permute", ["patches"], (0, 7, 1, 4, 2, 5, 3, 6)), ("reversed", "permute", ["map"], (4, 3, 2, 1, 0))]},
+    {"name": "layout_permute_f32", "kind": "layout", "dt": "f32", "seed": 32,
+     "inputs": {"matrix": (2, 40, 72), "heads": (1, 20, 3, 4, 8), "patches": (1, 2, 3, 4, 1, 2, 2, 16)},
+     "steps": [("transposed", "permute", ["matrix"], (0, 2, 1)), ("qkv", "permute", ["heads"], (2, 0, 3, 1, 4)),
+               ("unpatchified", "permute", ["patches"], (0, 7, 1, 4, 2, 5, 3, 6)), ("swapped", "permute", ["matrix"], (1, 0, 2))]},
+    {"name": "layout_slice_concat_bf16", "kind": "layout", "dt": "bf16", "seed": 33,
+     "inputs": {"proj": (1, 20, 64), "x": (2, 9, 24), "a": (2, 3, 8), "b": (2, 5, 8), "c": (2, 3, 5), "d": (2, 3, 3)},
+     "steps": [("first_half", "slice", ["proj"], (2, 0, 32)), ("second_half", "slice", ["proj"], (2, 32, 64)),
+               ("odd_inner", "slice", ["proj"], (2, 3, 10)), ("middle", "slice", ["x"], (1, 2, 7)), ("outer", "slice", ["x"], (0, 1, 2)),
+               ("from_the_end", "slice", ["x"], (-1, -5, 100)), ("clamped_start", "slice", ["x"], (1, -100, 3)),
+               ("joined_rows", "concat", ["a", "b"], 1), ("joined_inner", "concat", ["c", "d", "c"], -1),
+               ("joined_outer", "concat", ["a", "a", "a"], 0), ("halves_back", "concat", ["first_half", "second_half"], 2)]},
+    {"name": "layout_slice_concat_f32", "kind": "layout", "dt": "f32", "seed": 34,
+     "inputs": {"x": (3, 7, 10), "a": (1, 4, 6), "b": (2, 4, 6)},
+     "steps": [("inner", "slice", ["x"], (2, 1, 9)), ("aligned", "slice", ["x"], (2, 4, 8)), ("rows", "slice", ["x"], (1, 3, 4)),
+               ("joined", "concat", ["a", "b"], 0), ("joined_inner", "concat", ["a", "a"], 2)]},
+    {"name": "layout_pad_bf16", "kind": "layout", "dt": "bf16", "seed": 35,
+     "inputs": {"video": (1, 8, 3, 6, 16), "map": (1, 4, 2, 5, 7), "row": (1, 2)},
+     "steps": [("causal", "pad", ["video"], ((0, 0, 0, 0, 2, 2), 0.0, True)), ("spatial_zero", "pad", ["map"], ((1, 1, 1, 1), 0.0, False)),
+               ("all_axes_value", "pad", ["map"], ((1, 2, 0, 1, 2, 0), -1.3, False)), ("all_axes_edge", "pad", ["map"], ((1, 2, 0, 1, 2, 0), 0.0, True)),
+               ("row_edge", "pad", ["row"], ((1, 2), 0.0, True)), ("after_only", "pad", ["map"], ((0, 1, 0, 1), 0.0, False)),
+               ("outer_constant", "pad", ["video"], ((0, 0, 0, 0, 1, 0, 2, 1), 0.75, False))]},
+    {"name": "layout_pad_f32", "kind": "layout", "dt": "f32", "seed": 36,
+     "inputs": {"video": (1, 3, 2, 4, 8), "map": (2, 3, 5)},
+     "steps": [("causal", "pad", ["video"], ((0, 0, 0, 0, 1, 1), 0.0, True)), ("spatial_value", "pad", ["map"], ((2, 1, 1, 2), 0.1, False)),
+               ("spatial_edge", "pad", ["map"], ((2, 1, 1, 2), 0.0, True)), ("nothing", "pad", ["map"], ((0, 0), 0.0, False))]},
+    {"name": "layout_sinusoidal_f32", "kind": "layout", "dt": "f32", "seed": 37,
+     "inputs": {"positions": (0.0, 1.0, 0.5, 999.0, 37.25, -2.0, 1000.0, 250.0)},
+     "steps": [("timestep_256", "sinusoidal", ["positions"], (256, True, 0.0, False)), ("odd_width", "sinusoidal", ["positions"], (7, False, 1.0, False)),
+               ("double_320", "sinusoidal", ["positions"], (320, True, 0.0, True)), ("double_downscale", "sinusoidal", ["positions"], (64, False, 1.0, True))]},
+    {"name": "layout_sinusoidal_bf16", "kind": "layout", "dt": "bf16", "seed": 38,
+     "inputs": {"positions": (0.0, 1.0, 0.5, 999.0, 37.25, -2.0)},
+     "steps": [("timestep_256", "sinusoidal", ["positions"], (256, True, 0.0, False)), ("double_64", "sinusoidal", ["positions"], (64, False, 0.0, True))]},
     {"name": "linear_output_bf16_state", "kind": "linear_output", "m": 72, "n": 1536, "k": 16, "state": "bf16", "seed": 22, "subsample": 3},
     {"name": "linear_output_f32_state", "kind": "linear_output", "m": 40, "n": 3072, "k": 32, "state": "f32", "seed": 23, "subsample": 5},
 ]
+
+
+def run_layout(case, values, api, grab):
+    """The steps of a layout case -- (output name, operator, operand names, arguments) -- on any of the three
+    back ends; `api` supplies permute / slice / concat / pad / sinusoidal_embedding for that back end's tensors."""
+    for name, op, operands, args in case["steps"]:
+        x = [values[o] for o in operands]
+        if op == "permute":
+            values[name] = api.permute(x[0], list(args))
+        elif op == "slice":
+            values[name] = api.slice(x[0], *args)
+        elif op == "concat":
+            values[name] = api.concat(x, args)
+        elif op == "pad":
+            values[name] = api.pad(x[0], list(args[0]), args[1], args[2])
+        elif op == "sinusoidal":
+            values[name] = api.sinusoidal_embedding(x[0], *args)
+        else:
+            raise KeyError(op)
+        grab(name, values[name])
 
 
 def to_bits(a, dt):
@@ -219,6 +283,11 @@ def run_reference(rc, case):
         act = rc.activation(mod, 0)
         grab("silu", act, shape)
         grab("cast", rc.cast(act, ref.BF16), shape)
+    elif k == "layout":
+        class Api:
+            permute = staticmethod(rc.permute); slice = staticmethod(rc.slice); concat = staticmethod(rc.concat)
+            pad = staticmethod(rc.pad); sinusoidal_embedding = staticmethod(rc.sinusoidal_embedding)
+        run_layout(case, dict(h), Api, lambda name, handle: grab(name, handle, (int(rc.lib.refc_numel(ctypes.c_int64(handle))),)))
     elif k == "depth_to_space":
         b, c, t, h_, w = case["shape"]
         full = (b, c // 2, 2 * t, 2 * h_, 2 * w)
@@ -307,6 +376,8 @@ def run_oracle(orc, case):
         mod = orc.modulate(be, pol, normed, ins["shift"], ins["scale"])
         act = be.activation(mod, 0)
         grab("pnorm", normed); grab("pmod", mod); grab("silu", act); grab("cast", be.cast(act, "bf16"))
+    elif k == "layout":
+        run_layout(case, dict(ins), be, lambda name, t: grab(name, t.reshape((-1,))))
     elif k == "depth_to_space":
         grab("shuffle", be.pixel_shuffle_nd(ins["y"], (2, 2, 2)))
         grab("shuffle_122", be.pixel_shuffle_nd(ins["y"], (1, 2, 2)))
@@ -442,6 +513,8 @@ def run_library(be, ops, case, fused=True):
             mod = ops.modulate(be, pol, be.pixel_norm(ins["x"], 1, 1e-8), ins["shift"], ins["scale"])
             act = be.activation(mod, ops.SILU)
             grab("pmod", mod); grab("silu", act); grab("cast", be.cast(act, torch.bfloat16))
+    elif k == "layout":
+        run_layout(case, dict(ins), be, lambda name, t: grab(name, t.reshape(-1)))
     elif k == "depth_to_space":
         shuffled = be.pixel_shuffle_nd(ins["y"], (2, 2, 2))
         grab("shuffle", shuffled)

@@ -1,0 +1,212 @@
+"""Layout operators of the C ABI (vrb_permute / vrb_slice / vrb_concat / vrb_pad / vrb_sinusoidal_embedding) against
+the oracle: copies bit for bit over every kernel path (16-byte, 4-byte and element units; compile-time and
+run-time ranks; transposition tiles with ragged edges; 64-bit indexing), the reference's argument rules and
+error texts (cuda_backend.cu:3936-3970, :4190-4196, :4875-4883), and the embedding within the host-libm bound."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(torch, a, dt):
+    if dt == "bf16":
+        from vrhino_b200 import synth
+        return torch.from_numpy(synth.to_bf16_bits(a).view(np.int16).copy()).view(torch.bfloat16).cuda()
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+
+
+def _bits(torch, t):
+    t = t.detach().cpu().contiguous()
+    return t.view(torch.int16).numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.numpy().view(np.uint32)
+
+
+def _orc_bits(t):
+    return t.data if t.dtype == "bf16" else t.data.view(np.uint32)
+
+
+def _pair(orc, torch, shape, dt, seed):
+    from vrhino_b200 import synth
+    a = synth.normal(shape, seed=seed)
+    return _dev(torch, a, dt), orc.tensor(a, dt)
+
+
+PERMUTES = [
+    ((2, 6, 3, 4, 16), (0, 2, 1, 3, 4)),          # inner axes kept: 16-byte units
+    ((3, 5, 7), (1, 0, 2)),                       # inner axis kept, odd extent: element units
+    ((1, 1536, 333), (0, 2, 1)),                  # patch embedding: tiles, ragged in one direction
+    ((2, 70, 130), (0, 2, 1)),                    # tiles ragged in both
+    ((1, 24, 2, 5, 7), (0, 2, 3, 4, 1)),          # channels last
+    ((1, 2, 5, 7, 24), (0, 4, 1, 2, 3)),          # and back
+    ((1, 2, 3, 4, 1, 2, 2, 16), (0, 7, 1, 4, 2, 5, 3, 6)),   # Wan unpatchify, rank 8
+    ((2, 3, 4, 5, 6), (4, 3, 2, 1, 0)),           # full reversal: short tile sides, element walk
+    ((4, 9), (0, 1)),                             # identity
+    ((7,), (0,)),
+    ((2, 1, 40, 1, 24), (3, 2, 0, 1, 4)),         # extent-1 axes moved around
+]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("shape,dims", PERMUTES, ids=[f"{s}->{d}".replace(" ", "") for s, d in PERMUTES])
+def test_permute(orc, gpu, shape, dims, dt):
+    import torch
+    be, _ = gpu
+    x, ox = _pair(orc, torch, shape, dt, 3)
+    got = be.permute(x, dims)
+    want = orc.OracleBackend().permute(ox, dims)
+    assert tuple(got.shape) == want.shape
+    assert np.array_equal(_bits(torch, got), _orc_bits(want))
+
+
+SLICES = [
+    ((1, 20, 64), 2, 0, 32), ((1, 20, 64), 2, 32, 64), ((1, 20, 64), 2, 3, 10), ((2, 9, 24), 1, 2, 7), ((2, 9, 24), 0, 1, 2),
+    ((2, 9, 24), -1, -5, 100), ((2, 9, 24), 1, -100, 3), ((2, 9, 24), 1, 4, 4), ((2, 9, 24), 2, 30, 40), ((5, 6, 12), 2, 4, 12),
+    ((3, 4, 5, 6, 7, 2, 3, 4), 4, 2, 6), ((64,), 0, 8, 24),
+]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("shape,dim,start,stop", SLICES, ids=[f"{s}[{d}:{a}:{b}]".replace(" ", "") for s, d, a, b in SLICES])
+def test_slice(orc, gpu, shape, dim, start, stop, dt):
+    import torch
+    be, _ = gpu
+    x, ox = _pair(orc, torch, shape, dt, 4)
+    got = be.slice(x, dim, start, stop)
+    want = orc.OracleBackend().slice(ox, dim, start, stop)
+    assert tuple(got.shape) == want.shape
+    assert np.array_equal(_bits(torch, got), _orc_bits(want))
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_split_and_concat(orc, gpu, dt):
+    import torch
+    be, _ = gpu
+    obe = orc.OracleBackend()
+    x, ox = _pair(orc, torch, (2, 10, 48), dt, 5)
+    for dim, sections in ((2, (16, 32)), (-1, (5, 43)), (1, (3, 3, 4)), (0, (1, 1))):
+        parts, want = be.split(x, list(sections), dim), obe.split(ox, list(sections), dim)
+        for g, w in zip(parts, want):
+            assert np.array_equal(_bits(torch, g), _orc_bits(w))
+        back = be.concat(parts, dim)
+        assert torch.equal(back.view(torch.int16 if dt == "bf16" else torch.int32), x.view(torch.int16 if dt == "bf16" else torch.int32))
+        assert np.array_equal(_bits(torch, back), _orc_bits(obe.concat(want, dim)))
+    a, oa = _pair(orc, torch, (3, 4, 1, 5), dt, 6)
+    b, ob = _pair(orc, torch, (3, 4, 3, 5), dt, 7)
+    assert np.array_equal(_bits(torch, be.concat([a, b, a], 2)), _orc_bits(obe.concat([oa, ob, oa], 2)))
+    from vrhino_b200._lib import VrbError
+    with pytest.raises(VrbError, match="concat shape mismatch"):
+        be.concat([a, x[:, :4].contiguous().reshape(2, 4, 1, 48)], 2)
+    with pytest.raises(VrbError, match="concat requires inputs"):
+        be.concat([], 0)
+    with pytest.raises(VrbError, match="split sections mismatch"):
+        be.split(x, [1, 2], 1)
+
+
+PADS = [
+    ((1, 8, 3, 6, 16), (0, 0, 0, 0, 2, 2), 0.0, True),       # LTX causal padding: 16-byte units, rank 3 after merging
+    ((1, 8, 3, 6, 16), (0, 0, 0, 0, 1, 0), 0.5, False),
+    ((1, 4, 2, 5, 7), (1, 1, 1, 1), 0.0, False),             # spatial: element units
+    ((1, 4, 2, 5, 7), (1, 2, 0, 1, 2, 0), -1.3, False),
+    ((1, 4, 2, 5, 7), (1, 2, 0, 1, 2, 0), 0.0, True),
+    ((2, 3, 2, 5, 7), (1, 0, 1, 0, 1, 0, 1, 0, 1, 0), 2.0, False),   # every axis: run-time rank
+    ((1, 2), (1, 2), 0.0, True),
+    ((6, 40), (0, 8), 1.0, False),                           # inner axis by a multiple of the unit
+    ((2, 3, 5), (0, 0), 0.0, False),                         # nothing to do
+    ((2, 3, 5), (), 0.0, False),
+]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("shape,padding,value,replicate", PADS, ids=[f"{s}+{p}{'r' if r else 'c'}".replace(" ", "") for s, p, v, r in PADS])
+def test_pad(orc, gpu, shape, padding, value, replicate, dt):
+    import torch
+    be, _ = gpu
+    x, ox = _pair(orc, torch, shape, dt, 8)
+    got = be.pad(x, list(padding), value, replicate)
+    want = orc.OracleBackend().pad(ox, list(padding), value, replicate)
+    assert tuple(got.shape) == want.shape
+    assert np.array_equal(_bits(torch, got), _orc_bits(want))
+
+
+def test_argument_rules(orc, gpu):
+    import torch
+    from vrhino_b200._lib import VrbError
+    be, _ = gpu
+    x = torch.zeros(2, 3, 4, device="cuda")
+    with pytest.raises(VrbError, match="permute rank mismatch"):
+        be.permute(x, (0, 1))
+    with pytest.raises(VrbError, match="Invalid permutation"):
+        be.permute(x, (0, 1, 1))
+    with pytest.raises(VrbError, match="slice dimension invalid"):
+        be.slice(x, 3, 0, 1)
+    with pytest.raises(VrbError, match="Invalid pad vector"):
+        be.pad(x, [1, 1, 1])
+    with pytest.raises(VrbError, match="Negative padding unsupported"):
+        be.pad(x, [0, -1])
+    with pytest.raises(VrbError, match="sinusoidal embedding contract violation"):
+        be.sinusoidal_embedding(x, 8, True, 0.0, False)
+    assert be.slice(x, 1, 2, 1).shape == (2, 0, 4)       # an empty range launches nothing
+
+
+def test_raw_entry_point_checks(gpu, cuda_lib):
+    """The C entry points refuse what the wrappers would not pass on."""
+    import ctypes
+    import torch
+    x = torch.zeros(4, 4, device="cuda")
+    out = torch.zeros(4, 4, device="cuda")
+    P, I = ctypes.c_void_p, ctypes.c_int64
+    shape = (I * 2)(4, 4)
+    bad = (I * 2)(0, 0)
+    assert cuda_lib.vrb_permute(P(x.data_ptr()), P(out.data_ptr()), 0, 2, shape, bad, None) != 0
+    assert b"Invalid permutation" in cuda_lib.vrb_last_error()
+    assert cuda_lib.vrb_permute(P(x.data_ptr()), P(out.data_ptr()), 0, 9, shape, bad, None) != 0
+    neg = (I * 2)(0, -1)
+    zero = (I * 2)(0, 0)
+    assert cuda_lib.vrb_pad(P(x.data_ptr()), P(out.data_ptr()), 0, 2, shape, neg, zero, ctypes.c_float(0), 0, None) != 0
+    assert b"Negative padding unsupported" in cuda_lib.vrb_last_error()
+    ptrs = (ctypes.c_void_p * 1)(x.data_ptr())
+    ext = (I * 1)(3)
+    assert cuda_lib.vrb_concat(ptrs, ext, 1, P(out.data_ptr()), 0, 2, shape, 0, None) != 0
+    assert b"concat shape mismatch" in cuda_lib.vrb_last_error()
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_sinusoidal_embedding(orc, gpu, dt):
+    import torch
+    be, _ = gpu
+    positions = np.array([0.0, 1.0, 0.5, 999.0, 37.25, -2.0, 1000.0, 250.0], dtype=np.float32)
+    x, ox = _dev(torch, positions, dt), orc.tensor(positions, dt)
+    obe = orc.OracleBackend()
+    for width, flip, downscale, f64 in ((256, True, 0.0, False), (7, False, 1.0, False), (320, True, 0.0, True), (6, True, 0.0, False)):
+        got = be.sinusoidal_embedding(x, width, flip, downscale, f64).float().cpu().numpy()
+        want = obe.sinusoidal_embedding(ox, width, flip, downscale, f64).f32()
+        bound = (2e-5 + 2.0 ** -21 * np.abs(ox.f32().astype(np.float64)))[:, None] + (2.0 ** -8 * np.abs(want) if dt == "bf16" else 0.0)
+        assert (np.abs(got.astype(np.float64) - want) <= bound).all()
+        if width % 2:
+            assert (got[:, -1] == 0).all()
+
+
+def test_large_tensors_use_every_unit_and_wide_indices(orc, gpu):
+    """Full-size shapes: the Wan patch embedding transposition, a frames-first permute of a VAE feature map, LTX's causal
+    padding, SwiGLU's halves, and one tensor beyond 2^31 elements (64-bit index kernel) -- against torch's own copies."""
+    import torch
+    be, _ = gpu
+    bits = lambda t: t.view(torch.int16)
+    x = torch.randn(1, 1536, 32760, device="cuda").to(torch.bfloat16)
+    assert torch.equal(bits(be.permute(x, (0, 2, 1))), bits(x.permute(0, 2, 1).contiguous()))
+    x = torch.randn(1, 128, 9, 64, 96, device="cuda").to(torch.bfloat16)
+    assert torch.equal(bits(be.permute(x, (0, 2, 1, 3, 4))), bits(x.permute(0, 2, 1, 3, 4).contiguous()))
+    assert torch.equal(bits(be.permute(x, (0, 2, 3, 4, 1))), bits(x.permute(0, 2, 3, 4, 1).contiguous()))
+    padded = be.pad(x, [0, 0, 0, 0, 2, 2], 0.0, True)
+    want = torch.cat([x[:, :, :1].expand(-1, -1, 2, -1, -1), x, x[:, :, -1:].expand(-1, -1, 2, -1, -1)], 2)
+    assert torch.equal(bits(padded), bits(want.contiguous()))
+    spatial = be.pad(x, [1, 1, 1, 1], 0.0, False)
+    assert torch.equal(bits(spatial), bits(torch.nn.functional.pad(x, (1, 1, 1, 1))))
+    del padded, want, spatial
+    proj = torch.randn(1, 8192, 16384, device="cuda").to(torch.bfloat16)
+    a, g = be.split(proj, [8192, 8192], -1)
+    assert torch.equal(bits(a), bits(proj[..., :8192].contiguous())) and torch.equal(bits(g), bits(proj[..., 8192:].contiguous()))
+    del proj, a, g
+    big = torch.empty(5, 2 ** 29 + 8, device="cuda", dtype=torch.bfloat16)           # 2.5 Gi + 40 elements, 5 GiB
+    big.view(torch.int16).random_()
+    part = be.slice(big, 1, 3, big.shape[1] - 1)                                      # odd offset: 2-byte units, > 2^31 of them
+    assert torch.equal(bits(part), bits(big[:, 3:-1].contiguous()))

@@ -32,6 +32,42 @@ def test_pixel_norm_bit_exact(orc, gpu, shape, dt):
     assert_bits_equal(be.pixel_norm(to_torch(x), 1, 1e-8), want, "pixel_norm")
 
 
+@pytest.mark.parametrize("l2", [False, True], ids=["pixel_norm", "l2_normalize"])
+def test_quotient_guards_at_extreme_exponents(orc, gpu, l2):
+    """The tile kernels divide bf16 columns through a per-position reciprocal; outside its proven range (denominators
+    beyond [2^-30, 2^30], results below 2^-28, zeros of either sign, denormals, inf, NaN) they must fall back to the
+    division and still give the reference's bits.  Every position of this tensor is one such case."""
+    be, ops = gpu
+    from vrhino_b200 import synth
+    shape = (1, 64, 1, 4, 16)                         # 64 positions, tile path
+    x = synth.normal(shape, 0.0, 1.0, seed=77).reshape(64, 64)        # [channel, position]
+    scale = lambda position, factor: x.__setitem__((slice(None), position), x[:, position] * np.float32(factor))
+    scale(1, 2.0 ** -40); scale(2, 2.0 ** 40); scale(3, 2.0 ** -100); scale(4, 2.0 ** 100); scale(5, 2.0 ** -120)
+    scale(6, 2.0 ** 62); scale(7, 2.0 ** -29); scale(8, 2.0 ** 29.5)
+    x[:, 9] = 0.0; x[::2, 9] = -0.0                    # all zeros, both signs
+    x[:, 10] = 0.0; x[5, 10] = 3.0; x[6, 10] = -0.0    # zeros beside one value
+    x[:, 11] *= np.float32(2.0 ** -130)                # bf16 denormals
+    x[3, 12] = np.inf
+    x[3, 13] = np.nan
+    x[3, 14] = np.float32(2.0 ** 90); x[4, 14] = np.float32(2.0 ** -90)   # huge and tiny in one position
+    x[3, 15] = np.float32(2.0 ** 20); x[4:, 15] *= np.float32(2.0 ** -20)  # quotients near the 2^-28 floor
+    x[3, 16] = np.float32(2.0 ** 25); x[4:, 16] *= np.float32(2.0 ** -10)
+    x[:, 17] = np.float32(3.3895314e38)                # the largest bf16: the sum of squares overflows
+    t = orc.tensor(x.reshape(shape), "bf16")
+    obe = orc.OracleBackend()
+    with np.errstate(all="ignore"):
+        want = obe.l2_normalize(t, 1, 1e-10) if l2 else obe.pixel_norm(t, 1, 1e-8)
+    got = be.l2_normalize(to_torch(t), 1, 1e-10) if l2 else be.pixel_norm(to_torch(t), 1, 1e-8)
+    g = got.view(__import__("torch").int16).cpu().numpy().view(np.uint16).reshape(64, 64)
+    w = want.data.reshape(64, 64)
+    nan = lambda b: (b & 0x7FFF) > 0x7F80
+    same = (g == w) | (nan(g) & nan(w))
+    if l2:      # the sums are added in a different order there: compare the cases, not the last bit
+        d = orc.bf16_ulp_distance(g, w)
+        same |= d <= 2
+    assert same.all(), f"positions {sorted(set(np.argwhere(~same)[:, 1].tolist()))} differ"
+
+
 @pytest.mark.parametrize("shape", [s for s in SHAPES if len(s) == 5])
 @pytest.mark.parametrize("dt", ["bf16", "f32"])
 def test_pixel_norm_modulate_silu(orc, gpu, shape, dt):

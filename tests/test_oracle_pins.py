@@ -229,6 +229,34 @@ def test_l2_normalize(orc, be, shape):
         be.l2_normalize(orc.tensor(x), 7, 1e-10)
 
 
+def test_layout_known_answers(orc, be):
+    """primitive_tests.cpp:353-361 (permute, concat, slice), :457 (sinusoidal_embedding), :518-520 (pad)."""
+    t = lambda shape, values: orc.tensor(np.array(values, dtype=np.float32).reshape(shape))
+    flat = lambda r: r.data.reshape(-1)
+    close(flat(be.permute(t((2, 3), [0, 1, 2, 3, 4, 5]), (1, 0))), [0, 3, 1, 4, 2, 5])
+    close(flat(be.permute(t((1, 2, 2), [0, 1, 2, 3]), (2, 0, 1))), [0, 2, 1, 3])
+    close(flat(be.permute(t((2, 1, 2, 1), [0, 1, 2, 3]), (1, 3, 0, 2))), [0, 1, 2, 3])
+    close(flat(be.concat([t((1, 2), [1, 2]), t((1, 1), [3])], 1)), [1, 2, 3])
+    close(flat(be.concat([t((1, 1, 2), [1, 2]), t((2, 1, 2), [3, 4, 5, 6])], 0)), [1, 2, 3, 4, 5, 6])
+    close(flat(be.slice(t((2, 4), [0, 1, 2, 3, 4, 5, 6, 7]), 1, 1, 3)), [1, 2, 5, 6])
+    close(flat(be.slice(t((3, 2), [0, 1, 2, 3, 4, 5]), 0, 1, 3)), [2, 3, 4, 5])
+    close(flat(be.pad(t((1, 2), [1, 2]), [1, 1], 0.0, False)), [0, 1, 2, 0])
+    close(flat(be.pad(t((1, 1, 2), [1, 2]), [1, 0, 1, 0], -1.0, False)), [-1, -1, -1, -1, 1, 2])
+    close(flat(be.pad(t((1, 2), [1, 2]), [1, 2], 0.0, True)), [1, 1, 2, 2, 2])
+    for positions in ([0, 1], [-2, 0.5, 3]):
+        width, half, expected = 6, 3, []
+        for p in positions:
+            expected += [np.cos(np.float32(p) * np.exp(-np.log(np.float32(10000.0)) * i / half)) for i in range(half)]
+            expected += [np.sin(np.float32(p) * np.exp(-np.log(np.float32(10000.0)) * i / half)) for i in range(half)]
+        close(flat(be.sinusoidal_embedding(t((len(positions),), positions), width, True, 0.0, False)), expected, 2e-5)
+    with pytest.raises(ValueError, match="Invalid permutation"):
+        be.permute(t((2, 3), [0] * 6), (0, 0))
+    with pytest.raises(ValueError, match="Negative padding unsupported"):
+        be.pad(t((1, 2), [1, 2]), [-1, 0])
+    with pytest.raises(ValueError, match="concat shape mismatch"):
+        be.concat([t((1, 2), [1, 2]), t((2, 1), [3, 4])], 1)
+
+
 def test_clamp_exp_sqrt(orc, be):
     close(be.clamp(orc.tensor([-2, -1, 0, 1, 2]), -0.5, 0.75).data, [-0.5, -0.5, 0, 0.75, 0.75])
     close(be.clamp(orc.tensor([[-3, 0.2], [4, 0.8]]), 0, 1).data, [0, 0.2, 1, 0.8])

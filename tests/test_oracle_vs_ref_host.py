@@ -82,6 +82,21 @@ def test_cfg_and_euler_bit_exact(orc, be, host):
     assert np.array_equal(orc.euler_update(be, policy, orc.tensor(x), g, orc.scalar_f32(0.02), True).data, out)
 
 
+def test_layout_operators_bit_exact(orc, be, host):
+    """permute / slice / the one pad the host backend implements: pure copies, bit for bit; the sinusoidal embedding
+    (the host backend's phase is always double) against the oracle's double path at the F32 gate."""
+    x = data((2, 3, 4, 5), 11)
+    for axes in ((0, 2, 1, 3), (3, 2, 1, 0), (1, 0, 3, 2), (0, 1, 2, 3)):
+        assert np.array_equal(be.permute(orc.tensor(x), axes).data, host.permute(x, axes))
+    for axis, start, stop in ((3, 1, 4), (1, 0, 2), (0, 1, 2), (2, 3, 4)):
+        assert np.array_equal(be.slice(orc.tensor(x), axis, start, stop).data, host.slice(x, axis, start, stop))
+    rows = data((3, 8), 12)
+    assert np.array_equal(be.pad(orc.tensor(rows[None]), [0, 0, 0, 2], -0.5).data[0], host.pad_rows(rows, 2, -0.5))
+    positions = np.array([0.0, 1.0, 0.5, 999.0, 37.25, -2.0], dtype=np.float32)
+    for width, flip, shift in ((256, True, 0.0), (64, False, 1.0), (6, True, 0.0)):
+        gate(be.sinusoidal_embedding(orc.tensor(positions), width, flip, shift, True).data, host.sinusoidal_embedding(positions, width, flip, shift))
+
+
 def test_reference_chain_runs_threaded(host):
     sec, nbytes = host.wan_chain_seconds(tokens=64, threads=2, steps=1, ffn=256)
     assert sec > 0 and nbytes > 0

@@ -23,7 +23,7 @@ class VrbError(RuntimeError):
 
 
 _c = ctypes
-_vp, _i, _i64, _f, _sz = _c.c_void_p, _c.c_int, _c.c_int64, _c.c_float, _c.c_size_t
+_vp, _i, _i64, _f, _sz, _d = _c.c_void_p, _c.c_int, _c.c_int64, _c.c_float, _c.c_size_t, _c.c_double
 _pi64 = _c.POINTER(_c.c_int64)
 
 # name -> argtypes; every entry returns int unless listed in _RESTYPES
@@ -74,6 +74,11 @@ SIGNATURES = {
     "vrb_pixel_shuffle": [_vp, _vp, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _vp],
     "vrb_depth_to_space_residual": [_vp, _vp, _vp, _i, _i64, _i64, _i64, _i64, _i64, _vp],
     "vrb_l2_normalize": [_vp, _vp, _i, _i64, _i64, _i64, _f, _vp],
+    "vrb_permute": [_vp, _vp, _i, _i, _vp, _vp, _vp],
+    "vrb_slice": [_vp, _vp, _i, _i, _vp, _i, _i64, _i64, _vp],
+    "vrb_concat": [_vp, _vp, _i, _vp, _i, _i, _vp, _i, _vp],
+    "vrb_pad": [_vp, _vp, _i, _i, _vp, _vp, _vp, _f, _i, _vp],
+    "vrb_sinusoidal_embedding": [_vp, _vp, _i, _i64, _i64, _i, _d, _i, _vp],
     "vrb_pixel_norm": [_vp, _i, _vp, _vp, _i, _i, _vp, _i, _i64, _i64, _i64, _f, _vp],
     "vrb_linear_output": [_vp, _vp, _vp, _i64, _i64, _vp],
     "vrb_linear_output_activation": [_vp, _vp, _i, _vp, _i64, _i64, _vp],

@@ -76,10 +76,31 @@ __device__ __forceinline__ void async_copy_wait() { asm volatile("cp.async.wait_
 // Epilogue variants of the tile kernel, fixed at compile time.
 enum Mode { kNormOnly = 0, kModulate = 1, kModulateSilu = 2 };
 
+// x / d for a bf16-representable x without a division per element.  With r = RN(1 / d):
+//   q = RN(x * r);  e = x - d * q (one FMA, exact);  q' = RN(q + e * r)
+// equals RN(x / d) for EVERY pair (bf16 significand of x, F32 significand of d) -- all 2^7 x 2^23
+// pairs are enumerated by tests/test_reciprocal_division.py -- and scaling x or d by a power of two
+// changes nothing as long as x, d, r, q and e stay normal.  reciprocal_or_zero() therefore hands out r
+// only for d in [2^-30, 2^30] and 0 otherwise (also for an infinite or NaN d), and a result below
+// 2^-28 in magnitude, or NaN, -- a zero (its sign), a tiny x, or r == 0 -- takes the division.
+constexpr float kReciprocalLow = 9.313225746154785e-10f, kReciprocalHigh = 1073741824.0f;   // 2^-30, 2^30
+constexpr float kQuotientFloor = 3.725290298461914e-09f;                                     // 2^-28
+__device__ __forceinline__ float reciprocal_or_zero(float d) {
+    return d >= kReciprocalLow && d <= kReciprocalHigh ? __frcp_rn(d) : 0.0f;
+}
+__device__ __forceinline__ float quotient_of_bf16(float x, float d, float r) {
+    const float q = __fmul_rn(x, r);
+    const float corrected = __fmaf_rn(__fmaf_rn(-d, q, x), r, q);
+    if (!(fabsf(corrected) >= kQuotientFloor)) return __fdiv_rn(x, d);
+    return corrected;
+}
+
 // One normalised element to the stored value with everything known at compile time.
 template <bool X_BF16, int MODE>
-__device__ __forceinline__ float finish_tile(float x, float denominator, float one_plus_scale, float shift) {
-    float v = __fdiv_rn(x, denominator);
+__device__ __forceinline__ float finish_tile(float x, float denominator, float reciprocal, float one_plus_scale, float shift) {
+    float v;
+    if constexpr (X_BF16) v = quotient_of_bf16(x, denominator, reciprocal);
+    else v = __fdiv_rn(x, denominator);
     if constexpr (X_BF16 && MODE != kNormOnly) v = round_to_bf16(v);   // kNormOnly: the bf16 store rounds
     if constexpr (MODE != kNormOnly) v = __fadd_rn(__fmul_rn(v, one_plus_scale), shift);
     if constexpr (MODE == kModulateSilu) v = activation_value(VRB_SILU, v);
@@ -97,6 +118,7 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
     const int tile_chunks = channels * cols;
     float* const partial = reinterpret_cast<float*>(tiles_buffer + 2 * static_cast<size_t>(tile_chunks));   // [kLanes][positions]
     float* const denominator = partial + kLanes * positions;                                              // [positions]
+    float* const reciprocal = denominator + positions;                                                    // [positions], bf16 input only
     const int64_t inner_chunks = p.inner / EPC;
     const int64_t tiles_per_outer = (inner_chunks + cols - 1) / cols;
     const int64_t tiles = p.outer * tiles_per_outer;
@@ -161,7 +183,9 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
             float s[kLanes];
 #pragma unroll
             for (int a = 0; a < kLanes; ++a) s[a] = partial[a * positions + threadIdx.x];
-            denominator[threadIdx.x] = denominator_of(p, tree8(s), channel_count);
+            const float d = denominator_of(p, tree8(s), channel_count);
+            denominator[threadIdx.x] = d;
+            if constexpr (X_BF16) reciprocal[threadIdx.x] = reciprocal_or_zero(d);
         }
         __syncthreads();
         const int64_t out_chunk0 = o * p.channels * inner_chunks + chunk0;
@@ -179,13 +203,16 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
             const float4* d4 = reinterpret_cast<const float4*>(denominator + k * EPC);
             if constexpr (X_BF16) {
                 const float4 da = d4[0], db = d4[1];
+                const float4* r4 = reinterpret_cast<const float4*>(reciprocal + k * EPC);
+                const float4 ra = r4[0], rb = r4[1];
                 const float d[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+                const float r[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
                 const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
                 float v[8];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    v[2 * j] = finish_tile<true, MODE>(__uint_as_float(w[j] << 16), d[2 * j], ops, sh);
-                    v[2 * j + 1] = finish_tile<true, MODE>(__uint_as_float(w[j] & 0xffff0000u), d[2 * j + 1], ops, sh);
+                    v[2 * j] = finish_tile<true, MODE>(__uint_as_float(w[j] << 16), d[2 * j], r[2 * j], ops, sh);
+                    v[2 * j + 1] = finish_tile<true, MODE>(__uint_as_float(w[j] & 0xffff0000u), d[2 * j + 1], r[2 * j + 1], ops, sh);
                 }
                 if constexpr (MODE == kNormOnly || OUT_BF16) {
                     __stcs(static_cast<uint4*>(p.out) + chunk, make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
@@ -199,7 +226,7 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
                 const float in[4] = {__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w)};
                 float v[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = finish_tile<false, MODE>(in[j], d[j], ops, sh);
+                for (int j = 0; j < 4; ++j) v[j] = finish_tile<false, MODE>(in[j], d[j], 0.0f, ops, sh);
                 if constexpr (MODE != kNormOnly && OUT_BF16) {
                     __stcs(static_cast<uint2*>(p.out) + chunk, make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3])));
                 } else {
@@ -537,7 +564,7 @@ int pixel_norm_family(const void* x, int dtype, const void* scale, const void* s
         for (int budget_ctas : {3, 1}) {
             for (int cols = 8, log2 = 3; cols >= 1; cols >>= 1, --log2) {
                 if (cols > 1 && cols / 2 >= inner_chunks) continue;
-                const size_t smem = 2 * static_cast<size_t>(channels) * cols * 16 + static_cast<size_t>(kLanes + 1) * cols * epc * 4;
+                const size_t smem = 2 * static_cast<size_t>(channels) * cols * 16 + static_cast<size_t>(kLanes + 2) * cols * epc * 4;
                 if (smem > (budget_ctas == 3 ? 72 * 1024 : 200 * 1024) || smem > kMaxTileBytes) continue;
                 const int mode = !scale ? kNormOnly : fuse_silu ? kModulateSilu : kModulate;
                 const int variant = (dtype == VRB_BF16 ? 8 : 0) | (mode << 1) | (out_dtype == VRB_BF16 ? 1 : 0);

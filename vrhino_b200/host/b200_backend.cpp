@@ -435,6 +435,129 @@ Tensor B200Backend::l2_normalize(const Tensor& raw, int64_t dim, float eps) {
     });
 }
 
+// ---- layout operators ----------------------------------------------------------------------------------
+Tensor B200Backend::permute(const Tensor& raw, const std::vector<int64_t>& dims) {
+    return guarded([&] {   // VRHINO_PROFILE("permute") carries the failure guard (cuda_backend.cu:3938)
+        require(static_cast<int64_t>(dims.size()) == static_cast<int64_t>(raw.ndim()), "permute rank mismatch");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype);
+        std::vector<int64_t> shape(dims.size());
+        std::vector<bool> seen(dims.size());
+        for (size_t d = 0; d < dims.size(); ++d) {
+            require(dims[d] >= 0 && dims[d] < static_cast<int64_t>(x.ndim()) && !seen[dims[d]], "Invalid permutation");
+            seen[dims[d]] = true;
+            shape[d] = x.shape()[dims[d]];
+        }
+        Tensor out = rt_->allocate_device(shape, dtype);
+        ProfileRegion region(*this, [] { return std::string("permute"); }, bytes_of(x) + bytes_of(out));
+        check(vrb_permute(x.data(), out.data(), code(dtype), static_cast<int>(dims.size()), x.shape().data(), dims.data(), kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::concat(const std::vector<Tensor>& inputs, int64_t dim) {
+    return guarded([&] {   // VRHINO_PROFILE("concat") (cuda_backend.cu:3951)
+        require(!inputs.empty(), "concat requires inputs");
+        const int rank = static_cast<int>(inputs[0].ndim());
+        if (dim < 0) dim += rank;
+        require(dim >= 0 && dim < rank, "concat dimension invalid");
+        std::vector<int64_t> shape = inputs[0].shape();
+        shape[dim] = 0;
+        for (const Tensor& input : inputs) {
+            require(static_cast<int>(input.ndim()) == rank, "concat rank mismatch");
+            for (int d = 0; d < rank; ++d)
+                if (d != dim) require(input.shape()[d] == inputs[0].shape()[d], "concat shape mismatch");
+            shape[dim] += input.shape()[dim];
+        }
+        const DType dtype = operand_dtype(inputs[0]);
+        Tensor out = rt_->allocate_device(shape, dtype);
+        std::vector<Tensor> parts;          // converted inputs stay alive until the launches are enqueued
+        std::vector<const void*> pointers;
+        std::vector<int64_t> extents;
+        for (const Tensor& raw : inputs) {
+            parts.push_back(copy_to_device(raw, dtype));
+            pointers.push_back(parts.back().data());
+            extents.push_back(raw.shape()[dim]);
+        }
+        ProfileRegion region(*this, [] { return std::string("concat"); }, 2 * bytes_of(out));
+        check(vrb_concat(pointers.data(), extents.data(), static_cast<int>(parts.size()), out.data(), code(dtype), rank, shape.data(),
+                         static_cast<int>(dim), kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::slice(const Tensor& raw, int64_t dim, int64_t start, int64_t stop) {
+    return guarded([&] {   // VRHINO_PROFILE("slice") (cuda_backend.cu:3962)
+        if (dim < 0) dim += static_cast<int64_t>(raw.ndim());
+        require(dim >= 0 && dim < static_cast<int64_t>(raw.ndim()), "slice dimension invalid");
+        const int64_t size = raw.shape()[dim];
+        if (start < 0) start += size;
+        if (stop < 0) stop += size;
+        start = std::clamp<int64_t>(start, 0, size);
+        stop = std::clamp<int64_t>(stop, start, size);
+        std::vector<int64_t> shape = raw.shape();
+        shape[dim] = stop - start;
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype);
+        Tensor out = rt_->allocate_device(shape, dtype);
+        ProfileRegion region(*this, [] { return std::string("slice"); }, 2 * bytes_of(out));
+        check(vrb_slice(x.data(), out.data(), code(dtype), static_cast<int>(x.ndim()), x.shape().data(), static_cast<int>(dim), start, stop,
+                        kLegacyStream));
+        return out;
+    });
+}
+
+std::vector<Tensor> B200Backend::split(const Tensor& x, const std::vector<int64_t>& sections, int64_t dim) {
+    // cuda_backend.cu:3972-3976: consecutive slices
+    if (dim < 0) dim += static_cast<int64_t>(x.ndim());
+    require(dim >= 0 && dim < static_cast<int64_t>(x.ndim()), "slice dimension invalid");
+    int64_t total = 0;
+    for (int64_t section : sections) total += section;
+    require(total == x.shape()[dim], "split sections mismatch");
+    std::vector<Tensor> result;
+    int64_t offset = 0;
+    for (int64_t section : sections) {
+        result.push_back(slice(x, dim, offset, offset + section));
+        offset += section;
+    }
+    return result;
+}
+
+Tensor B200Backend::sinusoidal_embedding(const Tensor& raw, int64_t width, bool flip, double downscale, bool frequency_f64) {
+    return guarded([&] {   // VRHINO_PROFILE("sinusoidal_embedding") (cuda_backend.cu:4192)
+        require(raw.ndim() == 1 && width > 0, "sinusoidal embedding contract violation");
+        const DType dtype = operand_dtype(raw);
+        Tensor positions = copy_to_device(raw, dtype);
+        Tensor out = rt_->allocate_device({raw.numel(), width}, dtype);
+        ProfileRegion region(*this, [] { return std::string("sinusoidal_embedding"); }, bytes_of(positions) + bytes_of(out));
+        check(vrb_sinusoidal_embedding(positions.data(), out.data(), code(dtype), raw.numel(), width, flip ? 1 : 0, downscale,
+                                       frequency_f64 ? 1 : 0, kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::pad(const Tensor& raw, const std::vector<int64_t>& padding, float value, vrhino::PadMode mode) {
+    return guarded([&] {   // VRHINO_PROFILE("pad") (cuda_backend.cu:4877)
+        require(padding.size() % 2 == 0 && padding.size() <= static_cast<size_t>(2 * raw.ndim()), "Invalid pad vector");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype);
+        const int rank = static_cast<int>(x.ndim());
+        std::vector<int64_t> shape = x.shape(), before(rank, 0), after(rank, 0);
+        for (size_t pair = 0; pair < padding.size() / 2; ++pair) {
+            const int d = rank - 1 - static_cast<int>(pair);
+            require(padding[2 * pair] >= 0 && padding[2 * pair + 1] >= 0, "Negative padding unsupported");
+            before[d] = padding[2 * pair];
+            after[d] = padding[2 * pair + 1];
+            shape[d] += before[d] + after[d];
+        }
+        Tensor out = rt_->allocate_device(shape, dtype);
+        ProfileRegion region(*this, [] { return std::string("pad"); }, bytes_of(x) + bytes_of(out));
+        check(vrb_pad(x.data(), out.data(), code(dtype), rank, x.shape().data(), before.data(), after.data(), value,
+                      mode == vrhino::PadMode::Replicate ? 1 : 0, kLegacyStream));
+        return out;
+    });
+}
+
 Tensor B200Backend::pixel_shuffle_nd(const Tensor& raw, const std::vector<int64_t>& factors) {
     return guarded([&] {   // VRHINO_PROFILE("pixel_shuffle") carries the failure guard (cuda_backend.cu:5114)
         require(raw.ndim() == 5 && factors.size() == 3, "pixel_shuffle_nd requires 5D and 3 factors");

@@ -14,7 +14,8 @@
 // Replaced virtuals (same signatures, defaults, dtype rules and error texts as
 // native/src/backend/cuda/cuda_backend.cu): add, mul, div, maximum (:3871-3902), cast (:3978),
 // layer_norm (:4057), rms_norm (:4091), activation (:4179), rope_nd (:4198), group_norm (:4919),
-// clamp (:5128), exp, sqrt (:5134-5173), pixel_norm (:5048), l2_normalize (:5088), pixel_shuffle_nd (:5112)
+// clamp (:5128), exp, sqrt (:5134-5173), pixel_norm (:5048), l2_normalize (:5088), pixel_shuffle_nd (:5112),
+// permute / concat / split / slice (:3936-3976), sinusoidal_embedding (:4190), pad (:4875)
 // and the quantised branch of copy_to_device (:3214-3296).
 // Kernels run on the legacy default stream, which the runtime's pool reuse relies on
 // (cuda_backend.cu:55-59).
@@ -59,6 +60,15 @@ public:
     Tensor pixel_norm(const Tensor& x, int64_t dim, float eps) override;
     Tensor pixel_shuffle_nd(const Tensor& x, const std::vector<int64_t>& factors) override;
     Tensor l2_normalize(const Tensor& x, int64_t dim, float eps) override;
+    // layout operators (:3936-3976, :4190-4196, :4875-4883)
+    Tensor permute(const Tensor& x, const std::vector<int64_t>& dims) override;
+    Tensor concat(const std::vector<Tensor>& tensors, int64_t dim) override;
+    std::vector<Tensor> split(const Tensor& x, const std::vector<int64_t>& sections, int64_t dim) override;
+    Tensor slice(const Tensor& x, int64_t dim, int64_t start, int64_t stop) override;
+    Tensor sinusoidal_embedding(const Tensor& positions, int64_t width, bool flip, double downscale_shift,
+                                bool require_f64_semantics) override;
+    Tensor pad(const Tensor& x, const std::vector<int64_t>& padding, float value = 0.0f,
+               vrhino::PadMode mode = vrhino::PadMode::Constant) override;
 
     // ---- fused forms (one kernel each); see the free functions below for the call-site view --
     Tensor layer_norm_modulate(const Tensor& x, const Tensor* weight, const Tensor* bias, float eps,
@@ -169,19 +179,13 @@ public:
     Tensor linear(const Tensor& x, const Tensor& w, const Tensor* b = nullptr, DType c = DType::F16, DType o = DType::F16) override { return rt_->linear(x, w, b, c, o); }
     Tensor batched_matmul(const Tensor& a, const Tensor& b) override { return rt_->batched_matmul(a, b); }
     Tensor reshape(const Tensor& x, const std::vector<int64_t>& s) override { return rt_->reshape(x, s); }
-    Tensor permute(const Tensor& x, const std::vector<int64_t>& d) override { return rt_->permute(x, d); }
-    Tensor concat(const std::vector<Tensor>& t, int64_t d) override { return rt_->concat(t, d); }
-    std::vector<Tensor> split(const Tensor& x, const std::vector<int64_t>& s, int64_t d) override { return rt_->split(x, s, d); }
-    Tensor slice(const Tensor& x, int64_t d, int64_t a, int64_t b) override { return rt_->slice(x, d, a, b); }
     Tensor indexed_gather(const Tensor& t, const Tensor& i) override { return rt_->indexed_gather(t, i); }
-    Tensor sinusoidal_embedding(const Tensor& p, int64_t w, bool f, double d, bool r) override { return rt_->sinusoidal_embedding(p, w, f, d, r); }
     Tensor attention(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor* mask = nullptr, bool causal = false,
                      float scale = 0.0f, const Tensor* bias = nullptr, vrhino::AttentionObservation* obs = nullptr) override {
         return rt_->attention(q, k, v, mask, causal, scale, bias, obs);
     }
     Tensor conv3d(const Tensor& x, const Tensor& w, const Tensor* b, const std::vector<int>& s, const std::vector<int>& p,
                   const std::vector<int>& d = {1, 1, 1}, int g = 1) override { return rt_->conv3d(x, w, b, s, p, d, g); }
-    Tensor pad(const Tensor& x, const std::vector<int64_t>& p, float v = 0.0f, vrhino::PadMode m = vrhino::PadMode::Constant) override { return rt_->pad(x, p, v, m); }
     Tensor reduce_sum(const Tensor& x, int64_t d, bool k = false) override { return rt_->reduce_sum(x, d, k); }
     Tensor softmax(const Tensor& x, int64_t a) override { return rt_->softmax(x, a); }
     Tensor conv2d(const Tensor& x, const Tensor& w, const Tensor* b, const std::vector<int>& s, const std::vector<int>& p,

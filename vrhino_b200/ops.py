@@ -228,6 +228,107 @@ class B200Backend:
              ctypes.c_float(eps), _stream())
         return out
 
+    # ---- layout operators (cuda_backend.cu:3936-3970, :4190-4196, :4875-4883) ----
+    @staticmethod
+    def _extents(values):
+        return (ctypes.c_int64 * max(len(values), 1))(*[int(v) for v in values])
+
+    def permute(self, raw, dims, out=None):
+        """CudaBackend::permute: out[c] = x[c permuted back]; "Invalid permutation" unless dims permutes the axes."""
+        if len(dims) != raw.dim():
+            raise VrbError("permute rank mismatch")
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        if sorted(int(d) for d in dims) != list(range(x.dim())):
+            raise VrbError("Invalid permutation")
+        out = _result(out, tuple(x.shape[int(d)] for d in dims), dtype, x.device)
+        call("vrb_permute", _ptr(x), _ptr(out), _code(dtype), x.dim(), self._extents(x.shape), self._extents(dims), _stream())
+        return out
+
+    def slice(self, raw, dim, start, stop, out=None):
+        """CudaBackend::slice: negative dim / start / stop count from the end, then start is clamped into
+        [0, extent] and stop into [start, extent]."""
+        if dim < 0:
+            dim += raw.dim()
+        if not 0 <= dim < raw.dim():
+            raise VrbError("slice dimension invalid")
+        size = raw.shape[dim]
+        start = start + size if start < 0 else start
+        stop = stop + size if stop < 0 else stop
+        start = min(max(start, 0), size)
+        stop = min(max(stop, start), size)
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        shape = list(x.shape)
+        shape[dim] = stop - start
+        out = _result(out, tuple(shape), dtype, x.device)
+        call("vrb_slice", _ptr(x), _ptr(out), _code(dtype), x.dim(), self._extents(x.shape), dim, start, stop, _stream())
+        return out
+
+    def split(self, x, sections, dim):
+        """CudaBackend::split (cuda_backend.cu:3972-3976): consecutive slices."""
+        if dim < 0:
+            dim += x.dim()
+        if sum(sections) != x.shape[dim]:
+            raise VrbError("split sections mismatch")
+        parts, offset = [], 0
+        for section in sections:
+            parts.append(self.slice(x, dim, offset, offset + section))
+            offset += section
+        return parts
+
+    def concat(self, tensors, dim, out=None):
+        """CudaBackend::concat: the dtype is the first input's (a device F32 / BF16 tensor) else the execution dtype."""
+        if not tensors:
+            raise VrbError("concat requires inputs")
+        rank = tensors[0].dim()
+        if dim < 0:
+            dim += rank
+        if not 0 <= dim < rank:
+            raise VrbError("concat dimension invalid")
+        shape = list(tensors[0].shape)
+        shape[dim] = 0
+        for t in tensors:
+            if t.dim() != rank:
+                raise VrbError("concat rank mismatch")
+            if any(t.shape[d] != tensors[0].shape[d] for d in range(rank) if d != dim):
+                raise VrbError("concat shape mismatch")
+            shape[dim] += t.shape[dim]
+        dtype = self._dtype_of(tensors[0])
+        parts = [_dense(self.copy_to_device(t, dtype)) for t in tensors]
+        out = _result(out, tuple(shape), dtype, parts[0].device)
+        pointers = (ctypes.c_void_p * len(parts))(*[_ptr(t).value for t in parts])
+        call("vrb_concat", pointers, self._extents([t.shape[dim] for t in parts]), len(parts), _ptr(out), _code(dtype), rank,
+             self._extents(shape), dim, _stream())
+        return out
+
+    def pad(self, raw, padding, value=0.0, replicate=False, out=None):
+        """CudaBackend::pad: `padding` is (before, after) pairs from the innermost axis outwards."""
+        if len(padding) % 2 or len(padding) > 2 * raw.dim():
+            raise VrbError("Invalid pad vector")
+        if any(p < 0 for p in padding):
+            raise VrbError("Negative padding unsupported")
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        before, after = [0] * x.dim(), [0] * x.dim()
+        for pair in range(len(padding) // 2):
+            before[x.dim() - 1 - pair], after[x.dim() - 1 - pair] = int(padding[2 * pair]), int(padding[2 * pair + 1])
+        out = _result(out, tuple(s + b + a for s, b, a in zip(x.shape, before, after)), dtype, x.device)
+        call("vrb_pad", _ptr(x), _ptr(out), _code(dtype), x.dim(), self._extents(x.shape), self._extents(before), self._extents(after),
+             ctypes.c_float(value), int(bool(replicate)), _stream())
+        return out
+
+    def sinusoidal_embedding(self, raw, width, flip, downscale, frequency_f64, out=None):
+        """CudaBackend::sinusoidal_embedding: positions [n] -> [n, width]."""
+        if raw.dim() != 1 or width <= 0:
+            raise VrbError("sinusoidal embedding contract violation")
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        out = _result(out, (x.numel(), width), dtype, x.device)
+        call("vrb_sinusoidal_embedding", _ptr(x), _ptr(out), _code(dtype), x.numel(), width, int(bool(flip)),
+             ctypes.c_double(downscale), int(bool(frequency_f64)), _stream())
+        return out
+
     def pixel_shuffle_nd(self, raw, factors, out=None):
         """CudaBackend::pixel_shuffle_nd (native/src/backend/cuda/cuda_backend.cu:5112-5118)."""
         if raw.dim() != 5 or len(factors) != 3:

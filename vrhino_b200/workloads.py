@@ -458,9 +458,51 @@ class WanVaeRmsChannel:
         return [Launch("rms_channel", plain, n), Launch("rms_channel silu", silu, n)]
 
 
+class LayoutOps:
+    """The layout operators at the sizes the video paths call them with: the Wan patch embedding's transposition
+    [1, 1536, 32760] -> [1, 32760, 1536] (native/src/architectures/wan.cpp:159), Mochi's frames-first permute of a VAE
+    feature map and its channels-last permute (mochi.cpp:368, :384), LTX's causal replicate padding of the time axis and
+    its spatial zero padding (ltx.cpp:210-214), SwiGLU's two halves as slices (mochi.cpp:197-198) and a concat along the
+    channel axis.  Algorithmic bytes: what is read + what is written."""
+
+    def __init__(self, be, frames=8, dtype=BF16, seed=0):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        self.be = be
+        self.patches = _randn((1, 1536, 32760), dtype, g)
+        self.feature = _randn((1, 128, frames, 256, 384), dtype, g)
+        self.proj = _randn((1, 8192, 16384), dtype, g)
+        self.out = {}
+
+    def launches(self) -> List[Launch]:
+        be, o = self.be, self.out
+        size = lambda t: t.numel() * t.element_size()
+        f = self.feature
+        b, c, t, h, w = f.shape
+        padded_t = size(f) * (t + 4) // t
+        padded_hw = size(f) * ((h + 2) * (w + 2)) // (h * w)
+
+        def transpose(): o["tokens"] = be.permute(self.patches, (0, 2, 1), out=o.get("tokens"))
+        def frames_first(): o["frames"] = be.permute(f, (0, 2, 1, 3, 4), out=o.get("frames"))
+        def channels_last(): o["last"] = be.permute(f, (0, 2, 3, 4, 1), out=o.get("last"))
+        def causal(): o["causal"] = be.pad(f, [0, 0, 0, 0, 2, 2], 0.0, True, out=o.get("causal"))
+        def spatial(): o["spatial"] = be.pad(f, [1, 1, 1, 1], 0.0, False, out=o.get("spatial"))
+        def half(): o["half"] = be.slice(self.proj, 2, 8192, 16384, out=o.get("half"))
+        def joined(): o["joined"] = be.concat([f, f], 1, out=o.get("joined"))
+
+        return [
+            Launch("permute tokens<->channels", transpose, 2 * size(self.patches)),
+            Launch("permute frames first", frames_first, 2 * size(f)),
+            Launch("permute channels last", channels_last, 2 * size(f)),
+            Launch("pad time replicate", causal, size(f) + padded_t),
+            Launch("pad H, W zero", spatial, size(f) + padded_hw),
+            Launch("slice second half", half, size(self.proj)),
+            Launch("concat channels (2 launches)", joined, 4 * size(f)),
+        ]
+
+
 def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, batch=1):
     """The launch list of headline configuration 2..5 (optionally at a reduced token / frame count),
-    or of the additional measurement configurations 6..9."""
+    or of the additional measurement configurations 6..13."""
     if config == 2:
         t = tokens or 32760
         return WanBlock(be, tokens=t, grid=(21, 30, 52) if t == 32760 else (1, 1, t), hidden_dtype=hidden_dtype, batch=batch)
@@ -482,6 +524,8 @@ def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, b
         return LtxDepthToSpace(be, shape=(1, 256, frames or 16, 128, 192), dtype=hidden_dtype)
     if config == 12:
         return WanVaeRmsChannel(be, shape=(1, 192, frames or 4, 240, 416), dtype=hidden_dtype)
+    if config == 13:
+        return LayoutOps(be, frames=frames or 8, dtype=hidden_dtype)
     raise ValueError("config must be 2..12 (6 = config 5 as a pre-permuted per-frame tensor, 7 = per-frame statistics "
                      "on the unpermuted [N,C,T,H,W] tensor, 8 = linear epilogues merged with their consumers, "
                      "9 = the same as separate launches, 10 = LTX VAE pixel_norm -> modulate -> SiLU, "
@@ -490,7 +534,7 @@ def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, b
 
 def _main():
     """python -m vrhino_b200.workloads [--config C] [--tokens N] [--frames T] [--only PREFIX]
-    [--repeat R] [--hidden bf16|f32] [--batch B] [--fuse-residual-norm]
+    [--repeat R] [--hidden bf16|f32] [--batch B] [--fuse-residual-norm] [--pair-qk] [--merge-tail]
 
     Runs (selected) launches of one configuration a few times and prints their device times; a
     small, self-contained command for profilers."""
@@ -505,11 +549,15 @@ def _main():
     ap.add_argument("--batch", type=int, default=1, help="config 2: CFG branches batched into one tensor")
     ap.add_argument("--fuse-residual-norm", action="store_true",
                     help="config 2: residual update + following LayerNorm as one launch (9 launches per block)")
+    ap.add_argument("--pair-qk", action="store_true", help="config 2: q and k RMSNorm+RoPE as one launch")
+    ap.add_argument("--merge-tail", action="store_true", help="Mochi: residual update + next pre-norm as one launch")
     a = ap.parse_args()
     be = ops.B200Backend()
     work = build_config(be, a.config, tokens=a.tokens, hidden_dtype=BF16 if a.hidden == "bf16" else F32, frames=a.frames,
                         batch=a.batch)
-    listed = work.launches(fuse_residual_norm=True) if a.fuse_residual_norm else work.launches()
+    chosen = {k: True for k, on in (("fuse_residual_norm", a.fuse_residual_norm), ("pair_qk", a.pair_qk),
+                                          ("merge_tail", a.merge_tail)) if on}
+    listed = work.launches(**chosen)
     launches = [l for l in listed if l.name.startswith(a.only)]
     total, per = time_launches(launches, steps=a.repeat, warmup=1)
     for l in launches:
