@@ -164,6 +164,13 @@ int vrb_concat(const void* const* inputs, const int64_t* extents, int count, voi
 int vrb_pad(const void* x, void* out, int dtype, int rank, const int64_t* shape, const int64_t* before,
             const int64_t* after, float value, int replicate, vrb_stream stream);
 
+/* Two pads of the reference in one pass: per axis d, replicate_axes[d] != 0 replicates, 0 fills with `value`; an
+ * element outside the source along ANY constant-mode axis holds `value`, as if the replicate axes had been padded
+ * first and the constant axes afterwards.  That is LTX's edge_time_conv (native/src/architectures/ltx.cpp:205-215):
+ * pad(x, {0,0,0,0,t,t}, 0, Replicate) followed by pad(., {w,w,h,h}, 0) before every convolution. */
+int vrb_pad_axes(const void* x, void* out, int dtype, int rank, const int64_t* shape, const int64_t* before,
+                 const int64_t* after, float value, const int* replicate_axes, vrb_stream stream);
+
 /* CudaBackend::sinusoidal_embedding (:4190-4196, sinusoidal_kernel :1178-1198): positions [count] ->
  * out [count, width].  half = width / 2; logical column l = flip ? (column + half) % (2 half) : column;
  * out = (l < half ? sin : cos)(position * exp(-ln(10000) * (l % half) / (half - downscale))); an odd last

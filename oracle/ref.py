@@ -344,7 +344,7 @@ class RefDropin(RefCuda):
                      "refd_group_norm_silu", "refd_cfg_euler", "refd_gated_residual_layer_norm",
                      "refd_linear_activation", "refd_linear_gated_residual", "refd_linear_swiglu",
                      "refd_pixel_norm_modulate_silu", "refd_depth_to_space_residual", "refd_profile_report",
-                     "refd_dequantize_repeated", "refd_release_cached", "refd_rms_norm_rope_pair", "refd_mochi_residual_norm"):
+                     "refd_dequantize_repeated", "refd_release_cached", "refd_rms_norm_rope_pair", "refd_mochi_residual_norm", "refd_edge_time_pad"):
             getattr(self.lib, name).restype = _c.c_int64
 
     def profile(self, enabled): self.lib.refc_profile(int(enabled))
@@ -404,6 +404,8 @@ class RefDropin(RefCuda):
     def fused_pixel_norm_modulate_silu(self, policy, x, shift, scale, eps=1e-8, out_dtype=F32):
         return self._h(self.lib.refd_pixel_norm_modulate_silu(int(policy), self._i(x), self._i(shift), self._i(scale),
                                                               _c.c_float(eps), int(out_dtype)))
+    def fused_edge_time_pad(self, x, temporal, pad_h, pad_w):
+        return self._h(self.lib.refd_edge_time_pad(self._i(x), _c.c_int64(temporal), _c.c_int64(pad_h), _c.c_int64(pad_w)))
     def fused_depth_to_space_residual(self, projected, x):
         return self._h(self.lib.refd_depth_to_space_residual(self._i(projected), self._i(x)))
     def fused_swiglu(self, x): return self._h(self.lib.refd_swiglu(self._i(x)))

@@ -317,6 +317,9 @@ int64_t refd_pixel_norm_modulate_silu(int policy, int64_t x, int64_t shift, int6
                                                           static_cast<DType>(out_dtype)));
     });
 }
+int64_t refd_edge_time_pad(int64_t x, int64_t temporal, int64_t pad_h, int64_t pad_w) {
+    return guarded([&] { return keep(vrhino_b200::edge_time_pad(*g_backend, at(x), temporal, pad_h, pad_w)); });
+}
 int64_t refd_depth_to_space_residual(int64_t projected, int64_t input) {
     return guarded([&] { return keep(vrhino_b200::depth_to_space_residual(*g_backend, at(projected), at(input))); });
 }

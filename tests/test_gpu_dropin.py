@@ -174,6 +174,25 @@ def test_fused_call_site_forms(orc, golden, dropin, case):
         rd.clear()
 
 
+def test_edge_time_pad_call_site(orc, dropin):
+    """vrhino_b200::edge_time_pad on the replaced backend (one pass) against the reference's CUDA backend running
+    LTX's two pads (ltx.cpp:210-214), bit for bit."""
+    from oracle import ref
+    from vrhino_b200 import synth
+    if not ref.available_cuda():
+        pytest.skip("reference CUDA library not built")
+    shape = (1, 8, 3, 6, 16)
+    bits = cases.to_bits(synth.normal(shape, seed=41), "bf16")
+    rc = ref.RefCuda()
+    want = rc.pad(rc.pad(rc.upload(bits, ref.BF16), [0, 0, 0, 0, 1, 1], 0.0, True), [1, 1, 1, 1], 0.0, False)
+    want_bits, _ = rc.download(want, (1, 8, 5, 8, 18))
+    rc.clear()
+    got = dropin.fused_edge_time_pad(dropin.upload(bits, ref.BF16), 1, 1, 1)
+    got_bits, dt = dropin.download(got, (1, 8, 5, 8, 18))
+    dropin.clear()
+    assert dt == ref.BF16 and np.array_equal(got_bits, want_bits)
+
+
 @pytest.mark.parametrize("hidden", ["bf16", "f32"])
 def test_graph_fusion_pass(orc, dropin, hidden):
     """The non-GEMM part of the Wan self-attention graph (the reference's node sequence, q / k / the

@@ -68,6 +68,38 @@ def test_quotient_guards_at_extreme_exponents(orc, gpu, l2):
     assert same.all(), f"positions {sorted(set(np.argwhere(~same)[:, 1].tolist()))} differ"
 
 
+def test_bf16_store_silu_over_every_f32_argument(gpu):
+    """pixel_norm -> modulate -> SiLU with a bf16 result evaluates SiLU through approximate special functions wherever
+    the bf16 rounding provably cannot differ, else exactly.  All 2^32 F32 arguments go through the kernel here: with
+    x = 0 and scale = 0 the SiLU argument of channel c is shift[c] bit for bit, and the result must be the bf16
+    rounding of the exact expression (vrb_activation on F32, then vrb_cast)."""
+    import torch
+    be, ops = gpu
+    outer, channels, inner, per_call = 32768, 2048, 8, 1 << 26
+    x = torch.zeros(outer, channels, 1, 1, inner, device="cuda", dtype=torch.bfloat16)
+    scale = torch.zeros(outer, channels, 1, 1, 1, device="cuda")
+    index = torch.arange(per_call, device="cuda", dtype=torch.int64)
+    out = torch.empty_like(x)
+    mismatches, examples = 0, []
+    for call in range((1 << 32) // per_call):
+        bits = index + call * per_call
+        bits = torch.where(bits >= (1 << 31), bits - (1 << 32), bits).to(torch.int32)
+        v = bits.view(torch.float32)
+        got = ops.fused_pixel_norm_modulate(be, x, v.view(outer, channels, 1, 1, 1), scale, 1e-8, out_dtype=torch.bfloat16, out=out)
+        # the kernel's argument is 0 * 1 + shift: -0 arrives as +0 (every other argument unchanged)
+        want = be.cast(be.activation(v + 0.0, ops.SILU), torch.bfloat16).view(outer, channels)
+        g = got.view(outer, channels, inner).view(torch.int16)
+        w = want.view(torch.int16)
+        wrong = (g[:, :, 0] != w) | (g[:, :, inner - 1] != w)
+        count = int(wrong.sum())
+        if count:
+            mismatches += count
+            at = wrong.view(-1).nonzero().view(-1)[:4]
+            examples += [(hex(int(bits[i]) & 0xFFFFFFFF), hex(int(g[:, :, 0].reshape(-1)[i]) & 0xFFFF), hex(int(w.reshape(-1)[i]) & 0xFFFF))
+                         for i in at.tolist()]
+    assert mismatches == 0, f"{mismatches} arguments round to another bf16 value, e.g. (argument, got, want) {examples[:8]}"
+
+
 @pytest.mark.parametrize("shape", [s for s in SHAPES if len(s) == 5])
 @pytest.mark.parametrize("dt", ["bf16", "f32"])
 def test_pixel_norm_modulate_silu(orc, gpu, shape, dt):

@@ -44,6 +44,8 @@ __device__ __forceinline__ Unit unit_of(const uint4& fill) {
 }
 
 // RANK > 0: the number of dimensions is a compile-time constant; RANK == 0: any rank up to kMaxDims.
+// replicate: bit d set = positions outside the source along dimension d take the nearest source element,
+// clear = they (and the whole element) take the fill value.
 template <typename Unit, int RANK, bool PAD, typename Index>
 __global__ void __launch_bounds__(kThreads) walk_kernel(const Unit* __restrict__ in, Unit* __restrict__ out, const Walk w,
                                                         const uint4 fill, const int replicate) {
@@ -80,7 +82,7 @@ __global__ void __launch_bounds__(kThreads) walk_kernel(const Unit* __restrict__
                     if constexpr (PAD) {
                         from -= w.before[d];
                         if (from < 0 || from >= w.in_extent[d]) {
-                            valid = valid && replicate != 0;
+                            valid = valid && ((replicate >> d) & 1) != 0;
                             from = from < 0 ? 0 : w.in_extent[d] - 1;
                         }
                     }
@@ -93,6 +95,114 @@ __global__ void __launch_bounds__(kThreads) walk_kernel(const Unit* __restrict__
 #pragma unroll
         for (int k = 0; k < kUnroll; ++k)
             if (target[k] >= 0) out[target[k]] = value[k];
+    }
+}
+
+// Element units with a contiguous, 16-byte aligned output: a thread produces 16 adjacent output bytes (8 bf16 / 4 F32
+// elements).  The first element's index is decomposed once; its neighbours differ in the innermost coordinate only,
+// until a row ends (then the next index is decomposed again).  One 16-byte store per chunk instead of one
+// decomposition, one load and one 2- or 4-byte store per element: the padded innermost axes of a spatial pad, a slice
+// at an odd offset, a permute whose innermost axes are short.
+template <typename E, bool PAD, typename Index>
+__global__ void __launch_bounds__(kThreads) walk_chunks_kernel(const E* __restrict__ in, E* __restrict__ out, const Walk w,
+                                                               const uint4 fill, const int replicate) {
+    constexpr int K = 16 / sizeof(E);
+    pdl_launch_dependents();
+    pdl_wait();
+    const int last = w.rank - 1;
+    const Index extent_last = static_cast<Index>(w.extent[last]);
+    const int64_t stride_last = w.in_stride[last];
+    const int64_t before_last = PAD ? w.before[last] : 0, in_extent_last = PAD ? w.in_extent[last] : w.extent[last];
+    const bool replicate_last = ((replicate >> last) & 1) != 0;
+    const E fill_value = unit_of<E>(fill);
+    const int64_t chunks = (w.total + K - 1) / K;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * kThreads;
+    for (int64_t chunk = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; chunk < chunks; chunk += step) {
+        const int64_t first = chunk * K;
+        Index inner = 0;
+        int64_t outer_source = 0;
+        bool outer_valid = true;
+        // coordinates of element `index`: the innermost one in `inner`, the others folded into the source offset
+        auto locate = [&](int64_t at) {
+            const Index index = static_cast<Index>(at);
+            Index remaining = index / extent_last;
+            inner = index - remaining * extent_last;
+            outer_source = 0;
+            outer_valid = true;
+            for (int d = last - 1; d >= 0; --d) {
+                int64_t from = static_cast<int64_t>(remaining);
+                if (d > 0) {
+                    const Index extent = static_cast<Index>(w.extent[d]);
+                    const Index quotient = remaining / extent;
+                    from = static_cast<int64_t>(remaining - quotient * extent);
+                    remaining = quotient;
+                }
+                if constexpr (PAD) {
+                    from -= w.before[d];
+                    if (from < 0 || from >= w.in_extent[d]) {
+                        outer_valid = outer_valid && ((replicate >> d) & 1) != 0;
+                        from = from < 0 ? 0 : w.in_extent[d] - 1;
+                    }
+                }
+                outer_source += from * w.in_stride[d];
+            }
+        };
+        locate(first);
+        if (stride_last == 1 && outer_valid && first + K <= w.total && static_cast<int64_t>(inner) >= before_last) {
+            // a run of K adjacent source elements inside one source row: aligned 32-bit loads, shifted by half a word
+            // when the run starts at an odd 2-byte element (that form also reads the element after the run, so the run
+            // must end before its row does)
+            const E* const run = in + outer_source + (static_cast<int64_t>(inner) - before_last);
+            const uintptr_t address = reinterpret_cast<uintptr_t>(run);
+            const int odd = sizeof(E) == 2 && (address & 2) != 0 ? 1 : 0;
+            if (static_cast<int64_t>(inner) + K + odd <= before_last + in_extent_last) {
+                uint4 packed;
+                if constexpr (sizeof(E) == 4) {
+                    packed = make_uint4(run[0], run[1], run[2], run[3]);
+                } else {
+                    const uint32_t* const words = reinterpret_cast<const uint32_t*>(address & ~uintptr_t{3});
+                    const uint32_t w0 = words[0], w1 = words[1], w2 = words[2], w3 = words[3];
+                    if (!odd) {
+                        packed = make_uint4(w0, w1, w2, w3);
+                    } else {
+                        const uint32_t w4 = words[4];
+                        packed = make_uint4(__funnelshift_r(w0, w1, 16), __funnelshift_r(w1, w2, 16), __funnelshift_r(w2, w3, 16),
+                                            __funnelshift_r(w3, w4, 16));
+                    }
+                }
+                reinterpret_cast<uint4*>(out)[chunk] = packed;
+                continue;
+            }
+        }
+        E value[K];
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+            value[k] = fill_value;
+            if (first + k < w.total) {
+                int64_t from = static_cast<int64_t>(inner) - before_last;
+                bool valid = outer_valid;
+                if constexpr (PAD) {
+                    if (from < 0 || from >= in_extent_last) {
+                        valid = valid && replicate_last;
+                        from = from < 0 ? 0 : in_extent_last - 1;
+                    }
+                }
+                if (valid) value[k] = in[outer_source + from * stride_last];
+                if (++inner == extent_last && k + 1 < K) locate(first + k + 1);
+            }
+        }
+        if (first + K <= w.total) {
+            uint4 packed;
+            if constexpr (sizeof(E) == 2) {
+                packed = make_uint4(value[0] | (static_cast<uint32_t>(value[1]) << 16), value[2] | (static_cast<uint32_t>(value[3]) << 16),
+                                    value[4] | (static_cast<uint32_t>(value[5]) << 16), value[6] | (static_cast<uint32_t>(value[7]) << 16));
+            } else {
+                packed = make_uint4(value[0], value[1], value[2], value[3]);
+            }
+            reinterpret_cast<uint4*>(out)[chunk] = packed;
+        } else {
+            for (int k = 0; first + k < w.total; ++k) out[first + k] = value[k];
+        }
     }
 }
 
@@ -114,13 +224,21 @@ __global__ void __launch_bounds__(kThreads) transpose_kernel(const E* __restrict
     pdl_wait();
     const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
     for (int64_t t = blockIdx.x; t < g.tiles; t += gridDim.x) {
-        int64_t remaining = t;
-        const int64_t tile_b = remaining % g.tiles_b; remaining /= g.tiles_b;
-        const int64_t tile_a = remaining % g.tiles_a; remaining /= g.tiles_a;
+        // fewer than 2^31 tiles (the launcher checks): 32-bit divisions
+        uint32_t remaining = static_cast<uint32_t>(t);
+        const uint32_t tiles_b = static_cast<uint32_t>(g.tiles_b), tiles_a = static_cast<uint32_t>(g.tiles_a);
+        uint32_t quotient = remaining / tiles_b;
+        const int64_t tile_b = remaining - quotient * tiles_b;
+        remaining = quotient;
+        quotient = remaining / tiles_a;
+        const int64_t tile_a = remaining - quotient * tiles_a;
+        remaining = quotient;
         int64_t in_base = 0, out_base = 0;
         for (int d = g.batch_rank - 1; d >= 0; --d) {
-            const int64_t coordinate = remaining % g.batch_extent[d];
-            remaining /= g.batch_extent[d];
+            const uint32_t extent = static_cast<uint32_t>(g.batch_extent[d]);
+            quotient = remaining / extent;
+            const int64_t coordinate = remaining - quotient * extent;
+            remaining = quotient;
             in_base += coordinate * g.batch_in_stride[d];
             out_base += coordinate * g.batch_out_stride[d];
         }
@@ -139,10 +257,81 @@ __global__ void __launch_bounds__(kThreads) transpose_kernel(const E* __restrict
     }
 }
 
+// 2-byte elements with even extents, strides and offsets: the tile is moved as 32-bit words.  A thread loads the
+// words (a, a+1) of rows b and b+1, transposes the 2 x 2 block in registers (two byte permutes) and stores the words
+// (b, b+1) of rows a and a+1 into the tile, rows of even and odd a in separate halves so that the stores of a warp
+// fall into 32 different banks; the tile is then written out row by row, 8 bytes per thread.  2 memory instructions
+// per element instead of 4, and every global access is a full 32-byte sector.
+__global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
+                                                                   const Transpose g) {
+    constexpr int TILE = 64, HALF = TILE / 2, PITCH = HALF + 1;   // words per tile row: 32 b-pairs + 1
+    __shared__ uint32_t tile[TILE * PITCH];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+    for (int64_t t = blockIdx.x; t < g.tiles; t += gridDim.x) {
+        // fewer than 2^31 tiles (the launcher checks): 32-bit divisions
+        uint32_t remaining = static_cast<uint32_t>(t);
+        const uint32_t tiles_b = static_cast<uint32_t>(g.tiles_b), tiles_a = static_cast<uint32_t>(g.tiles_a);
+        uint32_t quotient = remaining / tiles_b;
+        const int64_t tile_b = remaining - quotient * tiles_b;
+        remaining = quotient;
+        quotient = remaining / tiles_a;
+        const int64_t tile_a = remaining - quotient * tiles_a;
+        remaining = quotient;
+        int64_t in_base = 0, out_base = 0;
+        for (int d = g.batch_rank - 1; d >= 0; --d) {
+            const uint32_t extent = static_cast<uint32_t>(g.batch_extent[d]);
+            quotient = remaining / extent;
+            const int64_t coordinate = remaining - quotient * extent;
+            remaining = quotient;
+            in_base += coordinate * g.batch_in_stride[d];
+            out_base += coordinate * g.batch_out_stride[d];
+        }
+        const int64_t a0 = tile_a * TILE, b0 = tile_b * TILE;
+        in_base += a0 + b0 * g.in_stride_b;          // elements; even
+        out_base += a0 * g.out_stride_a + b0;
+        // load: lane = pair of a, warp + 8 i = pair of b
+        const bool a_inside = a0 + 2 * lane < g.extent_a;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int pair_b = warp + 8 * i;
+            if (a_inside && b0 + 2 * pair_b < g.extent_b) {
+                const int64_t at = in_base + static_cast<int64_t>(2 * pair_b) * g.in_stride_b + 2 * lane;
+                const uint32_t row0 = in[at >> 1], row1 = in[(at + g.in_stride_b) >> 1];
+                tile[lane * PITCH + pair_b] = __byte_perm(row0, row1, 0x5410);             // a even: x(b, a), x(b + 1, a)
+                tile[(HALF + lane) * PITCH + pair_b] = __byte_perm(row0, row1, 0x7632);    // a odd
+            }
+        }
+        __syncthreads();
+        // store: 16 threads cover the 32 words of one output row, two words each; the two half-warps take adjacent
+        // tile rows (an odd pitch apart: no bank conflict)
+        const int word = 2 * (threadIdx.x % 16);
+        const bool first_inside = b0 + 2 * word < g.extent_b, second_inside = b0 + 2 * word + 2 < g.extent_b;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int tile_row = threadIdx.x / 16 + 16 * i;
+            const int a = tile_row < HALF ? 2 * tile_row : 2 * (tile_row - HALF) + 1;
+            if (first_inside && a0 + a < g.extent_a) {
+                const uint32_t w0 = tile[tile_row * PITCH + word], w1 = tile[tile_row * PITCH + word + 1];
+                const int64_t at = (out_base + static_cast<int64_t>(a) * g.out_stride_a) / 2 + word;
+                if (second_inside && (at & 1) == 0) {
+                    *reinterpret_cast<uint2*>(out + at) = make_uint2(w0, w1);
+                } else {
+                    out[at] = w0;
+                    if (second_inside) out[at + 1] = w1;
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------------
 struct Plan {
     int rank = 0;
     int64_t extent[kMaxDims]{}, in_stride[kMaxDims]{}, out_stride[kMaxDims]{}, in_extent[kMaxDims]{}, before[kMaxDims]{};
+    bool replicate[kMaxDims]{};              // pad: how positions outside the source along the dimension are filled
     int64_t in_offset = 0, out_offset = 0;   // elements
     bool padded = false;
     bool is_padded(int d) const { return before[d] != 0 || in_extent[d] != extent[d]; }
@@ -168,6 +357,7 @@ Plan simplified(const Plan& p) {
         }
         q.extent[q.rank] = p.extent[d]; q.in_extent[q.rank] = p.in_extent[d]; q.before[q.rank] = p.before[d];
         q.in_stride[q.rank] = p.in_stride[d]; q.out_stride[q.rank] = p.out_stride[d];
+        q.replicate[q.rank] = p.replicate[d];
         ++q.rank;
     }
     if (q.rank == 0) { q.rank = 1; q.extent[0] = q.in_extent[0] = 1; q.in_stride[0] = q.out_stride[0] = 1; }
@@ -209,13 +399,15 @@ void launch_walk_unit(const void* in, void* out, const Walk& w, bool padded, con
 bool multiple_of(int64_t value, int64_t unit) { return value % unit == 0; }
 
 // Runs a simplified plan: the walk in the widest unit that fits, or transposition tiles.
-int run_plan(const void* in, void* out, int dtype, const Plan& raw, float pad_value, int replicate, cudaStream_t stream,
-             const char* what) {
+int run_plan(const void* in, void* out, int dtype, const Plan& raw, float pad_value, cudaStream_t stream, const char* what) {
     const Plan p = simplified(raw);
+    int replicate = 0;
+    for (int d = 0; d < p.rank; ++d) replicate |= p.replicate[d] ? 1 << d : 0;
     const int64_t element = static_cast<int64_t>(dtype_bytes(dtype));
     int64_t count = 1;
     for (int d = 0; d < p.rank; ++d) count *= p.extent[d];
     if (count == 0) return VRB_OK;
+    VRB_REQUIRE(in && out, VRB_ERR_INVALID, "%s: null tensor", what);
     const char* source = static_cast<const char*>(in) + p.in_offset * element;
     char* destination = static_cast<char*>(out) + p.out_offset * element;
     const int last = p.rank - 1;
@@ -226,7 +418,7 @@ int run_plan(const void* in, void* out, int dtype, const Plan& raw, float pad_va
         int a = -1;
         for (int d = 0; d < last; ++d)
             if (p.in_stride[d] == 1) a = d;
-        if (a >= 0 && p.extent[a] >= 16 && p.extent[last] >= 16) {
+        if (a >= 0 && p.extent[a] >= 16 && p.extent[last] >= 16 && count / 256 < (int64_t{1} << 31)) {
             Transpose g{};
             for (int d = 0; d < last; ++d) {
                 if (d == a) continue;
@@ -240,7 +432,13 @@ int run_plan(const void* in, void* out, int dtype, const Plan& raw, float pad_va
             g.tiles = g.tiles_a * g.tiles_b;
             for (int d = 0; d < g.batch_rank; ++d) g.tiles *= g.batch_extent[d];
             const int grid = grid_for(g.tiles, kPerSm);
-            if (element == 2)
+            bool pairs = element == 2 && g.extent_a % 2 == 0 && g.extent_b % 2 == 0 && g.in_stride_b % 2 == 0 && g.out_stride_a % 2 == 0 &&
+                         reinterpret_cast<uintptr_t>(source) % 4 == 0 && reinterpret_cast<uintptr_t>(destination) % 4 == 0;
+            for (int d = 0; d < g.batch_rank && pairs; ++d) pairs = g.batch_in_stride[d] % 2 == 0 && g.batch_out_stride[d] % 2 == 0;
+            if (pairs)
+                launch_overlapped(transpose_pairs_kernel, dim3(grid), dim3(kThreads), 0, stream, reinterpret_cast<const uint32_t*>(source),
+                                  reinterpret_cast<uint32_t*>(destination), g);
+            else if (element == 2)
                 launch_overlapped(transpose_kernel<uint16_t, 64>, dim3(grid), dim3(kThreads), 0, stream,
                                   reinterpret_cast<const uint16_t*>(source), reinterpret_cast<uint16_t*>(destination), g);
             else
@@ -283,6 +481,33 @@ int run_plan(const void* in, void* out, int dtype, const Plan& raw, float pad_va
         memcpy(&pattern, &pad_value, 4);
     }
     const uint4 fill = make_uint4(pattern, pattern, pattern, pattern);
+    bool contiguous_output = aligned16(destination) && count >= 64;
+    {
+        int64_t running = 1;
+        for (int d = last; d >= 0 && contiguous_output; --d) {
+            contiguous_output = p.out_stride[d] == running;
+            running *= p.extent[d];
+        }
+    }
+    if (unit == element && contiguous_output) {
+        const int64_t chunks = (count * element + 15) / 16;
+        const int grid = grid_for((chunks + kThreads - 1) / kThreads, kPerSm);
+        const bool wide = count + 16 >= (int64_t{1} << 32);
+#define VRB_CHUNKS(E, PAD, INDEX)                                                                                          \
+    launch_overlapped(walk_chunks_kernel<E, PAD, INDEX>, dim3(grid), dim3(kThreads), 0, stream, reinterpret_cast<const E*>(source), \
+                      reinterpret_cast<E*>(destination), w, fill, replicate)
+        if (element == 2) {
+            if (wide) { if (p.padded) VRB_CHUNKS(uint16_t, true, int64_t); else VRB_CHUNKS(uint16_t, false, int64_t); }
+            else if (p.padded) VRB_CHUNKS(uint16_t, true, uint32_t);
+            else VRB_CHUNKS(uint16_t, false, uint32_t);
+        } else {
+            if (wide) { if (p.padded) VRB_CHUNKS(uint32_t, true, int64_t); else VRB_CHUNKS(uint32_t, false, int64_t); }
+            else if (p.padded) VRB_CHUNKS(uint32_t, true, uint32_t);
+            else VRB_CHUNKS(uint32_t, false, uint32_t);
+        }
+#undef VRB_CHUNKS
+        return after_launch(what);
+    }
     if (unit == 16) launch_walk_unit<uint4>(source, destination, w, p.padded, fill, replicate, stream);
     else if (unit == 4) launch_walk_unit<uint32_t>(source, destination, w, p.padded, fill, replicate, stream);
     else launch_walk_unit<uint16_t>(source, destination, w, p.padded, fill, replicate, stream);
@@ -346,7 +571,6 @@ using namespace vrb;
 
 extern "C" int vrb_permute(const void* x, void* out, int dtype, int rank, const int64_t* shape, const int64_t* dims,
                            vrb_stream stream) {
-    VRB_REQUIRE(x && out, VRB_ERR_INVALID, "permute: null tensor");
     VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "permute: dtype must be F32 or BF16");
     VRB_REQUIRE(valid_shape(rank, shape) && (rank == 0 || dims), VRB_ERR_INVALID, "permute rank mismatch");
     bool seen[kMaxDims] = {};
@@ -361,12 +585,11 @@ extern "C" int vrb_permute(const void* x, void* out, int dtype, int rank, const 
         p.in_stride[d] = strides[dims[d]];
     }
     contiguous_strides(rank, p.extent, p.out_stride);
-    return run_plan(x, out, dtype, p, 0.0f, 0, as_stream(stream), "permute");
+    return run_plan(x, out, dtype, p, 0.0f, as_stream(stream), "permute");
 }
 
 extern "C" int vrb_slice(const void* x, void* out, int dtype, int rank, const int64_t* shape, int dim, int64_t start, int64_t stop,
                          vrb_stream stream) {
-    VRB_REQUIRE(x && out, VRB_ERR_INVALID, "slice: null tensor");
     VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "slice: dtype must be F32 or BF16");
     VRB_REQUIRE(valid_shape(rank, shape) && rank > 0, VRB_ERR_INVALID, "slice: invalid shape");
     if (dim < 0) dim += rank;
@@ -382,20 +605,19 @@ extern "C" int vrb_slice(const void* x, void* out, int dtype, int rank, const in
     for (int d = 0; d < rank; ++d) p.extent[d] = p.in_extent[d] = d == dim ? stop - start : shape[d];
     contiguous_strides(rank, p.extent, p.out_stride);
     p.in_offset = start * p.in_stride[dim];
-    return run_plan(x, out, dtype, p, 0.0f, 0, as_stream(stream), "slice");
+    return run_plan(x, out, dtype, p, 0.0f, as_stream(stream), "slice");
 }
 
 extern "C" int vrb_concat(const void* const* inputs, const int64_t* extents, int count, void* out, int dtype, int rank,
                           const int64_t* shape, int dim, vrb_stream stream) {
     VRB_REQUIRE(count > 0 && inputs && extents, VRB_ERR_INVALID, "concat requires inputs");
-    VRB_REQUIRE(out, VRB_ERR_INVALID, "concat: null output");
     VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "concat: dtype must be F32 or BF16");
     VRB_REQUIRE(valid_shape(rank, shape) && rank > 0, VRB_ERR_INVALID, "concat: invalid shape");
     if (dim < 0) dim += rank;
     VRB_REQUIRE(dim >= 0 && dim < rank, VRB_ERR_INVALID, "concat dimension invalid");
     int64_t sum = 0;
     for (int k = 0; k < count; ++k) {
-        VRB_REQUIRE(inputs[k] && extents[k] >= 0, VRB_ERR_INVALID, "concat: null input or negative extent");
+        VRB_REQUIRE(extents[k] >= 0, VRB_ERR_INVALID, "concat: negative extent");
         sum += extents[k];
     }
     VRB_REQUIRE(sum == shape[dim], VRB_ERR_INVALID, "concat shape mismatch");
@@ -411,46 +633,60 @@ extern "C" int vrb_concat(const void* const* inputs, const int64_t* extents, int
         }
         contiguous_strides(rank, p.extent, p.in_stride);
         p.out_offset = offset * out_strides[dim];
-        const int status = run_plan(inputs[k], out, dtype, p, 0.0f, 0, as_stream(stream), "concat");
+        const int status = run_plan(inputs[k], out, dtype, p, 0.0f, as_stream(stream), "concat");
         if (status != VRB_OK) return status;
         offset += extents[k];
     }
     return VRB_OK;
 }
 
-extern "C" int vrb_pad(const void* x, void* out, int dtype, int rank, const int64_t* shape, const int64_t* before,
-                       const int64_t* after, float value, int replicate, vrb_stream stream) {
-    VRB_REQUIRE(x && out, VRB_ERR_INVALID, "pad: null tensor");
+namespace {
+int pad_any(const void* x, void* out, int dtype, int rank, const int64_t* shape, const int64_t* before, const int64_t* after,
+            float value, const int* replicate_axes, int replicate_all, cudaStream_t stream) {
     VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "pad: dtype must be F32 or BF16");
     VRB_REQUIRE(valid_shape(rank, shape) && rank > 0 && before && after, VRB_ERR_INVALID, "Invalid pad vector");
     Plan p;
     p.rank = rank;
     contiguous_strides(rank, shape, p.in_stride);
     int64_t source_count = 1;
+    bool any_replicate = false;
     for (int d = 0; d < rank; ++d) {
         VRB_REQUIRE(before[d] >= 0 && after[d] >= 0, VRB_ERR_INVALID, "Negative padding unsupported");
         p.in_extent[d] = shape[d];
         p.before[d] = before[d];
         p.extent[d] = shape[d] + before[d] + after[d];
+        p.replicate[d] = replicate_axes ? replicate_axes[d] != 0 : replicate_all != 0;
+        any_replicate = any_replicate || (p.replicate[d] && p.extent[d] != shape[d]);
         source_count *= shape[d];
     }
-    // an empty source has nothing to replicate from: the clamp of the kernel this replaces would read
-    // element -1; refuse it instead
-    VRB_REQUIRE(source_count > 0 || !replicate, VRB_ERR_INVALID, "pad: replicate padding of an empty tensor");
+    // an empty source has nothing to replicate from (the clamp of the kernel this replaces would read element -1)
+    VRB_REQUIRE(source_count > 0 || !any_replicate, VRB_ERR_INVALID, "pad: replicate padding of an empty tensor");
     if (source_count == 0) {
         // constant padding of an empty tensor: every output element is the pad value
-        for (int d = 0; d < rank; ++d) { p.in_extent[d] = 1; p.before[d] = p.extent[d]; p.in_stride[d] = 0; }
+        for (int d = 0; d < rank; ++d) { p.in_extent[d] = 1; p.before[d] = p.extent[d]; p.in_stride[d] = 0; p.replicate[d] = false; }
     }
     contiguous_strides(rank, p.extent, p.out_stride);
-    return run_plan(x, out, dtype, p, value, replicate, as_stream(stream), "pad");
+    return run_plan(x, out, dtype, p, value, stream, "pad");
+}
+}  // namespace
+
+extern "C" int vrb_pad(const void* x, void* out, int dtype, int rank, const int64_t* shape, const int64_t* before,
+                       const int64_t* after, float value, int replicate, vrb_stream stream) {
+    return pad_any(x, out, dtype, rank, shape, before, after, value, nullptr, replicate, as_stream(stream));
+}
+
+extern "C" int vrb_pad_axes(const void* x, void* out, int dtype, int rank, const int64_t* shape, const int64_t* before,
+                            const int64_t* after, float value, const int* replicate_axes, vrb_stream stream) {
+    VRB_REQUIRE(replicate_axes, VRB_ERR_INVALID, "pad: null mode array");
+    return pad_any(x, out, dtype, rank, shape, before, after, value, replicate_axes, 0, as_stream(stream));
 }
 
 extern "C" int vrb_sinusoidal_embedding(const void* positions, void* out, int dtype, int64_t count, int64_t width, int flip,
                                         double downscale, int frequency_f64, vrb_stream stream) {
-    VRB_REQUIRE(positions && out, VRB_ERR_INVALID, "sinusoidal_embedding: null tensor");
     VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "sinusoidal_embedding: dtype must be F32 or BF16");
     VRB_REQUIRE(count >= 0 && width > 0 && width < (int64_t{1} << 30), VRB_ERR_INVALID, "sinusoidal embedding contract violation");
     if (count == 0) return VRB_OK;
+    VRB_REQUIRE(positions && out, VRB_ERR_INVALID, "sinusoidal_embedding: null tensor");
     const int64_t total = count * width;
     const int grid = grid_for((total + kThreads - 1) / kThreads, kPerSm);
     if (dtype == VRB_BF16)

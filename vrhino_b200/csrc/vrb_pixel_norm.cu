@@ -95,15 +95,33 @@ __device__ __forceinline__ float quotient_of_bf16(float x, float d, float r) {
     return corrected;
 }
 
+// SiLU of an F32 value whose result is STORED AS bf16.  v / (1 + expf(-v)) costs two range-reduced special
+// functions and an IEEE division per element (four XU-pipe operations), which bounds the modulate + SiLU kernels.
+// The approximate form below (ex2.approx, rcp.approx: two XU operations) is within a few F32 ulp of it for
+// |v| <= 16, so both round to the same bf16 unless the approximation's low 16 bits lie within kSiluGuardUlps of
+// the rounding boundary 0x8000; those elements (1 in 1000), larger arguments and NaN evaluate the exact
+// expression.  The returned F32 value differs from the exact one, its bf16 rounding does not:
+// tests/test_gpu_pixel_norm.py drives all 2^32 arguments through the kernel against the exact expression.
+constexpr int kSiluGuardUlps = 32;
+__device__ __forceinline__ float silu_for_bf16_store(float v) {
+    float t, inverse;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(t) : "f"(__fmul_rn(v, -1.4426950408889634f)));
+    asm("rcp.approx.f32 %0, %1;" : "=f"(inverse) : "f"(__fadd_rn(1.0f, t)));
+    const float fast = __fmul_rn(v, inverse);
+    const int low = static_cast<int>(__float_as_uint(fast) & 0xffffu) - 0x8000;
+    if (!(fabsf(v) <= 16.0f) || abs(low) <= kSiluGuardUlps) return activation_value(VRB_SILU, v);
+    return fast;
+}
+
 // One normalised element to the stored value with everything known at compile time.
-template <bool X_BF16, int MODE>
+template <bool X_BF16, int MODE, bool OUT_BF16>
 __device__ __forceinline__ float finish_tile(float x, float denominator, float reciprocal, float one_plus_scale, float shift) {
     float v;
     if constexpr (X_BF16) v = quotient_of_bf16(x, denominator, reciprocal);
     else v = __fdiv_rn(x, denominator);
     if constexpr (X_BF16 && MODE != kNormOnly) v = round_to_bf16(v);   // kNormOnly: the bf16 store rounds
     if constexpr (MODE != kNormOnly) v = __fadd_rn(__fmul_rn(v, one_plus_scale), shift);
-    if constexpr (MODE == kModulateSilu) v = activation_value(VRB_SILU, v);
+    if constexpr (MODE == kModulateSilu) v = OUT_BF16 ? silu_for_bf16_store(v) : activation_value(VRB_SILU, v);
     return v;
 }
 
@@ -189,9 +207,26 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
         }
         __syncthreads();
         const int64_t out_chunk0 = o * p.channels * inner_chunks + chunk0;
-        for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads) {
-            const int c = idx >> cols_log2, k = idx & (cols - 1);
-            if (k >= valid) continue;
+        // a thread's chunks all lie in one chunk column (the block size is a multiple of cols): its positions'
+        // denominators and reciprocals are read from shared memory once per tile, not once per chunk
+        const int k = threadIdx.x & (cols - 1);
+        float d[EPC], r[EPC];
+        {
+            const float4* d4 = reinterpret_cast<const float4*>(denominator + k * EPC);
+            const float4* r4 = reinterpret_cast<const float4*>(reciprocal + k * EPC);
+            const float4 da = d4[0];
+            d[0] = da.x; d[1] = da.y; d[2] = da.z; d[3] = da.w;
+            if constexpr (X_BF16) {
+                const float4 db = d4[1], ra = r4[0], rb = r4[1];
+                d[4] = db.x; d[5] = db.y; d[6] = db.z; d[7] = db.w;
+                r[0] = ra.x; r[1] = ra.y; r[2] = ra.z; r[3] = ra.w; r[4] = rb.x; r[5] = rb.y; r[6] = rb.z; r[7] = rb.w;
+            } else {
+#pragma unroll
+                for (int j = 0; j < EPC; ++j) r[j] = 0.0f;
+            }
+        }
+        for (int idx = threadIdx.x; idx < tile_chunks && k < valid; idx += kThreads) {
+            const int c = idx >> cols_log2;
             float ops = 1.0f, sh = 0.0f;
             if constexpr (MODE != kNormOnly) {
                 const int64_t at = o * p.channels + c;
@@ -200,19 +235,13 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
             }
             const uint4 raw = tile[idx];
             const int64_t chunk = out_chunk0 + static_cast<int64_t>(c) * inner_chunks + k;   // in units of EPC elements
-            const float4* d4 = reinterpret_cast<const float4*>(denominator + k * EPC);
             if constexpr (X_BF16) {
-                const float4 da = d4[0], db = d4[1];
-                const float4* r4 = reinterpret_cast<const float4*>(reciprocal + k * EPC);
-                const float4 ra = r4[0], rb = r4[1];
-                const float d[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
-                const float r[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
                 const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
                 float v[8];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    v[2 * j] = finish_tile<true, MODE>(__uint_as_float(w[j] << 16), d[2 * j], r[2 * j], ops, sh);
-                    v[2 * j + 1] = finish_tile<true, MODE>(__uint_as_float(w[j] & 0xffff0000u), d[2 * j + 1], r[2 * j + 1], ops, sh);
+                    v[2 * j] = finish_tile<true, MODE, OUT_BF16>(__uint_as_float(w[j] << 16), d[2 * j], r[2 * j], ops, sh);
+                    v[2 * j + 1] = finish_tile<true, MODE, OUT_BF16>(__uint_as_float(w[j] & 0xffff0000u), d[2 * j + 1], r[2 * j + 1], ops, sh);
                 }
                 if constexpr (MODE == kNormOnly || OUT_BF16) {
                     __stcs(static_cast<uint4*>(p.out) + chunk, make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
@@ -221,12 +250,10 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
                     store8(p.out, VRB_F32, static_cast<int64_t>(chunk) * 8, v);
                 }
             } else {
-                const float4 da = d4[0];
-                const float d[4] = {da.x, da.y, da.z, da.w};
                 const float in[4] = {__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w)};
                 float v[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = finish_tile<false, MODE>(in[j], d[j], 0.0f, ops, sh);
+                for (int j = 0; j < 4; ++j) v[j] = finish_tile<false, MODE, OUT_BF16>(in[j], d[j], r[j], ops, sh);
                 if constexpr (MODE != kNormOnly && OUT_BF16) {
                     __stcs(static_cast<uint2*>(p.out) + chunk, make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3])));
                 } else {
@@ -438,14 +465,18 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
         }
         __syncthreads();
         const int64_t out_chunk0 = o * p.channels * inner_chunks + chunk0;
-        for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads) {
-            const int c = idx >> cols_log2, k = idx & (cols - 1);
-            if (k >= valid) continue;
+        // a thread's chunks all lie in one chunk column: its positions' inverses are read once per tile
+        const int k = threadIdx.x & (cols - 1);
+        const float4* i4 = reinterpret_cast<const float4*>(inverse + k * EPC);
+        const float4 ia = i4[0];
+        float4 ib = ia;
+        if constexpr (X_BF16) ib = i4[1];
+        for (int idx = threadIdx.x; idx < tile_chunks && k < valid; idx += kThreads) {
+            const int c = idx >> cols_log2;
             const bool weighted = p.weight != nullptr;
             const float w = weighted ? round_to(X_DT, load1(p.weight, p.w_dt, c)) : 1.0f;
             const uint4 raw = tile[idx];
             const int64_t chunk = out_chunk0 + static_cast<int64_t>(c) * inner_chunks + k;
-            const float4* i4 = reinterpret_cast<const float4*>(inverse + k * EPC);
             auto finish_one = [&](float v, float inv) {
                 float y = __fmul_rn(v, inv);
                 if constexpr (X_BF16) y = round_to_bf16(y);
@@ -463,7 +494,6 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
                 return y;
             };
             if constexpr (X_BF16) {
-                const float4 ia = i4[0], ib = i4[1];
                 const float inv[8] = {ia.x, ia.y, ia.z, ia.w, ib.x, ib.y, ib.z, ib.w};
                 const uint32_t wd[4] = {raw.x, raw.y, raw.z, raw.w};
                 float v[8];
@@ -475,7 +505,6 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
                 __stcs(static_cast<uint4*>(p.out) + chunk, make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
                                                                       pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])));
             } else {
-                const float4 ia = i4[0];
                 __stcs(static_cast<float4*>(p.out) + chunk,
                        make_float4(finish_one(__uint_as_float(raw.x), ia.x), finish_one(__uint_as_float(raw.y), ia.y),
                                    finish_one(__uint_as_float(raw.z), ia.z), finish_one(__uint_as_float(raw.w), ia.w)));

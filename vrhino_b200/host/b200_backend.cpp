@@ -558,6 +558,28 @@ Tensor B200Backend::pad(const Tensor& raw, const std::vector<int64_t>& padding, 
     });
 }
 
+Tensor B200Backend::pad_axes(const Tensor& raw, const std::vector<int64_t>& before, const std::vector<int64_t>& after, float value,
+                             const std::vector<bool>& replicate) {
+    return guarded([&] {
+        const size_t rank = static_cast<size_t>(raw.ndim());
+        require(before.size() == rank && after.size() == rank && replicate.size() == rank, "Invalid pad vector");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype);
+        std::vector<int64_t> shape = x.shape();
+        std::vector<int> modes(rank);
+        for (size_t d = 0; d < rank; ++d) {
+            require(before[d] >= 0 && after[d] >= 0, "Negative padding unsupported");
+            shape[d] += before[d] + after[d];
+            modes[d] = replicate[d] ? 1 : 0;
+        }
+        Tensor out = rt_->allocate_device(shape, dtype);
+        ProfileRegion region(*this, [] { return std::string("fused.pad"); }, bytes_of(x) + bytes_of(out));
+        check(vrb_pad_axes(x.data(), out.data(), code(dtype), static_cast<int>(rank), x.shape().data(), before.data(), after.data(), value,
+                           modes.data(), kLegacyStream));
+        return out;
+    });
+}
+
 Tensor B200Backend::pixel_shuffle_nd(const Tensor& raw, const std::vector<int64_t>& factors) {
     return guarded([&] {   // VRHINO_PROFILE("pixel_shuffle") carries the failure guard (cuda_backend.cu:5114)
         require(raw.ndim() == 5 && factors.size() == 3, "pixel_shuffle_nd requires 5D and 3 factors");
@@ -1015,6 +1037,15 @@ Tensor pixel_norm_modulate_silu(vrhino::Backend& backend, const vrhino::Precisio
     Tensor y = backend.activation(vrhino::modulate(backend, policy, backend.pixel_norm(x, 1, eps), shift, scale),
                                   vrhino::Activation::Silu);
     return y.dtype() == output ? y : backend.cast(y, output);
+}
+
+Tensor edge_time_pad(vrhino::Backend& backend, const Tensor& x, int64_t temporal, int64_t pad_h, int64_t pad_w) {
+    if (auto* b200 = dynamic_cast<B200Backend*>(&backend); b200 && x.ndim() == 5 && (temporal > 0 || pad_h > 0 || pad_w > 0))
+        return b200->pad_axes(x, {0, 0, temporal, pad_h, pad_w}, {0, 0, temporal, pad_h, pad_w}, 0.0f, {false, false, true, false, false});
+    Tensor padded = x;   // the reference's two calls (ltx.cpp:210-214)
+    if (temporal) padded = backend.pad(padded, {0, 0, 0, 0, temporal, temporal}, 0.0f, vrhino::PadMode::Replicate);
+    if (pad_h > 0 || pad_w > 0) padded = backend.pad(padded, {pad_w, pad_w, pad_h, pad_h}, 0.0f);
+    return padded;
 }
 
 Tensor depth_to_space_residual(vrhino::Backend& backend, const Tensor& projected, const Tensor& input) {

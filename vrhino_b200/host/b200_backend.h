@@ -69,6 +69,9 @@ public:
                                 bool require_f64_semantics) override;
     Tensor pad(const Tensor& x, const std::vector<int64_t>& padding, float value = 0.0f,
                vrhino::PadMode mode = vrhino::PadMode::Constant) override;
+    // per-axis extents and modes in one pass (replicate axes first, then the constant axes)
+    Tensor pad_axes(const Tensor& x, const std::vector<int64_t>& before, const std::vector<int64_t>& after, float value,
+                    const std::vector<bool>& replicate);
 
     // ---- fused forms (one kernel each); see the free functions below for the call-site view --
     Tensor layer_norm_modulate(const Tensor& x, const Tensor* weight, const Tensor* bias, float eps,
@@ -283,6 +286,9 @@ vrhino::Tensor pixel_norm_modulate_silu(vrhino::Backend& backend, const vrhino::
 // LTX depth_to_space (ltx.cpp:250-259) after its convolution `projected` = edge_time_conv(input): the two
 // pixel_shuffles, the four-fold concat, the two slices and the add as one kernel
 vrhino::Tensor depth_to_space_residual(vrhino::Backend& backend, const vrhino::Tensor& projected, const vrhino::Tensor& input);
+// pad(pad(x, {0,0,0,0,temporal,temporal}, 0, Replicate), {pad_w,pad_w,pad_h,pad_h}, 0) on x [B, C, T, H, W]: the two
+// pads in front of every LTX convolution (edge_time_conv, ltx.cpp:205-215) as one pass
+vrhino::Tensor edge_time_pad(vrhino::Backend& backend, const vrhino::Tensor& x, int64_t temporal, int64_t pad_h, int64_t pad_w);
 // mul(parts[0], silu(parts[1])), parts = split(projected, {H, H}, -1)   (mochi.cpp:195-202)
 vrhino::Tensor swiglu(vrhino::Backend& backend, const vrhino::Tensor& projected);
 // activation(group_norm(x, groups, weight, bias, eps), Silu)   (autoencoder_kl.cpp:31-41)

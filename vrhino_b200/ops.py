@@ -318,6 +318,20 @@ class B200Backend:
              ctypes.c_float(value), int(bool(replicate)), _stream())
         return out
 
+    def pad_axes(self, raw, before, after, value, replicate_axes, out=None):
+        """vrb_pad_axes: per-axis before / after extents and per-axis mode (True replicates, False fills with value)."""
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        if not (len(before) == len(after) == len(replicate_axes) == x.dim()):
+            raise VrbError("Invalid pad vector")
+        if any(p < 0 for p in list(before) + list(after)):
+            raise VrbError("Negative padding unsupported")
+        out = _result(out, tuple(s + b + a for s, b, a in zip(x.shape, before, after)), dtype, x.device)
+        modes = (ctypes.c_int * x.dim())(*[int(bool(m)) for m in replicate_axes])
+        call("vrb_pad_axes", _ptr(x), _ptr(out), _code(dtype), x.dim(), self._extents(x.shape), self._extents(before),
+             self._extents(after), ctypes.c_float(value), modes, _stream())
+        return out
+
     def sinusoidal_embedding(self, raw, width, flip, downscale, frequency_f64, out=None):
         """CudaBackend::sinusoidal_embedding: positions [n] -> [n, width]."""
         if raw.dim() != 1 or width <= 0:
@@ -783,6 +797,12 @@ def fused_pixel_norm_modulate(be, x, shift, scale, eps=1e-8, silu=True, out_dtyp
     call("vrb_pixel_norm", _ptr(x), _code(x), _ptr(_dense(scale)), _ptr(_dense(shift)), _code(scale), int(bool(silu)),
          _ptr(out), _code(out_dtype), x.shape[0], channels, inner, ctypes.c_float(eps), _stream())
     return out
+
+
+def fused_edge_time_pad(be, x, temporal, pad_h, pad_w, out=None):
+    """The two pads in front of every LTX convolution (edge_time_conv, native/src/architectures/ltx.cpp:205-215) in one
+    pass: replicate `temporal` frames at both ends of T, then zeros around H and W, on x [B, C, T, H, W]."""
+    return be.pad_axes(x, [0, 0, temporal, pad_h, pad_w], [0, 0, temporal, pad_h, pad_w], 0.0, [False, False, True, False, False], out=out)
 
 
 def fused_depth_to_space_residual(be, projected, x, out=None):
