@@ -61,6 +61,7 @@ SLICES = [
     ((1, 20, 64), 2, 0, 32), ((1, 20, 64), 2, 32, 64), ((1, 20, 64), 2, 3, 10), ((2, 9, 24), 1, 2, 7), ((2, 9, 24), 0, 1, 2),
     ((2, 9, 24), -1, -5, 100), ((2, 9, 24), 1, -100, 3), ((2, 9, 24), 1, 4, 4), ((2, 9, 24), 2, 30, 40), ((5, 6, 12), 2, 4, 12),
     ((3, 4, 5, 6, 7, 2, 3, 4), 4, 2, 6), ((64,), 0, 8, 24),
+    ((4, 300), 1, 3, 250), ((2, 3, 1000), 2, 1, 999), ((5, 129), 1, 0, 65),      # long rows at odd offsets: a warp per row
 ]
 
 
@@ -110,6 +111,9 @@ PADS = [
     ((2, 3, 2, 5, 7), (1, 0, 1, 0, 1, 0, 1, 0, 1, 0), 2.0, False),   # every axis: run-time rank
     ((1, 2), (1, 2), 0.0, True),
     ((6, 40), (0, 8), 1.0, False),                           # inner axis by a multiple of the unit
+    ((2, 3, 70), (3, 2), -2.5, False),                       # long padded rows: a warp per row
+    ((2, 3, 70), (3, 2, 1, 1), 0.0, True),
+    ((1, 2, 3, 130), (1, 0, 0, 0, 2, 1), 0.25, False),
     ((2, 3, 5), (0, 0), 0.0, False),                         # nothing to do
     ((2, 3, 5), (), 0.0, False),
 ]

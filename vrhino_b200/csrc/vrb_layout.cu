@@ -62,8 +62,11 @@ __global__ void __launch_bounds__(kThreads) walk_kernel(const Unit* __restrict__
             const Index index = base + static_cast<Index>(k) * stride;
             target[k] = -1;
             if (index < total) {
+                // Index == uint32_t: every offset on either side fits 31 bits (the launcher checks), so the address
+                // arithmetic is 32-bit as well
+                using Offset = typename std::conditional<sizeof(Index) == 4, int32_t, int64_t>::type;
                 Index remaining = index;
-                int64_t source = 0, destination = 0;
+                Offset source = 0, destination = 0;
                 bool valid = true;
 #pragma unroll
                 for (int d = (RANK > 0 ? RANK : kMaxDims) - 1; d >= 0; --d) {
@@ -77,16 +80,16 @@ __global__ void __launch_bounds__(kThreads) walk_kernel(const Unit* __restrict__
                         coordinate = remaining - quotient * extent;
                         remaining = quotient;
                     }
-                    destination += static_cast<int64_t>(coordinate) * w.out_stride[d];
-                    int64_t from = static_cast<int64_t>(coordinate);
+                    destination += static_cast<Offset>(coordinate) * static_cast<Offset>(w.out_stride[d]);
+                    Offset from = static_cast<Offset>(coordinate);
                     if constexpr (PAD) {
-                        from -= w.before[d];
-                        if (from < 0 || from >= w.in_extent[d]) {
+                        from -= static_cast<Offset>(w.before[d]);
+                        if (from < 0 || from >= static_cast<Offset>(w.in_extent[d])) {
                             valid = valid && ((replicate >> d) & 1) != 0;
-                            from = from < 0 ? 0 : w.in_extent[d] - 1;
+                            from = from < 0 ? 0 : static_cast<Offset>(w.in_extent[d]) - 1;
                         }
                     }
-                    source += from * w.in_stride[d];
+                    source += from * static_cast<Offset>(w.in_stride[d]);
                 }
                 target[k] = destination;
                 value[k] = valid ? in[source] : unit_of<Unit>(fill);
@@ -95,6 +98,76 @@ __global__ void __launch_bounds__(kThreads) walk_kernel(const Unit* __restrict__
 #pragma unroll
         for (int k = 0; k < kUnroll; ++k)
             if (target[k] >= 0) out[target[k]] = value[k];
+    }
+}
+
+// Element units with long innermost rows: a warp takes one row of the iteration space at a time, decomposes the row
+// index once, and its lanes move the row's elements with coalesced 2- or 4-byte loads and stores (four in flight per
+// lane).  Whatever the alignment of either side, every access of a warp is one contiguous segment: the form for a
+// pad of the innermost axes and for a slice at an odd offset.
+template <typename E, bool PAD>
+__global__ void __launch_bounds__(kThreads) walk_rows_kernel(const E* __restrict__ in, E* __restrict__ out, const Walk w,
+                                                             const uint4 fill, const int replicate, const uint32_t rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int last = w.rank - 1;
+    const int lane = threadIdx.x % 32;
+    const uint32_t warps = gridDim.x * (kThreads / 32);
+    const int extent_last = static_cast<int>(w.extent[last]);
+    const int before_last = PAD ? static_cast<int>(w.before[last]) : 0;
+    const int in_extent_last = PAD ? static_cast<int>(w.in_extent[last]) : extent_last;
+    const int64_t in_stride_last = w.in_stride[last], out_stride_last = w.out_stride[last];
+    const bool replicate_last = ((replicate >> last) & 1) != 0;
+    const E fill_value = unit_of<E>(fill);
+    for (uint32_t row = blockIdx.x * (kThreads / 32) + threadIdx.x / 32; row < rows; row += warps) {
+        uint32_t remaining = row;
+        int64_t source = 0, destination = 0;
+        bool row_valid = true;
+        for (int d = last - 1; d >= 0; --d) {
+            uint32_t coordinate = remaining;
+            if (d > 0) {
+                const uint32_t extent = static_cast<uint32_t>(w.extent[d]);
+                const uint32_t quotient = remaining / extent;
+                coordinate = remaining - quotient * extent;
+                remaining = quotient;
+            }
+            destination += static_cast<int64_t>(coordinate) * w.out_stride[d];
+            int64_t from = coordinate;
+            if constexpr (PAD) {
+                from -= w.before[d];
+                if (from < 0 || from >= w.in_extent[d]) {
+                    row_valid = row_valid && ((replicate >> d) & 1) != 0;
+                    from = from < 0 ? 0 : w.in_extent[d] - 1;
+                }
+            }
+            source += from * w.in_stride[d];
+        }
+        const E* const src = in + source;
+        E* const dst = out + destination;
+        for (int j0 = lane; j0 < extent_last; j0 += 32 * kUnroll) {
+            E value[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int j = j0 + 32 * u;
+                value[u] = fill_value;
+                if (j < extent_last) {
+                    int from = j - before_last;
+                    bool valid = row_valid;
+                    if constexpr (PAD) {
+                        if (from < 0 || from >= in_extent_last) {
+                            valid = valid && replicate_last;
+                            from = from < 0 ? 0 : in_extent_last - 1;
+                        }
+                    }
+                    if (valid) value[u] = src[from * in_stride_last];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int j = j0 + 32 * u;
+                if (j < extent_last) dst[j * out_stride_last] = value[u];
+            }
+        }
     }
 }
 
@@ -369,7 +442,13 @@ template <typename Unit, int RANK, bool PAD>
 void launch_walk(const void* in, void* out, const Walk& w, const uint4& fill, int replicate, cudaStream_t stream) {
     const int64_t per_block = static_cast<int64_t>(kThreads) * kUnroll;
     const int grid = grid_for((w.total + per_block - 1) / per_block, kPerSm);
-    const bool wide = w.total + static_cast<int64_t>(grid) * per_block >= (int64_t{1} << 31);
+    int64_t reach_in = 0, reach_out = 0;   // largest offsets on either side, in units
+    for (int d = 0; d < w.rank; ++d) {
+        reach_in += ((PAD ? w.in_extent[d] : w.extent[d]) - 1) * w.in_stride[d];
+        reach_out += (w.extent[d] - 1) * w.out_stride[d];
+    }
+    const int64_t limit = int64_t{1} << 31;
+    const bool wide = w.total + static_cast<int64_t>(grid) * per_block >= limit || reach_in >= limit || reach_out >= limit;
     if (wide)
         launch_overlapped(walk_kernel<Unit, 0, PAD, int64_t>, dim3(grid), dim3(kThreads), 0, stream, static_cast<const Unit*>(in),
                           static_cast<Unit*>(out), w, fill, replicate);
@@ -488,6 +567,18 @@ int run_plan(const void* in, void* out, int dtype, const Plan& raw, float pad_va
             contiguous_output = p.out_stride[d] == running;
             running *= p.extent[d];
         }
+    }
+    if (unit == element && p.in_stride[last] == 1 && p.out_stride[last] == 1 && p.extent[last] >= 64 && p.extent[last] < (int64_t{1} << 30) &&
+        count / p.extent[last] < (int64_t{1} << 31)) {
+        const uint32_t rows = static_cast<uint32_t>(count / p.extent[last]);
+        const int grid = grid_for((static_cast<int64_t>(rows) + kThreads / 32 - 1) / (kThreads / 32), kPerSm);
+#define VRB_ROWS(E, PAD)                                                                                                      \
+    launch_overlapped(walk_rows_kernel<E, PAD>, dim3(grid), dim3(kThreads), 0, stream, reinterpret_cast<const E*>(source), \
+                      reinterpret_cast<E*>(destination), w, fill, replicate, rows)
+        if (element == 2) { if (p.padded) VRB_ROWS(uint16_t, true); else VRB_ROWS(uint16_t, false); }
+        else { if (p.padded) VRB_ROWS(uint32_t, true); else VRB_ROWS(uint32_t, false); }
+#undef VRB_ROWS
+        return after_launch(what);
     }
     if (unit == element && contiguous_output) {
         const int64_t chunks = (count * element + 15) / 16;

@@ -82,54 +82,67 @@ enum Mode { kNormOnly = 0, kModulate = 1, kModulateSilu = 2 };
 // pairs are enumerated by tests/test_reciprocal_division.py -- and scaling x or d by a power of two
 // changes nothing as long as x, d, r, q and e stay normal.  reciprocal_or_zero() therefore hands out r
 // only for d in [2^-30, 2^30] and 0 otherwise (also for an infinite or NaN d), and a result below
-// 2^-28 in magnitude, or NaN, -- a zero (its sign), a tiny x, or r == 0 -- takes the division.
+// 2^-28 in magnitude, or NaN, -- a zero (its sign), a tiny x, or r == 0 -- is redone with the division.
 constexpr float kReciprocalLow = 9.313225746154785e-10f, kReciprocalHigh = 1073741824.0f;   // 2^-30, 2^30
 constexpr float kQuotientFloor = 3.725290298461914e-09f;                                     // 2^-28
 __device__ __forceinline__ float reciprocal_or_zero(float d) {
     return d >= kReciprocalLow && d <= kReciprocalHigh ? __frcp_rn(d) : 0.0f;
 }
-__device__ __forceinline__ float quotient_of_bf16(float x, float d, float r) {
-    const float q = __fmul_rn(x, r);
-    const float corrected = __fmaf_rn(__fmaf_rn(-d, q, x), r, q);
-    if (!(fabsf(corrected) >= kQuotientFloor)) return __fdiv_rn(x, d);
-    return corrected;
-}
 
 // SiLU of an F32 value whose result is STORED AS bf16.  v / (1 + expf(-v)) costs two range-reduced special
-// functions and an IEEE division per element (four XU-pipe operations), which bounds the modulate + SiLU kernels.
-// The approximate form below (ex2.approx, rcp.approx: two XU operations) is within a few F32 ulp of it for
-// |v| <= 16, so both round to the same bf16 unless the approximation's low 16 bits lie within kSiluGuardUlps of
-// the rounding boundary 0x8000; those elements (1 in 1000), larger arguments and NaN evaluate the exact
-// expression.  The returned F32 value differs from the exact one, its bf16 rounding does not:
-// tests/test_gpu_pixel_norm.py drives all 2^32 arguments through the kernel against the exact expression.
-constexpr int kSiluGuardUlps = 32;
-__device__ __forceinline__ float silu_for_bf16_store(float v) {
+// functions and an IEEE division per element.  The approximate form (ex2.approx, rcp.approx and three F32
+// operations) is within a few F32 ulp of it for |v| <= 8, so both round to the same bf16 unless the
+// approximation's low 16 bits lie within kSiluGuardUlps of the rounding boundary 0x8000; those elements (1 in
+// 3000), larger arguments and NaN are redone with the exact expression.  The F32 value differs from the exact one,
+// its bf16 rounding does not: tests/test_gpu_pixel_norm.py drives all 2^32 arguments through the kernel against
+// the exact expression.  (The flush-to-zero forms are exact here: 1 + t is in [1, 2^24] and a denormal argument
+// gives t = 1 either way.)
+constexpr int kSiluGuardUlps = 10;
+__device__ __forceinline__ float silu_approximate(float v, bool& redo) {
     float t, inverse;
-    asm("ex2.approx.f32 %0, %1;" : "=f"(t) : "f"(__fmul_rn(v, -1.4426950408889634f)));
-    asm("rcp.approx.f32 %0, %1;" : "=f"(inverse) : "f"(__fadd_rn(1.0f, t)));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(__fmul_rn(v, -1.4426950408889634f)));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inverse) : "f"(__fadd_rn(1.0f, t)));
     const float fast = __fmul_rn(v, inverse);
     const int low = static_cast<int>(__float_as_uint(fast) & 0xffffu) - 0x8000;
-    if (!(fabsf(v) <= 16.0f) || abs(low) <= kSiluGuardUlps) return activation_value(VRB_SILU, v);
+    redo = redo || !(fabsf(v) <= 8.0f) || abs(low) <= kSiluGuardUlps;
     return fast;
 }
 
-// One normalised element to the stored value with everything known at compile time.
-template <bool X_BF16, int MODE, bool OUT_BF16>
-__device__ __forceinline__ float finish_tile(float x, float denominator, float reciprocal, float one_plus_scale, float shift) {
+// One normalised element to the stored value, everything known at compile time.  EXACT: the reference's operations
+// one by one.  Otherwise the short forms above where the template arguments allow them, with `redo` set when the
+// element has to be evaluated again with EXACT (the caller does that once per 16-byte chunk, so the common path has
+// one branch per chunk).
+template <bool X_BF16, int MODE, bool OUT_BF16, bool EXACT>
+__device__ __forceinline__ float finish_tile(float x, float denominator, float reciprocal, float one_plus_scale, float shift,
+                                             bool& redo) {
     float v;
-    if constexpr (X_BF16) v = quotient_of_bf16(x, denominator, reciprocal);
-    else v = __fdiv_rn(x, denominator);
+    if constexpr (X_BF16 && !EXACT) {
+        const float q = __fmul_rn(x, reciprocal);
+        v = __fmaf_rn(__fmaf_rn(-denominator, q, x), reciprocal, q);
+        redo = redo || !(fabsf(v) >= kQuotientFloor);
+    } else {
+        v = __fdiv_rn(x, denominator);
+    }
     if constexpr (X_BF16 && MODE != kNormOnly) v = round_to_bf16(v);   // kNormOnly: the bf16 store rounds
     if constexpr (MODE != kNormOnly) v = __fadd_rn(__fmul_rn(v, one_plus_scale), shift);
-    if constexpr (MODE == kModulateSilu) v = OUT_BF16 ? silu_for_bf16_store(v) : activation_value(VRB_SILU, v);
+    if constexpr (MODE == kModulateSilu) {
+        if constexpr (OUT_BF16 && !EXACT) v = silu_approximate(v, redo);
+        else v = activation_value(VRB_SILU, v);
+    }
     return v;
 }
+// whether the short forms exist for a variant (else the first evaluation is already the exact one)
+template <bool X_BF16, int MODE, bool OUT_BF16>
+constexpr bool kHasShortForm = X_BF16 || (MODE == kModulateSilu && OUT_BF16);
 
-// Tile kernel: inner % EPC == 0, 16-byte aligned tensors; `cols` (a power of two) 16-byte chunks per
-// channel.  kNormOnly stores x's dtype; the modulated forms store F32 or (OUT_BF16) bf16.
+// Tile kernel: inner % EPC == 0, 16-byte aligned tensors, fewer than 2^31 tiles and chunks per channel row; `cols` (a
+// power of two, at most 8) 16-byte chunks per channel.  kNormOnly stores x's dtype; the modulated forms store F32 or
+// (OUT_BF16) bf16.  The block size is a multiple of cols, so a thread's chunks all lie in one chunk column k and
+// its channel advances by kThreads / cols per step: addresses are advanced, not recomputed.
 template <bool X_BF16, int MODE, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNormParams p, int cols, int cols_log2) {
     constexpr int EPC = X_BF16 ? 8 : 4;   // elements per 16-byte chunk
+    constexpr int OUT_CHUNK = (MODE == kNormOnly ? X_BF16 : OUT_BF16) ? EPC * 2 : EPC * 4;   // bytes written per chunk
     extern __shared__ __align__(16) uint4 tiles_buffer[];   // two tiles of [channels][cols], then the reduction scratch
     const int channels = static_cast<int>(p.channels);
     const int positions = cols * EPC;
@@ -137,24 +150,25 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
     float* const partial = reinterpret_cast<float*>(tiles_buffer + 2 * static_cast<size_t>(tile_chunks));   // [kLanes][positions]
     float* const denominator = partial + kLanes * positions;                                              // [positions]
     float* const reciprocal = denominator + positions;                                                    // [positions], bf16 input only
-    const int64_t inner_chunks = p.inner / EPC;
-    const int64_t tiles_per_outer = (inner_chunks + cols - 1) / cols;
-    const int64_t tiles = p.outer * tiles_per_outer;
+    const uint32_t inner_chunks = static_cast<uint32_t>(p.inner / EPC);
+    const uint32_t tiles_per_outer = (inner_chunks + cols - 1) >> cols_log2;
+    const uint32_t tiles = static_cast<uint32_t>(p.outer) * tiles_per_outer;
     const float channel_count = static_cast<float>(p.channels);
-    const uint4* const x = static_cast<const uint4*>(p.x);
+    const int k = threadIdx.x & (cols - 1), c0 = threadIdx.x >> cols_log2, c_step = kThreads >> cols_log2;
+    const int64_t row_step = static_cast<int64_t>(c_step) * inner_chunks;   // chunks between a thread's consecutive channels
 
     // asynchronous copy of tile t into buffer b (one committed group per tile and thread)
-    auto request = [&](int64_t t, int b) {
+    auto request = [&](uint32_t t, int b) {
         if (t < tiles) {
-            const int64_t o = t / tiles_per_outer;
-            const int64_t chunk0 = (t - o * tiles_per_outer) * cols;
-            const int valid = static_cast<int>(inner_chunks - chunk0 < cols ? inner_chunks - chunk0 : cols);
-            const uint4* const src = x + o * p.channels * inner_chunks + chunk0;
-            uint4* const dst = tiles_buffer + static_cast<size_t>(b) * tile_chunks;
-            for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads) {
-                const int c = idx >> cols_log2, k = idx & (cols - 1);
-                if (k < valid) async_copy16(dst + idx, src + static_cast<int64_t>(c) * inner_chunks + k);
-                else dst[idx] = make_uint4(0, 0, 0, 0);
+            const uint32_t o = t / tiles_per_outer;
+            const uint32_t chunk0 = (t - o * tiles_per_outer) << cols_log2;
+            const bool inside = chunk0 + k < inner_chunks;
+            const uint4* src = static_cast<const uint4*>(p.x) + (static_cast<int64_t>(o) * channels + c0) * inner_chunks + chunk0 + k;
+            uint4* dst = tiles_buffer + static_cast<size_t>(b) * tile_chunks + threadIdx.x;
+            if (inside) {
+                for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads, src += row_step, dst += kThreads) async_copy16(dst, src);
+            } else {
+                for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads, dst += kThreads) *dst = make_uint4(0, 0, 0, 0);
             }
         }
         async_copy_commit();
@@ -162,21 +176,20 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
 
     int buffer = 0;
     request(blockIdx.x, 0);
-    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, buffer ^= 1) {
-        const int64_t o = t / tiles_per_outer;
-        const int64_t chunk0 = (t - o * tiles_per_outer) * cols;
-        const int valid = static_cast<int>(inner_chunks - chunk0 < cols ? inner_chunks - chunk0 : cols);
+    for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, buffer ^= 1) {
+        const uint32_t o = t / tiles_per_outer;
+        const uint32_t chunk0 = (t - o * tiles_per_outer) << cols_log2;
         const uint4* const tile = tiles_buffer + static_cast<size_t>(buffer) * tile_chunks;
         request(t + gridDim.x, buffer ^ 1);   // the next tile arrives while this one is reduced and written
         async_copy_wait<1>();
         __syncthreads();
         // (lane, position) partial sums in the reference's order; a thread takes the positions of one
-        // 32-bit shared-memory word (two bf16 positions, one F32 position)
+        // 32-bit shared-memory word (two bf16 positions, one F32 position); words is a power of two
         constexpr int PPW = X_BF16 ? 2 : 1;
-        const int words = positions / PPW;
+        const int words_log2 = cols_log2 + 2, words = 1 << words_log2;
         const uint32_t* const tile_words = reinterpret_cast<const uint32_t*>(tile);
         for (int item = threadIdx.x; item < words * kLanes; item += kThreads) {
-            const int lane = item / words, word = item - lane * words;
+            const int lane = item >> words_log2, word = item & (words - 1);
             float q0 = 0.0f, q1 = 0.0f;
             const uint32_t* e = tile_words + lane * words + word;
             const int step = kLanes * words;
@@ -193,8 +206,8 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
                     q0 = __fmaf_rn(v, v, q0);
                 }
             }
-            partial[lane * positions + word * PPW] = q0;
-            if constexpr (X_BF16) partial[lane * positions + word * PPW + 1] = q1;
+            if constexpr (X_BF16) *reinterpret_cast<float2*>(partial + lane * positions + word * 2) = make_float2(q0, q1);
+            else partial[lane * positions + word] = q0;
         }
         __syncthreads();
         if (threadIdx.x < positions) {
@@ -206,58 +219,70 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
             if constexpr (X_BF16) reciprocal[threadIdx.x] = reciprocal_or_zero(d);
         }
         __syncthreads();
-        const int64_t out_chunk0 = o * p.channels * inner_chunks + chunk0;
-        // a thread's chunks all lie in one chunk column (the block size is a multiple of cols): its positions'
-        // denominators and reciprocals are read from shared memory once per tile, not once per chunk
-        const int k = threadIdx.x & (cols - 1);
-        float d[EPC], r[EPC];
-        {
-            const float4* d4 = reinterpret_cast<const float4*>(denominator + k * EPC);
-            const float4* r4 = reinterpret_cast<const float4*>(reciprocal + k * EPC);
-            const float4 da = d4[0];
-            d[0] = da.x; d[1] = da.y; d[2] = da.z; d[3] = da.w;
-            if constexpr (X_BF16) {
-                const float4 db = d4[1], ra = r4[0], rb = r4[1];
-                d[4] = db.x; d[5] = db.y; d[6] = db.z; d[7] = db.w;
-                r[0] = ra.x; r[1] = ra.y; r[2] = ra.z; r[3] = ra.w; r[4] = rb.x; r[5] = rb.y; r[6] = rb.z; r[7] = rb.w;
-            } else {
-#pragma unroll
-                for (int j = 0; j < EPC; ++j) r[j] = 0.0f;
-            }
-        }
-        for (int idx = threadIdx.x; idx < tile_chunks && k < valid; idx += kThreads) {
-            const int c = idx >> cols_log2;
-            float ops = 1.0f, sh = 0.0f;
-            if constexpr (MODE != kNormOnly) {
-                const int64_t at = o * p.channels + c;
-                ops = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, at));
-                sh = load1(p.shift, p.mod_dt, at);
-            }
-            const uint4 raw = tile[idx];
-            const int64_t chunk = out_chunk0 + static_cast<int64_t>(c) * inner_chunks + k;   // in units of EPC elements
-            if constexpr (X_BF16) {
-                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-                float v[8];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    v[2 * j] = finish_tile<true, MODE, OUT_BF16>(__uint_as_float(w[j] << 16), d[2 * j], r[2 * j], ops, sh);
-                    v[2 * j + 1] = finish_tile<true, MODE, OUT_BF16>(__uint_as_float(w[j] & 0xffff0000u), d[2 * j + 1], r[2 * j + 1], ops, sh);
-                }
-                if constexpr (MODE == kNormOnly || OUT_BF16) {
-                    __stcs(static_cast<uint4*>(p.out) + chunk, make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
-                                                                          pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])));
+        if (chunk0 + k < inner_chunks) {
+            // this thread's positions: denominators and reciprocals once per tile
+            float d[EPC], r[EPC];
+            {
+                const float4* d4 = reinterpret_cast<const float4*>(denominator + k * EPC);
+                const float4* r4 = reinterpret_cast<const float4*>(reciprocal + k * EPC);
+                const float4 da = d4[0];
+                d[0] = da.x; d[1] = da.y; d[2] = da.z; d[3] = da.w;
+                if constexpr (X_BF16) {
+                    const float4 db = d4[1], ra = r4[0], rb = r4[1];
+                    d[4] = db.x; d[5] = db.y; d[6] = db.z; d[7] = db.w;
+                    r[0] = ra.x; r[1] = ra.y; r[2] = ra.z; r[3] = ra.w; r[4] = rb.x; r[5] = rb.y; r[6] = rb.z; r[7] = rb.w;
                 } else {
-                    store8(p.out, VRB_F32, static_cast<int64_t>(chunk) * 8, v);
-                }
-            } else {
-                const float in[4] = {__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w)};
-                float v[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = finish_tile<false, MODE, OUT_BF16>(in[j], d[j], r[j], ops, sh);
-                if constexpr (MODE != kNormOnly && OUT_BF16) {
-                    __stcs(static_cast<uint2*>(p.out) + chunk, make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3])));
+                    for (int j = 0; j < EPC; ++j) r[j] = 0.0f;
+                }
+            }
+            const int64_t first = (static_cast<int64_t>(o) * channels + c0) * inner_chunks + chunk0 + k;   // in chunks
+            char* out = static_cast<char*>(p.out) + first * OUT_CHUNK;
+            const int64_t out_step = row_step * OUT_CHUNK;
+            int64_t vector = static_cast<int64_t>(o) * channels + c0;                                     // into scale / shift
+            const uint4* chunk = tile + threadIdx.x;
+            for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads, chunk += kThreads, out += out_step, vector += c_step) {
+                float ops = 1.0f, sh = 0.0f;
+                if constexpr (MODE != kNormOnly) {
+                    ops = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, vector));
+                    sh = load1(p.shift, p.mod_dt, vector);
+                }
+                const uint4 raw = *chunk;
+                float in[EPC], v[EPC];
+                if constexpr (X_BF16) {
+                    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        in[2 * j] = __uint_as_float(w[j] << 16);
+                        in[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+                    }
                 } else {
-                    __stcs(static_cast<float4*>(p.out) + chunk, make_float4(v[0], v[1], v[2], v[3]));
+                    in[0] = __uint_as_float(raw.x); in[1] = __uint_as_float(raw.y); in[2] = __uint_as_float(raw.z); in[3] = __uint_as_float(raw.w);
+                }
+                bool redo = false;
+#pragma unroll
+                for (int j = 0; j < EPC; ++j) v[j] = finish_tile<X_BF16, MODE, OUT_BF16, false>(in[j], d[j], r[j], ops, sh, redo);
+                if constexpr (kHasShortForm<X_BF16, MODE, OUT_BF16>) {
+                    if (redo) {
+                        bool unused = false;
+#pragma unroll
+                        for (int j = 0; j < EPC; ++j) v[j] = finish_tile<X_BF16, MODE, OUT_BF16, true>(in[j], d[j], r[j], ops, sh, unused);
+                    }
+                }
+                if constexpr (X_BF16) {
+                    if constexpr (MODE == kNormOnly || OUT_BF16) {
+                        __stcs(reinterpret_cast<uint4*>(out), make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                                                         pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])));
+                    } else {
+                        store32(out, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3])),
+                                make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7])));
+                    }
+                } else {
+                    if constexpr (MODE != kNormOnly && OUT_BF16) {
+                        __stcs(reinterpret_cast<uint2*>(out), make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3])));
+                    } else {
+                        __stcs(reinterpret_cast<float4*>(out), make_float4(v[0], v[1], v[2], v[3]));
+                    }
                 }
             }
         }
@@ -402,22 +427,24 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
         }
         // visible to every thread after the first barrier of the tile loop
     }
-    const int64_t inner_chunks = p.inner / EPC;
-    const int64_t tiles_per_outer = (inner_chunks + cols - 1) / cols;
-    const int64_t tiles = p.outer * tiles_per_outer;
-    const uint4* const x = static_cast<const uint4*>(p.x);
+    // fewer than 2^31 tiles and chunks per channel row (the launcher checks); a thread's chunks all lie in chunk
+    // column k and its channel advances by kThreads / cols per step, so addresses are advanced, not recomputed
+    const uint32_t inner_chunks = static_cast<uint32_t>(p.inner / EPC);
+    const uint32_t tiles_per_outer = (inner_chunks + cols - 1) >> cols_log2;
+    const uint32_t tiles = static_cast<uint32_t>(p.outer) * tiles_per_outer;
+    const int k = threadIdx.x & (cols - 1), c0 = threadIdx.x >> cols_log2, c_step = kThreads >> cols_log2;
+    const int64_t row_step = static_cast<int64_t>(c_step) * inner_chunks;
 
-    auto request = [&](int64_t t, int b) {
+    auto request = [&](uint32_t t, int b) {
         if (t < tiles) {
-            const int64_t o = t / tiles_per_outer;
-            const int64_t chunk0 = (t - o * tiles_per_outer) * cols;
-            const int valid = static_cast<int>(inner_chunks - chunk0 < cols ? inner_chunks - chunk0 : cols);
-            const uint4* const src = x + o * p.channels * inner_chunks + chunk0;
-            uint4* const dst = tiles_buffer + static_cast<size_t>(b) * tile_chunks;
-            for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads) {
-                const int c = idx >> cols_log2, k = idx & (cols - 1);
-                if (k < valid) async_copy16(dst + idx, src + static_cast<int64_t>(c) * inner_chunks + k);
-                else dst[idx] = make_uint4(0, 0, 0, 0);
+            const uint32_t o = t / tiles_per_outer;
+            const uint32_t chunk0 = (t - o * tiles_per_outer) << cols_log2;
+            const uint4* src = static_cast<const uint4*>(p.x) + (static_cast<int64_t>(o) * channels + c0) * inner_chunks + chunk0 + k;
+            uint4* dst = tiles_buffer + static_cast<size_t>(b) * tile_chunks + threadIdx.x;
+            if (chunk0 + k < inner_chunks) {
+                for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads, src += row_step, dst += kThreads) async_copy16(dst, src);
+            } else {
+                for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads, dst += kThreads) *dst = make_uint4(0, 0, 0, 0);
             }
         }
         async_copy_commit();
@@ -425,19 +452,18 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
 
     int buffer = 0;
     request(blockIdx.x, 0);
-    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, buffer ^= 1) {
-        const int64_t o = t / tiles_per_outer;
-        const int64_t chunk0 = (t - o * tiles_per_outer) * cols;
-        const int valid = static_cast<int>(inner_chunks - chunk0 < cols ? inner_chunks - chunk0 : cols);
+    for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, buffer ^= 1) {
+        const uint32_t o = t / tiles_per_outer;
+        const uint32_t chunk0 = (t - o * tiles_per_outer) << cols_log2;
         const uint4* const tile = tiles_buffer + static_cast<size_t>(buffer) * tile_chunks;
         request(t + gridDim.x, buffer ^ 1);
         async_copy_wait<1>();
         __syncthreads();
         constexpr int PPW = X_BF16 ? 2 : 1;
-        const int words = positions / PPW;
+        const int words_log2 = cols_log2 + 2, words = 1 << words_log2;
         const uint32_t* const tile_words = reinterpret_cast<const uint32_t*>(tile);
         for (int item = threadIdx.x; item < words * kLanes; item += kThreads) {
-            const int lane = item / words, word = item - lane * words;
+            const int lane = item >> words_log2, word = item & (words - 1);
             double q0 = 0.0, q1 = 0.0;
             const uint32_t* e = tile_words + lane * words + word;
             const int step = kLanes * words;
@@ -464,19 +490,19 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
             inverse[threadIdx.x] = rsqrtf(__fadd_rn(static_cast<float>(total / static_cast<double>(p.channels)), p.eps));
         }
         __syncthreads();
-        const int64_t out_chunk0 = o * p.channels * inner_chunks + chunk0;
-        // a thread's chunks all lie in one chunk column: its positions' inverses are read once per tile
-        const int k = threadIdx.x & (cols - 1);
+        if (chunk0 + k < inner_chunks) {
+        // this thread's positions: inverses once per tile
         const float4* i4 = reinterpret_cast<const float4*>(inverse + k * EPC);
         const float4 ia = i4[0];
         float4 ib = ia;
         if constexpr (X_BF16) ib = i4[1];
-        for (int idx = threadIdx.x; idx < tile_chunks && k < valid; idx += kThreads) {
-            const int c = idx >> cols_log2;
-            const bool weighted = p.weight != nullptr;
+        const bool weighted = p.weight != nullptr;
+        uint4* out = static_cast<uint4*>(p.out) + (static_cast<int64_t>(o) * channels + c0) * inner_chunks + chunk0 + k;
+        const uint4* chunk_at = tile + threadIdx.x;
+        int c = c0;
+        for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads, chunk_at += kThreads, out += row_step, c += c_step) {
             const float w = weighted ? round_to(X_DT, load1(p.weight, p.w_dt, c)) : 1.0f;
-            const uint4 raw = tile[idx];
-            const int64_t chunk = out_chunk0 + static_cast<int64_t>(c) * inner_chunks + k;
+            const uint4 raw = *chunk_at;
             auto finish_one = [&](float v, float inv) {
                 float y = __fmul_rn(v, inv);
                 if constexpr (X_BF16) y = round_to_bf16(y);
@@ -502,13 +528,13 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
                     v[2 * j] = finish_one(__uint_as_float(wd[j] << 16), inv[2 * j]);
                     v[2 * j + 1] = finish_one(__uint_as_float(wd[j] & 0xffff0000u), inv[2 * j + 1]);
                 }
-                __stcs(static_cast<uint4*>(p.out) + chunk, make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
-                                                                      pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])));
+                __stcs(out, make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])));
             } else {
-                __stcs(static_cast<float4*>(p.out) + chunk,
+                __stcs(reinterpret_cast<float4*>(out),
                        make_float4(finish_one(__uint_as_float(raw.x), ia.x), finish_one(__uint_as_float(raw.y), ia.y),
                                    finish_one(__uint_as_float(raw.z), ia.z), finish_one(__uint_as_float(raw.w), ia.w)));
             }
+        }
         }
         __syncthreads();
     }
@@ -523,6 +549,7 @@ bool launch_rms_axis_tiles(const void* x, int dtype, const void* weight, int wei
     const int epc = dtype == VRB_BF16 ? 8 : 4;
     if (inner % epc != 0 || !aligned16(x) || !aligned16(out) || channels >= (int64_t{1} << 20)) return false;
     const int64_t inner_chunks = inner / epc;
+    if (outer * inner_chunks >= (int64_t{1} << 31)) return false;   // the tile kernel counts tiles and chunks in 32 bits
     RmsAxisParams p{x, out, weight, weight_dtype, outer, channels, inner, eps};
     for (int budget_ctas : {3, 1}) {
         for (int cols = 8, log2 = 3; cols >= 1; cols >>= 1, --log2) {
@@ -586,7 +613,8 @@ int pixel_norm_family(const void* x, int dtype, const void* scale, const void* s
         return after_launch("pixel_norm");
     }
     const int epc = dtype == VRB_BF16 ? 8 : 4;
-    if (inner % epc == 0 && aligned16(x) && aligned16(out) && channels < (int64_t{1} << 20)) {
+    if (inner % epc == 0 && aligned16(x) && aligned16(out) && channels < (int64_t{1} << 20) &&
+        outer * (inner / epc) < (int64_t{1} << 31)) {      // the tile kernel counts tiles and chunks in 32 bits
         const int64_t inner_chunks = inner / epc;
         // widest tile (16-byte chunks per channel row) that leaves room for three CTAs per SM, else
         // for one; never wider than the row
