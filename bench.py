@@ -196,6 +196,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     lib = _lib.load()
+    numa = bench_extras.bind_to_gpu_numa_node(local) if world > 1 else None      # before any pinned buffer is touched
     be = ops.B200Backend(device=f"cuda:{local}")
     peak, peak_kind = measured_hbm_peak()
 
@@ -331,6 +332,8 @@ def main():
                "ms_per_step": e2e_ms,
                "note": "the same step's operators (both CFG branches, 22 host-buffer calls; each rank its token rows), pinned host buffers, "
                        "3-stream upload/kernel/download pipeline per call"}
+    if numa is not None:
+        e2e_obj["numa"] = numa     # rank 0's GPU node and how many CPUs the rank was bound to
     lib.vrb_host_release()
 
     cpu = None

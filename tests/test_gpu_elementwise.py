@@ -274,6 +274,35 @@ def test_gated_residual_bit_exact(orc, gpu, res_dt, br_dt, state, rows, width, b
     assert_bits_equal(chain, want, "per-op chain")
 
 
+@pytest.mark.parametrize("batch,rows,width", [(3, 13000, 1024), (1, 32760, 1536), (2, 6200, 5120)])
+def test_gated_residual_staged_gate_path(orc, gpu, batch, rows, width):
+    """Large all-bf16 launches keep the gate vectors in shared memory and carry column / vector along instead of
+    dividing them out of the index.  Same bits as the general kernel (the same tensors in launches too small for the
+    staged path) and as the oracle on the first and last rows of every batch entry."""
+    import torch
+    be, ops = gpu
+    from vrhino_b200 import synth
+    g = torch.Generator(device="cuda").manual_seed(batch * 7 + width)
+    res = torch.randn(batch, rows, width, device="cuda", generator=g).to(torch.bfloat16)
+    br = torch.randn(batch, rows, width, device="cuda", generator=g).to(torch.bfloat16)
+    gate = torch.randn(batch, 1, width, device="cuda", generator=g) * 0.3
+    pol = ops.Policy(residual=torch.bfloat16)
+    got = ops.fused_gated_residual(be, pol, res, br, gate)
+    pieces = []
+    for b in range(batch):
+        for r0 in range(0, rows, 2048):          # 2048 rows: well below the staged path's threshold
+            pieces.append(ops.fused_gated_residual(be, pol, res[b:b + 1, r0:r0 + 2048].contiguous(), br[b:b + 1, r0:r0 + 2048].contiguous(),
+                                                   gate[b:b + 1]))
+    want = torch.cat(pieces, 1).view(batch, rows, width)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    obe, opol = orc.OracleBackend(), orc.Policy(residual="bf16")
+    bits = lambda t: orc.T(t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16), "bf16")
+    for b in range(batch):
+        for sl in (slice(0, 3), slice(rows - 3, rows)):
+            ref = orc.gated_residual(obe, opol, bits(res[b:b + 1, sl]), bits(br[b:b + 1, sl]), orc.tensor(gate[b:b + 1].cpu().numpy(), "f32"))
+            assert np.array_equal(got[b:b + 1, sl].contiguous().view(torch.int16).cpu().numpy().view(np.uint16), ref.data)
+
+
 @pytest.mark.parametrize("x_dt", DTYPES)
 @pytest.mark.parametrize("f_dt", DTYPES)
 @pytest.mark.parametrize("shape,f_shape", [((1, 3, 2, 6), (1, 3, 1, 6)), ((1, 3, 2, 64), (1, 3, 1, 64)), ((1, 3, 2, 128), (1, 3, 1, 128)),

@@ -163,6 +163,34 @@ def sharded_forms(be, world, rank, dist, barrier, max_over_ranks, peak, steps=10
     return out
 
 
+def bind_to_gpu_numa_node(device_index: int):
+    """Keep this rank's threads (and so the first touch of its pinned staging buffers) on the NUMA node its GPU hangs
+    off: with one rank per GPU the host side of `e2e` is otherwise placed wherever the launcher started the process.
+    Reads sysfs only; returns what it found and did ({"node": -1} = the platform reports no node, nothing bound)."""
+    import os
+    found = {"node": -1, "cpus_bound": 0}
+    try:
+        bus = torch.cuda.get_device_properties(device_index)
+        address = f"{bus.pci_domain_id:04x}:{bus.pci_bus_id:02x}:{bus.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{address}/numa_node") as fh:
+            node = int(fh.read().strip())
+        found["node"] = node
+        if node < 0:
+            return found
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as fh:
+            cpus = set()
+            for part in fh.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            found["cpus_bound"] = len(allowed)
+    except (OSError, ValueError, AttributeError):
+        pass
+    return found
+
+
 def pcie_probe(world, barrier, max_over_ranks, nbytes=256 << 20, steps=4):
     """Host<->device copy rates with every rank copying at once (pinned buffers): what bounds `e2e`."""
     host_a, host_b = torch.empty(nbytes, dtype=torch.uint8).pin_memory(), torch.empty(nbytes, dtype=torch.uint8).pin_memory()

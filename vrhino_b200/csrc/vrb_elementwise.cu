@@ -405,6 +405,73 @@ __global__ void __launch_bounds__(kThreads) gated_residual_typed_kernel(
     }
 }
 
+// All-bf16 tensors with a gate, large launches: the gate vectors are rounded to bf16 once per CTA into shared memory
+// (the reference rounds the gate to the state dtype before the multiply, so this is the same value), and the chunk's
+// column and vector are carried along instead of being divided out of the index: one 16-byte shared-memory load per
+// chunk where the general kernel has three 32-bit divisions, two 16-byte gate loads and four conversions.
+// gate_bf16 holds vectors * width_chunks chunks of 8 bf16.
+__global__ void __launch_bounds__(kThreads) gated_residual_staged_kernel(
+        const uint4* __restrict__ res, const uint4* __restrict__ branch, const void* __restrict__ gate, int gate_dt,
+        uint4* __restrict__ out, unsigned total, unsigned width_chunks, unsigned rows_per_vector, unsigned vectors) {
+    extern __shared__ __align__(16) uint4 gate_bf16[];
+    constexpr int U = 2;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (unsigned c = threadIdx.x; c < vectors * width_chunks; c += kThreads) {
+        float g[8];
+        load8<false>(gate, gate_dt, static_cast<int64_t>(c) * 8, g);
+        gate_bf16[c] = make_uint4(pack_bf16x2(g[0], g[1]), pack_bf16x2(g[2], g[3]), pack_bf16x2(g[4], g[5]), pack_bf16x2(g[6], g[7]));
+    }
+    __syncthreads();
+    const unsigned stride = gridDim.x * kThreads;
+    // chunk i lies in column i % width_chunks of vector (i / period) % vectors, period = rows_per_vector * width_chunks
+    // (a 64-bit product: with one vector the period only has to exceed every index)
+    const unsigned long long period = static_cast<unsigned long long>(rows_per_vector) * width_chunks;
+    const unsigned first = blockIdx.x * kThreads + threadIdx.x;
+    unsigned column = first % width_chunks;
+    unsigned long long within = first % period;
+    unsigned vector = static_cast<unsigned>((first / period) % vectors);
+    const unsigned column_step = stride % width_chunks;
+    const unsigned long long within_step = stride % period;
+    const unsigned vector_step = static_cast<unsigned>((stride / period) % vectors);
+    auto advance = [&] {
+        column += column_step;
+        if (column >= width_chunks) column -= width_chunks;
+        within += within_step;
+        vector += vector_step;
+        if (within >= period) { within -= period; ++vector; }
+        if (vector >= vectors) vector -= vectors;
+    };
+    for (unsigned i0 = first; i0 < total; i0 += stride * U) {
+        uint4 r[U], b[U], g[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const unsigned i = i0 + u * stride;
+            if (i < total) {
+                r[u] = __ldcs(res + i);
+                b[u] = __ldcs(branch + i);
+                g[u] = gate_bf16[vector * width_chunks + column];
+            }
+            advance();
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const unsigned i = i0 + u * stride;
+            if (i >= total) break;
+            const uint32_t rw[4] = {r[u].x, r[u].y, r[u].z, r[u].w}, bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+            const uint32_t gw[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const __nv_bfloat162 br = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&bw[k]), *reinterpret_cast<const __nv_bfloat162*>(&gw[k]));
+                const __nv_bfloat162 sum = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&rw[k]), br);
+                ow[k] = *reinterpret_cast<const uint32_t*>(&sum);
+            }
+            __stcs(out + i, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) gated_residual_scalar_kernel(
         const void* res, int res_dt, const void* branch, int br_dt, const void* gate, int gate_dt,
         void* out, int state_dt, int64_t rows, int64_t width, int64_t rows_per_vector, int64_t vectors) {
@@ -857,6 +924,15 @@ extern "C" int vrb_gated_residual(const void* residual, int residual_dtype, cons
         const unsigned rpv = static_cast<unsigned>(gate ? rows_per_vector : 1), nv = static_cast<unsigned>(gate ? gate_vectors : 1);
         cudaStream_t s = as_stream(stream);
         const int key = (residual_dtype == VRB_BF16 ? 4 : 0) | (branch_dtype == VRB_BF16 ? 2 : 0) | (state_dtype == VRB_BF16 ? 1 : 0);
+        // staged gate: worth its per-CTA prologue from 16 chunks per thread; the vectors must fit 48 KB of shared memory
+        const int64_t gate_bytes = static_cast<int64_t>(nv) * wc * 16;
+        if (key == 7 && gate && gate_bytes <= 48 * 1024 && chunks >= static_cast<int64_t>(grid) * kThreads * 16 &&
+            static_cast<int64_t>(total) + static_cast<int64_t>(grid) * kThreads * 2 < (int64_t{1} << 32)) {
+            launch_overlapped(gated_residual_staged_kernel, dim3(grid), dim3(kThreads), static_cast<size_t>(gate_bytes), s,
+                              static_cast<const uint4*>(residual), static_cast<const uint4*>(branch), gate, gate_dtype,
+                              static_cast<uint4*>(out), total, wc, rpv, nv);
+            return after_launch("gated_residual");
+        }
 #define VRB_GR(R, B, S) launch_overlapped(gated_residual_typed_kernel<R, B, S>, dim3(grid), dim3(kThreads), 0, s, residual, branch, gate, gate_dtype, out, total, wc, rpv, nv)
         switch (key) {
             case 0: VRB_GR(false, false, false); break;

@@ -112,6 +112,17 @@ __device__ __forceinline__ float silu_approximate(float v, bool& redo) {
 // one by one.  Otherwise the short forms above where the template arguments allow them, with `redo` set when the
 // element has to be evaluated again with EXACT (the caller does that once per 16-byte chunk, so the common path has
 // one branch per chunk).
+// The steps after the quotient: rounding to x's dtype, modulate, SiLU.
+template <bool X_BF16, int MODE, bool OUT_BF16, bool EXACT>
+__device__ __forceinline__ float finish_quotient(float v, float one_plus_scale, float shift, bool& redo) {
+    if constexpr (X_BF16 && MODE != kNormOnly) v = round_to_bf16(v);   // kNormOnly: the bf16 store rounds
+    if constexpr (MODE != kNormOnly) v = __fadd_rn(__fmul_rn(v, one_plus_scale), shift);
+    if constexpr (MODE == kModulateSilu) {
+        if constexpr (OUT_BF16 && !EXACT) v = silu_approximate(v, redo);
+        else v = activation_value(VRB_SILU, v);
+    }
+    return v;
+}
 template <bool X_BF16, int MODE, bool OUT_BF16, bool EXACT>
 __device__ __forceinline__ float finish_tile(float x, float denominator, float reciprocal, float one_plus_scale, float shift,
                                              bool& redo) {
@@ -123,13 +134,7 @@ __device__ __forceinline__ float finish_tile(float x, float denominator, float r
     } else {
         v = __fdiv_rn(x, denominator);
     }
-    if constexpr (X_BF16 && MODE != kNormOnly) v = round_to_bf16(v);   // kNormOnly: the bf16 store rounds
-    if constexpr (MODE != kNormOnly) v = __fadd_rn(__fmul_rn(v, one_plus_scale), shift);
-    if constexpr (MODE == kModulateSilu) {
-        if constexpr (OUT_BF16 && !EXACT) v = silu_approximate(v, redo);
-        else v = activation_value(VRB_SILU, v);
-    }
-    return v;
+    return finish_quotient<X_BF16, MODE, OUT_BF16, EXACT>(v, one_plus_scale, shift, redo);
 }
 // whether the short forms exist for a variant (else the first evaluation is already the exact one)
 template <bool X_BF16, int MODE, bool OUT_BF16>
@@ -260,8 +265,23 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
                     in[0] = __uint_as_float(raw.x); in[1] = __uint_as_float(raw.y); in[2] = __uint_as_float(raw.z); in[3] = __uint_as_float(raw.w);
                 }
                 bool redo = false;
+                if constexpr (X_BF16) {
+                    // the reciprocal form two elements at a time (packed F32 operations round like the scalar ones)
 #pragma unroll
-                for (int j = 0; j < EPC; ++j) v[j] = finish_tile<X_BF16, MODE, OUT_BF16, false>(in[j], d[j], r[j], ops, sh, redo);
+                    for (int j = 0; j < EPC; j += 2) {
+                        const unsigned long long x2 = pack_f32x2(in[j], in[j + 1]), r2 = pack_f32x2(r[j], r[j + 1]);
+                        const unsigned long long q2 = mul_f32x2(x2, r2);
+                        const unsigned long long c2 = fma_f32x2(fma_f32x2(pack_f32x2(-d[j], -d[j + 1]), q2, x2), r2, q2);
+                        float c0, c1;
+                        unpack_f32x2(c2, c0, c1);
+                        redo = redo || !(fabsf(c0) >= kQuotientFloor) || !(fabsf(c1) >= kQuotientFloor);
+                        v[j] = finish_quotient<true, MODE, OUT_BF16, false>(c0, ops, sh, redo);
+                        v[j + 1] = finish_quotient<true, MODE, OUT_BF16, false>(c1, ops, sh, redo);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < EPC; ++j) v[j] = finish_tile<X_BF16, MODE, OUT_BF16, false>(in[j], d[j], r[j], ops, sh, redo);
+                }
                 if constexpr (kHasShortForm<X_BF16, MODE, OUT_BF16>) {
                     if (redo) {
                         bool unused = false;
