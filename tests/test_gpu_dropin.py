@@ -430,7 +430,8 @@ def test_replaced_operators_appear_in_profile_stats_under_the_reference_names(dr
     rd.profile(True)
     try:
         made = [rd.layer_norm(x, None, None, 1e-6), rd.rms_norm(x, w, 1e-6), rd.activation(x, 2), rd.binary(0, x, x),
-                rd.cast(x, ref.F32), rd.clamp(x, -1.0, 1.0),
+                rd.cast(x, ref.F32), rd.clamp(x, -1.0, 1.0), rd.permute(x, (0, 2, 1)), rd.slice(x, 2, 0, 768), rd.concat([x, x], 1),
+                rd.pad(x, [0, 0, 1, 1], 0.0, True),
                 rd.fused_layer_norm_modulate(ref.POLICY_BF16, x, None, None, 1e-6,
                                              rd.upload(rng.standard_normal((1, 1, 1536)).astype(np.float32), ref.F32),
                                              rd.upload(rng.standard_normal((1, 1, 1536)).astype(np.float32), ref.F32))]
@@ -445,6 +446,7 @@ def test_replaced_operators_appear_in_profile_stats_under_the_reference_names(dr
         "elementwise.add": 3 * nbytes,
         "cast": 3 * nbytes,
         "clamp": 2 * nbytes,
+        "permute": 2 * nbytes, "slice": nbytes, "concat": 4 * nbytes, "pad": 2 * nbytes,
         "fused.norm.layer+modulate": 2 * nbytes,
     }
     for name, moved in expected.items():
