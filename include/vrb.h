@@ -127,6 +127,15 @@ int vrb_pixel_norm(const void* x, int dtype, const void* scale, const void* shif
                    int fuse_silu, void* out, int out_dtype, int64_t outer, int64_t channels,
                    int64_t inner, float eps, vrb_stream stream);
 
+/* The shared-memory tile kernels (vrb_pixel_norm, vrb_l2_normalize) load their tiles with tensor-map copies
+ * (cp.async.bulk.tensor, completion on an mbarrier) where the geometry allows.  vrb_set_tensor_map_tiles(0) makes them
+ * use per-thread 16-byte asynchronous copies instead (same shared-memory layout, same results); returns the previous
+ * setting.  Every wait on such a copy is bounded: a kernel whose wait runs out sets a flag in device memory and
+ * returns; vrb_async_wait_failures reads the flag (a synchronising copy; 0 = no wait has ever run out on the current
+ * device). */
+int vrb_set_tensor_map_tiles(int enabled);
+int vrb_async_wait_failures(int* failures);
+
 /* CudaBackend::l2_normalize (:5088-5110, l2_normalize_kernel :1142-1176) over the middle axis of
  * x [outer, channels, inner]:  y = x / (sqrtf(sum_c(x^2)) + eps)  in x's dtype; eps >= 0.  Same tiles and
  * F32 summation as vrb_pixel_norm (the reference's 256-thread tree adds the same squares in another

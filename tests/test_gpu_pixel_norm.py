@@ -68,6 +68,39 @@ def test_quotient_guards_at_extreme_exponents(orc, gpu, l2):
     assert same.all(), f"positions {sorted(set(np.argwhere(~same)[:, 1].tolist()))} differ"
 
 
+@pytest.mark.parametrize("shape", [(2, 128, 3, 8, 16), (1, 64, 1, 5, 8), (1, 1024, 2, 4, 12), (1, 512, 1, 7, 24), (3, 96, 2, 6, 40), (1, 4000, 1, 1, 16)])
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_tensor_map_tiles_equal_per_thread_copies(orc, gpu, cuda_lib, shape, dt):
+    """The tile kernels load through tensor maps (cp.async.bulk.tensor + mbarrier) where slab and tile sizes allow, else
+    through per-thread 16-byte copies: the same bits either way, on full and ragged tiles, one and several slabs of
+    channels, and no bounded wait may have run out."""
+    import ctypes
+    import torch
+    be, ops = gpu
+    from vrhino_b200 import synth
+    x = to_torch(orc.tensor(synth.normal(shape, 0.2, 1.5, seed=shape[1] + 1), dt))
+    vec = (shape[0], shape[1], 1, 1, 1)
+    shift, scale = to_torch(orc.tensor(synth.normal(vec, 0, 0.2, seed=1))), to_torch(orc.tensor(synth.normal(vec, 0, 0.2, seed=2)))
+
+    def run():
+        return [be.pixel_norm(x, 1, 1e-8), be.l2_normalize(x, 1, 1e-10), ops.fused_pixel_norm_modulate(be, x, shift, scale, 1e-8),
+                ops.fused_pixel_norm_modulate(be, x, shift, scale, 1e-8, out_dtype=torch.bfloat16),
+                ops.fused_pixel_norm_modulate(be, x, shift, scale, 1e-8, silu=False)]
+
+    previous = cuda_lib.vrb_set_tensor_map_tiles(1)
+    try:
+        with_maps = run()
+        cuda_lib.vrb_set_tensor_map_tiles(0)
+        without = run()
+    finally:
+        cuda_lib.vrb_set_tensor_map_tiles(previous)
+    bits = lambda t: t.view(torch.int16 if t.dtype == torch.bfloat16 else torch.int32)
+    for a, b in zip(with_maps, without):
+        assert torch.equal(bits(a), bits(b))
+    failures = ctypes.c_int(-1)
+    assert cuda_lib.vrb_async_wait_failures(ctypes.byref(failures)) == 0 and failures.value == 0
+
+
 def test_bf16_store_silu_over_every_f32_argument(gpu):
     """pixel_norm -> modulate -> SiLU with a bf16 result evaluates SiLU through approximate special functions wherever
     the bf16 rounding provably cannot differ, else exactly.  All 2^32 F32 arguments go through the kernel here: with

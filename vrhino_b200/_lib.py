@@ -74,6 +74,8 @@ SIGNATURES = {
     "vrb_pixel_shuffle": [_vp, _vp, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _vp],
     "vrb_depth_to_space_residual": [_vp, _vp, _vp, _i, _i64, _i64, _i64, _i64, _i64, _vp],
     "vrb_l2_normalize": [_vp, _vp, _i, _i64, _i64, _i64, _f, _vp],
+    "vrb_set_tensor_map_tiles": [_i],
+    "vrb_async_wait_failures": [_vp],
     "vrb_permute": [_vp, _vp, _i, _i, _vp, _vp, _vp],
     "vrb_slice": [_vp, _vp, _i, _i, _vp, _i, _i64, _i64, _vp],
     "vrb_concat": [_vp, _vp, _i, _vp, _i, _i, _vp, _i, _vp],

@@ -337,20 +337,35 @@ __global__ void __launch_bounds__(kThreads) gated_residual_typed_kernel(
     const unsigned stride = gridDim.x * blockDim.x;
     pdl_launch_dependents();
     pdl_wait();
-    for (unsigned i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
+    // all-bf16 form: the chunk's column and gate vector are carried from step to step instead of being divided out of
+    // the index (column = i % width_chunks, vector = (i / period) % vectors, period = rows_per_vector * width_chunks)
+    const unsigned first = blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned long long period = static_cast<unsigned long long>(rows_per_vector) * width_chunks;
+    unsigned column = 0, vector = 0, column_step = 0, vector_step = 0;
+    unsigned long long within = 0, within_step = 0;
+    if (RES_BF16 && BR_BF16 && STATE_BF16 && gate) {
+        column = first % width_chunks; within = first % period; vector = static_cast<unsigned>((first / period) % vectors);
+        column_step = stride % width_chunks; within_step = stride % period; vector_step = static_cast<unsigned>((stride / period) % vectors);
+    }
+    for (unsigned i0 = first; i0 < total; i0 += stride * U) {
         if constexpr (RES_BF16 && BR_BF16 && STATE_BF16) {
             uint4 r[U], b[U];
             float g[U][8];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const unsigned i = i0 + u * stride;
-                if (i >= total) break;
-                r[u] = __ldcs(static_cast<const uint4*>(res) + i);
-                b[u] = __ldcs(static_cast<const uint4*>(branch) + i);
+                if (i < total) {
+                    r[u] = __ldcs(static_cast<const uint4*>(res) + i);
+                    b[u] = __ldcs(static_cast<const uint4*>(branch) + i);
+                    if (gate) load8<false>(gate, gate_dt, (static_cast<int64_t>(vector) * width_chunks + column) * 8, g[u]);
+                }
                 if (gate) {
-                    const unsigned row = i / width_chunks, chunk = i - row * width_chunks;
-                    const unsigned vec = vectors > 1 ? (row / rows_per_vector) % vectors : 0;
-                    load8<false>(gate, gate_dt, (static_cast<int64_t>(vec) * width_chunks + chunk) * 8, g[u]);
+                    column += column_step;
+                    if (column >= width_chunks) column -= width_chunks;
+                    within += within_step;
+                    vector += vector_step;
+                    if (within >= period) { within -= period; ++vector; }
+                    if (vector >= vectors) vector -= vectors;
                 }
             }
 #pragma unroll

@@ -148,14 +148,24 @@ __global__ void __launch_bounds__(kThreads) walk_rows_kernel(const E* __restrict
         constexpr int kInFlight = 8;
         if (row_valid) {
             E* const body = dst + before_last;
-            for (int j0 = lane; j0 < in_extent_last; j0 += 32 * kInFlight) {
+            const E* from = src + lane;
+            E* to = body + lane;
+            int left = in_extent_last;
+            for (; left >= 32 * kInFlight; left -= 32 * kInFlight, from += 32 * kInFlight, to += 32 * kInFlight) {   // whole blocks: no tests
+                E value[kInFlight];
+#pragma unroll
+                for (int u = 0; u < kInFlight; ++u) value[u] = from[32 * u];
+#pragma unroll
+                for (int u = 0; u < kInFlight; ++u) to[32 * u] = value[u];
+            }
+            if (left > 0) {
                 E value[kInFlight];
 #pragma unroll
                 for (int u = 0; u < kInFlight; ++u)
-                    if (j0 + 32 * u < in_extent_last) value[u] = src[j0 + 32 * u];
+                    if (lane + 32 * u < left) value[u] = from[32 * u];
 #pragma unroll
                 for (int u = 0; u < kInFlight; ++u)
-                    if (j0 + 32 * u < in_extent_last) body[j0 + 32 * u] = value[u];
+                    if (lane + 32 * u < left) to[32 * u] = value[u];
             }
             if constexpr (PAD) {
                 const int after_last = extent_last - before_last - in_extent_last;
@@ -328,15 +338,25 @@ __global__ void __launch_bounds__(kThreads) transpose_kernel(const E* __restrict
     }
 }
 
-// 2-byte elements with even extents, strides and offsets: the tile is moved as 32-bit words.  A thread loads the
-// words (a, a+1) of rows b and b+1, transposes the 2 x 2 block in registers (two byte permutes) and stores the words
-// (b, b+1) of rows a and a+1 into the tile, rows of even and odd a in separate halves so that the stores of a warp
-// fall into 32 different banks; the tile is then written out row by row, 8 bytes per thread.  2 memory instructions
-// per element instead of 4, and every global access is a full 32-byte sector.
-__global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
-                                                                   const Transpose g) {
-    constexpr int TILE = 64, HALF = TILE / 2, PITCH = HALF + 1;   // words per tile row: 32 b-pairs + 1
-    __shared__ uint32_t tile[TILE * PITCH];
+// Even extents, strides and offsets: the tile is moved as pairs of elements (W = 32 bits for two bf16, 64 bits for two
+// F32).  A thread loads the pairs (a, a+1) of rows b and b+1, transposes the 2 x 2 block in registers and stores the
+// pairs (b, b+1) of rows a and a+1 into the tile, rows of even and odd a in separate halves so that the stores of a
+// warp fall into different banks; the tile is then written out row by row, two pairs per thread.  Half the memory
+// instructions of the element-wise tile, and every global access is a full 32-byte sector.
+template <typename W>
+__device__ __forceinline__ void transpose_2x2(W row0, W row1, W& even, W& odd) {
+    if constexpr (sizeof(W) == 4) {
+        even = __byte_perm(row0, row1, 0x5410);   // x(b, a), x(b + 1, a)
+        odd = __byte_perm(row0, row1, 0x7632);    // x(b, a + 1), x(b + 1, a + 1)
+    } else {
+        even = (row0 & 0xffffffffull) | (row1 << 32);
+        odd = (row0 >> 32) | (row1 & 0xffffffff00000000ull);
+    }
+}
+template <typename W>
+__global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const W* __restrict__ in, W* __restrict__ out, const Transpose g) {
+    constexpr int TILE = 64, HALF = TILE / 2, PITCH = HALF + 1;   // pairs per tile row: 32 + 1
+    __shared__ W tile[TILE * PITCH];
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
@@ -369,13 +389,14 @@ __global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const uint32_
             const int pair_b = warp + 8 * i;
             if (a_inside && b0 + 2 * pair_b < g.extent_b) {
                 const int64_t at = in_base + static_cast<int64_t>(2 * pair_b) * g.in_stride_b + 2 * lane;
-                const uint32_t row0 = in[at >> 1], row1 = in[(at + g.in_stride_b) >> 1];
-                tile[lane * PITCH + pair_b] = __byte_perm(row0, row1, 0x5410);             // a even: x(b, a), x(b + 1, a)
-                tile[(HALF + lane) * PITCH + pair_b] = __byte_perm(row0, row1, 0x7632);    // a odd
+                W even, odd;
+                transpose_2x2<W>(in[at >> 1], in[(at + g.in_stride_b) >> 1], even, odd);
+                tile[lane * PITCH + pair_b] = even;
+                tile[(HALF + lane) * PITCH + pair_b] = odd;
             }
         }
         __syncthreads();
-        // store: 16 threads cover the 32 words of one output row, two words each; the two half-warps take adjacent
+        // store: 16 threads cover the 32 pairs of one output row, two pairs each; the two half-warps take adjacent
         // tile rows (an odd pitch apart: no bank conflict)
         const int word = 2 * (threadIdx.x % 16);
         const bool first_inside = b0 + 2 * word < g.extent_b, second_inside = b0 + 2 * word + 2 < g.extent_b;
@@ -384,10 +405,11 @@ __global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const uint32_
             const int tile_row = threadIdx.x / 16 + 16 * i;
             const int a = tile_row < HALF ? 2 * tile_row : 2 * (tile_row - HALF) + 1;
             if (first_inside && a0 + a < g.extent_a) {
-                const uint32_t w0 = tile[tile_row * PITCH + word], w1 = tile[tile_row * PITCH + word + 1];
+                const W w0 = tile[tile_row * PITCH + word], w1 = tile[tile_row * PITCH + word + 1];
                 const int64_t at = (out_base + static_cast<int64_t>(a) * g.out_stride_a) / 2 + word;
-                if (second_inside && (at & 1) == 0) {
-                    *reinterpret_cast<uint2*>(out + at) = make_uint2(w0, w1);
+                if (second_inside && (at & 1) == 0) {   // the base is aligned to two pairs (the launcher checks)
+                    if constexpr (sizeof(W) == 4) *reinterpret_cast<uint2*>(out + at) = make_uint2(w0, w1);
+                    else *reinterpret_cast<ulonglong2*>(out + at) = make_ulonglong2(w0, w1);
                 } else {
                     out[at] = w0;
                     if (second_inside) out[at + 1] = w1;
@@ -504,17 +526,20 @@ int run_plan(const void* in, void* out, int dtype, const Plan& raw, float pad_va
             }
             g.extent_a = p.extent[a]; g.extent_b = p.extent[last];
             g.in_stride_b = p.in_stride[last]; g.out_stride_a = p.out_stride[a];
-            const int tile = element == 2 ? 64 : 32;
+            bool pairs = g.extent_a % 2 == 0 && g.extent_b % 2 == 0 && g.in_stride_b % 2 == 0 && g.out_stride_a % 2 == 0 &&
+                         reinterpret_cast<uintptr_t>(source) % (2 * element) == 0 && reinterpret_cast<uintptr_t>(destination) % (4 * element) == 0;
+            for (int d = 0; d < g.batch_rank && pairs; ++d) pairs = g.batch_in_stride[d] % 2 == 0 && g.batch_out_stride[d] % 2 == 0;
+            const int tile = pairs || element == 2 ? 64 : 32;
             g.tiles_a = (g.extent_a + tile - 1) / tile; g.tiles_b = (g.extent_b + tile - 1) / tile;
             g.tiles = g.tiles_a * g.tiles_b;
             for (int d = 0; d < g.batch_rank; ++d) g.tiles *= g.batch_extent[d];
             const int grid = grid_for(g.tiles, kPerSm);
-            bool pairs = element == 2 && g.extent_a % 2 == 0 && g.extent_b % 2 == 0 && g.in_stride_b % 2 == 0 && g.out_stride_a % 2 == 0 &&
-                         reinterpret_cast<uintptr_t>(source) % 4 == 0 && reinterpret_cast<uintptr_t>(destination) % 4 == 0;
-            for (int d = 0; d < g.batch_rank && pairs; ++d) pairs = g.batch_in_stride[d] % 2 == 0 && g.batch_out_stride[d] % 2 == 0;
-            if (pairs)
-                launch_overlapped(transpose_pairs_kernel, dim3(grid), dim3(kThreads), 0, stream, reinterpret_cast<const uint32_t*>(source),
-                                  reinterpret_cast<uint32_t*>(destination), g);
+            if (pairs && element == 2)
+                launch_overlapped(transpose_pairs_kernel<uint32_t>, dim3(grid), dim3(kThreads), 0, stream,
+                                  reinterpret_cast<const uint32_t*>(source), reinterpret_cast<uint32_t*>(destination), g);
+            else if (pairs)
+                launch_overlapped(transpose_pairs_kernel<unsigned long long>, dim3(grid), dim3(kThreads), 0, stream,
+                                  reinterpret_cast<const unsigned long long*>(source), reinterpret_cast<unsigned long long*>(destination), g);
             else if (element == 2)
                 launch_overlapped(transpose_kernel<uint16_t, 64>, dim3(grid), dim3(kThreads), 0, stream,
                                   reinterpret_cast<const uint16_t*>(source), reinterpret_cast<uint16_t*>(destination), g);

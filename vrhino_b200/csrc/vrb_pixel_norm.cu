@@ -20,6 +20,7 @@
 // normalise pass of the reference read it twice.  Two tile buffers: the next tile's copies are in
 // flight while the current tile is reduced and written.  P is chosen so that three CTAs fit on an SM.
 #include "vrb_common.cuh"
+#include "vrb_tma.cuh"
 
 #include <mutex>
 #include <vector>
@@ -140,30 +141,60 @@ __device__ __forceinline__ float finish_tile(float x, float denominator, float r
 template <bool X_BF16, int MODE, bool OUT_BF16>
 constexpr bool kHasShortForm = X_BF16 || (MODE == kModulateSilu && OUT_BF16);
 
+// set by a tile kernel whose bounded wait for a tensor-map copy ran out (vrb_async_wait_failures() reads it)
+__device__ int g_async_wait_gave_up = 0;
+
 // Tile kernel: inner % EPC == 0, 16-byte aligned tensors, fewer than 2^31 tiles and chunks per channel row; `cols` (a
 // power of two, at most 8) 16-byte chunks per channel.  kNormOnly stores x's dtype; the modulated forms store F32 or
 // (OUT_BF16) bf16.  The block size is a multiple of cols, so a thread's chunks all lie in one chunk column k and
 // its channel advances by kThreads / cols per step: addresses are advanced, not recomputed.
-template <bool X_BF16, int MODE, bool OUT_BF16>
-__global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNormParams p, int cols, int cols_log2) {
+// TMA: the tile is loaded by tensor-map copies (one per slab of `slab` channels, issued by thread 0, completion counted
+// on an mbarrier per buffer) instead of one cp.async per chunk and thread; needs tile and slab sizes that are multiples
+// of 128 bytes.  The shared-memory layout of the tile is the same either way.
+template <bool X_BF16, int MODE, bool OUT_BF16, bool TMA>
+__global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNormParams p, int cols, int cols_log2,
+                                                                   const __grid_constant__ CUtensorMap map, int slab) {
     constexpr int EPC = X_BF16 ? 8 : 4;   // elements per 16-byte chunk
     constexpr int OUT_CHUNK = (MODE == kNormOnly ? X_BF16 : OUT_BF16) ? EPC * 2 : EPC * 4;   // bytes written per chunk
-    extern __shared__ __align__(16) uint4 tiles_buffer[];   // two tiles of [channels][cols], then the reduction scratch
+    extern __shared__ __align__(128) uint4 tiles_buffer[];   // two tiles of [channels][cols], then the reduction scratch
     const int channels = static_cast<int>(p.channels);
     const int positions = cols * EPC;
     const int tile_chunks = channels * cols;
     float* const partial = reinterpret_cast<float*>(tiles_buffer + 2 * static_cast<size_t>(tile_chunks));   // [kLanes][positions]
     float* const denominator = partial + kLanes * positions;                                              // [positions]
     float* const reciprocal = denominator + positions;                                                    // [positions], bf16 input only
+    uint64_t* const barriers = reinterpret_cast<uint64_t*>(reciprocal + positions);                       // [2], TMA only
     const uint32_t inner_chunks = static_cast<uint32_t>(p.inner / EPC);
     const uint32_t tiles_per_outer = (inner_chunks + cols - 1) >> cols_log2;
     const uint32_t tiles = static_cast<uint32_t>(p.outer) * tiles_per_outer;
     const float channel_count = static_cast<float>(p.channels);
     const int k = threadIdx.x & (cols - 1), c0 = threadIdx.x >> cols_log2, c_step = kThreads >> cols_log2;
     const int64_t row_step = static_cast<int64_t>(c_step) * inner_chunks;   // chunks between a thread's consecutive channels
+    if constexpr (TMA) {
+        if (threadIdx.x == 0) {
+            mbarrier_init(&barriers[0], 1);
+            mbarrier_init(&barriers[1], 1);
+            mbarrier_init_fence();
+        }
+        __syncthreads();
+    }
+    unsigned phases = 0;   // bit b: parity of the phase buffer b's barrier completes next
 
-    // asynchronous copy of tile t into buffer b (one committed group per tile and thread)
+    // asynchronous copy of tile t into buffer b (cp.async: one committed group per tile and thread)
     auto request = [&](uint32_t t, int b) {
+        if constexpr (TMA) {
+            if (t < tiles && threadIdx.x == 0) {
+                const uint32_t o = t / tiles_per_outer;
+                const uint32_t chunk0 = (t - o * tiles_per_outer) << cols_log2;
+                uint4* const dst = tiles_buffer + static_cast<size_t>(b) * tile_chunks;
+                async_proxy_fence();   // the buffer was read through the generic proxy until the barrier before this call
+                mbarrier_expect_bytes(&barriers[b], static_cast<unsigned>(tile_chunks) * 16u);
+                // columns beyond the row's end are filled with zeros by the copy (and count as transferred bytes)
+                for (int c = 0; c < channels; c += slab)
+                    tma_load_3d(dst + static_cast<size_t>(c) * cols, &map, static_cast<int>(chunk0 * EPC), c, static_cast<int>(o), &barriers[b]);
+            }
+            return;
+        }
         if (t < tiles) {
             const uint32_t o = t / tiles_per_outer;
             const uint32_t chunk0 = (t - o * tiles_per_outer) << cols_log2;
@@ -186,8 +217,19 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
         const uint32_t chunk0 = (t - o * tiles_per_outer) << cols_log2;
         const uint4* const tile = tiles_buffer + static_cast<size_t>(buffer) * tile_chunks;
         request(t + gridDim.x, buffer ^ 1);   // the next tile arrives while this one is reduced and written
-        async_copy_wait<1>();
-        __syncthreads();
+        if constexpr (TMA) {
+            const bool arrived = mbarrier_wait_bounded(&barriers[buffer], (phases >> buffer) & 1u, &g_async_wait_gave_up);
+            phases ^= 1u << buffer;
+            if (!__syncthreads_and(arrived)) {
+                // a wait ran out somewhere in the CTA: every thread leaves, after one more bounded wait for the copy
+                // that may still be in flight into the other buffer
+                if (t + gridDim.x < tiles) mbarrier_wait_bounded(&barriers[buffer ^ 1], (phases >> (buffer ^ 1)) & 1u, &g_async_wait_gave_up);
+                break;
+            }
+        } else {
+            async_copy_wait<1>();
+            __syncthreads();
+        }
         // (lane, position) partial sums in the reference's order; a thread takes the positions of one
         // 32-bit shared-memory word (two bf16 positions, one F32 position); words is a power of two
         constexpr int PPW = X_BF16 ? 2 : 1;
@@ -603,6 +645,16 @@ int pixel_norm_family(const void* x, int dtype, const void* scale, const void* s
                       int out_dtype, int64_t outer, int64_t channels, int64_t inner, float eps, int l2, vrb_stream stream);
 }
 
+extern "C" int vrb_async_wait_failures(int* failures) {
+    VRB_REQUIRE(failures, VRB_ERR_INVALID, "async_wait_failures: null result");
+    const cudaError_t e = cudaMemcpyFromSymbol(failures, g_async_wait_gave_up, sizeof(int));
+    if (e != cudaSuccess) {
+        set_error("CUDA error: %s (async_wait_failures)", cudaGetErrorString(e));
+        return VRB_ERR_CUDA;
+    }
+    return VRB_OK;
+}
+
 extern "C" int vrb_pixel_norm(const void* x, int dtype, const void* scale, const void* shift, int mod_dtype, int fuse_silu,
                               void* out, int out_dtype, int64_t outer, int64_t channels, int64_t inner, float eps,
                               vrb_stream stream) {
@@ -647,12 +699,27 @@ int pixel_norm_family(const void* x, int dtype, const void* scale, const void* s
                 const int variant = (dtype == VRB_BF16 ? 8 : 0) | (mode << 1) | (out_dtype == VRB_BF16 ? 1 : 0);
                 const int64_t tiles = outer * ((inner_chunks + cols - 1) / cols);
                 bool launched = true;
-#define VRB_PN(XB, M, OB)                                                                               \
-    {                                                                                                   \
-        const int per_sm = tile_ctas_per_sm(pixel_norm_tile_kernel<XB, M, OB>, smem);                   \
-        if (per_sm < 1) { launched = false; break; }                                                    \
-        pixel_norm_tile_kernel<XB, M, OB><<<grid_for(tiles, per_sm), kThreads, smem, s>>>(p, cols, log2); \
-    }                                                                                                   \
+                // tensor-map loads: slabs of at most 256 channels whose bytes, like the tile's, are multiples of 128
+                CUtensorMap map{};
+                int slab = 0;
+                if (g_tma_tiles.load(std::memory_order_relaxed) != 0 && (channels * cols) % 8 == 0) {
+                    for (int candidate = static_cast<int>(channels < 256 ? channels : 256); candidate >= 8 && slab == 0; --candidate)
+                        if (channels % candidate == 0 && (static_cast<int64_t>(candidate) * cols) % 8 == 0) slab = candidate;
+                    if (slab != 0 && !encode_tile_map(&map, x, dtype, outer, channels, inner, cols * epc, slab)) slab = 0;
+                }
+                const size_t smem_all = smem + 16;   // + the two mbarriers
+#define VRB_PN(XB, M, OB)                                                                                             \
+    {                                                                                                                 \
+        if (slab != 0) {                                                                                              \
+            const int per_sm = tile_ctas_per_sm(pixel_norm_tile_kernel<XB, M, OB, true>, smem_all);                   \
+            if (per_sm < 1) { launched = false; break; }                                                              \
+            pixel_norm_tile_kernel<XB, M, OB, true><<<grid_for(tiles, per_sm), kThreads, smem_all, s>>>(p, cols, log2, map, slab); \
+        } else {                                                                                                      \
+            const int per_sm = tile_ctas_per_sm(pixel_norm_tile_kernel<XB, M, OB, false>, smem_all);                  \
+            if (per_sm < 1) { launched = false; break; }                                                              \
+            pixel_norm_tile_kernel<XB, M, OB, false><<<grid_for(tiles, per_sm), kThreads, smem_all, s>>>(p, cols, log2, map, slab); \
+        }                                                                                                             \
+    }                                                                                                                 \
     break
                 switch (variant) {
                     case 0: case 1: VRB_PN(false, kNormOnly, false);
