@@ -127,7 +127,7 @@ int vrb_pixel_norm(const void* x, int dtype, const void* scale, const void* shif
                    int fuse_silu, void* out, int out_dtype, int64_t outer, int64_t channels,
                    int64_t inner, float eps, vrb_stream stream);
 
-/* The shared-memory tile kernels (vrb_pixel_norm, vrb_l2_normalize) load their tiles with tensor-map copies
+/* The shared-memory tile kernels (vrb_pixel_norm, vrb_l2_normalize, vrb_rms_norm_axis) load their tiles with tensor-map copies
  * (cp.async.bulk.tensor, completion on an mbarrier) where the geometry allows.  vrb_set_tensor_map_tiles(0) makes them
  * use per-thread 16-byte asynchronous copies instead (same shared-memory layout, same results); returns the previous
  * setting.  Every wait on such a copy is bounded: a kernel whose wait runs out sets a flag in device memory and

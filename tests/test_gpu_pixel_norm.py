@@ -71,7 +71,7 @@ def test_quotient_guards_at_extreme_exponents(orc, gpu, l2):
 @pytest.mark.parametrize("shape", [(2, 128, 3, 8, 16), (1, 64, 1, 5, 8), (1, 1024, 2, 4, 12), (1, 512, 1, 7, 24), (3, 96, 2, 6, 40), (1, 4000, 1, 1, 16)])
 @pytest.mark.parametrize("dt", ["bf16", "f32"])
 def test_tensor_map_tiles_equal_per_thread_copies(orc, gpu, cuda_lib, shape, dt):
-    """The tile kernels load through tensor maps (cp.async.bulk.tensor + mbarrier) where slab and tile sizes allow, else
+    """The tile kernels (pixel_norm, l2_normalize, the axis RMSNorm) load through tensor maps (cp.async.bulk.tensor + mbarrier) where slab and tile sizes allow, else
     through per-thread 16-byte copies: the same bits either way, on full and ragged tiles, one and several slabs of
     channels, and no bounded wait may have run out."""
     import ctypes
@@ -81,11 +81,13 @@ def test_tensor_map_tiles_equal_per_thread_copies(orc, gpu, cuda_lib, shape, dt)
     x = to_torch(orc.tensor(synth.normal(shape, 0.2, 1.5, seed=shape[1] + 1), dt))
     vec = (shape[0], shape[1], 1, 1, 1)
     shift, scale = to_torch(orc.tensor(synth.normal(vec, 0, 0.2, seed=1))), to_torch(orc.tensor(synth.normal(vec, 0, 0.2, seed=2)))
+    gamma = to_torch(orc.tensor(synth.normal((shape[1],), 1.0, 0.1, seed=3)))
 
     def run():
         return [be.pixel_norm(x, 1, 1e-8), be.l2_normalize(x, 1, 1e-10), ops.fused_pixel_norm_modulate(be, x, shift, scale, 1e-8),
                 ops.fused_pixel_norm_modulate(be, x, shift, scale, 1e-8, out_dtype=torch.bfloat16),
-                ops.fused_pixel_norm_modulate(be, x, shift, scale, 1e-8, silu=False)]
+                ops.fused_pixel_norm_modulate(be, x, shift, scale, 1e-8, silu=False),
+                be.rms_norm(x, gamma, 1e-12, 1), ops.fused_rms_channel_silu(be, x, gamma, 1e-12)]
 
     previous = cuda_lib.vrb_set_tensor_map_tiles(1)
     try:

@@ -337,13 +337,13 @@ __global__ void __launch_bounds__(kThreads) gated_residual_typed_kernel(
     const unsigned stride = gridDim.x * blockDim.x;
     pdl_launch_dependents();
     pdl_wait();
-    // all-bf16 form: the chunk's column and gate vector are carried from step to step instead of being divided out of
+    // the chunk's column and gate vector are carried from step to step instead of being divided out of
     // the index (column = i % width_chunks, vector = (i / period) % vectors, period = rows_per_vector * width_chunks)
     const unsigned first = blockIdx.x * blockDim.x + threadIdx.x;
     const unsigned long long period = static_cast<unsigned long long>(rows_per_vector) * width_chunks;
     unsigned column = 0, vector = 0, column_step = 0, vector_step = 0;
     unsigned long long within = 0, within_step = 0;
-    if (RES_BF16 && BR_BF16 && STATE_BF16 && gate) {
+    if (gate) {
         column = first % width_chunks; within = first % period; vector = static_cast<unsigned>((first / period) % vectors);
         column_step = stride % width_chunks; within_step = stride % period; vector_step = static_cast<unsigned>((stride / period) % vectors);
     }
@@ -393,9 +393,13 @@ __global__ void __launch_bounds__(kThreads) gated_residual_typed_kernel(
                 load8_typed<RES_BF16>(res, static_cast<int64_t>(i) * 8, r[u]);
                 load8_typed<BR_BF16>(branch, static_cast<int64_t>(i) * 8, b[u]);
                 if (gate) {
-                    const unsigned row = i / width_chunks, chunk = i - row * width_chunks;
-                    const unsigned vec = vectors > 1 ? (row / rows_per_vector) % vectors : 0;
-                    load8<false>(gate, gate_dt, (static_cast<int64_t>(vec) * width_chunks + chunk) * 8, g[u]);
+                    load8<false>(gate, gate_dt, (static_cast<int64_t>(vector) * width_chunks + column) * 8, g[u]);
+                    column += column_step;
+                    if (column >= width_chunks) column -= width_chunks;
+                    within += within_step;
+                    vector += vector_step;
+                    if (within >= period) { within -= period; ++vector; }
+                    if (vector >= vectors) vector -= vectors;
                 }
             }
 #pragma unroll

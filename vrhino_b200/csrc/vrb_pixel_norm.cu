@@ -469,11 +469,12 @@ struct RmsAxisParams {
 constexpr int kSiluWindowLow = (127 - 8) << 7, kSiluWindowSpan = 12 << 7;   // in bf16 magnitude codes
 constexpr int kSiluWindowBytes = 2 * kSiluWindowSpan * 2;
 
-template <bool X_BF16, bool SILU>
-__global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisParams p, int cols, int cols_log2) {
+template <bool X_BF16, bool SILU, bool TMA>
+__global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisParams p, int cols, int cols_log2,
+                                                                 const __grid_constant__ CUtensorMap map, int slab) {
     constexpr int EPC = X_BF16 ? 8 : 4;
     constexpr int X_DT = X_BF16 ? VRB_BF16 : VRB_F32;
-    extern __shared__ __align__(16) uint4 tiles_buffer[];   // two tiles of [channels][cols], then the reduction scratch
+    extern __shared__ __align__(128) uint4 tiles_buffer[];   // two tiles of [channels][cols], then the reduction scratch
     const int channels = static_cast<int>(p.channels);
     const int positions = cols * EPC;
     const int tile_chunks = channels * cols;
@@ -481,6 +482,17 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
     float* const inverse = reinterpret_cast<float*>(partial + kLanes * positions);                          // [positions]
     constexpr bool kWindow = SILU && X_BF16;
     uint16_t* const window = reinterpret_cast<uint16_t*>(inverse + positions);                              // [2][kSiluWindowSpan]
+    // two mbarriers (TMA only) behind the window, 8-byte aligned: positions is a multiple of 4 and the window of 8 bytes
+    uint64_t* const barriers = reinterpret_cast<uint64_t*>(reinterpret_cast<char*>(inverse + positions) + (kWindow ? kSiluWindowBytes : 0));
+    if constexpr (TMA) {
+        if (threadIdx.x == 0) {
+            mbarrier_init(&barriers[0], 1);
+            mbarrier_init(&barriers[1], 1);
+            mbarrier_init_fence();
+        }
+        __syncthreads();
+    }
+    unsigned phases = 0;
     if constexpr (kWindow) {
         for (int e = threadIdx.x; e < 2 * kSiluWindowSpan; e += kThreads) {
             const uint32_t sign = e >= kSiluWindowSpan ? 0x8000u : 0u;
@@ -498,6 +510,18 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
     const int64_t row_step = static_cast<int64_t>(c_step) * inner_chunks;
 
     auto request = [&](uint32_t t, int b) {
+        if constexpr (TMA) {
+            if (t < tiles && threadIdx.x == 0) {
+                const uint32_t o = t / tiles_per_outer;
+                const uint32_t chunk0 = (t - o * tiles_per_outer) << cols_log2;
+                uint4* const dst = tiles_buffer + static_cast<size_t>(b) * tile_chunks;
+                async_proxy_fence();
+                mbarrier_expect_bytes(&barriers[b], static_cast<unsigned>(tile_chunks) * 16u);
+                for (int c = 0; c < channels; c += slab)
+                    tma_load_3d(dst + static_cast<size_t>(c) * cols, &map, static_cast<int>(chunk0 * EPC), c, static_cast<int>(o), &barriers[b]);
+            }
+            return;
+        }
         if (t < tiles) {
             const uint32_t o = t / tiles_per_outer;
             const uint32_t chunk0 = (t - o * tiles_per_outer) << cols_log2;
@@ -519,8 +543,17 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
         const uint32_t chunk0 = (t - o * tiles_per_outer) << cols_log2;
         const uint4* const tile = tiles_buffer + static_cast<size_t>(buffer) * tile_chunks;
         request(t + gridDim.x, buffer ^ 1);
-        async_copy_wait<1>();
-        __syncthreads();
+        if constexpr (TMA) {
+            const bool arrived = mbarrier_wait_bounded(&barriers[buffer], (phases >> buffer) & 1u, &g_async_wait_gave_up);
+            phases ^= 1u << buffer;
+            if (!__syncthreads_and(arrived)) {
+                if (t + gridDim.x < tiles) mbarrier_wait_bounded(&barriers[buffer ^ 1], (phases >> (buffer ^ 1)) & 1u, &g_async_wait_gave_up);
+                break;
+            }
+        } else {
+            async_copy_wait<1>();
+            __syncthreads();
+        }
         constexpr int PPW = X_BF16 ? 2 : 1;
         const int words_log2 = cols_log2 + 2, words = 1 << words_log2;
         const uint32_t* const tile_words = reinterpret_cast<const uint32_t*>(tile);
@@ -621,11 +654,25 @@ bool launch_rms_axis_tiles(const void* x, int dtype, const void* weight, int wei
             if (smem > (budget_ctas == 3 ? 72 * 1024 : 200 * 1024) || smem > kMaxTileBytes) continue;
             const int64_t tiles = outer * ((inner_chunks + cols - 1) / cols);
             bool launched = true;
-#define VRB_RA(XB, S)                                                                                     \
-    {                                                                                                     \
-        const int per_sm = tile_ctas_per_sm(rms_axis_tile_kernel<XB, S>, smem);                           \
-        if (per_sm < 1) launched = false;                                                                 \
-        else rms_axis_tile_kernel<XB, S><<<grid_for(tiles, per_sm), kThreads, smem, stream>>>(p, cols, log2); \
+            CUtensorMap map{};
+            int slab = 0;
+            if (g_tma_tiles.load(std::memory_order_relaxed) != 0 && (channels * cols) % 8 == 0) {
+                for (int candidate = static_cast<int>(channels < 256 ? channels : 256); candidate >= 8 && slab == 0; --candidate)
+                    if (channels % candidate == 0 && (static_cast<int64_t>(candidate) * cols) % 8 == 0) slab = candidate;
+                if (slab != 0 && !encode_tile_map(&map, x, dtype, outer, channels, inner, cols * epc, slab)) slab = 0;
+            }
+            const size_t smem_all = smem + 16;   // + the two mbarriers
+#define VRB_RA(XB, S)                                                                                                    \
+    {                                                                                                                    \
+        if (slab != 0) {                                                                                                 \
+            const int per_sm = tile_ctas_per_sm(rms_axis_tile_kernel<XB, S, true>, smem_all);                            \
+            if (per_sm < 1) launched = false;                                                                            \
+            else rms_axis_tile_kernel<XB, S, true><<<grid_for(tiles, per_sm), kThreads, smem_all, stream>>>(p, cols, log2, map, slab);  \
+        } else {                                                                                                         \
+            const int per_sm = tile_ctas_per_sm(rms_axis_tile_kernel<XB, S, false>, smem_all);                           \
+            if (per_sm < 1) launched = false;                                                                            \
+            else rms_axis_tile_kernel<XB, S, false><<<grid_for(tiles, per_sm), kThreads, smem_all, stream>>>(p, cols, log2, map, slab); \
+        }                                                                                                                \
     }
             if (dtype == VRB_BF16) { if (fuse_silu) VRB_RA(true, true) else VRB_RA(true, false) }
             else { if (fuse_silu) VRB_RA(false, true) else VRB_RA(false, false) }

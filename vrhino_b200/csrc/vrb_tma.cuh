@@ -1,7 +1,7 @@
 // Tensor-map (TMA) tile loads for the shared-memory tile kernels: one elected thread issues
 // cp.async.bulk.tensor copies of a [channels x positions] tile of a [outer, channels, inner] tensor and the CTA waits
 // on an mbarrier, instead of every thread issuing one 16-byte cp.async per chunk.  The maps cover this GPU's own
-// memory and the loads are plain (no cluster multicast).
+// memory; each copy has one destination, the issuing CTA.
 #pragma once
 
 #include <cuda.h>
