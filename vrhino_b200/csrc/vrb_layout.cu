@@ -12,7 +12,8 @@
 // concat, a permute that keeps the innermost axis, and a pad of outer axes move 16 bytes per
 // thread and step.  A permute that moves the innermost axis goes through shared-memory tiles over
 // (the input's innermost axis, the output's innermost axis), both sides coalesced; when either of
-// those axes is short it is walked element by element with coalesced stores.
+// those axes is short it is walked element by element with coalesced stores.  Element-unit walks with
+// long innermost rows (a pad of the innermost axes, a slice at an odd offset) take a warp per row.
 #include "vrb_common.cuh"
 
 #include <algorithm>
