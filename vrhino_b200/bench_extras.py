@@ -55,7 +55,7 @@ def _launch_table(launches, steps, warmup, peak):
 
 
 def single_gpu_configs(be, peak, steps=10, warmup=2):
-    """Headline configurations 3, 4 and 5 at full size on one GPU: per-launch device times."""
+    """Headline configurations 3, 4 and 5 at full size on one GPU, and the VAE / layout kernels: per-launch device times."""
     out = {}
     builders = {
         "wan22_step (config 3: D=5120 block chain, FP8 dequant 5120x13824, CFG + Euler on the F32 latent)":
@@ -64,6 +64,10 @@ def single_gpu_configs(be, peak, steps=10, warmup=2):
         "mochi_block, fewest launches (q+k as one launch, residual update + next pre-norm + tanh(gate) as one)":
             lambda: workloads.MochiBlock(be, tokens=44520).launches(merge_tail=True),
         "vae_group_norm_silu (config 5: [1,256,28,240,424] bf16, 32 groups)": lambda: workloads.VaeGroupNorm(be).launches(),
+        "ltx_vae_pixel_norm ([1,128,16,256,384] bf16: pixel_norm, + modulate + SiLU -> F32 / bf16)":
+            lambda: workloads.LtxVaeNorm(be, shape=(1, 128, 16, 256, 384)).launches(),
+        "wan_vae_rms_channel ([1,192,4,240,416] bf16, + SiLU)": lambda: workloads.WanVaeRmsChannel(be).launches(),
+        "layout_operators ([1,128,8,256,384] feature map, [1,1536,32760] patch embedding, bf16)": lambda: workloads.LayoutOps(be).launches(),
     }
     for name, build in builders.items():
         try:
