@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
                 } else {
                     in[0] = __uint_as_float(raw.x); in[1] = __uint_as_float(raw.y); in[2] = __uint_as_float(raw.z); in[3] = __uint_as_float(raw.w);
                 }
-                bool redo = false;
+                unsigned redo = 0;   // bit j: element j has to be evaluated with the exact forms
                 if constexpr (X_BF16) {
                     // the reciprocal form two elements at a time (packed F32 operations round like the scalar ones)
 #pragma unroll
@@ -316,19 +316,25 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
                         const unsigned long long c2 = fma_f32x2(fma_f32x2(pack_f32x2(-d[j], -d[j + 1]), q2, x2), r2, q2);
                         float c0, c1;
                         unpack_f32x2(c2, c0, c1);
-                        redo = redo || !(fabsf(c0) >= kQuotientFloor) || !(fabsf(c1) >= kQuotientFloor);
-                        v[j] = finish_quotient<true, MODE, OUT_BF16, false>(c0, ops, sh, redo);
-                        v[j + 1] = finish_quotient<true, MODE, OUT_BF16, false>(c1, ops, sh, redo);
+                        bool again0 = !(fabsf(c0) >= kQuotientFloor), again1 = !(fabsf(c1) >= kQuotientFloor);
+                        v[j] = finish_quotient<true, MODE, OUT_BF16, false>(c0, ops, sh, again0);
+                        v[j + 1] = finish_quotient<true, MODE, OUT_BF16, false>(c1, ops, sh, again1);
+                        redo |= (again0 ? 1u : 0u) << j | (again1 ? 2u : 0u) << j;
                     }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < EPC; ++j) v[j] = finish_tile<X_BF16, MODE, OUT_BF16, false>(in[j], d[j], r[j], ops, sh, redo);
+                    for (int j = 0; j < EPC; ++j) {
+                        bool again = false;
+                        v[j] = finish_tile<X_BF16, MODE, OUT_BF16, false>(in[j], d[j], r[j], ops, sh, again);
+                        redo |= (again ? 1u : 0u) << j;
+                    }
                 }
                 if constexpr (kHasShortForm<X_BF16, MODE, OUT_BF16>) {
-                    if (redo) {
+                    if (redo != 0) {   // rare: only the flagged elements, with the reference's operations one by one
                         bool unused = false;
 #pragma unroll
-                        for (int j = 0; j < EPC; ++j) v[j] = finish_tile<X_BF16, MODE, OUT_BF16, true>(in[j], d[j], r[j], ops, sh, unused);
+                        for (int j = 0; j < EPC; ++j)
+                            if ((redo >> j) & 1u) v[j] = finish_tile<X_BF16, MODE, OUT_BF16, true>(in[j], d[j], r[j], ops, sh, unused);
                     }
                 }
                 if constexpr (X_BF16) {
