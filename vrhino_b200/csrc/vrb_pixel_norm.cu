@@ -621,15 +621,30 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
                 return y;
             };
             if constexpr (X_BF16) {
+                // two elements at a time: F32 products rounded to bf16 as a pair (one conversion), the weight applied as a
+                // bf16 x bf16 product rounded once (exact product, same rounding as the F32 multiply + store of the
+                // reference), SiLU per element on the bf16 bits
                 const float inv[8] = {ia.x, ia.y, ia.z, ia.w, ib.x, ib.y, ib.z, ib.w};
                 const uint32_t wd[4] = {raw.x, raw.y, raw.z, raw.w};
-                float v[8];
+                const __nv_bfloat162 w2 = __floats2bfloat162_rn(w, w);     // w is on the bf16 grid already
+                uint32_t ow[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    v[2 * j] = finish_one(__uint_as_float(wd[j] << 16), inv[2 * j]);
-                    v[2 * j + 1] = finish_one(__uint_as_float(wd[j] & 0xffff0000u), inv[2 * j + 1]);
+                    __nv_bfloat162 y2 = __floats2bfloat162_rn(__fmul_rn(__uint_as_float(wd[j] << 16), inv[2 * j]),
+                                                              __fmul_rn(__uint_as_float(wd[j] & 0xffff0000u), inv[2 * j + 1]));
+                    if (weighted) y2 = __hmul2_rn(y2, w2);
+                    uint32_t word = *reinterpret_cast<const uint32_t*>(&y2);
+                    if constexpr (SILU) {
+                        auto silu_bits = [&](uint32_t bits) -> uint32_t {
+                            const uint32_t at = (bits & 0x7fffu) - static_cast<uint32_t>(kSiluWindowLow);
+                            if (at < static_cast<uint32_t>(kSiluWindowSpan)) return window[(bits >> 15) * kSiluWindowSpan + at];
+                            return float_to_bf16_bits(activation_value(VRB_SILU, bf16_bits_to_float(bits)));
+                        };
+                        word = silu_bits(word & 0xffffu) | (silu_bits(word >> 16) << 16);
+                    }
+                    ow[j] = word;
                 }
-                __stcs(out, make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])));
+                __stcs(out, make_uint4(ow[0], ow[1], ow[2], ow[3]));
             } else {
                 __stcs(reinterpret_cast<float4*>(out),
                        make_float4(finish_one(__uint_as_float(raw.x), ia.x), finish_one(__uint_as_float(raw.y), ia.y),
