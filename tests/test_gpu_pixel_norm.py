@@ -103,6 +103,25 @@ def test_tensor_map_tiles_equal_per_thread_copies(orc, gpu, cuda_lib, shape, dt)
     assert cuda_lib.vrb_async_wait_failures(ctypes.byref(failures)) == 0 and failures.value == 0
 
 
+def test_rms_channel_silu_over_every_bf16_argument(gpu):
+    """The axis RMSNorm's fused SiLU takes a bf16 argument: with x = 1 everywhere the normalised value is exactly 1 and
+    the argument of channel c is weight[c], so a weight vector running through all 65536 bf16 codes drives every
+    argument through the kernel; the result must be SiLU of that bf16 value as vrb_activation gives it."""
+    import torch
+    be, ops = gpu
+    channels = 2048
+    x = torch.ones(1, channels, 1, 1, 8, device="cuda", dtype=torch.bfloat16)
+    for start in range(0, 1 << 16, channels):
+        codes = torch.arange(start, start + channels, device="cuda", dtype=torch.int32)
+        w = codes.to(torch.int16).view(torch.bfloat16)
+        got = ops.fused_rms_channel_silu(be, x, w.float(), 1e-12)
+        want = be.activation(w, ops.SILU)
+        g, e = got.view(channels, 8).view(torch.int16), want.view(torch.int16)
+        nan = lambda t: (t & 0x7FFF) > 0x7F80
+        same = (g[:, 0] == e) | (nan(g[:, 0]) & nan(e))
+        assert bool(same.all()) and bool((g == g[:, :1]).all()), f"codes {codes[~same][:8].tolist()} differ"
+
+
 def test_bf16_store_silu_over_every_f32_argument(gpu):
     """pixel_norm -> modulate -> SiLU with a bf16 result evaluates SiLU through approximate special functions wherever
     the bf16 rounding provably cannot differ, else exactly.  All 2^32 F32 arguments go through the kernel here: with

@@ -486,7 +486,7 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
     const int tile_chunks = channels * cols;
     double* const partial = reinterpret_cast<double*>(tiles_buffer + 2 * static_cast<size_t>(tile_chunks));   // [kLanes][positions]
     float* const inverse = reinterpret_cast<float*>(partial + kLanes * positions);                          // [positions]
-    constexpr bool kWindow = SILU && X_BF16;
+    constexpr bool kWindow = false;   // (the bf16 SiLU goes through silu_approximate; no table)
     uint16_t* const window = reinterpret_cast<uint16_t*>(inverse + positions);                              // [2][kSiluWindowSpan]
     // two mbarriers (TMA only) behind the window, 8-byte aligned: positions is a multiple of 4 and the window of 8 bytes
     uint64_t* const barriers = reinterpret_cast<uint64_t*>(reinterpret_cast<char*>(inverse + positions) + (kWindow ? kSiluWindowBytes : 0));
@@ -635,12 +635,17 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
                     if (weighted) y2 = __hmul2_rn(y2, w2);
                     uint32_t word = *reinterpret_cast<const uint32_t*>(&y2);
                     if constexpr (SILU) {
-                        auto silu_bits = [&](uint32_t bits) -> uint32_t {
-                            const uint32_t at = (bits & 0x7fffu) - static_cast<uint32_t>(kSiluWindowLow);
-                            if (at < static_cast<uint32_t>(kSiluWindowSpan)) return window[(bits >> 15) * kSiluWindowSpan + at];
-                            return float_to_bf16_bits(activation_value(VRB_SILU, bf16_bits_to_float(bits)));
-                        };
-                        word = silu_bits(word & 0xffffu) | (silu_bits(word >> 16) << 16);
+                        // the approximate form wherever its bf16 rounding provably equals the exact expression's
+                        // (silu_approximate above; all 65536 bf16 arguments are checked by tests/test_gpu_pixel_norm.py),
+                        // else the exact expression
+                        const float lo = __uint_as_float(word << 16), hi = __uint_as_float(word & 0xffff0000u);
+                        bool again_lo = false, again_hi = false;
+                        float s_lo = silu_approximate(lo, again_lo), s_hi = silu_approximate(hi, again_hi);
+                        if (again_lo || again_hi) {
+                            if (again_lo) s_lo = activation_value(VRB_SILU, lo);
+                            if (again_hi) s_hi = activation_value(VRB_SILU, hi);
+                        }
+                        word = pack_bf16x2(s_lo, s_hi);
                     }
                     ow[j] = word;
                 }
