@@ -469,12 +469,6 @@ struct RmsAxisParams {
     float eps;
 };
 
-// SiLU of a bf16 value whose magnitude lies in [2^-8, 2^4) -- nearly every normalised activation --
-// is read from a 6 KB window of the function table (both signs, 12 exponents x 128 mantissas), filled
-// per CTA with the expression the direct evaluation uses; other magnitudes are evaluated directly.
-constexpr int kSiluWindowLow = (127 - 8) << 7, kSiluWindowSpan = 12 << 7;   // in bf16 magnitude codes
-constexpr int kSiluWindowBytes = 2 * kSiluWindowSpan * 2;
-
 template <bool X_BF16, bool SILU, bool TMA>
 __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisParams p, int cols, int cols_log2,
                                                                  const __grid_constant__ CUtensorMap map, int slab) {
@@ -486,10 +480,8 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
     const int tile_chunks = channels * cols;
     double* const partial = reinterpret_cast<double*>(tiles_buffer + 2 * static_cast<size_t>(tile_chunks));   // [kLanes][positions]
     float* const inverse = reinterpret_cast<float*>(partial + kLanes * positions);                          // [positions]
-    constexpr bool kWindow = false;   // (the bf16 SiLU goes through silu_approximate; no table)
-    uint16_t* const window = reinterpret_cast<uint16_t*>(inverse + positions);                              // [2][kSiluWindowSpan]
-    // two mbarriers (TMA only) behind the window, 8-byte aligned: positions is a multiple of 4 and the window of 8 bytes
-    uint64_t* const barriers = reinterpret_cast<uint64_t*>(reinterpret_cast<char*>(inverse + positions) + (kWindow ? kSiluWindowBytes : 0));
+    // two mbarriers (TMA only) behind the scratch, 8-byte aligned: positions is a multiple of 4
+    uint64_t* const barriers = reinterpret_cast<uint64_t*>(inverse + positions);
     if constexpr (TMA) {
         if (threadIdx.x == 0) {
             mbarrier_init(&barriers[0], 1);
@@ -499,14 +491,6 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
         __syncthreads();
     }
     unsigned phases = 0;
-    if constexpr (kWindow) {
-        for (int e = threadIdx.x; e < 2 * kSiluWindowSpan; e += kThreads) {
-            const uint32_t sign = e >= kSiluWindowSpan ? 0x8000u : 0u;
-            const uint32_t code = sign | static_cast<uint32_t>(kSiluWindowLow + (e >= kSiluWindowSpan ? e - kSiluWindowSpan : e));
-            window[e] = static_cast<uint16_t>(float_to_bf16_bits(activation_value(VRB_SILU, bf16_bits_to_float(code))));
-        }
-        // visible to every thread after the first barrier of the tile loop
-    }
     // fewer than 2^31 tiles and chunks per channel row (the launcher checks); a thread's chunks all lie in chunk
     // column k and its channel advances by kThreads / cols per step, so addresses are advanced, not recomputed
     const uint32_t inner_chunks = static_cast<uint32_t>(p.inner / EPC);
@@ -608,16 +592,7 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
                 float y = __fmul_rn(v, inv);
                 if constexpr (X_BF16) y = round_to_bf16(y);
                 if (weighted) { y = __fmul_rn(y, w); if constexpr (X_BF16) y = round_to_bf16(y); }
-                if constexpr (kWindow) {
-                    const uint32_t bits = __float_as_uint(y) >> 16;   // y is on the bf16 grid here
-                    const uint32_t at = (bits & 0x7fffu) - static_cast<uint32_t>(kSiluWindowLow);
-                    if (at < static_cast<uint32_t>(kSiluWindowSpan))
-                        y = bf16_bits_to_float(window[(bits >> 15) * kSiluWindowSpan + at]);
-                    else
-                        y = activation_value(VRB_SILU, y);
-                } else if constexpr (SILU) {
-                    y = activation_value(VRB_SILU, y);
-                }
+                if constexpr (SILU) y = activation_value(VRB_SILU, y);
                 return y;
             };
             if constexpr (X_BF16) {
@@ -675,8 +650,7 @@ bool launch_rms_axis_tiles(const void* x, int dtype, const void* weight, int wei
     for (int budget_ctas : {3, 1}) {
         for (int cols = 8, log2 = 3; cols >= 1; cols >>= 1, --log2) {
             if (cols > 1 && cols / 2 >= inner_chunks) continue;
-            const size_t smem = 2 * static_cast<size_t>(channels) * cols * 16 + static_cast<size_t>(cols) * epc * (kLanes * 8 + 4) +
-                                (fuse_silu && dtype == VRB_BF16 ? kSiluWindowBytes : 0);
+            const size_t smem = 2 * static_cast<size_t>(channels) * cols * 16 + static_cast<size_t>(cols) * epc * (kLanes * 8 + 4);
             if (smem > (budget_ctas == 3 ? 72 * 1024 : 200 * 1024) || smem > kMaxTileBytes) continue;
             const int64_t tiles = outer * ((inner_chunks + cols - 1) / cols);
             bool launched = true;
