@@ -143,7 +143,7 @@ def reference_cuda_arm():
     if not ref.available_cuda():
         return {"unavailable": "oracle/_ref/libvrhino_ref_cuda.so is not built"}
     out = {}
-    for config in ("wan21", "wan22_sampler", "vae_gn", "mochi"):
+    for config in ("wan21", "wan22_sampler", "vae_gn", "mochi", "vae_layout"):
         try:
             proc = subprocess.run([sys.executable, "-m", "oracle.ref_timing", "--config", config], cwd=ROOT,
                                   capture_output=True, text=True, timeout=420)

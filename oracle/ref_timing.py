@@ -6,7 +6,7 @@ group_norm -> activation, quantised copy_to_device, cfg_combine -> euler_update)
 TEST / BASELINE INFRASTRUCTURE ONLY: this is the "GPU number to beat", reported beside the
 library's own; nothing in the product path uses it.  Run as a process of its own
 
-    python -m oracle.ref_timing [--config wan21|wan22_sampler|vae_gn|mochi] [--tokens N] [--repeat R]
+    python -m oracle.ref_timing [--config wan21|wan22|wan22_sampler|vae_gn|mochi|vae_layout] [--tokens N] [--repeat R]
 
 and it prints one JSON object.  Each seam is bracketed by a device synchronisation and timed with the
 host clock (the seams take 0.1-3 ms, far above launch latency); where the reference's profiler is
@@ -214,9 +214,53 @@ def mochi(rc, tokens, repeat, seed=3):
     return t.result(tokens=S)
 
 
+def vae_layout(rc, repeat, frames=8, seed=4):
+    """LTX / Wan VAE kernels outside the headline chains: pixel_norm -> modulate -> silu (ltx.cpp:221-227), the two pads in
+    front of an LTX convolution (ltx.cpp:205-215), rms_channel + silu of the Wan VAE, and the Wan patch embedding's
+    transposition (wan.cpp:159), on the shapes `workloads --config 10 / 12 / 13` use."""
+    rng = Pool(seed)
+    P = ref.POLICY_BF16
+    t = Timer(rc, repeat)
+    shape = (1, 128, frames, 256, 384)
+    n = int(np.prod(shape))
+    x = rc.upload(_bf16_bits(rng.standard_normal(shape, dtype=np.float32) * 1.5 + 0.2), ref.BF16)
+    shift = rc.upload((0.2 * rng.standard_normal((1, 128, 1, 1, 1))).astype(np.float32), ref.F32)
+    scale = rc.upload((0.2 * rng.standard_normal((1, 128, 1, 1, 1))).astype(np.float32), ref.F32)
+
+    def norm_chain():
+        a = rc.pixel_norm(x, 1, 1e-8)
+        b = rc.modulate(P, a, shift, scale)
+        return [a, b, rc.activation(b, SILU)]
+
+    def pads():
+        a = rc.pad(x, [0, 0, 0, 0, 1, 1], 0.0, True)
+        return [a, rc.pad(a, [1, 1, 1, 1], 0.0, False)]
+
+    t.seam("pixel_norm", n * 4, lambda: [rc.pixel_norm(x, 1, 1e-8)])
+    t.seam("pixel_norm -> modulate -> silu (F32 result)", n * 6, norm_chain)
+    t.seam("pad T replicate, then pad H, W zero", n * 2 + n * 2 * (frames + 2) * 258 * 386 // (frames * 256 * 384), pads)
+    t.seam("permute frames first (0,2,1,3,4)", n * 4, lambda: [rc.permute(x, (0, 2, 1, 3, 4))])
+    rc.free(x)
+    wan = (1, 192, 4, 240, 416)
+    m = int(np.prod(wan))
+    y = rc.upload(_bf16_bits(rng.standard_normal(wan, dtype=np.float32)), ref.BF16)
+    gamma = rc.upload((1 + 0.1 * rng.standard_normal(192)).astype(np.float32), ref.F32)
+
+    def rms_silu():
+        a = rc.rms_norm(y, gamma, 1e-12, axis=1)
+        return [a, rc.activation(a, SILU)]
+
+    t.seam("rms_channel", m * 4, lambda: [rc.rms_norm(y, gamma, 1e-12, axis=1)])
+    t.seam("rms_channel -> silu", m * 4, rms_silu)
+    rc.free(y)
+    patches = rc.upload(_bf16_bits(rng.standard_normal((1, 1536, 32760), dtype=np.float32)), ref.BF16)
+    t.seam("permute [1,1536,32760] -> [1,32760,1536]", 1536 * 32760 * 4, lambda: [rc.permute(patches, (0, 2, 1))])
+    return t.result(shape=list(shape))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default="wan21", choices=["wan21", "wan22", "wan22_sampler", "vae_gn", "mochi"])
+    ap.add_argument("--config", default="wan21", choices=["wan21", "wan22", "wan22_sampler", "vae_gn", "mochi", "vae_layout"])
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--frames", type=int, default=28)
     ap.add_argument("--repeat", type=int, default=3)
@@ -233,6 +277,8 @@ def main():
         out = sampler_and_dequant(rc, a.repeat)
     elif a.config == "vae_gn":
         out = vae_group_norm(rc, a.repeat, frames=a.frames)
+    elif a.config == "vae_layout":
+        out = vae_layout(rc, a.repeat)
     else:
         out = mochi(rc, a.tokens or 44520, a.repeat)
     out["config"] = a.config

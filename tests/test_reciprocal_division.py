@@ -1,4 +1,4 @@
-"""The division-free quotient of the pixel_norm / l2_normalize tile kernels (vrb_pixel_norm.cu, quotient_of_bf16)
+"""The division-free quotient of the pixel_norm / l2_normalize tile kernels (vrb_pixel_norm.cu: q = x r, e = x - d q, q + e r with r = RN(1 / d))
 is the correctly rounded quotient: all 2^30 (bf16 significand, F32 significand) pairs, enumerated on the host with
 IEEE single-precision arithmetic (no contraction), plus the negative control without the correction step."""
 import os
