@@ -584,7 +584,8 @@ int run_plan(const void* in, void* out, int dtype, const Plan& raw, float pad_va
         memcpy(&pattern, &pad_value, 4);
     }
     const uint4 fill = make_uint4(pattern, pattern, pattern, pattern);
-    bool contiguous_output = aligned16(destination) && count >= 64;
+    // (a 4-byte aligned source: the chunk kernel's word loads may start one 2-byte element before a run, never before the tensor)
+    bool contiguous_output = aligned16(destination) && count >= 64 && reinterpret_cast<uintptr_t>(source) % 4 == 0;
     {
         int64_t running = 1;
         for (int d = last; d >= 0 && contiguous_output; --d) {

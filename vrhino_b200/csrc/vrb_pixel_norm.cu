@@ -317,8 +317,28 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
                         float c0, c1;
                         unpack_f32x2(c2, c0, c1);
                         bool again0 = !(fabsf(c0) >= kQuotientFloor), again1 = !(fabsf(c1) >= kQuotientFloor);
-                        v[j] = finish_quotient<true, MODE, OUT_BF16, false>(c0, ops, sh, again0);
-                        v[j + 1] = finish_quotient<true, MODE, OUT_BF16, false>(c1, ops, sh, again1);
+                        if constexpr (MODE == kNormOnly) {
+                            v[j] = c0;      // the bf16 store rounds
+                            v[j + 1] = c1;
+                        } else {
+                            // rounding to bf16 as a pair (one conversion); modulate: a multiplication and an addition,
+                            // each rounded
+                            const __nv_bfloat162 y2 = __floats2bfloat162_rn(c0, c1);
+                            const uint32_t yw = *reinterpret_cast<const uint32_t*>(&y2);
+                            c0 = __fadd_rn(__fmul_rn(__uint_as_float(yw << 16), ops), sh);
+                            c1 = __fadd_rn(__fmul_rn(__uint_as_float(yw & 0xffff0000u), ops), sh);
+                            if constexpr (MODE == kModulateSilu) {
+                                if constexpr (OUT_BF16) {
+                                    c0 = silu_approximate(c0, again0);
+                                    c1 = silu_approximate(c1, again1);
+                                } else {
+                                    c0 = activation_value(VRB_SILU, c0);
+                                    c1 = activation_value(VRB_SILU, c1);
+                                }
+                            }
+                            v[j] = c0;
+                            v[j + 1] = c1;
+                        }
                         redo |= (again0 ? 1u : 0u) << j | (again1 ? 2u : 0u) << j;
                     }
                 } else {
