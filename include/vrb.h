@@ -180,6 +180,14 @@ int vrb_pad(const void* x, void* out, int dtype, int rank, const int64_t* shape,
 int vrb_pad_axes(const void* x, void* out, int dtype, int rank, const int64_t* shape, const int64_t* before,
                  const int64_t* after, float value, const int* replicate_axes, vrb_stream stream);
 
+/* CudaBackend::interpolate_nearest (:5010-5016, interpolate_kernel :2033-2045): out[c] = x[floor(c_d * in_shape[d] /
+ * out_shape[d]) along every axis d]; the caller computes out_shape (the reference: floor(extent * factor) on the
+ * trailing axes).  At most three axes may differ between the shapes, and they must be the trailing ones after any
+ * number of equal leading axes.  The Wan VAE's 2x spatial upsampling (wan.cpp:268) takes a form that reads 16 bytes
+ * and writes them doubled into both output rows. */
+int vrb_interpolate_nearest(const void* x, void* out, int dtype, int rank, const int64_t* in_shape,
+                            const int64_t* out_shape, vrb_stream stream);
+
 /* CudaBackend::sinusoidal_embedding (:4190-4196, sinusoidal_kernel :1178-1198): positions [count] ->
  * out [count, width].  half = width / 2; logical column l = flip ? (column + half) % (2 half) : column;
  * out = (l < half ? sin : cos)(position * exp(-ln(10000) * (l % half) / (half - downscale))); an odd last

@@ -276,6 +276,24 @@ class OracleBackend:
         fill = tensor(np.array(value, dtype=np.float32), x.dtype).data.reshape(())
         return T(np.pad(x.data, widths, mode="constant", constant_values=fill), x.dtype)
 
+    def interpolate_nearest(self, raw: T, factors) -> T:
+        """CudaBackend::interpolate_nearest (:5010-5016, interpolate_kernel :2033-2045): the trailing len(factors) axes
+        grow to floor(extent * factor); every output coordinate c reads input coordinate c * in // out."""
+        if len(factors) > len(raw.shape) - 2:
+            raise ValueError("interpolate factor rank mismatch")
+        if any(f <= 0 for f in factors):
+            raise ValueError("Invalid interpolation factor")
+        x = self.copy_to_device(raw, self._dtype_of(raw))
+        data = x.data
+        start = len(x.shape) - len(factors)
+        for i, f in enumerate(factors):
+            axis = start + i
+            size = x.shape[axis]
+            grown = int(np.floor(size * float(f)))
+            index = (np.arange(grown, dtype=np.int64) * size) // max(grown, 1)
+            data = np.take(data, index, axis=axis)
+        return T(data, x.dtype)
+
     def sinusoidal_embedding(self, raw: T, width: int, flip: bool, downscale: float, frequency_f64: bool) -> T:
         """CudaBackend::sinusoidal_embedding (:4190-4196, sinusoidal_kernel :1178-1198).  The single-precision path
         rounds after every operation like the kernel; exp / sin / cos come from the host's libm, whose last bit

@@ -150,6 +150,15 @@ CASES = [
      "inputs": {"video": (1, 3, 2, 4, 8), "map": (2, 3, 5)},
      "steps": [("causal", "pad", ["video"], ((0, 0, 0, 0, 1, 1), 0.0, True)), ("spatial_value", "pad", ["map"], ((2, 1, 1, 2), 0.1, False)),
                ("spatial_edge", "pad", ["map"], ((2, 1, 1, 2), 0.0, True)), ("nothing", "pad", ["map"], ((0, 0), 0.0, False))]},
+    {"name": "layout_nearest_bf16", "kind": "layout", "dt": "bf16", "seed": 39,
+     "inputs": {"frames": (3, 4, 6, 16), "video": (1, 2, 3, 5, 7), "row": (1, 1, 24)},
+     "steps": [("wan_upsample", "nearest", ["frames"], (2.0, 2.0)), ("width_only", "nearest", ["frames"], (1.0, 2.0)),
+               ("all_three", "nearest", ["video"], (2.0, 2.0, 2.0)), ("spatial_of_video", "nearest", ["video"], (1.0, 2.0, 2.0)),
+               ("fractional", "nearest", ["video"], (1.5, 0.5)), ("shrink", "nearest", ["row"], (0.5,)), ("triple", "nearest", ["row"], (3.0,))]},
+    {"name": "layout_nearest_f32", "kind": "layout", "dt": "f32", "seed": 40,
+     "inputs": {"frames": (2, 3, 5, 8), "odd": (1, 2, 3, 5)},
+     "steps": [("wan_upsample", "nearest", ["frames"], (2.0, 2.0)), ("odd_doubled", "nearest", ["odd"], (2.0, 2.0)),
+               ("fractional", "nearest", ["odd"], (2.5, 1.4))]},
     {"name": "layout_sinusoidal_f32", "kind": "layout", "dt": "f32", "seed": 37,
      "inputs": {"positions": (0.0, 1.0, 0.5, 999.0, 37.25, -2.0, 1000.0, 250.0)},
      "steps": [("timestep_256", "sinusoidal", ["positions"], (256, True, 0.0, False)), ("odd_width", "sinusoidal", ["positions"], (7, False, 1.0, False)),
@@ -175,6 +184,8 @@ def run_layout(case, values, api, grab):
             values[name] = api.concat(x, args)
         elif op == "pad":
             values[name] = api.pad(x[0], list(args[0]), args[1], args[2])
+        elif op == "nearest":
+            values[name] = api.interpolate_nearest(x[0], list(args))
         elif op == "sinusoidal":
             values[name] = api.sinusoidal_embedding(x[0], *args)
         else:
@@ -287,6 +298,7 @@ def run_reference(rc, case):
         class Api:
             permute = staticmethod(rc.permute); slice = staticmethod(rc.slice); concat = staticmethod(rc.concat)
             pad = staticmethod(rc.pad); sinusoidal_embedding = staticmethod(rc.sinusoidal_embedding)
+            interpolate_nearest = staticmethod(rc.interpolate_nearest)
         run_layout(case, dict(h), Api, lambda name, handle: grab(name, handle, (int(rc.lib.refc_numel(ctypes.c_int64(handle))),)))
     elif k == "depth_to_space":
         b, c, t, h_, w = case["shape"]

@@ -148,6 +148,49 @@ def test_edge_time_pad_equals_the_two_pads(orc, gpu, shape, temporal, pad_h, pad
     assert np.array_equal(_bits(torch, got), _bits(torch, two))
 
 
+NEAREST = [
+    ((3, 4, 6, 16), (2.0, 2.0)),            # doubled width and height: 16 bytes in, 2 x 32 bytes out
+    ((3, 4, 6, 16), (1.0, 2.0)),            # doubled width only
+    ((2, 3, 5, 8), (2.0, 2.0)),
+    ((1, 2, 3, 5), (2.0, 2.0)),             # odd width: a warp per row
+    ((1, 2, 3, 5, 7), (2.0, 2.0, 2.0)),     # three resized axes
+    ((1, 2, 3, 5, 7), (1.0, 2.0, 2.0)),
+    ((1, 2, 3, 5, 7), (1.5, 0.5)),          # fractional factors, shrinking
+    ((1, 1, 24), (0.5,)), ((1, 1, 24), (3.0,)), ((2, 3, 40), (2.0,)),
+    ((1, 2, 3, 5), (2.5, 1.4)),
+]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("shape,factors", NEAREST, ids=[f"{s}x{f}".replace(" ", "") for s, f in NEAREST])
+def test_interpolate_nearest(orc, gpu, shape, factors, dt):
+    import torch
+    be, _ = gpu
+    x, ox = _pair(orc, torch, shape, dt, 10)
+    got = be.interpolate_nearest(x, list(factors))
+    want = orc.OracleBackend().interpolate_nearest(ox, list(factors))
+    assert tuple(got.shape) == want.shape
+    assert np.array_equal(_bits(torch, got), _orc_bits(want))
+
+
+def test_interpolate_nearest_at_size_and_rules(gpu):
+    """The Wan VAE's 2x spatial upsampling of [frames, C, H, W] (wan.cpp:266-268) against torch's nearest resize, in
+    both dtypes; the reference's argument rules."""
+    import torch
+    from vrhino_b200._lib import VrbError
+    be, _ = gpu
+    x = torch.randn(6, 96, 120, 208, device="cuda")
+    for t in (x, x.to(torch.bfloat16)):
+        got = be.interpolate_nearest(t, [2.0, 2.0])
+        want = torch.nn.functional.interpolate(t, scale_factor=2.0, mode="nearest")
+        assert torch.equal(got, want)
+        assert torch.equal(be.interpolate_nearest(t, [1.0, 2.0]), torch.nn.functional.interpolate(t, scale_factor=(1.0, 2.0), mode="nearest"))
+    with pytest.raises(VrbError, match="interpolate factor rank mismatch"):
+        be.interpolate_nearest(x, [2.0, 2.0, 2.0])
+    with pytest.raises(VrbError, match="Invalid interpolation factor"):
+        be.interpolate_nearest(x, [0.0, 2.0])
+
+
 def test_argument_rules(orc, gpu):
     import torch
     from vrhino_b200._lib import VrbError

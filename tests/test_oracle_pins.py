@@ -240,6 +240,8 @@ def test_layout_known_answers(orc, be):
     close(flat(be.concat([t((1, 1, 2), [1, 2]), t((2, 1, 2), [3, 4, 5, 6])], 0)), [1, 2, 3, 4, 5, 6])
     close(flat(be.slice(t((2, 4), [0, 1, 2, 3, 4, 5, 6, 7]), 1, 1, 3)), [1, 2, 5, 6])
     close(flat(be.slice(t((3, 2), [0, 1, 2, 3, 4, 5]), 0, 1, 3)), [2, 3, 4, 5])
+    close(flat(be.interpolate_nearest(t((1, 1, 2), [1, 2]), [2])), [1, 1, 2, 2])                       # primitive_tests.cpp:540-541
+    close(flat(be.interpolate_nearest(t((1, 1, 1, 2), [1, 2]), [2, 2])), [1, 1, 2, 2, 1, 1, 2, 2])
     close(flat(be.pad(t((1, 2), [1, 2]), [1, 1], 0.0, False)), [0, 1, 2, 0])
     close(flat(be.pad(t((1, 1, 2), [1, 2]), [1, 0, 1, 0], -1.0, False)), [-1, -1, -1, -1, 1, 2])
     close(flat(be.pad(t((1, 2), [1, 2]), [1, 2], 0.0, True)), [1, 1, 2, 2, 2])

@@ -1,4 +1,4 @@
-// Layout operators: permute, slice, concat, pad and the sinusoidal position embedding
+// Layout operators: permute, slice, concat, pad, nearest-neighbour resize and the sinusoidal position embedding
 // (CudaBackend::permute / concat / slice, native/src/backend/cuda/cuda_backend.cu:3936-3970, kernels
 // :767-813; CudaBackend::pad :4875-4883, pad_kernel :1771-1788; CudaBackend::sinusoidal_embedding
 // :4190-4196, sinusoidal_kernel :1178-1198).  Index work only (plus one F32 -> bf16 rounding of the
@@ -637,6 +637,70 @@ bool valid_shape(int rank, const int64_t* shape) {
     return true;
 }
 
+// ---- nearest-neighbour resize --------------------------------------------------------------------------
+// CudaBackend::interpolate_nearest (native/src/backend/cuda/cuda_backend.cu:5010-5016, interpolate_kernel :2033-2045):
+// out[c_0 .. c_{r-1}] = x[floor(c_d * in_d / out_d) for every d].  Leading axes of equal extent are planes.
+struct Resize {
+    int64_t planes;                 // product of the leading axes the resize leaves alone
+    int rank;                       // resized axes (at most 3), outermost first
+    int64_t in_extent[3], out_extent[3];
+};
+
+// General factors: a warp per output row (the row index decomposed and mapped once), lanes over the row's elements.
+template <typename E>
+__global__ void __launch_bounds__(kThreads) resize_rows_kernel(const E* __restrict__ in, E* __restrict__ out, const Resize g,
+                                                               const uint32_t rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x % 32;
+    const uint32_t warps = gridDim.x * (kThreads / 32);
+    const int last = g.rank - 1;
+    const uint32_t in_w = static_cast<uint32_t>(g.in_extent[last]), out_w = static_cast<uint32_t>(g.out_extent[last]);
+    for (uint32_t row = blockIdx.x * (kThreads / 32) + threadIdx.x / 32; row < rows; row += warps) {
+        uint32_t remaining = row;
+        int64_t source = 0, stride = in_w;
+        for (int d = last - 1; d >= 0; --d) {
+            const uint32_t extent = static_cast<uint32_t>(g.out_extent[d]);
+            const uint32_t quotient = remaining / extent;
+            const uint32_t coordinate = remaining - quotient * extent;
+            remaining = quotient;
+            source += (static_cast<int64_t>(coordinate) * g.in_extent[d] / g.out_extent[d]) * stride;
+            stride *= g.in_extent[d];
+        }
+        source += static_cast<int64_t>(remaining) * stride;   // the plane
+        const E* const src = in + source;
+        E* const dst = out + static_cast<int64_t>(row) * out_w;
+        for (uint32_t j = lane; j < out_w; j += 32)
+            dst[j] = src[static_cast<uint32_t>(static_cast<uint64_t>(j) * in_w / out_w)];
+    }
+}
+
+// Exactly twice the width (and once or twice the height): a thread reads 16 bytes of an input row and writes them
+// doubled -- 32 adjacent bytes -- into one output row (TWO_ROWS: into the two output rows that copy this input row).
+template <typename E, bool TWO_ROWS>
+__global__ void __launch_bounds__(kThreads) resize_double_kernel(const uint4* __restrict__ in, char* __restrict__ out,
+                                                                 const uint32_t chunks_per_row, const uint32_t total_chunks) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t step = gridDim.x * kThreads;
+    for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < total_chunks; i += step) {
+        const uint4 v = __ldcs(in + i);
+        uint4 lo, hi;
+        if constexpr (sizeof(E) == 2) {
+            lo = make_uint4(__byte_perm(v.x, v.x, 0x1010), __byte_perm(v.x, v.x, 0x3232), __byte_perm(v.y, v.y, 0x1010), __byte_perm(v.y, v.y, 0x3232));
+            hi = make_uint4(__byte_perm(v.z, v.z, 0x1010), __byte_perm(v.z, v.z, 0x3232), __byte_perm(v.w, v.w, 0x1010), __byte_perm(v.w, v.w, 0x3232));
+        } else {
+            lo = make_uint4(v.x, v.x, v.y, v.y);
+            hi = make_uint4(v.z, v.z, v.w, v.w);
+        }
+        const uint32_t row = i / chunks_per_row, chunk = i - row * chunks_per_row;
+        const int64_t row_bytes = static_cast<int64_t>(chunks_per_row) * 32;
+        char* const to = out + (TWO_ROWS ? 2 : 1) * static_cast<int64_t>(row) * row_bytes + static_cast<int64_t>(chunk) * 32;
+        store32_aligned(to, lo, hi);
+        if constexpr (TWO_ROWS) store32_aligned(to + row_bytes, lo, hi);
+    }
+}
+
 // ---- sinusoidal embedding ------------------------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ float load_position(const T* p, int64_t i) {
@@ -795,6 +859,56 @@ extern "C" int vrb_pad_axes(const void* x, void* out, int dtype, int rank, const
                             const int64_t* after, float value, const int* replicate_axes, vrb_stream stream) {
     VRB_REQUIRE(replicate_axes, VRB_ERR_INVALID, "pad: null mode array");
     return pad_any(x, out, dtype, rank, shape, before, after, value, replicate_axes, 0, as_stream(stream));
+}
+
+extern "C" int vrb_interpolate_nearest(const void* x, void* out, int dtype, int rank, const int64_t* in_shape, const int64_t* out_shape,
+                                       vrb_stream stream) {
+    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "interpolate_nearest: dtype must be F32 or BF16");
+    VRB_REQUIRE(valid_shape(rank, in_shape) && valid_shape(rank, out_shape) && rank > 0, VRB_ERR_INVALID, "interpolate_nearest: invalid shape");
+    int64_t count = 1, source_count = 1;
+    for (int d = 0; d < rank; ++d) { count *= out_shape[d]; source_count *= in_shape[d]; }
+    if (count == 0) return VRB_OK;
+    VRB_REQUIRE(source_count > 0, VRB_ERR_INVALID, "Invalid interpolation factor");
+    VRB_REQUIRE(x && out, VRB_ERR_INVALID, "interpolate_nearest: null tensor");
+    Resize g{};
+    g.planes = 1;
+    int first = 0;
+    while (first < rank - 1 && in_shape[first] == out_shape[first]) g.planes *= in_shape[first++];
+    VRB_REQUIRE(rank - first <= 3, VRB_ERR_UNSUPPORTED, "interpolate_nearest: at most three resized axes");
+    g.rank = rank - first;
+    for (int d = first; d < rank; ++d) { g.in_extent[d - first] = in_shape[d]; g.out_extent[d - first] = out_shape[d]; }
+    const int64_t element = static_cast<int64_t>(dtype_bytes(dtype));
+    const int last = g.rank - 1;
+    cudaStream_t s = as_stream(stream);
+    const int64_t in_w = g.in_extent[last], out_w = g.out_extent[last];
+    // twice the width, once or twice the height, nothing else resized
+    bool doubled = out_w == 2 * in_w && (in_w * element) % 16 == 0 && aligned16(x) && (reinterpret_cast<uintptr_t>(out) & 31u) == 0 &&
+                   source_count * element / 16 < (int64_t{1} << 32);
+    bool two_rows = false;
+    if (doubled && g.rank >= 2) {
+        two_rows = g.out_extent[last - 1] == 2 * g.in_extent[last - 1];
+        doubled = two_rows || g.out_extent[last - 1] == g.in_extent[last - 1];
+        for (int d = 0; d < last - 1 && doubled; ++d) doubled = g.out_extent[d] == g.in_extent[d];
+    }
+    if (doubled) {
+        const uint32_t chunks_per_row = static_cast<uint32_t>(in_w * element / 16);
+        const uint32_t total = static_cast<uint32_t>(source_count * element / 16);
+        const int grid = grid_for((static_cast<int64_t>(total) + kThreads - 1) / kThreads, kPerSm);
+#define VRB_DOUBLE(E, TWO) launch_overlapped(resize_double_kernel<E, TWO>, dim3(grid), dim3(kThreads), 0, s, static_cast<const uint4*>(x), static_cast<char*>(out), chunks_per_row, total)
+        if (element == 2) { if (two_rows) VRB_DOUBLE(uint16_t, true); else VRB_DOUBLE(uint16_t, false); }
+        else { if (two_rows) VRB_DOUBLE(uint32_t, true); else VRB_DOUBLE(uint32_t, false); }
+#undef VRB_DOUBLE
+        return after_launch("interpolate_nearest");
+    }
+    VRB_REQUIRE(out_w < (int64_t{1} << 31) && in_w < (int64_t{1} << 31) && count / out_w < (int64_t{1} << 31), VRB_ERR_UNSUPPORTED,
+                "interpolate_nearest: extents beyond the 32-bit row arithmetic");
+    const uint32_t rows = static_cast<uint32_t>(count / out_w);
+    const int grid = grid_for((static_cast<int64_t>(rows) + kThreads / 32 - 1) / (kThreads / 32), kPerSm);
+    if (element == 2)
+        launch_overlapped(resize_rows_kernel<uint16_t>, dim3(grid), dim3(kThreads), 0, s, static_cast<const uint16_t*>(x), static_cast<uint16_t*>(out), g, rows);
+    else
+        launch_overlapped(resize_rows_kernel<uint32_t>, dim3(grid), dim3(kThreads), 0, s, static_cast<const uint32_t*>(x), static_cast<uint32_t*>(out), g, rows);
+    return after_launch("interpolate_nearest");
 }
 
 extern "C" int vrb_sinusoidal_embedding(const void* positions, void* out, int dtype, int64_t count, int64_t width, int flip,

@@ -8,6 +8,7 @@
 #include "b200_backend.h"
 
 #include <algorithm>
+#include <cmath>
 #include <limits>
 
 #include "vrb.h"
@@ -554,6 +555,25 @@ Tensor B200Backend::pad(const Tensor& raw, const std::vector<int64_t>& padding, 
         ProfileRegion region(*this, [] { return std::string("pad"); }, bytes_of(x) + bytes_of(out));
         check(vrb_pad(x.data(), out.data(), code(dtype), rank, x.shape().data(), before.data(), after.data(), value,
                       mode == vrhino::PadMode::Replicate ? 1 : 0, kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::interpolate_nearest(const Tensor& raw, const std::vector<double>& factors) {
+    return guarded([&] {   // VRHINO_PROFILE("interpolate_nearest") (cuda_backend.cu:5012)
+        require(factors.size() <= static_cast<size_t>(raw.ndim() - 2), "interpolate factor rank mismatch");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype);
+        std::vector<int64_t> shape = x.shape();
+        const size_t start = static_cast<size_t>(raw.ndim()) - factors.size();
+        for (size_t index = 0; index < factors.size(); ++index) {
+            require(factors[index] > 0, "Invalid interpolation factor");
+            shape[start + index] = static_cast<int64_t>(std::floor(shape[start + index] * factors[index]));
+        }
+        Tensor out = rt_->allocate_device(shape, dtype);
+        ProfileRegion region(*this, [] { return std::string("interpolate_nearest"); }, bytes_of(x) + bytes_of(out));
+        check(vrb_interpolate_nearest(x.data(), out.data(), code(dtype), static_cast<int>(x.ndim()), x.shape().data(), shape.data(),
+                                      kLegacyStream));
         return out;
     });
 }

@@ -69,6 +69,7 @@ public:
                                 bool require_f64_semantics) override;
     Tensor pad(const Tensor& x, const std::vector<int64_t>& padding, float value = 0.0f,
                vrhino::PadMode mode = vrhino::PadMode::Constant) override;
+    Tensor interpolate_nearest(const Tensor& x, const std::vector<double>& factors) override;   // :5010-5016
     // per-axis extents and modes in one pass (replicate axes first, then the constant axes)
     Tensor pad_axes(const Tensor& x, const std::vector<int64_t>& before, const std::vector<int64_t>& after, float value,
                     const std::vector<bool>& replicate);
@@ -198,7 +199,6 @@ public:
         return rt_->conv_transpose2d(x, w, b, s, p, op, d, g);
     }
     Tensor max_pool2d(const Tensor& x, const std::vector<int>& k, const std::vector<int>& s, const std::vector<int>& p = {0, 0}) override { return rt_->max_pool2d(x, k, s, p); }
-    Tensor interpolate_nearest(const Tensor& x, const std::vector<double>& f) override { return rt_->interpolate_nearest(x, f); }
     Tensor interpolate_bilinear_2d(const Tensor& x, int64_t h, int64_t w, bool a) override { return rt_->interpolate_bilinear_2d(x, h, w, a); }
     Tensor rng_normal(vrhino::RngState& s, const std::vector<int64_t>& shape, DType d) override { return rt_->rng_normal(s, shape, d); }
 

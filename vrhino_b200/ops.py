@@ -332,6 +332,24 @@ class B200Backend:
              self._extents(after), ctypes.c_float(value), modes, _stream())
         return out
 
+    def interpolate_nearest(self, raw, factors, out=None):
+        """CudaBackend::interpolate_nearest (cuda_backend.cu:5010-5016): the trailing len(factors) axes grow to
+        floor(extent * factor); out[c] = x[floor(c * in / out)] along every axis."""
+        import math
+        if len(factors) > raw.dim() - 2:
+            raise VrbError("interpolate factor rank mismatch")
+        if any(f <= 0 for f in factors):
+            raise VrbError("Invalid interpolation factor")
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        shape = list(x.shape)
+        start = x.dim() - len(factors)
+        for i, f in enumerate(factors):
+            shape[start + i] = int(math.floor(shape[start + i] * float(f)))
+        out = _result(out, tuple(shape), dtype, x.device)
+        call("vrb_interpolate_nearest", _ptr(x), _ptr(out), _code(dtype), x.dim(), self._extents(x.shape), self._extents(shape), _stream())
+        return out
+
     def sinusoidal_embedding(self, raw, width, flip, downscale, frequency_f64, out=None):
         """CudaBackend::sinusoidal_embedding: positions [n] -> [n, width]."""
         if raw.dim() != 1 or width <= 0:

@@ -487,6 +487,7 @@ class LayoutOps:
         def causal(): o["causal"] = be.pad(f, [0, 0, 0, 0, 2, 2], 0.0, True, out=o.get("causal"))
         def spatial(): o["spatial"] = be.pad(f, [1, 1, 1, 1], 0.0, False, out=o.get("spatial"))
         def edge(): o["edge"] = ops.fused_edge_time_pad(be, f, 1, 1, 1, out=o.get("edge"))
+        def nearest(): o["nearest"] = be.interpolate_nearest(f.view(c * t // 8, 8, h, w), [2.0, 2.0], out=o.get("nearest"))
         def half(): o["half"] = be.slice(self.proj, 2, 8192, 16384, out=o.get("half"))
         def joined(): o["joined"] = be.concat([f, f], 1, out=o.get("joined"))
 
@@ -497,6 +498,7 @@ class LayoutOps:
             Launch("pad time replicate", causal, size(f) + padded_t),
             Launch("pad H, W zero", spatial, size(f) + padded_hw),
             Launch("pad T replicate + H, W zero, one pass", edge, size(f) + size(f) * ((t + 2) * (h + 2) * (w + 2)) // (t * h * w)),
+            Launch("nearest 2x in H and W (Wan VAE upsample)", nearest, 5 * size(f)),
             Launch("slice second half", half, size(self.proj)),
             Launch("concat channels (2 launches)", joined, 4 * size(f)),
         ]
