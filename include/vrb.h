@@ -188,6 +188,12 @@ int vrb_pad_axes(const void* x, void* out, int dtype, int rank, const int64_t* s
 int vrb_interpolate_nearest(const void* x, void* out, int dtype, int rank, const int64_t* in_shape,
                             const int64_t* out_shape, vrb_stream stream);
 
+/* CudaBackend::reduce_sum (:4885-4892, reduce_sum_kernel :1790-1806) over the middle axis of x [outer, reduced, inner]:
+ * out[o, i] = sum of x[o, r, i] for r = 0, 1, ... in that order, accumulated in F32 and stored in x's dtype (the
+ * reference's order, so the same bits).  reduced == 0 gives zeros. */
+int vrb_reduce_sum(const void* x, void* out, int dtype, int64_t outer, int64_t reduced, int64_t inner,
+                   vrb_stream stream);
+
 /* CudaBackend::sinusoidal_embedding (:4190-4196, sinusoidal_kernel :1178-1198): positions [count] ->
  * out [count, width].  half = width / 2; logical column l = flip ? (column + half) % (2 half) : column;
  * out = (l < half ? sin : cos)(position * exp(-ln(10000) * (l % half) / (half - downscale))); an odd last

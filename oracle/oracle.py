@@ -294,6 +294,22 @@ class OracleBackend:
             data = np.take(data, index, axis=axis)
         return T(data, x.dtype)
 
+    def reduce_sum(self, raw: T, dim: int, keepdim: bool = False) -> T:
+        """CudaBackend::reduce_sum (:4885-4892, reduce_sum_kernel :1790-1806): F32 accumulation in increasing index
+        order along `dim`, stored in the operand dtype."""
+        if dim < 0:
+            dim += len(raw.shape)
+        if not 0 <= dim < len(raw.shape):
+            raise ValueError("reduce dimension invalid")
+        x = self.copy_to_device(raw, self._dtype_of(raw))
+        values = np.moveaxis(x.f32(), dim, 0)
+        total = np.zeros(values.shape[1:], dtype=np.float32)
+        for r in range(values.shape[0]):
+            total = (total + values[r]).astype(np.float32)
+        if keepdim:
+            total = np.expand_dims(total, dim)
+        return tensor(total, x.dtype)
+
     def sinusoidal_embedding(self, raw: T, width: int, flip: bool, downscale: float, frequency_f64: bool) -> T:
         """CudaBackend::sinusoidal_embedding (:4190-4196, sinusoidal_kernel :1178-1198).  The single-precision path
         rounds after every operation like the kernel; exp / sin / cos come from the host's libm, whose last bit

@@ -162,6 +162,9 @@ int64_t refc_pad(int64_t x, int entries, const int64_t* padding, float value, in
 int64_t refc_interpolate_nearest(int64_t x, int count, const double* factors) {
     return guarded([&] { return keep(g_backend->interpolate_nearest(at(x), std::vector<double>(factors, factors + count))); });
 }
+int64_t refc_reduce_sum(int64_t x, int64_t dim, int keepdim) {
+    return guarded([&] { return keep(g_backend->reduce_sum(at(x), dim, keepdim != 0)); });
+}
 int64_t refc_sinusoidal(int64_t positions, int64_t width, int flip, double downscale, int frequency_f64) {
     return guarded([&] { return keep(g_backend->sinusoidal_embedding(at(positions), width, flip != 0, downscale, frequency_f64 != 0)); });
 }

@@ -159,6 +159,13 @@ CASES = [
      "inputs": {"frames": (2, 3, 5, 8), "odd": (1, 2, 3, 5)},
      "steps": [("wan_upsample", "nearest", ["frames"], (2.0, 2.0)), ("odd_doubled", "nearest", ["odd"], (2.0, 2.0)),
                ("fractional", "nearest", ["odd"], (2.5, 1.4))]},
+    {"name": "layout_reduce_sum_bf16", "kind": "layout", "dt": "bf16", "seed": 41,
+     "inputs": {"text": (2, 37, 64), "odd": (3, 5, 7)},
+     "steps": [("pooled", "reduce", ["text"], (1, True)), ("last_axis", "reduce", ["text"], (-1, False)), ("first_axis", "reduce", ["text"], (0, False)),
+               ("odd_middle", "reduce", ["odd"], (1, False)), ("odd_last", "reduce", ["odd"], (2, True))]},
+    {"name": "layout_reduce_sum_f32", "kind": "layout", "dt": "f32", "seed": 42,
+     "inputs": {"text": (2, 37, 64), "odd": (3, 5, 7)},
+     "steps": [("pooled", "reduce", ["text"], (1, True)), ("last_axis", "reduce", ["text"], (-1, False)), ("odd_middle", "reduce", ["odd"], (1, False))]},
     {"name": "layout_sinusoidal_f32", "kind": "layout", "dt": "f32", "seed": 37,
      "inputs": {"positions": (0.0, 1.0, 0.5, 999.0, 37.25, -2.0, 1000.0, 250.0)},
      "steps": [("timestep_256", "sinusoidal", ["positions"], (256, True, 0.0, False)), ("odd_width", "sinusoidal", ["positions"], (7, False, 1.0, False)),
@@ -184,6 +191,8 @@ def run_layout(case, values, api, grab):
             values[name] = api.concat(x, args)
         elif op == "pad":
             values[name] = api.pad(x[0], list(args[0]), args[1], args[2])
+        elif op == "reduce":
+            values[name] = api.reduce_sum(x[0], *args)
         elif op == "nearest":
             values[name] = api.interpolate_nearest(x[0], list(args))
         elif op == "sinusoidal":
@@ -298,7 +307,7 @@ def run_reference(rc, case):
         class Api:
             permute = staticmethod(rc.permute); slice = staticmethod(rc.slice); concat = staticmethod(rc.concat)
             pad = staticmethod(rc.pad); sinusoidal_embedding = staticmethod(rc.sinusoidal_embedding)
-            interpolate_nearest = staticmethod(rc.interpolate_nearest)
+            interpolate_nearest = staticmethod(rc.interpolate_nearest); reduce_sum = staticmethod(rc.reduce_sum)
         run_layout(case, dict(h), Api, lambda name, handle: grab(name, handle, (int(rc.lib.refc_numel(ctypes.c_int64(handle))),)))
     elif k == "depth_to_space":
         b, c, t, h_, w = case["shape"]

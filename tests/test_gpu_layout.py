@@ -191,6 +191,20 @@ def test_interpolate_nearest_at_size_and_rules(gpu):
         be.interpolate_nearest(x, [0.0, 2.0])
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("shape,dim,keep", [((2, 37, 64), 1, True), ((2, 37, 64), -1, False), ((2, 37, 64), 0, False), ((3, 5, 7), 1, False),
+                                            ((3, 5, 7), 2, True), ((1, 256, 1536), 1, True), ((4, 1, 9), 1, False), ((2, 6), 1, False)])
+def test_reduce_sum(orc, gpu, shape, dim, keep, dt):
+    """F32 accumulation in index order, like the reference's one-thread-per-output loop: the same bits."""
+    import torch
+    be, _ = gpu
+    x, ox = _pair(orc, torch, shape, dt, 11)
+    got = be.reduce_sum(x, dim, keep)
+    want = orc.OracleBackend().reduce_sum(ox, dim, keep)
+    assert tuple(got.shape) == want.shape
+    assert np.array_equal(_bits(torch, got), _orc_bits(want))
+
+
 def test_argument_rules(orc, gpu):
     import torch
     from vrhino_b200._lib import VrbError
@@ -206,6 +220,8 @@ def test_argument_rules(orc, gpu):
         be.pad(x, [1, 1, 1])
     with pytest.raises(VrbError, match="Negative padding unsupported"):
         be.pad(x, [0, -1])
+    with pytest.raises(VrbError, match="reduce dimension invalid"):
+        be.reduce_sum(x, 3)
     with pytest.raises(VrbError, match="sinusoidal embedding contract violation"):
         be.sinusoidal_embedding(x, 8, True, 0.0, False)
     assert be.slice(x, 1, 2, 1).shape == (2, 0, 4)       # an empty range launches nothing

@@ -242,6 +242,8 @@ def test_layout_known_answers(orc, be):
     close(flat(be.slice(t((3, 2), [0, 1, 2, 3, 4, 5]), 0, 1, 3)), [2, 3, 4, 5])
     close(flat(be.interpolate_nearest(t((1, 1, 2), [1, 2]), [2])), [1, 1, 2, 2])                       # primitive_tests.cpp:540-541
     close(flat(be.interpolate_nearest(t((1, 1, 1, 2), [1, 2]), [2, 2])), [1, 1, 2, 2, 1, 1, 2, 2])
+    close(flat(be.reduce_sum(t((2, 3), [1, 2, 3, 4, 5, 6]), 1, False)), [6, 15])                        # primitive_tests.cpp:521-522
+    close(flat(be.reduce_sum(t((2, 2, 2), [1, 2, 3, 4, 5, 6, 7, 8]), 0, False)), [6, 8, 10, 12])
     close(flat(be.pad(t((1, 2), [1, 2]), [1, 1], 0.0, False)), [0, 1, 2, 0])
     close(flat(be.pad(t((1, 1, 2), [1, 2]), [1, 0, 1, 0], -1.0, False)), [-1, -1, -1, -1, 1, 2])
     close(flat(be.pad(t((1, 2), [1, 2]), [1, 2], 0.0, True)), [1, 1, 2, 2, 2])

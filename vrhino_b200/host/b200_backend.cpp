@@ -578,6 +578,26 @@ Tensor B200Backend::interpolate_nearest(const Tensor& raw, const std::vector<dou
     });
 }
 
+Tensor B200Backend::reduce_sum(const Tensor& raw, int64_t dim, bool keepdim) {
+    return guarded([&] {   // VRHINO_PROFILE("reduce_sum") (cuda_backend.cu:4887)
+        if (dim < 0) dim += static_cast<int64_t>(raw.ndim());
+        require(dim >= 0 && dim < static_cast<int64_t>(raw.ndim()), "reduce dimension invalid");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype);
+        std::vector<int64_t> shape = x.shape();
+        int64_t outer = 1, inner = 1;
+        for (int64_t d = 0; d < dim; ++d) outer *= shape[d];
+        for (int64_t d = dim + 1; d < static_cast<int64_t>(shape.size()); ++d) inner *= shape[d];
+        const int64_t reduced = shape[dim];
+        if (keepdim) shape[dim] = 1;
+        else shape.erase(shape.begin() + dim);
+        Tensor out = rt_->allocate_device(shape, dtype);
+        ProfileRegion region(*this, [] { return std::string("reduce_sum"); }, bytes_of(x) + bytes_of(out));
+        check(vrb_reduce_sum(x.data(), out.data(), code(dtype), outer, reduced, inner, kLegacyStream));
+        return out;
+    });
+}
+
 Tensor B200Backend::pad_axes(const Tensor& raw, const std::vector<int64_t>& before, const std::vector<int64_t>& after, float value,
                              const std::vector<bool>& replicate) {
     return guarded([&] {

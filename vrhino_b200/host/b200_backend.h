@@ -70,6 +70,7 @@ public:
     Tensor pad(const Tensor& x, const std::vector<int64_t>& padding, float value = 0.0f,
                vrhino::PadMode mode = vrhino::PadMode::Constant) override;
     Tensor interpolate_nearest(const Tensor& x, const std::vector<double>& factors) override;   // :5010-5016
+    Tensor reduce_sum(const Tensor& x, int64_t dim, bool keepdim = false) override;              // :4885-4892
     // per-axis extents and modes in one pass (replicate axes first, then the constant axes)
     Tensor pad_axes(const Tensor& x, const std::vector<int64_t>& before, const std::vector<int64_t>& after, float value,
                     const std::vector<bool>& replicate);
@@ -190,7 +191,6 @@ public:
     }
     Tensor conv3d(const Tensor& x, const Tensor& w, const Tensor* b, const std::vector<int>& s, const std::vector<int>& p,
                   const std::vector<int>& d = {1, 1, 1}, int g = 1) override { return rt_->conv3d(x, w, b, s, p, d, g); }
-    Tensor reduce_sum(const Tensor& x, int64_t d, bool k = false) override { return rt_->reduce_sum(x, d, k); }
     Tensor softmax(const Tensor& x, int64_t a) override { return rt_->softmax(x, a); }
     Tensor conv2d(const Tensor& x, const Tensor& w, const Tensor* b, const std::vector<int>& s, const std::vector<int>& p,
                   const std::vector<int>& d = {1, 1}, int g = 1) override { return rt_->conv2d(x, w, b, s, p, d, g); }

@@ -350,6 +350,28 @@ class B200Backend:
         call("vrb_interpolate_nearest", _ptr(x), _ptr(out), _code(dtype), x.dim(), self._extents(x.shape), self._extents(shape), _stream())
         return out
 
+    def reduce_sum(self, raw, dim, keepdim=False, out=None):
+        """CudaBackend::reduce_sum (cuda_backend.cu:4885-4892): the sum over `dim`, accumulated in F32 in index order."""
+        if dim < 0:
+            dim += raw.dim()
+        if not 0 <= dim < raw.dim():
+            raise VrbError("reduce dimension invalid")
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        outer, inner = 1, 1
+        for d in x.shape[:dim]:
+            outer *= d
+        for d in x.shape[dim + 1:]:
+            inner *= d
+        shape = list(x.shape)
+        if keepdim:
+            shape[dim] = 1
+        else:
+            del shape[dim]
+        out = _result(out, tuple(shape), dtype, x.device)
+        call("vrb_reduce_sum", _ptr(x), _ptr(out), _code(dtype), outer, x.shape[dim], inner, _stream())
+        return out
+
     def sinusoidal_embedding(self, raw, width, flip, downscale, frequency_f64, out=None):
         """CudaBackend::sinusoidal_embedding: positions [n] -> [n, width]."""
         if raw.dim() != 1 or width <= 0:
