@@ -354,10 +354,12 @@ __device__ __forceinline__ void transpose_2x2(W row0, W row1, W& even, W& odd) {
         odd = (row0 >> 32) | (row1 & 0xffffffff00000000ull);
     }
 }
-template <typename W>
+// A_PAIRS: pairs of the input-contiguous axis per tile (32: 64 x 64 element tiles; 64: 128 x 64, i.e. twice as many
+// contiguous bytes per input row visit).
+template <typename W, int A_PAIRS>
 __global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const W* __restrict__ in, W* __restrict__ out, const Transpose g) {
-    constexpr int TILE = 64, HALF = TILE / 2, PITCH = HALF + 1;   // pairs per tile row: 32 + 1
-    __shared__ W tile[TILE * PITCH];
+    constexpr int TILE_A = 2 * A_PAIRS, TILE_B = 64, B_PAIRS = TILE_B / 2, PITCH = B_PAIRS + 1;   // tile rows: a; columns: pairs of b
+    __shared__ W tile[TILE_A * PITCH];
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
@@ -380,31 +382,67 @@ __global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const W* __re
             in_base += coordinate * g.batch_in_stride[d];
             out_base += coordinate * g.batch_out_stride[d];
         }
-        const int64_t a0 = tile_a * TILE, b0 = tile_b * TILE;
+        const int64_t a0 = tile_a * TILE_A, b0 = tile_b * TILE_B;
         in_base += a0 + b0 * g.in_stride_b;          // elements; even
         out_base += a0 * g.out_stride_a + b0;
-        // load: lane = pair of a, warp + 8 i = pair of b
-        const bool a_inside = a0 + 2 * lane < g.extent_a;
+        const bool interior = a0 + TILE_A <= g.extent_a && b0 + TILE_B <= g.extent_b;
+        // load: lane (+ 32) = pair of a, warp + 8 i = pair of b
+        if (interior) {
+            // no bounds tests, and the row pointers are advanced instead of recomputed
+            const int64_t row_step = g.in_stride_b >> 1;                                   // one row of b, in pairs
+            const W* rows = in + ((in_base + static_cast<int64_t>(2 * warp) * g.in_stride_b) >> 1) + lane;
+            W* even_at = tile + lane * PITCH + warp;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int pair_b = warp + 8 * i;
-            if (a_inside && b0 + 2 * pair_b < g.extent_b) {
-                const int64_t at = in_base + static_cast<int64_t>(2 * pair_b) * g.in_stride_b + 2 * lane;
-                W even, odd;
-                transpose_2x2<W>(in[at >> 1], in[(at + g.in_stride_b) >> 1], even, odd);
-                tile[lane * PITCH + pair_b] = even;
-                tile[(HALF + lane) * PITCH + pair_b] = odd;
+            for (int i = 0; i < B_PAIRS / 8; ++i, rows += 16 * row_step, even_at += 8) {
+#pragma unroll
+                for (int h = 0; h < A_PAIRS / 32; ++h) {
+                    W even, odd;
+                    transpose_2x2<W>(rows[32 * h], rows[32 * h + row_step], even, odd);
+                    even_at[32 * h * PITCH] = even;
+                    even_at[(A_PAIRS + 32 * h) * PITCH] = odd;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < B_PAIRS / 8; ++i) {
+                const int pair_b = warp + 8 * i;
+                if (b0 + 2 * pair_b < g.extent_b) {
+#pragma unroll
+                    for (int h = 0; h < A_PAIRS / 32; ++h) {
+                        const int pair_a = lane + 32 * h;
+                        if (a0 + 2 * pair_a < g.extent_a) {
+                            const int64_t at = in_base + static_cast<int64_t>(2 * pair_b) * g.in_stride_b + 2 * pair_a;
+                            W even, odd;
+                            transpose_2x2<W>(in[at >> 1], in[(at + g.in_stride_b) >> 1], even, odd);
+                            tile[pair_a * PITCH + pair_b] = even;
+                            tile[(A_PAIRS + pair_a) * PITCH + pair_b] = odd;
+                        }
+                    }
+                }
             }
         }
         __syncthreads();
         // store: 16 threads cover the 32 pairs of one output row, two pairs each; the two half-warps take adjacent
         // tile rows (an odd pitch apart: no bank conflict)
         const int word = 2 * (threadIdx.x % 16);
+        if (interior && (((out_base >> 1) | (g.out_stride_a >> 1)) & 1) == 0) {
+            // every row start is aligned to two pairs: one vector store per thread and row, no tests
+            const int row0 = threadIdx.x / 16;
+#pragma unroll
+            for (int i = 0; i < TILE_A / 16; ++i) {
+                const int tile_row = row0 + 16 * i;
+                const int a = tile_row < A_PAIRS ? 2 * tile_row : 2 * (tile_row - A_PAIRS) + 1;
+                const W w0 = tile[tile_row * PITCH + word], w1 = tile[tile_row * PITCH + word + 1];
+                W* const to = out + ((out_base + static_cast<int64_t>(a) * g.out_stride_a) >> 1) + word;
+                if constexpr (sizeof(W) == 4) *reinterpret_cast<uint2*>(to) = make_uint2(w0, w1);
+                else *reinterpret_cast<ulonglong2*>(to) = make_ulonglong2(w0, w1);
+            }
+        } else {
         const bool first_inside = b0 + 2 * word < g.extent_b, second_inside = b0 + 2 * word + 2 < g.extent_b;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < TILE_A / 16; ++i) {
             const int tile_row = threadIdx.x / 16 + 16 * i;
-            const int a = tile_row < HALF ? 2 * tile_row : 2 * (tile_row - HALF) + 1;
+            const int a = tile_row < A_PAIRS ? 2 * tile_row : 2 * (tile_row - A_PAIRS) + 1;
             if (first_inside && a0 + a < g.extent_a) {
                 const W w0 = tile[tile_row * PITCH + word], w1 = tile[tile_row * PITCH + word + 1];
                 const int64_t at = (out_base + static_cast<int64_t>(a) * g.out_stride_a) / 2 + word;
@@ -416,6 +454,7 @@ __global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const W* __re
                     if (second_inside) out[at + 1] = w1;
                 }
             }
+        }
         }
         __syncthreads();
     }
@@ -530,16 +569,23 @@ int run_plan(const void* in, void* out, int dtype, const Plan& raw, float pad_va
             bool pairs = g.extent_a % 2 == 0 && g.extent_b % 2 == 0 && g.in_stride_b % 2 == 0 && g.out_stride_a % 2 == 0 &&
                          reinterpret_cast<uintptr_t>(source) % (2 * element) == 0 && reinterpret_cast<uintptr_t>(destination) % (4 * element) == 0;
             for (int d = 0; d < g.batch_rank && pairs; ++d) pairs = g.batch_in_stride[d] % 2 == 0 && g.batch_out_stride[d] % 2 == 0;
+            const int wide_a = pairs && g.extent_a >= 128 ? 1 : 0;   // 128 x 64 tiles: twice the contiguous bytes per input row visit
             const int tile = pairs || element == 2 ? 64 : 32;
-            g.tiles_a = (g.extent_a + tile - 1) / tile; g.tiles_b = (g.extent_b + tile - 1) / tile;
+            g.tiles_a = (g.extent_a + (tile << wide_a) - 1) / (tile << wide_a); g.tiles_b = (g.extent_b + tile - 1) / tile;
             g.tiles = g.tiles_a * g.tiles_b;
             for (int d = 0; d < g.batch_rank; ++d) g.tiles *= g.batch_extent[d];
             const int grid = grid_for(g.tiles, kPerSm);
-            if (pairs && element == 2)
-                launch_overlapped(transpose_pairs_kernel<uint32_t>, dim3(grid), dim3(kThreads), 0, stream,
+            if (pairs && element == 2 && wide_a)
+                launch_overlapped(transpose_pairs_kernel<uint32_t, 64>, dim3(grid), dim3(kThreads), 0, stream,
                                   reinterpret_cast<const uint32_t*>(source), reinterpret_cast<uint32_t*>(destination), g);
+            else if (pairs && element == 2)
+                launch_overlapped(transpose_pairs_kernel<uint32_t, 32>, dim3(grid), dim3(kThreads), 0, stream,
+                                  reinterpret_cast<const uint32_t*>(source), reinterpret_cast<uint32_t*>(destination), g);
+            else if (pairs && wide_a)
+                launch_overlapped(transpose_pairs_kernel<unsigned long long, 64>, dim3(grid), dim3(kThreads), 0, stream,
+                                  reinterpret_cast<const unsigned long long*>(source), reinterpret_cast<unsigned long long*>(destination), g);
             else if (pairs)
-                launch_overlapped(transpose_pairs_kernel<unsigned long long>, dim3(grid), dim3(kThreads), 0, stream,
+                launch_overlapped(transpose_pairs_kernel<unsigned long long, 32>, dim3(grid), dim3(kThreads), 0, stream,
                                   reinterpret_cast<const unsigned long long*>(source), reinterpret_cast<unsigned long long*>(destination), g);
             else if (element == 2)
                 launch_overlapped(transpose_kernel<uint16_t, 64>, dim3(grid), dim3(kThreads), 0, stream,
@@ -929,3 +975,4 @@ extern "C" int vrb_sinusoidal_embedding(const void* positions, void* out, int dt
                           frequency_f64);
     return after_launch("sinusoidal_embedding");
 }
+
