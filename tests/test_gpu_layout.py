@@ -61,7 +61,7 @@ SLICES = [
     ((1, 20, 64), 2, 0, 32), ((1, 20, 64), 2, 32, 64), ((1, 20, 64), 2, 3, 10), ((2, 9, 24), 1, 2, 7), ((2, 9, 24), 0, 1, 2),
     ((2, 9, 24), -1, -5, 100), ((2, 9, 24), 1, -100, 3), ((2, 9, 24), 1, 4, 4), ((2, 9, 24), 2, 30, 40), ((5, 6, 12), 2, 4, 12),
     ((3, 4, 5, 6, 7, 2, 3, 4), 4, 2, 6), ((64,), 0, 8, 24),
-    ((4, 300), 1, 3, 250), ((2, 3, 1000), 2, 1, 999), ((5, 129), 1, 0, 65),      # long rows at odd offsets: a warp per row
+    ((4, 300), 1, 3, 250), ((2, 3, 1000), 2, 1, 999), ((5, 129), 1, 0, 65),      # long rows at odd offsets: the row form
 ]
 
 
@@ -75,6 +75,26 @@ def test_slice(orc, gpu, shape, dim, start, stop, dt):
     want = orc.OracleBackend().slice(ox, dim, start, stop)
     assert tuple(got.shape) == want.shape
     assert np.array_equal(_bits(torch, got), _orc_bits(want))
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_row_copies_at_every_pair_of_phases(orc, gpu, dt):
+    """Long rows whose two sides start at every combination of offsets inside a 16-byte chunk (the row length moves
+    the output side from row to row, the slice's start moves the source side), as a slice and under a pad."""
+    import torch
+    be, _ = gpu
+    obe = orc.OracleBackend()
+    x, ox = _pair(orc, torch, (9, 211), dt, 41)
+    for start in range(9):
+        for length in (64, 65, 71, 78, 200):
+            got, want = be.slice(x, 1, start, start + length), obe.slice(ox, 1, start, start + length)
+            assert np.array_equal(_bits(torch, got), _orc_bits(want)), (start, length)
+    for width in (66, 67, 69, 72):
+        y, oy = _pair(orc, torch, (5, 3, width), dt, 42 + width)
+        for left, right in ((1, 1), (2, 0), (0, 3), (5, 8)):
+            for replicate in (False, True):
+                got, want = be.pad(y, [left, right], -0.5, replicate), obe.pad(oy, [left, right], -0.5, replicate)
+                assert np.array_equal(_bits(torch, got), _orc_bits(want)), (width, left, right, replicate)
 
 
 @pytest.mark.parametrize("dt", ["bf16", "f32"])
@@ -111,9 +131,13 @@ PADS = [
     ((2, 3, 2, 5, 7), (1, 0, 1, 0, 1, 0, 1, 0, 1, 0), 2.0, False),   # every axis: run-time rank
     ((1, 2), (1, 2), 0.0, True),
     ((6, 40), (0, 8), 1.0, False),                           # inner axis by a multiple of the unit
-    ((2, 3, 70), (3, 2), -2.5, False),                       # long padded rows: a warp per row
+    ((2, 3, 70), (3, 2), -2.5, False),                       # long padded rows: the row form
     ((2, 3, 70), (3, 2, 1, 1), 0.0, True),
     ((1, 2, 3, 130), (1, 0, 0, 0, 2, 1), 0.25, False),
+    ((3, 5, 4), (40, 40), 0.75, False),                      # a source row shorter than one 16-byte chunk inside a long output row
+    ((3, 5, 4), (40, 40), 0.0, True),
+    ((2, 7, 90), (9, 17), 0.0, True),                        # replicated pads wider than a chunk
+    ((40, 33, 67), (1, 1, 1, 1), 0.0, False),                # more rows than one warp's group
     ((2, 3, 5), (0, 0), 0.0, False),                         # nothing to do
     ((2, 3, 5), (), 0.0, False),
 ]

@@ -13,7 +13,8 @@
 // thread and step.  A permute that moves the innermost axis goes through shared-memory tiles over
 // (the input's innermost axis, the output's innermost axis), both sides coalesced; when either of
 // those axes is short it is walked element by element with coalesced stores.  Element-unit walks with
-// long innermost rows (a pad of the innermost axes, a slice at an odd offset) take a warp per row.
+// long innermost rows (a pad of the innermost axes, a slice at an odd offset) go by rows: whole 16-byte
+// chunks at any phase of either side, a warp per group of rows.
 #include "vrb_common.cuh"
 
 #include <algorithm>
@@ -102,24 +103,35 @@ __global__ void __launch_bounds__(kThreads) walk_kernel(const Unit* __restrict__
     }
 }
 
-// Element units with long innermost rows: a warp takes one row of the iteration space at a time, decomposes the row
-// index once, and its lanes move the row's elements with coalesced 2- or 4-byte loads and stores (four in flight per
-// lane).  Whatever the alignment of either side, every access of a warp is one contiguous segment: the form for a
-// pad of the innermost axes and for a slice at an odd offset.
+// Element units with long innermost rows (both innermost strides 1), whatever the alignment of either side: the form
+// for a pad of the innermost axes and for a slice at an odd offset.  A warp takes `group` adjacent rows of the
+// iteration space at a time, in three passes.  (1) Its first `group` lanes decompose one row index each (the
+// divisions of all the rows run side by side).  (2) The lanes share out the aligned 16-byte chunks that lie inside
+// the copied part of those output rows, each lane fetching its row's addresses from the lane that found them: a
+// chunk is cut out of the two aligned 16-byte source blocks that hold it (words selected and shifted by the
+// difference of the two sides' 16-byte phases; the second block is a cache hit, its neighbour's first) and stored
+// whole, two chunks per lane in flight, their loads issued before the first store.  (3) What is left of every row
+// (the pads, and the copied elements before the first and after the last whole chunk) goes one element per lane,
+// the lanes shared out over all the rows' leftovers.  A row without a source is filled by the whole warp.  Loads of
+// whole blocks touch only aligned 16-byte blocks that hold at least one byte of the source row.
 template <typename E, bool PAD>
 __global__ void __launch_bounds__(kThreads) walk_rows_kernel(const E* __restrict__ in, E* __restrict__ out, const Walk w,
-                                                             const uint4 fill, const int replicate, const uint32_t rows) {
+                                                             const uint4 fill, const int replicate, const uint32_t rows,
+                                                             const uint32_t group) {
+    constexpr int kPerChunk = 16 / static_cast<int>(sizeof(E));
+    constexpr int kInFlight = 2;
     pdl_launch_dependents();
     pdl_wait();
     const int last = w.rank - 1;
-    const int lane = threadIdx.x % 32;
+    const uint32_t lane = threadIdx.x % 32;
     const uint32_t warps = gridDim.x * (kThreads / 32);
-    const int extent_last = static_cast<int>(w.extent[last]);
-    const int before_last = PAD ? static_cast<int>(w.before[last]) : 0;
-    const int in_extent_last = PAD ? static_cast<int>(w.in_extent[last]) : extent_last;
-    const bool replicate_last = ((replicate >> last) & 1) != 0;
+    const int out_bytes = static_cast<int>(w.extent[last]) * static_cast<int>(sizeof(E));
+    const int before_bytes = PAD ? static_cast<int>(w.before[last]) * static_cast<int>(sizeof(E)) : 0;
+    const int in_bytes = PAD ? static_cast<int>(w.in_extent[last]) * static_cast<int>(sizeof(E)) : out_bytes;
+    const bool replicate_last = PAD && ((replicate >> last) & 1) != 0;
     const E fill_value = unit_of<E>(fill);
-    for (uint32_t row = blockIdx.x * (kThreads / 32) + threadIdx.x / 32; row < rows; row += warps) {
+    // where row `row` starts on either side, and whether it has a source at all
+    auto locate = [&](const uint32_t row, const E*& src, E*& dst) {
         uint32_t remaining = row;
         int64_t source = 0, destination = 0;
         bool row_valid = true;
@@ -142,40 +154,112 @@ __global__ void __launch_bounds__(kThreads) walk_rows_kernel(const E* __restrict
             }
             source += from * w.in_stride[d];
         }
-        // both innermost strides are 1 (the launcher's condition): the row is [leading pad | copy of the source row |
-        // trailing pad], and the copy needs no test per element
-        const E* const src = in + source;
-        E* const dst = out + destination;
-        constexpr int kInFlight = 8;
-        if (row_valid) {
-            E* const body = dst + before_last;
-            const E* from = src + lane;
-            E* to = body + lane;
-            int left = in_extent_last;
-            for (; left >= 32 * kInFlight; left -= 32 * kInFlight, from += 32 * kInFlight, to += 32 * kInFlight) {   // whole blocks: no tests
-                E value[kInFlight];
+        src = in + source;
+        dst = out + destination;
+        return row_valid;
+    };
+    constexpr int kSize = static_cast<int>(sizeof(E));
+    // whole chunks inside a row's copied part: at most body_slots, at least least_full (the part may start up to 14
+    // bytes past a chunk boundary); everything else of a row is at most `leftovers` elements
+    const uint32_t body_slots = static_cast<uint32_t>(in_bytes) / 16;
+    const int least_full = in_bytes >= 30 ? (in_bytes - 14) / 16 : 0;
+    const uint32_t leftovers = static_cast<uint32_t>(out_bytes / kSize - kPerChunk * least_full);
+    const uint64_t stride = static_cast<uint64_t>(warps) * group;
+    for (uint64_t first = static_cast<uint64_t>(blockIdx.x * (kThreads / 32) + threadIdx.x / 32) * group; first < rows; first += stride) {
+        const uint32_t count = rows - first < group ? static_cast<uint32_t>(rows - first) : group;
+        const E* my_src = in;
+        E* my_dst = out;
+        bool my_valid = false;
+        if (lane < count) my_valid = locate(static_cast<uint32_t>(first) + lane, my_src, my_dst);
+        const unsigned long long my_from = reinterpret_cast<unsigned long long>(my_src);
+        // (the copied part's first byte on the output side; bit 0 is free in a 2-byte aligned address: the row has a source)
+        const unsigned long long my_to = (reinterpret_cast<unsigned long long>(my_dst) + before_bytes) | (my_valid ? 1ull : 0ull);
+
+        if (body_slots != 0) {
+            const uint32_t items = count * body_slots;
+            const uint32_t step_rows = 32 / body_slots, step_slots = 32 % body_slots;
+            uint32_t row = lane / body_slots, slot = lane % body_slots;
+            for (uint32_t base = 0; base < items; base += 32 * kInFlight) {
+                uint4 a[kInFlight], b[kInFlight];
+                uint4* target[kInFlight];
+                int phase[kInFlight];
 #pragma unroll
-                for (int u = 0; u < kInFlight; ++u) value[u] = from[32 * u];
+                for (int u = 0; u < kInFlight; ++u) {
+                    const bool active = base + 32 * u + lane < items;
+                    const uint32_t owner = active ? row : 0;
+                    const unsigned long long from = __shfl_sync(0xffffffffu, my_from, owner);
+                    const unsigned long long to = __shfl_sync(0xffffffffu, my_to, owner);
+                    const int head = static_cast<int>((16 - (to & 14)) & 15);
+                    const int full = in_bytes >= head + 16 ? (in_bytes - head) >> 4 : 0;
+                    a[u] = b[u] = make_uint4(0, 0, 0, 0);
+                    phase[u] = 0;
+                    target[u] = nullptr;
+                    if (active && (to & 1) != 0 && static_cast<int>(slot) < full) {
+                        const int at = head + 16 * static_cast<int>(slot);
+                        target[u] = reinterpret_cast<uint4*>((to & ~1ull) + at);
+                        const unsigned long long source = from + at;
+                        phase[u] = static_cast<int>(source & 15);
+                        const uint4* const blocks = reinterpret_cast<const uint4*>(source - phase[u]);
+                        a[u] = __ldg(blocks);
+                        if (phase[u] != 0) b[u] = __ldg(blocks + 1);
+                    }
+                    row += step_rows;
+                    slot += step_slots;
+                    if (slot >= body_slots) { slot -= body_slots; ++row; }
+                }
 #pragma unroll
-                for (int u = 0; u < kInFlight; ++u) to[32 * u] = value[u];
+                for (int u = 0; u < kInFlight; ++u) {
+                    if (target[u] == nullptr) continue;
+                    // words [phase / 4, phase / 4 + 4] of the two blocks, then half a word further when the phase is odd in 2-byte elements
+                    uint32_t v0 = a[u].x, v1 = a[u].y, v2 = a[u].z, v3 = a[u].w, v4 = b[u].x, v5 = b[u].y, v6 = b[u].z, v7 = b[u].w;
+                    if (phase[u] & 8) { v0 = v2; v1 = v3; v2 = v4; v3 = v5; v4 = v6; v5 = v7; }
+                    if (phase[u] & 4) { v0 = v1; v1 = v2; v2 = v3; v3 = v4; v4 = v5; }
+                    const int shift = (phase[u] & 2) * 8;
+                    *target[u] = make_uint4(__funnelshift_r(v0, v1, shift), __funnelshift_r(v1, v2, shift), __funnelshift_r(v2, v3, shift),
+                                            __funnelshift_r(v3, v4, shift));
+                }
             }
-            if (left > 0) {
-                E value[kInFlight];
-#pragma unroll
-                for (int u = 0; u < kInFlight; ++u)
-                    if (lane + 32 * u < left) value[u] = from[32 * u];
-#pragma unroll
-                for (int u = 0; u < kInFlight; ++u)
-                    if (lane + 32 * u < left) to[32 * u] = value[u];
+        }
+
+        if (leftovers != 0) {
+            const uint32_t items = count * leftovers;
+            const uint32_t step_rows = 32 / leftovers, step_slots = 32 % leftovers;
+            uint32_t row = lane / leftovers, slot = lane % leftovers;
+            for (uint32_t base = 0; base < items; base += 32) {
+                const bool active = base + lane < items;
+                const uint32_t owner = active ? row : 0;
+                const unsigned long long from = __shfl_sync(0xffffffffu, my_from, owner);
+                const unsigned long long to = __shfl_sync(0xffffffffu, my_to, owner);
+                if (active && (to & 1) != 0) {
+                    const int head = static_cast<int>((16 - (to & 14)) & 15);
+                    const int full = in_bytes >= head + 16 ? (in_bytes - head) >> 4 : 0;
+                    // leftover bytes of this row: [0, lead) and [lead + 16 * full, out_bytes)
+                    const int lead = before_bytes + (full != 0 ? head : in_bytes);
+                    int at = static_cast<int>(slot) * kSize;
+                    if (at >= lead) at += 16 * full;
+                    if (at < out_bytes) {
+                        int source = at - before_bytes;
+                        const bool inside = source >= 0 && source < in_bytes;
+                        if (!inside) source = source < 0 ? 0 : in_bytes - kSize;
+                        E value = fill_value;
+                        if (inside || replicate_last) value = *reinterpret_cast<const E*>(from + source);
+                        *reinterpret_cast<E*>((to & ~1ull) - before_bytes + at) = value;
+                    }
+                }
+                row += step_rows;
+                slot += step_slots;
+                if (slot >= leftovers) { slot -= leftovers; ++row; }
             }
-            if constexpr (PAD) {
-                const int after_last = extent_last - before_last - in_extent_last;
-                const E head = replicate_last ? src[0] : fill_value, tail = replicate_last ? src[in_extent_last - 1] : fill_value;
-                for (int j = lane; j < before_last; j += 32) dst[j] = head;
-                for (int j = lane; j < after_last; j += 32) dst[before_last + in_extent_last + j] = tail;
+        }
+
+        if constexpr (PAD) {
+            unsigned without_source = __ballot_sync(0xffffffffu, lane < count && !my_valid);
+            while (without_source != 0) {
+                const int owner = __ffs(without_source) - 1;
+                without_source &= without_source - 1;
+                E* const dst = reinterpret_cast<E*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), owner));
+                for (int j = lane; j < out_bytes / kSize; j += 32) dst[j] = fill_value;
             }
-        } else {
-            for (int j = lane; j < extent_last; j += 32) dst[j] = fill_value;
         }
     }
 }
@@ -639,13 +723,21 @@ int run_plan(const void* in, void* out, int dtype, const Plan& raw, float pad_va
             running *= p.extent[d];
         }
     }
-    if (unit == element && p.in_stride[last] == 1 && p.out_stride[last] == 1 && p.extent[last] >= 64 && p.extent[last] < (int64_t{1} << 30) &&
+    if (unit == element && p.in_stride[last] == 1 && p.out_stride[last] == 1 && p.extent[last] >= 64 && p.extent[last] < (int64_t{1} << 28) &&
         count / p.extent[last] < (int64_t{1} << 31)) {
         const uint32_t rows = static_cast<uint32_t>(count / p.extent[last]);
-        const int grid = grid_for((static_cast<int64_t>(rows) + kThreads / 32 - 1) / (kThreads / 32), kPerSm);
+        // rows a warp decomposes side by side: about 512 chunks' worth (measured on the VAE's pads: 8 rows of 768 bytes,
+        // 4 of 1536; fewer pay the decomposition more often, more leave the warps out of step), and never so many that
+        // a resident warp (five CTAs per SM) has fewer than four groups to take
+        const int64_t row_chunks = std::max<int64_t>(1, p.in_extent[last] * element / 16);
+        uint32_t group = 32;
+        while (group > 1 && (group * row_chunks > 512 || static_cast<int64_t>(rows) / group < int64_t{4} * sm_count() * 5 * (kThreads / 32)))
+            group /= 2;
+        const int64_t groups = (static_cast<int64_t>(rows) + group - 1) / group;
+        const int grid = grid_for((groups + kThreads / 32 - 1) / (kThreads / 32), kPerSm);
 #define VRB_ROWS(E, PAD)                                                                                                      \
     launch_overlapped(walk_rows_kernel<E, PAD>, dim3(grid), dim3(kThreads), 0, stream, reinterpret_cast<const E*>(source), \
-                      reinterpret_cast<E*>(destination), w, fill, replicate, rows)
+                      reinterpret_cast<E*>(destination), w, fill, replicate, rows, group)
         if (element == 2) { if (p.padded) VRB_ROWS(uint16_t, true); else VRB_ROWS(uint16_t, false); }
         else { if (p.padded) VRB_ROWS(uint32_t, true); else VRB_ROWS(uint32_t, false); }
 #undef VRB_ROWS
