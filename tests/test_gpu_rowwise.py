@@ -196,16 +196,18 @@ def test_rms_norm_scale_mochi(orc, gpu, x_dt, width, batch):
 
 
 @pytest.mark.parametrize("out_dt", DTYPES)
-@pytest.mark.parametrize("mode", ["wan", "wan_no_rope", "mochi_per_head_tables", "hunyuan_shared_tables"])
+@pytest.mark.parametrize("mode", ["wan", "wan_no_rope", "mochi_per_head_tables", "hunyuan_shared_tables", "ltx_per_batch_tables"])
 def test_rms_norm_rope(orc, gpu, out_dt, mode):
-    """attention_norm -> split_heads -> operation_rope -> attention operand cast."""
+    """attention_norm -> split_heads -> operation_rope -> attention operand cast.  (LTX: the norm over the full
+    width, then tables [B, S, width] of its own for every batch entry, ltx_self_attention_graph.cpp:30-44.)"""
     be, ops = gpu
     from vrhino_b200 import synth
     obe, opol = orc.OracleBackend(), orc.Policy()
     heads, d = (12, 128) if mode.startswith("wan") else (24, 128) if mode.startswith("mochi") else (4, 64)
     tokens, width = 2 * 3 * 4, heads * d
-    x = orc.tensor(synth.normal((1, tokens, width), seed=7), "bf16")
-    per_head = not mode.startswith("wan")
+    batch = 2 if mode.startswith("ltx") else 1
+    x = orc.tensor(synth.normal((batch, tokens, width), seed=7), "bf16")
+    per_head = not (mode.startswith("wan") or mode.startswith("ltx"))
     wn = d if per_head else width
     w = orc.tensor(synth.normal((wn,), 1.0, 0.1, seed=8), "f32")
     if mode == "wan" or mode == "hunyuan_shared_tables":
@@ -214,20 +216,20 @@ def test_rms_norm_rope(orc, gpu, out_dt, mode):
         else:
             ph = synth.uniform_range((1, tokens, 1, d), -3, 3, seed=9)
             c, s = np.cos(ph), np.sin(ph)
-    elif mode == "mochi_per_head_tables":
-        ph = synth.uniform_range((1, tokens, heads, d), -3, 3, seed=9)
+    elif mode == "mochi_per_head_tables" or mode == "ltx_per_batch_tables":
+        ph = synth.uniform_range((batch, tokens, heads, d), -3, 3, seed=9)
         c, s = np.cos(ph), np.sin(ph)
     else:
         c = s = None
-    eps = 1e-5 if per_head else 1e-6
+    eps = 1e-6 if mode.startswith("wan") else 1e-5
     if per_head:
-        normed = orc.attention_norm(obe, opol, x.reshape((1, tokens, heads, d)), w, eps)
+        normed = orc.attention_norm(obe, opol, x.reshape((batch, tokens, heads, d)), w, eps)
     else:
-        normed = orc.attention_norm(obe, opol, x, w, eps).reshape((1, tokens, heads, d))
+        normed = orc.attention_norm(obe, opol, x, w, eps).reshape((batch, tokens, heads, d))
     if c is not None:
         co, si = orc.tensor(c), orc.tensor(s)
         normed = orc.operation_rope(obe, opol, normed, co, si)
-    want = obe.cast(normed, out_dt).reshape((1, tokens, width))
+    want = obe.cast(normed, out_dt).reshape((batch, tokens, width))
     got = ops.fused_rms_norm_rope(be, to_torch(x), to_torch(w), eps, to_torch(co) if c is not None else None,
                                   to_torch(si) if c is not None else None, heads=heads, per_head_norm=per_head,
                                   out_dtype=_torch_dtype(out_dt))

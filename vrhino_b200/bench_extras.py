@@ -63,6 +63,8 @@ def single_gpu_configs(be, peak, steps=10, warmup=2):
         "mochi_block (config 4: 44520 tokens x 3072, SwiGLU 8192)": lambda: workloads.MochiBlock(be, tokens=44520).launches(),
         "mochi_block, fewest launches (q+k as one launch, residual update + next pre-norm + tanh(gate) as one)":
             lambda: workloads.MochiBlock(be, tokens=44520).launches(merge_tail=True),
+        "ltx_block (LTX-Video block chain, both CFG branches: [2, 6144, 2048], 32 heads x 64, FFN 8192, per-batch RoPE tables [2, 6144, 2048])":
+            lambda: workloads.LtxBlock(be).launches(),
         "vae_group_norm_silu (config 5: [1,256,28,240,424] bf16, 32 groups)": lambda: workloads.VaeGroupNorm(be).launches(),
         "ltx_vae_pixel_norm ([1,128,16,256,384] bf16: pixel_norm, + modulate + SiLU -> F32 / bf16)":
             lambda: workloads.LtxVaeNorm(be, shape=(1, 128, 16, 256, 384)).launches(),

@@ -318,6 +318,63 @@ class MochiBlock:
         ]
 
 
+class LtxBlock:
+    """LTX-Video transformer block, both CFG branches as the batch the reference evaluates them in
+    (native/src/architectures/ltx.cpp:100-151, ltx_self_attention_graph.cpp:30-44): B=2, S tokens of
+    dim 2048, 32 heads x 64, FFN 8192, 128 text tokens.  A rms_norm(no weight, 1e-6) -> modulate -> bf16;
+    B q, k: rms_norm(w, 1e-5) over 2048 -> RoPE with per-batch tables [B, S, 2048] (the fractional
+    positions make them as large as q in F32) -> bf16; C x + proj * gate; E rms_norm(w) of the
+    cross-attention q and of the text k; F x + cross; G rms_norm -> modulate; H GELU-tanh on [B, S, 8192];
+    I x + ffn * gate.  per_token: modulation vectors [B, S, 2048] (one set per token) instead of [B, 1, 2048]."""
+
+    def __init__(self, be, tokens=6144, dim=2048, heads=32, ffn=8192, text_tokens=128, batch=2, hidden_dtype=BF16,
+                 per_token=False, seed=0):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        self.be, S, D, B = be, tokens, dim, batch
+        self.policy = ops.Policy(BF16, hidden_dtype)
+        self.x = _randn((B, S, D), hidden_dtype, g)
+        m = S if per_token else 1
+        self.rows = [_randn((B, m, D), F32, g, std=0.1) for _ in range(6)]
+        self.q, self.k, self.proj, self.cross_q, self.cross, self.ffn_out = (_randn((B, S, D), BF16, g) for _ in range(6))
+        self.cross_k = _randn((B, text_tokens, D), BF16, g)
+        self.ffn_hidden = _randn((B, S, ffn), BF16, g)
+        self.wq, self.wk, self.wcq, self.wck = (_randn((D,), F32, g, 1.0, 0.1) for _ in range(4))
+        phase = torch.rand((B, S, heads, D // heads), device="cuda", generator=g) * 6.2831853
+        self.cos, self.sin = torch.cos(phase), torch.sin(phase)
+        del phase
+        self.heads = heads
+        self.out = {}
+
+    def launches(self) -> List[Launch]:
+        be, p, r, o = self.be, self.policy, self.rows, self.out
+        act = self.x.numel()
+        hb = self.x.element_size()
+        vec = r[0].numel() * 4
+        table = self.cos.numel() * 4 * 2
+
+        def A(): o["A"] = ops.fused_rms_norm_modulate(be, self.x, 1e-6, r[0], r[1], out=o.get("A"))
+        def Bqk(): o["Bq"], o["Bk"] = ops.fused_rms_norm_rope_pair(be, self.q, self.wq, self.k, self.wk, 1e-5, self.cos, self.sin,
+                                                                   heads=self.heads, out=(o.get("Bq"), o.get("Bk")))
+        def C(): o["C"] = ops.fused_gated_residual(be, p, self.x, self.proj, r[2], out=o.get("C"))
+        def Eqk(): o["Eq"], o["Ek"] = ops.fused_rms_norm_rope_pair(be, self.cross_q, self.wcq, self.cross_k, self.wck, 1e-5, None, None,
+                                                                   heads=self.heads, out=(o.get("Eq"), o.get("Ek")))
+        def Fr(): o["F"] = ops.fused_gated_residual(be, p, self.x, self.cross, None, out=o.get("F"))
+        def G(): o["G"] = ops.fused_rms_norm_modulate(be, self.x, 1e-6, r[3], r[4], out=o.get("G"))
+        def H(): o["H"] = be.activation(self.ffn_hidden, ops.GELU_TANH, out=o.get("H"))
+        def I(): o["I"] = ops.fused_gated_residual(be, p, self.x, self.ffn_out, r[5], out=o.get("I"))
+
+        return [
+            Launch("A rms_modulate", A, act * (hb + 2) + 2 * vec),
+            Launch("B rms_rope q+k (tables as large as q)", Bqk, 2 * act * 4 + table),
+            Launch("C gated_residual", C, act * (hb + 2 + hb) + vec),
+            Launch("E rms cross q+k", Eqk, act * 4 + self.cross_k.numel() * 4),
+            Launch("F residual_add", Fr, act * (hb + 2 + hb)),
+            Launch("G rms_modulate", G, act * (hb + 2) + 2 * vec),
+            Launch("H gelu_tanh", H, self.ffn_hidden.numel() * 4),
+            Launch("I gated_residual", I, act * (hb + 2 + hb) + vec),
+        ]
+
+
 class VaeGroupNorm:
     """VAE decoder GroupNorm(32 groups, eps 1e-6) + SiLU on [N, 256, T, H, W] bf16 ~N(0, 2)
     (native/src/components/autoencoder_kl.cpp:31-41).  Statistics pass + apply pass: the input
@@ -530,10 +587,13 @@ def build_config(be, config: int, tokens=None, hidden_dtype=BF16, frames=None, b
         return WanVaeRmsChannel(be, shape=(1, 192, frames or 4, 240, 416), dtype=hidden_dtype)
     if config == 13:
         return LayoutOps(be, frames=frames or 8, dtype=hidden_dtype)
-    raise ValueError("config must be 2..12 (6 = config 5 as a pre-permuted per-frame tensor, 7 = per-frame statistics "
+    if config in (14, 15):
+        return LtxBlock(be, tokens=tokens or 6144, batch=batch if batch > 1 else 2, hidden_dtype=hidden_dtype, per_token=config == 15)
+    raise ValueError("config must be 2..15 (6 = config 5 as a pre-permuted per-frame tensor, 7 = per-frame statistics "
                      "on the unpermuted [N,C,T,H,W] tensor, 8 = linear epilogues merged with their consumers, "
                      "9 = the same as separate launches, 10 = LTX VAE pixel_norm -> modulate -> SiLU, "
-                     "11 = LTX VAE depth_to_space, 12 = Wan VAE rms_channel + SiLU)")
+                     "11 = LTX VAE depth_to_space, 12 = Wan VAE rms_channel + SiLU, 13 = layout operators, "
+                     "14 = LTX block chain, 15 = the same with per-token modulation)")
 
 
 def _main():
