@@ -33,7 +33,8 @@ extern "C" {
 
 #define VRB_ABI_VERSION 1
 
-typedef enum vrb_dtype { VRB_F32 = 0, VRB_BF16 = 2, VRB_U8 = 5 } vrb_dtype;
+/* enum class DType, native/include/vrhino/tensor.h:13 (the same codes) */
+typedef enum vrb_dtype { VRB_F32 = 0, VRB_BF16 = 2, VRB_I64 = 3, VRB_I32 = 4, VRB_U8 = 5 } vrb_dtype;
 
 typedef enum vrb_status {
     VRB_OK = 0,
@@ -187,6 +188,19 @@ int vrb_pad_axes(const void* x, void* out, int dtype, int rank, const int64_t* s
  * and writes them doubled into both output rows. */
 int vrb_interpolate_nearest(const void* x, void* out, int dtype, int rank, const int64_t* in_shape,
                             const int64_t* out_shape, vrb_stream stream);
+
+/* CudaBackend::indexed_gather (:3981-4055, indexed_gather_kernel :1754-1768): out [batches, indices_per_batch, width] =
+ * table [batches, rows, width] gathered along rows by indices [batches, indices_per_batch] (index_dtype VRB_I64 or
+ * VRB_I32, on the device).  batches == 0: one table [rows, width] for all indices_per_batch indices.  The caller
+ * validates 0 <= index < rows beforehand (the reference does so on the host and raises "indexed_gather index out of
+ * range"); a row with an index out of range is left unwritten. */
+int vrb_indexed_gather(const void* table, const void* indices, int index_dtype, void* out, int dtype, int64_t batches,
+                       int64_t rows, int64_t width, int64_t indices_per_batch, vrb_stream stream);
+
+/* CudaBackend::softmax (:4893-4917, softmax_axis_kernel :1808-1829) over the middle axis of x [outer, axis, inner]:
+ * maximum, then the sum of expf(x - max) accumulated in F32 in index order (the reference's order: same bits), then
+ * expf(x - max) / sum stored in x's dtype. */
+int vrb_softmax(const void* x, void* out, int dtype, int64_t outer, int64_t axis, int64_t inner, vrb_stream stream);
 
 /* CudaBackend::reduce_sum (:4885-4892, reduce_sum_kernel :1790-1806) over the middle axis of x [outer, reduced, inner]:
  * out[o, i] = sum of x[o, r, i] for r = 0, 1, ... in that order, accumulated in F32 and stored in x's dtype (the

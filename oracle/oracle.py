@@ -310,6 +310,48 @@ class OracleBackend:
             total = np.expand_dims(total, dim)
         return tensor(total, x.dtype)
 
+    def softmax(self, raw: T, axis: int) -> T:
+        """CudaBackend::softmax (:4893-4917, softmax_axis_kernel :1808-1829): maximum over the axis, then the sum of
+        expf(x - max) accumulated in F32 in increasing index order, then expf(x - max) / sum, stored in x's dtype.
+        (expf here is the host's; its last bit can differ from the device function.)"""
+        if axis < 0:
+            axis += len(raw.shape)
+        if not 0 <= axis < len(raw.shape):
+            raise ValueError("softmax axis invalid")
+        x = self.copy_to_device(raw, self._dtype_of(raw))
+        values = np.moveaxis(x.f32(), axis, 0)
+        maximum = np.full(values.shape[1:], -np.inf, dtype=np.float32)
+        for r in range(values.shape[0]):
+            maximum = np.fmax(maximum, values[r])
+        shifted = np.exp((values - maximum).astype(np.float32)).astype(np.float32)
+        denominator = np.zeros(values.shape[1:], dtype=np.float32)
+        for r in range(values.shape[0]):
+            denominator = (denominator + shifted[r]).astype(np.float32)
+        return tensor(np.moveaxis((shifted / denominator).astype(np.float32), 0, axis), x.dtype)
+
+    def indexed_gather(self, table_raw: T, indices) -> T:
+        """CudaBackend::indexed_gather (:3981-4055, indexed_gather_kernel :1754-1768): rows of table [rows, width] (or
+        of table[b] when the table is [batch, rows, width] and indices [batch, ...]) picked by integer indices;
+        the result has the indices' shape plus the width, in the execution dtype."""
+        indices = np.asarray(indices)
+        if len(table_raw.shape) not in (2, 3):
+            raise ValueError("indexed_gather table must have rank 2 or 3")
+        if indices.ndim < 1 or indices.dtype not in (np.int64, np.int32):
+            raise ValueError("indexed_gather indices must be rank >=1 int64/int32")
+        batched = len(table_raw.shape) == 3
+        if batched and indices.shape[0] != table_raw.shape[0]:
+            raise ValueError("indexed_gather batch dimension mismatch")
+        rows = table_raw.shape[-2]
+        if indices.size and (indices.min() < 0 or indices.max() >= rows):
+            raise ValueError("indexed_gather index out of range")
+        table = self.copy_to_device(table_raw, self.execution_dtype).f32()
+        if batched:
+            picked = np.stack([table[b][indices[b]] for b in range(indices.shape[0])]) if indices.shape[0] else \
+                np.zeros(indices.shape + (table.shape[-1],), dtype=np.float32)
+        else:
+            picked = table[indices]
+        return tensor(picked, self.execution_dtype)
+
     def sinusoidal_embedding(self, raw: T, width: int, flip: bool, downscale: float, frequency_f64: bool) -> T:
         """CudaBackend::sinusoidal_embedding (:4190-4196, sinusoidal_kernel :1178-1198).  The single-precision path
         rounds after every operation like the kernel; exp / sin / cos come from the host's libm, whose last bit

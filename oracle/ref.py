@@ -202,7 +202,8 @@ class RefCuda:
                      "refc_exp", "refc_sqrt", "refc_dequantize", "refc_modulate", "refc_attention_norm", "refc_operation_rope",
                      "refc_residual_add", "refc_gated_residual", "refc_cfg_combine", "refc_euler_update", "refc_flow_to_x0",
                      "refc_frame_group_norm", "refc_linear", "refc_pixel_norm", "refc_pixel_shuffle", "refc_repeat",
-                     "refc_l2_normalize", "refc_permute", "refc_concat", "refc_pad", "refc_sinusoidal", "refc_interpolate_nearest", "refc_reduce_sum"):
+                     "refc_l2_normalize", "refc_permute", "refc_concat", "refc_pad", "refc_sinusoidal", "refc_interpolate_nearest", "refc_reduce_sum",
+                     "refc_softmax", "refc_indexed_gather"):
             getattr(lib, name).restype = _c.c_int64
         lib.refc_profile_total_ms.restype = _c.c_double
         self.lib = lib
@@ -268,6 +269,13 @@ class RefCuda:
         return self._h(self.lib.refc_pad(self._i(x), len(padding), p, _c.c_float(value), int(bool(replicate))))
     def reduce_sum(self, x, dim, keepdim=False):
         return self._h(self.lib.refc_reduce_sum(self._i(x), _c.c_int64(dim), int(bool(keepdim))))
+    def softmax(self, x, axis): return self._h(self.lib.refc_softmax(self._i(x), _c.c_int64(axis)))
+    def indexed_gather(self, table, indices):
+        import numpy as np
+        indices = np.ascontiguousarray(indices)
+        shape, rank = self._shape(tuple(int(v) for v in indices.shape))
+        return self._h(self.lib.refc_indexed_gather(self._i(table), 64 if indices.dtype == np.int64 else 32, rank, shape,
+                                                    indices.ctypes.data_as(_c.c_void_p)))
     def interpolate_nearest(self, x, factors):
         f = (_c.c_double * max(len(factors), 1))(*[float(v) for v in factors])
         return self._h(self.lib.refc_interpolate_nearest(self._i(x), len(factors), f))

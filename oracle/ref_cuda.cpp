@@ -165,6 +165,15 @@ int64_t refc_interpolate_nearest(int64_t x, int count, const double* factors) {
 int64_t refc_reduce_sum(int64_t x, int64_t dim, int keepdim) {
     return guarded([&] { return keep(g_backend->reduce_sum(at(x), dim, keepdim != 0)); });
 }
+int64_t refc_softmax(int64_t x, int64_t axis) { return guarded([&] { return keep(g_backend->softmax(at(x), axis)); }); }
+// indices: host values of `index_bits` (64 or 32) bits each, shape [rank]; handed over as a host tensor, as the callers do
+int64_t refc_indexed_gather(int64_t table, int index_bits, int rank, const int64_t* shape, const void* indices) {
+    return guarded([&] {
+        Tensor h = Tensor::host(std::vector<int64_t>(shape, shape + rank), index_bits == 64 ? DType::I64 : DType::I32);
+        std::memcpy(h.data(), indices, h.bytes());
+        return keep(g_backend->indexed_gather(at(table), h));
+    });
+}
 int64_t refc_sinusoidal(int64_t positions, int64_t width, int flip, double downscale, int frequency_f64) {
     return guarded([&] { return keep(g_backend->sinusoidal_embedding(at(positions), width, flip != 0, downscale, frequency_f64 != 0)); });
 }

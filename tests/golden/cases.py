@@ -166,6 +166,20 @@ CASES = [
     {"name": "layout_reduce_sum_f32", "kind": "layout", "dt": "f32", "seed": 42,
      "inputs": {"text": (2, 37, 64), "odd": (3, 5, 7)},
      "steps": [("pooled", "reduce", ["text"], (1, True)), ("last_axis", "reduce", ["text"], (-1, False)), ("odd_middle", "reduce", ["odd"], (1, False))]},
+    {"name": "layout_softmax_bf16", "kind": "layout", "dt": "bf16", "seed": 43,
+     "inputs": {"scores": (3, 5, 77), "map": (2, 19, 6, 4), "wide": (2, 1100)},
+     "steps": [("last_axis", "softmax", ["scores"], (-1,)), ("classes", "softmax", ["map"], (1,)), ("first_axis", "softmax", ["scores"], (0,)),
+               ("long_rows", "softmax", ["wide"], (1,))]},
+    {"name": "layout_softmax_f32", "kind": "layout", "dt": "f32", "seed": 44,
+     "inputs": {"scores": (3, 5, 77), "map": (2, 19, 6, 4)},
+     "steps": [("last_axis", "softmax", ["scores"], (-1,)), ("classes", "softmax", ["map"], (1,)), ("middle", "softmax", ["scores"], (1,))]},
+    {"name": "layout_gather_bf16", "kind": "layout", "dt": "bf16", "seed": 45,
+     "inputs": {"embedding": (50, 64), "odd": (9, 7), "batched": (2, 11, 24)},
+     "steps": [("tokens", "gather", ["embedding"], ([[3, 0, 49, 7, 7], [1, 48, 2, 0, 31]], "i64")),
+               ("tokens_i32", "gather", ["embedding"], ([5, 4, 3, 2, 1, 0], "i32")),
+               ("odd_width", "gather", ["odd"], ([8, 0, 3], "i64")),
+               ("per_batch", "gather", ["batched"], ([[10, 0, 5], [1, 1, 9]], "i64")),
+               ("per_batch_2d", "gather", ["batched"], ([[[0, 1], [2, 3]], [[10, 9], [8, 7]]], "i32"))]},
     {"name": "layout_sinusoidal_f32", "kind": "layout", "dt": "f32", "seed": 37,
      "inputs": {"positions": (0.0, 1.0, 0.5, 999.0, 37.25, -2.0, 1000.0, 250.0)},
      "steps": [("timestep_256", "sinusoidal", ["positions"], (256, True, 0.0, False)), ("odd_width", "sinusoidal", ["positions"], (7, False, 1.0, False)),
@@ -197,6 +211,10 @@ def run_layout(case, values, api, grab):
             values[name] = api.interpolate_nearest(x[0], list(args))
         elif op == "sinusoidal":
             values[name] = api.sinusoidal_embedding(x[0], *args)
+        elif op == "softmax":
+            values[name] = api.softmax(x[0], args[0])
+        elif op == "gather":
+            values[name] = api.indexed_gather(x[0], np.asarray(args[0], dtype=np.int64 if args[1] == "i64" else np.int32))
         else:
             raise KeyError(op)
         grab(name, values[name])
@@ -308,6 +326,7 @@ def run_reference(rc, case):
             permute = staticmethod(rc.permute); slice = staticmethod(rc.slice); concat = staticmethod(rc.concat)
             pad = staticmethod(rc.pad); sinusoidal_embedding = staticmethod(rc.sinusoidal_embedding)
             interpolate_nearest = staticmethod(rc.interpolate_nearest); reduce_sum = staticmethod(rc.reduce_sum)
+            softmax = staticmethod(rc.softmax); indexed_gather = staticmethod(rc.indexed_gather)
         run_layout(case, dict(h), Api, lambda name, handle: grab(name, handle, (int(rc.lib.refc_numel(ctypes.c_int64(handle))),)))
     elif k == "depth_to_space":
         b, c, t, h_, w = case["shape"]

@@ -229,6 +229,68 @@ def test_reduce_sum(orc, gpu, shape, dim, keep, dt):
     assert np.array_equal(_bits(torch, got), _orc_bits(want))
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("shape,axis", [((3, 5, 77), -1), ((3, 5, 77), 1), ((3, 5, 77), 0), ((2, 19, 6, 4), 1), ((4, 1100), 1), ((6, 1), 1),
+                                        ((2, 32), -1), ((1, 33), -1), ((600, 512), 1)])
+def test_softmax(orc, gpu, shape, axis, dt):
+    """Maximum, denominator in index order, quotient: the oracle differs from the device only by its host expf."""
+    import torch
+    be, _ = gpu
+    from vrhino_b200 import synth
+    scores = (synth.normal(shape, seed=12) * 3.0).astype(np.float32)
+    x, ox = _dev(torch, scores, dt), orc.tensor(scores, dt)
+    got = be.softmax(x, axis)
+    want = orc.OracleBackend().softmax(ox, axis)
+    assert tuple(got.shape) == want.shape
+    if dt == "bf16":
+        assert int(orc.bf16_ulp_distance(_bits(torch, got), _orc_bits(want)).max()) <= 1
+    else:
+        assert np.allclose(got.cpu().numpy(), want.f32(), rtol=2e-6, atol=1e-9)
+    total = got.float().sum(dim=axis)
+    assert torch.allclose(total, torch.ones_like(total), atol=2e-2 if dt == "bf16" else 1e-5)
+    # the primitive tests' known answers (primitive_tests.cpp:523-524)
+    kat = be.softmax(torch.tensor([[80.0, 81.0], [-80.0, -79.0]], device="cuda"), -1).cpu().numpy().reshape(-1)
+    assert np.allclose(kat, [0.26894143, 0.7310586, 0.26894143, 0.7310586], atol=2e-5)
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_indexed_gather(orc, gpu, dt):
+    import torch
+    from vrhino_b200._lib import VrbError
+    from vrhino_b200 import ops as vops
+    be = vops.B200Backend(execution_dtype=torch.bfloat16 if dt == "bf16" else torch.float32)
+    obe = orc.OracleBackend(execution_dtype=dt)
+    rng = np.random.default_rng(3)
+    for shape, index_shape, itype in (((50, 64), (2, 5), np.int64), ((50, 64), (7,), np.int32), ((9, 7), (3,), np.int64),
+                                      ((1000, 4096), (2, 512), np.int64), ((33, 6), (4, 4), np.int32), ((5, 8), (0,), np.int64)):
+        table, otable = _pair(orc, torch, shape, dt, 13)
+        indices = rng.integers(0, shape[0], size=index_shape).astype(itype)
+        got, want = be.indexed_gather(table, indices), obe.indexed_gather(otable, indices)
+        assert tuple(got.shape) == want.shape == tuple(index_shape) + (shape[1],)
+        assert np.array_equal(_bits(torch, got), _orc_bits(want))
+        assert np.array_equal(_bits(torch, be.indexed_gather(table, torch.from_numpy(indices).cuda())), _orc_bits(want))   # indices on the device
+    table, otable = _pair(orc, torch, (3, 11, 24), dt, 14)                    # a table per batch entry
+    for index_shape in ((3, 4), (3, 2, 5)):
+        indices = rng.integers(0, 11, size=index_shape).astype(np.int64)
+        got, want = be.indexed_gather(table, indices), obe.indexed_gather(otable, indices)
+        assert np.array_equal(_bits(torch, got), _orc_bits(want))
+    # a table of the other dtype is converted to the execution dtype first (copy_to_device, cuda_backend.cu:4032)
+    other = "f32" if dt == "bf16" else "bf16"
+    table, otable = _pair(orc, torch, (12, 16), other, 15)
+    indices = np.array([11, 0, 5], dtype=np.int64)
+    assert np.array_equal(_bits(torch, be.indexed_gather(table, indices)), _orc_bits(obe.indexed_gather(otable, indices)))
+    with pytest.raises(VrbError, match="index out of range"):
+        be.indexed_gather(table, np.array([12], dtype=np.int64))
+    with pytest.raises(VrbError, match="index out of range"):
+        be.indexed_gather(table, np.array([-1], dtype=np.int32))
+    with pytest.raises(VrbError, match="rank 2 or 3"):
+        be.indexed_gather(table.reshape(-1), indices)
+    with pytest.raises(VrbError, match="int64/int32"):
+        be.indexed_gather(table, np.array([1.0], dtype=np.float32))
+    with pytest.raises(VrbError, match="batch dimension mismatch"):
+        be.indexed_gather(table.reshape(2, 6, 16), np.zeros((3, 2), dtype=np.int64))
+
+
 def test_argument_rules(orc, gpu):
     import torch
     from vrhino_b200._lib import VrbError

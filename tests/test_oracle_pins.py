@@ -230,7 +230,8 @@ def test_l2_normalize(orc, be, shape):
 
 
 def test_layout_known_answers(orc, be):
-    """primitive_tests.cpp:353-361 (permute, concat, slice), :457 (sinusoidal_embedding), :518-520 (pad)."""
+    """primitive_tests.cpp:353-361 (permute, concat, slice), :370-375 (indexed_gather), :457 (sinusoidal_embedding),
+    :518-520 (pad), :523-524 (softmax)."""
     t = lambda shape, values: orc.tensor(np.array(values, dtype=np.float32).reshape(shape))
     flat = lambda r: r.data.reshape(-1)
     close(flat(be.permute(t((2, 3), [0, 1, 2, 3, 4, 5]), (1, 0))), [0, 3, 1, 4, 2, 5])
@@ -244,6 +245,12 @@ def test_layout_known_answers(orc, be):
     close(flat(be.interpolate_nearest(t((1, 1, 1, 2), [1, 2]), [2, 2])), [1, 1, 2, 2, 1, 1, 2, 2])
     close(flat(be.reduce_sum(t((2, 3), [1, 2, 3, 4, 5, 6]), 1, False)), [6, 15])                        # primitive_tests.cpp:521-522
     close(flat(be.reduce_sum(t((2, 2, 2), [1, 2, 3, 4, 5, 6, 7, 8]), 0, False)), [6, 8, 10, 12])
+    close(flat(be.softmax(t((1, 3), [0, 0, 0]), 1)), [1 / 3, 1 / 3, 1 / 3], 2e-5)                       # primitive_tests.cpp:523-524
+    close(flat(be.softmax(t((2, 2), [80, 81, -80, -79]), -1)), [0.26894143, 0.7310586, 0.26894143, 0.7310586], 2e-5)
+    close(flat(be.indexed_gather(t((4, 2), [10, 11, 20, 21, 30, 31, 40, 41]), np.array([[3, 0], [1, 2]], dtype=np.int64))),
+          [40, 41, 10, 11, 20, 21, 30, 31])                                                           # primitive_tests.cpp:370-375
+    close(flat(be.indexed_gather(t((2, 3, 2), [10, 11, 20, 21, 30, 31, 40, 41, 50, 51, 60, 61]), np.array([[2, 0], [1, 2]], dtype=np.int64))),
+          [30, 31, 10, 11, 50, 51, 60, 61])
     close(flat(be.pad(t((1, 2), [1, 2]), [1, 1], 0.0, False)), [0, 1, 2, 0])
     close(flat(be.pad(t((1, 1, 2), [1, 2]), [1, 0, 1, 0], -1.0, False)), [-1, -1, -1, -1, 1, 2])
     close(flat(be.pad(t((1, 2), [1, 2]), [1, 2], 0.0, True)), [1, 1, 2, 2, 2])

@@ -882,6 +882,46 @@ __global__ void __launch_bounds__(kThreads) sinusoidal_kernel(const T* __restric
     }
 }
 
+// ---- indexed gather -------------------------------------------------------------------------------------
+// CudaBackend::indexed_gather (:3981-4055, indexed_gather_kernel :1754-1768): out[b, n, :] = table[b, indices[b, n], :]
+// (one table for all indices when it is not batched).  A warp per gathered row, the row moved in the widest unit its
+// width and the two base addresses allow.  The caller has validated the indices, as the reference does on the host;
+// a row whose index is out of range all the same is left unwritten rather than read from outside the table.
+template <typename Unit, typename Index>
+__global__ void __launch_bounds__(kThreads) gather_rows_kernel(const Unit* __restrict__ table, const Index* __restrict__ indices,
+                                                               Unit* __restrict__ out, const int64_t gathered, const int64_t per_batch,
+                                                               const int64_t rows, const int64_t units) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x % 32;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
+    for (int64_t n = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + threadIdx.x / 32; n < gathered; n += warps) {
+        const int64_t row = static_cast<int64_t>(indices[n]);
+        if (row < 0 || row >= rows) continue;
+        const int64_t batch = per_batch > 0 ? n / per_batch : 0;
+        const Unit* const from = table + (batch * rows + row) * units;
+        Unit* const to = out + n * units;
+        int64_t u = lane;
+        for (; u + 96 < units; u += 128) {
+            const Unit a = from[u], b = from[u + 32], c = from[u + 64], d = from[u + 96];
+            to[u] = a; to[u + 32] = b; to[u + 64] = c; to[u + 96] = d;
+        }
+        for (; u < units; u += 32) to[u] = from[u];
+    }
+}
+
+template <typename Unit>
+void launch_gather(const void* table, const void* indices, int index_dtype, void* out, int64_t gathered, int64_t per_batch, int64_t rows,
+                   int64_t units, cudaStream_t stream) {
+    const int grid = grid_for((gathered + kThreads / 32 - 1) / (kThreads / 32), kPerSm);
+    if (index_dtype == VRB_I64)
+        launch_overlapped(gather_rows_kernel<Unit, int64_t>, dim3(grid), dim3(kThreads), 0, stream, static_cast<const Unit*>(table),
+                          static_cast<const int64_t*>(indices), static_cast<Unit*>(out), gathered, per_batch, rows, units);
+    else
+        launch_overlapped(gather_rows_kernel<Unit, int32_t>, dim3(grid), dim3(kThreads), 0, stream, static_cast<const Unit*>(table),
+                          static_cast<const int32_t*>(indices), static_cast<Unit*>(out), gathered, per_batch, rows, units);
+}
+
 }  // namespace
 }  // namespace vrb
 
@@ -1068,3 +1108,25 @@ extern "C" int vrb_sinusoidal_embedding(const void* positions, void* out, int dt
     return after_launch("sinusoidal_embedding");
 }
 
+
+extern "C" int vrb_indexed_gather(const void* table, const void* indices, int index_dtype, void* out, int dtype, int64_t batches,
+                                  int64_t rows, int64_t width, int64_t indices_per_batch, vrb_stream stream) {
+    VRB_REQUIRE(is_float_dtype(dtype), VRB_ERR_UNSUPPORTED, "indexed_gather: dtype must be F32 or BF16");
+    VRB_REQUIRE(index_dtype == VRB_I64 || index_dtype == VRB_I32, VRB_ERR_INVALID, "indexed_gather indices must be rank >=1 int64/int32");
+    VRB_REQUIRE(batches >= 0 && rows >= 0 && width >= 0 && indices_per_batch >= 0, VRB_ERR_INVALID, "indexed_gather: invalid shape");
+    // batches == 0: one table for every index (indices_per_batch is then the whole count)
+    const int64_t gathered = (batches > 0 ? batches : 1) * indices_per_batch;
+    if (gathered * width == 0) return VRB_OK;
+    VRB_REQUIRE(rows > 0, VRB_ERR_INVALID, "indexed_gather index out of range");
+    VRB_REQUIRE(table && indices && out, VRB_ERR_INVALID, "indexed_gather: null tensor");
+    const int64_t row_bytes = width * static_cast<int64_t>(dtype_bytes(dtype));
+    const int64_t per_batch = batches > 0 ? indices_per_batch : 0;
+    cudaStream_t s = as_stream(stream);
+    if (row_bytes % 16 == 0 && aligned16(table) && aligned16(out))
+        launch_gather<uint4>(table, indices, index_dtype, out, gathered, per_batch, rows, row_bytes / 16, s);
+    else if (row_bytes % 4 == 0 && reinterpret_cast<uintptr_t>(table) % 4 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0)
+        launch_gather<uint32_t>(table, indices, index_dtype, out, gathered, per_batch, rows, row_bytes / 4, s);
+    else
+        launch_gather<uint16_t>(table, indices, index_dtype, out, gathered, per_batch, rows, row_bytes / 2, s);
+    return after_launch("indexed_gather");
+}

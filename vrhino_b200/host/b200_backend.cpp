@@ -598,6 +598,52 @@ Tensor B200Backend::reduce_sum(const Tensor& raw, int64_t dim, bool keepdim) {
     });
 }
 
+Tensor B200Backend::softmax(const Tensor& raw, int64_t axis) {
+    return guarded([&] {   // VRHINO_PROFILE("softmax") (cuda_backend.cu:4895)
+        if (axis < 0) axis += static_cast<int64_t>(raw.ndim());
+        require(axis >= 0 && axis < static_cast<int64_t>(raw.ndim()), "softmax axis invalid");
+        const DType dtype = operand_dtype(raw);
+        Tensor x = copy_to_device(raw, dtype);
+        int64_t outer = 1, inner = 1;
+        for (int64_t d = 0; d < axis; ++d) outer *= x.dim(d);
+        for (int64_t d = axis + 1; d < static_cast<int64_t>(x.ndim()); ++d) inner *= x.dim(d);
+        Tensor out = rt_->allocate_device(x.shape(), dtype);
+        ProfileRegion region(*this, [] { return std::string("softmax"); }, bytes_of(x) + bytes_of(out));
+        check(vrb_softmax(x.data(), out.data(), code(dtype), outer, x.dim(axis), inner, kLegacyStream));
+        return out;
+    });
+}
+
+Tensor B200Backend::indexed_gather(const Tensor& table_raw, const Tensor& indices_raw) {
+    return guarded([&] {   // VRHINO_PROFILE("indexed_gather") (cuda_backend.cu:3983)
+        require(table_raw.ndim() == 2 || table_raw.ndim() == 3, "indexed_gather table must have rank 2 or 3");
+        require(indices_raw.ndim() >= 1 && (indices_raw.dtype() == DType::I64 || indices_raw.dtype() == DType::I32),
+                "indexed_gather indices must be rank >=1 int64/int32");
+        const bool batched = table_raw.ndim() == 3;
+        if (batched) require(indices_raw.dim(0) == table_raw.dim(0), "indexed_gather batch dimension mismatch");
+        // quantised tables and dense host tables (of which the reference uploads the selected rows only) keep the runtime's path
+        if (table_raw.is_quantized() || table_raw.device().is_host()) return rt_->indexed_gather(table_raw, indices_raw);
+        const int64_t rows = table_raw.dim(batched ? 1 : 0), width = table_raw.dim(-1);
+        const Tensor host_indices = indices_raw.device().is_host() ? indices_raw : copy_to_host(indices_raw);
+        for (int64_t k = 0; k < host_indices.numel(); ++k) {
+            const int64_t value = host_indices.dtype() == DType::I64 ? host_indices.data_as<int64_t>()[k]
+                                                                      : static_cast<int64_t>(host_indices.data_as<int32_t>()[k]);
+            require(value >= 0 && value < rows, "indexed_gather index out of range");
+        }
+        const DType dtype = execution_dtype();
+        Tensor table = copy_to_device(table_raw, dtype);
+        Tensor indices = copy_to_device(indices_raw, indices_raw.dtype());
+        std::vector<int64_t> shape = indices_raw.shape();
+        shape.push_back(width);
+        Tensor out = rt_->allocate_device(shape, dtype);
+        const int64_t per_batch = batched ? (indices_raw.dim(0) ? indices_raw.numel() / indices_raw.dim(0) : 0) : indices_raw.numel();
+        ProfileRegion region(*this, [] { return std::string("indexed_gather"); }, 2 * bytes_of(out));
+        check(vrb_indexed_gather(table.data(), indices.data(), indices_raw.dtype() == DType::I64 ? VRB_I64 : VRB_I32, out.data(), code(dtype),
+                                 batched ? table.dim(0) : 0, rows, width, per_batch, kLegacyStream));
+        return out;
+    });
+}
+
 Tensor B200Backend::pad_axes(const Tensor& raw, const std::vector<int64_t>& before, const std::vector<int64_t>& after, float value,
                              const std::vector<bool>& replicate) {
     return guarded([&] {

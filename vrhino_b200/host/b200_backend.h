@@ -71,6 +71,8 @@ public:
                vrhino::PadMode mode = vrhino::PadMode::Constant) override;
     Tensor interpolate_nearest(const Tensor& x, const std::vector<double>& factors) override;   // :5010-5016
     Tensor reduce_sum(const Tensor& x, int64_t dim, bool keepdim = false) override;              // :4885-4892
+    Tensor softmax(const Tensor& x, int64_t axis) override;                                      // :4893-4917
+    Tensor indexed_gather(const Tensor& table, const Tensor& indices) override;                  // :3981-4055
     // per-axis extents and modes in one pass (replicate axes first, then the constant axes)
     Tensor pad_axes(const Tensor& x, const std::vector<int64_t>& before, const std::vector<int64_t>& after, float value,
                     const std::vector<bool>& replicate);
@@ -184,14 +186,12 @@ public:
     Tensor linear(const Tensor& x, const Tensor& w, const Tensor* b = nullptr, DType c = DType::F16, DType o = DType::F16) override { return rt_->linear(x, w, b, c, o); }
     Tensor batched_matmul(const Tensor& a, const Tensor& b) override { return rt_->batched_matmul(a, b); }
     Tensor reshape(const Tensor& x, const std::vector<int64_t>& s) override { return rt_->reshape(x, s); }
-    Tensor indexed_gather(const Tensor& t, const Tensor& i) override { return rt_->indexed_gather(t, i); }
     Tensor attention(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor* mask = nullptr, bool causal = false,
                      float scale = 0.0f, const Tensor* bias = nullptr, vrhino::AttentionObservation* obs = nullptr) override {
         return rt_->attention(q, k, v, mask, causal, scale, bias, obs);
     }
     Tensor conv3d(const Tensor& x, const Tensor& w, const Tensor* b, const std::vector<int>& s, const std::vector<int>& p,
                   const std::vector<int>& d = {1, 1, 1}, int g = 1) override { return rt_->conv3d(x, w, b, s, p, d, g); }
-    Tensor softmax(const Tensor& x, int64_t a) override { return rt_->softmax(x, a); }
     Tensor conv2d(const Tensor& x, const Tensor& w, const Tensor* b, const std::vector<int>& s, const std::vector<int>& p,
                   const std::vector<int>& d = {1, 1}, int g = 1) override { return rt_->conv2d(x, w, b, s, p, d, g); }
     Tensor conv_transpose2d(const Tensor& x, const Tensor& w, const Tensor* b, const std::vector<int>& s, const std::vector<int>& p,

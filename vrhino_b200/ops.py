@@ -372,6 +372,49 @@ class B200Backend:
         call("vrb_reduce_sum", _ptr(x), _ptr(out), _code(dtype), outer, x.shape[dim], inner, _stream())
         return out
 
+    def softmax(self, raw, axis, out=None):
+        """CudaBackend::softmax (cuda_backend.cu:4893-4917): over `axis`, the denominator accumulated in F32 in index order."""
+        if axis < 0:
+            axis += raw.dim()
+        if not 0 <= axis < raw.dim():
+            raise VrbError("softmax axis invalid")
+        dtype = self._dtype_of(raw)
+        x = _dense(self.copy_to_device(raw, dtype))
+        outer, inner = 1, 1
+        for d in x.shape[:axis]:
+            outer *= d
+        for d in x.shape[axis + 1:]:
+            inner *= d
+        out = _result(out, tuple(x.shape), dtype, x.device)
+        call("vrb_softmax", _ptr(x), _ptr(out), _code(dtype), outer, x.shape[axis], inner, _stream())
+        return out
+
+    def indexed_gather(self, table_raw, indices_raw, out=None):
+        """CudaBackend::indexed_gather (cuda_backend.cu:3981-4055): table [rows, width] or [batch, rows, width], integer
+        indices [...] (their first axis the batch when the table has one) -> [..., width] in the execution dtype.  The
+        indices are checked on the host first, as the reference does."""
+        import numpy as np
+        if table_raw.dim() not in (2, 3):
+            raise VrbError("indexed_gather table must have rank 2 or 3")
+        indices = torch.as_tensor(np.asarray(indices_raw)) if not isinstance(indices_raw, torch.Tensor) else indices_raw
+        if indices.dim() < 1 or indices.dtype not in (torch.int64, torch.int32):
+            raise VrbError("indexed_gather indices must be rank >=1 int64/int32")
+        batched = table_raw.dim() == 3
+        if batched and indices.shape[0] != table_raw.shape[0]:
+            raise VrbError("indexed_gather batch dimension mismatch")
+        rows, width = table_raw.shape[-2], table_raw.shape[-1]
+        host = indices.cpu()
+        if host.numel() and (int(host.min()) < 0 or int(host.max()) >= rows):
+            raise VrbError("indexed_gather index out of range")
+        dtype = self.execution_dtype
+        table = _dense(self.copy_to_device(table_raw, dtype))
+        device_indices = _dense(indices.to(table.device))
+        out = _result(out, tuple(indices.shape) + (width,), dtype, table.device)
+        per_batch = indices.numel() // indices.shape[0] if batched else indices.numel()
+        call("vrb_indexed_gather", _ptr(table), _ptr(device_indices), 3 if indices.dtype == torch.int64 else 4, _ptr(out), _code(dtype),
+             table.shape[0] if batched else 0, rows, width, per_batch, _stream())
+        return out
+
     def sinusoidal_embedding(self, raw, width, flip, downscale, frequency_f64, out=None):
         """CudaBackend::sinusoidal_embedding: positions [n] -> [n, width]."""
         if raw.dim() != 1 or width <= 0:
