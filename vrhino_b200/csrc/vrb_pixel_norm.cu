@@ -99,14 +99,38 @@ __device__ __forceinline__ float reciprocal_or_zero(float d) {
 // the exact expression.  (The flush-to-zero forms are exact here: 1 + t is in [1, 2^24] and a denormal argument
 // gives t = 1 either way.)
 constexpr int kSiluGuardUlps = 10;
+// whether the low 16 bits of an F32 value lie within kSiluGuardUlps of 0x8000, where its bf16 rounding turns
+__device__ __forceinline__ bool near_bf16_boundary(float value) {
+    return ((__float_as_uint(value) - (0x8000u - kSiluGuardUlps)) & 0xffffu) <= 2u * kSiluGuardUlps;
+}
 __device__ __forceinline__ float silu_approximate(float v, bool& redo) {
     float t, inverse;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(__fmul_rn(v, -1.4426950408889634f)));
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inverse) : "f"(__fadd_rn(1.0f, t)));
     const float fast = __fmul_rn(v, inverse);
-    const int low = static_cast<int>(__float_as_uint(fast) & 0xffffu) - 0x8000;
-    redo = redo || !(fabsf(v) <= 8.0f) || abs(low) <= kSiluGuardUlps;
+    redo = redo || !(fabsf(v) <= 8.0f) || near_bf16_boundary(fast);
     return fast;
+}
+
+// The same for two values at once, the multiplications and the addition as packed F32 operations (they round like
+// the scalar ones).  Returns whether either result has to be redone (silu_redo() says which).
+__device__ __forceinline__ bool silu_approximate_pair(float v0, float v1, float& s0, float& s1) {
+    const unsigned long long v2 = pack_f32x2(v0, v1);
+    float t0, t1, i0, i1;
+    unpack_f32x2(mul_f32x2(v2, pack_f32x2(-1.4426950408889634f, -1.4426950408889634f)), t0, t1);
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t0) : "f"(t0));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t1) : "f"(t1));
+    unpack_f32x2(add_f32x2(pack_f32x2(t0, t1), pack_f32x2(1.0f, 1.0f)), t0, t1);
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(i0) : "f"(t0));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(i1) : "f"(t1));
+    unpack_f32x2(mul_f32x2(v2, pack_f32x2(i0, i1)), s0, s1);
+    return !(fabsf(v0) <= 8.0f) || !(fabsf(v1) <= 8.0f) || near_bf16_boundary(s0) || near_bf16_boundary(s1);
+}
+// Whether an approximate result has to be redone, judged from the result alone (the argument is no longer at hand):
+// an argument outside [-8, 8] or NaN shows as a result above 7.9, in (-0.01, 0], or NaN.  A superset of
+// silu_approximate's own conditions; where it flags a valid result the exact expression gives the same bits.
+__device__ __forceinline__ bool silu_redo(float approximate) {
+    return !(approximate <= 7.9f) || !(approximate <= -0.01f || approximate > 0.0f) || near_bf16_boundary(approximate);
 }
 
 // One normalised element to the stored value, everything known at compile time.  EXACT: the reference's operations
@@ -306,9 +330,12 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
                 } else {
                     in[0] = __uint_as_float(raw.x); in[1] = __uint_as_float(raw.y); in[2] = __uint_as_float(raw.z); in[3] = __uint_as_float(raw.w);
                 }
-                unsigned redo = 0;   // bit j: element j has to be evaluated with the exact forms
                 if constexpr (X_BF16) {
-                    // the reciprocal form two elements at a time (packed F32 operations round like the scalar ones)
+                    // The short forms, two elements at a time (packed F32 operations round like the scalar ones).  `any`
+                    // collects, for the whole chunk, whether some element must be evaluated again with the exact forms;
+                    // which ones is found out afterwards, from values still in registers, only in the chunks that need it.
+                    bool any = false;
+                    const unsigned long long ops2 = pack_f32x2(ops, ops);
 #pragma unroll
                     for (int j = 0; j < EPC; j += 2) {
                         const unsigned long long x2 = pack_f32x2(in[j], in[j + 1]), r2 = pack_f32x2(r[j], r[j + 1]);
@@ -316,45 +343,62 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
                         const unsigned long long c2 = fma_f32x2(fma_f32x2(pack_f32x2(-d[j], -d[j + 1]), q2, x2), r2, q2);
                         float c0, c1;
                         unpack_f32x2(c2, c0, c1);
-                        bool again0 = !(fabsf(c0) >= kQuotientFloor), again1 = !(fabsf(c1) >= kQuotientFloor);
-                        if constexpr (MODE == kNormOnly) {
-                            v[j] = c0;      // the bf16 store rounds
-                            v[j + 1] = c1;
-                        } else {
+                        any = any || !(fabsf(c0) >= kQuotientFloor) || !(fabsf(c1) >= kQuotientFloor);
+                        if constexpr (MODE != kNormOnly) {
                             // rounding to bf16 as a pair (one conversion); modulate: a multiplication and an addition,
                             // each rounded
                             const __nv_bfloat162 y2 = __floats2bfloat162_rn(c0, c1);
                             const uint32_t yw = *reinterpret_cast<const uint32_t*>(&y2);
-                            c0 = __fadd_rn(__fmul_rn(__uint_as_float(yw << 16), ops), sh);
-                            c1 = __fadd_rn(__fmul_rn(__uint_as_float(yw & 0xffff0000u), ops), sh);
+                            // (the product packed, the sums scalar: with the addition packed as well, 28 % of the results were
+                            // one ulp off -- the rate of a fused multiply-add -- although both instructions carry .rn)
+                            unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(yw << 16), __uint_as_float(yw & 0xffff0000u)), ops2), c0, c1);
+                            c0 = __fadd_rn(c0, sh);
+                            c1 = __fadd_rn(c1, sh);
                             if constexpr (MODE == kModulateSilu) {
                                 if constexpr (OUT_BF16) {
-                                    c0 = silu_approximate(c0, again0);
-                                    c1 = silu_approximate(c1, again1);
+                                    float s0, s1;
+                                    any = silu_approximate_pair(c0, c1, s0, s1) || any;
+                                    c0 = s0;
+                                    c1 = s1;
                                 } else {
                                     c0 = activation_value(VRB_SILU, c0);
                                     c1 = activation_value(VRB_SILU, c1);
                                 }
                             }
-                            v[j] = c0;
-                            v[j + 1] = c1;
                         }
-                        redo |= (again0 ? 1u : 0u) << j | (again1 ? 2u : 0u) << j;
+                        v[j] = c0;
+                        v[j + 1] = c1;
+                    }
+                    if (any) {
+                        // rare (one chunk in a few hundred).  An element is evaluated again with the reference's operations
+                        // one by one if its reciprocal was withheld, its quotient may lie below the floor (|x| < 2^-27 d is a
+                        // superset of |x / d| < 2^-28), or -- approximate SiLU -- its result says the argument may have been
+                        // outside [-8, 8] (SiLU > 7.9, or in (-0.01, 0]) or lies near the rounding boundary; a few elements
+                        // too many are harmless, the exact form gives the same bits where both are valid.
+                        bool unused = false;
+#pragma unroll
+                        for (int j = 0; j < EPC; ++j) {
+                            bool again = r[j] == 0.0f || !(fabsf(in[j]) >= __fmul_rn(d[j], 2.0f * kQuotientFloor));
+                            if constexpr (MODE == kModulateSilu && OUT_BF16)
+                                again = again || silu_redo(v[j]);
+                            if (again) v[j] = finish_tile<X_BF16, MODE, OUT_BF16, true>(in[j], d[j], r[j], ops, sh, unused);
+                        }
                     }
                 } else {
+                    unsigned redo = 0;   // bit j: element j has to be evaluated with the exact forms
 #pragma unroll
                     for (int j = 0; j < EPC; ++j) {
                         bool again = false;
                         v[j] = finish_tile<X_BF16, MODE, OUT_BF16, false>(in[j], d[j], r[j], ops, sh, again);
                         redo |= (again ? 1u : 0u) << j;
                     }
-                }
-                if constexpr (kHasShortForm<X_BF16, MODE, OUT_BF16>) {
-                    if (redo != 0) {   // rare: only the flagged elements, with the reference's operations one by one
-                        bool unused = false;
+                    if constexpr (kHasShortForm<X_BF16, MODE, OUT_BF16>) {
+                        if (redo != 0) {   // rare: only the flagged elements, with the reference's operations one by one
+                            bool unused = false;
 #pragma unroll
-                        for (int j = 0; j < EPC; ++j)
-                            if ((redo >> j) & 1u) v[j] = finish_tile<X_BF16, MODE, OUT_BF16, true>(in[j], d[j], r[j], ops, sh, unused);
+                            for (int j = 0; j < EPC; ++j)
+                                if ((redo >> j) & 1u) v[j] = finish_tile<X_BF16, MODE, OUT_BF16, true>(in[j], d[j], r[j], ops, sh, unused);
+                        }
                     }
                 }
                 if constexpr (X_BF16) {
@@ -625,8 +669,10 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
                 uint32_t ow[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    __nv_bfloat162 y2 = __floats2bfloat162_rn(__fmul_rn(__uint_as_float(wd[j] << 16), inv[2 * j]),
-                                                              __fmul_rn(__uint_as_float(wd[j] & 0xffff0000u), inv[2 * j + 1]));
+                    float a, b;
+                    unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(wd[j] << 16), __uint_as_float(wd[j] & 0xffff0000u)),
+                                           pack_f32x2(inv[2 * j], inv[2 * j + 1])), a, b);
+                    __nv_bfloat162 y2 = __floats2bfloat162_rn(a, b);
                     if (weighted) y2 = __hmul2_rn(y2, w2);
                     uint32_t word = *reinterpret_cast<const uint32_t*>(&y2);
                     if constexpr (SILU) {
@@ -634,11 +680,10 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
                         // (silu_approximate above; all 65536 bf16 arguments are checked by tests/test_gpu_pixel_norm.py),
                         // else the exact expression
                         const float lo = __uint_as_float(word << 16), hi = __uint_as_float(word & 0xffff0000u);
-                        bool again_lo = false, again_hi = false;
-                        float s_lo = silu_approximate(lo, again_lo), s_hi = silu_approximate(hi, again_hi);
-                        if (again_lo || again_hi) {
-                            if (again_lo) s_lo = activation_value(VRB_SILU, lo);
-                            if (again_hi) s_hi = activation_value(VRB_SILU, hi);
+                        float s_lo, s_hi;
+                        if (silu_approximate_pair(lo, hi, s_lo, s_hi)) {
+                            if (!(fabsf(lo) <= 8.0f) || near_bf16_boundary(s_lo)) s_lo = activation_value(VRB_SILU, lo);
+                            if (!(fabsf(hi) <= 8.0f) || near_bf16_boundary(s_hi)) s_hi = activation_value(VRB_SILU, hi);
                         }
                         word = pack_bf16x2(s_lo, s_hi);
                     }
