@@ -188,6 +188,7 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
     float* const denominator = partial + kLanes * positions;                                              // [positions]
     float* const reciprocal = denominator + positions;                                                    // [positions], bf16 input only
     uint64_t* const barriers = reinterpret_cast<uint64_t*>(reciprocal + positions);                       // [2], TMA only
+    float2* const modulation = reinterpret_cast<float2*>(barriers + 2);                                   // [channels] (1 + scale, shift)
     const uint32_t inner_chunks = static_cast<uint32_t>(p.inner / EPC);
     const uint32_t tiles_per_outer = (inner_chunks + cols - 1) >> cols_log2;
     const uint32_t tiles = static_cast<uint32_t>(p.outer) * tiles_per_outer;
@@ -235,6 +236,7 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
     };
 
     int buffer = 0;
+    uint32_t modulation_of = 0xffffffffu;   // the batch entry whose vectors the table holds
     request(blockIdx.x, 0);
     for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, buffer ^= 1) {
         const uint32_t o = t / tiles_per_outer;
@@ -289,6 +291,16 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
             denominator[threadIdx.x] = d;
             if constexpr (X_BF16) reciprocal[threadIdx.x] = reciprocal_or_zero(d);
         }
+        if constexpr (MODE != kNormOnly) {
+            // this batch entry's (1 + scale, shift) per channel, once per tile instead of once per chunk
+            if (o != modulation_of) {
+                for (int c = threadIdx.x; c < channels; c += kThreads) {
+                    const int64_t vector = static_cast<int64_t>(o) * channels + c;
+                    modulation[c] = make_float2(__fadd_rn(1.0f, load1(p.scale, p.mod_dt, vector)), load1(p.shift, p.mod_dt, vector));
+                }
+                modulation_of = o;
+            }
+        }
         __syncthreads();
         if (chunk0 + k < inner_chunks) {
             // this thread's positions: denominators and reciprocals once per tile
@@ -310,13 +322,17 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
             const int64_t first = (static_cast<int64_t>(o) * channels + c0) * inner_chunks + chunk0 + k;   // in chunks
             char* out = static_cast<char*>(p.out) + first * OUT_CHUNK;
             const int64_t out_step = row_step * OUT_CHUNK;
-            int64_t vector = static_cast<int64_t>(o) * channels + c0;                                     // into scale / shift
+            float minus_d[EPC];
+#pragma unroll
+            for (int j = 0; j < EPC; ++j) minus_d[j] = -d[j];
+            const float2* vectors = modulation + c0;
             const uint4* chunk = tile + threadIdx.x;
-            for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads, chunk += kThreads, out += out_step, vector += c_step) {
+            for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads, chunk += kThreads, out += out_step, vectors += c_step) {
                 float ops = 1.0f, sh = 0.0f;
                 if constexpr (MODE != kNormOnly) {
-                    ops = __fadd_rn(1.0f, load1(p.scale, p.mod_dt, vector));
-                    sh = load1(p.shift, p.mod_dt, vector);
+                    const float2 pair = *vectors;
+                    ops = pair.x;
+                    sh = pair.y;
                 }
                 const uint4 raw = *chunk;
                 float in[EPC], v[EPC];
@@ -340,7 +356,7 @@ __global__ void __launch_bounds__(kThreads) pixel_norm_tile_kernel(const PixelNo
                     for (int j = 0; j < EPC; j += 2) {
                         const unsigned long long x2 = pack_f32x2(in[j], in[j + 1]), r2 = pack_f32x2(r[j], r[j + 1]);
                         const unsigned long long q2 = mul_f32x2(x2, r2);
-                        const unsigned long long c2 = fma_f32x2(fma_f32x2(pack_f32x2(-d[j], -d[j + 1]), q2, x2), r2, q2);
+                        const unsigned long long c2 = fma_f32x2(fma_f32x2(pack_f32x2(minus_d[j], minus_d[j + 1]), q2, x2), r2, q2);
                         float c0, c1;
                         unpack_f32x2(c2, c0, c1);
                         any = any || !(fabsf(c0) >= kQuotientFloor) || !(fabsf(c1) >= kQuotientFloor);
@@ -805,9 +821,11 @@ int pixel_norm_family(const void* x, int dtype, const void* scale, const void* s
         for (int budget_ctas : {3, 1}) {
             for (int cols = 8, log2 = 3; cols >= 1; cols >>= 1, --log2) {
                 if (cols > 1 && cols / 2 >= inner_chunks) continue;
-                const size_t smem = 2 * static_cast<size_t>(channels) * cols * 16 + static_cast<size_t>(kLanes + 2) * cols * epc * 4;
-                if (smem > (budget_ctas == 3 ? 72 * 1024 : 200 * 1024) || smem > kMaxTileBytes) continue;
                 const int mode = !scale ? kNormOnly : fuse_silu ? kModulateSilu : kModulate;
+                // two tile buffers, the partial sums / denominators / reciprocals, and (1 + scale, shift) per channel
+                const size_t smem = 2 * static_cast<size_t>(channels) * cols * 16 + static_cast<size_t>(kLanes + 2) * cols * epc * 4 +
+                                    (mode != kNormOnly ? static_cast<size_t>(channels) * 8 : 0);
+                if (smem > (budget_ctas == 3 ? 72 * 1024 : 200 * 1024) || smem > kMaxTileBytes) continue;
                 const int variant = (dtype == VRB_BF16 ? 8 : 0) | (mode << 1) | (out_dtype == VRB_BF16 ? 1 : 0);
                 const int64_t tiles = outer * ((inner_chunks + cols - 1) / cols);
                 bool launched = true;
