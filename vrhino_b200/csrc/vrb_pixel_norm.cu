@@ -562,6 +562,15 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
     float* const inverse = reinterpret_cast<float*>(partial + kLanes * positions);                          // [positions]
     // two mbarriers (TMA only) behind the scratch, 8-byte aligned: positions is a multiple of 4
     uint64_t* const barriers = reinterpret_cast<uint64_t*>(inverse + positions);
+    // the weight per channel, rounded to x's dtype (a bf16 weight twice in one word, for the packed product)
+    uint32_t* const weights = reinterpret_cast<uint32_t*>(barriers + 2);
+    if (p.weight != nullptr) {
+        for (int c = threadIdx.x; c < channels; c += kThreads) {
+            const float w = round_to(X_DT, load1(p.weight, p.w_dt, c));
+            weights[c] = X_BF16 ? (__float_as_uint(w) >> 16) * 0x10001u : __float_as_uint(w);
+        }
+    }
+    __syncthreads();
     if constexpr (TMA) {
         if (threadIdx.x == 0) {
             mbarrier_init(&barriers[0], 1);
@@ -664,9 +673,10 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
         const bool weighted = p.weight != nullptr;
         uint4* out = static_cast<uint4*>(p.out) + (static_cast<int64_t>(o) * channels + c0) * inner_chunks + chunk0 + k;
         const uint4* chunk_at = tile + threadIdx.x;
-        int c = c0;
-        for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads, chunk_at += kThreads, out += row_step, c += c_step) {
-            const float w = weighted ? round_to(X_DT, load1(p.weight, p.w_dt, c)) : 1.0f;
+        const uint32_t* weight_at = weights + c0;
+        for (int idx = threadIdx.x; idx < tile_chunks; idx += kThreads, chunk_at += kThreads, out += row_step, weight_at += c_step) {
+            const uint32_t weight_word = weighted ? *weight_at : 0u;
+            const float w = weighted ? (X_BF16 ? __uint_as_float(weight_word << 16) : __uint_as_float(weight_word)) : 1.0f;
             const uint4 raw = *chunk_at;
             auto finish_one = [&](float v, float inv) {
                 float y = __fmul_rn(v, inv);
@@ -681,7 +691,7 @@ __global__ void __launch_bounds__(kThreads) rms_axis_tile_kernel(const RmsAxisPa
                 // reference), SiLU per element on the bf16 bits
                 const float inv[8] = {ia.x, ia.y, ia.z, ia.w, ib.x, ib.y, ib.z, ib.w};
                 const uint32_t wd[4] = {raw.x, raw.y, raw.z, raw.w};
-                const __nv_bfloat162 w2 = __floats2bfloat162_rn(w, w);     // w is on the bf16 grid already
+                const __nv_bfloat162 w2 = *reinterpret_cast<const __nv_bfloat162*>(&weight_word);
                 uint32_t ow[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -731,7 +741,9 @@ bool launch_rms_axis_tiles(const void* x, int dtype, const void* weight, int wei
     for (int budget_ctas : {3, 1}) {
         for (int cols = 8, log2 = 3; cols >= 1; cols >>= 1, --log2) {
             if (cols > 1 && cols / 2 >= inner_chunks) continue;
-            const size_t smem = 2 * static_cast<size_t>(channels) * cols * 16 + static_cast<size_t>(cols) * epc * (kLanes * 8 + 4);
+            // two tile buffers, the partial sums and inverses, the weight per channel
+            const size_t smem = 2 * static_cast<size_t>(channels) * cols * 16 + static_cast<size_t>(cols) * epc * (kLanes * 8 + 4) +
+                                (weight ? static_cast<size_t>(channels) * 4 : 0);
             if (smem > (budget_ctas == 3 ? 72 * 1024 : 200 * 1024) || smem > kMaxTileBytes) continue;
             const int64_t tiles = outer * ((inner_chunks + cols - 1) / cols);
             bool launched = true;
