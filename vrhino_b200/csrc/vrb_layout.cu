@@ -36,6 +36,8 @@ struct Walk {
     int64_t in_extent[kMaxDims];   // pad: extent of the source along the dimension
     int64_t before[kMaxDims];      // pad: leading pad along the dimension
     int64_t total;                 // units to move
+    int64_t step[kMaxDims];        // the distance between a thread's consecutive units (grid size x block size), as
+                                   // coordinates: digits in the mixed radix of the extents (step[0] may exceed extent[0])
 };
 
 template <typename Unit>
@@ -56,6 +58,65 @@ __global__ void __launch_bounds__(kThreads) walk_kernel(const Unit* __restrict__
     const Index total = static_cast<Index>(w.total);
     const Index stride = static_cast<Index>(gridDim.x) * kThreads;
     const int rank = RANK > 0 ? RANK : w.rank;
+    if constexpr (RANK > 0) {
+        // Compile-time rank: the coordinates of the thread's first unit are found by division once; from one unit to
+        // the thread's next they advance by the launch's step, digit by digit with carries -- no division in the loop.
+        using Offset = typename std::conditional<sizeof(Index) == 4, int32_t, int64_t>::type;
+        Index coordinate[RANK];
+        {
+            Index remaining = static_cast<Index>(blockIdx.x) * kThreads + threadIdx.x;
+#pragma unroll
+            for (int d = RANK - 1; d > 0; --d) {
+                const Index extent = static_cast<Index>(w.extent[d]);
+                const Index quotient = remaining / extent;
+                coordinate[d] = remaining - quotient * extent;
+                remaining = quotient;
+            }
+            coordinate[0] = remaining;
+        }
+        for (Index base = static_cast<Index>(blockIdx.x) * kThreads + threadIdx.x; base < total; base += stride * kUnroll) {
+            Unit value[kUnroll];
+            Offset target[kUnroll];
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) {
+                target[k] = -1;
+                if (base + static_cast<Index>(k) * stride < total) {
+                    Offset source = 0, destination = 0;
+                    bool valid = true;
+#pragma unroll
+                    for (int d = 0; d < RANK; ++d) {
+                        destination += static_cast<Offset>(coordinate[d]) * static_cast<Offset>(w.out_stride[d]);
+                        Offset from = static_cast<Offset>(coordinate[d]);
+                        if constexpr (PAD) {
+                            from -= static_cast<Offset>(w.before[d]);
+                            if (from < 0 || from >= static_cast<Offset>(w.in_extent[d])) {
+                                valid = valid && ((replicate >> d) & 1) != 0;
+                                from = from < 0 ? 0 : static_cast<Offset>(w.in_extent[d]) - 1;
+                            }
+                        }
+                        source += from * static_cast<Offset>(w.in_stride[d]);
+                    }
+                    target[k] = destination;
+                    value[k] = valid ? in[source] : unit_of<Unit>(fill);
+                }
+                // on to the thread's next unit (past the end the coordinates are no longer used)
+                Index carry = 0;
+#pragma unroll
+                for (int d = RANK - 1; d > 0; --d) {
+                    const Index extent = static_cast<Index>(w.extent[d]);
+                    Index next = coordinate[d] + static_cast<Index>(w.step[d]) + carry;
+                    carry = next >= extent ? 1 : 0;
+                    if (carry) next -= extent;
+                    coordinate[d] = next;
+                }
+                coordinate[0] += static_cast<Index>(w.step[0]) + carry;
+            }
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k)
+                if (target[k] >= 0) out[target[k]] = value[k];
+        }
+        return;
+    }
     for (Index base = static_cast<Index>(blockIdx.x) * kThreads + threadIdx.x; base < total; base += stride * kUnroll) {
         Unit value[kUnroll];
         int64_t target[kUnroll];
@@ -593,12 +654,20 @@ void launch_walk(const void* in, void* out, const Walk& w, const uint4& fill, in
     }
     const int64_t limit = int64_t{1} << 31;
     const bool wide = w.total + static_cast<int64_t>(grid) * per_block >= limit || reach_in >= limit || reach_out >= limit;
+    // the step between a thread's units, in coordinates
+    Walk stepped = w;
+    int64_t remaining = static_cast<int64_t>(grid) * kThreads;
+    for (int d = w.rank - 1; d > 0; --d) {
+        stepped.step[d] = remaining % w.extent[d];
+        remaining /= w.extent[d];
+    }
+    stepped.step[0] = remaining;
     if (wide)
         launch_overlapped(walk_kernel<Unit, 0, PAD, int64_t>, dim3(grid), dim3(kThreads), 0, stream, static_cast<const Unit*>(in),
-                          static_cast<Unit*>(out), w, fill, replicate);
+                          static_cast<Unit*>(out), stepped, fill, replicate);
     else
         launch_overlapped(walk_kernel<Unit, RANK, PAD, uint32_t>, dim3(grid), dim3(kThreads), 0, stream, static_cast<const Unit*>(in),
-                          static_cast<Unit*>(out), w, fill, replicate);
+                          static_cast<Unit*>(out), stepped, fill, replicate);
 }
 
 template <typename Unit>
