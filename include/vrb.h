@@ -202,6 +202,11 @@ int vrb_indexed_gather(const void* table, const void* indices, int index_dtype, 
  * expf(x - max) / sum stored in x's dtype. */
 int vrb_softmax(const void* x, void* out, int dtype, int64_t outer, int64_t axis, int64_t inner, vrb_stream stream);
 
+/* CudaBackend::rng_normal (:5120-5126, rng_normal_kernel :2225-2231): out[i] = the first normal of cuRAND's
+ * Philox4x32-10 stream (seed, subsequence i, offset), F32 or rounded to bf16: the reference's values bit for bit.
+ * The caller keeps the RngState (native/include/vrhino/backend.h:17-21) and adds 4 to its offset after every call. */
+int vrb_rng_normal(void* out, int dtype, int64_t count, uint64_t seed, uint64_t offset, vrb_stream stream);
+
 /* CudaBackend::reduce_sum (:4885-4892, reduce_sum_kernel :1790-1806) over the middle axis of x [outer, reduced, inner]:
  * out[o, i] = sum of x[o, r, i] for r = 0, 1, ... in that order, accumulated in F32 and stored in x's dtype (the
  * reference's order, so the same bits).  reduced == 0 gives zeros. */

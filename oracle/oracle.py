@@ -310,6 +310,41 @@ class OracleBackend:
             total = np.expand_dims(total, dim)
         return tensor(total, x.dtype)
 
+    def rng_normal(self, state, shape, dtype: str) -> T:
+        """CudaBackend::rng_normal (:5120-5126, rng_normal_kernel :2225-2231): element i is the first normal of
+        cuRAND's Philox4x32-10 stream (seed, subsequence i, offset).  Restated from the published algorithm
+        (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", 2011: ten rounds of two 32 x 32 -> 64
+        multiplications with the constants below, the key bumped by the Weyl constants between rounds) with cuRAND's
+        layout -- key = the seed's halves, counter = (offset / 4 low, offset / 4 high, subsequence low, subsequence
+        high) -- and its Box-Muller step on the first two outputs x, y: u = x * 2^-32 + 2^-33,
+        v = y * (2 pi * 2^-32) + pi * 2^-32, value = sqrt(-2 ln u) * sin v.  Pinned by the reference's own known answers
+        (primitive_tests.cpp:549: seed 5701, offset 0, eight values to 1e-6); log / sin here are the host's.
+        `state` is any object with seed, offset and algorithm_id; its offset grows by 4."""
+        if state.algorithm_id != "pytorch_compat.v1":
+            raise ValueError("Unsupported RNG algorithm")
+        if dtype not in (F32, BF16):
+            raise ValueError("rng_normal dtype unsupported")
+        if state.offset % 4:
+            raise ValueError("rng_normal: this restatement covers offsets that are multiples of 4 (all the reference produces)")
+        count = int(np.prod(shape, dtype=np.int64)) if len(shape) else 1
+        mask = np.uint64(0xFFFFFFFF)
+        index = np.arange(count, dtype=np.uint64)
+        block = np.uint64(state.offset // 4)
+        c = [np.full(count, block & mask, dtype=np.uint64), np.full(count, block >> np.uint64(32), dtype=np.uint64),
+             index & mask, index >> np.uint64(32)]
+        k0, k1 = int(state.seed) & 0xFFFFFFFF, (int(state.seed) >> 32) & 0xFFFFFFFF
+        for _ in range(10):
+            p0, p1 = np.uint64(0xD2511F53) * c[0], np.uint64(0xCD9E8D57) * c[2]
+            c = [((p1 >> np.uint64(32)) ^ c[1] ^ np.uint64(k0)) & mask, p1 & mask,
+                 ((p0 >> np.uint64(32)) ^ c[3] ^ np.uint64(k1)) & mask, p0 & mask]
+            k0, k1 = (k0 + 0x9E3779B9) & 0xFFFFFFFF, (k1 + 0xBB67AE85) & 0xFFFFFFFF
+        x, y = c[0].astype(np.float32), c[1].astype(np.float32)
+        u = x * np.float32(2.0 ** -32) + np.float32(2.0 ** -33)
+        v = y * np.float32(2.0 ** -32 * 6.283185307179586) + np.float32(2.0 ** -33 * 6.283185307179586)
+        values = (np.sqrt(np.float32(-2.0) * np.log(u)).astype(np.float32) * np.sin(v).astype(np.float32)).astype(np.float32)
+        state.offset += 4
+        return tensor(values.reshape(tuple(shape)), dtype)
+
     def softmax(self, raw: T, axis: int) -> T:
         """CudaBackend::softmax (:4893-4917, softmax_axis_kernel :1808-1829): maximum over the axis, then the sum of
         expf(x - max) accumulated in F32 in increasing index order, then expf(x - max) / sum, stored in x's dtype.

@@ -203,7 +203,7 @@ class RefCuda:
                      "refc_residual_add", "refc_gated_residual", "refc_cfg_combine", "refc_euler_update", "refc_flow_to_x0",
                      "refc_frame_group_norm", "refc_linear", "refc_pixel_norm", "refc_pixel_shuffle", "refc_repeat",
                      "refc_l2_normalize", "refc_permute", "refc_concat", "refc_pad", "refc_sinusoidal", "refc_interpolate_nearest", "refc_reduce_sum",
-                     "refc_softmax", "refc_indexed_gather"):
+                     "refc_softmax", "refc_indexed_gather", "refc_rng_normal"):
             getattr(lib, name).restype = _c.c_int64
         lib.refc_profile_total_ms.restype = _c.c_double
         self.lib = lib
@@ -269,6 +269,9 @@ class RefCuda:
         return self._h(self.lib.refc_pad(self._i(x), len(padding), p, _c.c_float(value), int(bool(replicate))))
     def reduce_sum(self, x, dim, keepdim=False):
         return self._h(self.lib.refc_reduce_sum(self._i(x), _c.c_int64(dim), int(bool(keepdim))))
+    def rng_normal(self, seed, offset, shape, dtype):
+        s, r = self._shape(tuple(int(v) for v in shape))
+        return self._h(self.lib.refc_rng_normal(_c.c_uint64(seed), _c.c_uint64(offset), r, s, int(dtype)))
     def softmax(self, x, axis): return self._h(self.lib.refc_softmax(self._i(x), _c.c_int64(axis)))
     def indexed_gather(self, table, indices):
         import numpy as np

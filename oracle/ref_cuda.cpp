@@ -165,6 +165,15 @@ int64_t refc_interpolate_nearest(int64_t x, int count, const double* factors) {
 int64_t refc_reduce_sum(int64_t x, int64_t dim, int keepdim) {
     return guarded([&] { return keep(g_backend->reduce_sum(at(x), dim, keepdim != 0)); });
 }
+// one call of rng_normal on a fresh RngState{seed, offset}
+int64_t refc_rng_normal(uint64_t seed, uint64_t offset, int rank, const int64_t* shape, int dtype) {
+    return guarded([&] {
+        RngState state{seed, offset, "pytorch_compat.v1"};
+        Tensor made = g_backend->rng_normal(state, std::vector<int64_t>(shape, shape + rank), static_cast<DType>(dtype));
+        require(state.offset == offset + 4, "RNG offset mismatch");
+        return keep(made);
+    });
+}
 int64_t refc_softmax(int64_t x, int64_t axis) { return guarded([&] { return keep(g_backend->softmax(at(x), axis)); }); }
 // indices: host values of `index_bits` (64 or 32) bits each, shape [rank]; handed over as a host tensor, as the callers do
 int64_t refc_indexed_gather(int64_t table, int index_bits, int rank, const int64_t* shape, const void* indices) {

@@ -166,6 +166,11 @@ CASES = [
     {"name": "layout_reduce_sum_f32", "kind": "layout", "dt": "f32", "seed": 42,
      "inputs": {"text": (2, 37, 64), "odd": (3, 5, 7)},
      "steps": [("pooled", "reduce", ["text"], (1, True)), ("last_axis", "reduce", ["text"], (-1, False)), ("odd_middle", "reduce", ["odd"], (1, False))]},
+    {"name": "layout_rng_normal_f32", "kind": "layout", "dt": "f32", "seed": 46, "inputs": {},
+     "steps": [("known_answers", "rng", [], (5701, 0, (8,))), ("latent", "rng", [], (1234567890123, 0, (1, 16, 3, 8, 12))),
+               ("second_call", "rng", [], (5701, 4, (2, 256))), ("later_call", "rng", [], (99, 4000, (5, 7)))]},
+    {"name": "layout_rng_normal_bf16", "kind": "layout", "dt": "bf16", "seed": 47, "inputs": {},
+     "steps": [("known_answers", "rng", [], (5701, 0, (8,))), ("latent", "rng", [], (2 ** 63 + 11, 8, (1, 16, 3, 8, 12)))]},
     {"name": "layout_softmax_bf16", "kind": "layout", "dt": "bf16", "seed": 43,
      "inputs": {"scores": (3, 5, 77), "map": (2, 19, 6, 4), "wide": (2, 1100)},
      "steps": [("last_axis", "softmax", ["scores"], (-1,)), ("classes", "softmax", ["map"], (1,)), ("first_axis", "softmax", ["scores"], (0,)),
@@ -192,12 +197,22 @@ CASES = [
 ]
 
 
-def run_layout(case, values, api, grab):
+class RngState:
+    """struct RngState (native/include/vrhino/backend.h:17-21) for the back ends that take one."""
+
+    def __init__(self, seed, offset):
+        self.seed, self.offset, self.algorithm_id = seed, offset, "pytorch_compat.v1"
+
+
+def run_layout(case, values, api, grab, rng=None):
     """The steps of a layout case -- (output name, operator, operand names, arguments) -- on any of the three
-    back ends; `api` supplies permute / slice / concat / pad / sinusoidal_embedding for that back end's tensors."""
+    back ends; `api` supplies permute / slice / concat / pad / sinusoidal_embedding for that back end's tensors,
+    `rng(seed, offset, shape)` one rng_normal call on a fresh state in the case's dtype."""
     for name, op, operands, args in case["steps"]:
         x = [values[o] for o in operands]
-        if op == "permute":
+        if op == "rng":
+            values[name] = rng(args[0], args[1], tuple(args[2]))
+        elif op == "permute":
             values[name] = api.permute(x[0], list(args))
         elif op == "slice":
             values[name] = api.slice(x[0], *args)
@@ -327,7 +342,8 @@ def run_reference(rc, case):
             pad = staticmethod(rc.pad); sinusoidal_embedding = staticmethod(rc.sinusoidal_embedding)
             interpolate_nearest = staticmethod(rc.interpolate_nearest); reduce_sum = staticmethod(rc.reduce_sum)
             softmax = staticmethod(rc.softmax); indexed_gather = staticmethod(rc.indexed_gather)
-        run_layout(case, dict(h), Api, lambda name, handle: grab(name, handle, (int(rc.lib.refc_numel(ctypes.c_int64(handle))),)))
+        run_layout(case, dict(h), Api, lambda name, handle: grab(name, handle, (int(rc.lib.refc_numel(ctypes.c_int64(handle))),)),
+                   rng=lambda seed, offset, shape: rc.rng_normal(seed, offset, shape, code[case["dt"]]))
     elif k == "depth_to_space":
         b, c, t, h_, w = case["shape"]
         full = (b, c // 2, 2 * t, 2 * h_, 2 * w)
@@ -417,7 +433,8 @@ def run_oracle(orc, case):
         act = be.activation(mod, 0)
         grab("pnorm", normed); grab("pmod", mod); grab("silu", act); grab("cast", be.cast(act, "bf16"))
     elif k == "layout":
-        run_layout(case, dict(ins), be, lambda name, t: grab(name, t.reshape((-1,))))
+        run_layout(case, dict(ins), be, lambda name, t: grab(name, t.reshape((-1,))),
+                   rng=lambda seed, offset, shape: be.rng_normal(RngState(seed, offset), shape, case["dt"]))
     elif k == "depth_to_space":
         grab("shuffle", be.pixel_shuffle_nd(ins["y"], (2, 2, 2)))
         grab("shuffle_122", be.pixel_shuffle_nd(ins["y"], (1, 2, 2)))
@@ -554,7 +571,8 @@ def run_library(be, ops, case, fused=True):
             act = be.activation(mod, ops.SILU)
             grab("pmod", mod); grab("silu", act); grab("cast", be.cast(act, torch.bfloat16))
     elif k == "layout":
-        run_layout(case, dict(ins), be, lambda name, t: grab(name, t.reshape(-1)))
+        run_layout(case, dict(ins), be, lambda name, t: grab(name, t.reshape(-1)),
+                   rng=lambda seed, offset, shape: be.rng_normal(RngState(seed, offset), shape, tdt[case["dt"]]))
     elif k == "depth_to_space":
         shuffled = be.pixel_shuffle_nd(ins["y"], (2, 2, 2))
         grab("shuffle", shuffled)

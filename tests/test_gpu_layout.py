@@ -291,6 +291,39 @@ def test_indexed_gather(orc, gpu, dt):
         be.indexed_gather(table.reshape(2, 6, 16), np.zeros((3, 2), dtype=np.int64))
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_rng_normal(orc, gpu, dt):
+    """The reference's Philox stream: its known answers (primitive_tests.cpp:549), the oracle's restatement (host
+    log / sin: a few F32 ulp), the offset bookkeeping, and the moments of a latent-sized draw."""
+    import torch
+    from vrhino_b200._lib import VrbError
+    from vrhino_b200 import ops as vops
+    be, _ = gpu
+    tdt = torch.bfloat16 if dt == "bf16" else torch.float32
+    state = vops.RngState(5701, 0)
+    got = be.rng_normal(state, (8,), tdt)
+    want = [-1.1955757141, .5111286044, -1.0140079260, -.4857170284, -.2519632876, -1.9857326746, 1.1355758905, .4264008999]
+    assert state.offset == 4
+    assert np.allclose(got.float().cpu().numpy(), want, atol=1e-6 if dt == "f32" else 8e-3)
+    for seed, offset, shape in ((5701, 4, (2, 256)), (2 ** 63 + 11, 4000, (1, 16, 21, 60, 104)), (0, 0, (3,))):
+        mine, theirs = vops.RngState(seed, offset), vops.RngState(seed, offset)
+        got = be.rng_normal(mine, shape, tdt)
+        want = orc.OracleBackend().rng_normal(theirs, shape, dt)
+        assert mine.offset == theirs.offset == offset + 4 and tuple(got.shape) == want.shape
+        diff = np.abs(got.float().cpu().numpy().astype(np.float64) - want.f32().astype(np.float64))
+        bound = 2e-5 + (2.0 ** -7 * np.abs(want.f32().astype(np.float64)) if dt == "bf16" else 0.0)   # + one bf16 ulp of the value
+        assert (diff <= bound).all(), diff.max()
+    latent = be.rng_normal(vops.RngState(7, 0), (1, 16, 21, 60, 104), tdt).float()
+    assert abs(float(latent.mean())) < 5e-3 and abs(float(latent.std()) - 1.0) < 5e-3
+    again = be.rng_normal(vops.RngState(7, 0), (1, 16, 21, 60, 104), tdt).float()
+    assert torch.equal(latent, again)
+    assert not torch.equal(latent, be.rng_normal(vops.RngState(7, 4), (1, 16, 21, 60, 104), tdt).float())
+    with pytest.raises(VrbError, match="Unsupported RNG algorithm"):
+        be.rng_normal(vops.RngState(1, 0, "mt19937"), (4,), tdt)
+    with pytest.raises(VrbError, match="dtype unsupported"):
+        be.rng_normal(vops.RngState(1, 0), (4,), torch.float16)
+
+
 def test_argument_rules(orc, gpu):
     import torch
     from vrhino_b200._lib import VrbError

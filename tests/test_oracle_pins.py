@@ -268,6 +268,23 @@ def test_layout_known_answers(orc, be):
         be.concat([t((1, 2), [1, 2]), t((2, 1), [3, 4])], 1)
 
 
+def test_rng_normal_known_answers(orc, be):
+    """primitive_tests.cpp:549-550: RngState{5701, 0, "pytorch_compat.v1"}, eight values to 1e-6, the offset at 4 afterwards."""
+    class State:
+        seed, offset, algorithm_id = 5701, 0, "pytorch_compat.v1"
+    state = State()
+    got = be.rng_normal(state, (8,), "f32")
+    close(got.data, [-1.1955757141, .5111286044, -1.0140079260, -.4857170284, -.2519632876, -1.9857326746, 1.1355758905, .4264008999], 1e-6)
+    assert state.offset == 4
+    wide = be.rng_normal(state, (2, 256), "bf16")
+    assert wide.shape == (2, 256) and wide.dtype == "bf16" and state.offset == 8
+    values = be.rng_normal(State(), (1 << 16,), "f32").data
+    assert abs(float(values.mean())) < 0.02 and abs(float(values.std()) - 1.0) < 0.02
+    state.algorithm_id = "other"
+    with pytest.raises(ValueError, match="Unsupported RNG algorithm"):
+        be.rng_normal(state, (2,), "f32")
+
+
 def test_clamp_exp_sqrt(orc, be):
     close(be.clamp(orc.tensor([-2, -1, 0, 1, 2]), -0.5, 0.75).data, [-0.5, -0.5, 0, 0.75, 0.75])
     close(be.clamp(orc.tensor([[-3, 0.2], [4, 0.8]]), 0, 1).data, [0, 0.2, 1, 0.8])

@@ -84,6 +84,7 @@ SIGNATURES = {
     "vrb_interpolate_nearest": [_vp, _vp, _i, _i, _vp, _vp, _vp],
     "vrb_reduce_sum": [_vp, _vp, _i, _i64, _i64, _i64, _vp],
     "vrb_softmax": [_vp, _vp, _i, _i64, _i64, _i64, _vp],
+    "vrb_rng_normal": [_vp, _i, _i64, _c.c_uint64, _c.c_uint64, _vp],
     "vrb_indexed_gather": [_vp, _vp, _i, _vp, _i, _i64, _i64, _i64, _i64, _vp],
     "vrb_sinusoidal_embedding": [_vp, _vp, _i, _i64, _i64, _i, _d, _i, _vp],
     "vrb_pixel_norm": [_vp, _i, _vp, _vp, _i, _i, _vp, _i, _i64, _i64, _i64, _f, _vp],

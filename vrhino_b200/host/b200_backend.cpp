@@ -598,6 +598,18 @@ Tensor B200Backend::reduce_sum(const Tensor& raw, int64_t dim, bool keepdim) {
     });
 }
 
+Tensor B200Backend::rng_normal(vrhino::RngState& state, const std::vector<int64_t>& shape, DType dtype) {
+    return guarded([&] {   // VRHINO_PROFILE("rng_normal") (cuda_backend.cu:5122)
+        require(state.algorithm_id == "pytorch_compat.v1", "Unsupported RNG algorithm");
+        require(dtype == DType::F32 || dtype == DType::BF16, "rng_normal dtype unsupported");
+        Tensor out = rt_->allocate_device(shape, dtype);
+        ProfileRegion region(*this, [] { return std::string("rng_normal"); }, bytes_of(out));
+        check(vrb_rng_normal(out.data(), code(dtype), out.numel(), state.seed, state.offset, kLegacyStream));
+        state.offset += 4;
+        return out;
+    });
+}
+
 Tensor B200Backend::softmax(const Tensor& raw, int64_t axis) {
     return guarded([&] {   // VRHINO_PROFILE("softmax") (cuda_backend.cu:4895)
         if (axis < 0) axis += static_cast<int64_t>(raw.ndim());

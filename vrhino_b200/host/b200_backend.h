@@ -72,6 +72,7 @@ public:
     Tensor interpolate_nearest(const Tensor& x, const std::vector<double>& factors) override;   // :5010-5016
     Tensor reduce_sum(const Tensor& x, int64_t dim, bool keepdim = false) override;              // :4885-4892
     Tensor softmax(const Tensor& x, int64_t axis) override;                                      // :4893-4917
+    Tensor rng_normal(vrhino::RngState& state, const std::vector<int64_t>& shape, DType dtype) override; // :5120-5126
     Tensor indexed_gather(const Tensor& table, const Tensor& indices) override;                  // :3981-4055
     // per-axis extents and modes in one pass (replicate axes first, then the constant axes)
     Tensor pad_axes(const Tensor& x, const std::vector<int64_t>& before, const std::vector<int64_t>& after, float value,
@@ -200,7 +201,6 @@ public:
     }
     Tensor max_pool2d(const Tensor& x, const std::vector<int>& k, const std::vector<int>& s, const std::vector<int>& p = {0, 0}) override { return rt_->max_pool2d(x, k, s, p); }
     Tensor interpolate_bilinear_2d(const Tensor& x, int64_t h, int64_t w, bool a) override { return rt_->interpolate_bilinear_2d(x, h, w, a); }
-    Tensor rng_normal(vrhino::RngState& s, const std::vector<int64_t>& shape, DType d) override { return rt_->rng_normal(s, shape, d); }
 
 private:
     DType operand_dtype(const Tensor& t) const;

@@ -69,6 +69,14 @@ def _result(out, shape, dtype, device):
     return out
 
 
+@dataclass
+class RngState:
+    """struct RngState, native/include/vrhino/backend.h:17-21."""
+    seed: int = 0
+    offset: int = 0
+    algorithm_id: str = "pytorch_compat.v1"
+
+
 class HostScalar:
     """A rank-0 host F32 value (scalar_f32 of native/src/tensor_util.cpp:20)."""
 
@@ -370,6 +378,19 @@ class B200Backend:
             del shape[dim]
         out = _result(out, tuple(shape), dtype, x.device)
         call("vrb_reduce_sum", _ptr(x), _ptr(out), _code(dtype), outer, x.shape[dim], inner, _stream())
+        return out
+
+    def rng_normal(self, state, shape, dtype, out=None):
+        """CudaBackend::rng_normal (cuda_backend.cu:5120-5126): element i = the first normal of the Philox4x32-10 stream
+        (state.seed, subsequence i, state.offset); the state's offset grows by 4."""
+        if state.algorithm_id != "pytorch_compat.v1":
+            raise VrbError("Unsupported RNG algorithm")
+        if dtype not in (F32, BF16):
+            raise VrbError("rng_normal dtype unsupported")
+        out = _result(out, tuple(shape), dtype, self.device)
+        call("vrb_rng_normal", _ptr(out), _code(dtype), out.numel(), int(state.seed) & (2 ** 64 - 1), int(state.offset) & (2 ** 64 - 1),
+             _stream())
+        state.offset += 4
         return out
 
     def softmax(self, raw, axis, out=None):
