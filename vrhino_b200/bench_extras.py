@@ -59,7 +59,7 @@ def single_gpu_configs(be, peak, steps=10, warmup=2):
     out = {}
     builders = {
         "wan22_step (config 3: D=5120 block chain, FP8 dequant 5120x13824, CFG + Euler on the F32 latent)":
-            lambda: workloads.Wan22Step(be, tokens=32760).launches(),
+            lambda: workloads.Wan22Step(be, tokens=32760).launches(pair_qk=True),
         "mochi_block (config 4: 44520 tokens x 3072, SwiGLU 8192)": lambda: workloads.MochiBlock(be, tokens=44520).launches(),
         "mochi_block, fewest launches (q+k as one launch, residual update + next pre-norm + tanh(gate) as one)":
             lambda: workloads.MochiBlock(be, tokens=44520).launches(merge_tail=True),

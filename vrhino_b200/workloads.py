@@ -242,7 +242,8 @@ class Wan22Step:
         self.policy = ops.Policy.fp32()
         self.out = {}
 
-    def launches(self) -> List[Launch]:
+    def launches(self, pair_qk: bool = False) -> List[Launch]:
+        """pair_qk: as in WanBlock.launches (q and k, and the cross-attention q and text k, as one launch each)."""
         be, o = self.be, self.out
         n = self.latent.numel()
 
@@ -257,7 +258,7 @@ class Wan22Step:
             Launch("euler_update", euler, n * 12),
             Launch("cfg+euler fused", both, n * 16),
         ]
-        return (self.block.launches() if self.block is not None else []) + extra
+        return (self.block.launches(pair_qk=pair_qk) if self.block is not None else []) + extra
 
 
 class MochiBlock:
