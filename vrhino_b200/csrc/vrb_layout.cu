@@ -504,11 +504,17 @@ __device__ __forceinline__ void transpose_2x2(W row0, W row1, W& even, W& odd) {
 template <typename W, int A_PAIRS>
 __global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const W* __restrict__ in, W* __restrict__ out, const Transpose g) {
     constexpr int TILE_A = 2 * A_PAIRS, TILE_B = 64, B_PAIRS = TILE_B / 2, PITCH = B_PAIRS + 1;   // tile rows: a; columns: pairs of b
+    constexpr int kHeld = (B_PAIRS / 8) * (A_PAIRS / 32) * 2;   // words of an interior tile a thread loads
+    constexpr bool kAhead = sizeof(W) == 4;                     // (64-bit words: twice the registers, and no faster)
     __shared__ W tile[TILE_A * PITCH];
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
-    for (int64_t t = blockIdx.x; t < g.tiles; t += gridDim.x) {
+    struct TileAt {
+        int64_t in_base, out_base, a0, b0;
+        bool interior;
+    };
+    auto locate = [&](int64_t t) {
         // fewer than 2^31 tiles (the launcher checks): 32-bit divisions
         uint32_t remaining = static_cast<uint32_t>(t);
         const uint32_t tiles_b = static_cast<uint32_t>(g.tiles_b), tiles_a = static_cast<uint32_t>(g.tiles_a);
@@ -518,31 +524,53 @@ __global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const W* __re
         quotient = remaining / tiles_a;
         const int64_t tile_a = remaining - quotient * tiles_a;
         remaining = quotient;
-        int64_t in_base = 0, out_base = 0;
+        TileAt at{0, 0, tile_a * TILE_A, tile_b * TILE_B, false};
         for (int d = g.batch_rank - 1; d >= 0; --d) {
             const uint32_t extent = static_cast<uint32_t>(g.batch_extent[d]);
             quotient = remaining / extent;
             const int64_t coordinate = remaining - quotient * extent;
             remaining = quotient;
-            in_base += coordinate * g.batch_in_stride[d];
-            out_base += coordinate * g.batch_out_stride[d];
+            at.in_base += coordinate * g.batch_in_stride[d];
+            at.out_base += coordinate * g.batch_out_stride[d];
         }
-        const int64_t a0 = tile_a * TILE_A, b0 = tile_b * TILE_B;
-        in_base += a0 + b0 * g.in_stride_b;          // elements; even
-        out_base += a0 * g.out_stride_a + b0;
-        const bool interior = a0 + TILE_A <= g.extent_a && b0 + TILE_B <= g.extent_b;
-        // load: lane (+ 32) = pair of a, warp + 8 i = pair of b
+        at.in_base += at.a0 + at.b0 * g.in_stride_b;          // elements; even
+        at.out_base += at.a0 * g.out_stride_a + at.b0;
+        at.interior = at.a0 + TILE_A <= g.extent_a && at.b0 + TILE_B <= g.extent_b;
+        return at;
+    };
+    // An interior tile's words are fetched into registers one tile ahead (32-bit words): the loads of the next tile
+    // are in flight while this one is written out.  lane (+ 32) = pair of a, warp + 8 i = pair of b; no bounds tests, the row
+    // pointers advanced instead of recomputed.
+    W held[kHeld];
+    auto fetch = [&](const TileAt& at) {
+        const int64_t row_step = g.in_stride_b >> 1;                                   // one row of b, in pairs
+        const W* rows = in + ((at.in_base + static_cast<int64_t>(2 * warp) * g.in_stride_b) >> 1) + lane;
+        int n = 0;
+#pragma unroll
+        for (int i = 0; i < B_PAIRS / 8; ++i, rows += 16 * row_step) {
+#pragma unroll
+            for (int h = 0; h < A_PAIRS / 32; ++h) {
+                held[n++] = rows[32 * h];
+                held[n++] = rows[32 * h + row_step];
+            }
+        }
+    };
+    if (static_cast<int64_t>(blockIdx.x) >= g.tiles) return;
+    TileAt here = locate(blockIdx.x);
+    if (kAhead && here.interior) fetch(here);
+    for (int64_t t = blockIdx.x; t < g.tiles; t += gridDim.x) {
+        const int64_t in_base = here.in_base, out_base = here.out_base, a0 = here.a0, b0 = here.b0;
+        const bool interior = here.interior;
         if (interior) {
-            // no bounds tests, and the row pointers are advanced instead of recomputed
-            const int64_t row_step = g.in_stride_b >> 1;                                   // one row of b, in pairs
-            const W* rows = in + ((in_base + static_cast<int64_t>(2 * warp) * g.in_stride_b) >> 1) + lane;
+            if constexpr (!kAhead) fetch(here);
             W* even_at = tile + lane * PITCH + warp;
+            int n = 0;
 #pragma unroll
-            for (int i = 0; i < B_PAIRS / 8; ++i, rows += 16 * row_step, even_at += 8) {
+            for (int i = 0; i < B_PAIRS / 8; ++i, even_at += 8) {
 #pragma unroll
-                for (int h = 0; h < A_PAIRS / 32; ++h) {
+                for (int h = 0; h < A_PAIRS / 32; ++h, n += 2) {
                     W even, odd;
-                    transpose_2x2<W>(rows[32 * h], rows[32 * h + row_step], even, odd);
+                    transpose_2x2<W>(held[n], held[n + 1], even, odd);
                     even_at[32 * h * PITCH] = even;
                     even_at[(A_PAIRS + 32 * h) * PITCH] = odd;
                 }
@@ -567,6 +595,12 @@ __global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const W* __re
             }
         }
         __syncthreads();
+        // the next tile: located now, and, if it is an interior one, requested before this one is written out
+        TileAt next = here;
+        if (t + gridDim.x < g.tiles) {
+            next = locate(t + gridDim.x);
+            if (kAhead && next.interior) fetch(next);
+        }
         // store: 16 threads cover the 32 pairs of one output row, two pairs each; the two half-warps take adjacent
         // tile rows (an odd pitch apart: no bank conflict)
         const int word = 2 * (threadIdx.x % 16);
@@ -602,6 +636,7 @@ __global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const W* __re
         }
         }
         __syncthreads();
+        here = next;
     }
 }
 
