@@ -366,6 +366,25 @@ def test_raw_entry_point_checks(gpu, cuda_lib):
     ext = (I * 1)(3)
     assert cuda_lib.vrb_concat(ptrs, ext, 1, P(out.data_ptr()), 0, 2, shape, 0, None) != 0
     assert b"concat shape mismatch" in cuda_lib.vrb_last_error()
+    U = ctypes.c_uint64
+    assert cuda_lib.vrb_softmax(P(x.data_ptr()), P(out.data_ptr()), 5, I(4), I(4), I(1), None) != 0          # a dtype that is not a float type
+    assert cuda_lib.vrb_softmax(None, P(out.data_ptr()), 0, I(4), I(4), I(1), None) != 0
+    assert cuda_lib.vrb_softmax(None, None, 0, I(0), I(4), I(1), None) == 0                                  # nothing to do
+    indices = torch.zeros(2, dtype=torch.int64, device="cuda")
+    assert cuda_lib.vrb_indexed_gather(P(x.data_ptr()), P(indices.data_ptr()), 0, P(out.data_ptr()), 0, I(0), I(4), I(4), I(2), None) != 0
+    assert b"int64/int32" in cuda_lib.vrb_last_error()
+    assert cuda_lib.vrb_indexed_gather(P(x.data_ptr()), None, 3, P(out.data_ptr()), 0, I(0), I(4), I(4), I(2), None) != 0
+    # an index out of range (the wrappers refuse it earlier) leaves its row unwritten instead of reading outside the table
+    indices[1] = 7
+    out.fill_(-1.0)
+    table = torch.arange(16, dtype=torch.float32, device="cuda").reshape(4, 4) + 1.0
+    assert cuda_lib.vrb_indexed_gather(P(table.data_ptr()), P(indices.data_ptr()), 3, P(out.data_ptr()), 0, I(0), I(4), I(4), I(2), None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out[0], table[0]) and bool((out[1:] == -1.0).all())
+    assert cuda_lib.vrb_rng_normal(P(out.data_ptr()), 5, I(16), U(1), U(0), None) != 0
+    assert b"rng_normal dtype unsupported" in cuda_lib.vrb_last_error()
+    assert cuda_lib.vrb_rng_normal(None, 0, I(16), U(1), U(0), None) != 0
+    assert cuda_lib.vrb_rng_normal(None, 0, I(0), U(1), U(0), None) == 0
 
 
 @pytest.mark.parametrize("dt", ["bf16", "f32"])
