@@ -3,10 +3,14 @@
 // The reference's operators accept host tensors and upload them on demand (copy_to_device,
 // native/src/backend/cuda/cuda_backend.cu:3195) and results are fetched with copy_to_host.
 // For a bandwidth-bound operator that round trip is all PCIe time, so it is pipelined: the rows
-// are cut into blocks of a few MiB and dealt round-robin onto kSlots streams; each stream runs
-// upload -> kernel -> download for its blocks in order, so at any moment one block is uploading,
-// one is computing and one is downloading, and both PCIe directions stay busy.  Operands that
-// are shared by all rows (modulation vectors, norm weights) are uploaded once.
+// are cut into blocks of a few MiB that pass through kSlots staging buffers.  One stream carries
+// every upload, one every kernel, one every download, and events hand a block from one to the
+// next (uploaded -> computed -> downloaded, the last one freeing the slot for the upload three
+// blocks later): each copy engine always has its next copy queued behind the current one, so
+// both PCIe directions stay busy.  (With a stream per slot -- upload, kernel and download of a
+// block in one stream -- every upload sat behind the previous download of its stream; this order
+// measured 2-5 % more upload bandwidth per call.)
+// Operands that are shared by all rows (modulation vectors, norm weights) are uploaded once.
 //
 // Device staging buffers and streams are owned by the library, one set per device (the device that is
 // current when a call is made), grown on demand and freed by vrb_host_release(); these are the only
@@ -23,18 +27,19 @@
 namespace vrb {
 namespace {
 
-constexpr int kSlots = 3;                          // 2, 4 and 6 slots measured no faster
-constexpr size_t kBlockBytes = size_t{16} << 20;   // per-row-stream bytes per full block, about (8 and 32 MiB: the same)
+constexpr int kSlots = 3;                          // 4 and 6 slots measured no faster
+constexpr size_t kBlockBytes = size_t{16} << 20;   // per-row-stream bytes per full block, about (4 and 8 MiB: 4-12 % slower; 32 MiB: the same)
 
 struct Arena {
     void* base = nullptr;
     size_t bytes = 0;
 };
 
+constexpr int kStreams = 3;   // upload, compute, download
 struct HostPipe {
     std::mutex mutex;
-    cudaStream_t streams[kSlots] = {};
-    cudaEvent_t shared_ready = nullptr;
+    cudaStream_t streams[kStreams] = {};
+    cudaEvent_t uploaded[kSlots] = {}, computed[kSlots] = {}, downloaded[kSlots] = {};
     Arena slots[kSlots];
     Arena shared;
 };
@@ -73,7 +78,10 @@ template <typename Launch>
 int enqueue_pipeline(HostPipe& pipe, std::vector<Operand>& ops, int64_t rows, Launch launch) {
     for (auto& s : pipe.streams)
         if (!s) VRB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "stream create");
-    if (!pipe.shared_ready) VRB_CUDA(cudaEventCreateWithFlags(&pipe.shared_ready, cudaEventDisableTiming), "event create");
+    for (cudaEvent_t* events : {pipe.uploaded, pipe.computed, pipe.downloaded})
+        for (int k = 0; k < kSlots; ++k)
+            if (!events[k]) VRB_CUDA(cudaEventCreateWithFlags(&events[k], cudaEventDisableTiming), "event create");
+    cudaStream_t up = pipe.streams[0], compute = pipe.streams[1], down = pipe.streams[2];
 
     size_t widest = 1, shared_bytes = 0;
     for (const auto& o : ops) {
@@ -88,17 +96,15 @@ int enqueue_pipeline(HostPipe& pipe, std::vector<Operand>& ops, int64_t rows, La
     for (auto& a : pipe.slots) if (int rc = ensure(a, slot_bytes)) return rc;
     if (int rc = ensure(pipe.shared, shared_bytes ? shared_bytes : 256)) return rc;
 
-    // shared operands: once, on stream 0; the other streams wait for them
+    // shared operands: once, at the head of the upload stream (every block's kernel waits for an upload behind them)
     std::vector<void*> dev(ops.size(), nullptr);
     size_t off = 0;
     for (size_t k = 0; k < ops.size(); ++k) {
         if (ops[k].row_bytes || !ops[k].host_in) continue;
         dev[k] = static_cast<char*>(pipe.shared.base) + off;
         off += align256(ops[k].total_bytes);
-        VRB_CUDA(cudaMemcpyAsync(dev[k], ops[k].host_in, ops[k].total_bytes, cudaMemcpyHostToDevice, pipe.streams[0]), "upload shared operand");
+        VRB_CUDA(cudaMemcpyAsync(dev[k], ops[k].host_in, ops[k].total_bytes, cudaMemcpyHostToDevice, up), "upload shared operand");
     }
-    VRB_CUDA(cudaEventRecord(pipe.shared_ready, pipe.streams[0]), "event record");
-    for (int s = 1; s < kSlots; ++s) VRB_CUDA(cudaStreamWaitEvent(pipe.streams[s], pipe.shared_ready, 0), "event wait");
 
     // Block sizes ramp up at the start and down at the end (1/8, 1/4, 1/2 of a full block): the call
     // returns only when everything is back on the host, so the first upload and the last download
@@ -120,8 +126,9 @@ int enqueue_pipeline(HostPipe& pipe, std::vector<Operand>& ops, int64_t rows, La
     int64_t r0 = 0;
     for (size_t b = 0; b < sizes.size(); r0 += sizes[b], ++b) {
         const int slot = static_cast<int>(b % kSlots);
-        cudaStream_t st = pipe.streams[slot];
         const int64_t n = sizes[b];
+        // the slot is free once the block that used it last has been downloaded
+        if (b >= static_cast<size_t>(kSlots)) VRB_CUDA(cudaStreamWaitEvent(up, pipe.downloaded[slot], 0), "event wait");
         size_t so = 0;
         for (size_t k = 0; k < ops.size(); ++k) {
             if (!ops[k].row_bytes) continue;
@@ -129,13 +136,18 @@ int enqueue_pipeline(HostPipe& pipe, std::vector<Operand>& ops, int64_t rows, La
             so += align256(ops[k].row_bytes * static_cast<size_t>(block_rows));
             if (ops[k].host_in)
                 VRB_CUDA(cudaMemcpyAsync(dev[k], static_cast<const char*>(ops[k].host_in) + static_cast<size_t>(r0) * ops[k].row_bytes,
-                                         static_cast<size_t>(n) * ops[k].row_bytes, cudaMemcpyHostToDevice, st), "upload rows");
+                                         static_cast<size_t>(n) * ops[k].row_bytes, cudaMemcpyHostToDevice, up), "upload rows");
         }
-        if (int rc = launch(n, dev.data(), st)) return rc;
+        VRB_CUDA(cudaEventRecord(pipe.uploaded[slot], up), "event record");
+        VRB_CUDA(cudaStreamWaitEvent(compute, pipe.uploaded[slot], 0), "event wait");
+        if (int rc = launch(n, dev.data(), compute)) return rc;
+        VRB_CUDA(cudaEventRecord(pipe.computed[slot], compute), "event record");
+        VRB_CUDA(cudaStreamWaitEvent(down, pipe.computed[slot], 0), "event wait");
         for (size_t k = 0; k < ops.size(); ++k)
             if (ops[k].row_bytes && ops[k].host_out)
                 VRB_CUDA(cudaMemcpyAsync(static_cast<char*>(ops[k].host_out) + static_cast<size_t>(r0) * ops[k].row_bytes, dev[k],
-                                         static_cast<size_t>(n) * ops[k].row_bytes, cudaMemcpyDeviceToHost, st), "download rows");
+                                         static_cast<size_t>(n) * ops[k].row_bytes, cudaMemcpyDeviceToHost, down), "download rows");
+        VRB_CUDA(cudaEventRecord(pipe.downloaded[slot], down), "event record");
     }
     return VRB_OK;
 }
@@ -244,5 +256,7 @@ extern "C" void vrb_host_release(void) {
     if (pipe.shared.base) cudaFree(pipe.shared.base);
     pipe.shared = Arena{};
     for (auto& s : pipe.streams) { if (s) cudaStreamDestroy(s); s = nullptr; }
-    if (pipe.shared_ready) { cudaEventDestroy(pipe.shared_ready); pipe.shared_ready = nullptr; }
+    for (cudaEvent_t* events : {pipe.uploaded, pipe.computed, pipe.downloaded})
+        for (int k = 0; k < kSlots; ++k)
+            if (events[k]) { cudaEventDestroy(events[k]); events[k] = nullptr; }
 }
