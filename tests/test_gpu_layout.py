@@ -98,6 +98,32 @@ def test_row_copies_at_every_pair_of_phases(orc, gpu, dt):
 
 
 @pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_inner_runs_of_whole_2_kb_blocks(orc, gpu, dt):
+    """Padded walks whose innermost axis is a contiguous run of a multiple of 2 KB on both sides take the block form (a
+    warp per 2 KB block): pads of outer axes in both modes -- and, on the unit walk, permutes that keep the inner axes,
+    slices and concats of outer axes -- with row counts around and beyond one pass of the grid."""
+    import torch
+    be, _ = gpu
+    obe = orc.OracleBackend()
+    inner = 1024 if dt == "bf16" else 512                       # 2 KB
+    for shape in ((2, 5, 3, inner), (3, 7, 2 * inner), (1, 37, 11, 3 * inner)):
+        x, ox = _pair(orc, torch, shape, dt, 51)
+        rank = len(shape)
+        for padding, replicate in (((0, 0) * (rank - 2) + (2, 1), True), ((0, 0) * (rank - 2) + (2, 1), False),
+                                   ((0, 0) * (rank - 2) + (0, 3, 1, 0), False), ((0, 0) * (rank - 2) + (1, 1, 1, 1), True)):
+            got, want = be.pad(x, list(padding), 0.25, replicate), obe.pad(ox, list(padding), 0.25, replicate)
+            assert np.array_equal(_bits(torch, got), _orc_bits(want)), (shape, padding, replicate)
+        dims = (1, 0) + tuple(range(2, rank))
+        assert np.array_equal(_bits(torch, be.permute(x, dims)), _orc_bits(obe.permute(ox, dims))), shape
+        assert np.array_equal(_bits(torch, be.slice(x, 1, 1, shape[1] - 1)), _orc_bits(obe.slice(ox, 1, 1, shape[1] - 1))), shape
+        assert np.array_equal(_bits(torch, be.concat([x, x, x], 1)), _orc_bits(obe.concat([ox, ox, ox], 1))), shape
+    # more blocks than one pass of the grid takes: [40, 257, 4 KB] -> 20560 blocks
+    x, ox = _pair(orc, torch, (40, 257, 2 * inner), dt, 52)
+    assert np.array_equal(_bits(torch, be.pad(x, [0, 0, 1, 2], 0.0, True)), _orc_bits(obe.pad(ox, [0, 0, 1, 2], 0.0, True)))
+    assert np.array_equal(_bits(torch, be.permute(x, (1, 0, 2))), _orc_bits(obe.permute(ox, (1, 0, 2))))
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
 def test_split_and_concat(orc, gpu, dt):
     import torch
     be, _ = gpu
