@@ -576,7 +576,7 @@ template <typename W, int A_PAIRS>
 __global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const W* __restrict__ in, W* __restrict__ out, const Transpose g) {
     constexpr int TILE_A = 2 * A_PAIRS, TILE_B = 64, B_PAIRS = TILE_B / 2, PITCH = B_PAIRS + 1;   // tile rows: a; columns: pairs of b
     constexpr int kHeld = (B_PAIRS / 8) * (A_PAIRS / 32) * 2;   // words of an interior tile a thread loads
-    constexpr bool kAhead = sizeof(W) == 4;                     // (64-bit words: twice the registers, and no faster)
+    constexpr bool kAhead = sizeof(W) == 4 || A_PAIRS == 32;    // (64-bit words in 128-row tiles: twice the registers, and no faster)
     __shared__ W tile[TILE_A * PITCH];
     pdl_launch_dependents();
     pdl_wait();
@@ -609,8 +609,8 @@ __global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const W* __re
         at.interior = at.a0 + TILE_A <= g.extent_a && at.b0 + TILE_B <= g.extent_b;
         return at;
     };
-    // An interior tile's words are fetched into registers one tile ahead (32-bit words): the loads of the next tile
-    // are in flight while this one is written out.  lane (+ 32) = pair of a, warp + 8 i = pair of b; no bounds tests, the row
+    // An interior tile's words are fetched into registers one tile ahead (32-bit words, and 64-bit words in the
+    // 64-row tiles): the loads of the next tile are in flight while this one is written out.  lane (+ 32) = pair of a, warp + 8 i = pair of b; no bounds tests, the row
     // pointers advanced instead of recomputed.
     W held[kHeld];
     auto fetch = [&](const TileAt& at) {
@@ -866,7 +866,7 @@ int run_plan(const void* in, void* out, int dtype, const Plan& raw, float pad_va
             bool pairs = g.extent_a % 2 == 0 && g.extent_b % 2 == 0 && g.in_stride_b % 2 == 0 && g.out_stride_a % 2 == 0 &&
                          reinterpret_cast<uintptr_t>(source) % (2 * element) == 0 && reinterpret_cast<uintptr_t>(destination) % (4 * element) == 0;
             for (int d = 0; d < g.batch_rank && pairs; ++d) pairs = g.batch_in_stride[d] % 2 == 0 && g.batch_out_stride[d] % 2 == 0;
-            const int wide_a = pairs && g.extent_a >= 128 ? 1 : 0;   // 128 x 64 tiles: twice the contiguous bytes per input row visit
+            const int wide_a = pairs && g.extent_a >= 128 && element == 2 ? 1 : 0;   // bf16: 128 x 64 tiles, 256 contiguous bytes per input row visit (F32 has them with 64 rows)
             const int tile = pairs || element == 2 ? 64 : 32;
             g.tiles_a = (g.extent_a + (tile << wide_a) - 1) / (tile << wide_a); g.tiles_b = (g.extent_b + tile - 1) / tile;
             g.tiles = g.tiles_a * g.tiles_b;
