@@ -576,7 +576,7 @@ template <typename W, int A_PAIRS>
 __global__ void __launch_bounds__(kThreads) transpose_pairs_kernel(const W* __restrict__ in, W* __restrict__ out, const Transpose g) {
     constexpr int TILE_A = 2 * A_PAIRS, TILE_B = 64, B_PAIRS = TILE_B / 2, PITCH = B_PAIRS + 1;   // tile rows: a; columns: pairs of b
     constexpr int kHeld = (B_PAIRS / 8) * (A_PAIRS / 32) * 2;   // words of an interior tile a thread loads
-    constexpr bool kAhead = sizeof(W) == 4 || A_PAIRS == 32;    // (64-bit words in 128-row tiles: twice the registers, and no faster)
+    constexpr bool kAhead = true;                               // (64-bit words in 128-row tiles, twice the registers, were no faster: F32 uses 64-row tiles)
     __shared__ W tile[TILE_A * PITCH];
     pdl_launch_dependents();
     pdl_wait();
@@ -878,9 +878,6 @@ int run_plan(const void* in, void* out, int dtype, const Plan& raw, float pad_va
             else if (pairs && element == 2)
                 launch_overlapped(transpose_pairs_kernel<uint32_t, 32>, dim3(grid), dim3(kThreads), 0, stream,
                                   reinterpret_cast<const uint32_t*>(source), reinterpret_cast<uint32_t*>(destination), g);
-            else if (pairs && wide_a)
-                launch_overlapped(transpose_pairs_kernel<unsigned long long, 64>, dim3(grid), dim3(kThreads), 0, stream,
-                                  reinterpret_cast<const unsigned long long*>(source), reinterpret_cast<unsigned long long*>(destination), g);
             else if (pairs)
                 launch_overlapped(transpose_pairs_kernel<unsigned long long, 32>, dim3(grid), dim3(kThreads), 0, stream,
                                   reinterpret_cast<const unsigned long long*>(source), reinterpret_cast<unsigned long long*>(destination), g);
