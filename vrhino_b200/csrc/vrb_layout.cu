@@ -306,6 +306,11 @@ __global__ void __launch_bounds__(kThreads) walk_rows_kernel(const E* __restrict
         const unsigned long long my_from = reinterpret_cast<unsigned long long>(my_src);
         // (the copied part's first byte on the output side; bit 0 is free in a 2-byte aligned address: the row has a source)
         const unsigned long long my_to = (reinterpret_cast<unsigned long long>(my_dst) + before_bytes) | (my_valid ? 1ull : 0ull);
+        // what the chunk pass needs of a row, worked out once by the lane that located it: where the first whole
+        // chunk starts on either side, and how many there are (none for a row without a source)
+        const int my_head = static_cast<int>((16 - (my_to & 14)) & 15);
+        const int my_full = my_valid && in_bytes >= my_head + 16 ? (in_bytes - my_head) >> 4 : 0;
+        const unsigned long long my_chunks_from = my_from + my_head, my_chunks_to = (my_to & ~1ull) + my_head;
 
         if (body_slots != 0) {
             const uint32_t items = count * body_slots;
@@ -319,16 +324,15 @@ __global__ void __launch_bounds__(kThreads) walk_rows_kernel(const E* __restrict
                 for (int u = 0; u < kInFlight; ++u) {
                     const bool active = base + 32 * u + lane < items;
                     const uint32_t owner = active ? row : 0;
-                    const unsigned long long from = __shfl_sync(0xffffffffu, my_from, owner);
-                    const unsigned long long to = __shfl_sync(0xffffffffu, my_to, owner);
-                    const int head = static_cast<int>((16 - (to & 14)) & 15);
-                    const int full = in_bytes >= head + 16 ? (in_bytes - head) >> 4 : 0;
+                    const unsigned long long from = __shfl_sync(0xffffffffu, my_chunks_from, owner);
+                    const unsigned long long to = __shfl_sync(0xffffffffu, my_chunks_to, owner);
+                    const int full = __shfl_sync(0xffffffffu, my_full, owner);
                     a[u] = b[u] = make_uint4(0, 0, 0, 0);
                     phase[u] = 0;
                     target[u] = nullptr;
-                    if (active && (to & 1) != 0 && static_cast<int>(slot) < full) {
-                        const int at = head + 16 * static_cast<int>(slot);
-                        target[u] = reinterpret_cast<uint4*>((to & ~1ull) + at);
+                    if (active && static_cast<int>(slot) < full) {
+                        const unsigned int at = 16u * slot;
+                        target[u] = reinterpret_cast<uint4*>(to + at);
                         const unsigned long long source = from + at;
                         phase[u] = static_cast<int>(source & 15);
                         const uint4* const blocks = reinterpret_cast<const uint4*>(source - phase[u]);
